@@ -1,0 +1,495 @@
+#include "engine.h"
+
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <fstream>
+#include <stdexcept>
+
+#include "common/clock.h"
+#include "common/env.h"
+#include "common/hash.h"
+#include "common/json.h"
+#include "common/log.h"
+#include "mem/shm_device.h"
+
+namespace pccl {
+
+namespace {
+constexpr uint64_t kMiB = 1ull << 20;
+uint64_t alignUp(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+std::string readHostId() {
+  std::string v = LaunchEnvironments::getEnv("PCCL_HOST_ID");
+  if (!v.empty()) return v;
+  std::ifstream f("/proc/sys/kernel/random/boot_id");
+  std::string id;
+  if (f && std::getline(f, id) && !id.empty()) return id;
+  char name[256] = {0};
+  ::gethostname(name, sizeof(name) - 1);
+  return name;
+}
+
+void cudaCheck(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string("engine: ") + what + ": " + cudaGetErrorString(e));
+}
+}  // namespace
+
+Engine::Engine(int rank, int world) : rank_(rank), world_(world) {
+  if (world < 1 || rank < 0 || rank >= world) throw std::runtime_error("Engine: need 0 <= rank < world");
+  if (world > kMaxRanks) throw std::runtime_error("Engine: world size above the compiled maximum");
+  registerBuiltinOptions();
+}
+
+Engine::~Engine() {
+  try {
+    exitCluster();
+  } catch (...) {
+  }
+  for (auto& kv : ops_)
+    for (auto& dc : kv.second.device_cache) {
+      if (dc.second.instrs) cudaFree(dc.second.instrs);
+      if (dc.second.starts) cudaFree(dc.second.starts);
+    }
+  dropPeers();
+  if (tcp_) tcp_->shutdown();
+  if (heap_) {
+    auto dev = getDev(device_);
+    if (dev) {
+      try {
+        if (device_ == "cuda") static_cast<CudaDevice*>(dev.get())->multicastRelease();
+        dev->deallocate(heap_);
+      } catch (...) {
+      }
+    }
+    heap_ = nullptr;
+  }
+}
+
+void Engine::buildLayout(uint64_t heap_bytes) {
+  HeapLayout& L = layout_;
+  L.workspace_bytes = static_cast<uint64_t>(LaunchEnvironments::getInt("PCCL_WORKSPACE_MB", 256)) * kMiB;
+  L.lanes = static_cast<int>(LaunchEnvironments::getInt("PCCL_LANES", 2));
+  if (L.lanes < 1) L.lanes = 1;
+  L.signal_off = L.workspace_bytes;
+  L.num_signals = 65536;
+  L.flag_off = L.signal_off + L.num_signals * 8;
+  L.flag_bytes = alignUp(8ull * kMaxBlocksPerColl * kMaxRanks * 8, 256 * 1024);
+  L.status_off = L.flag_off + L.flag_bytes;
+  L.status_bytes = 4096;
+  L.user_off = alignUp(L.status_off + L.status_bytes, 2 * kMiB);
+  L.total = alignUp(std::max(heap_bytes, L.user_off), 2 * kMiB);
+  user_top_ = L.user_off;
+}
+
+void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
+  if (initialized_) return;
+  registerCpuDevice();
+  registerCudaDevice();
+  device_ = device;
+  if (device_ == "auto") device_ = getDev("cuda")->allocatorAvailable() ? "cuda" : "cpu";
+  auto dev = getDev(device_);
+  if (!dev) throw std::runtime_error("initEngine: unknown device kind '" + device_ + "'");
+  if (!dev->allocatorAvailable()) throw std::runtime_error("initEngine: device '" + device_ + "' is not usable here");
+  timeout_ms_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_WAIT_TIMEOUT_MS", 30000));
+  spin_limit_ = static_cast<uint64_t>(LaunchEnvironments::getInt("PCCL_SPIN_LIMIT", static_cast<int64_t>(kDefaultSpinLimit)));
+  bounds_check_ = LaunchEnvironments::getBool("PCCL_BOUNDS_CHECK", true);
+  max_width_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_MAX_SMS", 32));
+  host_id_ = readHostId();
+  buildLayout(heap_bytes);
+  heap_ = static_cast<char*>(dev->allocateIpcBuffer(layout_.total, &heap_handle_));
+  uint64_t ctl = layout_.user_off - layout_.signal_off;
+  if (device_ == "cuda") {
+    cudaCheck(cudaMemset(heap_ + layout_.signal_off, 0, ctl), "clearing the signal area");
+    cudaCheck(cudaDeviceSynchronize(), "synchronize after heap set-up");
+  } else {
+    std::memset(heap_ + layout_.signal_off, 0, ctl);
+  }
+  peer_heaps_.assign(world_, nullptr);
+  peer_heaps_[rank_] = heap_;
+  lane_epochs_.assign(8, 0);
+
+  configs_["host_id"] = host_id_;
+  configs_["device"] = device_;
+  configs_["pid"] = std::to_string(::getpid());
+  configs_["heap.bytes"] = std::to_string(layout_.total);
+  configs_["ipc." + device_ + ".handle"] = heap_handle_;
+  if (device_ == "cpu") {
+    tcp_ = std::make_unique<TcpTransport>();
+    std::string host = LaunchEnvironments::getStr("PCCL_TCP_HOST", "127.0.0.1");
+    tcp_->setAdvertisedHost(host);
+    configs_["remote.tcp.endpoint"] = tcp_->activate();
+    tcp_key_ = tcp_->regBuffer(heap_, layout_.total);
+    tcp_->setSignals(reinterpret_cast<std::atomic<uint64_t>*>(heap_ + layout_.signal_off),
+                     static_cast<uint32_t>(layout_.num_signals));
+    configs_["remote.tcp.buffer.cpu.key"] = std::to_string(tcp_key_);
+  }
+  std::string why;
+  configs_["remote.verbs.available"] = verbsAvailable(&why) ? "1" : "0";
+  configs_["remote.verbs.note"] = why;
+  initialized_ = true;
+  PCCL_LOG_INFO("engine: rank %d/%d on %s, heap %llu MiB", rank_, world_, device_.c_str(),
+                static_cast<unsigned long long>(layout_.total / kMiB));
+}
+
+std::string Engine::exportEndpoint() {
+  if (!initialized_) throw std::runtime_error("exportEndpoint: call initEngine first");
+  NodeMeta m;
+  m.rank_ = rank_;
+  m.endpoint_configs_ = configs_;
+  return m.serialize();
+}
+
+void Engine::dropPeers() {
+  auto dev = getDev(device_);
+  for (int r = 0; r < static_cast<int>(peer_heaps_.size()); ++r) {
+    if (r == rank_ || !peer_heaps_[r]) continue;
+    try {
+      if (dev) dev->unmapBuffer(peer_heaps_[r]);
+    } catch (...) {
+    }
+    peer_heaps_[r] = nullptr;
+  }
+  if (tcp_)
+    for (int r = 0; r < world_; ++r) tcp_->disconnect(r);
+}
+
+void Engine::setupPeers(const std::map<int, NodeMeta>& nodes) {
+  auto dev = getDev(device_);
+  std::string forced = LaunchEnvironments::getEnv("PCCL_TRANSPORT");
+  for (auto& kv : nodes) {
+    int r = kv.first;
+    if (r == rank_ || r < 0 || r >= world_) continue;
+    const auto& cfg = kv.second.endpoint_configs_;
+    auto get = [&](const std::string& k) {
+      auto it = cfg.find(k);
+      return it == cfg.end() ? std::string() : it->second;
+    };
+    if (get("device") != device_) throw std::runtime_error("setupPeers: rank " + std::to_string(r) + " runs on a different device kind");
+    bool same_host = get("host_id") == host_id_;
+    bool use_tcp = device_ == "cpu" && (forced == "tcp" || !same_host);
+    if (!use_tcp) {
+      if (!same_host) throw std::runtime_error("setupPeers: CUDA ranks on different hosts need a network transport that this build lacks");
+      if (!peer_heaps_[r]) peer_heaps_[r] = static_cast<char*>(dev->mapBuffer(get("ipc." + device_ + ".handle")));
+    } else {
+      tcp_->regRemoteHandle(r, get("remote.tcp.endpoint"));
+      tcp_->connect(r);
+    }
+  }
+}
+
+void Engine::importEndpoints(const std::vector<std::string>& docs) {
+  if (!initialized_) throw std::runtime_error("importEndpoints: call initEngine first");
+  std::map<int, NodeMeta> nodes;
+  for (auto& d : docs) {
+    NodeMeta m;
+    if (!NodeMeta::deserialize(d, &m)) throw std::runtime_error("importEndpoints: unreadable endpoint document");
+    nodes[m.rank_] = m;
+  }
+  setupPeers(nodes);
+}
+
+void Engine::joinCluster(const std::string& master_endpoint, int timeout_ms) {
+  if (!initialized_) throw std::runtime_error("joinCluster: call initEngine first");
+  cluster_ = std::make_unique<ClusterManager>(rank_, world_, configs_);
+  if (!cluster_->initializeDaemonServer(master_endpoint)) throw std::runtime_error("joinCluster: control plane did not start");
+  if (!cluster_->waitForWorld(world_, timeout_ms)) {
+    size_t have = cluster_->nodes().size();
+    throw std::runtime_error("joinCluster: only " + std::to_string(have) + " of " + std::to_string(world_) + " ranks joined in time");
+  }
+  setupPeers(cluster_->nodes());
+}
+
+void Engine::exitCluster() {
+  if (cluster_) {
+    cluster_->killDaemonServer();
+    cluster_.reset();
+  }
+}
+
+std::vector<int> Engine::aliveRanks() {
+  if (!cluster_) {
+    std::vector<int> all;
+    for (int r = 0; r < world_; ++r) all.push_back(r);
+    return all;
+  }
+  return cluster_->aliveRanks();
+}
+
+std::map<int, int> Engine::resizeWorld() {
+  if (!cluster_) throw std::runtime_error("resizeWorld: not in a cluster");
+  return cluster_->resizeWorld();
+}
+
+std::map<int, int> Engine::lastResize() { return cluster_ ? cluster_->lastResize() : std::map<int, int>(); }
+
+bool Engine::waitForDeparture(int rank, int timeout_ms) { return cluster_ && cluster_->waitForDeparture(rank, timeout_ms); }
+
+void Engine::rebind(int new_rank, int new_world) {
+  // Peers are re-mapped by the next importEndpoints/joinCluster; registered programs of the old
+  // world size stay registered but cannot run (their world differs).
+  dropPeers();
+  char* mine = heap_;
+  rank_ = new_rank;
+  world_ = new_world;
+  peer_heaps_.assign(world_, nullptr);
+  peer_heaps_[rank_] = mine;
+  if (device_ == "cpu") std::memset(heap_ + layout_.signal_off, 0, layout_.num_signals * 8);
+  for (auto& kv : ops_) kv.second.epoch = 0;
+}
+
+void Engine::injectFault(const std::string& kind) {
+  if (!cluster_) throw std::runtime_error("injectFault: not in a cluster");
+  if (kind == "silence") cluster_->daemon().injectSilence(true);
+  else if (kind == "close") cluster_->daemon().injectAbruptClose();
+  else throw std::runtime_error("injectFault: unknown kind (silence|close)");
+}
+
+void Engine::regOp(const std::string& name, const std::string& path_or_json) {
+  size_t i = path_or_json.find_first_not_of(" \t\r\n");
+  Json doc = (i != std::string::npos && path_or_json[i] == '{') ? Json::parse(path_or_json) : Json::parseFile(path_or_json);
+  Program p = Program::fromJson(doc);
+  std::lock_guard<std::mutex> g(mu_);
+  if (ops_.count(name)) throw std::runtime_error("regOp: '" + name + "' is already registered");
+  Op op;
+  op.slots_reserved = p.num_slots * static_cast<uint32_t>(max_width_);
+  if (initialized_ && next_slot_ + op.slots_reserved > layout_.num_signals)
+    throw std::runtime_error("regOp: out of signal words");
+  op.slot_base = next_slot_;
+  next_slot_ += op.slots_reserved;
+  op.program = std::move(p);
+  ops_.emplace(name, std::move(op));
+}
+
+uint64_t Engine::heapBase(int rank) const {
+  if (rank < 0 || rank >= static_cast<int>(peer_heaps_.size())) return 0;
+  return reinterpret_cast<uint64_t>(peer_heaps_[rank]);
+}
+
+uint64_t Engine::allocSymmetric(uint64_t bytes, uint64_t align) {
+  if (align < 256) align = 256;
+  uint64_t off = alignUp(user_top_, align);
+  if (off + bytes > layout_.total) throw std::runtime_error("allocSymmetric: symmetric heap exhausted (raise heap_bytes)");
+  user_top_ = off + bytes;
+  return off;
+}
+
+void Engine::resetSymmetric(uint64_t mark) {
+  if (mark < layout_.user_off || mark > layout_.total) throw std::runtime_error("resetSymmetric: bad mark");
+  user_top_ = mark;
+}
+
+World Engine::worldTable() const {
+  World w{};
+  w.world = world_;
+  for (int r = 0; r < world_; ++r) w.heap[r] = peer_heaps_[r];
+  w.mc_heap = static_cast<char*>(mc_base_);
+  w.signal_off = layout_.signal_off;
+  w.flag_off = layout_.flag_off;
+  return w;
+}
+
+bool Engine::multicastSupported() {
+  if (device_ != "cuda") return false;
+  return static_cast<CudaDevice*>(getDev("cuda").get())->multicastSupported();
+}
+
+std::string Engine::mcCreate() {
+  auto* dev = static_cast<CudaDevice*>(getDev("cuda").get());
+  size_t gran = dev->multicastGranularity(world_, layout_.total);
+  if (layout_.total % gran) throw std::runtime_error("mcCreate: heap size is not a multiple of the multicast granularity");
+  return dev->multicastCreate(layout_.total, world_);
+}
+
+void Engine::mcJoin(const std::string& handle) { static_cast<CudaDevice*>(getDev("cuda").get())->multicastJoin(handle); }
+
+void Engine::mcBind() { mc_base_ = static_cast<CudaDevice*>(getDev("cuda").get())->multicastBind(heap_); }
+
+uint64_t Engine::nextEpoch(int lane) {
+  if (lane < 0 || lane >= static_cast<int>(lane_epochs_.size())) throw std::runtime_error("nextEpoch: bad lane");
+  return ++lane_epochs_[lane];
+}
+
+uint64_t Engine::statusPtr(int lane) const { return reinterpret_cast<uint64_t>(heap_ + layout_.status_off + 64ull * lane); }
+
+std::vector<uint32_t> Engine::checkStatus(int lane) {
+  std::vector<uint32_t> st(4, 0);
+  if (device_ == "cuda") {
+    cudaCheck(cudaDeviceSynchronize(), "checkStatus");
+    cudaCheck(cudaMemcpy(st.data(), reinterpret_cast<void*>(statusPtr(lane)), 16, cudaMemcpyDeviceToHost), "reading status");
+    if (st[0] != ST_OK) cudaMemset(reinterpret_cast<void*>(statusPtr(lane)), 0, 16);
+  } else {
+    std::memcpy(st.data(), reinterpret_cast<void*>(statusPtr(lane)), 16);
+    std::memset(reinterpret_cast<void*>(statusPtr(lane)), 0, 16);
+  }
+  return st;
+}
+
+int Engine::exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes,
+                  const std::string& dtype, int width, int lane, uint64_t stream) {
+  if (!initialized_) throw std::runtime_error("exeOp: call initEngine first");
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("exeOp: no op named '" + name + "'");
+  Op& op = it->second;
+  if (op.program.world != world_) throw std::runtime_error("exeOp: '" + name + "' was written for another world size");
+  if (lane < 0 || lane >= layout_.lanes) throw std::runtime_error("exeOp: lane out of range");
+  for (int r = 0; r < world_; ++r)
+    if (r != rank_ && !peer_heaps_[r] && !(tcp_ && device_ == "cpu"))
+      throw std::runtime_error("exeOp: peers are not connected (joinCluster/importEndpoints first)");
+  uint32_t dt = parseDType(dtype);
+  if (width < 1) width = 1;
+  if (width > max_width_) width = max_width_;
+  if (device_ == "cpu") return exeOnCpu(op, in_ptr, out_ptr, in_bytes, dt, width, lane);
+  return exeOnCuda(op, in_ptr, out_ptr, in_bytes, dt, width, lane, stream);
+}
+
+int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dt, int width, int lane) {
+  const Program& p = op.program;
+  uint64_t bb = p.blockBytesForInput(in_bytes);
+  if (bb % dtypeSize(dt)) throw std::runtime_error("exeOp: block size is not a whole number of elements");
+  if (p.needs_multicast || p.remote_io) throw std::runtime_error("exeOp: this program needs GPU symmetric memory");
+  auto key = std::make_pair(bb, width);
+  auto hc = op.host_cache.find(key);
+  if (hc == op.host_cache.end()) hc = op.host_cache.emplace(key, p.materialize(rank_, bb, width)).first;
+  const Materialized& m = hc->second;
+  uint64_t lane_bytes = layout_.workspace_bytes / layout_.lanes, half = lane_bytes / 2 / 4096 * 4096;
+  if (m.buf_bytes[BUF_SCRATCH] > half)
+    throw std::runtime_error("exeOp: message needs " + std::to_string(m.buf_bytes[BUF_SCRATCH]) +
+                             " bytes of scratch but a workspace lane half holds " + std::to_string(half) +
+                             " (raise PCCL_WORKSPACE_MB or split the message)");
+  uint64_t scratch_off = lane * lane_bytes + (op.epoch & 1) * half;
+  CpuExecContext ctx;
+  ctx.rank = rank_;
+  ctx.world = world_;
+  ctx.local[BUF_INPUT] = reinterpret_cast<char*>(in_ptr);
+  ctx.local[BUF_OUTPUT] = reinterpret_cast<char*>(p.in_place ? in_ptr : out_ptr);
+  ctx.local[BUF_SCRATCH] = heap_ + scratch_off;
+  for (int b = 0; b < BUF_COUNT; ++b) ctx.local_bytes[b] = m.buf_bytes[b];
+  ctx.peer_scratch.assign(world_, nullptr);
+  ctx.peer_signals.assign(world_, nullptr);
+  for (int r = 0; r < world_; ++r) {
+    if (!peer_heaps_[r]) continue;
+    ctx.peer_scratch[r] = peer_heaps_[r] + scratch_off;
+    ctx.peer_signals[r] = reinterpret_cast<std::atomic<uint64_t>*>(peer_heaps_[r] + layout_.signal_off);
+  }
+  ctx.tcp = tcp_.get();
+  ctx.tcp_scratch_key = tcp_key_;
+  ctx.tcp_scratch_off = scratch_off;
+  ctx.slot_base = op.slot_base;
+  ctx.epoch = op.epoch;
+  ctx.dtype = dt;
+  ctx.redop = parseRedOp(p.redop);
+  ctx.timeout_ms = timeout_ms_;
+  ctx.bounds_check = bounds_check_;
+  CpuExecResult res = runOnCpu(m, ctx);
+  op.epoch++;
+  op.launches++;
+  op.bytes += m.bytes_moved;
+  op.nanos += res.nanos;
+  uint32_t* st = reinterpret_cast<uint32_t*>(statusPtr(lane));
+  st[0] = res.status;
+  st[1] = static_cast<uint32_t>(res.failed_stream);
+  st[2] = static_cast<uint32_t>(res.failed_pc);
+  if (res.status == ST_TIMEOUT) op.timeouts++;
+  if (res.status != ST_OK)
+    PCCL_LOG_ERROR("exeOp '%s': status %u at stream %d pc %d", p.name.c_str(), res.status, res.failed_stream, res.failed_pc);
+  return static_cast<int>(res.status);
+}
+
+int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dt, int width, int lane,
+                      uint64_t stream) {
+  const Program& p = op.program;
+  uint64_t bb = p.blockBytesForInput(in_bytes);
+  if (bb % dtypeSize(dt)) throw std::runtime_error("exeOp: block size is not a whole number of elements");
+  if (p.needs_multicast && !mc_base_) throw std::runtime_error("exeOp: program needs NVLS multicast, which is not set up");
+  auto key = std::make_pair(bb, width);
+  auto dc = op.device_cache.find(key);
+  if (dc == op.device_cache.end()) {
+    Op::DeviceCopy c;
+    c.m = p.materialize(rank_, bb, width);
+    std::vector<Instr> flat;
+    std::vector<uint32_t> starts;
+    for (auto& s : c.m.streams) {
+      starts.push_back(static_cast<uint32_t>(flat.size()));
+      flat.insert(flat.end(), s.begin(), s.end());
+    }
+    c.n_streams = static_cast<int>(starts.size());
+    cudaCheck(cudaMalloc(&c.instrs, flat.size() * sizeof(Instr)), "cudaMalloc(instructions)");
+    cudaCheck(cudaMalloc(&c.starts, starts.size() * sizeof(uint32_t)), "cudaMalloc(stream table)");
+    cudaCheck(cudaMemcpy(c.instrs, flat.data(), flat.size() * sizeof(Instr), cudaMemcpyHostToDevice), "upload instructions");
+    cudaCheck(cudaMemcpy(c.starts, starts.data(), starts.size() * sizeof(uint32_t), cudaMemcpyHostToDevice), "upload stream table");
+    dc = op.device_cache.emplace(key, std::move(c)).first;
+  }
+  const Op::DeviceCopy& c = dc->second;
+  uint64_t lane_bytes = layout_.workspace_bytes / layout_.lanes, half = lane_bytes / 2 / 4096 * 4096;
+  if (c.m.buf_bytes[BUF_SCRATCH] > half)
+    throw std::runtime_error("exeOp: message needs more scratch than a workspace lane half holds (raise PCCL_WORKSPACE_MB)");
+  auto heapOff = [&](uint64_t ptr) -> long long {
+    uint64_t base = reinterpret_cast<uint64_t>(heap_);
+    return (ptr >= base && ptr < base + layout_.total) ? static_cast<long long>(ptr - base) : -1;
+  };
+  InterpLaunch L{};
+  L.w = worldTable();
+  L.nvirt = 1;
+  L.slot_base = op.slot_base;
+  L.epoch = op.epoch;
+  L.dtype = dt;
+  L.redop = parseRedOp(p.redop);
+  L.spin_limit = spin_limit_;
+  L.bounds_check = bounds_check_ ? 1 : 0;
+  InterpRank& R = L.r[0];
+  R.rank = rank_;
+  R.n_streams = c.n_streams;
+  R.instrs = c.instrs;
+  R.stream_start = c.starts;
+  R.input = reinterpret_cast<char*>(in_ptr);
+  R.output = reinterpret_cast<char*>(p.in_place ? in_ptr : out_ptr);
+  R.input_heap_off = heapOff(in_ptr);
+  R.output_heap_off = heapOff(p.in_place ? in_ptr : out_ptr);
+  if (p.remote_io && (R.input_heap_off < 0 || R.output_heap_off < 0))
+    throw std::runtime_error("exeOp: this program lets peers touch the tensors, so both must come from the symmetric heap");
+  R.scratch_off = lane * lane_bytes + (op.epoch & 1) * half;
+  for (int b = 0; b < BUF_COUNT; ++b) R.buf_bytes[b] = c.m.buf_bytes[b];
+  R.status = reinterpret_cast<uint32_t*>(statusPtr(lane));
+  int err = launchInterpreter(L, 512, reinterpret_cast<cudaStream_t>(stream));
+  if (err != 0) throw std::runtime_error(std::string("exeOp: kernel launch failed: ") + cudaErrorName(err));
+  op.epoch++;
+  op.launches++;
+  op.bytes += c.m.bytes_moved;
+  return 0;
+}
+
+std::string Engine::stats() {
+  Json j = Json::object();
+  j.set("rank", rank_);
+  j.set("world", world_);
+  j.set("device", device_);
+  j.set("heap_bytes", layout_.total);
+  j.set("workspace_bytes", layout_.workspace_bytes);
+  j.set("signals_used", static_cast<uint64_t>(next_slot_));
+  j.set("multicast", mc_base_ != nullptr);
+  j.set("log_file", Logger::get().path());
+  j.set("log_errors", Logger::get().count(LogLevel::Error));
+  if (tcp_) {
+    j.set("tcp_bytes_sent", tcp_->bytesSent());
+    j.set("tcp_bytes_received", tcp_->bytesReceived());
+  }
+  Json ops = Json::object();
+  for (auto& kv : ops_) {
+    Json o = Json::object();
+    o.set("collective", kv.second.program.collective);
+    o.set("launches", kv.second.launches);
+    o.set("bytes", kv.second.bytes);
+    o.set("timeouts", kv.second.timeouts);
+    o.set("host_nanos", kv.second.nanos);
+    double gbps = kv.second.nanos ? static_cast<double>(kv.second.bytes) / static_cast<double>(kv.second.nanos) : 0.0;
+    o.set("host_gb_per_s", gbps);
+    o.set("fingerprint", fnv1a(kv.second.program.name));
+    ops.set(kv.first, o);
+  }
+  j.set("ops", ops);
+  return j.dump();
+}
+
+}  // namespace pccl

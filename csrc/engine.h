@@ -1,0 +1,134 @@
+// Engine: the runtime object behind `pccl.engine`.
+//
+// Same public surface as the reference engine (include/engine.h:13-33, csrc/python_api.cc:13-20):
+// Engine(rank, world) with initEngine, regOp, exeOp, exportEndpoint, joinCluster, exitCluster.
+// In the reference initEngine allocates a 256 MiB workspace plus 256 int signals per device and
+// fills a flat endpoint map (csrc/engine.cc:42-100); regOp is empty and the other four methods have
+// no definition.  Here:
+//   * one symmetric heap per rank = [scratch workspace | uint64 signal words | barrier flags |
+//     status | user region]; the heap is POSIX shm for CPU ranks and a VMM allocation (peer-mapped
+//     over NVLink, optionally bound to an NVLS multicast object) for CUDA ranks;
+//   * regOp parses a schedule document and reserves a private range of signal words for it;
+//   * exeOp binds the schedule to the tensors, a worker budget (`width` -> CTAs or threads: the
+//     reference's "runtime resource control") and a workspace lane (ops on different lanes may run
+//     concurrently on different streams: "comm-comm overlap"), then runs it on the CPU executor or
+//     launches the persistent interpreter kernel;
+//   * joinCluster/exitCluster drive the control-plane daemon; importEndpoints is the same peer
+//     set-up for launchers that already have a rendezvous (torchrun).
+#pragma once
+#include <atomic>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "cluster/manager.h"
+#include "exec/cpu_executor.h"
+#include "exec/program.h"
+#include "kernels/api.h"
+#include "mem/cuda_device.h"
+#include "transport/tcp_transport.h"
+
+namespace pccl {
+
+struct HeapLayout {
+  uint64_t workspace_bytes = 0;
+  uint64_t signal_off = 0, num_signals = 0;
+  uint64_t flag_off = 0, flag_bytes = 0;
+  uint64_t status_off = 0, status_bytes = 0;
+  uint64_t user_off = 0;
+  uint64_t total = 0;
+  int lanes = 2;
+};
+
+class Engine {
+ public:
+  Engine(int rank, int world);
+  ~Engine();
+
+  void initEngine(const std::string& device = "auto", uint64_t heap_bytes = 0);
+  void regOp(const std::string& name, const std::string& path_or_json);
+  // Returns an ExecStatus for CPU ranks (synchronous); 0 for CUDA ranks (asynchronous on `stream`;
+  // call checkStatus() to synchronise and read the device status words).
+  int exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes,
+            const std::string& dtype, int width, int lane, uint64_t stream);
+  std::string exportEndpoint();
+  void importEndpoints(const std::vector<std::string>& docs);
+  void joinCluster(const std::string& master_endpoint, int timeout_ms = 60000);
+  void exitCluster();
+  std::string stats();
+
+  // symmetric heap
+  const std::string& deviceKind() const { return device_; }
+  uint64_t heapBase(int rank) const;
+  uint64_t heapBytes() const { return layout_.total; }
+  uint64_t allocSymmetric(uint64_t bytes, uint64_t align);   // returns heap offset (same on all ranks
+                                                             // when called in the same order)
+  void resetSymmetric(uint64_t mark);
+  uint64_t symmetricMark() const { return user_top_; }
+  const HeapLayout& layout() const { return layout_; }
+  World worldTable() const;
+
+  // NVLS multicast bring-up (three steps with a barrier of the caller's choice between them)
+  bool multicastSupported();
+  std::string mcCreate();
+  void mcJoin(const std::string& handle);
+  void mcBind();
+  uint64_t mcBase() const { return reinterpret_cast<uint64_t>(mc_base_); }
+
+  // status / elastic
+  std::vector<uint32_t> checkStatus(int lane);
+  uint64_t statusPtr(int lane) const;
+  std::vector<int> aliveRanks();
+  std::map<int, int> resizeWorld();      // master: renumber the survivors and announce it
+  std::map<int, int> lastResize();
+  bool waitForDeparture(int rank, int timeout_ms);
+  void rebind(int new_rank, int new_world);   // adopt a ResizeWorld result (drops peer mappings)
+  void injectFault(const std::string& kind);  // host-side fault injection for tests
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+  uint64_t nextEpoch(int flag_lane);          // per-lane launch counter for hand-written collectives
+
+ private:
+  struct Op {
+    Program program;
+    uint32_t slot_base = 0;
+    uint32_t slots_reserved = 0;
+    uint64_t epoch = 0;
+    uint64_t launches = 0, bytes = 0, nanos = 0, timeouts = 0;
+    struct DeviceCopy { Instr* instrs = nullptr; uint32_t* starts = nullptr; int n_streams = 0; Materialized m; };
+    std::map<std::pair<uint64_t, int>, DeviceCopy> device_cache;
+    std::map<std::pair<uint64_t, int>, Materialized> host_cache;
+  };
+  void buildLayout(uint64_t heap_bytes);
+  void setupPeers(const std::map<int, NodeMeta>& nodes);
+  void dropPeers();
+  int exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane);
+  int exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane, uint64_t stream);
+
+  int rank_, world_;
+  bool initialized_ = false;
+  std::string device_;
+  std::string host_id_;
+  HeapLayout layout_;
+  char* heap_ = nullptr;
+  std::string heap_handle_;
+  std::vector<char*> peer_heaps_;
+  void* mc_base_ = nullptr;
+  uint64_t user_top_ = 0;
+  std::map<std::string, std::string> configs_;
+  std::unique_ptr<ClusterManager> cluster_;
+  std::unique_ptr<TcpTransport> tcp_;
+  uint32_t tcp_key_ = 0;
+  std::map<std::string, Op> ops_;
+  uint32_t next_slot_ = 0;
+  std::mutex mu_;
+  std::vector<uint64_t> lane_epochs_;
+  int timeout_ms_ = 30000;
+  uint64_t spin_limit_ = kDefaultSpinLimit;
+  bool bounds_check_ = true;
+  int max_width_ = 32;
+};
+
+}  // namespace pccl

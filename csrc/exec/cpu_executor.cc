@@ -1,0 +1,141 @@
+#include "cpu_executor.h"
+
+#include <chrono>
+#include <cstring>
+#include <thread>
+
+#include "../common/clock.h"
+#include "../common/log.h"
+#include "reduce_cpu.h"
+
+namespace pccl {
+
+namespace {
+
+struct Shared {
+  std::atomic<uint32_t> status{ST_OK};
+  std::atomic<int> failed_stream{-1};
+  std::atomic<int> failed_pc{-1};
+  void fail(uint32_t st, int stream, int pc) {
+    uint32_t expect = ST_OK;
+    if (status.compare_exchange_strong(expect, st)) {
+      failed_stream.store(stream);
+      failed_pc.store(pc);
+    }
+  }
+};
+
+bool waitFor(std::atomic<uint64_t>* word, uint64_t target, const CpuExecContext& ctx, Shared& sh) {
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(ctx.timeout_ms);
+  int spins = 0;
+  while (word->load(std::memory_order_acquire) < target) {
+    if (sh.status.load(std::memory_order_relaxed) != ST_OK) return false;
+    if (++spins < 64) continue;
+    spins = 0;
+    std::this_thread::yield();
+    if (std::chrono::steady_clock::now() >= deadline) return false;
+  }
+  return true;
+}
+
+void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext& ctx, Shared& sh) {
+  std::atomic<uint64_t>* my_signals = ctx.peer_signals[ctx.rank];
+  auto resolve = [&](int rank, uint32_t buf, uint64_t off, uint64_t bytes, bool* remote_tcp) -> char* {
+    *remote_tcp = false;
+    if (rank == ctx.rank) {
+      if (ctx.bounds_check && (off > ctx.local_bytes[buf] || bytes > ctx.local_bytes[buf] - off)) return nullptr;
+      return ctx.local[buf] + off;
+    }
+    if (buf != BUF_SCRATCH) return nullptr;   // peers only see the symmetric workspace
+    if (ctx.bounds_check && (off > ctx.local_bytes[BUF_SCRATCH] || bytes > ctx.local_bytes[BUF_SCRATCH] - off)) return nullptr;
+    if (ctx.peer_scratch[rank]) return ctx.peer_scratch[rank] + off;
+    *remote_tcp = true;
+    return reinterpret_cast<char*>(1);   // non-null marker; the caller must use the transport
+  };
+  for (size_t pc = 0; pc < prog.size(); ++pc) {
+    if (sh.status.load(std::memory_order_relaxed) != ST_OK) return;
+    const Instr& in = prog[pc];
+    switch (in.op) {
+      case OP_NOP: break;
+      case OP_END: return;
+      case OP_COPY:
+      case OP_REDUCE: {
+        if (in.bytes == 0) break;
+        bool src_tcp, dst_tcp;
+        char* s = resolve(in.src_rank, in.src_buf, in.src_off, in.bytes, &src_tcp);
+        char* d = resolve(in.dst_rank, in.dst_buf, in.dst_off, in.bytes, &dst_tcp);
+        if (!s || !d) { sh.fail(ST_BOUNDS, stream, static_cast<int>(pc)); return; }
+        if (src_tcp || (dst_tcp && in.op == OP_REDUCE)) { sh.fail(ST_UNSUPPORTED, stream, static_cast<int>(pc)); return; }
+        if (dst_tcp) {
+          if (!ctx.tcp || !ctx.tcp->put(in.dst_rank, ctx.tcp_scratch_key, ctx.tcp_scratch_off + in.dst_off, s, in.bytes)) {
+            sh.fail(ST_PEER_GONE, stream, static_cast<int>(pc));
+            return;
+          }
+        } else if (in.op == OP_COPY) {
+          if (s != d) std::memmove(d, s, in.bytes);
+        } else if (!reduceInto(d, s, in.bytes, ctx.dtype, ctx.redop)) {
+          sh.fail(ST_UNSUPPORTED, stream, static_cast<int>(pc));
+          return;
+        }
+        break;
+      }
+      case OP_NOTIFY: {
+        uint32_t slot = ctx.slot_base + in.slot;
+        if (ctx.peer_signals[in.dst_rank]) {
+          ctx.peer_signals[in.dst_rank][slot].fetch_add(1, std::memory_order_release);
+        } else if (!ctx.tcp || !ctx.tcp->signal(in.dst_rank, slot, 1)) {
+          sh.fail(ST_PEER_GONE, stream, static_cast<int>(pc));
+          return;
+        }
+        break;
+      }
+      case OP_WAIT: {
+        uint64_t target = ctx.epoch * in.count + in.value;
+        if (!waitFor(&my_signals[ctx.slot_base + in.slot], target, ctx, sh)) {
+          sh.fail(ST_TIMEOUT, stream, static_cast<int>(pc));
+          return;
+        }
+        break;
+      }
+      case OP_BARRIER: {
+        uint32_t slot = ctx.slot_base + in.slot;
+        for (int r = 0; r < ctx.world; ++r) {
+          if (ctx.peer_signals[r]) ctx.peer_signals[r][slot].fetch_add(1, std::memory_order_acq_rel);
+          else if (!ctx.tcp || !ctx.tcp->signal(r, slot, 1)) {
+            sh.fail(ST_PEER_GONE, stream, static_cast<int>(pc));
+            return;
+          }
+        }
+        uint64_t target = static_cast<uint64_t>(ctx.world) * (ctx.epoch * in.count + in.value);
+        if (!waitFor(&my_signals[slot], target, ctx, sh)) {
+          sh.fail(ST_TIMEOUT, stream, static_cast<int>(pc));
+          return;
+        }
+        break;
+      }
+      default:   // multimem ops need NVSwitch hardware
+        sh.fail(ST_UNSUPPORTED, stream, static_cast<int>(pc));
+        return;
+    }
+  }
+}
+
+}  // namespace
+
+CpuExecResult runOnCpu(const Materialized& m, const CpuExecContext& ctx) {
+  Shared sh;
+  uint64_t t0 = monotonicNanos();
+  std::vector<std::thread> threads;
+  for (size_t i = 1; i < m.streams.size(); ++i)
+    threads.emplace_back([&, i] { runStream(m.streams[i], static_cast<int>(i), ctx, sh); });
+  if (!m.streams.empty()) runStream(m.streams[0], 0, ctx, sh);
+  for (auto& t : threads) t.join();
+  CpuExecResult r;
+  r.status = sh.status.load();
+  r.failed_stream = sh.failed_stream.load();
+  r.failed_pc = sh.failed_pc.load();
+  r.nanos = monotonicNanos() - t0;
+  return r;
+}
+
+}  // namespace pccl

@@ -1,0 +1,45 @@
+// CPU executor: runs a rank's instruction streams on host threads.
+//
+// The reference's cpu executor header is empty (include/plugins/cpu_executor/executor.h); its
+// intended loop is "pop an op, run the primitive, release dependants" over the layouts of
+// include/base/operator.h:7-38.  Here each stream (channel x width replica) gets one thread that
+// walks its instructions in order; COPY / REDUCE touch local memory, a same-host peer's mapped
+// workspace, or go through the TCP transport; NOTIFY / WAIT / BARRIER use counting signal words.
+// Every wait is bounded: on time-out the worker records ST_TIMEOUT, raises the abort flag so its
+// sibling workers stop too, and the call returns the status to the caller.
+#pragma once
+#include <atomic>
+#include <cstdint>
+#include <vector>
+
+#include "../transport/tcp_transport.h"
+#include "program.h"
+
+namespace pccl {
+
+struct CpuExecContext {
+  int rank = 0, world = 1;
+  char* local[BUF_COUNT] = {nullptr, nullptr, nullptr};   // input, output, scratch (this launch's lane)
+  uint64_t local_bytes[BUF_COUNT] = {0, 0, 0};
+  std::vector<char*> peer_scratch;                         // per rank; nullptr = reach it over TCP
+  std::vector<std::atomic<uint64_t>*> peer_signals;        // per rank; nullptr = over TCP
+  TcpTransport* tcp = nullptr;
+  uint32_t tcp_scratch_key = 0;
+  uint64_t tcp_scratch_off = 0;      // lane offset inside the peer's registered workspace
+  uint32_t slot_base = 0;            // first signal slot of this op
+  uint64_t epoch = 0;                // launches of this op so far
+  uint32_t dtype = DT_F32, redop = RED_SUM;
+  int timeout_ms = 30000;
+  bool bounds_check = true;
+};
+
+struct CpuExecResult {
+  uint32_t status = ST_OK;
+  int failed_stream = -1;
+  int failed_pc = -1;
+  uint64_t nanos = 0;
+};
+
+CpuExecResult runOnCpu(const Materialized& m, const CpuExecContext& ctx);
+
+}  // namespace pccl

@@ -1,0 +1,100 @@
+// Host-callable entry points of the sm_100a kernels.  Plain C++ types only (no torch headers):
+// the Python layer passes raw device pointers and the CUDA stream handle.
+//
+// Multi-rank convention.  Every communication kernel takes a `World`: the table of all ranks'
+// symmetric-heap base addresses as mapped into THIS process, the multicast address of the heap
+// (or null), and the offset of the signal area.  In production one process drives one GPU and
+// launches the kernel for its own rank (`nvirt == 1`).  For single-GPU tests the same kernel is
+// launched once, cooperatively, with `nvirt == world` and blockIdx.y selecting the rank whose
+// part a block plays, all "heaps" being buffers of that one GPU (ranks that wait on one another
+// must never be separate launches on one GPU).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../base/instr.h"
+
+namespace pccl {
+
+constexpr int kMaxRanks = 16;
+constexpr int kMaxBlocksPerColl = 160;        // flag rows reserved per collective "lane"
+constexpr uint64_t kDefaultSpinLimit = 400ull * 1000 * 1000;   // polls; ~1 s at ~2.5 ns per poll
+
+struct World {
+  int world;
+  int pad;
+  char* heap[kMaxRanks];     // heap[r] = rank r's symmetric heap, addressable from the launching GPU
+  char* mc_heap;             // multicast (NVLS) address of the heap, or nullptr
+  uint64_t signal_off;       // byte offset of the uint64 signal words inside every heap
+  uint64_t flag_off;         // byte offset of the per-block barrier flags inside every heap
+};
+
+// ---------------------------------------------------------------------------------------------
+// K6: persistent interpreter of lowered collective programs
+// ---------------------------------------------------------------------------------------------
+struct InterpRank {
+  int rank;
+  int n_streams;
+  const Instr* instrs;            // all streams of this rank, back to back
+  const uint32_t* stream_start;   // n_streams entries: index of each stream's first instruction
+  char* input;
+  char* output;
+  long long input_heap_off;       // >= 0 when the tensor lives in the symmetric heap (peers may touch it)
+  long long output_heap_off;
+  uint64_t scratch_off;           // offset of this launch's scratch lane inside the heap
+  uint64_t buf_bytes[BUF_COUNT];
+  uint32_t* status;               // [0]=status code, [1]=stream, [2]=pc, [3]=detail
+};
+
+struct InterpLaunch {
+  World w;
+  int nvirt;                      // 1, or world for single-GPU emulation
+  uint32_t slot_base;
+  uint64_t epoch;
+  uint32_t dtype, redop;
+  uint64_t spin_limit;
+  int bounds_check;
+  InterpRank r[kMaxRanks];
+};
+
+// grid = (max n_streams, nvirt); cooperative launch.  Returns a cudaError_t as int.
+int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// K1-K4, K10: hand-written collectives over the symmetric heap (offsets are heap-relative)
+// ---------------------------------------------------------------------------------------------
+enum CollAlgo : int { ALGO_P2P = 0, ALGO_NVLS = 1 };
+
+struct CollArgs {
+  World w;
+  int nvirt;                 // 1 or world (emulation)
+  int rank;                  // ignored when nvirt > 1
+  int algo;                  // CollAlgo
+  uint32_t dtype, redop;
+  uint64_t in_off;           // heap offset of the input (symmetric)
+  uint64_t out_off;          // heap offset of the output (symmetric)
+  uint64_t count;            // elements: AR total, RS/AG per-shard, A2A per-block
+  uint64_t epoch;            // strictly increasing per launch on a given flag lane
+  int flag_lane;             // which flag rows this launch uses (concurrent launches use distinct lanes)
+  float scale;               // RS epilogue: out = reduce(in) * scale
+  uint32_t out_dtype;        // RS epilogue cast (DT_F32 or same as dtype)
+  uint64_t spin_limit;
+  uint32_t* status[kMaxRanks];   // per virtual rank status words (4 x u32)
+  // Optional plain (non-symmetric) local tensors, per virtual rank: the all-gather / all-to-all
+  // input and the reduce-scatter output are only touched by their own rank.
+  const void* local_in[kMaxRanks];
+  void* local_out[kMaxRanks];
+};
+
+int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
+int launchReduceScatter(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
+int launchAllGather(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
+int launchAllToAll(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
+// Bounded-wait self test: waits on a flag nobody sets; must come back with ST_TIMEOUT.
+int launchWaitTimeoutProbe(uint64_t* flag, uint64_t spin_limit, uint32_t* status, cudaStream_t stream);
+
+int deviceSmCount();
+const char* cudaErrorName(int err);
+
+}  // namespace pccl

@@ -1,0 +1,339 @@
+// Hand-written collectives over the symmetric heap: all-reduce, reduce-scatter (+ scale/cast
+// epilogue for gradient buckets), all-gather, all-to-all; P2P (ld/st over NVLink) and NVLS
+// (multimem through the switch) forms.
+//
+// The reference has only the three multimem wrappers and no kernel that uses them
+// (include/plugins/cuda_executor/utils/multimem.h:12-127).  These kernels are what its README
+// bullets ("NVLS", "CUDA IPC") stand for, built for NVSwitch: every GPU reaches every peer at full
+// port bandwidth, so each collective is one hop -- a rank pull-reduces (or ld_reduce's) its own
+// slice from all peers and pushes (or multicast-stores) results -- instead of a ring.
+//
+// Synchronisation: CTA b of every rank shares one row of flags with CTA b of every other rank
+// (flags[lane][b][source rank], uint64, in the symmetric heap).  A launch with epoch e uses values
+// 4e+1 (entry) and 4e+2 (exit); values only grow, so nothing is ever cleared and a late flag
+// from an old launch cannot release a newer wait.  Waits are bounded (see prims.cuh).
+#include "api.h"
+#include "prims.cuh"
+
+namespace pccl {
+
+using namespace dev;
+
+namespace {
+
+__device__ __forceinline__ uint64_t* flag_ptr(const World& W, int owner, int lane, int block, int src) {
+  return reinterpret_cast<uint64_t*>(W.heap[owner] + W.flag_off) +
+         ((static_cast<uint64_t>(lane) * kMaxBlocksPerColl + block) * kMaxRanks + src);
+}
+
+// Returns false (after recording ST_TIMEOUT) if some peer did not arrive in time.
+__device__ __forceinline__ bool peer_barrier(const CollArgs& A, int me, uint64_t value, uint32_t* s_fail) {
+  __syncthreads();
+  if (threadIdx.x < static_cast<uint32_t>(A.w.world)) {
+    const int p = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(flag_ptr(A.w, p, A.flag_lane, blockIdx.x, me), value);
+    if (!wait_ge(flag_ptr(A.w, me, A.flag_lane, blockIdx.x, p), value, A.spin_limit, nullptr)) {
+      *s_fail = 1;
+      report(A.status[A.nvirt > 1 ? me : 0], ST_TIMEOUT, blockIdx.x, static_cast<uint32_t>(p), static_cast<uint32_t>(value & 3));
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+__device__ __forceinline__ int my_rank(const CollArgs& A) { return A.nvirt > 1 ? static_cast<int>(blockIdx.y) : A.rank; }
+
+// Sum/max/min of vector i (16 bytes) of every rank's `in` at heap offset `off`, accumulated in fp32.
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ void pull_reduce(const CollArgs& A, int me, uint64_t off, float* acc) {
+  constexpr int N = Lanes<DT>::n;
+  const int n = A.w.world;
+  // Peers are visited eight at a time with the loads fully unrolled and predicated, so the
+  // vectors stay in registers and up to eight 16-byte NVLink loads are in flight per thread.
+  for (int g = 0; g < n; g += 8) {
+    Vec16 v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (g + k < n) {
+        int p = me + g + k;
+        if (p >= n) p -= n;
+        v[k] = ld16(A.w.heap[p] + off);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (g + k < n) {
+        if (g + k == 0) {
+          unpack<DT>(v[0], acc);
+        } else {
+          float f[N];
+          unpack<DT>(v[k], f);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] = red1<OP>(acc[j], f[j]);
+        }
+      }
+    }
+  }
+}
+
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ float pull_reduce1(const CollArgs& A, int me, uint64_t off) {
+  float acc = load1<DT>(A.w.heap[me] + off);
+  for (int k = 1; k < A.w.world; ++k) acc = red1<OP>(acc, load1<DT>(A.w.heap[(me + k) % A.w.world] + off));
+  return acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-reduce: two-shot (slice r is reduced by rank r and written to every rank's output)
+// ---------------------------------------------------------------------------------------------
+template <uint32_t DT, uint32_t OP, bool NVLS>
+__global__ void __launch_bounds__(512) allreduce_kernel(const __grid_constant__ CollArgs A) {
+  constexpr int N = Lanes<DT>::n;
+  constexpr int ES = 16 / N;
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = my_rank(A), n = A.w.world;
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+
+  const uint64_t bytes = A.count * ES;
+  const uint64_t nvec = bytes >> 4;
+  const uint64_t per = (nvec + n - 1) / n;
+  const uint64_t lo = min(per * me, nvec), hi = min(per * (me + 1), nvec);
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  for (uint64_t i = lo + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += stride) {
+    const uint64_t o = i << 4;
+    if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
+      Vec16 r = multimem_ld_reduce<DT, OP>(A.w.mc_heap + A.in_off + o);
+      multimem_st(A.w.mc_heap + A.out_off + o, r);
+    } else {
+      float acc[N];
+      pull_reduce<DT, OP>(A, me, A.in_off + o, acc);
+      Vec16 r = pack<DT>(acc);
+      for (int k = 0; k < n; ++k) {
+        int p = me + k;
+        if (p >= n) p -= n;
+        st16(A.w.heap[p] + A.out_off + o, r);
+      }
+    }
+  }
+  // ragged tail (bytes not a multiple of 16): the last rank handles it element by element
+  if (me == n - 1 && blockIdx.x == 0) {
+    for (uint64_t b = (nvec << 4) + static_cast<uint64_t>(threadIdx.x) * ES; b + ES <= bytes; b += static_cast<uint64_t>(blockDim.x) * ES) {
+      float r = pull_reduce1<DT, OP>(A, me, A.in_off + b);
+      for (int p = 0; p < n; ++p) store1<DT>(A.w.heap[p] + A.out_off + b, r);
+    }
+  }
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+// one-shot: every rank reduces everything into its own output (out must not alias in)
+template <uint32_t DT, uint32_t OP, bool NVLS>
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_constant__ CollArgs A) {
+  constexpr int N = Lanes<DT>::n;
+  constexpr int ES = 16 / N;
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = my_rank(A);
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const uint64_t bytes = A.count * ES;
+  const uint64_t nvec = bytes >> 4;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  char* out = A.w.heap[me] + A.out_off;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const uint64_t o = i << 4;
+    if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
+      st16(out + o, multimem_ld_reduce<DT, OP>(A.w.mc_heap + A.in_off + o));
+    } else {
+      float acc[N];
+      pull_reduce<DT, OP>(A, me, A.in_off + o, acc);
+      st16(out + o, pack<DT>(acc));
+    }
+  }
+  if (blockIdx.x == 0)
+    for (uint64_t b = (nvec << 4) + static_cast<uint64_t>(threadIdx.x) * ES; b + ES <= bytes; b += static_cast<uint64_t>(blockDim.x) * ES)
+      store1<DT>(out + b, pull_reduce1<DT, OP>(A, me, A.in_off + b));
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+// ---------------------------------------------------------------------------------------------
+// reduce-scatter with epilogue: out_r[i] = cast(scale * reduce_p in_p[r*count + i])
+// ---------------------------------------------------------------------------------------------
+template <uint32_t DT, uint32_t OP, bool NVLS, bool OUT_F32>
+__global__ void __launch_bounds__(512) reduce_scatter_kernel(const __grid_constant__ CollArgs A) {
+  constexpr int N = Lanes<DT>::n;
+  constexpr int ES = 16 / N;
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = my_rank(A);
+  const int slot = A.nvirt > 1 ? me : 0;
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const uint64_t bytes = A.count * ES;
+  const uint64_t nvec = bytes >> 4;
+  const uint64_t base = A.in_off + static_cast<uint64_t>(me) * bytes;
+  char* out = A.local_out[slot] ? static_cast<char*>(A.local_out[slot]) : A.w.heap[me] + A.out_off;
+  const bool aligned = ((base | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const float scale = A.scale;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  const uint64_t gtid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  uint64_t done = 0;
+  if (aligned) {
+    for (uint64_t i = gtid; i < nvec; i += stride) {
+      const uint64_t o = i << 4;
+      float acc[N];
+      if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
+        unpack<DT>(multimem_ld_reduce<DT, OP>(A.w.mc_heap + base + o), acc);
+      } else {
+        pull_reduce<DT, OP>(A, me, base + o, acc);
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] *= scale;
+      if constexpr (OUT_F32 && DT != DT_F32) {
+        float* of = reinterpret_cast<float*>(out) + i * N;
+#pragma unroll
+        for (int j = 0; j < N; j += 4) {
+          Vec16 r;
+          r.w[0] = __float_as_uint(acc[j]); r.w[1] = __float_as_uint(acc[j + 1]);
+          r.w[2] = __float_as_uint(acc[j + 2]); r.w[3] = __float_as_uint(acc[j + 3]);
+          st16(of + j, r);
+        }
+      } else {
+        st16(out + o, pack<DT>(acc));
+      }
+    }
+    done = nvec << 4;
+  }
+  for (uint64_t b = done + gtid * ES; b + ES <= bytes; b += stride * ES) {
+    float r = pull_reduce1<DT, OP>(A, me, base + b) * scale;
+    if constexpr (OUT_F32 && DT != DT_F32) reinterpret_cast<float*>(out)[b / ES] = r;
+    else store1<DT>(out + b, r);
+  }
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+// ---------------------------------------------------------------------------------------------
+// all-gather (push) and all-to-all (push); `count` is in bytes here
+// ---------------------------------------------------------------------------------------------
+template <bool NVLS>
+__global__ void __launch_bounds__(1024) allgather_kernel(const __grid_constant__ CollArgs A) {
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = my_rank(A), n = A.w.world;
+  const int slot = A.nvirt > 1 ? me : 0;
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const uint64_t bytes = A.count;
+  const char* in = A.local_in[slot] ? static_cast<const char*>(A.local_in[slot]) : A.w.heap[me] + A.in_off;
+  const uint64_t dst = A.out_off + static_cast<uint64_t>(me) * bytes;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in) | dst) & 15) == 0;
+  const uint64_t nvec = aligned ? bytes >> 4 : 0;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  const uint64_t gtid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (uint64_t i = gtid; i < nvec; i += stride) {
+    Vec16 v = ld16(in + (i << 4));
+    if constexpr (NVLS) {
+      multimem_st(A.w.mc_heap + dst + (i << 4), v);
+    } else {
+      for (int k = 0; k < n; ++k) {
+        int p = me + k;
+        if (p >= n) p -= n;
+        st16(A.w.heap[p] + dst + (i << 4), v);
+      }
+    }
+  }
+  for (uint64_t b = (nvec << 4) + gtid; b < bytes; b += stride) {
+    char c = in[b];
+    for (int p = 0; p < n; ++p) A.w.heap[p][dst + b] = c;
+  }
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+__global__ void __launch_bounds__(1024) alltoall_kernel(const __grid_constant__ CollArgs A) {
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = my_rank(A), n = A.w.world;
+  const int slot = A.nvirt > 1 ? me : 0;
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const uint64_t bytes = A.count;
+  const char* in = A.local_in[slot] ? static_cast<const char*>(A.local_in[slot]) : A.w.heap[me] + A.in_off;
+  const uint64_t dst = A.out_off + static_cast<uint64_t>(me) * bytes;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in) | dst | bytes) & 15) == 0;
+  const uint64_t nvec = aligned ? bytes >> 4 : 0;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  const uint64_t gtid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (int k = 0; k < n; ++k) {
+    int p = me + k;
+    if (p >= n) p -= n;
+    const char* src = in + static_cast<uint64_t>(p) * bytes;
+    char* out = A.w.heap[p] + dst;
+    for (uint64_t i = gtid; i < nvec; i += stride) st16(out + (i << 4), ld16(src + (i << 4)));
+    for (uint64_t b = (nvec << 4) + gtid; b < bytes; b += stride) out[b] = src[b];
+  }
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+template <typename K>
+int launchCoop(K kernel, const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocksPerColl) blocks = kMaxBlocksPerColl;
+  if (a.flag_lane < 0 || a.flag_lane >= 8) return static_cast<int>(cudaErrorInvalidValue);
+  if (a.algo == ALGO_NVLS && (!a.w.mc_heap || a.nvirt > 1)) return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid(blocks, a.nvirt > 1 ? a.nvirt : 1), block(threads);
+  void* args[] = {const_cast<CollArgs*>(&a)};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), grid, block, args, 0, stream));
+}
+
+#define PCCL_DISPATCH_DT_OP(CALL)                                                    \
+  switch (a.dtype) {                                                                 \
+    case DT_F32:                                                                     \
+      switch (a.redop) { case RED_SUM: CALL(DT_F32, RED_SUM) case RED_MAX: CALL(DT_F32, RED_MAX) case RED_MIN: CALL(DT_F32, RED_MIN) default: break; } break; \
+    case DT_BF16:                                                                    \
+      switch (a.redop) { case RED_SUM: CALL(DT_BF16, RED_SUM) case RED_MAX: CALL(DT_BF16, RED_MAX) case RED_MIN: CALL(DT_BF16, RED_MIN) default: break; } break; \
+    case DT_F16:                                                                     \
+      switch (a.redop) { case RED_SUM: CALL(DT_F16, RED_SUM) case RED_MAX: CALL(DT_F16, RED_MAX) case RED_MIN: CALL(DT_F16, RED_MIN) default: break; } break; \
+    case DT_FP8_E4M3:                                                                \
+      switch (a.redop) { case RED_SUM: CALL(DT_FP8_E4M3, RED_SUM) case RED_MAX: CALL(DT_FP8_E4M3, RED_MAX) default: break; } break; \
+    default: break;                                                                  \
+  }
+
+}  // namespace
+
+int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
+  const bool nvls = a.algo == ALGO_NVLS;
+  const uint64_t bytes = a.count * dtypeSize(a.dtype);
+  // One-shot below 256 KiB when the output does not alias the input: one barrier pair, no second hop.
+  const bool oneshot = bytes <= (256u << 10) && a.in_off != a.out_off;
+#define PCCL_AR(DT_, OP_)                                                                              \
+  return oneshot ? (nvls ? launchCoop(allreduce_oneshot_kernel<DT_, OP_, true>, a, blocks, threads, stream)  \
+                         : launchCoop(allreduce_oneshot_kernel<DT_, OP_, false>, a, blocks, threads, stream)) \
+                 : (nvls ? launchCoop(allreduce_kernel<DT_, OP_, true>, a, blocks, threads, stream)           \
+                         : launchCoop(allreduce_kernel<DT_, OP_, false>, a, blocks, threads, stream));
+  PCCL_DISPATCH_DT_OP(PCCL_AR)
+#undef PCCL_AR
+  return static_cast<int>(cudaErrorNotSupported);
+}
+
+int launchReduceScatter(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
+  const bool nvls = a.algo == ALGO_NVLS;
+  const bool f32out = a.out_dtype == DT_F32 && a.dtype != DT_F32;
+#define PCCL_RS(DT_, OP_)                                                                                       \
+  return f32out ? (nvls ? launchCoop(reduce_scatter_kernel<DT_, OP_, true, true>, a, blocks, threads, stream)   \
+                        : launchCoop(reduce_scatter_kernel<DT_, OP_, false, true>, a, blocks, threads, stream)) \
+                : (nvls ? launchCoop(reduce_scatter_kernel<DT_, OP_, true, false>, a, blocks, threads, stream)  \
+                        : launchCoop(reduce_scatter_kernel<DT_, OP_, false, false>, a, blocks, threads, stream));
+  PCCL_DISPATCH_DT_OP(PCCL_RS)
+#undef PCCL_RS
+  return static_cast<int>(cudaErrorNotSupported);
+}
+
+int launchAllGather(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
+  return a.algo == ALGO_NVLS ? launchCoop(allgather_kernel<true>, a, blocks, threads, stream)
+                             : launchCoop(allgather_kernel<false>, a, blocks, threads, stream);
+}
+
+int launchAllToAll(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
+  CollArgs b = a;
+  b.algo = ALGO_P2P;
+  return launchCoop(alltoall_kernel, b, blocks, threads, stream);
+}
+
+}  // namespace pccl

@@ -1,0 +1,264 @@
+// Persistent interpreter of lowered collective programs (one CTA = one instruction stream).
+//
+// This is the CUDA executor the reference never wrote (include/plugins/cuda_executor/executor.h is
+// empty) for the operator graph it sketched (include/base/operator.h:19-38).  A CTA fetches its
+// 64-byte instructions in order and runs them with all of its threads:
+//   COPY / REDUCE        16-byte vector loops over local memory or a peer's mapped heap (NVLink)
+//   NOTIFY / WAIT        counting signal words: red.release.sys on the consumer's heap, bounded
+//                        ld.acquire.sys polling on our own
+//   BARRIER              every rank increments one word on every rank
+//   MM_LD_REDUCE / MM_ST in-switch reduction / multicast store through the NVLS mapping
+// A wait that runs out of polls writes ST_TIMEOUT with the stream and pc into the status words and
+// the CTA leaves; sibling CTAs notice the status word and leave too.  Nothing traps or spins forever.
+#include <cooperative_groups.h>
+
+#include "api.h"
+#include "prims.cuh"
+
+namespace pccl {
+
+using namespace dev;
+
+namespace {
+
+__device__ __forceinline__ void copy_range(char* dst, const char* src, uint64_t bytes) {
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0) {
+    const uint64_t nvec = bytes >> 4;
+    uint64_t i = tid;
+    // four independent 16-byte loads in flight per thread
+    for (; i + 3ull * nt < nvec; i += 4ull * nt) {
+      Vec16 a = ld16(src + (i << 4)), b = ld16(src + ((i + nt) << 4));
+      Vec16 c = ld16(src + ((i + 2ull * nt) << 4)), d = ld16(src + ((i + 3ull * nt) << 4));
+      st16(dst + (i << 4), a);
+      st16(dst + ((i + nt) << 4), b);
+      st16(dst + ((i + 2ull * nt) << 4), c);
+      st16(dst + ((i + 3ull * nt) << 4), d);
+    }
+    for (; i < nvec; i += nt) st16(dst + (i << 4), ld16(src + (i << 4)));
+    for (uint64_t b = (nvec << 4) + tid; b < bytes; b += nt) dst[b] = src[b];
+  } else {
+    for (uint64_t b = tid; b < bytes; b += nt) dst[b] = src[b];
+  }
+}
+
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ void reduce_range_f(char* dst, const char* src, uint64_t bytes) {
+  constexpr int N = Lanes<DT>::n;
+  constexpr int ES = 16 / N;
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  uint64_t done = 0;
+  if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0) {
+    const uint64_t nvec = bytes >> 4;
+    for (uint64_t i = tid; i < nvec; i += nt) {
+      Vec16 a = ld16(dst + (i << 4)), b = ld16(src + (i << 4));
+      float fa[N], fb[N];
+      unpack<DT>(a, fa);
+      unpack<DT>(b, fb);
+#pragma unroll
+      for (int k = 0; k < N; ++k) fa[k] = red1<OP>(fa[k], fb[k]);
+      st16(dst + (i << 4), pack<DT>(fa));
+    }
+    done = nvec << 4;
+  }
+  for (uint64_t b = done + static_cast<uint64_t>(tid) * ES; b + ES <= bytes; b += static_cast<uint64_t>(nt) * ES)
+    store1<DT>(dst + b, red1<OP>(load1<DT>(dst + b), load1<DT>(src + b)));
+}
+
+template <typename T, uint32_t OP>
+__device__ __forceinline__ void reduce_range_i(char* dst, const char* src, uint64_t bytes) {
+  T* d = reinterpret_cast<T*>(dst);
+  const T* s = reinterpret_cast<const T*>(src);
+  for (uint64_t i = threadIdx.x; i < bytes / sizeof(T); i += blockDim.x) {
+    T a = d[i], b = s[i];
+    if constexpr (OP == RED_SUM) d[i] = a + b;
+    else if constexpr (OP == RED_MAX) d[i] = a > b ? a : b;
+    else if constexpr (OP == RED_MIN) d[i] = a < b ? a : b;
+    else d[i] = a * b;
+  }
+}
+
+template <uint32_t OP>
+__device__ __forceinline__ bool reduce_dispatch(uint32_t dt, char* dst, const char* src, uint64_t bytes) {
+  switch (dt) {
+    case DT_F32: reduce_range_f<DT_F32, OP>(dst, src, bytes); return true;
+    case DT_BF16: reduce_range_f<DT_BF16, OP>(dst, src, bytes); return true;
+    case DT_F16: reduce_range_f<DT_F16, OP>(dst, src, bytes); return true;
+    case DT_FP8_E4M3: reduce_range_f<DT_FP8_E4M3, OP>(dst, src, bytes); return true;
+    case DT_I32: reduce_range_i<int32_t, OP>(dst, src, bytes); return true;
+    case DT_I64: reduce_range_i<long long, OP>(dst, src, bytes); return true;
+    case DT_F64: reduce_range_i<double, OP>(dst, src, bytes); return true;
+    case DT_U8: reduce_range_i<uint8_t, OP>(dst, src, bytes); return true;
+    default: return false;
+  }
+}
+
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ void mm_ld_reduce_range(char* dst, const char* mc_src, uint64_t bytes) {
+  const uint64_t nvec = bytes >> 4;
+  for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x)
+    st16(dst + (i << 4), multimem_ld_reduce<DT, OP>(mc_src + (i << 4)));
+}
+
+__device__ __forceinline__ bool mm_ld_reduce_dispatch(uint32_t dt, uint32_t op, char* dst, const char* mc, uint64_t bytes) {
+#define PCCL_MM(DT_, OP_) if (dt == DT_ && op == OP_) { mm_ld_reduce_range<DT_, OP_>(dst, mc, bytes); return true; }
+  PCCL_MM(DT_F32, RED_SUM)
+  PCCL_MM(DT_BF16, RED_SUM) PCCL_MM(DT_BF16, RED_MAX) PCCL_MM(DT_BF16, RED_MIN)
+  PCCL_MM(DT_F16, RED_SUM) PCCL_MM(DT_F16, RED_MAX) PCCL_MM(DT_F16, RED_MIN)
+#undef PCCL_MM
+  return false;
+}
+
+__device__ __forceinline__ void mm_st_range(char* mc_dst, const char* src, uint64_t bytes) {
+  const uint64_t nvec = bytes >> 4;
+  for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) multimem_st(mc_dst + (i << 4), ld16(src + (i << 4)));
+}
+
+__global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ InterpLaunch L) {
+  const InterpRank& R = L.r[blockIdx.y];
+  const int stream = blockIdx.x;
+  if (stream >= R.n_streams) return;
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+
+  const World& W = L.w;
+  const int me = R.rank;
+  uint64_t* my_sig = reinterpret_cast<uint64_t*>(W.heap[me] + W.signal_off) + L.slot_base;
+  const Instr* prog = R.instrs + R.stream_start[stream];
+
+  // Address of (rank q, buffer b, offset) or nullptr when q's buffer b is not reachable.
+  auto resolve = [&](int q, uint32_t b, uint64_t off) -> char* {
+    if (b == BUF_SCRATCH) return W.heap[q] + R.scratch_off + off;
+    if (q == me) return (b == BUF_INPUT ? R.input : R.output) + off;
+    long long ho = b == BUF_INPUT ? R.input_heap_off : R.output_heap_off;
+    return ho < 0 ? nullptr : W.heap[q] + ho + off;
+  };
+  auto resolve_mc = [&](uint32_t b, uint64_t off) -> char* {
+    if (!W.mc_heap) return nullptr;
+    if (b == BUF_SCRATCH) return W.mc_heap + R.scratch_off + off;
+    long long ho = b == BUF_INPUT ? R.input_heap_off : R.output_heap_off;
+    return ho < 0 ? nullptr : W.mc_heap + ho + off;
+  };
+
+  for (uint32_t pc = 0;; ++pc) {
+    const Instr in = prog[pc];
+    if (in.op == OP_END) break;
+    uint32_t fail = 0;
+    switch (in.op) {
+      case OP_NOP: break;
+      case OP_COPY:
+      case OP_REDUCE:
+      case OP_MM_LD_REDUCE:
+      case OP_MM_ST: {
+        if (in.bytes == 0) break;
+        if (L.bounds_check && (in.src_off + in.bytes > R.buf_bytes[in.src_buf] || in.dst_off + in.bytes > R.buf_bytes[in.dst_buf])) {
+          fail = ST_BOUNDS;
+          break;
+        }
+        if (in.op == OP_COPY || in.op == OP_REDUCE) {
+          char* s = resolve(in.src_rank, in.src_buf, in.src_off);
+          char* d = resolve(in.dst_rank, in.dst_buf, in.dst_off);
+          if (!s || !d) { fail = ST_UNSUPPORTED; break; }
+          if (in.op == OP_COPY) {
+            if (s != d) copy_range(d, s, in.bytes);
+          } else {
+            bool ok = false;
+            switch (L.redop) {
+              case RED_SUM: ok = reduce_dispatch<RED_SUM>(L.dtype, d, s, in.bytes); break;
+              case RED_MAX: ok = reduce_dispatch<RED_MAX>(L.dtype, d, s, in.bytes); break;
+              case RED_MIN: ok = reduce_dispatch<RED_MIN>(L.dtype, d, s, in.bytes); break;
+              case RED_PROD: ok = reduce_dispatch<RED_PROD>(L.dtype, d, s, in.bytes); break;
+            }
+            if (!ok) fail = ST_UNSUPPORTED;
+          }
+        } else if (in.op == OP_MM_LD_REDUCE) {
+          char* mc = resolve_mc(in.src_buf, in.src_off);
+          char* d = resolve(me, in.dst_buf, in.dst_off);
+          if (!mc || !d || ((reinterpret_cast<uintptr_t>(mc) | reinterpret_cast<uintptr_t>(d) | in.bytes) & 15) ||
+              !mm_ld_reduce_dispatch(L.dtype, L.redop, d, mc, in.bytes))
+            fail = ST_UNSUPPORTED;
+        } else {
+          char* mc = resolve_mc(in.dst_buf, in.dst_off);
+          char* s = resolve(me, in.src_buf, in.src_off);
+          if (!mc || !s || ((reinterpret_cast<uintptr_t>(mc) | reinterpret_cast<uintptr_t>(s) | in.bytes) & 15)) fail = ST_UNSUPPORTED;
+          else mm_st_range(mc, s, in.bytes);
+        }
+        break;
+      }
+      case OP_NOTIFY: {
+        __syncthreads();   // every thread's stores of the preceding instruction are issued
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          uint64_t* sig = reinterpret_cast<uint64_t*>(W.heap[in.dst_rank] + W.signal_off) + L.slot_base + in.slot;
+          red_add_release_sys(sig, 1);
+        }
+        break;
+      }
+      case OP_WAIT: {
+        if (threadIdx.x == 0) {
+          uint64_t target = L.epoch * in.count + in.value;
+          if (!wait_ge(my_sig + in.slot, target, L.spin_limit, R.status)) s_fail = ST_TIMEOUT;
+        }
+        __syncthreads();
+        fail = s_fail;
+        break;
+      }
+      case OP_BARRIER: {
+        __syncthreads();
+        if (threadIdx.x < static_cast<uint32_t>(W.world)) {
+          __threadfence_system();
+          uint64_t* sig = reinterpret_cast<uint64_t*>(W.heap[threadIdx.x] + W.signal_off) + L.slot_base + in.slot;
+          red_add_release_sys(sig, 1);
+        }
+        if (threadIdx.x == 0) {
+          uint64_t target = static_cast<uint64_t>(W.world) * (L.epoch * in.count + in.value);
+          if (!wait_ge(my_sig + in.slot, target, L.spin_limit, R.status)) s_fail = ST_TIMEOUT;
+        }
+        __syncthreads();
+        fail = s_fail;
+        break;
+      }
+      default: fail = ST_BAD_OP;
+    }
+    if (fail) {
+      if (threadIdx.x == 0) report(R.status, fail, static_cast<uint32_t>(stream), pc, in.op);
+      return;
+    }
+  }
+}
+
+__global__ void wait_timeout_probe_kernel(uint64_t* flag, uint64_t spin_limit, uint32_t* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (!wait_ge(flag, 1, spin_limit, nullptr)) report(status, ST_TIMEOUT, 0, 0, OP_WAIT);
+  }
+}
+
+}  // namespace
+
+int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream) {
+  int max_streams = 0;
+  for (int v = 0; v < L.nvirt; ++v) max_streams = L.r[v].n_streams > max_streams ? L.r[v].n_streams : max_streams;
+  if (max_streams == 0) return 0;
+  dim3 grid(max_streams, L.nvirt), block(threads);
+  void* args[] = {const_cast<InterpLaunch*>(&L)};
+  // Streams wait on one another, so every CTA must be resident: a cooperative launch refuses
+  // (instead of hanging) when the grid does not fit.
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(interp_kernel), grid, block, args, 0, stream));
+}
+
+int launchWaitTimeoutProbe(uint64_t* flag, uint64_t spin_limit, uint32_t* status, cudaStream_t stream) {
+  wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(flag, spin_limit, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int deviceSmCount() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+const char* cudaErrorName(int err) { return cudaGetErrorString(static_cast<cudaError_t>(err)); }
+
+}  // namespace pccl

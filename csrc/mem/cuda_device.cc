@@ -1,0 +1,424 @@
+#include "cuda_device.h"
+
+#include <cuda.h>
+#include <dlfcn.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <stdexcept>
+
+#include "../cluster/wire.h"
+#include "../common/json.h"
+#include "../common/log.h"
+
+namespace pccl {
+
+namespace {
+
+// ---- driver API, resolved lazily -------------------------------------------------------------
+struct Driver {
+  bool ok = false;
+  std::string why;
+  CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+  CUresult (*CtxGetDevice)(CUdevice*) = nullptr;
+  CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice) = nullptr;
+  CUresult (*MemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*MemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*MemAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*MemAddressFree)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*MemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*MemUnmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  CUresult (*MemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+  CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  CUresult (*MulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*) = nullptr;
+  CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice) = nullptr;
+  CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t, unsigned long long) = nullptr;
+  CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
+  CUresult (*MulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags) = nullptr;
+};
+
+Driver& drv() {
+  static Driver d;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* lib = ::dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) {
+      d.why = "libcuda.so.1 not found (no NVIDIA driver on this machine)";
+      return;
+    }
+    using GetProc = CUresult (*)(const char*, void**, int, cuuint64_t, CUdriverProcAddressQueryResult*);
+    auto getproc = reinterpret_cast<GetProc>(::dlsym(lib, "cuGetProcAddress_v2"));
+    auto load = [&](const char* name, void** fn) {
+      *fn = nullptr;
+      if (getproc) {
+        CUdriverProcAddressQueryResult st;
+        if (getproc(name, fn, 12040, CU_GET_PROC_ADDRESS_DEFAULT, &st) == CUDA_SUCCESS && *fn) return true;
+      }
+      *fn = ::dlsym(lib, name);
+      return *fn != nullptr;
+    };
+    bool all = true;
+#define PCCL_LOAD(field, sym) all = load(sym, reinterpret_cast<void**>(&d.field)) && all
+    PCCL_LOAD(GetErrorString, "cuGetErrorString");
+    PCCL_LOAD(CtxGetDevice, "cuCtxGetDevice");
+    PCCL_LOAD(DeviceGetAttribute, "cuDeviceGetAttribute");
+    PCCL_LOAD(MemGetAllocationGranularity, "cuMemGetAllocationGranularity");
+    PCCL_LOAD(MemCreate, "cuMemCreate");
+    PCCL_LOAD(MemRelease, "cuMemRelease");
+    PCCL_LOAD(MemAddressReserve, "cuMemAddressReserve");
+    PCCL_LOAD(MemAddressFree, "cuMemAddressFree");
+    PCCL_LOAD(MemMap, "cuMemMap");
+    PCCL_LOAD(MemUnmap, "cuMemUnmap");
+    PCCL_LOAD(MemSetAccess, "cuMemSetAccess");
+    PCCL_LOAD(MemExportToShareableHandle, "cuMemExportToShareableHandle");
+    PCCL_LOAD(MemImportFromShareableHandle, "cuMemImportFromShareableHandle");
+    bool mc = true;
+#define PCCL_LOAD_MC(field, sym) mc = load(sym, reinterpret_cast<void**>(&d.field)) && mc
+    PCCL_LOAD_MC(MulticastCreate, "cuMulticastCreate");
+    PCCL_LOAD_MC(MulticastAddDevice, "cuMulticastAddDevice");
+    PCCL_LOAD_MC(MulticastBindMem, "cuMulticastBindMem");
+    PCCL_LOAD_MC(MulticastUnbind, "cuMulticastUnbind");
+    PCCL_LOAD_MC(MulticastGetGranularity, "cuMulticastGetGranularity");
+    if (!mc) d.MulticastCreate = nullptr;
+    d.ok = all;
+    if (!all) d.why = "libcuda.so.1 lacks the virtual memory management API";
+  });
+  return d;
+}
+
+thread_local std::string g_last_error;
+
+void check(CUresult r, const char* what) {
+  if (r == CUDA_SUCCESS) return;
+  const char* s = nullptr;
+  if (drv().GetErrorString) drv().GetErrorString(r, &s);
+  g_last_error = std::string(what) + " failed: " + (s ? s : "unknown CUDA error") + " (" + std::to_string(r) + ")";
+  throw std::runtime_error("cuda device: " + g_last_error);
+}
+
+CUdevice currentDevice() {
+  CUdevice dev;
+  check(drv().CtxGetDevice(&dev), "cuCtxGetDevice (is a CUDA context current on this thread?)");
+  return dev;
+}
+
+CUmemAllocationProp allocProp(CUdevice dev) {
+  CUmemAllocationProp p{};
+  p.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  p.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  p.location.id = dev;
+  p.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  return p;
+}
+
+size_t alignUp(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+std::string CudaDevice::lastError() { return g_last_error; }
+
+CudaDevice::CudaDevice() {}
+
+CudaDevice::~CudaDevice() {
+  serving_.store(false);
+  if (server_fd_ >= 0) wire::shutdownFd(server_fd_);
+  if (server_.joinable()) server_.join();
+  wire::closeFd(server_fd_);
+  try {
+    multicastRelease();
+  } catch (...) {
+  }
+  std::map<void*, Alloc> allocs;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    allocs.swap(allocs_);
+  }
+  if (!drv().ok) return;
+  for (auto& kv : allocs) {
+    CUdeviceptr p = reinterpret_cast<CUdeviceptr>(kv.first);
+    drv().MemUnmap(p, kv.second.bytes);
+    drv().MemAddressFree(p, kv.second.bytes);
+    drv().MemRelease(kv.second.handle);
+    if (kv.second.fd >= 0) ::close(kv.second.fd);
+  }
+}
+
+bool CudaDevice::allocatorAvailable() {
+  if (!drv().ok) return false;
+  CUdevice dev;
+  if (drv().CtxGetDevice(&dev) != CUDA_SUCCESS) return false;
+  int vmm = 0;
+  drv().DeviceGetAttribute(&vmm, CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED, dev);
+  return vmm != 0;
+}
+
+int CudaDevice::deviceOrdinal() { return static_cast<int>(currentDevice()); }
+
+void* CudaDevice::mapHandle(unsigned long long h, size_t bytes) {
+  CUdevice dev = currentDevice();
+  CUdeviceptr va = 0;
+  check(drv().MemAddressReserve(&va, bytes, 0, 0, 0), "cuMemAddressReserve");
+  CUresult r = drv().MemMap(va, bytes, 0, h, 0);
+  if (r != CUDA_SUCCESS) {
+    drv().MemAddressFree(va, bytes);
+    check(r, "cuMemMap");
+  }
+  CUmemAccessDesc acc{};
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = dev;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = drv().MemSetAccess(va, bytes, &acc, 1);
+  if (r != CUDA_SUCCESS) {
+    drv().MemUnmap(va, bytes);
+    drv().MemAddressFree(va, bytes);
+    check(r, "cuMemSetAccess");
+  }
+  return reinterpret_cast<void*>(va);
+}
+
+void* CudaDevice::allocate(size_t bytes) {
+  std::string unused;
+  return allocateIpcBuffer(bytes, &unused);
+}
+
+void* CudaDevice::allocateIpcBuffer(size_t bytes, std::string* handle) {
+  if (!drv().ok) throw std::runtime_error("cuda device: " + drv().why);
+  CUdevice dev = currentDevice();
+  CUmemAllocationProp prop = allocProp(dev);
+  size_t gran = 0;
+  check(drv().MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED), "cuMemGetAllocationGranularity");
+  if (gran < (2u << 20)) gran = 2u << 20;
+  size_t size = alignUp(bytes, gran);
+  Alloc a;
+  check(drv().MemCreate(&a.handle, size, &prop, 0), "cuMemCreate");
+  a.bytes = size;
+  a.id = next_id_.fetch_add(1);
+  void* ptr = nullptr;
+  try {
+    ptr = mapHandle(a.handle, size);
+    int fd = -1;
+    check(drv().MemExportToShareableHandle(&fd, a.handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+          "cuMemExportToShareableHandle");
+    a.fd = fd;
+  } catch (...) {
+    if (ptr) {
+      drv().MemUnmap(reinterpret_cast<CUdeviceptr>(ptr), size);
+      drv().MemAddressFree(reinterpret_cast<CUdeviceptr>(ptr), size);
+    }
+    drv().MemRelease(a.handle);
+    throw;
+  }
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    allocs_[ptr] = a;
+    exported_fds_[a.id] = a.fd;
+  }
+  startFdServer();
+  Json h = Json::object();
+  h.set("size", static_cast<uint64_t>(size));
+  h.set("id", a.id);
+  h.set("pid", static_cast<int64_t>(::getpid()));
+  h.set("sock", sock_name_);
+  h.set("device", static_cast<int>(dev));
+  if (handle) *handle = h.dump();
+  return ptr;
+}
+
+void CudaDevice::startFdServer() {
+  std::lock_guard<std::mutex> g(mu_);
+  if (serving_.load()) return;
+  sock_name_ = "pccl-vmm-" + std::to_string(::getpid()) + "-" + std::to_string(reinterpret_cast<uintptr_t>(this) & 0xffff);
+  server_fd_ = wire::unixListen(sock_name_);
+  if (server_fd_ < 0) throw std::runtime_error("cuda device: cannot create the handle-passing socket");
+  serving_.store(true);
+  server_ = std::thread([this] { fdServerLoop(); });
+}
+
+void CudaDevice::fdServerLoop() {
+  while (serving_.load()) {
+    int c = wire::acceptOne(server_fd_, 100);
+    if (c < 0) continue;
+    uint64_t id = 0;
+    if (wire::recvAll(c, &id, sizeof(id))) {
+      int fd = -1;
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = exported_fds_.find(id);
+        if (it != exported_fds_.end()) fd = it->second;
+      }
+      wire::sendFd(c, fd, id);
+    }
+    wire::closeFd(c);
+  }
+}
+
+static int fetchFd(const std::string& sock, uint64_t id) {
+  int c = wire::unixConnect(sock, 10000);
+  if (c < 0) throw std::runtime_error("cuda device: cannot reach peer handle socket " + sock);
+  int fd = -1;
+  uint64_t tag = 0;
+  bool ok = wire::sendAll(c, &id, sizeof(id)) && wire::recvFd(c, &fd, &tag);
+  wire::closeFd(c);
+  if (!ok || fd < 0 || tag != id) throw std::runtime_error("cuda device: peer did not hand over the memory handle");
+  return fd;
+}
+
+void* CudaDevice::mapBuffer(const std::string& handle) {
+  if (!drv().ok) throw std::runtime_error("cuda device: " + drv().why);
+  Json h = Json::parse(handle);
+  size_t size = static_cast<size_t>(h["size"].asInt());
+  uint64_t id = static_cast<uint64_t>(h["id"].asInt());
+  int fd = fetchFd(h["sock"].asString(), id);
+  Alloc a;
+  CUresult r = drv().MemImportFromShareableHandle(&a.handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                                  CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  ::close(fd);
+  check(r, "cuMemImportFromShareableHandle");
+  a.bytes = size;
+  a.imported = true;
+  void* ptr = nullptr;
+  try {
+    ptr = mapHandle(a.handle, size);
+  } catch (...) {
+    drv().MemRelease(a.handle);
+    throw;
+  }
+  std::lock_guard<std::mutex> g(mu_);
+  allocs_[ptr] = a;
+  return ptr;
+}
+
+void CudaDevice::unmapBuffer(void* ptr) { deallocate(ptr); }
+
+void CudaDevice::deallocate(void* ptr) {
+  Alloc a;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = allocs_.find(ptr);
+    if (it == allocs_.end()) return;
+    a = it->second;
+    allocs_.erase(it);
+    exported_fds_.erase(a.id);
+  }
+  if (ptr == mc_local_) multicastRelease();
+  CUdeviceptr p = reinterpret_cast<CUdeviceptr>(ptr);
+  drv().MemUnmap(p, a.bytes);
+  drv().MemAddressFree(p, a.bytes);
+  drv().MemRelease(a.handle);
+  if (a.fd >= 0) ::close(a.fd);
+}
+
+size_t CudaDevice::allocatedSize(void* ptr) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = allocs_.find(ptr);
+  return it == allocs_.end() ? 0 : it->second.bytes;
+}
+
+// ---- multicast ---------------------------------------------------------------------------------
+bool CudaDevice::multicastSupported() {
+  if (!drv().ok || !drv().MulticastCreate) return false;
+  CUdevice dev;
+  if (drv().CtxGetDevice(&dev) != CUDA_SUCCESS) return false;
+  int mc = 0;
+  drv().DeviceGetAttribute(&mc, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, dev);
+  return mc != 0;
+}
+
+size_t CudaDevice::multicastGranularity(int num_devices, size_t bytes) {
+  CUmulticastObjectProp p{};
+  p.numDevices = static_cast<unsigned>(num_devices);
+  p.size = bytes;
+  p.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  size_t g = 0;
+  check(drv().MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_RECOMMENDED), "cuMulticastGetGranularity");
+  return g;
+}
+
+std::string CudaDevice::multicastCreate(size_t bytes, int num_devices) {
+  if (!multicastSupported()) throw std::runtime_error("cuda device: multicast is not supported here");
+  CUmulticastObjectProp p{};
+  p.numDevices = static_cast<unsigned>(num_devices);
+  p.size = bytes;
+  p.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  CUmemGenericAllocationHandle h;
+  check(drv().MulticastCreate(&h, &p), "cuMulticastCreate");
+  int fd = -1;
+  CUresult r = drv().MemExportToShareableHandle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+  if (r != CUDA_SUCCESS) {
+    drv().MemRelease(h);
+    check(r, "cuMemExportToShareableHandle(multicast)");
+  }
+  uint64_t id = next_id_.fetch_add(1);
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    exported_fds_[id] = fd;
+    mc_handle_ = h;
+    mc_bytes_ = bytes;
+  }
+  startFdServer();
+  Json j = Json::object();
+  j.set("size", static_cast<uint64_t>(bytes));
+  j.set("id", id);
+  j.set("pid", static_cast<int64_t>(::getpid()));
+  j.set("sock", sock_name_);
+  j.set("num_devices", num_devices);
+  return j.dump();
+}
+
+void CudaDevice::multicastJoin(const std::string& handle) {
+  Json j = Json::parse(handle);
+  size_t bytes = static_cast<size_t>(j["size"].asInt());
+  if (j["pid"].asInt() != static_cast<int64_t>(::getpid()) || mc_handle_ == 0) {
+    int fd = fetchFd(j["sock"].asString(), static_cast<uint64_t>(j["id"].asInt()));
+    CUmemGenericAllocationHandle h;
+    CUresult r = drv().MemImportFromShareableHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                                    CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+    ::close(fd);
+    check(r, "cuMemImportFromShareableHandle(multicast)");
+    mc_handle_ = h;
+    mc_bytes_ = bytes;
+  }
+  check(drv().MulticastAddDevice(mc_handle_, currentDevice()), "cuMulticastAddDevice");
+}
+
+void* CudaDevice::multicastBind(void* local_ptr) {
+  Alloc a;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = allocs_.find(local_ptr);
+    if (it == allocs_.end()) throw std::runtime_error("cuda device: multicastBind of an unknown allocation");
+    a = it->second;
+  }
+  if (a.bytes < mc_bytes_) throw std::runtime_error("cuda device: allocation smaller than the multicast object");
+  check(drv().MulticastBindMem(mc_handle_, 0, a.handle, 0, mc_bytes_, 0), "cuMulticastBindMem");
+  mc_bound_ = true;
+  mc_local_ = local_ptr;
+  mc_va_ = mapHandle(mc_handle_, mc_bytes_);
+  return mc_va_;
+}
+
+void CudaDevice::multicastRelease() {
+  if (!drv().ok || mc_handle_ == 0) return;
+  if (mc_va_) {
+    CUdeviceptr p = reinterpret_cast<CUdeviceptr>(mc_va_);
+    drv().MemUnmap(p, mc_bytes_);
+    drv().MemAddressFree(p, mc_bytes_);
+    mc_va_ = nullptr;
+  }
+  if (mc_bound_) {
+    CUdevice dev;
+    if (drv().CtxGetDevice(&dev) == CUDA_SUCCESS) drv().MulticastUnbind(mc_handle_, dev, 0, mc_bytes_);
+    mc_bound_ = false;
+  }
+  drv().MemRelease(mc_handle_);
+  mc_handle_ = 0;
+  mc_local_ = nullptr;
+}
+
+void registerCudaDevice() {
+  if (!getDev("cuda")) regDev("cuda", std::make_shared<CudaDevice>());
+}
+
+}  // namespace pccl

@@ -1,0 +1,29 @@
+"""Loader of the native extension.  Importing it never silently falls back: if ``_C.so`` is
+missing it is built in-tree, and if that fails the import error says why."""
+from __future__ import annotations
+
+import importlib
+import os
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+
+
+def load():
+    so = _HERE / "_C.so"
+    if not so.exists() or os.environ.get("PCCL_REBUILD") == "1":
+        from . import _build
+        _build.build(verbose=os.environ.get("PCCL_BUILD_VERBOSE", "0") == "1")
+    try:
+        return importlib.import_module("pccl_b200._C")
+    except ImportError as e:  # stale object from another toolchain: rebuild once, then fail loudly
+        from . import _build
+        _build.build(verbose=True, force=True)
+        try:
+            return importlib.import_module("pccl_b200._C")
+        except ImportError:
+            raise ImportError(f"pccl_b200: native extension cannot be loaded ({e}); "
+                              f"run `python -m pccl_b200._build` to see the compiler output") from e
+
+
+C = load()

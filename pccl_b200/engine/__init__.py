@@ -1,0 +1,246 @@
+"""``pccl.engine``: Python face of the C++ engine.
+
+The reference leaves this package empty (pccl/engine/__init__.py is 0 bytes) and binds the C++
+class directly as ``pccl.engine_c.Engine`` with ``initEngine / regOp / exeOp / exportEndpoint /
+joinCluster / exitCluster`` (csrc/python_api.cc:13-20).  ``Engine`` here keeps those six names and
+adds the torch-facing conveniences: tensors instead of pointers, a rendezvous through
+``torch.distributed`` when one exists, symmetric tensors, NVLS bring-up and status checks.
+"""
+from __future__ import annotations
+
+import json
+import os
+import tempfile
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .._native import C
+from ..lang import CollectiveIR, to_schedule, verify
+from ..lang import algorithms as _alg
+
+engine_c = C     # the reference's module name for the raw bindings
+
+_DTYPE_NAMES = {
+    torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16", torch.float64: "f64",
+    torch.int32: "i32", torch.int64: "i64", torch.uint8: "u8", torch.int8: "u8",
+}
+if hasattr(torch, "float8_e4m3fn"):
+    _DTYPE_NAMES[torch.float8_e4m3fn] = "fp8_e4m3"
+
+STATUS_NAMES = {0: "ok", 1: "timeout", 2: "bounds", 3: "bad_op", 4: "unsupported", 5: "peer_gone"}
+
+
+class PcclError(RuntimeError):
+    pass
+
+
+class PcclTimeout(PcclError):
+    """A bounded wait ran out: some peer never signalled (it left, died, or never launched)."""
+
+
+def dtype_name(dt: torch.dtype) -> str:
+    try:
+        return _DTYPE_NAMES[dt]
+    except KeyError:
+        raise PcclError(f"unsupported dtype {dt}") from None
+
+
+class _CudaBlob:
+    """Exposes a raw device range to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int, owner=None):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+        self._owner = owner
+
+
+class Engine:
+    """One rank of a PCCL job.
+
+    >>> eng = Engine(rank, world); eng.initEngine(); eng.joinCluster("127.0.0.1:29700")
+    >>> eng.regOp("ar", ring_allreduce(world))         # a CollectiveIR, a JSON path or JSON text
+    >>> eng.exeOp("ar", x, y)
+    """
+
+    def __init__(self, rank: int, world: int):
+        self._e = C.Engine(rank, world)
+        self.rank, self.world = rank, world
+        self._tmpfiles: List[str] = []
+        self._initialized = False
+
+    # -- the six reference methods ---------------------------------------------------------------
+    def initEngine(self, device: str = "auto", heap_bytes: int = 0) -> None:
+        if device == "auto":
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        if device == "cuda":
+            torch.cuda.current_device()           # make the primary context current on this thread
+            torch.zeros(1, device="cuda")
+        self._e.initEngine(device, int(heap_bytes))
+        self.device = device
+        self._initialized = True
+
+    def regOp(self, name: str, program: Union[str, CollectiveIR, dict], check: bool = True) -> None:
+        """Register a collective program under ``name``.  ``program`` is a ``CollectiveIR`` (verified
+        and lowered here), a schedule dict, JSON text, or the path of a schedule file."""
+        if isinstance(program, CollectiveIR):
+            if check:
+                verify(program).raise_if_failed()
+            program = to_schedule(program)
+        if isinstance(program, dict):
+            program = json.dumps(program)
+        self._e.regOp(name, program)
+
+    def exeOp(self, name: str, input: torch.Tensor, output: Optional[torch.Tensor] = None, *,
+              width: int = 1, lane: int = 0, stream: Optional["torch.cuda.Stream"] = None,
+              check: Optional[bool] = None) -> int:
+        """Run a registered program on ``input`` (-> ``output``).  ``width`` replicates every channel
+        (more CTAs or threads: runtime resource control); ``lane`` picks the workspace lane so that
+        ops on different lanes may overlap on different streams."""
+        if not input.is_contiguous() or (output is not None and not output.is_contiguous()):
+            raise PcclError("exeOp needs contiguous tensors")
+        out = input if output is None else output
+        sh = 0
+        if input.is_cuda:
+            sh = (stream or torch.cuda.current_stream()).cuda_stream
+        st = self._e.exeOp(name, input.data_ptr(), out.data_ptr(), input.numel() * input.element_size(),
+                           dtype_name(input.dtype), int(width), int(lane), int(sh))
+        if check is None:
+            check = not input.is_cuda
+        if check:
+            if input.is_cuda:
+                st = self.check_status(lane)[0]
+            if st != 0:
+                exc = PcclTimeout if st == 1 else PcclError
+                raise exc(f"exeOp('{name}') finished with status {STATUS_NAMES.get(st, st)}")
+        return st
+
+    def exportEndpoint(self) -> str:
+        return self._e.exportEndpoint()
+
+    def joinCluster(self, master_endpoint: str, timeout_ms: int = 60000) -> None:
+        self._e.joinCluster(master_endpoint, timeout_ms)
+
+    def exitCluster(self) -> None:
+        self._e.exitCluster()
+
+    # -- rendezvous through torch.distributed ----------------------------------------------------
+    def connect(self, group=None, nvls: Optional[bool] = None) -> None:
+        """Exchange endpoint documents over an existing ``torch.distributed`` group, map every
+        peer's heap and (on NVSwitch machines) bind the heap to an NVLS multicast object."""
+        import torch.distributed as dist
+        docs: List[Optional[str]] = [None] * self.world
+        dist.all_gather_object(docs, self.exportEndpoint(), group=group)
+        self._e.importEndpoints([d for d in docs if d is not None])
+        if nvls is None:
+            nvls = os.environ.get("PCCL_NVLS", "1") != "0"
+        if self.device == "cuda" and nvls and self.world > 1:
+            flags = [None] * self.world
+            dist.all_gather_object(flags, bool(self._e.multicastSupported()), group=group)
+            if all(flags):
+                handle = [self._e.mcCreate() if self.rank == 0 else None]
+                dist.broadcast_object_list(handle, src=0, group=group)
+                self._e.mcJoin(handle[0])
+                dist.barrier(group=group)
+                self._e.mcBind()
+                dist.barrier(group=group)
+        dist.barrier(group=group)
+
+    # -- symmetric memory ------------------------------------------------------------------------
+    def symmetric_tensor(self, shape: Sequence[int], dtype: torch.dtype, align: int = 256) -> torch.Tensor:
+        """A tensor inside the symmetric heap.  Every rank must allocate the same sequence of shapes,
+        which gives the tensor the same heap offset everywhere (peers address it by offset)."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        off = self._e.allocSymmetric(max(nbytes, 16), align)
+        return self.tensor_at(off, shape, dtype)
+
+    def tensor_at(self, heap_off: int, shape: Sequence[int], dtype: torch.dtype, rank: Optional[int] = None) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        base = self._e.heapBase(self.rank if rank is None else rank)
+        if base == 0:
+            raise PcclError("that rank's heap is not mapped")
+        if self.device == "cuda":
+            t = torch.as_tensor(_CudaBlob(base + heap_off, max(nbytes, 1), self), device="cuda")
+        else:
+            import ctypes
+            buf = (ctypes.c_uint8 * max(nbytes, 1)).from_address(base + heap_off)
+            t = torch.frombuffer(buf, dtype=torch.uint8)
+        return t[:nbytes].view(dtype).view(*shape)
+
+    def heap_offset(self, t: torch.Tensor) -> int:
+        off = t.data_ptr() - self._e.heapBase(self.rank)
+        if off < 0 or off >= self._e.heapBytes():
+            raise PcclError("tensor is not inside the symmetric heap")
+        return off
+
+    def is_symmetric(self, t: torch.Tensor) -> bool:
+        off = t.data_ptr() - self._e.heapBase(self.rank)
+        return 0 <= off < self._e.heapBytes()
+
+    def symmetric_mark(self) -> int:
+        return self._e.symmetricMark()
+
+    def symmetric_reset(self, mark: int) -> None:
+        self._e.resetSymmetric(mark)
+
+    @property
+    def has_nvls(self) -> bool:
+        return self._e.mcBase() != 0
+
+    # -- status / introspection --------------------------------------------------------------------
+    def check_status(self, lane: int = 0) -> List[int]:
+        return list(self._e.checkStatus(lane))
+
+    def raise_on_status(self, lane: int = 0, what: str = "collective") -> None:
+        st = self.check_status(lane)
+        if st[0] != 0:
+            exc = PcclTimeout if st[0] == 1 else PcclError
+            raise exc(f"{what}: status {STATUS_NAMES.get(st[0], st[0])} (detail {st[1:]})")
+
+    def stats(self) -> Dict:
+        return json.loads(self._e.stats())
+
+    def layout(self) -> Dict:
+        return dict(self._e.layout())
+
+    @property
+    def raw(self):
+        return self._e
+
+    # elastic membership
+    def alive_ranks(self) -> List[int]:
+        return list(self._e.aliveRanks())
+
+    def wait_for_departure(self, rank: int, timeout_ms: int = 10000) -> bool:
+        return bool(self._e.waitForDeparture(rank, timeout_ms))
+
+    def resize_world(self) -> Dict[int, int]:
+        return dict(self._e.resizeWorld())
+
+    def last_resize(self) -> Dict[int, int]:
+        return dict(self._e.lastResize())
+
+    def rebind(self, new_rank: int, new_world: int) -> None:
+        self._e.rebind(new_rank, new_world)
+        self.rank, self.world = new_rank, new_world
+
+    def inject_fault(self, kind: str) -> None:
+        self._e.injectFault(kind)
+
+
+class LaunchEnvironments:
+    """Option registry (reference: ``utils.LaunchEnvironments`` in csrc/python_api.cc:22-27)."""
+    listOpt = staticmethod(C.utils.LaunchEnvironments.listOpt)
+    getEnv = staticmethod(C.utils.LaunchEnvironments.getEnv)
+    registerOpt = staticmethod(C.utils.LaunchEnvironments.registerOpt)
+    helpOf = staticmethod(C.utils.LaunchEnvironments.helpOf)
+    setOverride = staticmethod(C.utils.LaunchEnvironments.setOverride)
+
+
+__all__ = ["Engine", "LaunchEnvironments", "PcclError", "PcclTimeout", "engine_c", "dtype_name", "STATUS_NAMES"]

@@ -1,0 +1,13 @@
+"""``pccl.lang``: the collective-program DSL (IR, algorithm library, verifier, lowering)."""
+from .dag import DirectedGraph
+from .ir import (BUFFER_KINDS, Chunk, CollectiveIR, Device, DeviceType, Link, PrimitiveOp,
+                 PrimitiveOpType)
+from .verify import Report, VerificationError, port_load, verify
+from .lower import LoweringError, OPCODES, check_lowered_deadlock_free, lower, to_schedule
+from . import algorithms
+from .algorithms import ALGORITHMS, build
+
+__all__ = ["DirectedGraph", "BUFFER_KINDS", "Chunk", "CollectiveIR", "Device", "DeviceType", "Link",
+           "PrimitiveOp", "PrimitiveOpType", "Report", "VerificationError", "port_load", "verify",
+           "LoweringError", "OPCODES", "check_lowered_deadlock_free", "lower", "to_schedule",
+           "algorithms", "ALGORITHMS", "build"]

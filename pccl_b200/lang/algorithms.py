@@ -1,0 +1,464 @@
+"""Library of collective programs written in the IR.
+
+The reference ships no program at all (example/collective/allreduce.py is empty); these are the
+programs its vocabulary (pccl/lang/chunk.py:6-55) was evidently meant to express.  Each generator
+returns a ``CollectiveIR`` whose pre/post-conditions the symbolic verifier can check and whose
+JSON the CPU executor and the GPU interpreter kernel both run.
+
+Conventions
+-----------
+* Remote ranks may only touch the ``scratch`` buffer (the engine's symmetric workspace) unless
+  ``direct=True``, which states that the user's input/output tensors were themselves allocated
+  from the symmetric heap and may be read or written by peers.
+* ``channels`` splits every chunk ``channels`` ways; one channel = one executor worker (one CTA
+  group on the GPU, one thread on the CPU).
+* On NVSwitch every pair of GPUs has the same bandwidth and the limit is each GPU's port, so the
+  one-step "direct" forms are the bandwidth-optimal ones; rings are kept for link-limited
+  topologies, for the CPU/TCP transport and as verifier test material.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+from .ir import Chunk, CollectiveIR, Device, DeviceType, PrimitiveOpType
+
+
+def _new(name: str, collective: str, n: int, units: int, buffers, device_type=DeviceType.CUDA,
+         redop: str = "sum", in_place: bool = False, block_units: Optional[int] = None) -> CollectiveIR:
+    """``block_units``: a buffer is a run of blocks of that many units, and a block is what maps
+    onto an exact byte count at run time (a shard for gather/scatter/all-to-all, the whole vector
+    for all-reduce); every buffer size is a multiple of it."""
+    ir = CollectiveIR(name, collective, units, redop, buffers, in_place)
+    ir.attrs["block_units"] = units if block_units is None else block_units
+    for r in range(n):
+        ir.add_device(Device(r, device_type))
+    ir.fully_connect()
+    ir.attrs["world_size"] = n
+    return ir
+
+
+def _all(n: int):
+    return set(range(n))
+
+
+# ---------------------------------------------------------------------------------------------
+# pre/post-condition builders
+# ---------------------------------------------------------------------------------------------
+def allreduce_conditions(ir: CollectiveIR, n: int, units: int, out_buf: str = "output") -> None:
+    ir.set_precondition([Chunk({r}, r, units, 0, "input") for r in range(n)])
+    ir.set_postcondition([Chunk(_all(n), r, units, 0, out_buf) for r in range(n)])
+
+
+def reduce_scatter_conditions(ir: CollectiveIR, n: int, shard: int) -> None:
+    ir.set_precondition([Chunk({r}, r, n * shard, 0, "input") for r in range(n)])
+    ir.set_postcondition([Chunk(_all(n), r, shard, 0, "output", origin=r * shard) for r in range(n)])
+
+
+def allgather_conditions(ir: CollectiveIR, n: int, shard: int) -> None:
+    # origin encodes (source rank, unit) as rank*shard + unit
+    ir.set_precondition([Chunk({r}, r, shard, 0, "input", origin=r * shard) for r in range(n)])
+    post = []
+    for r in range(n):
+        for s in range(n):
+            post.append(Chunk({s}, r, shard, s * shard, "output", origin=s * shard))
+    ir.set_postcondition(post)
+
+
+def alltoall_conditions(ir: CollectiveIR, n: int, blk: int) -> None:
+    # input unit u on rank r has origin r*(n*blk)+u ; output block s on rank d holds input block d of rank s
+    U = n * blk
+    ir.set_precondition([Chunk({r}, r, U, 0, "input", origin=r * U) for r in range(n)])
+    post = []
+    for d in range(n):
+        for s in range(n):
+            post.append(Chunk({s}, d, blk, s * blk, "output", origin=s * U + d * blk))
+    ir.set_postcondition(post)
+
+
+# ---------------------------------------------------------------------------------------------
+# ring algorithms
+# ---------------------------------------------------------------------------------------------
+def ring_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum",
+                   direct: bool = False) -> CollectiveIR:
+    """Ring reduce-scatter followed by ring all-gather: 2(n-1) steps, n*channels chunks."""
+    U = n * channels
+    ir = _new(f"ring_allreduce_n{n}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": U}, device_type, redop)
+    allreduce_conditions(ir, n, U)
+    if n == 1:
+        ir.copy(Chunk({0}, 0, U, 0, "input"), Chunk({0}, 0, U, 0, "output"), step=0)
+        return ir
+    for ch in range(channels):
+        unit = lambda c: c * channels + ch  # noqa: E731  chunk c of this channel
+        # stage the input into the accumulator (output buffer)
+        last = {}   # (rank, chunk) -> op id that last wrote output[chunk] on rank
+        for r in range(n):
+            for c in range(n):
+                last[(r, c)] = ir.copy(Chunk({r}, r, 1, unit(c), "input"),
+                                       Chunk({r}, r, 1, unit(c), "output"), step=0, channel=ch)
+        # reduce-scatter: at step s rank r pushes chunk (r-s) to r+1, which folds it in
+        for s in range(n - 1):
+            new_last = {}
+            for r in range(n):
+                c, nxt = (r - s) % n, (r + 1) % n
+                have = set(((r - k) % n) for k in range(s + 1))
+                push = ir.copy(Chunk(have, r, 1, unit(c), "output"),
+                               Chunk(have, nxt, 1, unit(c), "scratch"),
+                               deps=[last[(r, c)]], step=1 + 2 * s, channel=ch)
+                red = ir.reduce(Chunk(have, nxt, 1, unit(c), "scratch"),
+                                Chunk(have | {nxt}, nxt, 1, unit(c), "output"),
+                                deps=[push, last[(nxt, c)]], step=2 + 2 * s, channel=ch)
+                new_last[(nxt, c)] = red
+            last.update(new_last)
+        # all-gather: rank r now owns chunk (r+1); at step s it forwards chunk (r+1-s)
+        base = 1 + 2 * (n - 1)
+        for s in range(n - 1):
+            new_last = {}
+            for r in range(n):
+                c, nxt = (r + 1 - s) % n, (r + 1) % n
+                if direct:
+                    new_last[(nxt, c)] = ir.copy(Chunk(_all(n), r, 1, unit(c), "output"),
+                                                 Chunk(_all(n), nxt, 1, unit(c), "output"),
+                                                 deps=[last[(r, c)], last[(nxt, c)]],
+                                                 step=base + 2 * s, channel=ch)
+                else:
+                    push = ir.copy(Chunk(_all(n), r, 1, unit(c), "output"),
+                                   Chunk(_all(n), nxt, 1, unit(c), "scratch"),
+                                   deps=[last[(r, c)], last[(nxt, c)]], step=base + 2 * s, channel=ch)
+                    new_last[(nxt, c)] = ir.copy(Chunk(_all(n), nxt, 1, unit(c), "scratch"),
+                                                 Chunk(_all(n), nxt, 1, unit(c), "output"),
+                                                 deps=[push, last[(nxt, c)]],
+                                                 step=base + 1 + 2 * s, channel=ch)
+            last.update(new_last)
+    return ir
+
+
+def ring_allgather(n: int, channels: int = 1, device_type=DeviceType.CUDA,
+                   explicit_signals: bool = False, name: Optional[str] = None) -> CollectiveIR:
+    """Ring all-gather; with ``explicit_signals`` the hand-off uses NOTIFY / GET_NOTIFIED ops
+    written into the program (the double-buffered block rotation of ring attention)."""
+    sh = channels
+    ir = _new(name or f"ring_allgather_n{n}_c{channels}", "allgather", n, sh,
+              {"input": sh, "output": n * sh, "scratch": n * sh}, device_type, block_units=sh)
+    allgather_conditions(ir, n, sh)
+    for ch in range(channels):
+        last = {}
+        for r in range(n):
+            last[(r, r)] = ir.copy(Chunk({r}, r, 1, ch, "input", origin=r * sh + ch),
+                                   Chunk({r}, r, 1, r * sh + ch, "output", origin=r * sh + ch),
+                                   step=0, channel=ch)
+        for s in range(n - 1):
+            new_last = {}
+            for r in range(n):
+                c, nxt = (r - s) % n, (r + 1) % n
+                org = c * sh + ch
+                push = ir.copy(Chunk({c}, r, 1, org, "output", origin=org),
+                               Chunk({c}, nxt, 1, org, "scratch", origin=org),
+                               deps=[last[(r, c)]], step=1 + 2 * s, channel=ch)
+                dep = push
+                if explicit_signals:
+                    nt = ir.notify(r, nxt, deps=[push], step=1 + 2 * s, channel=ch)
+                    dep = ir.get_notified(r, nxt, deps=[nt], step=2 + 2 * s, channel=ch)
+                new_last[(nxt, c)] = ir.copy(Chunk({c}, nxt, 1, org, "scratch", origin=org),
+                                             Chunk({c}, nxt, 1, org, "output", origin=org),
+                                             deps=[dep], step=2 + 2 * s, channel=ch)
+            last.update(new_last)
+    return ir
+
+
+def ring_kv_rotation(n: int, channels: int = 1, device_type=DeviceType.CUDA) -> CollectiveIR:
+    """Ring-attention / blockwise context parallelism: every rank's KV block visits every rank
+    in ring order, one hop per step, hand-offs by explicit NOTIFY / GET_NOTIFIED.  After step s
+    rank r holds the block of rank (r-s-1) mod n in ``output`` at that block's slot."""
+    ir = ring_allgather(n, channels, device_type, explicit_signals=True,
+                        name=f"ring_kv_rotation_n{n}_c{channels}")
+    ir.attrs["use"] = "ring_attention_kv"
+    return ir
+
+
+# ---------------------------------------------------------------------------------------------
+# direct (one hop through the switch) algorithms
+# ---------------------------------------------------------------------------------------------
+def direct_reduce_scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA,
+                          redop: str = "sum", direct: bool = False) -> CollectiveIR:
+    """Every rank sends shard d to rank d in one step; d folds the n contributions.
+
+    ``direct=True`` is the pull form: rank d reads its shard straight out of every peer's
+    (symmetric) input and reduces in registers; no scratch traffic."""
+    sh = channels
+    ir = _new(f"direct_reduce_scatter_n{n}_c{channels}{'_pull' if direct else ''}", "reduce_scatter",
+              n, n * sh, {"input": n * sh, "output": sh, "scratch": 0 if direct else n * sh},
+              device_type, redop, block_units=sh)
+    reduce_scatter_conditions(ir, n, sh)
+    for ch in range(channels):
+        for d in range(n):
+            acc = ir.copy(Chunk({d}, d, 1, d * sh + ch, "input"),
+                          Chunk({d}, d, 1, ch, "output", origin=d * sh + ch), step=0, channel=ch)
+            have = {d}
+            for k in range(1, n):
+                r = (d + k) % n     # rotate so that the n ranks never all target one peer
+                if direct:
+                    acc = ir.reduce(Chunk({r}, r, 1, d * sh + ch, "input"),
+                                    Chunk(have | {r}, d, 1, ch, "output", origin=d * sh + ch),
+                                    deps=[acc], step=k, channel=ch, executor=d)
+                else:
+                    push = ir.copy(Chunk({r}, r, 1, d * sh + ch, "input"),
+                                   Chunk({r}, d, 1, r * sh + ch, "scratch", origin=d * sh + ch),
+                                   step=0, channel=ch)
+                    acc = ir.reduce(Chunk({r}, d, 1, r * sh + ch, "scratch", origin=d * sh + ch),
+                                    Chunk(have | {r}, d, 1, ch, "output", origin=d * sh + ch),
+                                    deps=[acc, push], step=k, channel=ch)
+                have = have | {r}
+    return ir
+
+
+def direct_allgather(n: int, channels: int = 1, device_type=DeviceType.CUDA,
+                     direct: bool = False) -> CollectiveIR:
+    sh = channels
+    ir = _new(f"direct_allgather_n{n}_c{channels}{'_sym' if direct else ''}", "allgather", n, sh,
+              {"input": sh, "output": n * sh, "scratch": 0 if direct else n * sh}, device_type,
+              block_units=sh)
+    allgather_conditions(ir, n, sh)
+    for ch in range(channels):
+        for r in range(n):
+            org = r * sh + ch
+            src = Chunk({r}, r, 1, ch, "input", origin=org)
+            ir.copy(src, Chunk({r}, r, 1, org, "output", origin=org), step=0, channel=ch)
+            for k in range(1, n):
+                d = (r + k) % n
+                if direct:
+                    ir.copy(src, Chunk({r}, d, 1, org, "output", origin=org), step=0, channel=ch)
+                else:
+                    push = ir.copy(src, Chunk({r}, d, 1, org, "scratch", origin=org), step=0, channel=ch)
+                    ir.copy(Chunk({r}, d, 1, org, "scratch", origin=org),
+                            Chunk({r}, d, 1, org, "output", origin=org), deps=[push], step=1, channel=ch)
+    return ir
+
+
+def direct_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum",
+                     direct: bool = False) -> CollectiveIR:
+    """Two-shot: direct reduce-scatter into the output shard, then direct all-gather of shards.
+
+    Scratch is n+1 images of the vector: image r receives rank r's contribution (each unit keeps its
+    position inside the image, so source and target slices have the same length whatever the
+    message size), image n receives the gathered results."""
+    sh = channels
+    U = n * sh
+    ir = _new(f"direct_allreduce_n{n}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": (n + 1) * U}, device_type, redop)
+    allreduce_conditions(ir, n, U)
+    for ch in range(channels):
+        for d in range(n):
+            u = d * sh + ch
+            acc = ir.copy(Chunk({d}, d, 1, u, "input"), Chunk({d}, d, 1, u, "output"), step=0, channel=ch)
+            have = {d}
+            for k in range(1, n):
+                r = (d + k) % n
+                push = ir.copy(Chunk({r}, r, 1, u, "input"),
+                               Chunk({r}, d, 1, r * U + u, "scratch", origin=u), step=0, channel=ch)
+                acc = ir.reduce(Chunk({r}, d, 1, r * U + u, "scratch", origin=u),
+                                Chunk(have | {r}, d, 1, u, "output"), deps=[acc, push], step=k, channel=ch)
+                have = have | {r}
+            for k in range(1, n):
+                t = (d + k) % n
+                if direct:
+                    ir.copy(Chunk(_all(n), d, 1, u, "output"), Chunk(_all(n), t, 1, u, "output"),
+                            deps=[acc], step=n, channel=ch)
+                else:
+                    push = ir.copy(Chunk(_all(n), d, 1, u, "output"),
+                                   Chunk(_all(n), t, 1, n * U + u, "scratch", origin=u),
+                                   deps=[acc], step=n, channel=ch)
+                    ir.copy(Chunk(_all(n), t, 1, n * U + u, "scratch", origin=u),
+                            Chunk(_all(n), t, 1, u, "output"), deps=[push], step=n + 1, channel=ch)
+    return ir
+
+
+def oneshot_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA,
+                      redop: str = "sum") -> CollectiveIR:
+    """Latency-optimal small-message form: everyone sends everything, everyone reduces."""
+    U = channels
+    ir = _new(f"oneshot_allreduce_n{n}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": n * U}, device_type, redop)
+    allreduce_conditions(ir, n, U)
+    for ch in range(channels):
+        for d in range(n):
+            acc = ir.copy(Chunk({d}, d, 1, ch, "input"), Chunk({d}, d, 1, ch, "output"), step=0, channel=ch)
+            have = {d}
+            for k in range(1, n):
+                r = (d + k) % n
+                push = ir.copy(Chunk({r}, r, 1, ch, "input"),
+                               Chunk({r}, d, 1, r * U + ch, "scratch", origin=ch), step=0, channel=ch)
+                acc = ir.reduce(Chunk({r}, d, 1, r * U + ch, "scratch", origin=ch),
+                                Chunk(have | {r}, d, 1, ch, "output"), deps=[acc, push], step=k, channel=ch)
+                have = have | {r}
+    return ir
+
+
+def tree_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA,
+                   redop: str = "sum") -> CollectiveIR:
+    """Binomial-tree reduce to rank 0 followed by binomial broadcast (log2 n steps each)."""
+    U = channels
+    ir = _new(f"tree_allreduce_n{n}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": 2 * U * max(1, n.bit_length())}, device_type, redop)
+    allreduce_conditions(ir, n, U)
+    for ch in range(channels):
+        last, have = {}, {}
+        for r in range(n):
+            last[r] = ir.copy(Chunk({r}, r, 1, ch, "input"), Chunk({r}, r, 1, ch, "output"), step=0, channel=ch)
+            have[r] = {r}
+        lvl, dist, step = 0, 1, 1
+        while dist < n:
+            for r in range(0, n, 2 * dist):
+                s = r + dist
+                if s >= n:
+                    continue
+                slot = lvl * U + ch
+                push = ir.copy(Chunk(have[s], s, 1, ch, "output"),
+                               Chunk(have[s], r, 1, slot, "scratch", origin=ch),
+                               deps=[last[s]], step=step, channel=ch)
+                last[r] = ir.reduce(Chunk(have[s], r, 1, slot, "scratch", origin=ch),
+                                    Chunk(have[r] | have[s], r, 1, ch, "output"),
+                                    deps=[push, last[r]], step=step + 1, channel=ch)
+                have[r] = have[r] | have[s]
+            dist *= 2
+            lvl += 1
+            step += 2
+        nl = lvl
+        dist //= 2
+        while dist >= 1:
+            lvl -= 1
+            for r in range(0, n, 2 * dist):
+                s = r + dist
+                if s >= n:
+                    continue
+                slot = (nl + lvl) * U + ch
+                push = ir.copy(Chunk(_all(n), r, 1, ch, "output"),
+                               Chunk(_all(n), s, 1, slot, "scratch", origin=ch),
+                               deps=[last[r], last[s]], step=step, channel=ch)
+                last[s] = ir.copy(Chunk(_all(n), s, 1, slot, "scratch", origin=ch),
+                                  Chunk(_all(n), s, 1, ch, "output"), deps=[push], step=step + 1, channel=ch)
+            dist //= 2
+            step += 2
+    return ir
+
+
+def alltoall(n: int, channels: int = 1, device_type=DeviceType.CUDA, direct: bool = False,
+             name: Optional[str] = None) -> CollectiveIR:
+    """Block d of rank s's input becomes block s of rank d's output."""
+    blk = channels
+    U = n * blk
+    ir = _new(name or f"alltoall_n{n}_c{channels}", "alltoall", n, U,
+              {"input": U, "output": U, "scratch": 0 if direct else U}, device_type, block_units=blk)
+    alltoall_conditions(ir, n, blk)
+    for ch in range(channels):
+        for s in range(n):
+            for k in range(n):
+                d = (s + k) % n
+                org = s * U + d * blk + ch
+                src = Chunk({s}, s, 1, d * blk + ch, "input", origin=org)
+                dst = Chunk({s}, d, 1, s * blk + ch, "output", origin=org)
+                if d == s or direct:
+                    ir.copy(src, dst, step=0, channel=ch)
+                else:
+                    mid = Chunk({s}, d, 1, s * blk + ch, "scratch", origin=org)
+                    push = ir.copy(src, mid, step=0, channel=ch)
+                    ir.copy(mid, dst, deps=[push], step=1, channel=ch)
+    return ir
+
+
+def ulysses_alltoall(n: int, channels: int = 1, device_type=DeviceType.CUDA) -> CollectiveIR:
+    """DeepSpeed-Ulysses sequence<->head exchange: an all-to-all whose block d of rank s is the
+    slice (sequence shard s, head group d); after it rank d holds every sequence shard of its
+    head group."""
+    ir = alltoall(n, channels, device_type, name=f"ulysses_alltoall_n{n}_c{channels}")
+    ir.attrs["use"] = "ulysses_seq_to_head"
+    return ir
+
+
+# ---------------------------------------------------------------------------------------------
+# NVLS (in-switch) algorithms — GPU only, symmetric input/output bound to a multicast object
+# ---------------------------------------------------------------------------------------------
+def nvls_allreduce(n: int, channels: int = 1, redop: str = "sum") -> CollectiveIR:
+    """Two-shot through the switch: rank r ld_reduce's slice r (the switch sums the n replicas)
+    and multicast-stores the result into every replica of the output."""
+    sh = channels
+    U = n * sh
+    ir = _new(f"nvls_allreduce_n{n}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": 0}, DeviceType.CUDA, redop, in_place=True)
+    ir.attrs["requires"] = "multicast"
+    allreduce_conditions(ir, n, U)
+    for ch in range(channels):
+        bars = [ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r,
+                                    metadata={"step": 0, "channel": ch}) for r in range(n)]
+        sts = []
+        for r in range(n):
+            u = r * sh + ch
+            ld = ir.create_operation(PrimitiveOpType.MM_LD_REDUCE, Chunk(_all(n), r, 1, u, "input"),
+                                     Chunk(_all(n), r, 1, u, "output"), r, r, bars,
+                                     {"step": 1, "channel": ch})
+            sts.append(ir.create_operation(PrimitiveOpType.MM_ST, Chunk(_all(n), r, 1, u, "output"),
+                                           Chunk(_all(n), r, 1, u, "output"), r, r, [ld],
+                                           {"step": 2, "channel": ch}))
+        for r in range(n):
+            ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, sts,
+                                {"step": 3, "channel": ch})
+    return ir
+
+
+def nvls_reduce_scatter(n: int, channels: int = 1, redop: str = "sum") -> CollectiveIR:
+    sh = channels
+    ir = _new(f"nvls_reduce_scatter_n{n}_c{channels}", "reduce_scatter", n, n * sh,
+              {"input": n * sh, "output": sh, "scratch": 0}, DeviceType.CUDA, redop, block_units=sh)
+    ir.attrs["requires"] = "multicast"
+    reduce_scatter_conditions(ir, n, sh)
+    for ch in range(channels):
+        bars = [ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r,
+                                    metadata={"step": 0, "channel": ch}) for r in range(n)]
+        lds = [ir.create_operation(PrimitiveOpType.MM_LD_REDUCE,
+                                   Chunk(_all(n), r, 1, r * sh + ch, "input"),
+                                   Chunk(_all(n), r, 1, ch, "output", origin=r * sh + ch), r, r, bars,
+                                   {"step": 1, "channel": ch}) for r in range(n)]
+        for r in range(n):
+            ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, lds, {"step": 2, "channel": ch})
+    return ir
+
+
+def nvls_allgather(n: int, channels: int = 1) -> CollectiveIR:
+    sh = channels
+    ir = _new(f"nvls_allgather_n{n}_c{channels}", "allgather", n, sh,
+              {"input": sh, "output": n * sh, "scratch": 0}, DeviceType.CUDA, block_units=sh)
+    ir.attrs["requires"] = "multicast"
+    allgather_conditions(ir, n, sh)
+    for ch in range(channels):
+        bars = [ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r,
+                                    metadata={"step": 0, "channel": ch}) for r in range(n)]
+        sts = [ir.create_operation(PrimitiveOpType.MM_ST,
+                                   Chunk({r}, r, 1, ch, "input", origin=r * sh + ch),
+                                   Chunk({r}, r, 1, r * sh + ch, "output", origin=r * sh + ch), r, r, bars,
+                                   {"step": 1, "channel": ch}) for r in range(n)]
+        for r in range(n):
+            ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, sts, {"step": 2, "channel": ch})
+    return ir
+
+
+ALGORITHMS = {
+    "ring_allreduce": ring_allreduce,
+    "ring_allgather": ring_allgather,
+    "ring_kv_rotation": ring_kv_rotation,
+    "direct_reduce_scatter": direct_reduce_scatter,
+    "direct_allgather": direct_allgather,
+    "direct_allreduce": direct_allreduce,
+    "oneshot_allreduce": oneshot_allreduce,
+    "tree_allreduce": tree_allreduce,
+    "alltoall": alltoall,
+    "ulysses_alltoall": ulysses_alltoall,
+    "nvls_allreduce": nvls_allreduce,
+    "nvls_reduce_scatter": nvls_reduce_scatter,
+    "nvls_allgather": nvls_allgather,
+}
+
+
+def build(name: str, n: int, **kw) -> CollectiveIR:
+    if name not in ALGORITHMS:
+        raise KeyError(f"unknown algorithm {name!r}; have {sorted(ALGORITHMS)}")
+    return ALGORITHMS[name](n, **kw)

@@ -1,0 +1,130 @@
+"""Multi-process CPU ranks: lang -> JSON schedule -> C++ engine -> CPU executor over shm and TCP."""
+import json
+import os
+
+import pytest
+import torch
+
+from _ranks import run_ranks
+
+
+def _collective_rank(rank, world, port, algo, transport, dtype_name, n_elems, channels, width, kwargs):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, build
+    dtype = getattr(torch, dtype_name)
+    e = Engine(rank, world)
+    e.initEngine("cpu")
+    e.joinCluster(f"127.0.0.1:{port}")
+    ir = build(algo, world, channels=channels, device_type=DeviceType.CPU, **kwargs)
+    e.regOp("op", ir)
+    g = torch.Generator().manual_seed(0)
+    coll = ir.collective
+    per_rank = {"allreduce": n_elems, "reduce_scatter": n_elems * world, "allgather": n_elems,
+                "alltoall": n_elems * world}[coll]
+    xs = [((torch.rand(per_rank, generator=g) * 2 - 1) * 4).to(dtype) for _ in range(world)]
+    out_elems = {"allreduce": n_elems, "reduce_scatter": n_elems, "allgather": n_elems * world,
+                 "alltoall": n_elems * world}[coll]
+    errs = []
+    for it in range(3):     # repeated launches exercise the epoch-counting signals and scratch halves
+        x = (xs[rank].float() + it).to(dtype)
+        y = torch.full((out_elems,), -777, dtype=dtype)
+        e.exeOp("op", x, y, width=width)
+        full = [(v.float() + it).to(dtype).float() for v in xs]
+        if coll == "allreduce":
+            ref = torch.stack(full).sum(0)
+        elif coll == "reduce_scatter":
+            ref = torch.stack(full).sum(0)[rank * n_elems:(rank + 1) * n_elems]
+        elif coll == "allgather":
+            ref = torch.cat(full)
+        else:
+            ref = torch.cat([f[rank * n_elems:(rank + 1) * n_elems] for f in full])
+        errs.append((y.float() - ref).abs().max().item())
+    st = e.stats()
+    e.exitCluster()
+    return {"err": max(errs), "launches": st["ops"]["op"]["launches"], "tcp": st.get("tcp_bytes_sent", 0)}
+
+
+def _baseline_rank(rank, world, port, transport):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, algorithms
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ring", algorithms.ring_allreduce(world, channels=2, device_type=DeviceType.CPU))
+    g = torch.Generator().manual_seed(0)
+    xs = [torch.rand(4 * 1024 * 1024, generator=g) * 2 - 1 for _ in range(world)]
+    y = torch.empty_like(xs[rank])
+    e.exeOp("ring", xs[rank], y, width=2)
+    ref = xs[0] + xs[1]
+    tcp = e.stats()["tcp_bytes_sent"]
+    e.exitCluster()
+    return (torch.equal(y, ref), (y - ref).abs().max().item(), tcp)
+
+
+def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
+    # ring allreduce (sum) of 4M fp32 per rank, uniform[-1,1) from seed 0, world 2, checked against torch sum
+    for transport in ("shm", "tcp"):
+        env = {"PCCL_WORKSPACE_MB": "128", "PCCL_TRANSPORT": transport}
+        res = run_ranks(_baseline_rank, 2, args=(transport,), env=env)
+        for r in (0, 1):
+            assert res[r][0], f"{transport}: rank {r} differs from torch sum by {res[r][1]}"
+            assert (res[r][2] > 0) == (transport == "tcp")
+
+
+@pytest.mark.parametrize("algo,kwargs", [
+    ("ring_allreduce", {}), ("direct_allreduce", {}), ("oneshot_allreduce", {}), ("tree_allreduce", {}),
+    ("direct_reduce_scatter", {}), ("direct_allgather", {}), ("ring_allgather", {}), ("ring_kv_rotation", {}),
+    ("alltoall", {}), ("ulysses_alltoall", {})])
+def test_algorithms_on_cpu_ranks_shm(algo, kwargs):
+    res = run_ranks(_collective_rank, 4, args=(algo, "shm", "float32", 1000 + 17, 2, 2, kwargs),
+                    env={"PCCL_WORKSPACE_MB": "16"})
+    for r, v in res.items():
+        assert v["err"] < 1e-4 and v["launches"] == 3, (algo, r, v)
+
+
+@pytest.mark.parametrize("algo", ["ring_allreduce", "direct_reduce_scatter", "alltoall"])
+def test_algorithms_on_cpu_ranks_tcp_bf16(algo):
+    res = run_ranks(_collective_rank, 3, args=(algo, "tcp", "bfloat16", 4096 + 8, 1, 1, {}),
+                    env={"PCCL_WORKSPACE_MB": "16", "PCCL_TRANSPORT": "tcp"})
+    for r, v in res.items():
+        assert v["err"] <= 0.26 and v["tcp"] > 0, (algo, r, v)   # bf16 rounding of sums up to ~24
+
+
+def test_regop_accepts_file_and_rejects_garbage(tmp_path):
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import build, to_schedule
+    e = Engine(0, 1)
+    e.initEngine("cpu")
+    path = tmp_path / "ar.json"
+    path.write_text(json.dumps(to_schedule(build("ring_allreduce", 1))))
+    e.regOp("from_file", str(path))
+    x = torch.arange(10, dtype=torch.float32); y = torch.zeros(10)
+    e.exeOp("from_file", x, y)
+    assert torch.equal(x, y)
+    with pytest.raises(RuntimeError):
+        e.regOp("from_file", str(path))            # duplicate name
+    with pytest.raises(RuntimeError):
+        e.regOp("bad", "{\"name\": \"x\"}")         # no lowered section
+    with pytest.raises(RuntimeError):
+        e.exeOp("nope", x, y)
+    doc = json.loads(e.exportEndpoint())
+    assert doc["rank"] == 0 and "ipc.cpu.handle" in doc["endpoint_configs"] and "host_id" in doc["endpoint_configs"]
+    lay = e.layout()
+    assert lay["signal_off"] == lay["workspace_bytes"] and lay["total"] % (2 << 20) == 0
+
+
+def test_exeop_reports_scratch_overflow():
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import build
+    from pccl_b200.engine import LaunchEnvironments
+    LaunchEnvironments.setOverride("PCCL_WORKSPACE_MB", "4")   # the environment is snapshotted at load
+    try:
+        e = Engine(0, 1); e.initEngine("cpu")
+    finally:
+        LaunchEnvironments.setOverride("PCCL_WORKSPACE_MB", "64")
+    ir = build("oneshot_allreduce", 1)
+    ir.buffers["scratch"] = 1
+    e.regOp("big", ir, check=False)
+    x = torch.zeros(2 << 20)
+    with pytest.raises(RuntimeError, match="scratch"):
+        e.exeOp("big", x, torch.empty_like(x))

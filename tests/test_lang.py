@@ -1,0 +1,122 @@
+import json
+
+import pytest
+
+from pccl_b200.lang import (ALGORITHMS, Chunk, CollectiveIR, Device, DeviceType, DirectedGraph, Link,
+                            LoweringError, PrimitiveOpType, build, check_lowered_deadlock_free, lower,
+                            port_load, to_schedule, verify)
+
+
+def test_graph_basics():
+    g = DirectedGraph()
+    for n in (10, 20, 30, 40):
+        g.add_node(n)
+    g.add_edge(10, 20); g.add_edge(20, 30); g.add_edge(10, 30)
+    assert g.is_acyclic()
+    order = g.topological_sort()
+    assert order.index(10) < order.index(20) < order.index(30)
+    assert sorted(map(sorted, g.get_connected_components())) == [[10, 20, 30], [40]]
+    assert g.get_predecessors(30) == [20, 10] or sorted(g.get_predecessors(30)) == [10, 20]
+    g.add_edge(30, 10)
+    assert not g.is_acyclic()
+    with pytest.raises(ValueError):
+        g.topological_sort()
+    assert g.remove_edge(30, 10) and g.is_acyclic()
+    with pytest.raises(ValueError):
+        g.add_edge(10, 99)
+
+
+def test_graph_ids_are_the_callers():
+    # device ids need not be 0..n-1 in insertion order
+    ir = CollectiveIR("t")
+    for d in (7, 3):
+        ir.add_device(Device(d, DeviceType.CUDA))
+    ir.add_link(Link(7, 3))
+    assert ir.validate_topology()
+    assert ir.get_device_bandwidth_matrix()[(3, 7)] == ir.get_device_bandwidth_matrix()[(7, 3)]
+
+
+def test_ir_builder_and_reference_api():
+    ir = CollectiveIR("two_rank_sum", "allreduce", units=1, buffers={"input": 1, "output": 1, "scratch": 1})
+    ir.add_device(Device(0, DeviceType.CPU, 1e11, 0)); ir.add_device(Device(1, DeviceType.CPU, 1e11, 0))
+    ir.add_link(Link(0, 1, 1e10, 1e-5))
+    ir.set_precondition([Chunk({0}, 0, 1, 0), Chunk({1}, 1, 1, 0)])
+    a = ir.create_operation(PrimitiveOpType.COPY, Chunk({0}, 0, 1, 0, "input"), Chunk({0}, 0, 1, 0, "output"))
+    b = ir.create_operation(PrimitiveOpType.COPY, Chunk({1}, 1, 1, 0, "input"), Chunk({1}, 0, 1, 0, "scratch"))
+    c = ir.create_operation(PrimitiveOpType.REDUCE, Chunk({1}, 0, 1, 0, "scratch"), Chunk({0, 1}, 0, 1, 0, "output"),
+                            dependencies=[a, b])
+    ir.set_postcondition([Chunk({0, 1}, 0, 1, 0, "output")])
+    assert ir.validate_dag() and ir.validate_topology()
+    assert [o.op_id for o in ir.get_operation_sequence()][-1] == c
+    assert verify(ir).ok
+    with pytest.raises(ValueError):
+        ir.create_operation(PrimitiveOpType.COPY, dependencies=[999])
+
+
+@pytest.mark.parametrize("name", sorted(ALGORITHMS))
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+def test_every_algorithm_verifies_and_lowers(name, n):
+    ir = build(name, n, channels=2)
+    rep = verify(ir)
+    assert rep.ok, rep.errors[:3]
+    low = lower(ir)
+    assert low["num_ranks"] == n and len(low["slot_counts"]) == low["num_slots"]
+    assert check_lowered_deadlock_free(low)
+    again = CollectiveIR.from_json(ir.to_json())
+    assert verify(again).ok and lower(again) == low
+
+
+def test_verifier_catches_double_count_missing_data_and_races():
+    ir = build("direct_reduce_scatter", 2)
+    # reduce the same contribution twice
+    red = [o for o in ir.ops.values() if o.op_type == PrimitiveOpType.REDUCE][0]
+    ir.create_operation(PrimitiveOpType.REDUCE, red.src_chunk.copy(), red.tgt_chunk.copy(), dependencies=[red.op_id])
+    rep = verify(ir, check_annotations=False)
+    assert not rep.ok and any("twice" in e for e in rep.errors)
+
+    ir = build("direct_allgather", 3)
+    # drop one op's effect by pointing the postcondition at data nobody wrote
+    ir.postcondition.append(Chunk({0}, 1, 1, 0, "scratch", origin=0))
+    ir.buffers["scratch"] = 3
+    bad = build("ring_allreduce", 3)
+    victim = [o for o in bad.ops.values() if o.op_type == PrimitiveOpType.REDUCE][0]
+    victim.dependencies.clear()
+    for p in bad.op_dag.get_predecessors(victim.op_id):
+        bad.op_dag.remove_edge(p, victim.op_id)
+    rep = verify(bad)
+    assert not rep.ok   # either reads undefined data or races with the producer
+
+
+def test_port_load_of_direct_forms_is_balanced():
+    n = 8
+    for name in ("direct_reduce_scatter", "direct_allgather", "alltoall"):
+        load = port_load(build(name, n))
+        assert len({v for v in load.values()}) == 1
+        assert load[0][0] == n - 1 and load[0][1] == n - 1
+    ring = port_load(build("ring_allreduce", n))
+    assert ring[0] == (2 * (n - 1), 2 * (n - 1))
+
+
+def test_schedule_document_shape():
+    doc = to_schedule(build("ring_allreduce", 2))
+    text = json.dumps(doc)
+    back = json.loads(text)
+    assert back["lowered"]["num_ranks"] == 2 and back["attrs"]["block_units"] == back["units"]
+    ins = back["lowered"]["programs"][0][0][0]
+    assert len(ins) == 10
+
+
+def test_lowering_rejects_missing_barrier_partner():
+    ir = build("nvls_allreduce", 2)
+    # remove rank 1's final barrier: rank 0's barrier then has no partner
+    last = max(i for i, o in ir.ops.items() if o.op_type == PrimitiveOpType.BARRIER and o.executor == 1)
+    del ir.ops[last]
+    ir2 = CollectiveIR("broken", "allreduce", ir.units, buffers=ir.buffers, in_place=True)
+    for d in ir.devices.values():
+        ir2.add_device(d)
+    remap = {}
+    for i, o in ir.ops.items():
+        remap[i] = ir2.create_operation(o.op_type, o.src_chunk, o.tgt_chunk, o.src_device, o.tgt_device,
+                                        [remap[d] for d in o.dependencies if d in remap], o.metadata)
+    with pytest.raises(LoweringError):
+        lower(ir2)
