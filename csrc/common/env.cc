@@ -107,7 +107,7 @@ void registerBuiltinOptions() {
   L::registerOpt("PCCL_SLOT_KB", "workspace slot granule in KiB (default 1024)");
   L::registerOpt("PCCL_MAX_SMS", "upper bound on CTAs a collective may use (default 32)");
   L::registerOpt("PCCL_CHANNELS", "default channel count for generated schedules");
-  L::registerOpt("PCCL_SPIN_LIMIT", "bounded-wait budget of device spins, in polls");
+  L::registerOpt("PCCL_SPIN_LIMIT", "bounded-wait budget of device-side waits, in nanoseconds (default 2e9)");
   L::registerOpt("PCCL_WAIT_TIMEOUT_MS", "bounded-wait budget of host executors in ms (default 30000)");
   L::registerOpt("PCCL_TRANSPORT", "nvls|p2p|shm|tcp: force a transport");
   L::registerOpt("PCCL_TRACE", "1: record per-instruction timestamps");

@@ -19,7 +19,7 @@ namespace pccl {
 
 constexpr int kMaxRanks = 16;
 constexpr int kMaxBlocksPerColl = 160;        // flag rows reserved per collective "lane"
-constexpr uint64_t kDefaultSpinLimit = 400ull * 1000 * 1000;   // polls; ~1 s at ~2.5 ns per poll
+constexpr uint64_t kDefaultSpinLimit = 2000ull * 1000 * 1000;   // nanoseconds a device-side wait may last
 
 struct World {
   int world;

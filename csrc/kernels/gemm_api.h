@@ -1,8 +1,30 @@
-// Host entry points of the tcgen05 GEMM family (declared here, defined in gemm_*.cu).
+// Host entry points of the tcgen05 GEMM family (defined in gemm_*.cu).  Raw pointers, no torch.
 #pragma once
 #include <cuda_runtime.h>
 
 #include <cstdint>
 
+#include "api.h"
+
 namespace pccl {
+
+enum GemmFlags : uint32_t {
+  GEMM_A_MN = 1u << 0,        // A is the transposed view of a row-major [K, M] tensor
+  GEMM_B_MN = 1u << 1,        // B is the transposed view of a row-major [K, N] tensor
+  GEMM_OUT_F32 = 1u << 2,     // D is fp32 (default bf16)
+  GEMM_ACCUMULATE = 1u << 3,  // D += A*B^T (D is read)
+  GEMM_GELU = 1u << 4,        // D2 = gelu_tanh(D) written next to D (D keeps the pre-activation)
+  GEMM_BIAS = 1u << 5,        // D = A*B^T + bias[n] (bf16 bias)
+};
+
+// D[M,N] (ldd) = A * B^T.  K-major operands: A is [M,K] with row stride lda, B is [N,K] with row
+// stride ldb.  MN-major operands: A is stored [K,M] (row stride lda), B is stored [K,N] (ldb).
+// All strides in elements and multiples of 8; pointers 16-byte aligned.  Asynchronous on `stream`.
+// `sms` limits the CTAs (0 = one per SM).  `status` (device, 4 x u32, may be null... must not be
+// null) receives ST_TIMEOUT if a pipeline wait runs out.
+int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
+             uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status, cudaStream_t stream);
+
+const char* gemmLastError();
+
 }  // namespace pccl

@@ -52,18 +52,27 @@ __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
   return v;
 }
 
-// Polls until *p >= target.  Gives up after `limit` polls, or as soon as *abort_word != 0 (another
-// worker of this rank already failed).  Returns true on success.  Never traps, never spins forever.
-__device__ __forceinline__ bool wait_ge(const uint64_t* p, uint64_t target, uint64_t limit,
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Polls until *p >= target.  Gives up after `limit_ns` nanoseconds of waiting, or as soon as
+// *abort_word != 0 (another worker of this rank already failed).  Returns true on success.
+// Never traps, never spins forever.
+__device__ __forceinline__ bool wait_ge(const uint64_t* p, uint64_t target, uint64_t limit_ns,
                                         const uint32_t* abort_word) {
-  for (uint64_t i = 0; i < limit; ++i) {
+  if (ld_acquire_sys(p) >= target) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (ld_acquire_sys(p) >= target) return true;
-    if ((i & 1023) == 1023) {
+    if ((i & 63) == 0) {
       if (abort_word && ld_volatile_u32(abort_word) != 0) return false;
-      __nanosleep(64);
+      if (global_timer_ns() - t0 > limit_ns) return false;
+      __nanosleep(32);
     }
   }
-  return false;
 }
 
 // First failure wins; later ones keep the first record.

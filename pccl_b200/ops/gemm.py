@@ -1,0 +1,111 @@
+"""bf16 GEMM on the tcgen05/TMEM pipeline (csrc/kernels/gemm_tc05.cu).
+
+``gemm(a, b, a_t=False, b_t=False)`` computes ``op(a) @ op(b)`` for row-major tensors, where the
+flags say which operand is consumed in its transposed ("MN-major") form — the kernel reads such an
+operand through a different TMA box and shared-memory descriptor, no transpose pass is made.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .._native import C
+
+_status: Dict[int, torch.Tensor] = {}
+_launches = 0
+
+
+def status_words(device=None) -> torch.Tensor:
+    """Per-device status words that kernels write when a bounded wait runs out (all zero = fine)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx not in _status:
+        _status[idx] = torch.zeros(64, dtype=torch.int32, device=f"cuda:{idx}")
+    return _status[idx]
+
+
+def check_status(what: str = "kernel") -> None:
+    """Synchronises and raises if a kernel reported a failure since the last check."""
+    st = status_words()
+    vals = st[:4].tolist()
+    if vals[0] != 0:
+        st.zero_()
+        raise RuntimeError(f"{what}: device status {vals} (1 = bounded wait timed out)")
+
+
+def launch_count() -> int:
+    """Number of kernels of this package launched by this process (benchmarks report it)."""
+    return _launches
+
+
+def count_launch(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"gemm: {name} must be a 2-D CUDA bf16 tensor with unit inner stride")
+    if t.stride(0) % 8 or t.data_ptr() % 16:
+        raise ValueError(f"gemm: {name} needs a row stride that is a multiple of 8 and a 16-byte aligned base")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+         bias: Optional[torch.Tensor] = None, gelu_out: Optional[torch.Tensor] = None,
+         accumulate: bool = False, sms: int = 0) -> torch.Tensor:
+    """``out = op(a) @ op(b)`` with ``op(a) = a.T if a_t else a`` (a: [M,K] or [K,M]) and
+    ``op(b) = b if b_t else b.T`` (b: [N,K], or [K,N] when ``b_t``).  So the default is the linear
+    layer form ``a @ b.T``.  ``bias`` (bf16 [N]) is added; ``gelu_out`` receives gelu_tanh(out)."""
+    _check(a, "a")
+    _check(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if a_t else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_t else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    if out is None:
+        ldd = (N + 7) // 8 * 8
+        store = torch.empty((M, ldd), dtype=out_dtype, device=a.device)
+        out = store[:, :N] if ldd != N else store
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError("gemm: out must be [M,N] bf16/fp32 with unit inner stride")
+    flags = 0
+    if a_t:
+        flags |= C.GEMM_A_MN
+    if b_t:
+        flags |= C.GEMM_B_MN
+    if out.dtype == torch.float32:
+        flags |= C.GEMM_OUT_F32
+    if accumulate:
+        flags |= C.GEMM_ACCUMULATE
+    bias_ptr = 0
+    if bias is not None:
+        if bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous():
+            raise ValueError("gemm: bias must be a contiguous bf16 vector of length N")
+        flags |= C.GEMM_BIAS
+        bias_ptr = bias.data_ptr()
+    d2 = 0
+    if gelu_out is not None:
+        if gelu_out.shape != out.shape or gelu_out.stride() != out.stride() or gelu_out.dtype != torch.bfloat16:
+            raise ValueError("gemm: gelu_out must match out")
+        flags |= C.GEMM_GELU
+        d2 = gelu_out.data_ptr()
+    C.gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), M, N, K, flags,
+                bias_ptr, d2, sms, status_words(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return out
+
+
+def gemm_nt(a, b, **kw):
+    """a[M,K] @ b[N,K].T"""
+    return gemm(a, b, **kw)
+
+
+def gemm_nn(a, b, **kw):
+    """a[M,K] @ b[K,N]"""
+    return gemm(a, b, b_t=True, **kw)
+
+
+def gemm_tn(a, b, **kw):
+    """a[K,M].T @ b[K,N]"""
+    return gemm(a, b, a_t=True, b_t=True, **kw)

@@ -1,0 +1,168 @@
+"""Hand-written collectives and the interpreter kernel, all ranks emulated on one GPU (one
+cooperative launch plays every rank; 'heaps' are buffers of that GPU)."""
+import json
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SIGNAL_OFF = 0            # layout of each emulated heap: [signals 64 KiB | flags 256 KiB | data]
+FLAG_OFF = 64 * 1024
+DATA_OFF = 512 * 1024
+NAMES = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}
+
+
+def _heaps(world, data_bytes):
+    hs = [torch.zeros(DATA_OFF + data_bytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    return hs, st
+
+
+def _view(h, off, n, dtype):
+    es = torch.empty((), dtype=dtype).element_size()
+    return h[DATA_OFF + off: DATA_OFF + off + n * es].view(dtype)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("count", [1, 7, 1024, 256 * 1024 + 17])
+def test_allreduce_emulated(native, world, dtype, count):
+    es = torch.empty((), dtype=dtype).element_size()
+    size = (count * es + 255) // 256 * 256
+    hs, st = _heaps(world, 2 * size)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    xs = [torch.randn(count, generator=g, device="cuda").to(dtype) for _ in range(world)]
+    for epoch in (1, 2):
+        for r in range(world):
+            _view(hs[r], 0, count, dtype).copy_(xs[r] * epoch)
+        native.emu_collective("allreduce", [h.data_ptr() for h in hs], SIGNAL_OFF, FLAG_OFF, NAMES[dtype], "sum",
+                              DATA_OFF, DATA_OFF + size, count, epoch, 0, 1.0, "", 4, 256,
+                              torch.cuda.current_stream().cuda_stream, [s.data_ptr() for s in st], [], [], 0)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st)
+        ref = torch.stack([x.float() * epoch for x in xs]).sum(0)
+        tol = 1e-5 * world if dtype == torch.float32 else 0.04 * world
+        for r in range(world):
+            got = _view(hs[r], size, count, dtype).float()
+            assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("redop", ["max", "min"])
+def test_allreduce_minmax_in_place(native, world, redop):
+    count, dtype = 5000, torch.bfloat16
+    hs, st = _heaps(world, 1 << 16)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    xs = [torch.randn(count, generator=g, device="cuda").to(dtype) for _ in range(world)]
+    for r in range(world):
+        _view(hs[r], 0, count, dtype).copy_(xs[r])
+    native.emu_collective("allreduce", [h.data_ptr() for h in hs], SIGNAL_OFF, FLAG_OFF, "bf16", redop, DATA_OFF, DATA_OFF,
+                          count, 1, 1, 1.0, "", 3, 128, torch.cuda.current_stream().cuda_stream,
+                          [s.data_ptr() for s in st], [], [], 0)
+    torch.cuda.synchronize()
+    ref = torch.stack(xs).float().max(0).values if redop == "max" else torch.stack(xs).float().min(0).values
+    for r in range(world):
+        assert torch.equal(_view(hs[r], 0, count, dtype).float(), ref)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("count", [16, 4096 + 8, 100003])
+def test_reduce_scatter_scale_cast_emulated(native, world, count):
+    """Gradient-bucket form: bf16 in, sum over ranks, x 1/world, fp32 out into a plain tensor."""
+    dtype = torch.bfloat16
+    size = (world * count * 2 + 255) // 256 * 256
+    hs, st = _heaps(world, size)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    xs = [torch.randn(world * count, generator=g, device="cuda").to(dtype) for _ in range(world)]
+    outs = [torch.zeros(count, dtype=torch.float32, device="cuda") for _ in range(world)]
+    for r in range(world):
+        _view(hs[r], 0, world * count, dtype).copy_(xs[r])
+    native.emu_collective("reduce_scatter", [h.data_ptr() for h in hs], SIGNAL_OFF, FLAG_OFF, "bf16", "sum", DATA_OFF, 0,
+                          count, 1, 2, 1.0 / world, "f32", 4, 256, torch.cuda.current_stream().cuda_stream,
+                          [s.data_ptr() for s in st], [], [o.data_ptr() for o in outs], 0)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st)
+    full = torch.stack([x.float() for x in xs]).sum(0) / world
+    for r in range(world):
+        assert (outs[r] - full[r * count:(r + 1) * count]).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("kind", ["allgather", "alltoall"])
+@pytest.mark.parametrize("nbytes", [16, 1000, 64 * 1024 + 48])
+def test_allgather_alltoall_emulated(native, world, kind, nbytes):
+    size = (world * nbytes + 255) // 256 * 256
+    hs, st = _heaps(world, size)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    n_in = nbytes if kind == "allgather" else world * nbytes
+    xs = [torch.randint(0, 255, (n_in,), generator=g, device="cuda", dtype=torch.uint8) for _ in range(world)]
+    native.emu_collective(kind, [h.data_ptr() for h in hs], SIGNAL_OFF, FLAG_OFF, "f32", "sum", 0, DATA_OFF, nbytes, 1, 3,
+                          1.0, "", 2, 256, torch.cuda.current_stream().cuda_stream, [s.data_ptr() for s in st],
+                          [x.data_ptr() for x in xs], [], 0)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st)
+    for r in range(world):
+        got = hs[r][DATA_OFF:DATA_OFF + world * nbytes]
+        if kind == "allgather":
+            ref = torch.cat(xs)
+        else:
+            ref = torch.cat([x[r * nbytes:(r + 1) * nbytes] for x in xs])
+        assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("algo", ["ring_allreduce", "direct_allreduce", "oneshot_allreduce", "tree_allreduce",
+                                  "direct_reduce_scatter", "direct_allgather", "ring_kv_rotation", "alltoall"])
+@pytest.mark.parametrize("world,width", [(2, 1), (4, 2)])
+def test_interpreter_runs_lowered_programs(native, algo, world, width):
+    from pccl_b200.lang import build, to_schedule
+    ir = build(algo, world, channels=2)
+    doc = json.dumps(to_schedule(ir))
+    dtype, n = torch.float32, 3000 + 5
+    coll = ir.collective
+    n_in = {"allreduce": n, "reduce_scatter": n * world, "allgather": n, "alltoall": n * world}[coll]
+    n_out = {"allreduce": n, "reduce_scatter": n, "allgather": n * world, "alltoall": n * world}[coll]
+    hs, st = _heaps(world, 16 << 20)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    xs = [torch.randn(n_in, generator=g, device="cuda") for _ in range(world)]
+    ys = [torch.full((n_out,), -5.0, device="cuda") for _ in range(world)]
+    for epoch in (0, 1):
+        native.emu_program(doc, [h.data_ptr() for h in hs], SIGNAL_OFF, [x.data_ptr() for x in xs],
+                           [y.data_ptr() for y in ys], n_in * 4, "f32", width, DATA_OFF + epoch * (8 << 20), 0, epoch,
+                           0, [s.data_ptr() for s in st], [], torch.cuda.current_stream().cuda_stream)
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        full = torch.stack(xs)
+        for r in range(world):
+            if coll == "allreduce":
+                ref = full.sum(0)
+            elif coll == "reduce_scatter":
+                ref = full.sum(0)[r * n:(r + 1) * n]
+            elif coll == "allgather":
+                ref = torch.cat(xs)
+            else:
+                ref = torch.cat([x[r * n:(r + 1) * n] for x in xs])
+            assert (ys[r] - ref).abs().max().item() < 1e-4, (algo, r)
+
+
+def test_bounded_wait_returns_timeout_status(native):
+    """A wait on a flag nobody sets comes back with ST_TIMEOUT; the context stays usable."""
+    flag = torch.zeros(1, dtype=torch.int64, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    native.wait_timeout_probe(flag.data_ptr(), 200_000, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert st[0].item() == 1
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+def test_interpreter_peer_never_arrives(native):
+    """Rank 1's streams are left out: rank 0 gives up after its poll budget and reports where."""
+    from pccl_b200.lang import build, to_schedule
+    doc = json.dumps(to_schedule(build("ring_allreduce", 2)))
+    hs, st = _heaps(2, 1 << 20)
+    xs = [torch.ones(1024, device="cuda") for _ in range(2)]
+    ys = [torch.zeros(1024, device="cuda") for _ in range(2)]
+    native.emu_program(doc, [h.data_ptr() for h in hs], SIGNAL_OFF, [x.data_ptr() for x in xs], [y.data_ptr() for y in ys],
+                       4096, "f32", 1, DATA_OFF, 0, 0, 100_000, [s.data_ptr() for s in st], [1],
+                       torch.cuda.current_stream().cuda_stream)
+    assert st[0][0].item() == 1 and st[1][0].item() == 0
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
