@@ -43,8 +43,8 @@ def test_gemm_epilogues():
     check_status("gemm")
     ref = a.float() @ b.float().t() + bias.float()
     assert (pre.float() - ref).abs().max().item() < 0.05
-    ref_act = torch.nn.functional.gelu(pre.float(), approximate="tanh")
-    assert (act.float() - ref_act).abs().max().item() < 0.02
+    ref_act = torch.nn.functional.gelu(ref, approximate="tanh")    # the kernel applies GELU before rounding
+    assert ((act.float() - ref_act).abs() <= 0.01 + 0.01 * ref_act.abs()).all()
     acc = torch.ones((M, N), dtype=torch.float32, device="cuda")
     gemm(a, b, out=acc, accumulate=True)
     assert (acc - (a.float() @ b.float().t() + 1)).abs().max().item() < 1e-2
