@@ -5,6 +5,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "kernels/elementwise_api.h"
 #include "kernels/gemm_api.h"
 
 namespace py = pybind11;
@@ -23,6 +24,20 @@ void bindGemm(py::module_& m) {
         py::arg("a"), py::arg("lda"), py::arg("b"), py::arg("ldb"), py::arg("d"), py::arg("ldd"), py::arg("M"),
         py::arg("N"), py::arg("K"), py::arg("flags"), py::arg("bias") = 0, py::arg("d2") = 0, py::arg("sms") = 0,
         py::arg("status") = 0, py::arg("stream") = 0);
+  m.def("adamw", [](uint64_t p, uint64_t mm, uint64_t v, uint64_t g, uint64_t pb, long long n, float lr, float b1, float b2,
+                    float eps, float wd, int step, float grad_scale, uint64_t stream) {
+    int err = launchAdamW(reinterpret_cast<float*>(p), reinterpret_cast<float*>(mm), reinterpret_cast<float*>(v),
+                          reinterpret_cast<const float*>(g), reinterpret_cast<void*>(pb), n, lr, b1, b2, eps, wd, step,
+                          grad_scale, reinterpret_cast<cudaStream_t>(stream));
+    if (err != 0) throw std::runtime_error(std::string("adamw: ") + cudaErrorName(err));
+  });
+  m.def("cross_entropy", [](uint64_t logits, uint64_t targets, uint64_t loss, long long rows, int vocab, long long ld,
+                            float grad_scale, long long ignore_index, uint64_t stream) {
+    int err = launchCrossEntropy(reinterpret_cast<void*>(logits), reinterpret_cast<const long long*>(targets),
+                                 reinterpret_cast<float*>(loss), rows, vocab, ld, grad_scale, ignore_index,
+                                 reinterpret_cast<cudaStream_t>(stream));
+    if (err != 0) throw std::runtime_error(std::string("cross_entropy: ") + cudaErrorName(err));
+  });
   m.attr("GEMM_A_MN") = static_cast<uint32_t>(GEMM_A_MN);
   m.attr("GEMM_B_MN") = static_cast<uint32_t>(GEMM_B_MN);
   m.attr("GEMM_OUT_F32") = static_cast<uint32_t>(GEMM_OUT_F32);

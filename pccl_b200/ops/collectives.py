@@ -1,0 +1,87 @@
+"""Hand-written collectives over the engine's symmetric heap (csrc/kernels/collectives.cu).
+
+Tensors that peers touch must come from ``Engine.symmetric_tensor`` (same heap offset on every
+rank).  ``algo``: ``"nvls"`` uses multimem through the switch (needs the multicast binding made by
+``Engine.connect``), ``"p2p"`` plain loads/stores over NVLink, ``"auto"`` picks NVLS when it exists
+and the dtype/op has an in-switch form.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .._native import C
+from ..engine import Engine, dtype_name
+from .gemm import count_launch
+
+_NVLS_OK = {("f32", "sum"), ("bf16", "sum"), ("bf16", "max"), ("bf16", "min"), ("f16", "sum"), ("f16", "max"), ("f16", "min")}
+
+
+def _algo(eng: Engine, algo: str, dt: str, op: str, nbytes: int) -> str:
+    if algo == "auto":
+        return "nvls" if (eng.has_nvls and (dt, op) in _NVLS_OK and nbytes % 16 == 0) else "p2p"
+    if algo == "nvls" and not eng.has_nvls:
+        raise RuntimeError("NVLS requested but the heap is not bound to a multicast object")
+    return algo
+
+
+def _blocks(nbytes: int, blocks: Optional[int]) -> int:
+    if blocks:
+        return blocks
+    # enough CTAs to fill NVLink, few enough to leave the GPU to concurrent compute
+    return max(1, min(64, nbytes // (256 << 10) + 1))
+
+
+def all_reduce(eng: Engine, inp: torch.Tensor, out: Optional[torch.Tensor] = None, op: str = "sum", algo: str = "auto",
+               blocks: Optional[int] = None, threads: int = 512, lane: int = 0, stream=None) -> torch.Tensor:
+    out = inp if out is None else out
+    dt = dtype_name(inp.dtype)
+    nbytes = inp.numel() * inp.element_size()
+    a = _algo(eng, algo, dt, op, nbytes)
+    s = (stream or torch.cuda.current_stream()).cuda_stream
+    C.collective(eng.raw, "allreduce", a, dt, op, eng.heap_offset(inp), eng.heap_offset(out), inp.numel(), lane, 1.0, "",
+                 _blocks(nbytes, blocks), threads, s, 0, 0, 0)
+    count_launch()
+    return out
+
+
+def reduce_scatter(eng: Engine, inp: torch.Tensor, out: torch.Tensor, op: str = "sum", scale: float = 1.0,
+                   algo: str = "auto", blocks: Optional[int] = None, threads: int = 512, lane: int = 0, stream=None) -> torch.Tensor:
+    """``out = cast(scale * reduce_over_ranks(inp[rank * n : (rank + 1) * n]))`` with n = out.numel().
+    ``inp`` is symmetric; ``out`` may be any local tensor of inp's dtype or fp32 (fused cast)."""
+    dt = dtype_name(inp.dtype)
+    n = out.numel()
+    if inp.numel() != n * eng.world:
+        raise ValueError("reduce_scatter: inp must hold world * out.numel() elements")
+    a = _algo(eng, algo, dt, op, n * inp.element_size())
+    s = (stream or torch.cuda.current_stream()).cuda_stream
+    sym_out = eng.is_symmetric(out)
+    C.collective(eng.raw, "reduce_scatter", a, dt, op, eng.heap_offset(inp), eng.heap_offset(out) if sym_out else 0, n, lane,
+                 float(scale), dtype_name(out.dtype), _blocks(n * inp.element_size() * eng.world, blocks), threads, s, 0,
+                 0 if sym_out else out.data_ptr(), 0)
+    count_launch()
+    return out
+
+
+def all_gather(eng: Engine, inp: torch.Tensor, out: torch.Tensor, algo: str = "auto", blocks: Optional[int] = None,
+               threads: int = 512, lane: int = 0, stream=None) -> torch.Tensor:
+    """``out`` (symmetric, world * inp.numel()) receives every rank's ``inp`` at its rank's slot."""
+    nbytes = inp.numel() * inp.element_size()
+    a = "nvls" if (algo in ("auto", "nvls") and eng.has_nvls and nbytes % 16 == 0 and inp.data_ptr() % 16 == 0) else "p2p"
+    s = (stream or torch.cuda.current_stream()).cuda_stream
+    C.collective(eng.raw, "allgather", a, "u8", "sum", 0, eng.heap_offset(out), nbytes, lane, 1.0, "",
+                 _blocks(nbytes * eng.world, blocks), threads, s, inp.data_ptr(), 0, 0)
+    count_launch()
+    return out
+
+
+def all_to_all(eng: Engine, inp: torch.Tensor, out: torch.Tensor, blocks: Optional[int] = None, threads: int = 512,
+               lane: int = 0, stream=None) -> torch.Tensor:
+    """Block d of ``inp`` goes to rank d; ``out`` (symmetric) receives block s from rank s."""
+    nbytes = inp.numel() * inp.element_size() // eng.world
+    s = (stream or torch.cuda.current_stream()).cuda_stream
+    C.collective(eng.raw, "alltoall", "p2p", "u8", "sum", 0, eng.heap_offset(out), nbytes, lane, 1.0, "",
+                 _blocks(nbytes * eng.world, blocks), threads, s, inp.data_ptr(), 0, 0)
+    count_launch()
+    return out

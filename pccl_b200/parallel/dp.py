@@ -1,0 +1,208 @@
+"""Data parallelism with bucketed gradient reduce-scatter overlapped with backward.
+
+Gradients live in flat bf16 buckets (25 MB by default) inside the symmetric heap.  The moment the
+last gradient of a bucket has been written (the weight-gradient GEMMs write there directly), the
+bucket's reduce-scatter kernel is queued on a side stream with a small CTA budget: each rank
+pull-reduces its 1/world slice from every peer over NVLink (or multimem.ld_reduce through the
+switch), multiplies by 1/world and stores fp32 -- reduction, scaling and cast in one pass, while
+backward keeps the other SMs.  The optimizer is sharded the same way (ZeRO-1): fused AdamW on the
+fp32 slice writes the new bf16 parameters into the flat parameter buffer, and an all-gather kernel
+pushes each slice to every rank.  With a world of one the same kernels run (the reduce-scatter
+degenerates to the scale/cast pass), so single-GPU and multi-GPU steps share one code path.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..engine import Engine
+from ..ops import collectives as coll
+from ..ops.elementwise import adamw_step
+
+
+class _Bucket:
+    def __init__(self, index: int):
+        self.index = index
+        self.params: List[nn.Parameter] = []
+        self.offsets: List[int] = []
+        self.numel = 0            # padded
+        self.pending = 0
+        self.grads: torch.Tensor = None      # bf16 view in the symmetric heap
+        self.values: torch.Tensor = None     # bf16 view of the flat parameters
+        self.grad_shard: torch.Tensor = None  # fp32, numel / world
+        self.master: torch.Tensor = None
+        self.exp_avg: torch.Tensor = None
+        self.exp_avg_sq: torch.Tensor = None
+        self.decay = True
+
+
+class ShardedDataParallel:
+    """Wraps a model for data-parallel training over an ``Engine`` (one process per GPU).
+
+    ``train_step(inputs, targets)`` runs forward, backward (with overlapped gradient reduction) and
+    the sharded optimizer step, and returns the loss tensor.
+    """
+
+    def __init__(self, model: nn.Module, engine: Optional[Engine] = None, *, lr: float = 3e-4, betas=(0.9, 0.95),
+                 eps: float = 1e-8, weight_decay: float = 0.1, bucket_mb: float = 25.0, heap_bytes: int = 0,
+                 comm_blocks: int = 16, algo: str = "auto", group=None):
+        self.model = model
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.comm_blocks, self.algo = comm_blocks, algo
+        params = []
+        seen = set()
+        for p in model.parameters():
+            if p.requires_grad and id(p) not in seen:
+                seen.add(id(p))
+                params.append(p)
+        total = sum(p.numel() for p in params)
+        if engine is None:
+            need = 2 * 2 * (total + 64 * len(params)) + (64 << 20)
+            engine = Engine(0, 1)
+            os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
+            engine.initEngine("cuda", max(heap_bytes, need + (512 << 20)))
+        self.engine = engine
+        self.world, self.rank = engine.world, engine.rank
+        self.comm_stream = torch.cuda.Stream()
+        self.step_count = 0
+        self._build_buckets(params, int(bucket_mb * (1 << 20)) // 2)
+        self._ready_events: Dict[int, torch.cuda.Event] = {}
+
+    # ------------------------------------------------------------------------------------------
+    def _build_buckets(self, params: List[nn.Parameter], cap_elems: int) -> None:
+        world = self.world
+        align = 8 * world                      # every rank's slice starts on a 16-byte boundary
+        self.buckets: List[_Bucket] = []
+        # Matrices (weight decay) and vectors (no decay) go to separate buckets, so that one fused
+        # AdamW launch per bucket has one decay setting.
+        open_buckets: Dict[bool, _Bucket] = {}
+        for p in reversed(params):             # gradients arrive roughly in reverse parameter order
+            decay = p.dim() >= 2
+            n = (p.numel() + 7) // 8 * 8
+            cur = open_buckets.get(decay)
+            if cur is None or (cur.params and cur.numel + n > cap_elems):
+                cur = _Bucket(len(self.buckets))
+                cur.decay = decay
+                self.buckets.append(cur)
+                open_buckets[decay] = cur
+            cur.params.append(p)
+            cur.offsets.append(cur.numel)
+            cur.numel += n
+        eng = self.engine
+        for b in self.buckets:
+            b.numel = (b.numel + align - 1) // align * align
+        total = sum(b.numel for b in self.buckets)
+        flat_g = eng.symmetric_tensor((total,), torch.bfloat16, align=256)
+        flat_p = eng.symmetric_tensor((total,), torch.bfloat16, align=256)
+        flat_g.zero_()
+        flat_p.zero_()
+        self.flat_grads, self.flat_params = flat_g, flat_p
+        base = 0
+        for b in self.buckets:
+            b.grads = flat_g[base:base + b.numel]
+            b.values = flat_p[base:base + b.numel]
+            shard = b.numel // world
+            for p, off in zip(b.params, b.offsets):
+                view = b.values[off:off + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.main_grad = b.grads[off:off + p.numel()].view(p.shape)
+                p._pccl_written = False
+                p._pccl_seen = 0
+                if not hasattr(p, "_pccl_uses"):
+                    p._pccl_uses = 1           # a model sets 2 on a weight it uses twice (tied embeddings)
+                p._pccl_ready = self._make_ready(b, p)
+                if not getattr(p, "_pccl_hooked", False):
+                    p.register_post_accumulate_grad_hook(self._autograd_hook)
+                    p._pccl_hooked = True
+            lo = self.rank * shard
+            b.master = b.values[lo:lo + shard].float().clone()
+            b.exp_avg = torch.zeros_like(b.master)
+            b.exp_avg_sq = torch.zeros_like(b.master)
+            b.grad_shard = torch.empty_like(b.master)
+            base += b.numel
+        torch.cuda.synchronize()
+
+    def _make_ready(self, bucket: _Bucket, p: torch.Tensor):
+        def ready():
+            p._pccl_seen += 1
+            if p._pccl_seen < p._pccl_uses:
+                return
+            bucket.pending -= 1
+            if bucket.pending == 0:
+                self._launch_reduce(bucket)
+        return ready
+
+    @staticmethod
+    def _autograd_hook(p: torch.Tensor) -> None:
+        """Parameters whose gradient autograd produced (norms, biases without a fused path)."""
+        g = p.grad
+        if g is None:
+            return
+        if p._pccl_written:
+            p.main_grad.add_(g.to(p.main_grad.dtype))
+        else:
+            p.main_grad.copy_(g)
+        p.grad = None
+        p._pccl_written = True
+        p._pccl_ready()
+
+    def _launch_reduce(self, b: _Bucket) -> None:
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.comm_stream.wait_event(ev)
+        coll.reduce_scatter(self.engine, b.grads, b.grad_shard, scale=1.0 / self.world, algo=self.algo,
+                            blocks=self.comm_blocks, lane=1, stream=self.comm_stream)
+
+    # ------------------------------------------------------------------------------------------
+    def zero_grad(self) -> None:
+        for b in self.buckets:
+            b.pending = len(b.params)
+            for p in b.params:
+                p._pccl_written = False
+                p._pccl_seen = 0
+                p.grad = None
+
+    def optimizer_step(self) -> None:
+        """Sharded AdamW + parameter all-gather, on the communication stream behind the reductions."""
+        self.step_count += 1
+        with torch.cuda.stream(self.comm_stream):
+            for b in self.buckets:
+                if b.pending != 0:
+                    raise RuntimeError(f"bucket {b.index}: {b.pending} gradient(s) never arrived "
+                                       "(a parameter took no part in the loss)")
+                shard = b.numel // self.world
+                lo = self.rank * shard
+                dst = b.values[lo:lo + shard]
+                adamw_step(b.master, b.exp_avg, b.exp_avg_sq, b.grad_shard, dst, lr=self.lr, betas=self.betas,
+                           eps=self.eps, weight_decay=self.weight_decay if b.decay else 0.0,
+                           step=self.step_count, stream=self.comm_stream)
+                if self.world > 1:
+                    coll.all_gather(self.engine, dst, b.values, algo=self.algo, blocks=self.comm_blocks, lane=2,
+                                    stream=self.comm_stream)
+        torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def train_step(self, inputs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        self.zero_grad()
+        loss = self.model(inputs, targets)
+        loss.backward()
+        self.optimizer_step()
+        return loss.detach()
+
+    def gather_full_state(self) -> Dict[str, torch.Tensor]:
+        """Checkpoint helper: this rank's optimizer shards plus the (replicated) bf16 parameters."""
+        return {"step": torch.tensor(self.step_count), "flat_params": self.flat_params.clone(),
+                **{f"master.{b.index}": b.master.clone() for b in self.buckets},
+                **{f"exp_avg.{b.index}": b.exp_avg.clone() for b in self.buckets},
+                **{f"exp_avg_sq.{b.index}": b.exp_avg_sq.clone() for b in self.buckets}}
+
+    def load_full_state(self, state: Dict[str, torch.Tensor]) -> None:
+        self.step_count = int(state["step"])
+        self.flat_params.copy_(state["flat_params"])
+        for b in self.buckets:
+            b.master.copy_(state[f"master.{b.index}"])
+            b.exp_avg.copy_(state[f"exp_avg.{b.index}"])
+            b.exp_avg_sq.copy_(state[f"exp_avg_sq.{b.index}"])

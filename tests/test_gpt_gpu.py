@@ -1,0 +1,96 @@
+"""The GPT model on this package's kernels against the same network written with stock PyTorch ops
+in fp32, and the sharded data-parallel step with a world of one."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference_loss(model, ids, targets):
+    """Same weights, fp32 math, stock ops."""
+    cfg = model.cfg
+    f = lambda t: t.detach().float().requires_grad_(True)  # noqa: E731
+    P = {n: f(p) for n, p in model.named_parameters()}
+    B, T = ids.shape
+    x = P["wte.weight"][ids] + P["wpe.weight"][torch.arange(T, device=ids.device)][None]
+    for i in range(cfg.n_layer):
+        g = lambda n: P[f"blocks.{i}.{n}"]  # noqa: E731
+        h = F.layer_norm(x, (cfg.d_model,), g("ln1.weight"), g("ln1.bias"))
+        qkv = F.linear(h, g("qkv.weight"), g("qkv.bias")).view(B, T, 3, cfg.n_head, -1)
+        q, k, v = (qkv[:, :, j].transpose(1, 2) for j in range(3))
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, -1)
+        x = x + F.linear(a, g("proj.weight"), g("proj.bias"))
+        h = F.layer_norm(x, (cfg.d_model,), g("ln2.weight"), g("ln2.bias"))
+        x = x + F.linear(F.gelu(F.linear(h, g("fc1.weight"), g("fc1.bias")), approximate="tanh"), g("fc2.weight"), g("fc2.bias"))
+    x = F.layer_norm(x, (cfg.d_model,), P["ln_f.weight"], P["ln_f.bias"])
+    loss = F.cross_entropy(F.linear(x, P["wte.weight"]).view(B * T, -1), targets.reshape(-1))
+    loss.backward()
+    return loss.item(), {n: p.grad for n, p in P.items()}
+
+
+def test_gpt_forward_backward_matches_fp32_reference():
+    from pccl_b200.models import GPT, GPTConfig
+    from pccl_b200.ops import check_status
+    torch.manual_seed(0)
+    cfg = GPTConfig.tiny()
+    model = GPT(cfg, device="cuda")
+    ids = torch.randint(0, cfg.vocab_size, (4, cfg.seq_len), device="cuda")
+    tgt = ids.roll(-1, 1)
+    loss = model(ids, tgt)
+    loss.backward()
+    check_status("gpt")
+    ref_loss, ref_grads = _reference_loss(model, ids, tgt)
+    assert abs(loss.item() - ref_loss) < 0.02 * ref_loss
+    for name in ("blocks.0.qkv.weight", "blocks.1.fc1.weight", "blocks.1.fc2.weight", "blocks.0.proj.bias", "wte.weight",
+                 "wpe.weight", "blocks.1.ln2.weight"):
+        got = dict(model.named_parameters())[name].grad.float()
+        ref = ref_grads[name]
+        denom = ref.abs().max().item() + 1e-8
+        assert (got - ref).abs().max().item() / denom < 0.08, name
+
+
+def test_fused_cross_entropy_matches_torch():
+    from pccl_b200.nn import fused_cross_entropy
+    torch.manual_seed(1)
+    rows, vocab, ld = 300, 50257, 50264
+    store = (torch.randn(rows, ld, device="cuda") * 3).bfloat16()
+    logits = store[:, :vocab]
+    tgt = torch.randint(0, vocab, (rows,), device="cuda")
+    ref_in = logits.float().clone().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, tgt)
+    ref.backward()
+    x = logits.clone().as_strided(logits.shape, logits.stride()) if False else store.clone()[:, :vocab]
+    x.requires_grad_(True)
+    loss = fused_cross_entropy(x, tgt)
+    loss.backward()
+    assert abs(loss.item() - ref.item()) < 1e-3
+    assert (x.grad.float() - ref_in.grad).abs().max().item() < 2e-5 + 0.01 * ref_in.grad.abs().max().item()
+
+
+def test_adamw_kernel_matches_torch():
+    from pccl_b200.ops.elementwise import adamw_step
+    torch.manual_seed(2)
+    n = 100003
+    p = torch.randn(n, device="cuda"); g = torch.randn(n, device="cuda") * 0.1
+    ref_p = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v, out = torch.zeros_like(p), torch.zeros_like(p), torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        ref_p.grad = g.clone() * step
+        opt.step()
+        adamw_step(p, m, v, g * step, out, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, step=step)
+    assert (p - ref_p.detach()).abs().max().item() < 1e-5
+    assert torch.equal(out, p.bfloat16())
+
+
+def test_sharded_dp_world_of_one_trains_and_matches_plain_adamw():
+    from pccl_b200.models import GPT, GPTConfig
+    from pccl_b200.models.gpt import smoke_step
+    from pccl_b200.ops import check_status, launch_count
+    before = launch_count()
+    last = smoke_step()
+    check_status("dp")
+    assert math.isfinite(last) and launch_count() - before > 50
