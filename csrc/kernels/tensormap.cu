@@ -26,6 +26,13 @@ EncodeFn encoder() {
 
 bool makeTensorMap2D(CUtensorMap* out, const void* base, TmDType dt, uint64_t inner, uint64_t outer, uint64_t row_stride,
                      uint32_t box_inner, uint32_t box_outer, std::string* err) {
+  // The driver call needs a current context; a thread that has only made runtime calls that do
+  // not touch the device (an autograd worker, say) may not have bound the primary context yet.
+  static thread_local bool ctx_ready = false;
+  if (!ctx_ready) {
+    cudaFree(nullptr);
+    ctx_ready = true;
+  }
   EncodeFn fn = encoder();
   if (!fn) {
     if (err) *err = "cuTensorMapEncodeTiled is not available from this driver";

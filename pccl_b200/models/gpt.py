@@ -67,7 +67,7 @@ class Block(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, T, D = x.shape
         qkv = self.qkv(self.ln1(x)).view(B, T, 3, self.n_head, D // self.n_head)
-        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))    # unbind: one stacked gradient, no zero-fills
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.proj(a.transpose(1, 2).reshape(B, T, D))
         return x + self.fc2(self.fc1(self.ln2(x)))

@@ -1,0 +1,188 @@
+"""Worker run by tests/test_multigpu.py under torch.distributed.run (one process per GPU).
+
+Every case ends with a barrier and an orderly teardown, also when an assertion fails, so that no
+rank leaves while its memory is still bound to the multicast object or while a peer's kernel waits.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def case_heap(eng, rank, world):
+    """Peer mapping: every rank writes a pattern into its symmetric tensor and reads its neighbour's."""
+    t = eng.symmetric_tensor((1024,), torch.float32)
+    t.fill_(float(rank + 1))
+    torch.cuda.synchronize(); dist.barrier()
+    nxt = (rank + 1) % world
+    peer = eng.tensor_at(eng.heap_offset(t), (1024,), torch.float32, rank=nxt)
+    assert torch.all(peer == float(nxt + 1)), "peer read returned the wrong data"
+    peer[:8] = 100.0 + rank                      # peer write
+    torch.cuda.synchronize(); dist.barrier()
+    prev = (rank - 1) % world
+    assert torch.all(t[:8] == 100.0 + prev) and torch.all(t[8:] == float(rank + 1))
+    return {"nvls": eng.has_nvls}
+
+
+def _coll_checks(eng, rank, world, algo):
+    from pccl_b200.ops import collectives as C
+    res = {}
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        for n in (8, 1024, 1 << 20, (1 << 20) + 24):
+            g = torch.Generator(device="cuda").manual_seed(7)
+            xs = [torch.randn(n, generator=g, device="cuda").to(dtype) for _ in range(world)]
+            mark = eng.symmetric_mark()
+            inp = eng.symmetric_tensor((n,), dtype); out = eng.symmetric_tensor((n,), dtype)
+            for it in range(2):
+                inp.copy_(xs[rank] * (it + 1))
+                C.all_reduce(eng, inp, out, algo=algo)
+                torch.cuda.synchronize()
+                ref = torch.stack([x.float() * (it + 1) for x in xs]).sum(0)
+                err = (out.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+                assert err <= tol * world, f"allreduce {algo} {dtype} n={n}: {err}"
+            # in place (two-shot)
+            inp.copy_(xs[rank]); C.all_reduce(eng, inp, algo=algo); torch.cuda.synchronize()
+            ref = torch.stack([x.float() for x in xs]).sum(0)
+            assert (inp.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item()) <= tol * world
+            # reduce-scatter with scale and fp32 output into a plain tensor
+            if n % world == 0:
+                inp.copy_(xs[rank])
+                shard = torch.empty(n // world, dtype=torch.float32, device="cuda")
+                C.reduce_scatter(eng, inp, shard, scale=1.0 / world, algo=algo); torch.cuda.synchronize()
+                ref = (torch.stack([x.float() for x in xs]).sum(0) / world)[rank * (n // world):(rank + 1) * (n // world)]
+                assert (shard - ref).abs().max().item() <= tol
+                # all-gather of the shards back
+                src = xs[rank][: n // world].contiguous()
+                C.all_gather(eng, src, out, algo=algo); torch.cuda.synchronize()
+                ref = torch.cat([x[: n // world] for x in xs])
+                assert torch.equal(out, ref), f"allgather {algo} n={n}"
+                # all-to-all
+                C.all_to_all(eng, xs[rank], out); torch.cuda.synchronize()
+                blk = n // world
+                ref = torch.cat([x[rank * blk:(rank + 1) * blk] for x in xs])
+                assert torch.equal(out, ref), "alltoall"
+            eng.symmetric_reset(mark)
+            dist.barrier()
+    eng.raise_on_status(8, "collectives")
+    res["ok"] = True
+    return res
+
+
+def case_coll_p2p(eng, rank, world):
+    return _coll_checks(eng, rank, world, "p2p")
+
+
+def case_coll_nvls(eng, rank, world):
+    if not eng.has_nvls:
+        return {"skipped": "no multicast"}
+    return _coll_checks(eng, rank, world, "nvls")
+
+
+def case_interp(eng, rank, world):
+    """Lowered programs through the interpreter kernel, including the NVLS ones."""
+    from pccl_b200.lang import build
+    names = ["ring_allreduce", "direct_allreduce", "direct_reduce_scatter", "direct_allgather", "alltoall", "tree_allreduce"]
+    if eng.has_nvls:
+        names += ["nvls_allreduce", "nvls_reduce_scatter", "nvls_allgather"]
+    n = 64 * 1024
+    for name in names:
+        ir = build(name, world, channels=2)
+        eng.regOp(name, ir)
+        coll = ir.collective
+        n_in = {"allreduce": n, "reduce_scatter": n * world, "allgather": n, "alltoall": n * world}[coll]
+        n_out = {"allreduce": n, "reduce_scatter": n, "allgather": n * world, "alltoall": n * world}[coll]
+        g = torch.Generator(device="cuda").manual_seed(11)
+        xs = [torch.randn(n_in, generator=g, device="cuda") for _ in range(world)]
+        mark = eng.symmetric_mark()
+        inp = eng.symmetric_tensor((n_in,), torch.float32); out = eng.symmetric_tensor((n_out,), torch.float32)
+        for it in range(2):
+            inp.copy_(xs[rank] + it)
+            if name.startswith("nvls"):
+                torch.cuda.synchronize(); dist.barrier()
+            eng.exeOp(name, inp, out, width=4, check=True)
+            full = torch.stack([x + it for x in xs])
+            res = inp if ir.in_place else out
+            if coll == "allreduce":
+                ref = full.sum(0)
+            elif coll == "reduce_scatter":
+                ref = full.sum(0)[rank * n:(rank + 1) * n]
+            elif coll == "allgather":
+                ref = torch.cat(list(full))
+            else:
+                ref = torch.cat([f[rank * n:(rank + 1) * n] for f in full])
+            err = (res - ref).abs().max().item()
+            assert err < 1e-3, f"{name} iteration {it}: {err}"
+            dist.barrier()
+        eng.symmetric_reset(mark)
+    return {"programs": names}
+
+
+def case_dp(eng, rank, world):
+    """Two steps of sharded data-parallel training give every rank the same parameters, equal to a
+    single-process run on the concatenated batch (up to bf16 rounding)."""
+    from pccl_b200.models import GPT, GPTConfig
+    from pccl_b200.parallel import ShardedDataParallel
+    cfg = GPTConfig.tiny()
+    torch.manual_seed(0)
+    model = GPT(cfg, device="cuda")
+    dp = ShardedDataParallel(model, eng, lr=1e-3, bucket_mb=0.25)
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, cfg.vocab_size, (2 * world, cfg.seq_len + 1), generator=g)
+    mine = data[2 * rank:2 * rank + 2].cuda()
+    losses = [float(dp.train_step(mine[:, :-1], mine[:, 1:])) for _ in range(3)]
+    torch.cuda.synchronize()
+    flat = dp.flat_params.float()
+    ref = flat.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(ref, flat), "ranks disagree on the parameters after the all-gather"
+    lt = torch.tensor(losses, device="cuda"); dist.all_reduce(lt); lt /= world
+    assert lt[-1] < lt[0], f"mean loss did not go down: {lt.tolist()}"
+    eng.raise_on_status(9, "dp reduce-scatter"); eng.raise_on_status(10, "dp all-gather")
+    return {"losses": lt.tolist()}
+
+
+CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
+
+
+def main():
+    case = sys.argv[1]
+    out_path = sys.argv[2]
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from pccl_b200.engine import Engine
+    os.environ.setdefault("PCCL_WORKSPACE_MB", "256")
+    eng = Engine(rank, world)
+    result = {"ok": False}
+    try:
+        eng.initEngine("cuda", heap_bytes=2 << 30)
+        eng.connect(nvls=os.environ.get("PCCL_TEST_NVLS", "1") == "1")
+        info = CASES[case](eng, rank, world)
+        result = {"ok": True, "info": info}
+    except BaseException as e:  # noqa: BLE001
+        result = {"ok": False, "error": f"{type(e).__name__}: {e}", "trace": traceback.format_exc()}
+    try:
+        torch.cuda.synchronize()
+    except Exception:  # noqa: BLE001
+        pass
+    flags = [None] * world
+    dist.all_gather_object(flags, result)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(flags, f)
+    dist.barrier()
+    del eng
+    dist.destroy_process_group()
+    sys.exit(0 if all(f["ok"] for f in flags) else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,40 @@
+"""Multi-GPU tests: one process per GPU under torch.distributed.run, NCCL only for the rendezvous."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from _ranks import free_port
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(case, nproc, tmp_path, env=None, timeout=600):
+    out = tmp_path / f"{case}.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), os.path.join(HERE, "mp_worker.py"), case, str(out)]
+    e = dict(os.environ)
+    e.update(env or {})
+    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=timeout)
+    results = json.loads(out.read_text()) if out.exists() else None
+    assert results is not None, f"workers left no result file\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
+    for rank, res in enumerate(results):
+        assert res["ok"], f"rank {rank}: {res.get('error')}\n{res.get('trace', '')}"
+    return results
+
+
+def _world():
+    return min(torch.cuda.device_count(), 8)
+
+
+@pytest.mark.parametrize("case", ["heap", "coll_p2p", "coll_nvls", "interp", "dp"])
+def test_case(case, tmp_path):
+    _run(case, _world(), tmp_path)
+
+
+def test_collectives_without_nvls(tmp_path):
+    _run("coll_p2p", _world(), tmp_path, env={"PCCL_TEST_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
