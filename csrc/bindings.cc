@@ -234,6 +234,10 @@ PYBIND11_MODULE(_C, m) {
     throwIfCuda(launchWaitTimeoutProbe(reinterpret_cast<uint64_t*>(flag), spin_limit, reinterpret_cast<uint32_t*>(status),
                                        reinterpret_cast<cudaStream_t>(stream)), "wait_timeout_probe");
   });
+  m.def("memcpy_d2d", [](uint64_t dst, uint64_t src, uint64_t nbytes, uint64_t stream) {
+    throwIfCuda(static_cast<int>(cudaMemcpyAsync(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), nbytes,
+                                                 cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream))), "memcpy_d2d");
+  });
   m.def("sm_count", &deviceSmCount);
   m.attr("MAX_RANKS") = kMaxRanks;
   m.attr("MAX_BLOCKS_PER_COLL") = kMaxBlocksPerColl;

@@ -332,7 +332,7 @@ size_t CudaDevice::multicastGranularity(int num_devices, size_t bytes) {
   p.size = bytes;
   p.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
   size_t g = 0;
-  check(drv().MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_RECOMMENDED), "cuMulticastGetGranularity");
+  check(drv().MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_MINIMUM), "cuMulticastGetGranularity");
   return g;
 }
 

@@ -162,6 +162,8 @@ class Engine:
         for s in shape:
             n *= int(s)
         nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if rank is not None and rank != self.rank and self.device == "cuda":
+            raise PcclError("a peer's heap cannot be wrapped as a torch tensor; use read_peer / write_peer")
         base = self._e.heapBase(self.rank if rank is None else rank)
         if base == 0:
             raise PcclError("that rank's heap is not mapped")
@@ -172,6 +174,26 @@ class Engine:
             buf = (ctypes.c_uint8 * max(nbytes, 1)).from_address(base + heap_off)
             t = torch.frombuffer(buf, dtype=torch.uint8)
         return t[:nbytes].view(dtype).view(*shape)
+
+    def read_peer(self, rank: int, heap_off: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Copy of `shape` elements at `heap_off` of rank `rank`'s heap (a device-to-device copy over
+        NVLink for CUDA ranks, a shared-memory read for CPU ranks)."""
+        if self.device != "cuda":
+            return self.tensor_at(heap_off, shape, dtype, rank=rank).clone()
+        out = torch.empty(tuple(shape), dtype=dtype, device="cuda")
+        base = self._e.heapBase(rank)
+        if base == 0:
+            raise PcclError("that rank's heap is not mapped")
+        C.memcpy_d2d(out.data_ptr(), base + heap_off, out.numel() * out.element_size(), torch.cuda.current_stream().cuda_stream)
+        return out
+
+    def write_peer(self, rank: int, heap_off: int, src: torch.Tensor) -> None:
+        if self.device != "cuda":
+            self.tensor_at(heap_off, src.shape, src.dtype, rank=rank).copy_(src)
+            return
+        src = src.contiguous()
+        C.memcpy_d2d(self._e.heapBase(rank) + heap_off, src.data_ptr(), src.numel() * src.element_size(),
+                     torch.cuda.current_stream().cuda_stream)
 
     def heap_offset(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self._e.heapBase(self.rank)

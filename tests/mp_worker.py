@@ -23,9 +23,9 @@ def case_heap(eng, rank, world):
     t.fill_(float(rank + 1))
     torch.cuda.synchronize(); dist.barrier()
     nxt = (rank + 1) % world
-    peer = eng.tensor_at(eng.heap_offset(t), (1024,), torch.float32, rank=nxt)
+    peer = eng.read_peer(nxt, eng.heap_offset(t), (1024,), torch.float32)
     assert torch.all(peer == float(nxt + 1)), "peer read returned the wrong data"
-    peer[:8] = 100.0 + rank                      # peer write
+    eng.write_peer(nxt, eng.heap_offset(t), torch.full((8,), 100.0 + rank, device="cuda"))
     torch.cuda.synchronize(); dist.barrier()
     prev = (rank - 1) % world
     assert torch.all(t[:8] == 100.0 + prev) and torch.all(t[8:] == float(rank + 1))
