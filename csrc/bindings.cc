@@ -181,7 +181,8 @@ py::dict layoutDict(const Engine& e) {
 
 }  // namespace
 
-void bindGemm(py::module_& m);   // gemm_bindings.cc
+void bindGemm(py::module_& m);    // gemm_bindings.cc
+void bindFused(py::module_& m);   // fused_bindings.cc
 
 PYBIND11_MODULE(_C, m) {
   m.doc() = "pccl_b200 native runtime";
@@ -243,6 +244,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("MAX_BLOCKS_PER_COLL") = kMaxBlocksPerColl;
 
   bindGemm(m);
+  bindFused(m);
 
   auto utils = m.def_submodule("utils");
   py::class_<LaunchEnvironments, std::unique_ptr<LaunchEnvironments, py::nodelete>>(utils, "LaunchEnvironments")

@@ -1,0 +1,68 @@
+// Host entry points of the kernels that fuse a collective into the tcgen05 GEMM (fused_tp.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "api.h"
+
+namespace pccl {
+
+constexpr int kMaxVirt = 4;   // ranks that one launch can emulate on a single GPU (tests)
+
+struct AgGemmRank {
+  CUtensorMap tmA, tmB;       // filled by launchAgGemm
+  void* D;                    // [M, N] bf16 output (local)
+  long long ldd;
+  const void* bias;           // bf16 [N] or null
+  uint32_t* ready;            // local, zero-initialised once: one counter per 128-row chunk of the gathered X
+  uint32_t* status;
+  int rank;
+  int pad;
+};
+
+struct AgGemmArgs {
+  World w;
+  int nvirt;                  // 1, or the emulated world size
+  int M, N, K, M_local;       // M = M_local * world
+  uint64_t x_off;             // heap offset of the symmetric gathered-X buffer [M, K] bf16; rows
+                              // [rank*M_local, (rank+1)*M_local) hold the rank's own activations
+  uint64_t epoch;             // 1, 2, 3, ... per launch on these buffers
+  int n_copy;                 // CTAs that pull peer rows (the rest compute)
+  int flag_lane;
+  uint64_t spin_ns;
+  uint32_t flags;             // GEMM_BIAS
+  uint32_t pad;
+  AgGemmRank r[kMaxVirt];
+};
+
+struct AgGemmHost { const void* W; long long ldw; };   // W1 shard [N, K] bf16, per (virtual) rank
+
+struct GemmRsRank {
+  CUtensorMap tmA, tmB;
+  void* out;                  // [M_local, N] bf16 (local)
+  long long ldo;
+  uint32_t* status;
+  int rank;
+  int pad;
+};
+
+struct GemmRsArgs {
+  World w;
+  int nvirt;
+  int M, N, K, M_local;
+  uint64_t stage_off;         // heap offset of the symmetric staging buffer [world][M_local][N] bf16
+  uint64_t flag_off2;         // heap offset of the symmetric tile flags uint64 [world][M_local/128 * N/256], zeroed once
+  uint64_t epoch;
+  uint64_t spin_ns;
+  GemmRsRank r[kMaxVirt];
+};
+
+struct GemmRsHost { const void* Y; long long ldy; const void* W; long long ldw; };   // Y [M, K], W2 shard [N, K]
+
+int launchAgGemm(AgGemmArgs& args, const AgGemmHost* host, int ctas, cudaStream_t stream);
+int launchGemmRs(GemmRsArgs& args, const GemmRsHost* host, int ctas, cudaStream_t stream);
+const char* fusedLastError();
+
+}  // namespace pccl

@@ -1,0 +1,96 @@
+// Epilogue that stores a GEMM tile to local memory: optional bias, optional GELU side output, bf16 or
+// fp32, optional accumulation into D.  Shared by the plain GEMM and the all-gather -> GEMM kernel.
+#pragma once
+#include "gemm_api.h"
+#include "gemm_pipeline.cuh"
+
+namespace pccl {
+namespace gemm {
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+
+struct StoreEpi {
+  void* D;
+  void* D2;
+  const __nv_bfloat16* bias;
+  long long ldd;
+  int M, N;
+  uint32_t flags;
+
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.m * BM; }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * BN; }
+  __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
+
+  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
+    const int row = t.m * BM + row_in_tile, col = t.n * BN + col_in_tile;
+    if (row >= M || col >= N) return;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    const bool full = col + 32 <= N;
+    if (flags & GEMM_BIAS) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (full || col + i < N) v[i] += __bfloat162float(bias[col + i]);
+    }
+    if (flags & GEMM_OUT_F32) {
+      float* d = static_cast<float*>(D) + static_cast<long long>(row) * ldd + col;
+      if (full) {
+        if (flags & GEMM_ACCUMULATE) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 o = *reinterpret_cast<float4*>(d + i);
+            v[i] += o.x; v[i + 1] += o.y; v[i + 2] += o.z; v[i + 3] += o.w;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(d + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col + i < N) d[i] = (flags & GEMM_ACCUMULATE) ? d[i] + v[i] : v[i];
+      }
+      return;
+    }
+    __nv_bfloat16* d = static_cast<__nv_bfloat16*>(D) + static_cast<long long>(row) * ldd + col;
+    if (full) {
+      if (flags & GEMM_ACCUMULATE) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          dev::Vec16 o = dev::ld16(d + i);
+          float f[8];
+          dev::unpack<DT_BF16>(o, f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i + j] += f[j];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) dev::st16(d + i, dev::pack<DT_BF16>(v + i));
+      if (flags & GEMM_GELU) {
+        __nv_bfloat16* d2 = static_cast<__nv_bfloat16*>(D2) + static_cast<long long>(row) * ldd + col;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) dev::st16(d2 + i, dev::pack<DT_BF16>(v + i));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (col + i >= N) continue;
+        float x = (flags & GEMM_ACCUMULATE) ? v[i] + __bfloat162float(d[i]) : v[i];
+        d[i] = __float2bfloat16_rn(x);
+        if (flags & GEMM_GELU)
+          (static_cast<__nv_bfloat16*>(D2) + static_cast<long long>(row) * ldd + col)[i] = __float2bfloat16_rn(gelu_tanh(x));
+      }
+    }
+  }
+};
+
+}  // namespace gemm
+}  // namespace pccl

@@ -33,6 +33,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;              // two 128x256 fp32 accumulators
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_SMEM_OFFSET = STAGES * STAGE_BYTES + 256;   // epilogues that stage through shared memory start here
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -108,6 +109,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
+  epi.attach_smem(smem + EPI_SMEM_OFFSET);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer

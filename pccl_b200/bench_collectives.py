@@ -1,0 +1,133 @@
+"""Collective micro-benchmarks: this library's kernels (NVLS and P2P forms) against NCCL on the same
+GPUs, same sizes.  Device-timed with CUDA events, maximum over ranks; buffers rotate through a pool
+larger than the 126 MB L2 so that consecutive iterations do not find their data cached.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m pccl_b200.bench_collectives \\
+        --min-bytes 1024 --max-bytes 1073741824 --out sweep.json
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .engine import Engine
+from .ops import collectives as C
+
+POOL_BYTES = 320 << 20
+
+
+def _time(fn_at, n_slots: int, iters: int, warmup: int) -> float:
+    """Median-free mean of `iters` back-to-back calls (events bracket the whole train of calls)."""
+    for i in range(warmup):
+        fn_at(i % n_slots)
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn_at((warmup + i) % n_slots)
+    b.record()
+    b.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def bus_factor(kind: str, n: int) -> float:
+    return 2.0 * (n - 1) / n if kind == "allreduce" else (n - 1) / n
+
+
+def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: List[str], iters: Optional[int] = None) -> Dict:
+    """`nbytes` = bytes of the full vector (all-reduce) or of the gathered/scattered whole (RS/AG)."""
+    world = eng.world
+    es = torch.empty((), dtype=dtype).element_size()
+    n = max(world * 16 // es, nbytes // es // (world * 16 // es) * (world * 16 // es))
+    nbytes = n * es
+    if iters is None:
+        iters = 200 if nbytes <= (1 << 20) else (50 if nbytes <= (64 << 20) else 10)
+    warmup = max(3, iters // 10)
+    slot = (nbytes + 255) // 256 * 256
+    n_slots = max(1, min(64, POOL_BYTES // (2 * slot)))
+    mark = eng.symmetric_mark()
+    pool_in = eng.symmetric_tensor((n_slots * slot,), torch.uint8)
+    pool_out = eng.symmetric_tensor((n_slots * slot,), torch.uint8)
+    pool_in.view(torch.int16)[:] = 0x3C00 if dtype != torch.float32 else 0     # finite values in every dtype
+    shard = n // world
+    ins = [pool_in[i * slot:i * slot + nbytes].view(dtype) for i in range(n_slots)]
+    outs = [pool_out[i * slot:i * slot + nbytes].view(dtype) for i in range(n_slots)]
+    res = {"kind": kind, "dtype": str(dtype).replace("torch.", ""), "bytes": nbytes, "n_gpus": world}
+    for impl in impls:
+        if impl == "nccl":
+            if kind == "allreduce":
+                fn = lambda i: dist.all_reduce(ins[i])  # noqa: E731
+            elif kind == "reduce_scatter":
+                fn = lambda i: dist.reduce_scatter_tensor(outs[i][:shard], ins[i])  # noqa: E731
+            else:
+                fn = lambda i: dist.all_gather_into_tensor(outs[i], ins[i][:shard])  # noqa: E731
+        else:
+            if impl == "nvls" and not eng.has_nvls:
+                continue
+            if kind == "allreduce":
+                fn = lambda i, a=impl: C.all_reduce(eng, ins[i], outs[i], algo=a)  # noqa: E731
+            elif kind == "reduce_scatter":
+                fn = lambda i, a=impl: C.reduce_scatter(eng, ins[i], outs[i][:shard], algo=a)  # noqa: E731
+            else:
+                fn = lambda i, a=impl: C.all_gather(eng, ins[i][:shard], outs[i], algo=a)  # noqa: E731
+        ms = _time(fn, n_slots, iters, warmup)
+        alg = nbytes / (ms * 1e-3) / 1e9
+        res[impl] = {"us": ms * 1e3, "algbw_gbs": alg, "busbw_gbs": alg * bus_factor(kind, world)}
+    eng.symmetric_reset(mark)
+    return res
+
+
+def quick_micro(eng: Engine) -> Dict:
+    """Three all-reduce sizes, ours against NCCL; cheap enough to ride along with bench.py."""
+    out = []
+    for nbytes in (1 << 20, 16 << 20, 256 << 20):
+        out.append(bench_size(eng, "allreduce", torch.bfloat16, nbytes, ["nvls", "p2p", "nccl"], iters=20 if nbytes > (1 << 24) else 50))
+    return {"allreduce_bf16": out}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-bytes", type=int, default=1024)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--kinds", default="allreduce,reduce_scatter,allgather")
+    ap.add_argument("--dtypes", default="bf16,f32")
+    ap.add_argument("--impls", default="nvls,p2p,nccl")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
+    eng = Engine(rank, world)
+    eng.initEngine("cuda", heap_bytes=(2 * POOL_BYTES) + 4 * args.max_bytes + (512 << 20))
+    eng.connect()
+    dtypes = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}
+    rows = []
+    for kind in args.kinds.split(","):
+        for dn in args.dtypes.split(","):
+            nbytes = args.min_bytes
+            while nbytes <= args.max_bytes:
+                r = bench_size(eng, kind, dtypes[dn], nbytes, args.impls.split(","))
+                rows.append(r)
+                if rank == 0:
+                    print(json.dumps(r), flush=True)
+                nbytes *= 2
+    eng.raise_on_status(8, "sweep")
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            json.dump({"n_gpus": world, "nvls": eng.has_nvls, "rows": rows}, f)
+    dist.barrier()
+    del eng
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -166,3 +166,63 @@ def test_interpreter_peer_never_arrives(native):
                        torch.cuda.current_stream().cuda_stream)
     assert st[0][0].item() == 1 and st[1][0].item() == 0
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+# ---------------------------------------------------------------------------------------------
+# fused collective + GEMM kernels, ranks emulated on one GPU
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("world", [2, 4])
+def test_ag_gemm_emulated(native, world):
+    M_local, K, N = 256, 512, 520
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(9)
+    xs = [(torch.randn(M_local, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16() for _ in range(world)]
+    x_off = DATA_OFF
+    heaps = [torch.zeros(DATA_OFF + M * K * 2, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ready = [torch.zeros(M // 128, dtype=torch.int32, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ctas = 148 // world
+    for epoch in (1, 2):
+        for r in range(world):
+            full = heaps[r][x_off:x_off + M * K * 2].view(torch.bfloat16).view(M, K)
+            full.zero_()
+            full[r * M_local:(r + 1) * M_local] = xs[r] * epoch
+        native.emu_ag_gemm([h.data_ptr() for h in heaps], FLAG_OFF, x_off, M, N, K, [w.data_ptr() for w in ws], K,
+                           [o.data_ptr() for o in outs], N, [t.data_ptr() for t in ready], epoch, 4, ctas,
+                           [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        X = torch.cat(xs).float() * epoch
+        for r in range(world):
+            ref = X @ ws[r].float().t()
+            assert (outs[r].float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+            gathered = heaps[r][x_off:x_off + M * K * 2].view(torch.bfloat16).view(M, K)
+            assert torch.equal(gathered.float(), X)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gemm_rs_emulated(native, world):
+    M_local, K, N = 128, 448, 512
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(10)
+    ys = [(torch.randn(M, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16() for _ in range(world)]
+    stage_bytes = world * M_local * N * 2
+    n_flags = world * (M_local // 128) * (N // 256)
+    heaps = [torch.zeros(DATA_OFF + stage_bytes + n_flags * 8, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(M_local, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for epoch in (1, 2):
+        native.emu_gemm_rs([h.data_ptr() for h in heaps], [y.data_ptr() for y in ys], K, [w.data_ptr() for w in ws], K,
+                           [o.data_ptr() for o in outs], N, M, N, K, DATA_OFF, DATA_OFF + stage_bytes, epoch, 148 // world,
+                           [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        total = sum(ys[r].float() @ ws[r].float().t() for r in range(world))
+        for r in range(world):
+            ref = total[r * M_local:(r + 1) * M_local]
+            assert (outs[r].float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+        for y in ys:
+            y.mul_(0.5)
