@@ -1,0 +1,151 @@
+"""Tensor-parallel MLP micro-benchmark: the fused all-gather->GEMM and GEMM->reduce-scatter kernels
+against NCCL + torch.matmul (cuBLAS) on the same GPUs and shapes.
+
+Shapes (bf16): X is [tokens, d_model] sharded over ranks by rows; W1 is [d_ff / TP, d_model],
+W2 is [d_model, d_ff / TP].  Defaults: tokens 8192, d_model 8192, d_ff 28672.  Device-timed with
+CUDA events, max over ranks; every iteration is preceded by an L2 flush.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m pccl_b200.bench_tp --out tp.json
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .engine import Engine
+from .ops import check_status
+from .ops.fused_tp import AllGatherGemm, GemmReduceScatter
+from .ops.gemm import gemm
+from .utils import L2Flusher
+
+
+def _time(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        total += a.elapsed_time(b)
+    t = torch.tensor([total / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) * 1e3      # microseconds
+
+
+def run(eng: Engine, tokens: int, d_model: int, d_ff: int, iters: int = 20, warmup: int = 5, n_copy: int = 16,
+        peak_tflops: float = 1701.7, link_gbs: float = 770.0):
+    world, rank = eng.world, eng.rank
+    n1 = d_ff // world
+    m_local = tokens // world
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x_local = torch.randn(m_local, d_model, generator=g, device="cuda").bfloat16()
+    w1 = (torch.randn(n1, d_model, generator=g, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(d_model, n1, generator=g, device="cuda") * 0.02).bfloat16()
+    flush = L2Flusher()
+    rows = []
+
+    # ---- all-gather -> GEMM -------------------------------------------------------------------
+    ag = AllGatherGemm(eng, tokens, d_model, n_copy=n_copy)
+    ag.x_local.copy_(x_local)
+    y = torch.empty(tokens, n1, dtype=torch.bfloat16, device="cuda")
+    xg = torch.empty(tokens, d_model, dtype=torch.bfloat16, device="cuda")
+    y_ref = torch.empty_like(y)
+
+    def nccl_ag_gemm():
+        dist.all_gather_into_tensor(xg, x_local)
+        torch.matmul(xg, w1.t(), out=y_ref)
+
+    fused = _time(lambda: ag(w1, out=y), iters, warmup, flush)
+    check_status("ag_gemm")
+    base = _time(nccl_ag_gemm, iters, warmup, flush)
+    gemm_cublas = _time(lambda: torch.matmul(xg, w1.t(), out=y_ref), iters, warmup, flush)
+    gemm_ours = _time(lambda: gemm(xg, w1, out=y_ref), iters, warmup, flush)
+    comm_only = _time(lambda: dist.all_gather_into_tensor(xg, x_local), iters, warmup, flush)
+    err = (y.float() - y_ref.float()).abs().max().item()
+    flops = 2.0 * tokens * n1 * d_model
+    comm_bytes = (world - 1) * m_local * d_model * 2
+    roof = max(flops / (peak_tflops * 1e12), comm_bytes / (link_gbs * 1e9)) * 1e6
+    rows.append({"op": "allgather_gemm", "n_gpus": world, "M": tokens, "N": n1, "K": d_model, "fused_us": fused,
+                 "nccl_plus_cublas_us": base, "cublas_gemm_us": gemm_cublas, "own_gemm_us": gemm_ours, "nccl_allgather_us": comm_only,
+                 "speedup_vs_nccl_cublas": base / fused, "roofline_us": roof, "fraction_of_roofline": roof / fused,
+                 "max_abs_diff_vs_baseline": err})
+
+    # ---- GEMM -> reduce-scatter ---------------------------------------------------------------
+    rs = GemmReduceScatter(eng, tokens, d_model)
+    h = (torch.randn(tokens, n1, generator=g, device="cuda") * 0.5).bfloat16()
+    z = torch.empty(m_local, d_model, dtype=torch.bfloat16, device="cuda")
+    part = torch.empty(tokens, d_model, dtype=torch.bfloat16, device="cuda")
+    z_ref = torch.empty_like(z)
+
+    def nccl_gemm_rs():
+        torch.matmul(h, w2.t(), out=part)
+        dist.reduce_scatter_tensor(z_ref, part)
+
+    fused = _time(lambda: rs(h, w2, out=z), iters, warmup, flush)
+    check_status("gemm_rs")
+    base = _time(nccl_gemm_rs, iters, warmup, flush)
+    gemm_cublas = _time(lambda: torch.matmul(h, w2.t(), out=part), iters, warmup, flush)
+    gemm_ours = _time(lambda: gemm(h, w2, out=part), iters, warmup, flush)
+    comm_only = _time(lambda: dist.reduce_scatter_tensor(z_ref, part), iters, warmup, flush)
+    nccl_gemm_rs()
+    rs(h, w2, out=z)
+    torch.cuda.synchronize()
+    err = (z.float() - z_ref.float()).abs().max().item()
+    flops = 2.0 * tokens * d_model * n1
+    comm_bytes = (world - 1) * m_local * d_model * 2
+    roof = max(flops / (peak_tflops * 1e12), comm_bytes / (link_gbs * 1e9)) * 1e6
+    rows.append({"op": "gemm_reduce_scatter", "n_gpus": world, "M": tokens, "N": d_model, "K": n1, "fused_us": fused,
+                 "nccl_plus_cublas_us": base, "cublas_gemm_us": gemm_cublas, "own_gemm_us": gemm_ours,
+                 "nccl_reduce_scatter_us": comm_only, "speedup_vs_nccl_cublas": base / fused, "roofline_us": roof,
+                 "fraction_of_roofline": roof / fused, "max_abs_diff_vs_baseline": err})
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--d-model", type=int, default=8192)
+    ap.add_argument("--d-ff", type=int, default=28672)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--n-copy", type=int, default=16)
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
+    eng = Engine(rank, world)
+    heap = 3 * args.tokens * args.d_model * 2 + (1 << 30)
+    eng.initEngine("cuda", heap_bytes=heap)
+    eng.connect()
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    rows = run(eng, args.tokens, args.d_model, args.d_ff, iters=args.iters, n_copy=args.n_copy,
+               peak_tflops=float(peaks.get("bf16_tflops", 1590.0)))
+    if rank == 0:
+        for r in rows:
+            print(json.dumps(r), flush=True)
+        if args.out:
+            with open(args.out, "w") as f:
+                json.dump(rows, f)
+    dist.barrier()
+    del eng
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

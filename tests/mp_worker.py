@@ -149,6 +149,46 @@ def case_dp(eng, rank, world):
     return {"losses": lt.tolist()}
 
 
+def case_fused_tp(eng, rank, world):
+    """all-gather -> GEMM and GEMM -> reduce-scatter against gathered/reduced fp32 references."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.fused_tp import AllGatherGemm, GemmReduceScatter
+    M_local, K, N = 256, 1024, 768
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(21)
+    xs = [(torch.randn(M_local, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.05).bfloat16() for _ in range(world)]
+    ag = AllGatherGemm(eng, M, K, n_copy=8)
+    for it in range(3):
+        ag.x_local.copy_(xs[rank] * (it + 1))
+        out = ag(ws[rank])
+        torch.cuda.synchronize()
+        check_status("ag_gemm")
+        X = torch.cat(xs).float() * (it + 1)
+        ref = X @ ws[rank].float().t()
+        err = (out.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        assert err < 0.03, f"ag_gemm iteration {it}: {err}"
+        assert torch.equal(ag.x_full.float(), X), "gathered X differs"
+        dist.barrier()
+    # GEMM -> RS: y differs per rank (each rank holds its K-slice of the activations)
+    K2, N2 = 512, 1024
+    ys = [(torch.randn(M, K2, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    w2 = [(torch.randn(N2, K2, generator=g, device="cuda") * 0.05).bfloat16() for _ in range(world)]
+    rs = GemmReduceScatter(eng, M, N2)
+    dist.barrier()
+    for it in range(3):
+        out = rs(ys[rank] if it % 2 == 0 else ys[rank] * 0.5, w2[rank])
+        torch.cuda.synchronize()
+        check_status("gemm_rs")
+        sc = 1.0 if it % 2 == 0 else 0.5
+        total = sum((ys[r].float() * sc).bfloat16().float() @ w2[r].float().t() for r in range(world))
+        ref = total[rank * M_local:(rank + 1) * M_local]
+        err = (out.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        assert err < 0.03, f"gemm_rs iteration {it}: {err}"
+        dist.barrier()
+    return {"ok": True}
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 
