@@ -109,3 +109,28 @@ def gemm_nn(a, b, **kw):
 def gemm_tn(a, b, **kw):
     """a[K,M].T @ b[K,N]"""
     return gemm(a, b, a_t=True, b_t=True, **kw)
+
+
+if __name__ == "__main__":      # python -m pccl_b200.ops.gemm --m 4096 --n 4096 --k 4096 [--iters 3] [--a-t] [--b-t]
+    import argparse
+    ap = argparse.ArgumentParser(description="run the tcgen05 GEMM a few times (profiling / timing target)")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--a-t", action="store_true")
+    ap.add_argument("--b-t", action="store_true")
+    a_ = ap.parse_args()
+    A = torch.randn((a_.k, a_.m) if a_.a_t else (a_.m, a_.k), device="cuda").bfloat16()
+    B = torch.randn((a_.k, a_.n) if a_.b_t else (a_.n, a_.k), device="cuda").bfloat16()
+    D = torch.empty((a_.m, a_.n), device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(a_.iters + 1)]
+    ev[0].record()
+    for i in range(a_.iters):
+        gemm(A, B, a_t=a_.a_t, b_t=a_.b_t, out=D)
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    check_status("gemm")
+    ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(a_.iters)]
+    print({"ms": ms, "tflops": [2 * a_.m * a_.n * a_.k / t / 1e9 for t in ms]})

@@ -164,7 +164,7 @@ def case_fused_tp(eng, rank, world):
         out = ag(ws[rank])
         torch.cuda.synchronize()
         check_status("ag_gemm")
-        X = torch.cat(xs).float() * (it + 1)
+        X = torch.cat([x * (it + 1) for x in xs]).float()      # scaled in bf16, like the shards
         ref = X @ ws[rank].float().t()
         err = (out.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
         assert err < 0.03, f"ag_gemm iteration {it}: {err}"
