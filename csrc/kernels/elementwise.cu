@@ -148,3 +148,72 @@ int launchCrossEntropy(void* logits, const long long* targets, float* loss, long
 }
 
 }  // namespace pccl
+
+// =================================================================================================
+// Allocation-free mean cross-entropy (declared in no_alloc_api.h)
+// =================================================================================================
+#include "no_alloc_api.h"
+
+namespace pccl {
+namespace {
+
+// Per-row losses of the call in flight.  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels below name it directly.
+static __device__ __align__(256) float g_noalloc_row_loss[PCCL_NOALLOC_MAX_ROWS];
+
+__global__ void __launch_bounds__(1024) noalloc_mean_kernel(float* __restrict__ out, long long rows, float scale) {
+  __shared__ float part[32];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < rows; i += blockDim.x) s += g_noalloc_row_loss[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) out[0] = s * scale;
+  }
+}
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+bool g_noalloc_attr[kMaxDevices] = {false};
+int g_noalloc_cuda_error = 0;
+
+}  // namespace
+}  // namespace pccl
+
+extern "C" int pccl_noalloc_last_cuda_error(void) { return pccl::g_noalloc_cuda_error; }
+
+extern "C" int pccl_cross_entropy_mean_noalloc(void* logits, const long long* targets, float* mean_loss, long long rows, int vocab,
+                                               long long ld, cudaStream_t stream) {
+  using namespace pccl;
+  if (!logits || !targets || !mean_loss || rows <= 0 || vocab <= 0) return PCCL_NOALLOC_BAD_ARGUMENT;
+  if (rows > PCCL_NOALLOC_MAX_ROWS) return PCCL_NOALLOC_TOO_LARGE;
+  const size_t smem = (static_cast<size_t>(vocab) * 2 + 15) / 16 * 16;
+  if (smem > 200 * 1024 || ld % 8 || ld < vocab || reinterpret_cast<uintptr_t>(logits) % 16) return PCCL_NOALLOC_BAD_ARGUMENT;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
+  if (!g_noalloc_ptr[dev]) {
+    // once per device, with that device current: the device address of the static array
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_row_loss);
+    if (e != cudaSuccess || !p) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  if (!g_noalloc_attr[dev]) {
+    e = cudaFuncSetAttribute(cross_entropy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
+    g_noalloc_attr[dev] = true;
+  }
+  const float scale = 1.0f / static_cast<float>(rows);
+  cross_entropy_kernel<<<static_cast<unsigned>(rows), 512, smem, stream>>>(static_cast<__nv_bfloat16*>(logits), targets,
+                                                                          g_noalloc_ptr[dev], vocab, ld, scale, -(1ll << 62));
+  noalloc_mean_kernel<<<1, 1024, 0, stream>>>(mean_loss, rows, scale);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
+  return PCCL_NOALLOC_OK;
+}
