@@ -9,6 +9,7 @@
 #include "engine.h"
 #include "kernels/fused_api.h"
 #include "kernels/gemm_api.h"
+#include "kernels/moe_api.h"
 
 namespace py = pybind11;
 using namespace pccl;
@@ -29,7 +30,70 @@ void check(int err, const char* what) {
 
 }  // namespace
 
+namespace {
+MoeArgs moeArgs(const World& w, int nvirt, int rank, int tokens, int hidden, int topk, int epr, uint64_t recv_q_off,
+                uint64_t recv_s_off, uint64_t y_off, uint64_t epoch, int flag_lane, uint64_t spin_ns) {
+  MoeArgs a{};
+  a.w = w; a.nvirt = nvirt; a.rank = rank; a.tokens = tokens; a.hidden = hidden; a.topk = topk; a.experts_per_rank = epr;
+  a.recv_q_off = recv_q_off; a.recv_s_off = recv_s_off; a.y_off = y_off; a.epoch = epoch; a.flag_lane = flag_lane;
+  a.spin_ns = spin_ns ? spin_ns : kDefaultSpinLimit;
+  return a;
+}
+}  // namespace
+
 void bindFused(py::module_& m) {
+  // ---- MoE ---------------------------------------------------------------------------------------
+  // kind: "dispatch" | "combine".  Lists carry one entry per (virtual) rank: 1 in production.
+  m.def("moe_exchange", [](const std::string& kind, Engine* e, const std::vector<uint64_t>& heaps, uint64_t flag_off, int tokens,
+                           int hidden, int topk, int epr, uint64_t recv_q_off, uint64_t recv_s_off, uint64_t y_off, uint64_t epoch,
+                           int flag_lane, const std::vector<uint64_t>& x, const std::vector<uint64_t>& ids,
+                           const std::vector<uint64_t>& rows, const std::vector<uint64_t>& probs, const std::vector<uint64_t>& out,
+                           const std::vector<uint64_t>& status, int blocks, uint64_t spin_ns, uint64_t stream) {
+    MoeArgs a;
+    if (e) {
+      // barrier values come from the engine's per-lane counter, shared with every other user of the lane
+      a = moeArgs(e->worldTable(), 1, e->rank(), tokens, hidden, topk, epr, recv_q_off, recv_s_off, y_off, e->nextEpoch(flag_lane),
+                  flag_lane, spin_ns);
+    } else {
+      a = moeArgs(emuWorld2(heaps, flag_off), static_cast<int>(heaps.size()), 0, tokens, hidden, topk, epr, recv_q_off, recv_s_off,
+                  y_off, epoch, flag_lane, spin_ns);
+    }
+    size_t n = e ? 1 : heaps.size();
+    for (size_t r = 0; r < n; ++r) {
+      a.x[r] = x.empty() ? nullptr : reinterpret_cast<const void*>(x.at(r));
+      a.expert_ids[r] = reinterpret_cast<const int*>(ids.at(r));
+      a.dst_rows[r] = reinterpret_cast<const int*>(rows.at(r));
+      a.probs[r] = probs.empty() ? nullptr : reinterpret_cast<const float*>(probs.at(r));
+      a.out[r] = out.empty() ? nullptr : reinterpret_cast<void*>(out.at(r));
+      a.status[r] = reinterpret_cast<uint32_t*>(status.at(r));
+    }
+    int err = kind == "dispatch" ? launchMoeDispatch(a, blocks, reinterpret_cast<cudaStream_t>(stream))
+                                 : launchMoeCombine(a, blocks, reinterpret_cast<cudaStream_t>(stream));
+    check(err, kind.c_str());
+  }, py::arg("kind"), py::arg("engine").none(true), py::arg("heaps"), py::arg("flag_off"), py::arg("tokens"), py::arg("hidden"),
+     py::arg("topk"), py::arg("experts_per_rank"), py::arg("recv_q_off"), py::arg("recv_s_off"), py::arg("y_off"), py::arg("epoch"),
+     py::arg("flag_lane"), py::arg("x"), py::arg("ids"), py::arg("rows"), py::arg("probs"), py::arg("out"), py::arg("status"),
+     py::arg("blocks"), py::arg("spin_ns"), py::arg("stream"));
+  m.def("moe_dequant", [](uint64_t q, uint64_t s, uint64_t out, uint64_t n_rows, int max_rows, int hidden, uint64_t stream) {
+    check(launchMoeDequant(reinterpret_cast<const void*>(q), reinterpret_cast<const float*>(s), reinterpret_cast<void*>(out),
+                           reinterpret_cast<const int*>(n_rows), max_rows, hidden, reinterpret_cast<cudaStream_t>(stream)), "moe_dequant");
+  });
+  m.def("quant_fp8_rows", [](uint64_t x, uint64_t q, uint64_t s, long long rows, int hidden, uint64_t stream) {
+    check(launchQuantFp8Rows(reinterpret_cast<const void*>(x), reinterpret_cast<void*>(q), reinterpret_cast<float*>(s), rows, hidden,
+                             reinterpret_cast<cudaStream_t>(stream)), "quant_fp8_rows");
+  });
+  m.def("quant_fp8_blocks", [](uint64_t w, uint64_t q, uint64_t s, int rows, int cols, uint64_t stream) {
+    check(launchQuantFp8Blocks(reinterpret_cast<const void*>(w), reinterpret_cast<void*>(q), reinterpret_cast<float*>(s), rows, cols,
+                               reinterpret_cast<cudaStream_t>(stream)), "quant_fp8_blocks");
+  });
+  m.def("gemm_grouped", [](uint64_t a, int64_t lda, uint64_t b, int64_t ldb, uint64_t d, int64_t ldd, uint64_t row_off, int groups,
+                           int max_rows, int N, int K, uint32_t flags, int sms, uint64_t status, uint64_t stream) {
+    check(gemmGroupedBf16(reinterpret_cast<const void*>(a), lda, reinterpret_cast<const void*>(b), ldb, reinterpret_cast<void*>(d), ldd,
+                          reinterpret_cast<const int*>(row_off), groups, max_rows, N, K, flags, sms,
+                          reinterpret_cast<uint32_t*>(status), reinterpret_cast<cudaStream_t>(stream)), "gemm_grouped");
+  });
+  m.attr("GEMM_GELU_INPLACE") = static_cast<uint32_t>(GEMM_GELU_INPLACE);
+
   // ---- production: this process is one rank -------------------------------------------------------
   m.def("ag_gemm", [](Engine& e, uint64_t x_off, int M, int N, int K, uint64_t w, int64_t ldw, uint64_t d, int64_t ldd,
                       uint64_t bias, uint64_t ready, uint64_t epoch, int n_copy, int ctas, int flag_lane, uint64_t status,
@@ -38,7 +102,8 @@ void bindFused(py::module_& m) {
     A.w = e.worldTable();
     A.nvirt = 1;
     A.M = M; A.N = N; A.K = K; A.M_local = M / e.world();
-    A.x_off = x_off; A.epoch = epoch; A.n_copy = n_copy; A.flag_lane = flag_lane; A.spin_ns = kDefaultSpinLimit;
+    A.x_off = x_off; A.epoch = epoch; A.bar_epoch = e.nextEpoch(flag_lane); A.n_copy = n_copy; A.flag_lane = flag_lane;
+    A.spin_ns = kDefaultSpinLimit;
     A.flags = bias ? GEMM_BIAS : 0;
     A.r[0].D = reinterpret_cast<void*>(d); A.r[0].ldd = ldd; A.r[0].bias = reinterpret_cast<const void*>(bias);
     A.r[0].ready = reinterpret_cast<uint32_t*>(ready); A.r[0].status = reinterpret_cast<uint32_t*>(status);
@@ -68,7 +133,7 @@ void bindFused(py::module_& m) {
     int n = A.w.world;
     A.nvirt = n;
     A.M = M; A.N = N; A.K = K; A.M_local = M / n;
-    A.x_off = x_off; A.epoch = epoch; A.n_copy = n_copy; A.flag_lane = 0; A.spin_ns = spin_ns ? spin_ns : kDefaultSpinLimit;
+    A.x_off = x_off; A.epoch = epoch; A.bar_epoch = epoch; A.n_copy = n_copy; A.flag_lane = 0; A.spin_ns = spin_ns ? spin_ns : kDefaultSpinLimit;
     std::vector<AgGemmHost> h(n);
     for (int r = 0; r < n; ++r) {
       A.r[r].D = reinterpret_cast<void*>(d.at(r)); A.r[r].ldd = ldd;

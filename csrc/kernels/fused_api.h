@@ -28,7 +28,8 @@ struct AgGemmArgs {
   int M, N, K, M_local;       // M = M_local * world
   uint64_t x_off;             // heap offset of the symmetric gathered-X buffer [M, K] bf16; rows
                               // [rank*M_local, (rank+1)*M_local) hold the rank's own activations
-  uint64_t epoch;             // 1, 2, 3, ... per launch on these buffers
+  uint64_t epoch;             // 1, 2, 3, ... per launch on these buffers (chunk counters)
+  uint64_t bar_epoch;         // strictly increasing per launch on `flag_lane` (peer barriers)
   int n_copy;                 // CTAs that pull peer rows (the rest compute)
   int flag_lane;
   uint64_t spin_ns;

@@ -112,7 +112,7 @@ __device__ void ag_copy_role(const AgGemmArgs& A, const AgGemmRank& R, uint8_t* 
     tc::fence_barrier_init();
   }
   __syncthreads();
-  bool ok = cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.epoch + 1, A.spin_ns, R.status);
+  bool ok = cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 1, A.spin_ns, R.status);
   if (ok && threadIdx.x == 0) {
     const int chunks = A.M_local / BM;
     const long long chunk_bytes = static_cast<long long>(BM) * A.K * 2;
@@ -190,7 +190,7 @@ __device__ void ag_copy_role(const AgGemmArgs& A, const AgGemmRank& R, uint8_t* 
   }
   __syncthreads();
   // peers may still be pulling our rows: nobody leaves (and lets the next kernel overwrite X) before all are done
-  cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.epoch + 2, A.spin_ns, R.status);
+  cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 2, A.spin_ns, R.status);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgGemmArgs A) {

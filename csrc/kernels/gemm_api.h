@@ -15,6 +15,7 @@ enum GemmFlags : uint32_t {
   GEMM_ACCUMULATE = 1u << 3,  // D += A*B^T (D is read)
   GEMM_GELU = 1u << 4,        // D2 = gelu_tanh(D) written next to D (D keeps the pre-activation)
   GEMM_BIAS = 1u << 5,        // D = A*B^T + bias[n] (bf16 bias)
+  GEMM_GELU_INPLACE = 1u << 6,  // D = gelu_tanh(A*B^T (+bias)); no separate pre-activation
 };
 
 // D[M,N] (ldd) = A * B^T.  K-major operands: A is [M,K] with row stride lda, B is [N,K] with row
@@ -24,6 +25,13 @@ enum GemmFlags : uint32_t {
 // null) receives ST_TIMEOUT if a pipeline wait runs out.
 int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
              uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status, cudaStream_t stream);
+
+// Grouped GEMM for expert layers: group g multiplies rows [row_off[g], row_off[g+1]) of A [*, K] with
+// the g-th [N, K] block of B (stacked [groups*N, K]) into the same rows of D [*, N].  `row_off`
+// (groups+1 int32) lives on the device, so no host synchronisation is needed to know the sizes.
+// flags: GEMM_GELU_INPLACE.
+int gemmGroupedBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, const int* row_off,
+                    int groups, int max_rows, int N, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream);
 
 const char* gemmLastError();
 

@@ -60,6 +60,10 @@ struct StoreEpi {
     }
     __nv_bfloat16* d = static_cast<__nv_bfloat16*>(D) + static_cast<long long>(row) * ldd + col;
     if (full) {
+      if (flags & GEMM_GELU_INPLACE) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+      }
       if (flags & GEMM_ACCUMULATE) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {

@@ -1,0 +1,368 @@
+// Expert-parallel MoE data movement fused with its arithmetic, plus the fp8 block quantisers.
+//
+//   dispatch   one pass per token: bf16 row -> e4m3 with one fp32 scale per 128 values (amax / 448),
+//              staged in shared memory, then stored straight into the receive buffers of the ranks
+//              that own the token's top-k experts (NVLink stores, 16 bytes per thread per target)
+//   dequant    fp8 rows + scales -> bf16 rows for the grouped expert GEMM
+//   combine    one pass per token: pull the top-k expert outputs from their ranks (up to 32
+//              independent 16-byte NVLink loads in flight per thread), weight by the gate
+//              probability, accumulate in fp32, write bf16
+// Both communication kernels are persistent (one CTA per SM at most), open and close with a bounded
+// peer barrier on per-CTA flags in the symmetric heap, and can emulate all ranks in one launch.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "gemm_api.h"
+#include "gemm_epilogue.cuh"
+#include "gemm_pipeline.cuh"
+#include "moe_api.h"
+#include "prims.cuh"
+#include "tensormap.h"
+
+namespace pccl {
+
+namespace {
+
+using namespace dev;
+
+__device__ __forceinline__ uint64_t* moe_flag(const World& W, int owner, int lane, int block, int src) {
+  return reinterpret_cast<uint64_t*>(W.heap[owner] + W.flag_off) +
+         ((static_cast<uint64_t>(lane) * kMaxBlocksPerColl + block) * kMaxRanks + src);
+}
+
+__device__ __forceinline__ bool moe_barrier(const MoeArgs& A, int me, uint64_t value, uint32_t* s_fail) {
+  __syncthreads();
+  if (threadIdx.x < static_cast<uint32_t>(A.w.world)) {
+    const int p = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(moe_flag(A.w, p, A.flag_lane, blockIdx.x, me), value);
+    if (!wait_ge(moe_flag(A.w, me, A.flag_lane, blockIdx.x, p), value, A.spin_ns, nullptr)) {
+      *s_fail = 1;
+      report(A.status[A.nvirt > 1 ? me : 0], ST_TIMEOUT, blockIdx.x, static_cast<uint32_t>(p), static_cast<uint32_t>(value & 3));
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+// Quantises 8 bf16 values with a given inverse scale into 8 e4m3 bytes.
+__device__ __forceinline__ uint2 quant8(const float* f, float inv) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h] * inv, f[4 * h + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+    uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * h + 2] * inv, f[4 * h + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+    w[h] = (lo & 0xffffu) | (hi << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+// Quantise one row held in global memory into shared memory (q: hidden bytes, s: hidden/128 floats).
+// 16 consecutive lanes own one 128-value block, so the block amax is a half-warp shuffle reduction.
+__device__ __forceinline__ void quant_row_to_smem(const __nv_bfloat16* x, int hidden, uint8_t* q, float* s) {
+  const int nvec = hidden >> 3;
+  for (int v = threadIdx.x; v < ((nvec + 31) & ~31); v += blockDim.x) {     // warp-uniform trip count for the shuffles
+    float f[8];
+    float amax = 0.f;
+    if (v < nvec) {
+      unpack<DT_BF16>(ld16(x + v * 8), f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+    if (v < nvec) {
+      *reinterpret_cast<uint2*>(q + v * 8) = quant8(f, 1.0f / scale);
+      if ((v & 15) == 0) s[v >> 4] = scale;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_dispatch_kernel(const __grid_constant__ MoeArgs A) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = A.nvirt > 1 ? static_cast<int>(blockIdx.y) : A.rank;
+  const int slot = A.nvirt > 1 ? me : 0;
+  const int H = A.hidden, G = H >> 7;
+  uint8_t* q = dsm;
+  float* s = reinterpret_cast<float*>(dsm + H);
+  if (!moe_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(A.x[slot]);
+  const int qvec = H >> 4, svec = (G + 3) >> 2;       // 16-byte vectors of payload / of scales
+  for (int t = blockIdx.x; t < A.tokens; t += gridDim.x) {
+    __syncthreads();                                    // the previous token's stores have read the staging row
+    quant_row_to_smem(x + static_cast<long long>(t) * H, H, q, s);
+    __syncthreads();
+    for (int k = 0; k < A.topk; ++k) {
+      const int e = A.expert_ids[slot][t * A.topk + k];
+      const long long row = A.dst_rows[slot][t * A.topk + k];
+      if (e < 0 || row < 0) continue;                   // dropped assignment (receive buffer full)
+      char* base = A.w.heap[e / A.experts_per_rank];
+      char* dq = base + A.recv_q_off + row * H;
+      char* ds = base + A.recv_s_off + row * G * 4;
+      for (int v = threadIdx.x; v < qvec; v += blockDim.x) st16(dq + v * 16, *reinterpret_cast<const Vec16*>(q + v * 16));
+      if (threadIdx.x < svec) {
+        if ((G & 3) == 0) st16(ds + threadIdx.x * 16, *reinterpret_cast<const Vec16*>(reinterpret_cast<uint8_t*>(s) + threadIdx.x * 16));
+        else for (int i = threadIdx.x * 4; i < min(G, threadIdx.x * 4 + 4); ++i) reinterpret_cast<float*>(ds)[i] = s[i];
+      }
+    }
+  }
+  moe_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const __grid_constant__ MoeArgs A) {
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = A.nvirt > 1 ? static_cast<int>(blockIdx.y) : A.rank;
+  const int slot = A.nvirt > 1 ? me : 0;
+  const int H = A.hidden, nvec = H >> 3;
+  if (!moe_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(A.out[slot]);
+  for (int t = blockIdx.x; t < A.tokens; t += gridDim.x) {
+    const char* src[8];
+    float p[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      src[k] = nullptr;
+      p[k] = 0.f;
+      if (k < A.topk) {
+        const int e = A.expert_ids[slot][t * A.topk + k];
+        const long long row = A.dst_rows[slot][t * A.topk + k];
+        if (e >= 0 && row >= 0) {
+          src[k] = A.w.heap[e / A.experts_per_rank] + A.y_off + row * H * 2;
+          p[k] = A.probs[slot][t * A.topk + k];
+        }
+      }
+    }
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 2 * blockDim.x) {
+      const int v1 = v0 + blockDim.x;
+      Vec16 a[8], b[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {        // all loads first: up to 16 NVLink loads in flight per thread
+        if (src[k]) {
+          a[k] = ld16(src[k] + v0 * 16);
+          if (v1 < nvec) b[k] = ld16(src[k] + v1 * 16);
+        }
+      }
+      float acc0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (src[k]) {
+          float f[8];
+          unpack<DT_BF16>(a[k], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc0[j] += p[k] * f[j];
+          if (v1 < nvec) {
+            unpack<DT_BF16>(b[k], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc1[j] += p[k] * f[j];
+          }
+        }
+      }
+      st16(out + static_cast<long long>(t) * H + v0 * 8, pack<DT_BF16>(acc0));
+      if (v1 < nvec) st16(out + static_cast<long long>(t) * H + v1 * 8, pack<DT_BF16>(acc1));
+    }
+  }
+  moe_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+__global__ void __launch_bounds__(256) moe_dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
+                                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ n_rows,
+                                                          int max_rows, int hidden) {
+  const int rows = min(*n_rows, max_rows);
+  const int nvec = hidden >> 4, G = hidden >> 7;      // 16 fp8 values per 16-byte vector
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint8_t* qr = q + r * hidden;
+    const float* sr = scales + r * G;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float f[16];
+      unpack<DT_FP8_E4M3>(ld16(qr + v * 16), f);
+      const float sc = sr[v >> 3];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) f[k] *= sc;
+      st16(out + r * hidden + v * 16, pack<DT_BF16>(f));
+      st16(out + r * hidden + v * 16 + 8, pack<DT_BF16>(f + 8));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                                         float* __restrict__ scales, long long rows, int hidden) {
+  extern __shared__ __align__(16) uint8_t qsm[];
+  uint8_t* sq = qsm;
+  float* ss = reinterpret_cast<float*>(qsm + hidden);
+  const int G = hidden >> 7;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    __syncthreads();
+    quant_row_to_smem(x + r * hidden, hidden, sq, ss);
+    __syncthreads();
+    for (int v = threadIdx.x; v < (hidden >> 4); v += blockDim.x) st16(q + r * hidden + v * 16, *reinterpret_cast<const Vec16*>(sq + v * 16));
+    for (int g = threadIdx.x; g < G; g += blockDim.x) scales[r * G + g] = ss[g];
+  }
+}
+
+// one CTA per 128 x 128 block of a weight matrix
+__global__ void __launch_bounds__(256) quant_blocks_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ q,
+                                                           float* __restrict__ scales, int rows, int cols) {
+  __shared__ float red[8];
+  const int bc = blockIdx.x, br = blockIdx.y;
+  const __nv_bfloat16* base = w + static_cast<long long>(br) * 128 * cols + bc * 128;
+  float f[8][8];
+  float amax = 0.f;
+  // 128 x 128 values = 2048 vectors of 8; 256 threads take 8 each: thread -> (row group, vector in row)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = threadIdx.x + i * 256, r = idx >> 4, v = idx & 15;
+    unpack<DT_BF16>(ld16(base + static_cast<long long>(r) * cols + v * 8), f[i]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[i][k]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+  if (threadIdx.x == 0) scales[br * (cols >> 7) + bc] = scale;
+  const float inv = 1.0f / scale;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = threadIdx.x + i * 256, r = idx >> 4, v = idx & 15;
+    *reinterpret_cast<uint2*>(q + (static_cast<long long>(br) * 128 + r) * cols + bc * 128 + v * 8) = quant8(f[i], inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// grouped GEMM on the tcgen05 pipeline
+// ---------------------------------------------------------------------------------------------
+using namespace gemm;
+
+struct GroupedSched {
+  const int* row_off;    // groups + 1
+  int groups, tiles_n, first, stride;
+  // Tile `idx` of the concatenated per-group tile lists -> (group, m-tile inside group, n-tile).
+  __device__ __forceinline__ bool get(int it, TileCoord* t) const {
+    long long idx = first + static_cast<long long>(it) * stride;
+    for (int g = 0; g < groups; ++g) {
+      const int rows = row_off[g + 1] - row_off[g];
+      const long long tiles = static_cast<long long>((rows + BM - 1) / BM) * tiles_n;
+      if (idx < tiles) {
+        const int tm = (rows + BM - 1) / BM;
+        t->m = static_cast<int>(idx % tm);
+        t->n = static_cast<int>(idx / tm);
+        t->extra = g;
+        return true;
+      }
+      idx -= tiles;
+    }
+    return false;
+  }
+};
+
+struct GroupedEpi {
+  __nv_bfloat16* D;
+  long long ldd;
+  const int* row_off;
+  int N;
+  uint32_t flags;
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return row_off[t.extra] + t.m * BM; }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.extra * N + t.n * BN; }
+  __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
+  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
+    const int row = row_off[t.extra] + t.m * BM + row_in_tile;
+    const int col = t.n * BN + col_in_tile;
+    if (row >= row_off[t.extra + 1] || col >= N) return;     // rows past the group's end belong to the next group
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    if (flags & GEMM_GELU_INPLACE) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+    }
+    __nv_bfloat16* d = D + static_cast<long long>(row) * ldd + col;
+    if (col + 32 <= N) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) st16(d + i, pack<DT_BF16>(v + i));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col + i < N) d[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GroupedEpi epi, int groups, int K,
+                    uint32_t* status) {
+  GroupedSched sched{epi.row_off, groups, (epi.N + BN - 1) / BN, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
+  NoGate gate;
+  run<false, false>(&tmA, &tmB, K, sched, gate, epi, status);
+}
+
+template <typename K>
+int coop(K kernel, const MoeArgs& a, int blocks, size_t smem, cudaStream_t stream) {
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocksPerColl) blocks = kMaxBlocksPerColl;
+  if (a.topk > 8 || a.hidden % 128 || a.flag_lane < 0 || a.flag_lane >= 8) return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid(blocks, a.nvirt > 1 ? a.nvirt : 1), block(256);
+  void* args[] = {const_cast<MoeArgs*>(&a)};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), grid, block, args, smem, stream));
+}
+
+}  // namespace
+
+int launchMoeDispatch(const MoeArgs& a, int blocks, cudaStream_t stream) {
+  return coop(moe_dispatch_kernel, a, blocks, static_cast<size_t>(a.hidden) + (a.hidden >> 7) * 4 + 16, stream);
+}
+
+int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream) { return coop(moe_combine_kernel, a, blocks, 0, stream); }
+
+int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, cudaStream_t stream) {
+  if (hidden % 128) return static_cast<int>(cudaErrorInvalidValue);
+  moe_dequant_kernel<<<148 * 8, 256, 0, stream>>>(static_cast<const uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(out), n_rows, max_rows, hidden);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launchQuantFp8Rows(const void* x, void* q, float* scales, long long rows, int hidden, cudaStream_t stream) {
+  if (hidden % 128 || rows <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  long long blocks = rows < 148 * 8 ? rows : 148 * 8;
+  quant_rows_kernel<<<static_cast<int>(blocks), 256, static_cast<size_t>(hidden) + (hidden >> 7) * 4 + 16, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scales, rows, hidden);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launchQuantFp8Blocks(const void* w, void* q, float* scales, int rows, int cols, cudaStream_t stream) {
+  if (rows % 128 || cols % 128 || rows <= 0 || cols <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid(cols / 128, rows / 128);
+  quant_blocks_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), scales, rows, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gemmGroupedBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, const int* row_off,
+                    int groups, int max_rows, int N, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream) {
+  if (groups <= 0 || max_rows <= 0) return 0;
+  if ((lda | ldb | ldd) % 8) return static_cast<int>(cudaErrorInvalidValue);
+  CUtensorMap ta, tb;
+  std::string err;
+  if (!makeTensorMap2D(&ta, A, TM_BF16, K, max_rows, lda, BK, BM, &err)) return static_cast<int>(cudaErrorInvalidValue);
+  if (!makeTensorMap2D(&tb, B, TM_BF16, K, static_cast<uint64_t>(groups) * N, ldb, BK, BN, &err)) return static_cast<int>(cudaErrorInvalidValue);
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    set = true;
+  }
+  int n_sm = deviceSmCount();
+  if (sms > 0 && sms < n_sm) n_sm = sms;
+  GroupedEpi epi{static_cast<__nv_bfloat16*>(D), ldd, row_off, N, flags};
+  gemm_grouped_kernel<<<n_sm, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, epi, groups, K, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace pccl

@@ -1,0 +1,46 @@
+// Host entry points of the expert-parallel MoE kernels (moe.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "api.h"
+
+namespace pccl {
+
+struct MoeArgs {
+  World w;
+  int nvirt;              // 1, or the emulated world size (single-GPU tests)
+  int rank;               // ignored when nvirt > 1
+  int tokens;             // tokens of this rank
+  int hidden;             // multiple of 128
+  int topk;               // <= 8
+  int experts_per_rank;
+  uint64_t recv_q_off;    // heap offset: fp8 rows received [cap, hidden]
+  uint64_t recv_s_off;    // heap offset: fp32 scales received [cap, hidden/128]
+  uint64_t y_off;         // heap offset: expert outputs [cap, hidden] bf16 (read by the combine of every rank)
+  uint64_t epoch;
+  int flag_lane;
+  int pad;
+  uint64_t spin_ns;
+  // per (virtual) rank local tensors
+  const void* x[kMaxRanks];          // [tokens, hidden] bf16
+  const int* expert_ids[kMaxRanks];  // [tokens, topk] global expert ids
+  const int* dst_rows[kMaxRanks];    // [tokens, topk] row inside the destination rank's receive buffer
+  const float* probs[kMaxRanks];     // [tokens, topk] gate probabilities (combine)
+  void* out[kMaxRanks];              // [tokens, hidden] bf16 (combine)
+  uint32_t* status[kMaxRanks];
+};
+
+// fp8 (e4m3, one fp32 scale per 128 values) quantisation fused with the push to the experts' ranks.
+int launchMoeDispatch(const MoeArgs& a, int blocks, cudaStream_t stream);
+// out[t] = sum_k probs[t,k] * y[rank of expert (t,k)][dst_rows[t,k]]: pulls the rows over NVLink.
+int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream);
+// bf16 rows from fp8 rows + scales, for rows [0, *n_rows) (device count).
+int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, cudaStream_t stream);
+// Stand-alone block quantiser (1 x 128 blocks, e4m3 + fp32 scales).
+int launchQuantFp8Rows(const void* x, void* q, float* scales, long long rows, int hidden, cudaStream_t stream);
+// 128 x 128 block quantiser for weights [rows, cols] (both multiples of 128): e4m3 + fp32 scale per block.
+int launchQuantFp8Blocks(const void* w, void* q, float* scales, int rows, int cols, cudaStream_t stream);
+
+}  // namespace pccl

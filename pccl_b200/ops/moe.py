@@ -1,0 +1,138 @@
+"""Expert-parallel MoE: routing plan, fp8 dispatch, grouped expert FFN, weighted combine
+(csrc/kernels/moe.cu).  Everything stays on the device: token counts per expert are exchanged with
+this library's all-gather and turned into receive offsets with a few tensor ops, and the grouped
+GEMM reads the per-expert row ranges from device memory, so no step needs the host to know sizes.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .._native import C
+from ..engine import Engine
+from . import collectives as coll
+from .gemm import count_launch, status_words
+
+
+def quant_fp8_rows(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [rows, hidden] -> (e4m3 bytes [rows, hidden], fp32 scales [rows, hidden/128]); 1 x 128 blocks."""
+    rows, hidden = x.shape
+    q = torch.empty((rows, hidden), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, hidden // 128), dtype=torch.float32, device=x.device)
+    C.quant_fp8_rows(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, hidden, torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return q, s
+
+
+def quant_fp8_blocks(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [rows, cols] weights -> (e4m3 bytes, fp32 scales [rows/128, cols/128]); 128 x 128 blocks."""
+    rows, cols = w.shape
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=w.device)
+    s = torch.empty((rows // 128, cols // 128), dtype=torch.float32, device=w.device)
+    C.quant_fp8_blocks(w.data_ptr(), q.data_ptr(), s.data_ptr(), rows, cols, torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return q, s
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, row_off: torch.Tensor, n: int, out: Optional[torch.Tensor] = None,
+                 gelu: bool = False) -> torch.Tensor:
+    """Rows [row_off[g], row_off[g+1]) of ``a`` [*, K] times ``b[g*n:(g+1)*n]`` ([groups*n, K]) ^T -> same rows of out [*, n]."""
+    groups = row_off.numel() - 1
+    if out is None:
+        out = torch.empty((a.shape[0], n), dtype=torch.bfloat16, device=a.device)
+    C.gemm_grouped(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), row_off.data_ptr(), groups,
+                   a.shape[0], n, a.shape[1], C.GEMM_GELU_INPLACE if gelu else 0, 0, status_words().data_ptr(),
+                   torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return out
+
+
+class MoEExchange:
+    """Buffers and kernels of one expert-parallel MoE layer shape."""
+
+    def __init__(self, eng: Engine, tokens: int, hidden: int, n_experts: int, topk: int, capacity_factor: float = 2.0,
+                 blocks: Optional[int] = None, flag_lane: int = 5):
+        if n_experts % eng.world or hidden % 128 or topk > 8:
+            raise ValueError("MoEExchange: experts must divide over ranks, hidden % 128 == 0, top-k <= 8")
+        self.eng, self.T, self.H, self.E, self.K = eng, tokens, hidden, n_experts, topk
+        self.epr = n_experts // eng.world
+        self.cap = int(capacity_factor * tokens * topk) // 128 * 128 + 128
+        self.recv_q = eng.symmetric_tensor((self.cap, hidden), torch.uint8)
+        self.recv_s = eng.symmetric_tensor((self.cap, hidden // 128), torch.float32)
+        self.y = eng.symmetric_tensor((self.cap, hidden), torch.bfloat16)
+        self.counts_all = eng.symmetric_tensor((eng.world, n_experts), torch.int32)
+        self.x_bf16 = torch.empty((self.cap, hidden), dtype=torch.bfloat16, device="cuda")
+        self.epoch = 0
+        self.blocks = blocks or min(C.sm_count(), C.MAX_BLOCKS_PER_COLL)
+        self.flag_lane = flag_lane
+
+    # ---- routing -----------------------------------------------------------------------------
+    @staticmethod
+    def route(gate_logits: torch.Tensor, topk: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        probs = torch.softmax(gate_logits.float(), dim=-1)
+        p, ids = probs.topk(topk, dim=-1)
+        return ids.to(torch.int32), p.contiguous()
+
+    def plan(self, ids: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """Where every (token, k) assignment lands: its row in the destination rank's receive buffer."""
+        eng, E, epr = self.eng, self.E, self.epr
+        flat = ids.reshape(-1).long()
+        counts = torch.bincount(flat, minlength=E).to(torch.int32)
+        if eng.world > 1:
+            coll.all_gather(eng, counts, self.counts_all.view(-1), lane=self.flag_lane)
+            counts_all = self.counts_all
+        else:
+            counts_all = counts.view(1, E)
+        ca = counts_all.long()
+        per_expert = ca.sum(0)                                     # rows each expert receives
+        grp = per_expert.view(eng.world, epr)
+        expert_base = (grp.cumsum(1) - grp).reshape(-1)            # start of the expert's segment on its rank
+        src_prefix = (ca.cumsum(0) - ca)[eng.rank]                 # rows of lower ranks inside that segment
+        order = torch.argsort(flat, stable=True)
+        starts = counts.long().cumsum(0) - counts.long()
+        pos_sorted = torch.arange(flat.numel(), device=flat.device) - starts[flat[order]]
+        pos = torch.empty_like(pos_sorted)
+        pos[order] = pos_sorted
+        rows = expert_base[flat] + src_prefix[flat] + pos
+        rows = torch.where(rows < self.cap, rows, torch.full_like(rows, -1)).to(torch.int32).view_as(ids)
+        mine = grp[eng.rank]
+        row_off = torch.zeros(epr + 1, dtype=torch.int32, device=ids.device)
+        row_off[1:] = mine.cumsum(0).clamp(max=self.cap).to(torch.int32)
+        return {"rows": rows.contiguous(), "row_off": row_off, "n_rows": row_off[-1:].contiguous()}
+
+    # ---- kernels ----------------------------------------------------------------------------
+    def _exchange(self, kind: str, x, ids, rows, probs, out) -> None:
+        self.epoch += 1
+        st = status_words()
+        C.moe_exchange(kind, self.eng.raw, [], 0, self.T, self.H, self.K, self.epr, self.eng.heap_offset(self.recv_q),
+                       self.eng.heap_offset(self.recv_s), self.eng.heap_offset(self.y), self.epoch, self.flag_lane,
+                       [x.data_ptr()] if x is not None else [], [ids.data_ptr()], [rows.data_ptr()],
+                       [probs.data_ptr()] if probs is not None else [], [out.data_ptr()] if out is not None else [],
+                       [st.data_ptr()], self.blocks, 0, torch.cuda.current_stream().cuda_stream)
+        count_launch()
+
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor, plan: Dict[str, torch.Tensor]) -> None:
+        self._exchange("dispatch", x, ids, plan["rows"], None, None)
+
+    def experts(self, w1: torch.Tensor, w2: torch.Tensor, plan: Dict[str, torch.Tensor]) -> None:
+        """w1: [experts_per_rank * d_ff, hidden], w2: [experts_per_rank * hidden, d_ff]; result in self.y."""
+        C.moe_dequant(self.recv_q.data_ptr(), self.recv_s.data_ptr(), self.x_bf16.data_ptr(), plan["n_rows"].data_ptr(), self.cap,
+                      self.H, torch.cuda.current_stream().cuda_stream)
+        count_launch()
+        d_ff = w1.shape[0] // self.epr
+        h = grouped_gemm(self.x_bf16, w1, plan["row_off"], d_ff, gelu=True)
+        grouped_gemm(h, w2, plan["row_off"], self.H, out=self.y)
+
+    def combine(self, ids: torch.Tensor, probs: torch.Tensor, plan: Dict[str, torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((self.T, self.H), dtype=torch.bfloat16, device="cuda")
+        self._exchange("combine", None, ids, plan["rows"], probs, out)
+        return out
+
+    def forward(self, x: torch.Tensor, gate_logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+        ids, probs = self.route(gate_logits, self.K)
+        plan = self.plan(ids)
+        self.dispatch(x, ids, plan)
+        self.experts(w1, w2, plan)
+        return self.combine(ids, probs, plan)

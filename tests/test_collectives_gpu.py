@@ -226,3 +226,125 @@ def test_gemm_rs_emulated(native, world):
             assert (outs[r].float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
         for y in ys:
             y.mul_(0.5)
+
+
+# ---------------------------------------------------------------------------------------------
+# MoE kernels
+# ---------------------------------------------------------------------------------------------
+def test_fp8_quantisers_match_reference(native):
+    from pccl_b200.ops.moe import quant_fp8_blocks, quant_fp8_rows
+    torch.manual_seed(3)
+    x = (torch.randn(300, 1024, device="cuda") * 3).bfloat16()
+    q, s = quant_fp8_rows(x)
+    xf = x.float().view(300, 8, 128)
+    ref_s = xf.abs().amax(-1) / 448.0
+    assert torch.allclose(s, ref_s, rtol=1e-6, atol=0)
+    ref_q = (xf / ref_s[..., None]).to(torch.float8_e4m3fn).view(300, 1024)
+    assert torch.equal(q.view(torch.float8_e4m3fn).float(), ref_q.float())
+    w = (torch.randn(256, 384, device="cuda")).bfloat16()
+    qw, sw = quant_fp8_blocks(w)
+    wf = w.float().view(2, 128, 3, 128).permute(0, 2, 1, 3)
+    ref_sw = wf.abs().amax((-1, -2)) / 448.0
+    assert torch.allclose(sw, ref_sw, rtol=1e-6, atol=0)
+    deq = qw.view(torch.float8_e4m3fn).float().view(2, 128, 3, 128) * sw[:, None, :, None]
+    assert (deq.view(256, 384) - w.float()).abs().max().item() <= 0.07 * w.float().abs().max().item()
+
+
+def test_grouped_gemm_matches_per_group_reference(native):
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.moe import grouped_gemm
+    torch.manual_seed(4)
+    K, N = 512, 384
+    sizes = [130, 0, 257, 5, 128, 64]
+    off = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    total = int(off[-1])
+    a = (torch.randn(total + 200, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(len(sizes) * N, K, device="cuda") * 0.1).bfloat16()
+    out = torch.full((total + 200, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    grouped_gemm(a, b, off, N, out=out)
+    check_status("grouped gemm")
+    for g, n in enumerate(sizes):
+        lo = int(off[g])
+        ref = a[lo:lo + n].float() @ b[g * N:(g + 1) * N].float().t()
+        assert (out[lo:lo + n].float() - ref).abs().max().item() < 0.05 if n else True
+    assert torch.all(out[total:] == 7.0)        # rows past the last group are untouched
+
+
+def test_moe_dispatch_combine_emulated(native):
+    """Two emulated ranks: fp8 dispatch lands in the right rows with the right scales; combine pulls
+    rows back from both ranks and weights them."""
+    world, T, H, Kt, epr = 2, 64, 256, 2, 2
+    cap = 512
+    q_off, s_off, y_off = DATA_OFF, DATA_OFF + cap * H, DATA_OFF + cap * H + cap * (H // 128) * 4
+    heaps = [torch.zeros(y_off + cap * H * 2, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    g = torch.Generator(device="cuda").manual_seed(5)
+    xs = [(torch.randn(T, H, generator=g, device="cuda") * 2).bfloat16() for _ in range(world)]
+    ids = [torch.randint(0, world * epr, (T, Kt), generator=g, device="cuda", dtype=torch.int32) for _ in range(world)]
+    # every (rank, token, k) gets a unique row on its destination: rank r uses rows r*T*Kt + t*Kt + k
+    rows = [(torch.arange(T * Kt, device="cuda", dtype=torch.int32) + r * T * Kt).view(T, Kt).contiguous() for r in range(world)]
+    probs = [torch.rand(T, Kt, generator=g, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    native.moe_exchange("dispatch", None, [h.data_ptr() for h in heaps], FLAG_OFF, T, H, Kt, epr, q_off, s_off, y_off, 1, 0,
+                        [x.data_ptr() for x in xs], [i.data_ptr() for i in ids], [r.data_ptr() for r in rows], [], [],
+                        [s.data_ptr() for s in st], 8, 0, stream)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st)
+    from pccl_b200.ops.moe import quant_fp8_rows
+    for r in range(world):
+        q_ref, s_ref = quant_fp8_rows(xs[r])
+        for t in range(0, T, 7):
+            for k in range(Kt):
+                d, row = int(ids[r][t, k]) // epr, int(rows[r][t, k])
+                got_q = heaps[d][q_off + row * H: q_off + (row + 1) * H]
+                got_s = heaps[d][s_off + row * (H // 128) * 4: s_off + (row + 1) * (H // 128) * 4].view(torch.float32)
+                assert torch.equal(got_q, q_ref[t]) and torch.equal(got_s, s_ref[t])
+    # expert outputs: fill y on both ranks with a known function of (rank, row)
+    ys = []
+    for d in range(world):
+        y = heaps[d][y_off:y_off + cap * H * 2].view(torch.bfloat16).view(cap, H)
+        y.copy_((torch.randn(cap, H, generator=g, device="cuda")).bfloat16())
+        ys.append(y)
+    native.moe_exchange("combine", None, [h.data_ptr() for h in heaps], FLAG_OFF, T, H, Kt, epr, q_off, s_off, y_off, 2, 0,
+                        [], [i.data_ptr() for i in ids], [r.data_ptr() for r in rows], [p.data_ptr() for p in probs],
+                        [o.data_ptr() for o in outs], [s.data_ptr() for s in st], 8, 0, stream)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st)
+    for r in range(world):
+        ref = torch.zeros(T, H, device="cuda")
+        for k in range(Kt):
+            d = (ids[r][:, k] // epr).long()
+            picked = torch.stack([ys[int(d[t])][int(rows[r][t, k])] for t in range(T)]).float()
+            ref += probs[r][:, k, None] * picked
+        assert (outs[r].float() - ref).abs().max().item() < 0.05
+
+
+def test_moe_layer_world_of_one_matches_dense_reference(native):
+    from pccl_b200.engine import Engine
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.moe import MoEExchange
+    torch.manual_seed(6)
+    T, H, F, E, Kt = 256, 512, 256, 8, 2
+    eng = Engine(0, 1)
+    eng.initEngine("cuda", heap_bytes=512 << 20)
+    moe = MoEExchange(eng, T, H, E, Kt)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    logits = torch.randn(T, E, device="cuda")
+    w1 = (torch.randn(E * F, H, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(E * H, F, device="cuda") * 0.05).bfloat16()
+    out = moe.forward(x, logits, w1, w2)
+    check_status("moe")
+    ids, probs = MoEExchange.route(logits, Kt)
+    ref = torch.zeros(T, H, device="cuda")
+    xq = x.float().view(T, H // 128, 128)
+    sc = xq.abs().amax(-1, keepdim=True) / 448.0
+    xd = ((xq / sc).to(torch.float8_e4m3fn).float() * sc).view(T, H).bfloat16().float()   # what the experts see
+    for e in range(E):
+        h = torch.nn.functional.gelu(xd @ w1[e * F:(e + 1) * F].float().t(), approximate="tanh").bfloat16().float()
+        y = (h @ w2[e * H:(e + 1) * H].float().t()).bfloat16().float()
+        for k in range(Kt):
+            m = (ids[:, k] == e)
+            ref[m] += probs[m, k, None] * y[m]
+    assert (out.float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+    del moe, eng
