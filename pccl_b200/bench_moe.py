@@ -1,0 +1,164 @@
+"""Expert-parallel MoE layer micro-benchmark: 4096 tokens per rank, hidden 7168, 256 experts, top-8
+routing from softmax over random gate logits; fp8 dispatch, bf16 expert FFN 7168 -> 2048 -> 7168,
+gate-weighted combine.  Phases are device-timed (CUDA events, max over ranks, L2 flushed between
+iterations) and compared with NCCL all_to_all + per-expert torch.matmul.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m pccl_b200.bench_moe --out moe.json
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .engine import Engine
+from .ops import check_status
+from .ops.moe import MoEExchange
+from .utils import L2Flusher
+
+
+def _time(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(iters):
+        flush()
+        if dist.is_initialized():
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        tot += a.elapsed_time(b)
+    t = torch.tensor([tot / iters], device="cuda", dtype=torch.float64)
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item()) * 1e3
+
+
+def run(eng: Engine, tokens: int, hidden: int, d_ff: int, n_experts: int, topk: int, iters: int = 10, warmup: int = 3,
+        peak_tflops: float = 1701.7, link_gbs: float = 770.0):
+    world, rank = eng.world, eng.rank
+    epr = n_experts // world
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    x = torch.randn(tokens, hidden, generator=g, device="cuda").bfloat16()
+    logits = torch.randn(tokens, n_experts, generator=g, device="cuda")
+    w1 = (torch.randn(epr * d_ff, hidden, generator=g, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(epr * hidden, d_ff, generator=g, device="cuda") * 0.02).bfloat16()
+    moe = MoEExchange(eng, tokens, hidden, n_experts, topk)
+    flush = L2Flusher()
+    ids, probs = MoEExchange.route(logits, topk)
+    plan = moe.plan(ids)
+    out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    t_route = _time(lambda: moe.plan(MoEExchange.route(logits, topk)[0]), iters, warmup, flush)
+    t_disp = _time(lambda: moe.dispatch(x, ids, plan), iters, warmup, flush)
+    t_ffn = _time(lambda: moe.experts(w1, w2, plan), iters, warmup, flush)
+    t_comb = _time(lambda: moe.combine(ids, probs, plan, out), iters, warmup, flush)
+    t_total = _time(lambda: moe.forward(x, logits, w1, w2), iters, warmup, flush)
+    check_status("moe")
+
+    # ---- baseline: NCCL all_to_all (bf16 rows) + per-expert torch.matmul + all_to_all back ----------------
+    n_rows = int(plan["n_rows"])
+    send_counts = torch.bincount((ids.reshape(-1) // epr).long(), minlength=world).tolist()
+    order = torch.argsort(ids.reshape(-1).long(), stable=True)
+    send = x[(order // topk)].contiguous()
+    recv_counts_t = torch.tensor(send_counts, device="cuda")
+    all_counts = [torch.zeros_like(recv_counts_t) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(all_counts, recv_counts_t)
+        recv_counts = [int(c[rank]) for c in all_counts]
+    else:
+        recv_counts = send_counts
+    recv = torch.empty(sum(recv_counts), hidden, dtype=torch.bfloat16, device="cuda")
+    back = torch.empty_like(send)
+    off = plan["row_off"].tolist()
+
+    def nccl_a2a():
+        if world > 1:
+            dist.all_to_all_single(recv, send, recv_counts, send_counts)
+        else:
+            recv.copy_(send)
+
+    y_base = torch.empty_like(recv)
+
+    def base_ffn():
+        for e in range(epr):
+            lo, hi = off[e], off[e + 1]
+            if hi > lo:
+                h = torch.nn.functional.gelu(recv[lo:hi] @ w1[e * d_ff:(e + 1) * d_ff].t(), approximate="tanh")
+                torch.matmul(h, w2[e * hidden:(e + 1) * hidden].t(), out=y_base[lo:hi])
+
+    def nccl_back():
+        if world > 1:
+            dist.all_to_all_single(back, y_base, send_counts, recv_counts)
+        else:
+            back.copy_(y_base)
+
+    b_disp = _time(nccl_a2a, iters, warmup, flush)
+    b_ffn = _time(base_ffn, iters, warmup, flush)
+    b_comb = _time(nccl_back, iters, warmup, flush)
+
+    remote = (world - 1) / world
+    disp_bytes = tokens * topk * (hidden + hidden // 128 * 4) * remote
+    comb_bytes = tokens * topk * hidden * 2 * remote
+    ffn_flops = 2.0 * n_rows * hidden * d_ff * 2
+    roof = {"dispatch_us": disp_bytes / (link_gbs * 1e9) * 1e6, "combine_us": comb_bytes / (link_gbs * 1e9) * 1e6,
+            "ffn_us": ffn_flops / (peak_tflops * 1e12) * 1e6}
+    return {"n_gpus": world, "tokens_per_rank": tokens, "hidden": hidden, "d_ff": d_ff, "experts": n_experts, "topk": topk,
+            "rows_received": n_rows, "ours_us": {"route_plan": t_route, "dispatch_fp8": t_disp, "expert_ffn": t_ffn, "combine": t_comb,
+                                                 "layer_total": t_total},
+            "baseline_us": {"nccl_all_to_all_bf16": b_disp, "matmul_loop_ffn": b_ffn, "nccl_all_to_all_back": b_comb,
+                            "sum": b_disp + b_ffn + b_comb},
+            "roofline_us": roof,
+            "fraction_of_roofline": {"dispatch": roof["dispatch_us"] / t_disp if world > 1 else None,
+                                     "combine": roof["combine_us"] / t_comb if world > 1 else None, "ffn": roof["ffn_us"] / t_ffn}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--d-ff", type=int, default=2048)
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
+    eng = Engine(rank, world)
+    cap_rows = 2 * args.tokens * args.topk + 256
+    eng.initEngine("cuda", heap_bytes=cap_rows * args.hidden * 3 + cap_rows * args.hidden // 32 + (1 << 30))
+    if world > 1:
+        eng.connect()
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    experts = args.experts if args.experts % world == 0 else world * (args.experts // world)
+    res = run(eng, args.tokens, args.hidden, args.d_ff, experts, args.topk, iters=args.iters,
+              peak_tflops=float(peaks.get("bf16_tflops", 1590.0)))
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+        if args.out:
+            with open(args.out, "w") as f:
+                json.dump(res, f)
+    if world > 1:
+        dist.barrier()
+    del eng
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -189,6 +189,43 @@ def case_fused_tp(eng, rank, world):
     return {"ok": True}
 
 
+def case_moe(eng, rank, world):
+    """Expert-parallel MoE layer against a dense reference that every rank computes from the gathered inputs."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.moe import MoEExchange
+    T, H, F, E, Kt = 512, 512, 256, 4 * world, 4
+    epr = E // world
+    g = torch.Generator(device="cuda").manual_seed(31)
+    xs = [torch.randn(T, H, generator=g, device="cuda").bfloat16() for _ in range(world)]
+    logits = [torch.randn(T, E, generator=g, device="cuda") for _ in range(world)]
+    w1 = (torch.randn(E * F, H, generator=g, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(E * H, F, generator=g, device="cuda") * 0.05).bfloat16()
+    moe = MoEExchange(eng, T, H, E, Kt)
+    my_w1 = w1[rank * epr * F:(rank + 1) * epr * F].contiguous()
+    my_w2 = w2[rank * epr * H:(rank + 1) * epr * H].contiguous()
+    for it in range(2):
+        out = moe.forward(xs[rank], logits[rank] + it, my_w1, my_w2)
+        torch.cuda.synchronize()
+        check_status("moe")
+        ids, probs = MoEExchange.route(logits[rank] + it, Kt)
+        x = xs[rank]
+        xq = x.float().view(T, H // 128, 128)
+        sc = xq.abs().amax(-1, keepdim=True) / 448.0
+        xd = ((xq / sc).to(torch.float8_e4m3fn).float() * sc).view(T, H).bfloat16().float()
+        ref = torch.zeros(T, H, device="cuda")
+        for e in range(E):
+            h = torch.nn.functional.gelu(xd @ w1[e * F:(e + 1) * F].float().t(), approximate="tanh").bfloat16().float()
+            y = (h @ w2[e * H:(e + 1) * H].float().t()).bfloat16().float()
+            for k in range(Kt):
+                m = ids[:, k] == e
+                ref[m] += probs[m, k, None] * y[m]
+        err = (out.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        assert err < 0.03, f"moe iteration {it}: {err}"
+        dist.barrier()
+    eng.raise_on_status(8 + 5, "moe exchange")
+    return {"ok": True}
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 
