@@ -1,0 +1,101 @@
+"""MILP schedule synthesis: optimal values known by hand on small topologies, emitted programs verify,
+lower, and run on CPU ranks through the engine."""
+import json
+
+import pytest
+
+from pccl_b200.lang import check_lowered_deadlock_free, lower, to_schedule, verify
+from pccl_b200.synth import ScheduleCache, Topology, synthesize
+
+from _ranks import run_ranks
+
+
+def test_nvswitch_optimum_is_one_direct_step():
+    topo = Topology.nvswitch(8, port_gbs=770.0, alpha=4e-6)
+    nbytes = 64 << 20
+    r = synthesize("allgather", topo, nbytes)
+    # every rank must take in 7 shards through one port: alpha + 7 * S / bw, and one step achieves it
+    assert r.steps_used == 1
+    assert abs(r.objective_seconds - (4e-6 + 7 * nbytes / 770e9)) < 1e-8
+    assert abs(r.objective_seconds - r.lower_bound_seconds) < 1e-8
+    assert len(r.sends[0]) == 8 * 7
+    rs = synthesize("reduce_scatter", topo, nbytes)
+    assert rs.steps_used == 1 and abs(rs.objective_seconds - (4e-6 + 7 * (nbytes / 8) / 770e9)) < 1e-8
+
+
+def test_bidirectional_ring_needs_half_the_ring():
+    for n in (4, 6):
+        r = synthesize("allgather", Topology.ring(n, link_gbs=50.0), 1 << 20)
+        assert r.steps_used == n // 2          # diameter of a bidirectional ring
+        for step in r.sends:
+            for (_o, _c, u, v) in step:
+                assert (v - u) % n in (1, n - 1)      # only neighbour links are used
+
+
+def test_unidirectional_ring_needs_n_minus_1_steps():
+    r = synthesize("allgather", Topology.ring(4, link_gbs=50.0, bidirectional=False), 1 << 16)
+    assert r.steps_used == 3
+    # each step every rank forwards exactly one chunk to its successor: the classic ring
+    for step in r.sends:
+        assert sorted((u, v) for (_o, _c, u, v) in step) == [(0, 1), (1, 2), (2, 3), (3, 0)]
+
+
+def test_asymmetric_topology_is_solved_without_the_rotation_shortcut():
+    gbs = [[0, 100, 10], [100, 0, 100], [10, 100, 0]]      # 0 <-> 2 is a slow link
+    topo = Topology.from_matrix(gbs, port_gbs=200.0)
+    assert not topo.rotation_symmetric
+    r = synthesize("allgather", topo, 8 << 20)
+    assert verify(r.ir).ok
+    # the slow link must carry less than the fast ones
+    slow = sum(1 for st in r.sends for (_o, _c, u, v) in st if {u, v} == {0, 2})
+    assert slow <= 1
+
+
+@pytest.mark.parametrize("coll", ["allgather", "reduce_scatter", "allreduce"])
+@pytest.mark.parametrize("topo", [Topology.nvswitch(4), Topology.ring(4, 50.0)])
+def test_synthesised_programs_verify_and_lower(coll, topo):
+    r = synthesize(coll, topo, 1 << 20, chunks=2)
+    rep = verify(r.ir)
+    assert rep.ok, rep.errors[:3]
+    low = lower(r.ir)
+    assert check_lowered_deadlock_free(low)
+    assert r.ir.attrs["synthesized"] and r.ir.attrs["topology"] == topo.fingerprint()
+
+
+def test_schedule_cache_roundtrip(tmp_path):
+    cache = ScheduleCache(str(tmp_path))
+    topo = Topology.nvswitch(4)
+    a = cache.get_or_synthesize("reduce_scatter", topo, 3 << 20)
+    b = cache.get_or_synthesize("reduce_scatter", topo, (3 << 20) + 5)       # same size bucket
+    assert cache.misses == 1 and cache.hits == 1 and a == b
+    c = cache.get_or_synthesize("reduce_scatter", Topology.ring(4), 3 << 20)
+    assert cache.misses == 2 and c["name"] != a["name"]
+    assert json.loads(json.dumps(a))["lowered"]["num_ranks"] == 4
+
+
+def _run_synth(rank, world, port, coll, topo_kind):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.synth import Topology, synthesize
+    topo = Topology.nvswitch(world) if topo_kind == "switch" else Topology.ring(world, 50.0)
+    ir = synthesize(coll, topo, 1 << 20, chunks=2).ir
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("s", ir)
+    n = 5000
+    g = torch.Generator().manual_seed(0)
+    per = {"allgather": n, "reduce_scatter": n * world, "allreduce": n}[coll]
+    xs = [torch.randn(per, generator=g) for _ in range(world)]
+    out_n = {"allgather": n * world, "reduce_scatter": n, "allreduce": n}[coll]
+    y = torch.zeros(out_n)
+    e.exeOp("s", xs[rank], y, width=2)
+    full = torch.stack(xs)
+    ref = {"allgather": torch.cat(xs), "reduce_scatter": full.sum(0)[rank * n:(rank + 1) * n], "allreduce": full.sum(0)}[coll]
+    e.exitCluster()
+    return (y - ref).abs().max().item()
+
+
+@pytest.mark.parametrize("coll", ["allgather", "reduce_scatter", "allreduce"])
+@pytest.mark.parametrize("topo_kind", ["switch", "ring"])
+def test_synthesised_schedule_runs_on_cpu_ranks(coll, topo_kind):
+    res = run_ranks(_run_synth, 4, args=(coll, topo_kind), env={"PCCL_WORKSPACE_MB": "32"})
+    assert all(v < 1e-4 for v in res.values()), res
