@@ -97,7 +97,7 @@ void bindFused(py::module_& m) {
   // ---- production: this process is one rank -------------------------------------------------------
   m.def("ag_gemm", [](Engine& e, uint64_t x_off, int M, int N, int K, uint64_t w, int64_t ldw, uint64_t d, int64_t ldd,
                       uint64_t bias, uint64_t ready, uint64_t epoch, int n_copy, int ctas, int flag_lane, uint64_t status,
-                      uint64_t stream) {
+                      uint64_t stream, bool b_mn) {
     AgGemmArgs A{};
     A.w = e.worldTable();
     A.nvirt = 1;
@@ -108,11 +108,13 @@ void bindFused(py::module_& m) {
     A.r[0].D = reinterpret_cast<void*>(d); A.r[0].ldd = ldd; A.r[0].bias = reinterpret_cast<const void*>(bias);
     A.r[0].ready = reinterpret_cast<uint32_t*>(ready); A.r[0].status = reinterpret_cast<uint32_t*>(status);
     A.r[0].rank = e.rank();
-    AgGemmHost h{reinterpret_cast<const void*>(w), ldw};
+    AgGemmHost h{reinterpret_cast<const void*>(w), ldw, b_mn};
     check(launchAgGemm(A, &h, ctas, reinterpret_cast<cudaStream_t>(stream)), "ag_gemm");
-  });
+  }, py::arg("engine"), py::arg("x_off"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("w"), py::arg("ldw"), py::arg("d"), py::arg("ldd"),
+     py::arg("bias"), py::arg("ready"), py::arg("epoch"), py::arg("n_copy"), py::arg("ctas"), py::arg("flag_lane"), py::arg("status"),
+     py::arg("stream"), py::arg("b_mn") = false);
   m.def("gemm_rs", [](Engine& e, uint64_t y, int64_t ldy, uint64_t w, int64_t ldw, uint64_t out, int64_t ldo, int M, int N, int K,
-                      uint64_t stage_off, uint64_t flag_off2, uint64_t epoch, int ctas, uint64_t status, uint64_t stream) {
+                      uint64_t stage_off, uint64_t flag_off2, uint64_t epoch, int ctas, uint64_t status, uint64_t stream, bool b_mn) {
     GemmRsArgs A{};
     A.w = e.worldTable();
     A.nvirt = 1;
@@ -120,9 +122,11 @@ void bindFused(py::module_& m) {
     A.stage_off = stage_off; A.flag_off2 = flag_off2; A.epoch = epoch; A.spin_ns = kDefaultSpinLimit;
     A.r[0].out = reinterpret_cast<void*>(out); A.r[0].ldo = ldo; A.r[0].status = reinterpret_cast<uint32_t*>(status);
     A.r[0].rank = e.rank();
-    GemmRsHost h{reinterpret_cast<const void*>(y), ldy, reinterpret_cast<const void*>(w), ldw};
+    GemmRsHost h{reinterpret_cast<const void*>(y), ldy, reinterpret_cast<const void*>(w), ldw, b_mn};
     check(launchGemmRs(A, &h, ctas, reinterpret_cast<cudaStream_t>(stream)), "gemm_rs");
-  });
+  }, py::arg("engine"), py::arg("y"), py::arg("ldy"), py::arg("w"), py::arg("ldw"), py::arg("out"), py::arg("ldo"), py::arg("M"), py::arg("N"),
+     py::arg("K"), py::arg("stage_off"), py::arg("flag_off2"), py::arg("epoch"), py::arg("ctas"), py::arg("status"), py::arg("stream"),
+     py::arg("b_mn") = false);
   // ---- single-GPU emulation of all ranks in one cooperative launch (tests) ------------------------
   m.def("emu_ag_gemm", [](const std::vector<uint64_t>& heaps, uint64_t flag_off, uint64_t x_off, int M, int N, int K,
                           const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& d, int64_t ldd,
@@ -139,7 +143,7 @@ void bindFused(py::module_& m) {
       A.r[r].D = reinterpret_cast<void*>(d.at(r)); A.r[r].ldd = ldd;
       A.r[r].ready = reinterpret_cast<uint32_t*>(ready.at(r)); A.r[r].status = reinterpret_cast<uint32_t*>(status.at(r));
       A.r[r].rank = r;
-      h[r] = AgGemmHost{reinterpret_cast<const void*>(w.at(r)), ldw};
+      h[r] = AgGemmHost{reinterpret_cast<const void*>(w.at(r)), ldw, false};
     }
     check(launchAgGemm(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "emu_ag_gemm");
   });
@@ -157,7 +161,7 @@ void bindFused(py::module_& m) {
     for (int r = 0; r < n; ++r) {
       A.r[r].out = reinterpret_cast<void*>(out.at(r)); A.r[r].ldo = ldo;
       A.r[r].status = reinterpret_cast<uint32_t*>(status.at(r)); A.r[r].rank = r;
-      h[r] = GemmRsHost{reinterpret_cast<const void*>(y.at(r)), ldy, reinterpret_cast<const void*>(w.at(r)), ldw};
+      h[r] = GemmRsHost{reinterpret_cast<const void*>(y.at(r)), ldy, reinterpret_cast<const void*>(w.at(r)), ldw, false};
     }
     check(launchGemmRs(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "emu_gemm_rs");
   });

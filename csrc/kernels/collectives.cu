@@ -101,19 +101,38 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const __grid_constant__ 
   const uint64_t per = (nvec + n - 1) / n;
   const uint64_t lo = min(per * me, nvec), hi = min(per * (me + 1), nvec);
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-  for (uint64_t i = lo + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += stride) {
-    const uint64_t o = i << 4;
-    if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
-      Vec16 r = multimem_ld_reduce<DT, OP>(A.w.mc_heap + A.in_off + o);
-      multimem_st(A.w.mc_heap + A.out_off + o, r);
-    } else {
+  uint64_t i = lo + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
+    // four in-switch reductions in flight per thread before the first multicast store
+    for (; i + 3 * stride < hi; i += 4 * stride) {
+      Vec16 r[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) r[u] = multimem_ld_reduce<DT, OP>(A.w.mc_heap + A.in_off + ((i + u * stride) << 4));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) multimem_st(A.w.mc_heap + A.out_off + ((i + u * stride) << 4), r[u]);
+    }
+    for (; i < hi; i += stride) multimem_st(A.w.mc_heap + A.out_off + (i << 4), multimem_ld_reduce<DT, OP>(A.w.mc_heap + A.in_off + (i << 4)));
+  } else {
+    for (; i + stride < hi; i += 2 * stride) {     // two vectors = up to 16 peer loads in flight per thread
+      float acc0[N], acc1[N];
+      pull_reduce<DT, OP>(A, me, A.in_off + (i << 4), acc0);
+      pull_reduce<DT, OP>(A, me, A.in_off + ((i + stride) << 4), acc1);
+      Vec16 r0 = pack<DT>(acc0), r1 = pack<DT>(acc1);
+      for (int k = 0; k < n; ++k) {
+        int p = me + k;
+        if (p >= n) p -= n;
+        st16(A.w.heap[p] + A.out_off + (i << 4), r0);
+        st16(A.w.heap[p] + A.out_off + ((i + stride) << 4), r1);
+      }
+    }
+    for (; i < hi; i += stride) {
       float acc[N];
-      pull_reduce<DT, OP>(A, me, A.in_off + o, acc);
+      pull_reduce<DT, OP>(A, me, A.in_off + (i << 4), acc);
       Vec16 r = pack<DT>(acc);
       for (int k = 0; k < n; ++k) {
         int p = me + k;
         if (p >= n) p -= n;
-        st16(A.w.heap[p] + A.out_off + o, r);
+        st16(A.w.heap[p] + A.out_off + (i << 4), r);
       }
     }
   }
@@ -178,14 +197,7 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(const __grid_consta
   const uint64_t gtid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   uint64_t done = 0;
   if (aligned) {
-    for (uint64_t i = gtid; i < nvec; i += stride) {
-      const uint64_t o = i << 4;
-      float acc[N];
-      if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
-        unpack<DT>(multimem_ld_reduce<DT, OP>(A.w.mc_heap + base + o), acc);
-      } else {
-        pull_reduce<DT, OP>(A, me, base + o, acc);
-      }
+    auto finish = [&](uint64_t i, float* acc) {
 #pragma unroll
       for (int j = 0; j < N; ++j) acc[j] *= scale;
       if constexpr (OUT_F32 && DT != DT_F32) {
@@ -198,7 +210,39 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(const __grid_consta
           st16(of + j, r);
         }
       } else {
-        st16(out + o, pack<DT>(acc));
+        st16(out + (i << 4), pack<DT>(acc));
+      }
+    };
+    uint64_t i = gtid;
+    if constexpr (NVLS && MultimemSupported<DT, OP>::value) {
+      for (; i + 3 * stride < nvec; i += 4 * stride) {
+        Vec16 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) r[u] = multimem_ld_reduce<DT, OP>(A.w.mc_heap + base + ((i + u * stride) << 4));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float acc[N];
+          unpack<DT>(r[u], acc);
+          finish(i + u * stride, acc);
+        }
+      }
+      for (; i < nvec; i += stride) {
+        float acc[N];
+        unpack<DT>(multimem_ld_reduce<DT, OP>(A.w.mc_heap + base + (i << 4)), acc);
+        finish(i, acc);
+      }
+    } else {
+      for (; i + stride < nvec; i += 2 * stride) {
+        float acc0[N], acc1[N];
+        pull_reduce<DT, OP>(A, me, base + (i << 4), acc0);
+        pull_reduce<DT, OP>(A, me, base + ((i + stride) << 4), acc1);
+        finish(i, acc0);
+        finish(i + stride, acc1);
+      }
+      for (; i < nvec; i += stride) {
+        float acc[N];
+        pull_reduce<DT, OP>(A, me, base + (i << 4), acc);
+        finish(i, acc);
       }
     }
     done = nvec << 4;
@@ -228,15 +272,34 @@ __global__ void __launch_bounds__(1024) allgather_kernel(const __grid_constant__
   const uint64_t nvec = aligned ? bytes >> 4 : 0;
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
   const uint64_t gtid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  for (uint64_t i = gtid; i < nvec; i += stride) {
-    Vec16 v = ld16(in + (i << 4));
-    if constexpr (NVLS) {
-      multimem_st(A.w.mc_heap + dst + (i << 4), v);
-    } else {
-      for (int k = 0; k < n; ++k) {
-        int p = me + k;
-        if (p >= n) p -= n;
-        st16(A.w.heap[p] + dst + (i << 4), v);
+  {
+    uint64_t i = gtid;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      Vec16 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ld16(in + ((i + u * stride) << 4));
+      if constexpr (NVLS) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) multimem_st(A.w.mc_heap + dst + ((i + u * stride) << 4), v[u]);
+      } else {
+        for (int k = 0; k < n; ++k) {
+          int p = me + k;
+          if (p >= n) p -= n;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) st16(A.w.heap[p] + dst + ((i + u * stride) << 4), v[u]);
+        }
+      }
+    }
+    for (; i < nvec; i += stride) {
+      Vec16 v = ld16(in + (i << 4));
+      if constexpr (NVLS) {
+        multimem_st(A.w.mc_heap + dst + (i << 4), v);
+      } else {
+        for (int k = 0; k < n; ++k) {
+          int p = me + k;
+          if (p >= n) p -= n;
+          st16(A.w.heap[p] + dst + (i << 4), v);
+        }
       }
     }
   }

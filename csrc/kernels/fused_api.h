@@ -38,7 +38,9 @@ struct AgGemmArgs {
   AgGemmRank r[kMaxVirt];
 };
 
-struct AgGemmHost { const void* W; long long ldw; };   // W1 shard [N, K] bf16, per (virtual) rank
+// W shard per (virtual) rank: [N, K] bf16 row-major, or, with b_mn, stored [K, N] (the transposed view feeds
+// backward passes without a transpose)
+struct AgGemmHost { const void* W; long long ldw; bool b_mn; };
 
 struct GemmRsRank {
   CUtensorMap tmA, tmB;
@@ -60,7 +62,7 @@ struct GemmRsArgs {
   GemmRsRank r[kMaxVirt];
 };
 
-struct GemmRsHost { const void* Y; long long ldy; const void* W; long long ldw; };   // Y [M, K], W2 shard [N, K]
+struct GemmRsHost { const void* Y; long long ldy; const void* W; long long ldw; bool b_mn; };   // Y [M, K]; W [N, K], or [K, N] with b_mn
 
 int launchAgGemm(AgGemmArgs& args, const AgGemmHost* host, int ctas, cudaStream_t stream);
 int launchGemmRs(GemmRsArgs& args, const GemmRsHost* host, int ctas, cudaStream_t stream);

@@ -193,6 +193,7 @@ __device__ void ag_copy_role(const AgGemmArgs& A, const AgGemmRank& R, uint8_t* 
   cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 2, A.spin_ns, R.status);
 }
 
+template <bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgGemmArgs A) {
   const AgGemmRank& R = A.r[blockIdx.y];
   if (static_cast<int>(blockIdx.x) < A.n_copy) {
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_co
   AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy};
   AgGate gate{R.ready, R.rank, static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>((static_cast<long long>(BM) * A.K * 2) / kCopyPiece), A.spin_ns};
   StoreEpi epi{R.D, nullptr, static_cast<const __nv_bfloat16*>(R.bias), R.ldd, A.M, A.N, A.flags};
-  run<false, false>(&R.tmA, &R.tmB, A.K, sched, gate, epi, R.status);
+  run<false, B_MN>(&R.tmA, &R.tmB, A.K, sched, gate, epi, R.status);
 }
 
 // =================================================================================================
@@ -313,13 +314,14 @@ struct RsEpi {
   }
 };
 
+template <bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_constant__ GemmRsArgs A) {
   const GemmRsRank& R = A.r[blockIdx.y];
   const int tiles_ml = A.M_local / BM, tiles_n = A.N / BN;
   RsSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
   NoGate gate;
   RsEpi epi{&A, &R, nullptr, R.rank, tiles_ml, tiles_n};
-  run<false, false>(&R.tmA, &R.tmB, A.K, sched, gate, epi, R.status);
+  run<false, B_MN>(&R.tmA, &R.tmB, A.K, sched, gate, epi, R.status);
 }
 
 thread_local std::string g_err;
@@ -339,19 +341,23 @@ int launchAgGemm(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_t s
     // gathered X lives at x_off of this rank's own heap: TMA reads local memory only
     const void* xg = A.w.heap[A.r[v].rank] + A.x_off;
     if (!makeTensorMap2D(&A.r[v].tmA, xg, TM_BF16, A.K, A.M, A.K, BK, BM, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
-    if (!makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, BN, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
+    if (host[v].b_mn != host[0].b_mn) { g_err = "ag_gemm: all ranks must use the same operand form"; return static_cast<int>(cudaErrorInvalidValue); }
+    const bool okB = host[v].b_mn ? makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.N, A.K, host[v].ldw, 64, BK, &g_err)
+                                  : makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, BN, &g_err);
+    if (!okB) return static_cast<int>(cudaErrorInvalidValue);
   }
   if (A.w.world == 1) A.n_copy = 0;
   if (ctas <= A.n_copy) { g_err = "ag_gemm: need more CTAs than copy CTAs"; return static_cast<int>(cudaErrorInvalidValue); }
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  void* kern = host[0].b_mn ? reinterpret_cast<void*>(ag_gemm_kernel<true>) : reinterpret_cast<void*>(ag_gemm_kernel<false>);
+  static bool set[2] = {false, false};
+  if (!set[host[0].b_mn]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    set = true;
+    set[host[0].b_mn] = true;
   }
   dim3 grid(ctas, nv), block(NUM_THREADS);
   void* args[] = {&A};
-  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ag_gemm_kernel), grid, block, args, SMEM_BYTES, stream));
+  return static_cast<int>(cudaLaunchCooperativeKernel(kern, grid, block, args, SMEM_BYTES, stream));
 }
 
 int launchGemmRs(GemmRsArgs& A, const GemmRsHost* host, int ctas, cudaStream_t stream) {
@@ -363,17 +369,21 @@ int launchGemmRs(GemmRsArgs& A, const GemmRsHost* host, int ctas, cudaStream_t s
   }
   for (int v = 0; v < nv; ++v) {
     if (!makeTensorMap2D(&A.r[v].tmA, host[v].Y, TM_BF16, A.K, A.M, host[v].ldy, BK, BM, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
-    if (!makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, BN, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
+    if (host[v].b_mn != host[0].b_mn) { g_err = "gemm_rs: all ranks must use the same operand form"; return static_cast<int>(cudaErrorInvalidValue); }
+    const bool okB = host[v].b_mn ? makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.N, A.K, host[v].ldw, 64, BK, &g_err)
+                                  : makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, BN, &g_err);
+    if (!okB) return static_cast<int>(cudaErrorInvalidValue);
   }
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_SMEM_BYTES);
+  void* kern = host[0].b_mn ? reinterpret_cast<void*>(gemm_rs_kernel<true>) : reinterpret_cast<void*>(gemm_rs_kernel<false>);
+  static bool set[2] = {false, false};
+  if (!set[host[0].b_mn]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    set = true;
+    set[host[0].b_mn] = true;
   }
   dim3 grid(ctas, nv), block(NUM_THREADS);
   void* args[] = {&A};
-  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(gemm_rs_kernel), grid, block, args, RS_SMEM_BYTES, stream));
+  return static_cast<int>(cudaLaunchCooperativeKernel(kern, grid, block, args, RS_SMEM_BYTES, stream));
 }
 
 }  // namespace pccl

@@ -27,10 +27,11 @@ def _algo(eng: Engine, algo: str, dt: str, op: str, nbytes: int) -> str:
 
 
 def _blocks(nbytes: int, blocks: Optional[int]) -> int:
+    """CTAs for a collective that moves `nbytes` per rank: one CTA (512 threads, 4 x 16 bytes each in
+    flight) per 32 KiB keeps small messages to a single pass, 128 CTAs saturate NVLink for large ones."""
     if blocks:
         return blocks
-    # enough CTAs to fill NVLink, few enough to leave the GPU to concurrent compute
-    return max(1, min(64, nbytes // (256 << 10) + 1))
+    return max(1, min(128, (nbytes + (32 << 10) - 1) // (32 << 10)))
 
 
 def all_reduce(eng: Engine, inp: torch.Tensor, out: Optional[torch.Tensor] = None, op: str = "sum", algo: str = "auto",
@@ -41,7 +42,7 @@ def all_reduce(eng: Engine, inp: torch.Tensor, out: Optional[torch.Tensor] = Non
     a = _algo(eng, algo, dt, op, nbytes)
     s = (stream or torch.cuda.current_stream()).cuda_stream
     C.collective(eng.raw, "allreduce", a, dt, op, eng.heap_offset(inp), eng.heap_offset(out), inp.numel(), lane, 1.0, "",
-                 _blocks(nbytes, blocks), threads, s, 0, 0, 0)
+                 _blocks(nbytes // eng.world, blocks), threads, s, 0, 0, 0)
     count_launch()
     return out
 
@@ -58,7 +59,7 @@ def reduce_scatter(eng: Engine, inp: torch.Tensor, out: torch.Tensor, op: str = 
     s = (stream or torch.cuda.current_stream()).cuda_stream
     sym_out = eng.is_symmetric(out)
     C.collective(eng.raw, "reduce_scatter", a, dt, op, eng.heap_offset(inp), eng.heap_offset(out) if sym_out else 0, n, lane,
-                 float(scale), dtype_name(out.dtype), _blocks(n * inp.element_size() * eng.world, blocks), threads, s, 0,
+                 float(scale), dtype_name(out.dtype), _blocks(n * inp.element_size(), blocks), threads, s, 0,
                  0 if sym_out else out.data_ptr(), 0)
     count_launch()
     return out
@@ -71,7 +72,7 @@ def all_gather(eng: Engine, inp: torch.Tensor, out: torch.Tensor, algo: str = "a
     a = "nvls" if (algo in ("auto", "nvls") and eng.has_nvls and nbytes % 16 == 0 and inp.data_ptr() % 16 == 0) else "p2p"
     s = (stream or torch.cuda.current_stream()).cuda_stream
     C.collective(eng.raw, "allgather", a, "u8", "sum", 0, eng.heap_offset(out), nbytes, lane, 1.0, "",
-                 _blocks(nbytes * eng.world, blocks), threads, s, inp.data_ptr(), 0, 0)
+                 _blocks(nbytes, blocks), threads, s, inp.data_ptr(), 0, 0)
     count_launch()
     return out
 

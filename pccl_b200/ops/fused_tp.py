@@ -33,16 +33,18 @@ class AllGatherGemm:
         self.ctas = ctas or C.sm_count()
         self.flag_lane = flag_lane
 
-    def __call__(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        n = w.shape[0]
-        if w.dtype != torch.bfloat16 or w.shape[1] != self.K or w.stride(1) != 1:
-            raise ValueError("AllGatherGemm: w must be bf16 [N, K]")
+    def __call__(self, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 w_t: bool = False) -> torch.Tensor:
+        """``w`` is [N, K]; with ``w_t`` it is stored [K, N] and consumed transposed (no copy)."""
+        n = w.shape[1] if w_t else w.shape[0]
+        if w.dtype != torch.bfloat16 or w.shape[0 if w_t else 1] != self.K or w.stride(1) != 1:
+            raise ValueError("AllGatherGemm: w must be bf16 [N, K] (or [K, N] with w_t)")
         if out is None:
             out = torch.empty((self.M, n), dtype=torch.bfloat16, device="cuda")
         self.epoch += 1
         C.ag_gemm(self.eng.raw, self.eng.heap_offset(self.x_full), self.M, n, self.K, w.data_ptr(), w.stride(0), out.data_ptr(),
                   out.stride(0), bias.data_ptr() if bias is not None else 0, self.ready.data_ptr(), self.epoch, self.n_copy,
-                  self.ctas, self.flag_lane, status_words().data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  self.ctas, self.flag_lane, status_words().data_ptr(), torch.cuda.current_stream().cuda_stream, w_t)
         count_launch()
         return out
 
@@ -62,14 +64,16 @@ class GemmReduceScatter:
         self.epoch = 0
         self.ctas = ctas or C.sm_count()
 
-    def __call__(self, y: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if y.shape[0] != self.M or w.shape[0] != self.N or y.shape[1] != w.shape[1]:
+    def __call__(self, y: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, w_t: bool = False) -> torch.Tensor:
+        """``w`` is [N, K]; with ``w_t`` it is stored [K, N] and consumed transposed (no copy)."""
+        wn, wk = (w.shape[1], w.shape[0]) if w_t else (w.shape[0], w.shape[1])
+        if y.shape[0] != self.M or wn != self.N or y.shape[1] != wk:
             raise ValueError("GemmReduceScatter: shape mismatch")
         if out is None:
             out = torch.empty((self.M // self.eng.world, self.N), dtype=torch.bfloat16, device="cuda")
         self.epoch += 1
         C.gemm_rs(self.eng.raw, y.data_ptr(), y.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), self.M, self.N,
                   y.shape[1], self.eng.heap_offset(self.stage), self.eng.heap_offset(self.flags), self.epoch, self.ctas,
-                  status_words().data_ptr(), torch.cuda.current_stream().cuda_stream)
+                  status_words().data_ptr(), torch.cuda.current_stream().cuda_stream, w_t)
         count_launch()
         return out

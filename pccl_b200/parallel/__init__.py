@@ -1,4 +1,4 @@
 """Parallelism strategies built on the collectives and fused kernels."""
 from .dp import ShardedDataParallel
 
-__all__ = ["ShardedDataParallel"]
+__all__ = ["ShardedDataParallel", "tp", "ep", "pp"]

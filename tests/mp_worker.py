@@ -189,6 +189,44 @@ def case_fused_tp(eng, rank, world):
     return {"ok": True}
 
 
+def case_tp_mlp(eng, rank, world):
+    """Sequence/tensor-parallel MLP (fused forward and backward) against the single-device network."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.parallel.tp import TensorParallelMLP
+    tokens, d, ff = 256 * world, 512, 1024 * world
+    torch.manual_seed(40)
+    mlp = TensorParallelMLP(eng, tokens, d, ff, n_copy=4)
+    # every rank builds the full reference weights from all shards
+    def gather(p):
+        parts = [torch.empty_like(p.data) for _ in range(world)]
+        dist.all_gather(parts, p.data.contiguous())
+        return parts
+    w1 = torch.cat(gather(mlp.fc1.weight), 0).float().requires_grad_(True)       # [ff, d]
+    b1 = torch.cat(gather(mlp.fc1.bias), 0).float().requires_grad_(True)
+    w2 = torch.cat(gather(mlp.fc2.weight), 1).float().requires_grad_(True)       # [d, ff]
+    g = torch.Generator(device="cuda").manual_seed(41)
+    X = torch.randn(tokens, d, generator=g, device="cuda").bfloat16()
+    G = (torch.randn(tokens, d, generator=g, device="cuda") * 0.1).bfloat16()
+    ml = tokens // world
+    x_local = X[rank * ml:(rank + 1) * ml].clone().requires_grad_(True)
+    z = mlp(x_local)
+    z.backward(G[rank * ml:(rank + 1) * ml])
+    torch.cuda.synchronize()
+    check_status("tp mlp")
+    Xr = X.float().requires_grad_(True)
+    zr = torch.nn.functional.gelu(Xr @ w1.t() + b1, approximate="tanh") @ w2.t() + mlp.fc2.bias.float()
+    zr.backward(G.float())
+    def rel(a, b):
+        return (a.float() - b).abs().max().item() / max(1e-6, b.abs().max().item())
+    n1 = ff // world
+    assert rel(z, zr[rank * ml:(rank + 1) * ml].detach()) < 0.03
+    assert rel(x_local.grad, Xr.grad[rank * ml:(rank + 1) * ml]) < 0.04
+    assert rel(mlp.fc1.weight.grad, w1.grad[rank * n1:(rank + 1) * n1]) < 0.04
+    assert rel(mlp.fc2.weight.grad, w2.grad[:, rank * n1:(rank + 1) * n1]) < 0.04
+    assert rel(mlp.fc1.bias.grad, b1.grad[rank * n1:(rank + 1) * n1]) < 0.04
+    return {"ok": True}
+
+
 def case_moe(eng, rank, world):
     """Expert-parallel MoE layer against a dense reference that every rank computes from the gathered inputs."""
     from pccl_b200.ops import check_status
