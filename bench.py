@@ -67,7 +67,7 @@ def main() -> None:
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
 
     from pccl_b200.engine import Engine
     from pccl_b200.models import GPT, GPTConfig
@@ -177,6 +177,9 @@ def main() -> None:
         if micro is not None:
             out["micro"] = micro
         print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+    del dp, model, eng          # unbind and unmap the symmetric heap while every rank is still here
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

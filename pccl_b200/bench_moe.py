@@ -132,7 +132,7 @@ def main():
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
     os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
     eng = Engine(rank, world)
     cap_rows = 2 * args.tokens * args.topk + 256

@@ -122,7 +122,7 @@ def main():
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
     os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
     eng = Engine(rank, world)
     heap = 3 * args.tokens * args.d_model * 2 + (1 << 30)

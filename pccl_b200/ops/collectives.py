@@ -20,7 +20,12 @@ _NVLS_OK = {("f32", "sum"), ("bf16", "sum"), ("bf16", "max"), ("bf16", "min"), (
 
 def _algo(eng: Engine, algo: str, dt: str, op: str, nbytes: int) -> str:
     if algo == "auto":
-        return "nvls" if (eng.has_nvls and (dt, op) in _NVLS_OK and nbytes % 16 == 0) else "p2p"
+        ok = eng.has_nvls and (dt, op) in _NVLS_OK and nbytes % 16 == 0
+        # Between two GPUs the switch has nothing to add: one peer load per element beats a multimem
+        # round trip once the message is bandwidth-bound (measured cross-over near 8 MiB).
+        if ok and eng.world == 2 and nbytes >= (8 << 20):
+            ok = False
+        return "nvls" if ok else "p2p"
     if algo == "nvls" and not eng.has_nvls:
         raise RuntimeError("NVLS requested but the heap is not bound to a multicast object")
     return algo
@@ -42,7 +47,7 @@ def all_reduce(eng: Engine, inp: torch.Tensor, out: Optional[torch.Tensor] = Non
     a = _algo(eng, algo, dt, op, nbytes)
     s = (stream or torch.cuda.current_stream()).cuda_stream
     C.collective(eng.raw, "allreduce", a, dt, op, eng.heap_offset(inp), eng.heap_offset(out), inp.numel(), lane, 1.0, "",
-                 _blocks(nbytes // eng.world, blocks), threads, s, 0, 0, 0)
+                 _blocks(nbytes if (nbytes <= (256 << 10) and out is not inp) else nbytes // eng.world, blocks), threads, s, 0, 0, 0)
     count_launch()
     return out
 

@@ -272,7 +272,7 @@ def main():
     out_path = sys.argv[2]
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
     from pccl_b200.engine import Engine
     os.environ.setdefault("PCCL_WORKSPACE_MB", "256")
     eng = Engine(rank, world)
