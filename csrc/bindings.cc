@@ -201,6 +201,7 @@ PYBIND11_MODULE(_C, m) {
            py::call_guard<py::gil_scoped_release>())
       .def("exitCluster", &Engine::exitCluster, py::call_guard<py::gil_scoped_release>())
       .def("stats", &Engine::stats)
+      .def("trace", &Engine::trace)
       .def("deviceKind", &Engine::deviceKind)
       .def("heapBase", &Engine::heapBase)
       .def("heapBytes", &Engine::heapBytes)

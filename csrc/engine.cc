@@ -95,6 +95,7 @@ void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
   timeout_ms_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_WAIT_TIMEOUT_MS", 30000));
   spin_limit_ = static_cast<uint64_t>(LaunchEnvironments::getInt("PCCL_SPIN_LIMIT", static_cast<int64_t>(kDefaultSpinLimit)));
   bounds_check_ = LaunchEnvironments::getBool("PCCL_BOUNDS_CHECK", true);
+  trace_ = LaunchEnvironments::getBool("PCCL_TRACE", false);
   max_width_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_MAX_SMS", 32));
   host_id_ = readHostId();
   buildLayout(heap_bytes);
@@ -382,7 +383,9 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   ctx.redop = parseRedOp(p.redop);
   ctx.timeout_ms = timeout_ms_;
   ctx.bounds_check = bounds_check_;
+  ctx.trace = trace_;
   CpuExecResult res = runOnCpu(m, ctx);
+  for (auto& ev : res.trace) spans_.push_back(Span{p.name, ev.stream, ev.pc, ev.op, ev.t0_ns, ev.t1_ns, ev.bytes});
   op.epoch++;
   op.launches++;
   op.bytes += m.bytes_moved;
@@ -458,6 +461,31 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   op.launches++;
   op.bytes += c.m.bytes_moved;
   return 0;
+}
+
+std::string Engine::trace() {
+  static const char* names[] = {"NOP", "COPY", "REDUCE", "NOTIFY", "WAIT", "MM_LD_REDUCE", "MM_ST", "BARRIER", "END"};
+  Json events = Json::array();
+  for (auto& s : spans_) {
+    Json e = Json::object();
+    e.set("name", std::string(names[s.opcode < 9 ? s.opcode : 0]));
+    e.set("cat", s.op);
+    e.set("ph", "X");
+    e.set("pid", rank_);
+    e.set("tid", static_cast<int64_t>(s.stream));
+    e.set("ts", static_cast<double>(s.t0) / 1000.0);
+    e.set("dur", static_cast<double>(s.t1 - s.t0) / 1000.0);
+    Json args = Json::object();
+    args.set("pc", static_cast<int64_t>(s.pc));
+    args.set("bytes", s.bytes);
+    e.set("args", args);
+    events.push(e);
+  }
+  spans_.clear();
+  Json doc = Json::object();
+  doc.set("traceEvents", events);
+  doc.set("displayTimeUnit", "ns");
+  return doc.dump();
 }
 
 std::string Engine::stats() {

@@ -58,6 +58,9 @@ class Engine {
   void joinCluster(const std::string& master_endpoint, int timeout_ms = 60000);
   void exitCluster();
   std::string stats();
+  // Chrome-trace ("traceEvents") JSON of the CPU executor's instructions recorded while PCCL_TRACE=1;
+  // clears the record.
+  std::string trace();
 
   // symmetric heap
   const std::string& deviceKind() const { return device_; }
@@ -128,6 +131,9 @@ class Engine {
   int timeout_ms_ = 30000;
   uint64_t spin_limit_ = kDefaultSpinLimit;
   bool bounds_check_ = true;
+  bool trace_ = false;
+  struct Span { std::string op; uint32_t stream, pc, opcode; uint64_t t0, t1, bytes; };
+  std::vector<Span> spans_;
   int max_width_ = 32;
 };
 

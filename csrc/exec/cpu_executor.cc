@@ -38,7 +38,7 @@ bool waitFor(std::atomic<uint64_t>* word, uint64_t target, const CpuExecContext&
   return true;
 }
 
-void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext& ctx, Shared& sh) {
+void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext& ctx, Shared& sh, std::vector<TraceEvent>* trace) {
   std::atomic<uint64_t>* my_signals = ctx.peer_signals[ctx.rank];
   auto resolve = [&](int rank, uint32_t buf, uint64_t off, uint64_t bytes, bool* remote_tcp) -> char* {
     *remote_tcp = false;
@@ -55,6 +55,10 @@ void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext&
   for (size_t pc = 0; pc < prog.size(); ++pc) {
     if (sh.status.load(std::memory_order_relaxed) != ST_OK) return;
     const Instr& in = prog[pc];
+    struct Stamp {
+      std::vector<TraceEvent>* out; uint32_t stream, pc, op; uint64_t bytes, t0;
+      ~Stamp() { if (out) out->push_back(TraceEvent{stream, pc, op, t0, monotonicNanos(), bytes}); }
+    } stamp{trace, static_cast<uint32_t>(stream), static_cast<uint32_t>(pc), in.op, in.bytes, trace ? monotonicNanos() : 0};
     switch (in.op) {
       case OP_NOP: break;
       case OP_END: return;
@@ -126,11 +130,14 @@ CpuExecResult runOnCpu(const Materialized& m, const CpuExecContext& ctx) {
   Shared sh;
   uint64_t t0 = monotonicNanos();
   std::vector<std::thread> threads;
+  std::vector<std::vector<TraceEvent>> traces(ctx.trace ? m.streams.size() : 0);
+  auto tr = [&](size_t i) { return ctx.trace ? &traces[i] : nullptr; };
   for (size_t i = 1; i < m.streams.size(); ++i)
-    threads.emplace_back([&, i] { runStream(m.streams[i], static_cast<int>(i), ctx, sh); });
-  if (!m.streams.empty()) runStream(m.streams[0], 0, ctx, sh);
+    threads.emplace_back([&, i] { runStream(m.streams[i], static_cast<int>(i), ctx, sh, tr(i)); });
+  if (!m.streams.empty()) runStream(m.streams[0], 0, ctx, sh, tr(0));
   for (auto& t : threads) t.join();
   CpuExecResult r;
+  for (auto& v : traces) r.trace.insert(r.trace.end(), v.begin(), v.end());
   r.status = sh.status.load();
   r.failed_stream = sh.failed_stream.load();
   r.failed_pc = sh.failed_pc.load();

@@ -31,6 +31,12 @@ struct CpuExecContext {
   uint32_t dtype = DT_F32, redop = RED_SUM;
   int timeout_ms = 30000;
   bool bounds_check = true;
+  bool trace = false;                // record one TraceEvent per executed instruction
+};
+
+struct TraceEvent {
+  uint32_t stream, pc, op;
+  uint64_t t0_ns, t1_ns, bytes;      // monotonic clock
 };
 
 struct CpuExecResult {
@@ -38,6 +44,7 @@ struct CpuExecResult {
   int failed_stream = -1;
   int failed_pc = -1;
   uint64_t nanos = 0;
+  std::vector<TraceEvent> trace;
 };
 
 CpuExecResult runOnCpu(const Materialized& m, const CpuExecContext& ctx);

@@ -228,6 +228,25 @@ class Engine:
     def stats(self) -> Dict:
         return json.loads(self._e.stats())
 
+    def trace(self, path: Optional[str] = None) -> Dict:
+        """Instruction-level Chrome trace of the CPU executor (recorded while ``PCCL_TRACE=1``); written
+        to ``path`` when given (open it in chrome://tracing or Perfetto).  GPU launches are timed with
+        ``timed_exeOp``."""
+        doc = json.loads(self._e.trace())
+        if path:
+            with open(path, "w") as f:
+                json.dump(doc, f)
+        return doc
+
+    def timed_exeOp(self, name: str, input: torch.Tensor, output: Optional[torch.Tensor] = None, **kw) -> float:
+        """``exeOp`` bracketed by CUDA events on the launching stream; returns milliseconds on the device."""
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        self.exeOp(name, input, output, **kw)
+        b.record()
+        b.synchronize()
+        return a.elapsed_time(b)
+
     def layout(self) -> Dict:
         return dict(self._e.layout())
 

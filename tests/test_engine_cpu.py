@@ -128,3 +128,21 @@ def test_exeop_reports_scratch_overflow():
     x = torch.zeros(2 << 20)
     with pytest.raises(RuntimeError, match="scratch"):
         e.exeOp("big", x, torch.empty_like(x))
+
+
+def test_instruction_trace_is_chrome_trace_json(tmp_path):
+    from pccl_b200.engine import Engine, LaunchEnvironments
+    from pccl_b200.lang import build
+    LaunchEnvironments.setOverride("PCCL_TRACE", "1")
+    try:
+        e = Engine(0, 1); e.initEngine("cpu")
+    finally:
+        LaunchEnvironments.setOverride("PCCL_TRACE", "0")
+    e.regOp("ar", build("ring_allreduce", 1))
+    x = torch.ones(1000); y = torch.zeros(1000)
+    e.exeOp("ar", x, y)
+    doc = e.trace(str(tmp_path / "t.json"))
+    ev = doc["traceEvents"]
+    assert ev and ev[0]["ph"] == "X" and ev[0]["name"] == "COPY" and ev[0]["args"]["bytes"] == 4000
+    assert json.loads((tmp_path / "t.json").read_text())["traceEvents"] == ev
+    assert e.trace()["traceEvents"] == []       # reading clears the record
