@@ -16,6 +16,7 @@ enum GemmFlags : uint32_t {
   GEMM_GELU = 1u << 4,        // D2 = gelu_tanh(D) written next to D (D keeps the pre-activation)
   GEMM_BIAS = 1u << 5,        // D = A*B^T + bias[n] (bf16 bias)
   GEMM_GELU_INPLACE = 1u << 6,  // D = gelu_tanh(A*B^T (+bias)); no separate pre-activation
+  GEMM_PAIR = 1u << 7,        // CTA pairs (cta_group::2, 256 x 256 tiles) instead of single CTAs (128 x 256)
 };
 
 // D[M,N] (ldd) = A * B^T.  K-major operands: A is [M,K] with row stride lda, B is [N,K] with row

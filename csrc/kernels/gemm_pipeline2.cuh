@@ -1,0 +1,187 @@
+// CTA-pair variant of the tcgen05 GEMM pipeline: two CTAs of a cluster (cta_group::2) compute one
+// 256 x 256 tile.  Each CTA loads its own 128 rows of A and its own 128 rows of B (half of N) per
+// k-block -- 32 KiB instead of 48 KiB per 128 x 256 of output, which takes a third off the L2 -> SM
+// traffic that bounds the single-CTA kernel -- into a 6-stage ring; the leader CTA issues
+// tcgen05.mma.cta_group::2 (M = 256) that reads both CTAs' shared memory and writes both CTAs'
+// tensor memory; each CTA runs the epilogue of its own 128 accumulator rows.
+//
+// No load uses cluster multicast: the operands are not shared between the CTAs, only the completion
+// of both CTAs' loads is counted on the leader's barrier.  tcgen05.commit multicasts the "stage free"
+// and "accumulator ready" arrivals to both CTAs.  Same hooks (Sched / Gate / Epi) and the same bounded
+// waits as gemm_pipeline.cuh; every thread of both CTAs reaches the closing cluster barrier.
+#pragma once
+#include "gemm_pipeline.cuh"
+
+namespace pccl {
+namespace gemm2 {
+
+using gemm::TileCoord;
+constexpr int BM = 128;            // rows per CTA; the pair's tile is 2*BM x BN
+constexpr int PAIR_M = 256, BN = 256, HALF_N = 128, BK = 64, UMMA_K = 16;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KiB
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_SMEM_OFFSET = STAGES * STAGE_BYTES + 256;
+
+struct Barriers {
+  uint64_t full[STAGES];        // used in the leader: both CTAs' loads of the stage have landed
+  uint64_t empty[STAGES];       // per CTA: the MMAs that read this stage have retired
+  uint64_t tmem_full[2];        // per CTA: accumulator ready
+  uint64_t tmem_empty[2];       // used in the leader: both CTAs' epilogues have drained the accumulator
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+// `sched` enumerates pair tiles: t.m indexes 256-row blocks.  Epi sees per-CTA coordinates through
+// a_row0 / b_row0 (which must add cta_rank * 128) and strip(t, row_in_cta_tile, col, r).
+template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi>
+__device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* tmB, int K, const Sched& sched,
+                                    const Gate& gate, Epi& epi, uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = tc::cluster_ctarank();
+  const bool leader = cta == 0;
+  const int num_kb = (K + BK - 1) / BK;
+  volatile uint32_t* abort = &bar->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(&bar->full[s], 1);
+      tc::mbar_init(&bar->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      tc::mbar_init(&bar->tmem_full[a], 1);
+      tc::mbar_init(&bar->tmem_empty[a], 8);      // four epilogue warps in each CTA of the pair
+    }
+    tc::mbar_init(&bar->drain, 1);
+    bar->abort = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(tmA);
+    tc::tma_prefetch_desc(tmB);
+  }
+  __syncthreads();
+  tc::cluster_sync();                 // the peer's barriers are initialised before anything signals them
+  if (warp == 1) {
+    tc::tmem_alloc_pair(&bar->tmem_base, TMEM_COLS);
+    tc::tmem_relinquish_pair();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  epi.attach_smem(smem + EPI_SMEM_OFFSET);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (tc::elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      TileCoord t;
+      for (int it = 0; ok && sched.get(it, &t); ++it) {
+        if (!gate.wait(t, abort)) { ok = false; break; }
+        const int row0 = epi.a_row0(t), col0 = epi.b_row0(t);        // already offset by this CTA's half
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(&bar->empty[stage], phase ^ 1, abort)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          const uint32_t full_leader = tc::mapa(tc::smem_u32(&bar->full[stage]), 0);
+          if (leader) tc::mbar_arrive_expect_tx(&bar->full[stage], 2 * STAGE_BYTES);   // both CTAs' bytes
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tc::tma_load_2d_pair(sa, tmA, full_leader, k0, row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tc::tma_load_2d_pair(sa + j * (64 * BK * 2), tmA, full_leader, row0 + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tc::tma_load_2d_pair(sb, tmB, full_leader, k0, col0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HALF_N / 64; ++j) tc::tma_load_2d_pair(sb + j * (64 * BK * 2), tmB, full_leader, col0 + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && atomicExch(const_cast<uint32_t*>(&bar->abort), 1u) == 0) dev::report(status, ST_TIMEOUT, blockIdx.x, 0, 0);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && tc::elect_one()) {
+      constexpr uint32_t idesc = tc::make_idesc(1, 1, A_MN, B_MN, PAIR_M, BN);
+      constexpr uint32_t A_LBO = A_MN ? 64 * BK * 2 : 16, B_LBO = B_MN ? 64 * BK * 2 : 16, SBO = 1024;
+      constexpr uint32_t A_KSTEP = A_MN ? (UMMA_K / 8) * 1024 : UMMA_K * 2;
+      constexpr uint32_t B_KSTEP = B_MN ? (UMMA_K / 8) * 1024 : UMMA_K * 2;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      TileCoord t;
+      for (int it = 0; ok && sched.get(it, &t); ++it) {
+        if (!tc::mbar_wait(&bar->tmem_empty[acc], acc_phase ^ 1, abort)) { ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(&bar->full[stage], phase, abort)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sa = tc::smem_u32(smem + stage * STAGE_BYTES), sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da = tc::smem_desc_sw128(sa + k * A_KSTEP, A_LBO, SBO);
+            uint64_t db = tc::smem_desc_sw128(sb + k * B_KSTEP, B_LBO, SBO);
+            tc::mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          tc::mma_commit_pair(&bar->empty[stage], 3);       // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc::mma_commit_pair(&bar->tmem_full[acc], 3);       // accumulator ready in both CTAs
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok && atomicExch(const_cast<uint32_t*>(&bar->abort), 1u) == 0) dev::report(status, ST_TIMEOUT, blockIdx.x, 1, 0);
+      tc::mma_commit_pair(&bar->drain, 1);
+      for (uint32_t i = 0; i < (1u << 20) && !tc::mbar_try_wait(&bar->drain, 0); ++i) {}
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps, both CTAs)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    TileCoord t;
+    for (int it = 0; ok && sched.get(it, &t); ++it) {
+      if (!tc::mbar_wait(&bar->tmem_full[acc], acc_phase, abort)) { ok = false; break; }
+      tc::tc_fence_after();
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      epi.tile_begin(t);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(taddr + c * 32, r);
+        tc::tmem_ld_wait();
+        epi.strip(t, quarter * 32 + lane, c * 32, r);
+      }
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive_cluster(tc::mapa(tc::smem_u32(&bar->tmem_empty[acc]), 0));   // on the leader's barrier
+      epi.tile_done(t, abort);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok && lane == 0 && atomicExch(const_cast<uint32_t*>(&bar->abort), 1u) == 0) dev::report(status, ST_TIMEOUT, blockIdx.x, 2, 0);
+  }
+
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::cluster_sync();                 // the leader's MMAs no longer read the peer's shared memory
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc_pair(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm2
+}  // namespace pccl

@@ -10,6 +10,7 @@
 #include "gemm_api.h"
 #include "gemm_epilogue.cuh"
 #include "gemm_pipeline.cuh"
+#include "gemm_pipeline2.cuh"
 #include "tensormap.h"
 
 namespace pccl {
@@ -27,7 +28,58 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   run<A_MN, B_MN>(&tmA, &tmB, K, sched, gate, epi, status);
 }
 
+// ---- CTA-pair kernel ---------------------------------------------------------------------------------
+struct PairEpi {
+  StoreEpi base;
+  int cta;
+  __device__ __forceinline__ TileCoord mine(const TileCoord& t) const { return TileCoord{t.m * 2 + cta, t.n, t.extra}; }
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return (t.m * 2 + cta) * gemm2::BM; }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * gemm2::BN + cta * gemm2::HALF_N; }
+  __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
+  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
+    base.strip(mine(t), row_in_tile, col_in_tile, r);
+  }
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, StoreEpi epi, int K,
+                      uint32_t* status) {
+  GroupedSched sched{(epi.M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.N + gemm2::BN - 1) / gemm2::BN,
+                     static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
+  NoGate gate;
+  PairEpi pe{epi, static_cast<int>(tc::cluster_ctarank())};
+  gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, gate, pe, status);
+}
+
 thread_local std::string g_err;
+
+template <bool A_MN, bool B_MN>
+int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreEpi& epi, int K, int grid, uint32_t* status, cudaStream_t stream) {
+  static bool attr_set = false;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(gemm2::NUM_THREADS);
+  cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int Kc = K;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, tb, epi, Kc, status));
+}
 
 template <bool A_MN, bool B_MN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreEpi& epi, int K, int grid, uint32_t* status, cudaStream_t stream) {
@@ -65,6 +117,20 @@ int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, in
   if (!b_mn ? !makeTensorMap2D(&tb, B, TM_BF16, K, N, ldb, BK, BN, &g_err) : !makeTensorMap2D(&tb, B, TM_BF16, N, K, ldb, 64, BK, &g_err))
     return static_cast<int>(cudaErrorInvalidValue);
   StoreEpi epi{D, D2, static_cast<const __nv_bfloat16*>(bias), ldd, M, N, flags};
+  if (flags & GEMM_PAIR) {
+    // per-CTA boxes: 128 rows of A and 128 rows (half of N) of B
+    CUtensorMap pa, pb;
+    if (!a_mn ? !makeTensorMap2D(&pa, A, TM_BF16, K, M, lda, BK, 128, &g_err) : !makeTensorMap2D(&pa, A, TM_BF16, M, K, lda, 64, BK, &g_err))
+      return static_cast<int>(cudaErrorInvalidValue);
+    if (!b_mn ? !makeTensorMap2D(&pb, B, TM_BF16, K, N, ldb, BK, 128, &g_err) : !makeTensorMap2D(&pb, B, TM_BF16, N, K, ldb, 64, BK, &g_err))
+      return static_cast<int>(cudaErrorInvalidValue);
+    int pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    int n_sm2 = deviceSmCount();
+    if (sms > 0 && sms < n_sm2) n_sm2 = sms;
+    int grid2 = 2 * (pair_tiles < n_sm2 / 2 ? pair_tiles : n_sm2 / 2);
+    if (a_mn) return b_mn ? launchPair<true, true>(pa, pb, epi, K, grid2, status, stream) : launchPair<true, false>(pa, pb, epi, K, grid2, status, stream);
+    return b_mn ? launchPair<false, true>(pa, pb, epi, K, grid2, status, stream) : launchPair<false, false>(pa, pb, epi, K, grid2, status, stream);
+  }
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int n_sm = deviceSmCount();
   if (sms > 0 && sms < n_sm) n_sm = sms;
