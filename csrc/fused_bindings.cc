@@ -106,7 +106,7 @@ void bindFused(py::module_& m) {
     A.spin_ns = kDefaultSpinLimit;
     A.flags = bias ? GEMM_BIAS : 0;
     A.r[0].D = reinterpret_cast<void*>(d); A.r[0].ldd = ldd; A.r[0].bias = reinterpret_cast<const void*>(bias);
-    A.r[0].ready = reinterpret_cast<uint32_t*>(ready); A.r[0].status = reinterpret_cast<uint32_t*>(status);
+    A.ready_off = ready; A.r[0].status = reinterpret_cast<uint32_t*>(status);
     A.r[0].rank = e.rank();
     AgGemmHost h{reinterpret_cast<const void*>(w), ldw, b_mn};
     check(launchAgGemm(A, &h, ctas, reinterpret_cast<cudaStream_t>(stream)), "ag_gemm");
@@ -130,9 +130,10 @@ void bindFused(py::module_& m) {
   // ---- single-GPU emulation of all ranks in one cooperative launch (tests) ------------------------
   m.def("emu_ag_gemm", [](const std::vector<uint64_t>& heaps, uint64_t flag_off, uint64_t x_off, int M, int N, int K,
                           const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& d, int64_t ldd,
-                          const std::vector<uint64_t>& ready, uint64_t epoch, int n_copy, int ctas,
+                          uint64_t ready_off, uint64_t epoch, int n_copy, int ctas,
                           const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream) {
     AgGemmArgs A{};
+    A.ready_off = ready_off;
     A.w = emuWorld2(heaps, flag_off);
     int n = A.w.world;
     A.nvirt = n;
@@ -141,7 +142,7 @@ void bindFused(py::module_& m) {
     std::vector<AgGemmHost> h(n);
     for (int r = 0; r < n; ++r) {
       A.r[r].D = reinterpret_cast<void*>(d.at(r)); A.r[r].ldd = ldd;
-      A.r[r].ready = reinterpret_cast<uint32_t*>(ready.at(r)); A.r[r].status = reinterpret_cast<uint32_t*>(status.at(r));
+      A.r[r].status = reinterpret_cast<uint32_t*>(status.at(r));
       A.r[r].rank = r;
       h[r] = AgGemmHost{reinterpret_cast<const void*>(w.at(r)), ldw, false};
     }

@@ -44,4 +44,5 @@ void bindGemm(py::module_& m) {
   m.attr("GEMM_ACCUMULATE") = static_cast<uint32_t>(GEMM_ACCUMULATE);
   m.attr("GEMM_GELU") = static_cast<uint32_t>(GEMM_GELU);
   m.attr("GEMM_BIAS") = static_cast<uint32_t>(GEMM_BIAS);
+  m.attr("GEMM_PAIR") = static_cast<uint32_t>(GEMM_PAIR);
 }

@@ -16,7 +16,6 @@ struct AgGemmRank {
   void* D;                    // [M, N] bf16 output (local)
   long long ldd;
   const void* bias;           // bf16 [N] or null
-  uint32_t* ready;            // local, zero-initialised once: one counter per 128-row chunk of the gathered X
   uint32_t* status;
   int rank;
   int pad;
@@ -28,6 +27,7 @@ struct AgGemmArgs {
   int M, N, K, M_local;       // M = M_local * world
   uint64_t x_off;             // heap offset of the symmetric gathered-X buffer [M, K] bf16; rows
                               // [rank*M_local, (rank+1)*M_local) hold the rank's own activations
+  uint64_t ready_off;         // heap offset of the symmetric chunk counters: uint32 [M / 128], zeroed once
   uint64_t epoch;             // 1, 2, 3, ... per launch on these buffers (chunk counters)
   uint64_t bar_epoch;         // strictly increasing per launch on `flag_lane` (peer barriers)
   int n_copy;                 // CTAs that pull peer rows (the rest compute)

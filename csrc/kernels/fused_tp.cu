@@ -1,12 +1,12 @@
 // Tensor/sequence-parallel MLP halves with the collective fused into the GEMM kernel, tile by tile.
 //
 //   all-gather -> GEMM   Y[M,N] = gather_rows(X)[M,K] * W1[N,K]^T.  Every rank keeps its own row
-//       block of X inside a symmetric [M,K] buffer.  A few CTAs of the kernel pull the peers' row
-//       blocks over NVLink with bulk async copies (peer global -> shared -> local global, ~190 KB in
-//       flight per CTA) in 128-row chunks and raise a local flag per chunk; the other CTAs run the
-//       tcgen05 pipeline, starting with the local rows and taking the remote panels in arrival
-//       order; a tile's TMA loads are issued once its chunk's flag is up.  TMA only ever reads
-//       local memory and nothing uses cluster multicast.
+//       block of X inside a symmetric [M,K] buffer.  A few CTAs of the kernel push the rank's rows
+//       into every peer's buffer over NVLink (posted 16-byte stores, peers served in the order in
+//       which they will consume the panel) in 128-row chunks and bump a counter per chunk on the
+//       receiver; the other CTAs run the tcgen05 pipeline, starting with the local rows and taking
+//       the remote panels in arrival order; a tile's TMA loads are issued once its chunk's counter
+//       is complete.  TMA only ever reads local memory and nothing uses cluster multicast.
 //   GEMM -> reduce-scatter   Z_r = sum over ranks of (Y*W2^T)[rows of r].  Tiles are computed owner
 //       by owner, the local owner last.  A tile owned by a peer is rounded to bf16, staged through
 //       shared memory and written into that peer's staging slot with bulk copies, followed by a
@@ -75,17 +75,17 @@ struct AgSched {
 };
 
 struct AgGate {
-  const uint32_t* ready;   // per 128-row chunk of the gathered X: pieces copied so far (never reset)
+  const uint32_t* ready;   // per 128-row chunk of the gathered X: parts written so far by the owner's copy CTAs (never reset)
   int me;
-  uint32_t target;         // epoch * pieces per chunk
+  uint32_t target;         // epoch * copy CTAs
   uint64_t spin_ns;
   __device__ __forceinline__ bool wait(const TileCoord& t, const volatile uint32_t* abort) const {
     if (t.extra == me) return true;
     const uint32_t* f = ready + t.m;
-    if (dev::ld_acquire_gpu_u32(f) < target) {
+    if (dev::ld_acquire_sys_u32(f) < target) {
       const uint64_t t0 = dev::global_timer_ns();
       for (uint32_t i = 1;; ++i) {
-        if (dev::ld_acquire_gpu_u32(f) >= target) break;
+        if (dev::ld_acquire_sys_u32(f) >= target) break;
         if ((i & 31) == 0) {
           if (*abort) return false;
           if (dev::global_timer_ns() - t0 > spin_ns) return false;
@@ -93,118 +93,62 @@ struct AgGate {
         }
       }
     }
-    tc::fence_proxy_async();   // the chunk was written through the async proxy of other CTAs; TMA reads it next
+    tc::fence_proxy_async();   // the chunk was written by a peer's ordinary stores; TMA (async proxy) reads it next
     return true;
   }
 };
 
-constexpr int kCopyPiece = 32 * 1024;
-constexpr int kCopyBufs = 6;
-
-// One thread per copy CTA drives a ring of bulk copies: peer global -> shared -> local global.
-__device__ void ag_copy_role(const AgGemmArgs& A, const AgGemmRank& R, uint8_t* smem) {
+// Copy CTAs push this rank's rows into every peer's gathered buffer with plain 16-byte stores
+// (posted writes: no round trip per request, a handful of CTAs fills the NVLink port).  Peers are
+// served in the order in which they need the panel -- rank me-1 consumes it first, then me-2, ... --
+// so at any moment each receiver is fed by one sender.  A 128-row chunk is split across the copy
+// CTAs; each adds one to the receiver's counter for that chunk when its part has been written.
+__device__ void ag_push_role(const AgGemmArgs& A, const AgGemmRank& R) {
   const int me = R.rank, world = A.w.world, j = blockIdx.x;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kCopyBufs * kCopyPiece);
-  __shared__ uint32_t s_abort;
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    for (int b = 0; b < kCopyBufs; ++b) tc::mbar_init(&bars[b], 1);
-    tc::fence_barrier_init();
-  }
-  __syncthreads();
-  bool ok = cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 1, A.spin_ns, R.status);
-  if (ok && threadIdx.x == 0) {
-    const int chunks = A.M_local / BM;
-    const long long chunk_bytes = static_cast<long long>(BM) * A.K * 2;
-    const int pieces = static_cast<int>(chunk_bytes / kCopyPiece);      // host checks divisibility
-    // All pieces of all remote chunks form one list in the order the GEMM consumes them (panel
-    // me+1 first); CTA j takes pieces j, j+n_copy, ... so every chunk is pulled by all copy CTAs
-    // together and the first chunks are complete almost at once.
-    const long long all = static_cast<long long>(world - 1) * chunks * pieces;
-    const long long total = j < all ? (all - j + A.n_copy - 1) / A.n_copy : 0;
-    auto locate = [&](long long q, const char** src, char** dst, int* m_tile) {
-      const long long g = j + q * A.n_copy;
-      const int it = static_cast<int>(g / pieces), pc = static_cast<int>(g % pieces);
-      const int panel = 1 + it / chunks, c = it % chunks;
-      int s = me + panel;
-      if (s >= world) s -= world;
-      const long long off = static_cast<long long>(A.x_off) +
-                            (static_cast<long long>(s) * A.M_local + static_cast<long long>(c) * BM) * A.K * 2 +
-                            static_cast<long long>(pc) * kCopyPiece;
-      *src = A.w.heap[s] + off;
-      *dst = A.w.heap[me] + off;
-      *m_tile = s * chunks + c;
-    };
-    auto signal_piece = [&](long long q) {
-      const char* s; char* d; int mt;
-      locate(q, &s, &d, &mt);
-      tc::fence_proxy_async();
-      __threadfence();
-      asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(R.ready + mt) : "memory");
-    };
-    long long issued = 0;
-    uint32_t phase_bits = 0;     // wait parity per buffer
-    for (; issued < total && issued < kCopyBufs; ++issued) {
-      const char* s; char* d; int mt;
-      locate(issued, &s, &d, &mt);
-      tc::mbar_arrive_expect_tx(&bars[issued], kCopyPiece);
-      tc::bulk_load_g2s(smem + issued * kCopyPiece, s, kCopyPiece, &bars[issued]);
-    }
-    long long done = 0;          // pieces whose store has been issued
-    for (long long q = 0; q < total; ++q) {
-      const int b = static_cast<int>(q % kCopyBufs);
-      const char* s; char* d; int mt;
-      locate(q, &s, &d, &mt);
-      if (!tc::mbar_wait(&bars[b], (phase_bits >> b) & 1, &s_abort)) {
-        dev::report(R.status, ST_TIMEOUT, j, 3, static_cast<uint32_t>(q));
-        ok = false;
-        break;
+  if (!cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 1, A.spin_ns, R.status)) return;
+  const int chunks = A.M_local / BM;
+  const long long chunk_bytes = static_cast<long long>(BM) * A.K * 2;
+  const long long nvec = chunk_bytes >> 4;
+  const long long per = (nvec + A.n_copy - 1) / A.n_copy;
+  const long long lo = min(nvec, per * j), hi = min(nvec, per * (j + 1));
+  const int nt = blockDim.x;
+  for (int k = 1; k < world; ++k) {
+    int p = me - k;
+    if (p < 0) p += world;
+    for (int c = 0; c < chunks; ++c) {
+      const long long off = static_cast<long long>(A.x_off) + (static_cast<long long>(me) * A.M_local + static_cast<long long>(c) * BM) * A.K * 2;
+      const char* src = A.w.heap[me] + off;
+      char* dst = A.w.heap[p] + off;
+      long long i = lo + threadIdx.x;
+      for (; i + 3 * nt < hi; i += 4 * nt) {
+        dev::Vec16 v0 = dev::ld16(src + (i << 4)), v1 = dev::ld16(src + ((i + nt) << 4));
+        dev::Vec16 v2 = dev::ld16(src + ((i + 2 * nt) << 4)), v3 = dev::ld16(src + ((i + 3 * nt) << 4));
+        dev::st16(dst + (i << 4), v0);
+        dev::st16(dst + ((i + nt) << 4), v1);
+        dev::st16(dst + ((i + 2 * nt) << 4), v2);
+        dev::st16(dst + ((i + 3 * nt) << 4), v3);
       }
-      phase_bits ^= 1u << b;
-      tc::fence_proxy_async_smem();
-      tc::bulk_store_s2g(d, smem + b * kCopyPiece, kCopyPiece);
-      tc::bulk_commit();
-      done = q + 1;
-      if (q >= 1) {
-        tc::bulk_wait<1>();            // the store of piece q-1 has landed in local memory
-        signal_piece(q - 1);
-        if (issued < total) {          // its buffer is free again
-          const int fb = static_cast<int>((q - 1) % kCopyBufs);
-          const char* s2; char* d2; int mt2;
-          locate(issued, &s2, &d2, &mt2);
-          tc::mbar_arrive_expect_tx(&bars[fb], kCopyPiece);
-          tc::bulk_load_g2s(smem + fb * kCopyPiece, s2, kCopyPiece, &bars[fb]);
-          ++issued;
-        }
-      }
-    }
-    tc::bulk_wait<0>();
-    if (done >= 1 && ok) signal_piece(done - 1);
-    if (!ok) {
-      // loads still in flight must land before this CTA's shared memory is released
-      for (long long q = done; q < issued; ++q) {
-        const int b = static_cast<int>(q % kCopyBufs);
-        for (uint32_t i = 0; i < (1u << 16) && !tc::mbar_try_wait(&bars[b], (phase_bits >> b) & 1); ++i) {}
+      for (; i < hi; i += nt) dev::st16(dst + (i << 4), dev::ld16(src + (i << 4)));
+      __syncthreads();                        // every thread's stores of this chunk part are issued
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        uint32_t* cnt = reinterpret_cast<uint32_t*>(A.w.heap[p] + A.ready_off) + (me * chunks + c);
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
       }
     }
   }
-  __syncthreads();
-  // peers may still be pulling our rows: nobody leaves (and lets the next kernel overwrite X) before all are done
-  cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 2, A.spin_ns, R.status);
 }
 
 template <bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgGemmArgs A) {
   const AgGemmRank& R = A.r[blockIdx.y];
   if (static_cast<int>(blockIdx.x) < A.n_copy) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    if (A.w.world > 1) ag_copy_role(A, R, smem);
+    if (A.w.world > 1) ag_push_role(A, R);
     return;
   }
   const int tiles_ml = A.M_local / BM, tiles_n = (A.N + BN - 1) / BN;
   AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy};
-  AgGate gate{R.ready, R.rank, static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>((static_cast<long long>(BM) * A.K * 2) / kCopyPiece), A.spin_ns};
+  AgGate gate{reinterpret_cast<const uint32_t*>(A.w.heap[R.rank] + A.ready_off), R.rank, static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>(A.n_copy), A.spin_ns};
   StoreEpi epi{R.D, nullptr, static_cast<const __nv_bfloat16*>(R.bias), R.ldd, A.M, A.N, A.flags};
   run<false, B_MN>(&R.tmA, &R.tmB, A.K, sched, gate, epi, R.status);
 }
@@ -333,8 +277,8 @@ const char* fusedLastError() { return g_err.c_str(); }
 int launchAgGemm(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_t stream) {
   const int nv = A.nvirt > 1 ? A.nvirt : 1;
   if (nv > kMaxVirt) { g_err = "ag_gemm: at most 4 emulated ranks"; return static_cast<int>(cudaErrorInvalidValue); }
-  if (A.M_local % BM || A.M != A.M_local * A.w.world || A.K % 8 || (static_cast<long long>(BM) * A.K * 2) % kCopyPiece) {
-    g_err = "ag_gemm: rows per rank must be a multiple of 128 and 128*K*2 a multiple of 32 KiB";
+  if (A.M_local % BM || A.M != A.M_local * A.w.world || A.K % 8) {
+    g_err = "ag_gemm: rows per rank must be a multiple of 128 and K a multiple of 8";
     return static_cast<int>(cudaErrorInvalidValue);
   }
   for (int v = 0; v < nv; ++v) {

@@ -21,13 +21,15 @@ class AllGatherGemm:
     (the backward pass of a column-parallel layer needs them for the weight gradient)."""
 
     def __init__(self, eng: Engine, rows_total: int, k: int, n_copy: int = 16, ctas: Optional[int] = None, flag_lane: int = 4):
-        if rows_total % (128 * eng.world) or (128 * k * 2) % (32 * 1024):
-            raise ValueError("AllGatherGemm: rows per rank must be a multiple of 128 and 128*K*2 bytes a multiple of 32 KiB")
+        if rows_total % (128 * eng.world) or k % 8:
+            raise ValueError("AllGatherGemm: rows per rank must be a multiple of 128 and K a multiple of 8")
         self.eng, self.M, self.K = eng, rows_total, k
         self.x_full = eng.symmetric_tensor((rows_total, k), torch.bfloat16)
         m_local = rows_total // eng.world
         self.x_local = self.x_full[eng.rank * m_local:(eng.rank + 1) * m_local]
-        self.ready = torch.zeros(rows_total // 128, dtype=torch.int32, device="cuda")
+        self.ready = eng.symmetric_tensor((rows_total // 128,), torch.int32)     # peers bump these counters
+        self.ready.zero_()
+        torch.cuda.synchronize()
         self.epoch = 0
         self.n_copy = n_copy if eng.world > 1 else 0
         self.ctas = ctas or C.sm_count()
@@ -43,7 +45,7 @@ class AllGatherGemm:
             out = torch.empty((self.M, n), dtype=torch.bfloat16, device="cuda")
         self.epoch += 1
         C.ag_gemm(self.eng.raw, self.eng.heap_offset(self.x_full), self.M, n, self.K, w.data_ptr(), w.stride(0), out.data_ptr(),
-                  out.stride(0), bias.data_ptr() if bias is not None else 0, self.ready.data_ptr(), self.epoch, self.n_copy,
+                  out.stride(0), bias.data_ptr() if bias is not None else 0, self.eng.heap_offset(self.ready), self.epoch, self.n_copy,
                   self.ctas, self.flag_lane, status_words().data_ptr(), torch.cuda.current_stream().cuda_stream, w_t)
         count_launch()
         return out

@@ -12,6 +12,9 @@ import torch
 
 from .._native import C
 
+import os
+
+_PAIR_DEFAULT = os.environ.get("PCCL_GEMM_PAIR", "0") == "1"
 _status: Dict[int, torch.Tensor] = {}
 _launches = 0
 
@@ -53,10 +56,11 @@ def _check(t: torch.Tensor, name: str) -> None:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          bias: Optional[torch.Tensor] = None, gelu_out: Optional[torch.Tensor] = None,
-         accumulate: bool = False, sms: int = 0) -> torch.Tensor:
+         accumulate: bool = False, sms: int = 0, pair: Optional[bool] = None) -> torch.Tensor:
     """``out = op(a) @ op(b)`` with ``op(a) = a.T if a_t else a`` (a: [M,K] or [K,M]) and
     ``op(b) = b if b_t else b.T`` (b: [N,K], or [K,N] when ``b_t``).  So the default is the linear
-    layer form ``a @ b.T``.  ``bias`` (bf16 [N]) is added; ``gelu_out`` receives gelu_tanh(out)."""
+    layer form ``a @ b.T``.  ``bias`` (bf16 [N]) is added; ``gelu_out`` receives gelu_tanh(out).
+    ``pair`` selects the CTA-pair kernel (cta_group::2, 256 x 256 tiles); default from PCCL_GEMM_PAIR."""
     _check(a, "a")
     _check(b, "b")
     M, K = (a.shape[1], a.shape[0]) if a_t else (a.shape[0], a.shape[1])
@@ -78,6 +82,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         flags |= C.GEMM_OUT_F32
     if accumulate:
         flags |= C.GEMM_ACCUMULATE
+    if _PAIR_DEFAULT if pair is None else pair:
+        flags |= C.GEMM_PAIR
     bias_ptr = 0
     if bias is not None:
         if bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous():
@@ -120,6 +126,7 @@ if __name__ == "__main__":      # python -m pccl_b200.ops.gemm --m 4096 --n 4096
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--a-t", action="store_true")
     ap.add_argument("--b-t", action="store_true")
+    ap.add_argument("--pair", action="store_true")
     a_ = ap.parse_args()
     A = torch.randn((a_.k, a_.m) if a_.a_t else (a_.m, a_.k), device="cuda").bfloat16()
     B = torch.randn((a_.k, a_.n) if a_.b_t else (a_.n, a_.k), device="cuda").bfloat16()
@@ -128,7 +135,7 @@ if __name__ == "__main__":      # python -m pccl_b200.ops.gemm --m 4096 --n 4096
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(a_.iters + 1)]
     ev[0].record()
     for i in range(a_.iters):
-        gemm(A, B, a_t=a_.a_t, b_t=a_.b_t, out=D)
+        gemm(A, B, a_t=a_.a_t, b_t=a_.b_t, out=D, pair=a_.pair)
         ev[i + 1].record()
     torch.cuda.synchronize()
     check_status("gemm")

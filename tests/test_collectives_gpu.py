@@ -179,9 +179,9 @@ def test_ag_gemm_emulated(native, world):
     xs = [(torch.randn(M_local, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
     ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16() for _ in range(world)]
     x_off = DATA_OFF
-    heaps = [torch.zeros(DATA_OFF + M * K * 2, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ready_off = DATA_OFF + M * K * 2
+    heaps = [torch.zeros(ready_off + 4096, dtype=torch.uint8, device="cuda") for _ in range(world)]
     st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
-    ready = [torch.zeros(M // 128, dtype=torch.int32, device="cuda") for _ in range(world)]
     outs = [torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
     ctas = 148 // world
     for epoch in (1, 2):
@@ -190,7 +190,7 @@ def test_ag_gemm_emulated(native, world):
             full.zero_()
             full[r * M_local:(r + 1) * M_local] = xs[r] * epoch
         native.emu_ag_gemm([h.data_ptr() for h in heaps], FLAG_OFF, x_off, M, N, K, [w.data_ptr() for w in ws], K,
-                           [o.data_ptr() for o in outs], N, [t.data_ptr() for t in ready], epoch, 4, ctas,
+                           [o.data_ptr() for o in outs], N, ready_off, epoch, 4, ctas,
                            [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
         assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]

@@ -63,3 +63,19 @@ def test_gemm_padded_leading_dimension():
     wp.copy_(w)
     y = gemm(out, wp)
     assert (y.float() - out.float() @ w.float().t()).abs().max().item() < 1.0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 512), (1000, 520, 200), (72, 40, 136), (2048, 1024, 1024)])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, True), (True, False)])
+def test_cta_pair_gemm_matches_fp32_reference(M, N, K, a_t, b_t):
+    """cta_group::2 kernel: two CTAs per 256 x 256 tile."""
+    from pccl_b200.ops import gemm, check_status
+    a = _rand((K, M) if a_t else (M, K), 11)
+    b = _rand((K, N) if b_t else (N, K), 12)
+    out32 = gemm(a, b, a_t=a_t, b_t=b_t, out_dtype=torch.float32, pair=True)
+    check_status("pair gemm")
+    ref = _ref(a, b, a_t, b_t)
+    assert (out32 - ref).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item())
+    bias = _rand((N,), 13)
+    out = gemm(a, b, a_t=a_t, b_t=b_t, bias=bias, pair=True)
+    assert (out.float() - (ref + bias.float())).abs().max().item() <= 0.02 * max(1.0, ref.abs().max().item())
