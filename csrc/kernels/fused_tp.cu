@@ -23,6 +23,7 @@
 #include "fused_api.h"
 #include "gemm_epilogue.cuh"
 #include "gemm_pipeline.cuh"
+#include "gemm_pipeline2.cuh"
 #include "tensormap.h"
 
 namespace pccl {
@@ -139,14 +140,26 @@ __device__ void ag_push_role(const AgGemmArgs& A, const AgGemmRank& R) {
   }
 }
 
-template <bool B_MN>
+template <bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgGemmArgs A) {
   const AgGemmRank& R = A.r[blockIdx.y];
-  if (static_cast<int>(blockIdx.x) < A.n_copy) {
+  if (static_cast<int>(blockIdx.x) < A.n_copy) {      // n_copy is even with PAIR: whole clusters copy
     if (A.w.world > 1) ag_push_role(A, R);
     return;
   }
   const int tiles_ml = A.M_local / BM, tiles_n = (A.N + BN - 1) / BN;
+  if constexpr (PAIR) {
+    AgSched sched{R.rank, A.w.world, tiles_ml / 2, tiles_n, (static_cast<int>(blockIdx.x) - A.n_copy) >> 1,
+                  (static_cast<int>(gridDim.x) - A.n_copy) >> 1};
+    AgGate gate{reinterpret_cast<const uint32_t*>(A.w.heap[R.rank] + A.ready_off), R.rank,
+                static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>(A.n_copy), A.spin_ns};
+    StoreEpi epi{R.D, nullptr, static_cast<const __nv_bfloat16*>(R.bias), R.ldd, A.M, A.N, A.flags};
+    const int cta = static_cast<int>(tc::cluster_ctarank());
+    gemm2::PairEpi<StoreEpi> pe{epi, cta};
+    gemm2::PairGate<AgGate> pg{gate, cta};
+    gemm2::run<false, B_MN>(&R.tmA, &R.tmB, A.K, sched, pg, pe, R.status);
+    return;
+  }
   AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy};
   AgGate gate{reinterpret_cast<const uint32_t*>(A.w.heap[R.rank] + A.ready_off), R.rank, static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>(A.n_copy), A.spin_ns};
   StoreEpi epi{R.D, nullptr, static_cast<const __nv_bfloat16*>(R.bias), R.ldd, A.M, A.N, A.flags};
@@ -258,10 +271,20 @@ struct RsEpi {
   }
 };
 
-template <bool B_MN>
+template <bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_constant__ GemmRsArgs A) {
   const GemmRsRank& R = A.r[blockIdx.y];
   const int tiles_ml = A.M_local / BM, tiles_n = A.N / BN;
+  if constexpr (PAIR) {
+    RsSched sched{R.rank, A.w.world, tiles_ml / 2, tiles_n, static_cast<int>(blockIdx.x) >> 1, static_cast<int>(gridDim.x) >> 1};
+    NoGate gate;
+    RsEpi epi{&A, &R, nullptr, R.rank, tiles_ml, tiles_n};
+    const int cta = static_cast<int>(tc::cluster_ctarank());
+    gemm2::PairEpi<RsEpi> pe{epi, cta};
+    gemm2::PairGate<NoGate> pg{gate, cta};
+    gemm2::run<false, B_MN>(&R.tmA, &R.tmB, A.K, sched, pg, pe, R.status);
+    return;
+  }
   RsSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
   NoGate gate;
   RsEpi epi{&A, &R, nullptr, R.rank, tiles_ml, tiles_n};
@@ -292,16 +315,29 @@ int launchAgGemm(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_t s
   }
   if (A.w.world == 1) A.n_copy = 0;
   if (ctas <= A.n_copy) { g_err = "ag_gemm: need more CTAs than copy CTAs"; return static_cast<int>(cudaErrorInvalidValue); }
-  void* kern = host[0].b_mn ? reinterpret_cast<void*>(ag_gemm_kernel<true>) : reinterpret_cast<void*>(ag_gemm_kernel<false>);
-  static bool set[2] = {false, false};
-  if (!set[host[0].b_mn]) {
+  const bool pair = A.M_local % 256 == 0 && ctas % 2 == 0;
+  if (pair && (A.n_copy & 1)) A.n_copy += 1;
+  // per-CTA TMA boxes: 128 rows of A; 256 rows of B (single CTA) or 128 (pair)
+  if (pair) {
+    for (int v = 0; v < nv; ++v) {
+      const bool okB = host[v].b_mn ? true : makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, 128, &g_err);
+      if (!okB) return static_cast<int>(cudaErrorInvalidValue);
+    }
+  }
+  dim3 grid(ctas, nv);
+  const int which = (host[0].b_mn ? 1 : 0) + (pair ? 2 : 0);
+  static bool set[4] = {false, false, false, false};
+  auto k00 = ag_gemm_kernel<false, false>; auto k10 = ag_gemm_kernel<true, false>;
+  auto k01 = ag_gemm_kernel<false, true>;  auto k11 = ag_gemm_kernel<true, true>;
+  auto kern = which == 0 ? k00 : which == 1 ? k10 : which == 2 ? k01 : k11;
+  if (!set[which]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    set[host[0].b_mn] = true;
+    set[which] = true;
   }
-  dim3 grid(ctas, nv), block(NUM_THREADS);
+  if (pair) return static_cast<int>(gemm2::launch_pairs(kern, grid, NUM_THREADS, SMEM_BYTES, stream, true, A));
   void* args[] = {&A};
-  return static_cast<int>(cudaLaunchCooperativeKernel(kern, grid, block, args, SMEM_BYTES, stream));
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), grid, dim3(NUM_THREADS), args, SMEM_BYTES, stream));
 }
 
 int launchGemmRs(GemmRsArgs& A, const GemmRsHost* host, int ctas, cudaStream_t stream) {
@@ -318,16 +354,27 @@ int launchGemmRs(GemmRsArgs& A, const GemmRsHost* host, int ctas, cudaStream_t s
                                   : makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, BN, &g_err);
     if (!okB) return static_cast<int>(cudaErrorInvalidValue);
   }
-  void* kern = host[0].b_mn ? reinterpret_cast<void*>(gemm_rs_kernel<true>) : reinterpret_cast<void*>(gemm_rs_kernel<false>);
-  static bool set[2] = {false, false};
-  if (!set[host[0].b_mn]) {
+  const bool pair = A.M_local % 256 == 0 && ctas % 2 == 0;
+  if (pair) {
+    for (int v = 0; v < nv; ++v) {
+      const bool okB = host[v].b_mn ? true : makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_BF16, A.K, A.N, host[v].ldw, BK, 128, &g_err);
+      if (!okB) return static_cast<int>(cudaErrorInvalidValue);
+    }
+  }
+  dim3 grid(ctas, nv);
+  const int which = (host[0].b_mn ? 1 : 0) + (pair ? 2 : 0);
+  static bool set[4] = {false, false, false, false};
+  auto k00 = gemm_rs_kernel<false, false>; auto k10 = gemm_rs_kernel<true, false>;
+  auto k01 = gemm_rs_kernel<false, true>;  auto k11 = gemm_rs_kernel<true, true>;
+  auto kern = which == 0 ? k00 : which == 1 ? k10 : which == 2 ? k01 : k11;
+  if (!set[which]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RS_SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    set[host[0].b_mn] = true;
+    set[which] = true;
   }
-  dim3 grid(ctas, nv), block(NUM_THREADS);
+  if (pair) return static_cast<int>(gemm2::launch_pairs(kern, grid, NUM_THREADS, RS_SMEM_BYTES, stream, true, A));
   void* args[] = {&A};
-  return static_cast<int>(cudaLaunchCooperativeKernel(kern, grid, block, args, RS_SMEM_BYTES, stream));
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), grid, dim3(NUM_THREADS), args, RS_SMEM_BYTES, stream));
 }
 
 }  // namespace pccl

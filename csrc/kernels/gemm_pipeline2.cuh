@@ -10,6 +10,8 @@
 // and "accumulator ready" arrivals to both CTAs.  Same hooks (Sched / Gate / Epi) and the same bounded
 // waits as gemm_pipeline.cuh; every thread of both CTAs reaches the closing cluster barrier.
 #pragma once
+#include <utility>
+
 #include "gemm_pipeline.cuh"
 
 namespace pccl {
@@ -181,6 +183,51 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
     tc::tc_fence_after();
     tc::tmem_dealloc_pair(tmem, TMEM_COLS);
   }
+}
+
+// Adapters that let epilogues and gates written for 128-row tiles serve a CTA pair: the CTA with
+// cluster rank c handles 128-row tile 2*m + c of pair tile m and loads rows [c*128, c*128+128) of the
+// pair's 256 B rows.
+__device__ __forceinline__ TileCoord half_tile(const TileCoord& t, int cta) { return TileCoord{t.m * 2 + cta, t.n, t.extra}; }
+
+template <class Epi>
+struct PairEpi {
+  Epi& e;
+  int cta;
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return e.a_row0(half_tile(t, cta)); }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return e.b_row0(half_tile(t, cta)) + cta * HALF_N; }
+  __device__ __forceinline__ void attach_smem(uint8_t* p) { e.attach_smem(p); }
+  __device__ __forceinline__ void tile_begin(const TileCoord& t) { e.tile_begin(half_tile(t, cta)); }
+  __device__ __forceinline__ void tile_done(const TileCoord& t, const volatile uint32_t* abort) { e.tile_done(half_tile(t, cta), abort); }
+  __device__ __forceinline__ void strip(const TileCoord& t, int row, int col, uint32_t* r) { e.strip(half_tile(t, cta), row, col, r); }
+};
+
+template <class Gate>
+struct PairGate {
+  const Gate& g;
+  int cta;
+  __device__ __forceinline__ bool wait(const TileCoord& t, const volatile uint32_t* abort) const { return g.wait(half_tile(t, cta), abort); }
+};
+
+// Launch helper: cluster of two CTAs along x, optionally cooperative (kernels whose CTAs wait on one another).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pairs(void (*kernel)(KArgs...), dim3 grid, int threads, size_t smem, cudaStream_t stream, bool cooperative,
+                                Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeCooperative;
+  at[1].val.cooperative = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = cooperative ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 }  // namespace gemm2

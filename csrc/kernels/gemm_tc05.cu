@@ -29,20 +29,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ---- CTA-pair kernel ---------------------------------------------------------------------------------
-struct PairEpi {
-  StoreEpi base;
-  int cta;
-  __device__ __forceinline__ TileCoord mine(const TileCoord& t) const { return TileCoord{t.m * 2 + cta, t.n, t.extra}; }
-  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return (t.m * 2 + cta) * gemm2::BM; }
-  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * gemm2::BN + cta * gemm2::HALF_N; }
-  __device__ __forceinline__ void attach_smem(uint8_t*) {}
-  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
-  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
-  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
-    base.strip(mine(t), row_in_tile, col_in_tile, r);
-  }
-};
-
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, StoreEpi epi, int K,
@@ -50,8 +36,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   GroupedSched sched{(epi.M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.N + gemm2::BN - 1) / gemm2::BN,
                      static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
   NoGate gate;
-  PairEpi pe{epi, static_cast<int>(tc::cluster_ctarank())};
-  gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, gate, pe, status);
+  const int cta = static_cast<int>(tc::cluster_ctarank());
+  gemm2::PairEpi<StoreEpi> pe{epi, cta};
+  gemm2::PairGate<NoGate> pg{gate, cta};
+  gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, pg, pe, status);
 }
 
 thread_local std::string g_err;

@@ -15,6 +15,7 @@
 #include "gemm_api.h"
 #include "gemm_epilogue.cuh"
 #include "gemm_pipeline.cuh"
+#include "gemm_pipeline2.cuh"
 #include "moe_api.h"
 #include "prims.cuh"
 #include "tensormap.h"
@@ -244,14 +245,15 @@ using namespace gemm;
 struct GroupedSched {
   const int* row_off;    // groups + 1
   int groups, tiles_n, first, stride;
+  int tile_rows;         // 128 (single CTA) or 256 (CTA pair)
   // Tile `idx` of the concatenated per-group tile lists -> (group, m-tile inside group, n-tile).
   __device__ __forceinline__ bool get(int it, TileCoord* t) const {
     long long idx = first + static_cast<long long>(it) * stride;
     for (int g = 0; g < groups; ++g) {
       const int rows = row_off[g + 1] - row_off[g];
-      const long long tiles = static_cast<long long>((rows + BM - 1) / BM) * tiles_n;
+      const int tm = (rows + tile_rows - 1) / tile_rows;
+      const long long tiles = static_cast<long long>(tm) * tiles_n;
       if (idx < tiles) {
-        const int tm = (rows + BM - 1) / BM;
         t->m = static_cast<int>(idx % tm);
         t->n = static_cast<int>(idx / tm);
         t->extra = g;
@@ -300,9 +302,20 @@ struct GroupedEpi {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GroupedEpi epi, int groups, int K,
                     uint32_t* status) {
-  GroupedSched sched{epi.row_off, groups, (epi.N + BN - 1) / BN, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x)};
+  GroupedSched sched{epi.row_off, groups, (epi.N + BN - 1) / BN, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), BM};
   NoGate gate;
   run<false, false>(&tmA, &tmB, K, sched, gate, epi, status);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GroupedEpi epi, int groups, int K,
+                         uint32_t* status) {
+  GroupedSched sched{epi.row_off, groups, (epi.N + BN - 1) / BN, static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1), 2 * BM};
+  NoGate gate;
+  const int cta = static_cast<int>(tc::cluster_ctarank());
+  gemm2::PairEpi<GroupedEpi> pe{epi, cta};
+  gemm2::PairGate<NoGate> pg{gate, cta};
+  gemm2::run<false, false>(&tmA, &tmB, K, sched, pg, pe, status);
 }
 
 template <typename K>
@@ -351,6 +364,20 @@ int gemmGroupedBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void
   CUtensorMap ta, tb;
   std::string err;
   if (!makeTensorMap2D(&ta, A, TM_BF16, K, max_rows, lda, BK, BM, &err)) return static_cast<int>(cudaErrorInvalidValue);
+  int n_sm = deviceSmCount();
+  if (sms > 0 && sms < n_sm) n_sm = sms;
+  GroupedEpi epi{static_cast<__nv_bfloat16*>(D), ldd, row_off, N, flags};
+  if (N % 256 == 0 && n_sm >= 2) {       // CTA pairs: each CTA loads 128 of the 256 B rows of a tile
+    if (!makeTensorMap2D(&tb, B, TM_BF16, K, static_cast<uint64_t>(groups) * N, ldb, BK, 128, &err)) return static_cast<int>(cudaErrorInvalidValue);
+    static bool set2 = false;
+    if (!set2) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_grouped_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      set2 = true;
+    }
+    return static_cast<int>(gemm2::launch_pairs(gemm_grouped_pair_kernel, dim3(n_sm & ~1), NUM_THREADS, gemm2::SMEM_BYTES, stream, false, ta, tb,
+                                                epi, groups, K, status));
+  }
   if (!makeTensorMap2D(&tb, B, TM_BF16, K, static_cast<uint64_t>(groups) * N, ldb, BK, BN, &err)) return static_cast<int>(cudaErrorInvalidValue);
   static bool set = false;
   if (!set) {
@@ -358,9 +385,6 @@ int gemmGroupedBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void
     if (e != cudaSuccess) return static_cast<int>(e);
     set = true;
   }
-  int n_sm = deviceSmCount();
-  if (sms > 0 && sms < n_sm) n_sm = sms;
-  GroupedEpi epi{static_cast<__nv_bfloat16*>(D), ldd, row_off, N, flags};
   gemm_grouped_kernel<<<n_sm, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, epi, groups, K, status);
   return static_cast<int>(cudaGetLastError());
 }

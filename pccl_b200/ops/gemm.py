@@ -14,7 +14,7 @@ from .._native import C
 
 import os
 
-_PAIR_DEFAULT = os.environ.get("PCCL_GEMM_PAIR", "0") == "1"
+_PAIR_DEFAULT = os.environ.get("PCCL_GEMM_PAIR", "1") != "0"      # CTA pairs unless switched off
 _status: Dict[int, torch.Tensor] = {}
 _launches = 0
 
@@ -82,7 +82,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         flags |= C.GEMM_OUT_F32
     if accumulate:
         flags |= C.GEMM_ACCUMULATE
-    if _PAIR_DEFAULT if pair is None else pair:
+    if (_PAIR_DEFAULT and M > 128) if pair is None else pair:
         flags |= C.GEMM_PAIR
     bias_ptr = 0
     if bias is not None:

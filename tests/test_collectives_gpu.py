@@ -202,9 +202,9 @@ def test_ag_gemm_emulated(native, world):
             assert torch.equal(gathered.float(), X)
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_gemm_rs_emulated(native, world):
-    M_local, K, N = 128, 448, 512
+@pytest.mark.parametrize("world,M_local", [(2, 128), (2, 256), (4, 128)])
+def test_gemm_rs_emulated(native, world, M_local):
+    K, N = 448, 512     # 256 rows per rank and an even CTA count take the CTA-pair pipeline
     M = M_local * world
     g = torch.Generator(device="cuda").manual_seed(10)
     ys = [(torch.randn(M, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
