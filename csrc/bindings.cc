@@ -7,6 +7,8 @@
 
 #include <cuda_runtime.h>
 
+#include <cmath>
+
 #include "base/registry.h"
 #include "common/clock.h"
 #include "common/env.h"
@@ -230,6 +232,20 @@ PYBIND11_MODULE(_C, m) {
         py::arg("redop"), py::arg("in_off"), py::arg("out_off"), py::arg("count"), py::arg("flag_lane") = 0,
         py::arg("scale") = 1.0f, py::arg("out_dtype") = "", py::arg("blocks") = 32, py::arg("threads") = 512,
         py::arg("stream") = 0, py::arg("local_in") = 0, py::arg("local_out") = 0, py::arg("spin_limit") = 0);
+  m.def("reduce_scatter_adamw", [](Engine& e, const std::string& algo, uint64_t in_off, uint64_t count, int flag_lane, float scale,
+                                   uint64_t p, uint64_t mm, uint64_t v, uint64_t p_bf16, float lr, float b1, float b2, float eps,
+                                   float wd, int step, int blocks, int threads, uint64_t stream) {
+    CollArgs a = makeCollArgs(e.worldTable(), 1, e.rank(), algo, "bf16", "sum", in_off, 0, count, e.nextEpoch(flag_lane), flag_lane,
+                              scale, "", 0);
+    a.status[0] = reinterpret_cast<uint32_t*>(e.statusPtr(8 + flag_lane));
+    AdamArgs o{};
+    o.p = reinterpret_cast<float*>(p); o.m = reinterpret_cast<float*>(mm); o.v = reinterpret_cast<float*>(v);
+    o.p_bf16 = reinterpret_cast<void*>(p_bf16);
+    o.lr = lr; o.b1 = b1; o.b2 = b2; o.eps = eps; o.wd = wd;
+    o.inv_bc1 = 1.0f / (1.0f - std::pow(b1, static_cast<float>(step)));
+    o.inv_sqrt_bc2 = 1.0f / std::sqrt(1.0f - std::pow(b2, static_cast<float>(step)));
+    throwIfCuda(launchReduceScatterAdamW(a, o, blocks, threads, reinterpret_cast<cudaStream_t>(stream)), "reduce_scatter_adamw");
+  });
   m.def("emu_collective", &emuCollective);
   m.def("emu_program", &emuProgram);
   m.def("wait_timeout_probe", [](uint64_t flag, uint64_t spin_limit, uint64_t status, uint64_t stream) {

@@ -89,6 +89,15 @@ struct CollArgs {
 
 int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 int launchReduceScatter(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
+// Reduce-scatter of a bf16 gradient bucket fused with the sharded AdamW step: this rank's slice is
+// summed over the ranks (fp32), scaled, and consumed at once by the optimizer update of the fp32
+// master weights / moments; the new parameters are written as bf16.  No gradient shard is ever stored.
+struct AdamArgs {
+  float* p; float* m; float* v;   // fp32 shard state, `count` elements
+  void* p_bf16;                   // bf16 parameters of the shard (output)
+  float lr, b1, b2, eps, wd, inv_bc1, inv_sqrt_bc2;
+};
+int launchReduceScatterAdamW(const CollArgs& a, const AdamArgs& o, int blocks, int threads, cudaStream_t stream);
 int launchAllGather(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 int launchAllToAll(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 // Bounded-wait self test: waits on a flag nobody sets; must come back with ST_TIMEOUT.

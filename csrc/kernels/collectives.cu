@@ -334,6 +334,43 @@ __global__ void __launch_bounds__(1024) alltoall_kernel(const __grid_constant__ 
   peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
 }
 
+// ---------------------------------------------------------------------------------------------
+// reduce-scatter + AdamW (bf16 gradients; count % 8 == 0; shard 16-byte aligned)
+// ---------------------------------------------------------------------------------------------
+template <bool NVLS>
+__global__ void __launch_bounds__(512) reduce_scatter_adamw_kernel(const __grid_constant__ CollArgs A, const AdamArgs O) {
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = A.rank;
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const uint64_t nvec = (A.count * 2) >> 4;
+  const uint64_t base = A.in_off + static_cast<uint64_t>(me) * A.count * 2;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  const float scale = A.scale, one_m_b1 = 1.f - O.b1, one_m_b2 = 1.f - O.b2, decay = 1.f - O.lr * O.wd;
+  __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(O.p_bf16);
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float g[8];
+    if constexpr (NVLS) unpack<DT_BF16>(multimem_ld_reduce<DT_BF16, RED_SUM>(A.w.mc_heap + base + (i << 4)), g);
+    else pull_reduce<DT_BF16, RED_SUM>(A, me, base + (i << 4), g);
+    float P[8], M[8], V[8];
+    unpack<DT_F32>(ld16(O.p + i * 8), P); unpack<DT_F32>(ld16(O.p + i * 8 + 4), P + 4);
+    unpack<DT_F32>(ld16(O.m + i * 8), M); unpack<DT_F32>(ld16(O.m + i * 8 + 4), M + 4);
+    unpack<DT_F32>(ld16(O.v + i * 8), V); unpack<DT_F32>(ld16(O.v + i * 8 + 4), V + 4);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = g[k] * scale;
+      M[k] = O.b1 * M[k] + one_m_b1 * gk;
+      V[k] = O.b2 * V[k] + one_m_b2 * gk * gk;
+      P[k] = P[k] * decay - O.lr * (M[k] * O.inv_bc1) / (sqrtf(V[k]) * O.inv_sqrt_bc2 + O.eps);
+    }
+    st16(O.p + i * 8, pack<DT_F32>(P)); st16(O.p + i * 8 + 4, pack<DT_F32>(P + 4));
+    st16(O.m + i * 8, pack<DT_F32>(M)); st16(O.m + i * 8 + 4, pack<DT_F32>(M + 4));
+    st16(O.v + i * 8, pack<DT_F32>(V)); st16(O.v + i * 8 + 4, pack<DT_F32>(V + 4));
+    st16(pb + i * 8, pack<DT_BF16>(P));
+  }
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
 template <typename K>
 int launchCoop(K kernel, const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
   if (blocks < 1) blocks = 1;
@@ -386,6 +423,17 @@ int launchReduceScatter(const CollArgs& a, int blocks, int threads, cudaStream_t
   PCCL_DISPATCH_DT_OP(PCCL_RS)
 #undef PCCL_RS
   return static_cast<int>(cudaErrorNotSupported);
+}
+
+int launchReduceScatterAdamW(const CollArgs& a, const AdamArgs& o, int blocks, int threads, cudaStream_t stream) {
+  if (a.dtype != DT_BF16 || a.nvirt > 1 || a.count % 8 || a.flag_lane < 0 || a.flag_lane >= 8) return static_cast<int>(cudaErrorInvalidValue);
+  if (a.algo == ALGO_NVLS && !a.w.mc_heap) return static_cast<int>(cudaErrorInvalidValue);
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocksPerColl) blocks = kMaxBlocksPerColl;
+  void* args[] = {const_cast<CollArgs*>(&a), const_cast<AdamArgs*>(&o)};
+  void* kern = a.algo == ALGO_NVLS ? reinterpret_cast<void*>(reduce_scatter_adamw_kernel<true>)
+                                   : reinterpret_cast<void*>(reduce_scatter_adamw_kernel<false>);
+  return static_cast<int>(cudaLaunchCooperativeKernel(kern, dim3(blocks), dim3(threads), args, 0, stream));
 }
 
 int launchAllGather(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {

@@ -70,6 +70,24 @@ def reduce_scatter(eng: Engine, inp: torch.Tensor, out: torch.Tensor, op: str = 
     return out
 
 
+def reduce_scatter_adamw(eng: Engine, grads: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
+                         param_bf16: torch.Tensor, *, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
+                         step: int = 1, scale: float = 1.0, algo: str = "auto", blocks: Optional[int] = None, threads: int = 512,
+                         lane: int = 0, stream=None) -> None:
+    """Gradient-bucket reduce-scatter fused with the sharded AdamW step.  ``grads`` is the symmetric bf16
+    bucket (world * n elements); ``master`` / ``exp_avg`` / ``exp_avg_sq`` are this rank's fp32 slices (n
+    elements, n % 8 == 0); the updated parameters are written to ``param_bf16`` (bf16, n elements)."""
+    n = master.numel()
+    if grads.dtype != torch.bfloat16 or grads.numel() != n * eng.world or n % 8:
+        raise ValueError("reduce_scatter_adamw: bf16 bucket of world * n elements with n % 8 == 0 expected")
+    a = _algo(eng, algo, "bf16", "sum", n * 2)
+    s = (stream or torch.cuda.current_stream()).cuda_stream
+    C.reduce_scatter_adamw(eng.raw, a, eng.heap_offset(grads), n, lane, float(scale), master.data_ptr(), exp_avg.data_ptr(),
+                           exp_avg_sq.data_ptr(), param_bf16.data_ptr(), lr, betas[0], betas[1], eps, weight_decay, step,
+                           _blocks(n * 2, blocks), threads, s)
+    count_launch()
+
+
 def all_gather(eng: Engine, inp: torch.Tensor, out: torch.Tensor, algo: str = "auto", blocks: Optional[int] = None,
                threads: int = 512, lane: int = 0, stream=None) -> torch.Tensor:
     """``out`` (symmetric, world * inp.numel()) receives every rank's ``inp`` at its rank's slot."""

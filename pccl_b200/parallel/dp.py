@@ -48,10 +48,13 @@ class ShardedDataParallel:
 
     def __init__(self, model: nn.Module, engine: Optional[Engine] = None, *, lr: float = 3e-4, betas=(0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, bucket_mb: float = 25.0, heap_bytes: int = 0,
-                 comm_blocks: int = 16, algo: str = "auto", group=None):
+                 comm_blocks: int = 16, algo: str = "auto", group=None, fuse_optimizer: bool = True):
         self.model = model
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.comm_blocks, self.algo = comm_blocks, algo
+        # fused: the bucket's reduce-scatter kernel also performs the AdamW update of this rank's slice and
+        # the parameter all-gather follows at once, all while backward is still running
+        self.fuse_optimizer = fuse_optimizer
         params = []
         seen = set()
         for p in model.parameters():
@@ -154,11 +157,24 @@ class ShardedDataParallel:
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream())
         self.comm_stream.wait_event(ev)
-        coll.reduce_scatter(self.engine, b.grads, b.grad_shard, scale=1.0 / self.world, algo=self.algo,
-                            blocks=self.comm_blocks, lane=1, stream=self.comm_stream)
+        if not self.fuse_optimizer:
+            coll.reduce_scatter(self.engine, b.grads, b.grad_shard, scale=1.0 / self.world, algo=self.algo,
+                                blocks=self.comm_blocks, lane=1, stream=self.comm_stream)
+            return
+        shard = b.numel // self.world
+        dst = b.values[self.rank * shard:(self.rank + 1) * shard]
+        coll.reduce_scatter_adamw(self.engine, b.grads, b.master, b.exp_avg, b.exp_avg_sq, dst, lr=self.lr, betas=self.betas,
+                                  eps=self.eps, weight_decay=self.weight_decay if b.decay else 0.0, step=self.step_count,
+                                  scale=1.0 / self.world, algo=self.algo, blocks=self.comm_blocks, lane=1, stream=self.comm_stream)
+        if self.world > 1:
+            # every gradient of the bucket exists, so backward no longer reads these parameters on any rank
+            # that has reached this point; the all-gather's entry barrier waits for the others
+            coll.all_gather(self.engine, dst, b.values, algo=self.algo, blocks=self.comm_blocks, lane=2, stream=self.comm_stream)
 
     # ------------------------------------------------------------------------------------------
     def zero_grad(self) -> None:
+        if self.fuse_optimizer:
+            self.step_count += 1          # the optimizer runs inside backward: this is the step being taken
         for b in self.buckets:
             b.pending = len(b.params)
             for p in b.params:
@@ -167,7 +183,15 @@ class ShardedDataParallel:
                 p.grad = None
 
     def optimizer_step(self) -> None:
-        """Sharded AdamW + parameter all-gather, on the communication stream behind the reductions."""
+        """Sharded AdamW + parameter all-gather, on the communication stream behind the reductions.  In
+        fused mode both already ran bucket by bucket during backward; this only joins the streams."""
+        if self.fuse_optimizer:
+            for b in self.buckets:
+                if b.pending != 0:
+                    raise RuntimeError(f"bucket {b.index}: {b.pending} gradient(s) never arrived "
+                                       "(a parameter took no part in the loss)")
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            return
         self.step_count += 1
         with torch.cuda.stream(self.comm_stream):
             for b in self.buckets:
