@@ -38,6 +38,22 @@ void bindGemm(py::module_& m) {
                                  reinterpret_cast<cudaStream_t>(stream));
     if (err != 0) throw std::runtime_error(std::string("cross_entropy: ") + cudaErrorName(err));
   });
+  m.def("layernorm_fwd", [](uint64_t x, uint64_t g, uint64_t b, uint64_t y, uint64_t mean, uint64_t rstd, long long rows, int D, float eps,
+                            uint64_t stream) {
+    int err = launchLayerNormFwd(reinterpret_cast<const void*>(x), reinterpret_cast<const void*>(g), reinterpret_cast<const void*>(b),
+                                 reinterpret_cast<void*>(y), reinterpret_cast<float*>(mean), reinterpret_cast<float*>(rstd), rows, D, eps,
+                                 reinterpret_cast<cudaStream_t>(stream));
+    if (err != 0) throw std::runtime_error(std::string("layernorm_fwd: ") + cudaErrorName(err));
+  });
+  m.def("layernorm_bwd_parts", &layerNormBwdParts);
+  m.def("layernorm_bwd", [](uint64_t dy, uint64_t x, uint64_t g, uint64_t mean, uint64_t rstd, uint64_t dx, uint64_t dg, uint64_t db,
+                            uint64_t partials, long long rows, int D, uint64_t stream) {
+    int err = launchLayerNormBwd(reinterpret_cast<const void*>(dy), reinterpret_cast<const void*>(x), reinterpret_cast<const void*>(g),
+                                 reinterpret_cast<const float*>(mean), reinterpret_cast<const float*>(rstd), reinterpret_cast<void*>(dx),
+                                 reinterpret_cast<void*>(dg), reinterpret_cast<void*>(db), reinterpret_cast<float*>(partials), rows, D,
+                                 reinterpret_cast<cudaStream_t>(stream));
+    if (err != 0) throw std::runtime_error(std::string("layernorm_bwd: ") + cudaErrorName(err));
+  });
   m.attr("GEMM_A_MN") = static_cast<uint32_t>(GEMM_A_MN);
   m.attr("GEMM_B_MN") = static_cast<uint32_t>(GEMM_B_MN);
   m.attr("GEMM_OUT_F32") = static_cast<uint32_t>(GEMM_OUT_F32);

@@ -17,4 +17,12 @@ int launchAdamW(float* p, float* m, float* v, const float* g, void* p_bf16, long
 int launchCrossEntropy(void* logits, const long long* targets, float* loss, long long rows, int vocab, long long ld,
                        float grad_scale, long long ignore_index, cudaStream_t stream);
 
+// LayerNorm over the last dimension D (multiple of 8, <= 8192) of bf16 [rows, D]; mean / rstd are fp32 [rows].
+int launchLayerNormFwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, long long rows, int D,
+                       float eps, cudaStream_t stream);
+// Backward: dx bf16 [rows, D], dgamma / dbeta bf16 [D]; `partials` is fp32 scratch of 2 * layerNormBwdParts(rows) * D elements.
+int layerNormBwdParts(long long rows);
+int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx, void* dgamma,
+                       void* dbeta, float* partials, long long rows, int D, cudaStream_t stream);
+
 }  // namespace pccl

@@ -18,6 +18,7 @@ import torch.nn.functional as F
 
 from ..nn.linear import Embedding, Linear, LinearGelu, _LinearFn
 from ..nn.loss import fused_cross_entropy
+from ..nn.norm import LayerNorm
 
 
 @dataclass
@@ -57,10 +58,10 @@ class Block(nn.Module):
         super().__init__()
         d = cfg.d_model
         self.n_head = cfg.n_head
-        self.ln1 = nn.LayerNorm(d, device=device, dtype=torch.bfloat16)
+        self.ln1 = LayerNorm(d, device=device)
         self.qkv = Linear(d, 3 * d, device=device)
         self.proj = Linear(d, d, device=device, init_std=0.02 / math.sqrt(2 * cfg.n_layer))
-        self.ln2 = nn.LayerNorm(d, device=device, dtype=torch.bfloat16)
+        self.ln2 = LayerNorm(d, device=device)
         self.fc1 = LinearGelu(d, cfg.mlp_ratio * d, device=device)
         self.fc2 = Linear(cfg.mlp_ratio * d, d, device=device, init_std=0.02 / math.sqrt(2 * cfg.n_layer))
 
@@ -80,7 +81,7 @@ class GPT(nn.Module):
         self.wte = Embedding(cfg.vocab_size, cfg.d_model, device=device)
         self.wpe = Embedding(cfg.seq_len, cfg.d_model, device=device)
         self.blocks = nn.ModuleList(Block(cfg, device) for _ in range(cfg.n_layer))
-        self.ln_f = nn.LayerNorm(cfg.d_model, device=device, dtype=torch.bfloat16)
+        self.ln_f = LayerNorm(cfg.d_model, device=device)
         if cfg.tie_embeddings:
             self.wte.weight._pccl_uses = 2     # gradient arrives from the LM head and from the lookup
         else:

@@ -116,3 +116,26 @@ def test_fused_and_unfused_optimizer_paths_agree():
         del dp, model, eng
     assert (flats[0] - flats[1]).abs().max().item() <= 2e-2 * flats[1].abs().max().item()
     assert (flats[0] == flats[1]).float().mean().item() > 0.98      # identical except where bf16 rounding of the gradient path differs
+
+
+@pytest.mark.parametrize("rows,D", [(37, 256), (4096, 2048), (600, 4096), (130, 8192)])
+def test_layernorm_kernels_match_fp32_reference(rows, D):
+    from pccl_b200.nn import LayerNorm
+    torch.manual_seed(5)
+    ln = LayerNorm(D, device="cuda")
+    with torch.no_grad():
+        ln.weight.copy_((torch.randn(D, device="cuda") * 0.5 + 1).bfloat16())
+        ln.bias.copy_((torch.randn(D, device="cuda") * 0.1).bfloat16())
+    x = (torch.randn(rows, D, device="cuda") * 2 + 0.5).bfloat16().requires_grad_(True)
+    g = torch.randn(rows, D, device="cuda").bfloat16()
+    y = ln(x)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = ln.weight.detach().float().requires_grad_(True)
+    br = ln.bias.detach().float().requires_grad_(True)
+    yr = F.layer_norm(xr, (D,), wr, br, 1e-5)
+    yr.backward(g.float())
+    assert (y.float() - yr).abs().max().item() < 0.03
+    assert (x.grad.float() - xr.grad).abs().max().item() < 0.03 * max(1.0, xr.grad.abs().max().item())
+    assert (ln.weight.grad.float() - wr.grad).abs().max().item() < 0.02 * max(1.0, wr.grad.abs().max().item())
+    assert (ln.bias.grad.float() - br.grad).abs().max().item() < 0.02 * max(1.0, br.grad.abs().max().item())
