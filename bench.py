@@ -45,7 +45,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=int(os.environ.get("PCCL_BENCH_BATCH", "8")), help="sequences per GPU per step")
     ap.add_argument("--model", default="gpt-1.3b", choices=["gpt-1.3b", "tiny"])
     ap.add_argument("--bucket-mb", type=float, default=25.0)
-    ap.add_argument("--comm-blocks", type=int, default=16)
+    ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the gradient/optimizer kernels (0 = automatic)")
     ap.add_argument("--algo", default="auto", choices=["auto", "nvls", "p2p"])
     ap.add_argument("--no-micro", action="store_true", help="skip the collective micro-benchmarks at N > 1")
     args = ap.parse_args()

@@ -27,6 +27,22 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return r;
 }
 
+__device__ __forceinline__ void block_sum2(float a, float b, float* scratch, float* ra, float* rb) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) { scratch[warp] = a; scratch[8 + warp] = b; }
+  __syncthreads();
+  float x = 0.f, y = 0.f;
+  for (int w = 0; w < nw; ++w) { x += scratch[w]; y += scratch[8 + w]; }
+  *ra = x;
+  *rb = y;
+}
+
 template <int MAXV>
 __global__ void __launch_bounds__(256) ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                                                      const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
@@ -76,7 +92,7 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
                                                      const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean,
                                                      const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
                                                      float* __restrict__ part_g, float* __restrict__ part_b, long long rows, int D) {
-  __shared__ float scratch[8];
+  __shared__ float scratch[16];
   const int nvec = D >> 3;
   float g[MAXV][8], ag[MAXV][8], ab[MAXV][8];
 #pragma unroll
@@ -108,8 +124,10 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
         }
       }
     }
-    const float m1 = block_sum(s1, scratch) / D;
-    const float m2 = block_sum(s2, scratch) / D;
+    float m1, m2;
+    block_sum2(s1, s2, scratch, &m1, &m2);
+    m1 /= D;
+    m2 /= D;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int v = threadIdx.x + j * 256;
@@ -133,18 +151,28 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
   }
 }
 
+// 32 columns x 8 partial-row lanes per CTA: the partial rows are summed eight at a time in parallel
 __global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ part_g, const float* __restrict__ part_b,
                                                             __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta,
                                                             int nparts, int D) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
-  float sg = 0.f, sb = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    sg += part_g[static_cast<long long>(p) * D + c];
-    sb += part_b[static_cast<long long>(p) * D + c];
+  __shared__ float sg[8][33], sb[8][33];
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31), lane8 = threadIdx.x >> 5;
+  float g = 0.f, b = 0.f;
+  if (col < D) {
+    for (int p = lane8; p < nparts; p += 8) {
+      g += part_g[static_cast<long long>(p) * D + col];
+      b += part_b[static_cast<long long>(p) * D + col];
+    }
   }
-  dgamma[c] = __float2bfloat16_rn(sg);
-  dbeta[c] = __float2bfloat16_rn(sb);
+  sg[lane8][threadIdx.x & 31] = g;
+  sb[lane8][threadIdx.x & 31] = b;
+  __syncthreads();
+  if (lane8 == 0 && col < D) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) { g += sg[k][threadIdx.x]; b += sb[k][threadIdx.x]; }
+    dgamma[col] = __float2bfloat16_rn(g);
+    dbeta[col] = __float2bfloat16_rn(b);
+  }
 }
 
 }  // namespace
@@ -162,7 +190,7 @@ int launchLayerNormFwd(const void* x, const void* gamma, const void* beta, void*
   return static_cast<int>(cudaGetLastError());
 }
 
-int layerNormBwdParts(long long rows) { return static_cast<int>(rows < 148 * 4 ? rows : 148 * 4); }
+int layerNormBwdParts(long long rows) { return static_cast<int>(rows < 148 * 8 ? rows : 148 * 8); }
 
 int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx, void* dgamma,
                        void* dbeta, float* partials, long long rows, int D, cudaStream_t stream) {
@@ -176,7 +204,7 @@ int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const f
   if (D <= 2048) ln_bwd_kernel<1><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DX, pg, pb, rows, D);
   else if (D <= 4096) ln_bwd_kernel<2><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DX, pg, pb, rows, D);
   else ln_bwd_kernel<4><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DX, pg, pb, rows, D);
-  ln_bwd_reduce_kernel<<<(D + 255) / 256, 256, 0, stream>>>(pg, pb, static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta), parts, D);
+  ln_bwd_reduce_kernel<<<(D + 31) / 32, 256, 0, stream>>>(pg, pb, static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta), parts, D);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -48,10 +48,10 @@ class ShardedDataParallel:
 
     def __init__(self, model: nn.Module, engine: Optional[Engine] = None, *, lr: float = 3e-4, betas=(0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, bucket_mb: float = 25.0, heap_bytes: int = 0,
-                 comm_blocks: int = 16, algo: str = "auto", group=None, fuse_optimizer: bool = True):
+                 comm_blocks: Optional[int] = None, algo: str = "auto", group=None, fuse_optimizer: bool = True):
         self.model = model
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
-        self.comm_blocks, self.algo = comm_blocks, algo
+        self.algo = algo
         # fused: the bucket's reduce-scatter kernel also performs the AdamW update of this rank's slice and
         # the parameter all-gather follows at once, all while backward is still running
         self.fuse_optimizer = fuse_optimizer
@@ -69,7 +69,12 @@ class ShardedDataParallel:
             engine.initEngine("cuda", max(heap_bytes, need + (512 << 20)))
         self.engine = engine
         self.world, self.rank = engine.world, engine.rank
-        self.comm_stream = torch.cuda.Stream()
+        # Communication kernels run as short, wide bursts on a high-priority stream: they slip in at the
+        # boundary between two GEMM kernels and delay the next one by their own (tens of microseconds)
+        # duration.  A narrow long-running kernel would instead hold a few SMs for the whole GEMM and make
+        # the persistent GEMM's last CTAs start a full wave late.
+        self.comm_blocks = comm_blocks if comm_blocks else (128 if engine.world == 1 else 64)
+        self.comm_stream = torch.cuda.Stream(priority=-1)
         self.step_count = 0
         self._build_buckets(params, int(bucket_mb * (1 << 20)) // 2)
         self._ready_events: Dict[int, torch.cuda.Event] = {}
