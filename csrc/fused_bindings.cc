@@ -74,6 +74,18 @@ void bindFused(py::module_& m) {
      py::arg("topk"), py::arg("experts_per_rank"), py::arg("recv_q_off"), py::arg("recv_s_off"), py::arg("y_off"), py::arg("epoch"),
      py::arg("flag_lane"), py::arg("x"), py::arg("ids"), py::arg("rows"), py::arg("probs"), py::arg("out"), py::arg("status"),
      py::arg("blocks"), py::arg("spin_ns"), py::arg("stream"));
+  m.def("moe_route", [](uint64_t logits, uint64_t ids, uint64_t probs, uint64_t pos, uint64_t counts, int tokens, int experts, int topk,
+                        uint64_t stream) {
+    check(launchMoeRoute(reinterpret_cast<const float*>(logits), reinterpret_cast<int*>(ids), reinterpret_cast<float*>(probs),
+                         reinterpret_cast<int*>(pos), reinterpret_cast<int*>(counts), tokens, experts, topk,
+                         reinterpret_cast<cudaStream_t>(stream)), "moe_route");
+  });
+  m.def("moe_plan", [](uint64_t counts_all, uint64_t ids, uint64_t pos, uint64_t rows, uint64_t row_off, int world, int rank, int experts,
+                       int tokens, int topk, int cap, uint64_t stream) {
+    check(launchMoePlan(reinterpret_cast<const int*>(counts_all), reinterpret_cast<const int*>(ids), reinterpret_cast<const int*>(pos),
+                        reinterpret_cast<int*>(rows), reinterpret_cast<int*>(row_off), world, rank, experts, tokens, topk, cap,
+                        reinterpret_cast<cudaStream_t>(stream)), "moe_plan");
+  });
   m.def("moe_dequant", [](uint64_t q, uint64_t s, uint64_t out, uint64_t n_rows, int max_rows, int hidden, uint64_t stream) {
     check(launchMoeDequant(reinterpret_cast<const void*>(q), reinterpret_cast<const float*>(s), reinterpret_cast<void*>(out),
                            reinterpret_cast<const int*>(n_rows), max_rows, hidden, reinterpret_cast<cudaStream_t>(stream)), "moe_dequant");

@@ -318,6 +318,87 @@ gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   gemm2::run<false, false>(&tmA, &tmB, K, sched, pg, pe, status);
 }
 
+// ---------------------------------------------------------------------------------------------
+// routing and placement
+// ---------------------------------------------------------------------------------------------
+template <int PER_LANE>
+__global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ probs,
+                                                        int* __restrict__ pos, int* __restrict__ counts, int tokens, int experts, int topk) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  float v[PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int e = j * 32 + lane;
+    v[j] = e < experts ? logits[static_cast<long long>(t) * experts + e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    v[j] = __expf(v[j] - mx);
+    sum += v[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+  for (int k = 0; k < topk; ++k) {
+    float best = -1.f;
+    int bi = 0;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j)
+      if (v[j] > best) { best = v[j]; bi = j * 32 + lane; }
+    // warp arg-max; ties go to the lower expert id (what a stable top-k returns)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j)
+        if (j == (bi >> 5)) v[j] = -2.f;       // taken
+      ids[t * topk + k] = bi;
+      probs[t * topk + k] = best * inv;
+      pos[t * topk + k] = atomicAdd(counts + bi, 1);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_plan_kernel(const int* __restrict__ counts_all, const int* __restrict__ ids, const int* __restrict__ pos,
+                                                       int* __restrict__ rows, int* __restrict__ row_off, int world, int rank, int experts,
+                                                       int tokens, int topk, int cap) {
+  extern __shared__ int base[];            // experts entries: first row of (this rank's assignments to e) on e's rank
+  const int epr = experts / world;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int owner = e / epr;
+    int before = 0;                        // rows of the owner's earlier experts
+    for (int e2 = owner * epr; e2 < e; ++e2)
+      for (int r = 0; r < world; ++r) before += counts_all[r * experts + e2];
+    for (int r = 0; r < rank; ++r) before += counts_all[r * experts + e];     // lower ranks inside the expert's segment
+    base[e] = before;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int i = threadIdx.x; i <= epr; i += blockDim.x) {
+      int acc = 0;
+      for (int e2 = rank * epr; e2 < rank * epr + i; ++e2)
+        for (int r = 0; r < world; ++r) acc += counts_all[r * experts + e2];
+      row_off[i] = min(acc, cap);
+    }
+  }
+  const int total = tokens * topk;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int row = base[ids[i]] + pos[i];
+    rows[i] = row < cap ? row : -1;
+  }
+}
+
 template <typename K>
 int coop(K kernel, const MoeArgs& a, int blocks, size_t smem, cudaStream_t stream) {
   if (blocks < 1) blocks = 1;
@@ -354,6 +435,27 @@ int launchQuantFp8Blocks(const void* w, void* q, float* scales, int rows, int co
   if (rows % 128 || cols % 128 || rows <= 0 || cols <= 0) return static_cast<int>(cudaErrorInvalidValue);
   dim3 grid(cols / 128, rows / 128);
   quant_blocks_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w), static_cast<uint8_t*>(q), scales, rows, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launchMoeRoute(const float* logits, int* ids, float* probs, int* pos, int* counts, int tokens, int experts, int topk,
+                   cudaStream_t stream) {
+  if (experts % 32 || experts > 1024 || topk > experts || tokens <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int grid = (tokens + 7) / 8;
+  const int per = experts / 32;
+  if (per <= 4) moe_route_kernel<4><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);
+  else if (per <= 8) moe_route_kernel<8><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);
+  else if (per <= 16) moe_route_kernel<16><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);
+  else moe_route_kernel<32><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launchMoePlan(const int* counts_all, const int* ids, const int* pos, int* rows, int* row_off, int world, int rank, int experts,
+                  int tokens, int topk, int cap, cudaStream_t stream) {
+  if (experts % world || tokens <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  int grid = (tokens * topk + 255) / 256;
+  if (grid > 148) grid = 148;
+  moe_plan_kernel<<<grid, 256, experts * sizeof(int), stream>>>(counts_all, ids, pos, rows, row_off, world, rank, experts, tokens, topk, cap);
   return static_cast<int>(cudaGetLastError());
 }
 

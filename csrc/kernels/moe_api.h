@@ -43,4 +43,14 @@ int launchQuantFp8Rows(const void* x, void* q, float* scales, long long rows, in
 // 128 x 128 block quantiser for weights [rows, cols] (both multiples of 128): e4m3 + fp32 scale per block.
 int launchQuantFp8Blocks(const void* w, void* q, float* scales, int rows, int cols, cudaStream_t stream);
 
+// Routing: softmax over `experts` gate logits (fp32 [tokens, experts], experts % 32 == 0, <= 1024), top-k by
+// probability; writes ids / probs [tokens, k] and pos[tokens, k] = the assignment's arrival number among this
+// rank's assignments to the same expert (counts[experts] must be zero on entry and holds the totals afterwards).
+int launchMoeRoute(const float* logits, int* ids, float* probs, int* pos, int* counts, int tokens, int experts, int topk,
+                   cudaStream_t stream);
+// Placement: from the counts of all ranks ([world, experts]) compute, for every assignment, its row in the receive
+// buffer of the expert's rank (-1 when the buffer of `cap` rows is full), and for this rank row_off[experts_per_rank+1].
+int launchMoePlan(const int* counts_all, const int* ids, const int* pos, int* rows, int* row_off, int world, int rank, int experts,
+                  int tokens, int topk, int cap, cudaStream_t stream);
+
 }  // namespace pccl

@@ -55,7 +55,8 @@ def run(eng: Engine, tokens: int, hidden: int, d_ff: int, n_experts: int, topk: 
     ids, probs = MoEExchange.route(logits, topk)
     plan = moe.plan(ids)
     out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
-    t_route = _time(lambda: moe.plan(MoEExchange.route(logits, topk)[0]), iters, warmup, flush)
+    t_route = _time(lambda: moe.route_and_plan(logits), iters, warmup, flush)
+    t_route_torch = _time(lambda: moe.plan(MoEExchange.route(logits, topk)[0]), iters, warmup, flush)
     t_disp = _time(lambda: moe.dispatch(x, ids, plan), iters, warmup, flush)
     t_ffn = _time(lambda: moe.experts(w1, w2, plan), iters, warmup, flush)
     t_comb = _time(lambda: moe.combine(ids, probs, plan, out), iters, warmup, flush)
@@ -110,7 +111,7 @@ def run(eng: Engine, tokens: int, hidden: int, d_ff: int, n_experts: int, topk: 
     roof = {"dispatch_us": disp_bytes / (link_gbs * 1e9) * 1e6, "combine_us": comb_bytes / (link_gbs * 1e9) * 1e6,
             "ffn_us": ffn_flops / (peak_tflops * 1e12) * 1e6}
     return {"n_gpus": world, "tokens_per_rank": tokens, "hidden": hidden, "d_ff": d_ff, "experts": n_experts, "topk": topk,
-            "rows_received": n_rows, "ours_us": {"route_plan": t_route, "dispatch_fp8": t_disp, "expert_ffn": t_ffn, "combine": t_comb,
+            "rows_received": n_rows, "ours_us": {"route_plan": t_route, "route_plan_torch_ops": t_route_torch, "dispatch_fp8": t_disp, "expert_ffn": t_ffn, "combine": t_comb,
                                                  "layer_total": t_total},
             "baseline_us": {"nccl_all_to_all_bf16": b_disp, "matmul_loop_ffn": b_ffn, "nccl_all_to_all_back": b_comb,
                             "sum": b_disp + b_ffn + b_comb},

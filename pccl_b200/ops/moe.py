@@ -101,6 +101,31 @@ class MoEExchange:
         row_off[1:] = mine.cumsum(0).clamp(max=self.cap).to(torch.int32)
         return {"rows": rows.contiguous(), "row_off": row_off, "n_rows": row_off[-1:].contiguous()}
 
+    def route_and_plan(self, gate_logits: torch.Tensor):
+        """Fused routing: one kernel does softmax + top-k + per-expert counting (an assignment's position inside
+        its expert's segment is the value its atomic increment returned), the counts are all-gathered, and a
+        second kernel turns counts into receive rows.  Returns (ids, probs, plan)."""
+        eng, T, K, E = self.eng, self.T, self.K, self.E
+        dev = gate_logits.device
+        lg = gate_logits.float().contiguous()
+        ids = torch.empty((T, K), dtype=torch.int32, device=dev)
+        probs = torch.empty((T, K), dtype=torch.float32, device=dev)
+        pos = torch.empty((T, K), dtype=torch.int32, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        s = torch.cuda.current_stream().cuda_stream
+        C.moe_route(lg.data_ptr(), ids.data_ptr(), probs.data_ptr(), pos.data_ptr(), counts.data_ptr(), T, E, K, s)
+        if eng.world > 1:
+            coll.all_gather(eng, counts, self.counts_all.view(-1), lane=self.flag_lane)
+            counts_all = self.counts_all
+        else:
+            counts_all = counts
+        rows = torch.empty((T, K), dtype=torch.int32, device=dev)
+        row_off = torch.empty(self.epr + 1, dtype=torch.int32, device=dev)
+        C.moe_plan(counts_all.data_ptr(), ids.data_ptr(), pos.data_ptr(), rows.data_ptr(), row_off.data_ptr(), eng.world, eng.rank, E,
+                   T, K, self.cap, s)
+        count_launch(2)
+        return ids, probs, {"rows": rows, "row_off": row_off, "n_rows": row_off[-1:]}
+
     # ---- kernels ----------------------------------------------------------------------------
     def _exchange(self, kind: str, x, ids, rows, probs, out) -> None:
         self.epoch += 1
@@ -131,8 +156,7 @@ class MoEExchange:
         return out
 
     def forward(self, x: torch.Tensor, gate_logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
-        ids, probs = self.route(gate_logits, self.K)
-        plan = self.plan(ids)
+        ids, probs, plan = self.route_and_plan(gate_logits)
         self.dispatch(x, ids, plan)
         self.experts(w1, w2, plan)
         return self.combine(ids, probs, plan)

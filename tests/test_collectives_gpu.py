@@ -352,3 +352,27 @@ def test_moe_layer_world_of_one_matches_dense_reference(native):
             ref[m] += probs[m, k, None] * y[m]
     assert (out.float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
     del moe, eng
+
+
+def test_moe_route_and_plan_kernels_match_tensor_ops(native):
+    from pccl_b200.engine import Engine
+    from pccl_b200.ops.moe import MoEExchange
+    torch.manual_seed(8)
+    T, H, E, Kt = 1000, 256, 64, 6
+    eng = Engine(0, 1); eng.initEngine("cuda", heap_bytes=256 << 20)
+    moe = MoEExchange(eng, T, H, E, Kt)
+    logits = torch.randn(T, E, device="cuda")
+    ids, probs, plan = moe.route_and_plan(logits)
+    ref_ids, ref_probs = MoEExchange.route(logits, Kt)
+    ref_plan = moe.plan(ref_ids)
+    assert torch.equal(ids, ref_ids)
+    assert torch.allclose(probs, ref_probs, rtol=1e-4, atol=1e-7)
+    assert torch.equal(plan["row_off"], ref_plan["row_off"])
+    # rows are a permutation within each expert's segment: same multiset per expert, all distinct
+    rows, ref_rows = plan["rows"].view(-1).long(), ref_plan["rows"].view(-1).long()
+    assert rows.unique().numel() == rows.numel()
+    off = plan["row_off"].long()
+    flat = ids.view(-1).long()
+    assert ((rows >= off[flat]) & (rows < off[flat + 1])).all()
+    assert torch.equal(rows.sort().values, ref_rows.sort().values)
+    del moe, eng
