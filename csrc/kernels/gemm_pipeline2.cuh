@@ -10,6 +10,7 @@
 // and "accumulator ready" arrivals to both CTAs.  Same hooks (Sched / Gate / Epi) and the same bounded
 // waits as gemm_pipeline.cuh; every thread of both CTAs reaches the closing cluster barrier.
 #pragma once
+#include <cstdlib>
 #include <utility>
 
 #include "gemm_pipeline.cuh"
@@ -226,7 +227,10 @@ inline cudaError_t launch_pairs(void (*kernel)(KArgs...), dim3 grid, int threads
   at[1].id = cudaLaunchAttributeCooperative;
   at[1].val.cooperative = 1;
   cfg.attrs = at;
-  cfg.numAttrs = cooperative ? 2 : 1;
+  // PCCL_NO_COOP=1 drops the co-residency check of the cooperative launch (profilers that replay a kernel
+  // cannot replay cooperative launches); the kernels' waits stay bounded either way.
+  static const bool no_coop = std::getenv("PCCL_NO_COOP") != nullptr && std::getenv("PCCL_NO_COOP")[0] == '1';
+  cfg.numAttrs = (cooperative && !no_coop) ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 

@@ -440,9 +440,9 @@ int launchQuantFp8Blocks(const void* w, void* q, float* scales, int rows, int co
 
 int launchMoeRoute(const float* logits, int* ids, float* probs, int* pos, int* counts, int tokens, int experts, int topk,
                    cudaStream_t stream) {
-  if (experts % 32 || experts > 1024 || topk > experts || tokens <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (experts < 1 || experts > 1024 || topk > experts || tokens <= 0) return static_cast<int>(cudaErrorInvalidValue);
   const int grid = (tokens + 7) / 8;
-  const int per = experts / 32;
+  const int per = (experts + 31) / 32;
   if (per <= 4) moe_route_kernel<4><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);
   else if (per <= 8) moe_route_kernel<8><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);
   else if (per <= 16) moe_route_kernel<16><<<grid, 256, 0, stream>>>(logits, ids, probs, pos, counts, tokens, experts, topk);

@@ -43,7 +43,7 @@ int launchQuantFp8Rows(const void* x, void* q, float* scales, long long rows, in
 // 128 x 128 block quantiser for weights [rows, cols] (both multiples of 128): e4m3 + fp32 scale per block.
 int launchQuantFp8Blocks(const void* w, void* q, float* scales, int rows, int cols, cudaStream_t stream);
 
-// Routing: softmax over `experts` gate logits (fp32 [tokens, experts], experts % 32 == 0, <= 1024), top-k by
+// Routing: softmax over `experts` gate logits (fp32 [tokens, experts], experts <= 1024), top-k by
 // probability; writes ids / probs [tokens, k] and pos[tokens, k] = the assignment's arrival number among this
 // rank's assignments to the same expert (counts[experts] must be zero on entry and holds the totals afterwards).
 int launchMoeRoute(const float* logits, int* ids, float* probs, int* pos, int* counts, int tokens, int experts, int topk,
