@@ -139,6 +139,64 @@ void bindFused(py::module_& m) {
   }, py::arg("engine"), py::arg("y"), py::arg("ldy"), py::arg("w"), py::arg("ldw"), py::arg("out"), py::arg("ldo"), py::arg("M"), py::arg("N"),
      py::arg("K"), py::arg("stage_off"), py::arg("flag_off2"), py::arg("epoch"), py::arg("ctas"), py::arg("status"), py::arg("stream"),
      py::arg("b_mn") = false);
+  // ---- block-scaled fp8 forms ------------------------------------------------------------------------
+  // One entry per (virtual) rank in the lists; with an engine the lists have one entry and the world is the engine's.
+  m.def("ag_gemm_fp8", [](Engine* e, const std::vector<uint64_t>& heaps, uint64_t flag_off, uint64_t x_off, uint64_t xs_off, int M, int N,
+                          int K, const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& w_scale, int ld_ws,
+                          const std::vector<uint64_t>& d, int64_t ldd, const std::vector<uint64_t>& dq, const std::vector<uint64_t>& ds,
+                          int64_t ldq, uint64_t bias, uint32_t flags, uint64_t ready_off, uint64_t epoch, int n_copy, int ctas,
+                          int flag_lane, const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream) {
+    AgGemmArgs A{};
+    const int n = e ? 1 : static_cast<int>(heaps.size());
+    A.w = e ? e->worldTable() : emuWorld2(heaps, flag_off);
+    A.nvirt = e ? 1 : n;
+    A.M = M; A.N = N; A.K = K; A.M_local = M / A.w.world;
+    A.x_off = x_off; A.xs_off = xs_off; A.elem_bytes = 1; A.ready_off = ready_off; A.epoch = epoch;
+    A.bar_epoch = e ? e->nextEpoch(flag_lane) : epoch;
+    A.n_copy = n_copy; A.flag_lane = flag_lane; A.spin_ns = spin_ns ? spin_ns : kDefaultSpinLimit;
+    A.flags = flags | (bias ? GEMM_BIAS : 0);
+    std::vector<AgGemmHost> h(n);
+    for (int r = 0; r < n; ++r) {
+      A.r[r].D = d.empty() ? nullptr : reinterpret_cast<void*>(d.at(r)); A.r[r].ldd = ldd;
+      A.r[r].Dq = dq.empty() ? nullptr : reinterpret_cast<void*>(dq.at(r));
+      A.r[r].Ds = ds.empty() ? nullptr : reinterpret_cast<float*>(ds.at(r));
+      A.r[r].ldq = ldq;
+      A.r[r].bias = reinterpret_cast<const void*>(bias);
+      A.r[r].w_scale = reinterpret_cast<const float*>(w_scale.at(r)); A.r[r].ld_ws = ld_ws;
+      A.r[r].status = reinterpret_cast<uint32_t*>(status.at(r));
+      A.r[r].rank = e ? e->rank() : r;
+      h[r] = AgGemmHost{reinterpret_cast<const void*>(w.at(r)), ldw, false};
+    }
+    check(launchAgGemmFp8(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "ag_gemm_fp8");
+  }, py::arg("engine").none(true), py::arg("heaps"), py::arg("flag_off"), py::arg("x_off"), py::arg("xs_off"), py::arg("M"), py::arg("N"),
+     py::arg("K"), py::arg("w"), py::arg("ldw"), py::arg("w_scale"), py::arg("ld_ws"), py::arg("d"), py::arg("ldd"), py::arg("dq"),
+     py::arg("ds"), py::arg("ldq"), py::arg("bias"), py::arg("flags"), py::arg("ready_off"), py::arg("epoch"), py::arg("n_copy"),
+     py::arg("ctas"), py::arg("flag_lane"), py::arg("status"), py::arg("spin_ns"), py::arg("stream"));
+  m.def("gemm_rs_fp8", [](Engine* e, const std::vector<uint64_t>& heaps, const std::vector<uint64_t>& y, int64_t ldy,
+                          const std::vector<uint64_t>& y_scale, int ld_ys, const std::vector<uint64_t>& w, int64_t ldw,
+                          const std::vector<uint64_t>& w_scale, int ld_ws, const std::vector<uint64_t>& out, int64_t ldo, int M, int N,
+                          int K, uint64_t stage_off, uint64_t flag_off2, uint64_t epoch, int ctas,
+                          const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream) {
+    GemmRsArgs A{};
+    const int n = e ? 1 : static_cast<int>(heaps.size());
+    A.w = e ? e->worldTable() : emuWorld2(heaps, 0);
+    A.nvirt = e ? 1 : n;
+    A.M = M; A.N = N; A.K = K; A.M_local = M / A.w.world;
+    A.stage_off = stage_off; A.flag_off2 = flag_off2; A.epoch = epoch; A.spin_ns = spin_ns ? spin_ns : kDefaultSpinLimit;
+    std::vector<GemmRsHost> h(n);
+    for (int r = 0; r < n; ++r) {
+      A.r[r].out = reinterpret_cast<void*>(out.at(r)); A.r[r].ldo = ldo;
+      A.r[r].status = reinterpret_cast<uint32_t*>(status.at(r));
+      A.r[r].rank = e ? e->rank() : r;
+      A.r[r].y_scale = reinterpret_cast<const float*>(y_scale.at(r)); A.r[r].ld_ys = ld_ys;
+      A.r[r].w_scale = reinterpret_cast<const float*>(w_scale.at(r)); A.r[r].ld_ws = ld_ws;
+      h[r] = GemmRsHost{reinterpret_cast<const void*>(y.at(r)), ldy, reinterpret_cast<const void*>(w.at(r)), ldw, false};
+    }
+    check(launchGemmRsFp8(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "gemm_rs_fp8");
+  }, py::arg("engine").none(true), py::arg("heaps"), py::arg("y"), py::arg("ldy"), py::arg("y_scale"), py::arg("ld_ys"), py::arg("w"),
+     py::arg("ldw"), py::arg("w_scale"), py::arg("ld_ws"), py::arg("out"), py::arg("ldo"), py::arg("M"), py::arg("N"), py::arg("K"),
+     py::arg("stage_off"), py::arg("flag_off2"), py::arg("epoch"), py::arg("ctas"), py::arg("status"), py::arg("spin_ns"),
+     py::arg("stream"));
   // ---- single-GPU emulation of all ranks in one cooperative launch (tests) ------------------------
   m.def("emu_ag_gemm", [](const std::vector<uint64_t>& heaps, uint64_t flag_off, uint64_t x_off, int M, int N, int K,
                           const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& d, int64_t ldd,

@@ -19,6 +19,13 @@ struct AgGemmRank {
   uint32_t* status;
   int rank;
   int pad;
+  // block-scaled fp8 only
+  const float* w_scale;       // fp32 [N/128, ld_ws]: 128 x 128 scales of the W shard
+  int ld_ws;
+  int pad2;
+  void* Dq;                   // when set, the output is quantised instead: e4m3 [M, ldq] ...
+  float* Ds;                  // ... with fp32 1 x 128 scales [M, N/128]
+  long long ldq;
 };
 
 struct AgGemmArgs {
@@ -33,8 +40,9 @@ struct AgGemmArgs {
   int n_copy;                 // CTAs that pull peer rows (the rest compute)
   int flag_lane;
   uint64_t spin_ns;
-  uint32_t flags;             // GEMM_BIAS
-  uint32_t pad;
+  uint32_t flags;             // GEMM_BIAS, GEMM_GELU_INPLACE (fp8 path)
+  int elem_bytes;             // 2 (bf16 X) or 1 (e4m3 X with scales at xs_off); 0 is read as 2
+  uint64_t xs_off;            // fp8: heap offset of the symmetric gathered scales, fp32 [M, K/128]
   AgGemmRank r[kMaxVirt];
 };
 
@@ -49,6 +57,10 @@ struct GemmRsRank {
   uint32_t* status;
   int rank;
   int pad;
+  // block-scaled fp8 only
+  const float* y_scale;       // fp32 [M, ld_ys]
+  const float* w_scale;       // fp32 [N/128, ld_ws]
+  int ld_ys, ld_ws;
 };
 
 struct GemmRsArgs {
@@ -66,6 +78,10 @@ struct GemmRsHost { const void* Y; long long ldy; const void* W; long long ldw; 
 
 int launchAgGemm(AgGemmArgs& args, const AgGemmHost* host, int ctas, cudaStream_t stream);
 int launchGemmRs(GemmRsArgs& args, const GemmRsHost* host, int ctas, cudaStream_t stream);
+// Block-scaled fp8 forms (fused_tp_fp8.cu): X / Y and W are e4m3 bytes, K-major, K a multiple of 128, N a multiple of
+// 256; the scale fields of the argument structs must be filled.  Single-CTA tiles.
+int launchAgGemmFp8(AgGemmArgs& args, const AgGemmHost* host, int ctas, cudaStream_t stream);
+int launchGemmRsFp8(GemmRsArgs& args, const GemmRsHost* host, int ctas, cudaStream_t stream);
 const char* fusedLastError();
 
 }  // namespace pccl

@@ -21,8 +21,7 @@
 #include <string>
 
 #include "fused_api.h"
-#include "gemm_epilogue.cuh"
-#include "gemm_pipeline.cuh"
+#include "fused_tp.cuh"
 #include "gemm_pipeline2.cuh"
 #include "tensormap.h"
 
@@ -31,114 +30,7 @@ namespace pccl {
 namespace {
 
 using namespace gemm;
-
-__device__ __forceinline__ uint64_t* lane_flag(const World& W, int owner, int lane, int block, int src) {
-  return reinterpret_cast<uint64_t*>(W.heap[owner] + W.flag_off) +
-         ((static_cast<uint64_t>(lane) * kMaxBlocksPerColl + block) * kMaxRanks + src);
-}
-
-// Barrier among CTA `block` of every rank, executed by the first `world` threads of the CTA.
-__device__ __forceinline__ bool cta_peer_barrier(const World& W, int me, int lane, int block, uint64_t value, uint64_t spin_ns,
-                                                 uint32_t* status) {
-  __shared__ uint32_t s_bad;
-  if (threadIdx.x == 0) s_bad = 0;
-  __syncthreads();
-  if (threadIdx.x < static_cast<uint32_t>(W.world)) {
-    const int p = threadIdx.x;
-    __threadfence_system();
-    dev::st_release_sys(lane_flag(W, p, lane, block, me), value);
-    if (!dev::wait_ge(lane_flag(W, me, lane, block, p), value, spin_ns, nullptr)) {
-      s_bad = 1;
-      dev::report(status, ST_TIMEOUT, block, static_cast<uint32_t>(p), 100 + static_cast<uint32_t>(value & 3));
-    }
-  }
-  __syncthreads();
-  return s_bad == 0;
-}
-
-// =================================================================================================
-// all-gather -> GEMM
-// =================================================================================================
-struct AgSched {
-  int me, world, tiles_ml, tiles_n, first, stride;
-  __device__ __forceinline__ bool get(int it, TileCoord* t) const {
-    const long long idx = first + static_cast<long long>(it) * stride;
-    const int per_panel = tiles_ml * tiles_n;
-    if (idx >= static_cast<long long>(world) * per_panel) return false;
-    const int panel = static_cast<int>(idx / per_panel), r = static_cast<int>(idx % per_panel);
-    int src = me + panel;
-    if (src >= world) src -= world;
-    t->m = src * tiles_ml + r % tiles_ml;
-    t->n = r / tiles_ml;
-    t->extra = src;
-    return true;
-  }
-};
-
-struct AgGate {
-  const uint32_t* ready;   // per 128-row chunk of the gathered X: parts written so far by the owner's copy CTAs (never reset)
-  int me;
-  uint32_t target;         // epoch * copy CTAs
-  uint64_t spin_ns;
-  __device__ __forceinline__ bool wait(const TileCoord& t, const volatile uint32_t* abort) const {
-    if (t.extra == me) return true;
-    const uint32_t* f = ready + t.m;
-    if (dev::ld_acquire_sys_u32(f) < target) {
-      const uint64_t t0 = dev::global_timer_ns();
-      for (uint32_t i = 1;; ++i) {
-        if (dev::ld_acquire_sys_u32(f) >= target) break;
-        if ((i & 31) == 0) {
-          if (*abort) return false;
-          if (dev::global_timer_ns() - t0 > spin_ns) return false;
-          __nanosleep(64);
-        }
-      }
-    }
-    tc::fence_proxy_async();   // the chunk was written by a peer's ordinary stores; TMA (async proxy) reads it next
-    return true;
-  }
-};
-
-// Copy CTAs push this rank's rows into every peer's gathered buffer with plain 16-byte stores
-// (posted writes: no round trip per request, a handful of CTAs fills the NVLink port).  Peers are
-// served in the order in which they need the panel -- rank me-1 consumes it first, then me-2, ... --
-// so at any moment each receiver is fed by one sender.  A 128-row chunk is split across the copy
-// CTAs; each adds one to the receiver's counter for that chunk when its part has been written.
-__device__ void ag_push_role(const AgGemmArgs& A, const AgGemmRank& R) {
-  const int me = R.rank, world = A.w.world, j = blockIdx.x;
-  if (!cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 1, A.spin_ns, R.status)) return;
-  const int chunks = A.M_local / BM;
-  const long long chunk_bytes = static_cast<long long>(BM) * A.K * 2;
-  const long long nvec = chunk_bytes >> 4;
-  const long long per = (nvec + A.n_copy - 1) / A.n_copy;
-  const long long lo = min(nvec, per * j), hi = min(nvec, per * (j + 1));
-  const int nt = blockDim.x;
-  for (int k = 1; k < world; ++k) {
-    int p = me - k;
-    if (p < 0) p += world;
-    for (int c = 0; c < chunks; ++c) {
-      const long long off = static_cast<long long>(A.x_off) + (static_cast<long long>(me) * A.M_local + static_cast<long long>(c) * BM) * A.K * 2;
-      const char* src = A.w.heap[me] + off;
-      char* dst = A.w.heap[p] + off;
-      long long i = lo + threadIdx.x;
-      for (; i + 3 * nt < hi; i += 4 * nt) {
-        dev::Vec16 v0 = dev::ld16(src + (i << 4)), v1 = dev::ld16(src + ((i + nt) << 4));
-        dev::Vec16 v2 = dev::ld16(src + ((i + 2 * nt) << 4)), v3 = dev::ld16(src + ((i + 3 * nt) << 4));
-        dev::st16(dst + (i << 4), v0);
-        dev::st16(dst + ((i + nt) << 4), v1);
-        dev::st16(dst + ((i + 2 * nt) << 4), v2);
-        dev::st16(dst + ((i + 3 * nt) << 4), v3);
-      }
-      for (; i < hi; i += nt) dev::st16(dst + (i << 4), dev::ld16(src + (i << 4)));
-      __syncthreads();                        // every thread's stores of this chunk part are issued
-      if (threadIdx.x == 0) {
-        __threadfence_system();
-        uint32_t* cnt = reinterpret_cast<uint32_t*>(A.w.heap[p] + A.ready_off) + (me * chunks + c);
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
-      }
-    }
-  }
-}
+using namespace fused;
 
 template <bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_constant__ AgGemmArgs A) {
@@ -165,111 +57,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) ag_gemm_kernel(const __grid_co
   StoreEpi epi{R.D, nullptr, static_cast<const __nv_bfloat16*>(R.bias), R.ldd, A.M, A.N, A.flags};
   run<false, B_MN>(&R.tmA, &R.tmB, A.K, sched, gate, epi, R.status);
 }
-
-// =================================================================================================
-// GEMM -> reduce-scatter
-// =================================================================================================
-struct RsSched {
-  int me, world, tiles_ml, tiles_n, first, stride;
-  __device__ __forceinline__ bool get(int it, TileCoord* t) const {
-    const long long idx = first + static_cast<long long>(it) * stride;
-    const int per_panel = tiles_ml * tiles_n;
-    if (idx >= static_cast<long long>(world) * per_panel) return false;
-    const int panel = static_cast<int>(idx / per_panel), r = static_cast<int>(idx % per_panel);
-    int owner = me + 1 + panel;          // peers first, own rows last
-    if (owner >= world) owner -= world;
-    t->m = owner * tiles_ml + r % tiles_ml;
-    t->n = r / tiles_ml;
-    t->extra = owner;
-    return true;
-  }
-};
-
-constexpr int kRsPitch = 144;                       // bytes per staged row: 64 bf16 + 16 pad (bank-conflict free)
-constexpr int kRsStageBytes = 4 * 32 * kRsPitch;    // four epilogue warps
-constexpr int RS_SMEM_BYTES = SMEM_BYTES + kRsStageBytes;
-
-struct RsEpi {
-  const GemmRsArgs* A;
-  const GemmRsRank* R;
-  uint8_t* stage;      // this warp's 32 x 144 B staging rows
-  int me, tiles_ml, tiles_n;
-
-  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.m * BM; }
-  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * BN; }
-  __device__ __forceinline__ void attach_smem(uint8_t* p) { stage = p + ((threadIdx.x >> 5) & 3) * (32 * kRsPitch); }
-
-  __device__ __forceinline__ long long tile_local_index(const TileCoord& t) const {
-    return static_cast<long long>(t.m - t.extra * tiles_ml) * tiles_n + t.n;
-  }
-  __device__ __forceinline__ uint64_t* tile_flag(int owner, int src, long long tile_local) const {
-    return reinterpret_cast<uint64_t*>(A->w.heap[owner] + A->flag_off2) + static_cast<long long>(src) * tiles_ml * tiles_n + tile_local;
-  }
-
-  __device__ __forceinline__ void tile_begin(const TileCoord& t) {
-    if (t.extra != me) return;
-    // our own rows: the peers' partials of this tile must be in our staging slots
-    const int lane = threadIdx.x & 31;
-    if (lane < A->w.world && lane != me) {
-      if (!dev::wait_ge(tile_flag(me, lane, tile_local_index(t)), A->epoch, A->spin_ns, nullptr))
-        dev::report(R->status, ST_TIMEOUT, blockIdx.x, 4, static_cast<uint32_t>(lane));
-    }
-    __syncwarp();
-  }
-
-  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
-    const int lane = threadIdx.x & 31;
-    const int owner = t.extra;
-    const long long row_local = static_cast<long long>(t.m - owner * tiles_ml) * BM + row_in_tile;   // row inside the owner's block
-    const long long col = static_cast<long long>(t.n) * BN + col_in_tile;
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    if (owner != me) {
-      uint8_t* srow = stage + lane * kRsPitch + (col_in_tile & 32) * 2;
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) *reinterpret_cast<dev::Vec16*>(srow + i * 2) = dev::pack<DT_BF16>(v + i);
-      if (col_in_tile & 32) {
-        // 64 columns staged: one 128-byte bulk copy per row into the owner's slot for this rank
-        tc::fence_proxy_async_smem();
-        __syncwarp();
-        char* dst = A->w.heap[owner] + A->stage_off +
-                    ((static_cast<long long>(me) * A->M_local + row_local) * A->N + (col - 32)) * 2;
-        tc::bulk_store_s2g(dst, stage + lane * kRsPitch, 128);
-        tc::bulk_commit();
-        tc::bulk_wait_read<0>();      // the staging row may be overwritten by the next strip
-      }
-      return;
-    }
-    // own rows: add the peers' bf16 partials (local memory) to the fp32 accumulator and store the result
-    const char* base = A->w.heap[me] + A->stage_off;
-    for (int s = 0; s < A->w.world; ++s) {
-      if (s == me) continue;
-      const char* p = base + ((static_cast<long long>(s) * A->M_local + row_local) * A->N + col) * 2;
-#pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        float f[8];
-        dev::unpack<DT_BF16>(dev::ld16(p + i * 2), f);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) v[i + k] += f[k];
-      }
-    }
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(R->out) + row_local * R->ldo + col;
-#pragma unroll
-    for (int i = 0; i < 32; i += 8) dev::st16(out + i, dev::pack<DT_BF16>(v + i));
-  }
-
-  __device__ __forceinline__ void tile_done(const TileCoord& t, const volatile uint32_t*) {
-    if (t.extra == me) return;
-    tc::bulk_wait<0>();                  // this lane's rows have been written to the owner
-    tc::fence_proxy_async();
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
-    if ((threadIdx.x >> 5) == 2 && (threadIdx.x & 31) == 0) {
-      __threadfence_system();
-      dev::st_release_sys(tile_flag(t.extra, me, tile_local_index(t)), A->epoch);
-    }
-  }
-};
 
 template <bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_constant__ GemmRsArgs A) {

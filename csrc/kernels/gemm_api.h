@@ -34,6 +34,15 @@ int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, in
 int gemmGroupedBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, const int* row_off,
                     int groups, int max_rows, int N, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream);
 
+// Block-scaled fp8: A is e4m3 [M, K] (row stride lda bytes = elements) with fp32 scales sa [M, ld_sa], one per row and
+// 128 values of K; B is e4m3 [N, K] with fp32 scales sb [ceil(N/128), ld_sb], one per 128 x 128 block.
+//   D[m, n] = sum_kb sa[m, kb] * sb[n/128, kb] * dot(A[m, kb*128 .. +128], B[n, kb*128 .. +128])
+// K a multiple of 128; flags: GEMM_OUT_F32, GEMM_ACCUMULATE, GEMM_GELU, GEMM_BIAS, GEMM_GELU_INPLACE.
+int gemmFp8(const void* A, int64_t lda, const float* sa, int ld_sa, const void* B, int64_t ldb, const float* sb, int ld_sb,
+            void* D, int64_t ldd, int M, int N, int K, uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status,
+            cudaStream_t stream);
+const char* gemmFp8LastError();
+
 const char* gemmLastError();
 
 }  // namespace pccl

@@ -14,6 +14,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 
 struct StoreEpi {
+  static constexpr bool kRow128 = false;   // takes 32-column strips
   void* D;
   void* D2;
   const __nv_bfloat16* bias;

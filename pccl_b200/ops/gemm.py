@@ -102,6 +102,87 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     return out
 
 
+def quant_rows(x: torch.Tensor):
+    """bf16 [rows, K] -> (e4m3 bytes [rows, K], fp32 scales [rows, K/128]): one scale per row and 128 values."""
+    rows, k = x.shape
+    if k % 128 or not x.is_contiguous() or x.dtype != torch.bfloat16:
+        raise ValueError("quant_rows: contiguous bf16 with K % 128 == 0")
+    q = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, k // 128), dtype=torch.float32, device=x.device)
+    C.quant_fp8_rows(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, k, torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return q, s
+
+
+def quant_blocks(w: torch.Tensor):
+    """bf16 [N, K] weights -> (e4m3 bytes, fp32 scales [N/128, K/128]): one scale per 128 x 128 block."""
+    n, k = w.shape
+    if n % 128 or k % 128 or not w.is_contiguous() or w.dtype != torch.bfloat16:
+        raise ValueError("quant_blocks: contiguous bf16 with both sizes multiples of 128")
+    q = torch.empty((n, k), dtype=torch.uint8, device=w.device)
+    s = torch.empty((n // 128, k // 128), dtype=torch.float32, device=w.device)
+    C.quant_fp8_blocks(w.data_ptr(), q.data_ptr(), s.data_ptr(), n, k, torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return q, s
+
+
+def gemm_fp8(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, *,
+             out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+             bias: Optional[torch.Tensor] = None, gelu_inplace: bool = False, accumulate: bool = False,
+             sms: int = 0) -> torch.Tensor:
+    """Block-scaled fp8 linear form ``a @ b.T``: ``a_q`` e4m3 bytes [M, K] with ``a_s`` fp32 [M, K/128]
+    (1 x 128 scales), ``b_q`` e4m3 bytes [N, K] with ``b_s`` fp32 [ceil(N/128), K/128] (128 x 128 scales).
+    The partial product of every 128-wide K block is scaled and accumulated in fp32 (csrc/kernels/gemm_fp8.cu)."""
+    for t, name in ((a_q, "a_q"), (b_q, "b_q")):
+        if not t.is_cuda or t.element_size() != 1 or t.dim() != 2 or t.stride(1) != 1 or t.stride(0) % 16 or t.data_ptr() % 16:
+            raise ValueError(f"gemm_fp8: {name} must be 2-D one-byte elements, unit inner stride, 16-byte aligned rows")
+    M, K = a_q.shape
+    N, Kb = b_q.shape
+    if K != Kb or K % 128:
+        raise ValueError("gemm_fp8: inner sizes must agree and be a multiple of 128")
+    if a_s.dtype != torch.float32 or a_s.shape != (M, K // 128) or a_s.stride(1) != 1:
+        raise ValueError("gemm_fp8: a_s must be fp32 [M, K/128]")
+    if b_s.dtype != torch.float32 or b_s.shape != ((N + 127) // 128, K // 128) or b_s.stride(1) != 1:
+        raise ValueError("gemm_fp8: b_s must be fp32 [ceil(N/128), K/128]")
+    if out is None:
+        ldd = (N + 7) // 8 * 8
+        store = torch.empty((M, ldd), dtype=out_dtype, device=a_q.device)
+        out = store[:, :N] if ldd != N else store
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError("gemm_fp8: out must be [M,N] bf16/fp32 with unit inner stride")
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= C.GEMM_OUT_F32
+    if accumulate:
+        flags |= C.GEMM_ACCUMULATE
+    if gelu_inplace:
+        flags |= C.GEMM_GELU_INPLACE
+    bias_ptr = 0
+    if bias is not None:
+        if bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous():
+            raise ValueError("gemm_fp8: bias must be a contiguous bf16 vector of length N")
+        flags |= C.GEMM_BIAS
+        bias_ptr = bias.data_ptr()
+    C.gemm_fp8(a_q.data_ptr(), a_q.stride(0), a_s.data_ptr(), a_s.stride(0), b_q.data_ptr(), b_q.stride(0), b_s.data_ptr(),
+               b_s.stride(0), out.data_ptr(), out.stride(0), M, N, K, flags, bias_ptr, 0, sms,
+               status_words(a_q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return out
+
+
+def dequant_rows(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    """fp32 values of a 1 x 128 block-scaled e4m3 tensor (reference for tests; tensor ops)."""
+    v = q.view(torch.float8_e4m3fn).float()
+    return (v.view(q.shape[0], -1, 128) * s.unsqueeze(-1)).view(q.shape)
+
+
+def dequant_blocks(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    """fp32 values of a 128 x 128 block-scaled e4m3 tensor (reference for tests; tensor ops)."""
+    n, k = q.shape
+    v = q.view(torch.float8_e4m3fn).float().view(n // 128, 128, k // 128, 128)
+    return (v * s.view(n // 128, 1, k // 128, 1)).view(n, k)
+
+
 def gemm_nt(a, b, **kw):
     """a[M,K] @ b[N,K].T"""
     return gemm(a, b, **kw)
@@ -127,7 +208,23 @@ if __name__ == "__main__":      # python -m pccl_b200.ops.gemm --m 4096 --n 4096
     ap.add_argument("--a-t", action="store_true")
     ap.add_argument("--b-t", action="store_true")
     ap.add_argument("--pair", action="store_true")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 operands (1x128 / 128x128 scales)")
     a_ = ap.parse_args()
+    if a_.fp8:
+        Aq, As = quant_rows(torch.randn((a_.m, a_.k), device="cuda").bfloat16())
+        Bq, Bs = quant_blocks((torch.randn((a_.n, a_.k), device="cuda") * 0.02).bfloat16())
+        D = torch.empty((a_.m, a_.n), device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(a_.iters + 1)]
+        ev[0].record()
+        for i in range(a_.iters):
+            gemm_fp8(Aq, As, Bq, Bs, out=D)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        check_status("gemm_fp8")
+        ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(a_.iters)]
+        print({"fp8": True, "ms": ms, "tflops": [2 * a_.m * a_.n * a_.k / t / 1e9 for t in ms]})
+        raise SystemExit(0)
     A = torch.randn((a_.k, a_.m) if a_.a_t else (a_.m, a_.k), device="cuda").bfloat16()
     B = torch.randn((a_.k, a_.n) if a_.b_t else (a_.n, a_.k), device="cuda").bfloat16()
     D = torch.empty((a_.m, a_.n), device="cuda", dtype=torch.bfloat16)

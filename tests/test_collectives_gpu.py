@@ -228,6 +228,85 @@ def test_gemm_rs_emulated(native, world, M_local):
             y.mul_(0.5)
 
 
+@pytest.mark.parametrize("world,quant_out", [(2, False), (4, False), (2, True)])
+def test_ag_gemm_fp8_emulated(native, world, quant_out):
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, quant_blocks, quant_rows
+    M_local, K, N = 256, 1024, 512
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(19)
+    xs = [(torch.randn(M_local, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    ws = [quant_blocks((torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16()) for _ in range(world)]
+    x_off = DATA_OFF
+    xs_off = x_off + M * K
+    ready_off = xs_off + M * (K // 128) * 4
+    heaps = [torch.zeros(ready_off + 4096, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    oq = [torch.zeros(M, N, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    os_ = [torch.zeros(M, N // 128, dtype=torch.float32, device="cuda") for _ in range(world)]
+    ctas = 148 // world
+    for epoch in (1, 2):
+        X = []
+        for r in range(world):
+            q, s = quant_rows((xs[r].float() * epoch).bfloat16())
+            X.append(dequant_rows(q, s))
+            fq = heaps[r][x_off:x_off + M * K].view(M, K)
+            fs = heaps[r][xs_off:xs_off + M * (K // 128) * 4].view(torch.float32).view(M, K // 128)
+            fq.zero_()
+            fs.zero_()
+            fq[r * M_local:(r + 1) * M_local] = q
+            fs[r * M_local:(r + 1) * M_local] = s
+        native.ag_gemm_fp8(None, [h.data_ptr() for h in heaps], FLAG_OFF, x_off, xs_off, M, N, K, [w[0].data_ptr() for w in ws], K,
+                           [w[1].data_ptr() for w in ws], K // 128, [] if quant_out else [o.data_ptr() for o in outs], N,
+                           [o.data_ptr() for o in oq] if quant_out else [], [o.data_ptr() for o in os_] if quant_out else [], N,
+                           0, native.GEMM_GELU_INPLACE if quant_out else 0, ready_off, epoch, 4, ctas, 0,
+                           [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        X = torch.cat(X)
+        for r in range(world):
+            ref = X @ dequant_blocks(*ws[r]).t()
+            if quant_out:
+                ref = torch.nn.functional.gelu(ref, approximate="tanh")
+                got = dequant_rows(oq[r], os_[r])
+                # e4m3 keeps 3 mantissa bits: half a unit in the last place of the block maximum
+                assert (got - ref).abs().max().item() <= 0.07 * max(1.0, ref.abs().max().item())
+                assert torch.allclose(os_[r], ref.view(M, N // 128, 128).abs().amax(-1) / 448.0, rtol=2e-2, atol=1e-6)
+            else:
+                assert (outs[r].float() - ref).abs().max().item() < 0.02 * max(1.0, ref.abs().max().item())
+            gq = heaps[r][x_off:x_off + M * K].view(M, K)
+            gs = heaps[r][xs_off:xs_off + M * (K // 128) * 4].view(torch.float32).view(M, K // 128)
+            assert torch.equal(dequant_rows(gq, gs), X)
+
+
+@pytest.mark.parametrize("world,M_local", [(2, 128), (2, 256), (4, 128)])
+def test_gemm_rs_fp8_emulated(native, world, M_local):
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, quant_blocks, quant_rows
+    K, N = 512, 512
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(20)
+    ys = [quant_rows((torch.randn(M, K, generator=g, device="cuda") * 0.5).bfloat16()) for _ in range(world)]
+    ws = [quant_blocks((torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16()) for _ in range(world)]
+    stage_bytes = world * M_local * N * 2
+    n_flags = world * (M_local // 128) * (N // 256)
+    heaps = [torch.zeros(DATA_OFF + stage_bytes + n_flags * 8, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(M_local, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    total = sum(dequant_rows(*ys[r]) @ dequant_blocks(*ws[r]).t() for r in range(world))
+    for epoch in (1, 2):
+        native.gemm_rs_fp8(None, [h.data_ptr() for h in heaps], [y[0].data_ptr() for y in ys], K, [y[1].data_ptr() for y in ys], K // 128,
+                           [w[0].data_ptr() for w in ws], K, [w[1].data_ptr() for w in ws], K // 128, [o.data_ptr() for o in outs], N,
+                           M, N, K, DATA_OFF, DATA_OFF + stage_bytes, epoch, 148 // world, [s.data_ptr() for s in st], 0,
+                           torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        for r in range(world):
+            ref = total[r * M_local:(r + 1) * M_local]
+            assert (outs[r].float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+        for o in outs:
+            o.zero_()
+
+
 # ---------------------------------------------------------------------------------------------
 # MoE kernels
 # ---------------------------------------------------------------------------------------------

@@ -79,3 +79,40 @@ def test_cta_pair_gemm_matches_fp32_reference(M, N, K, a_t, b_t):
     bias = _rand((N,), 13)
     out = gemm(a, b, a_t=a_t, b_t=b_t, bias=bias, pair=True)
     assert (out.float() - (ref + bias.float())).abs().max().item() <= 0.02 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (384, 768, 2048), (1000, 640, 512), (72, 128, 256)])
+def test_fp8_block_scaled_gemm_matches_fp32_reference_of_the_quantised_operands(M, N, K):
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, gemm_fp8, quant_blocks, quant_rows
+    a = _rand((M, K), 3)
+    w = _rand((N, K), 4, scale=0.02)
+    # per-block magnitudes that differ by orders of magnitude, so that a wrong scale index shows
+    a = (a.float() * torch.logspace(-2, 2, K // 128, device="cuda").repeat_interleave(128)[None, :]).bfloat16()
+    aq, a_s = quant_rows(a)
+    wq, w_s = quant_blocks(w)
+    out32 = gemm_fp8(aq, a_s, wq, w_s, out_dtype=torch.float32)
+    check_status("gemm_fp8")
+    ref = dequant_rows(aq, a_s) @ dequant_blocks(wq, w_s).t()
+    scale = max(1.0, ref.abs().max().item())
+    # the kernel's sum is exact products of e4m3 values accumulated in fp32: only the order differs
+    assert (out32 - ref).abs().max().item() <= 2e-3 * scale
+    out = gemm_fp8(aq, a_s, wq, w_s)
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * scale
+    # and the quantised product stays close to the bf16 one
+    full = a.float() @ w.float().t()
+    assert (ref - full).abs().max().item() <= 0.08 * full.abs().max().item()
+
+
+def test_fp8_gemm_bias_and_accumulate():
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, gemm_fp8, quant_blocks, quant_rows
+    M, N, K = 256, 384, 512
+    aq, a_s = quant_rows(_rand((M, K), 5))
+    wq, w_s = quant_blocks(_rand((N, K), 6, scale=0.05))
+    bias = _rand((N,), 7)
+    ref = dequant_rows(aq, a_s) @ dequant_blocks(wq, w_s).t()
+    out = torch.ones((M, N), device="cuda", dtype=torch.float32)
+    gemm_fp8(aq, a_s, wq, w_s, out=out, bias=bias, accumulate=True)
+    check_status("gemm_fp8")
+    assert (out - (ref + bias.float()[None, :] + 1.0)).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
