@@ -166,6 +166,7 @@ def main() -> None:
                        "params": n_params, "global_batch": world * B, "seq_len": S, "parallelism": f"dp{world}",
                        "bucket_mb": args.bucket_mb, "optimizer": "sharded AdamW (ZeRO-1) + parameter all-gather",
                        "transport": "nvls" if eng.has_nvls else ("p2p" if world > 1 else "local"),
+                       "grad_rs_schedule": dp.schedule,
                        "l2": "no flush: each step streams >20 GB of weights/activations, far above the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": max(e2e_ms, wall_ms) / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4},

@@ -99,6 +99,21 @@ void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
   max_width_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_MAX_SMS", 32));
   host_id_ = readHostId();
   buildLayout(heap_bytes);
+  if (device_ == "cuda" && world_ > 1) {
+    // Size the heap in units of the RECOMMENDED multicast granularity (the minimum one still binds, but
+    // leaves the multicast mapping on small pages); PCCL_HEAP_ALIGN_MB overrides, 0 keeps 2 MiB.
+    auto* cdev = static_cast<CudaDevice*>(dev.get());
+    size_t g = 0;
+    const int64_t forced = LaunchEnvironments::getInt("PCCL_HEAP_ALIGN_MB", -1);
+    if (forced > 0) g = static_cast<size_t>(forced) * kMiB;
+    else if (forced < 0 && cdev->multicastSupported()) {
+      try {
+        g = cdev->multicastGranularity(world_, layout_.total, true);
+        PCCL_LOG_INFO("multicast granularity: minimum %zu, recommended %zu bytes", cdev->multicastGranularity(world_, layout_.total, false), g);
+      } catch (const std::exception&) { g = 0; }
+    }
+    if (g >= 2 * kMiB && g <= 1024 * kMiB) layout_.total = alignUp(layout_.total, g);
+  }
   heap_ = static_cast<char*>(dev->allocateIpcBuffer(layout_.total, &heap_handle_));
   uint64_t ctl = layout_.user_off - layout_.signal_off;
   if (device_ == "cuda") {

@@ -159,7 +159,13 @@ int CudaDevice::deviceOrdinal() { return static_cast<int>(currentDevice()); }
 void* CudaDevice::mapHandle(unsigned long long h, size_t bytes) {
   CUdevice dev = currentDevice();
   CUdeviceptr va = 0;
-  check(drv().MemAddressReserve(&va, bytes, 0, 0, 0), "cuMemAddressReserve");
+  // a mapping whose size allows it is aligned to 512 MiB (or its largest power-of-two divisor), so that the
+  // driver is free to back it with its largest pages
+  size_t align = 0;
+  for (size_t a = 512ull << 20; a >= (2ull << 20); a >>= 1)
+    if (bytes % a == 0) { align = a; break; }
+  if (drv().MemAddressReserve(&va, bytes, align, 0, 0) != CUDA_SUCCESS)
+    check(drv().MemAddressReserve(&va, bytes, 0, 0, 0), "cuMemAddressReserve");
   CUresult r = drv().MemMap(va, bytes, 0, h, 0);
   if (r != CUDA_SUCCESS) {
     drv().MemAddressFree(va, bytes);
@@ -326,13 +332,14 @@ bool CudaDevice::multicastSupported() {
   return mc != 0;
 }
 
-size_t CudaDevice::multicastGranularity(int num_devices, size_t bytes) {
+size_t CudaDevice::multicastGranularity(int num_devices, size_t bytes, bool recommended) {
   CUmulticastObjectProp p{};
   p.numDevices = static_cast<unsigned>(num_devices);
   p.size = bytes;
   p.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
   size_t g = 0;
-  check(drv().MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_MINIMUM), "cuMulticastGetGranularity");
+  check(drv().MulticastGetGranularity(&g, &p, recommended ? CU_MULTICAST_GRANULARITY_RECOMMENDED : CU_MULTICAST_GRANULARITY_MINIMUM),
+        "cuMulticastGetGranularity");
   return g;
 }
 

@@ -36,7 +36,7 @@ class CudaDevice : public DeviceBase {
 
   // ---- NVLS multicast ------------------------------------------------------------------------
   bool multicastSupported();
-  size_t multicastGranularity(int num_devices, size_t bytes);
+  size_t multicastGranularity(int num_devices, size_t bytes, bool recommended = false);
   // Rank 0: create the object for `num_devices` GPUs; returns a handle document for the others.
   std::string multicastCreate(size_t bytes, int num_devices);
   // Every rank (rank 0 passes its own document): import and add this process's device.

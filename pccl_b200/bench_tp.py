@@ -18,8 +18,8 @@ import torch.distributed as dist
 
 from .engine import Engine
 from .ops import check_status
-from .ops.fused_tp import AllGatherGemm, GemmReduceScatter
-from .ops.gemm import gemm
+from .ops.fused_tp import AllGatherGemm, AllGatherGemmFp8, GemmReduceScatter, GemmReduceScatterFp8
+from .ops.gemm import gemm, gemm_fp8, quant_blocks, quant_rows
 from .utils import L2Flusher
 
 
@@ -43,7 +43,7 @@ def _time(fn, iters, warmup, flush):
 
 
 def run(eng: Engine, tokens: int, d_model: int, d_ff: int, iters: int = 20, warmup: int = 5, n_copy: int = 16,
-        peak_tflops: float = 1701.7, link_gbs: float = 770.0):
+        peak_tflops: float = 1701.7, link_gbs: float = 770.0, fp8: bool = True):
     world, rank = eng.world, eng.rank
     n1 = d_ff // world
     m_local = tokens // world
@@ -108,6 +108,104 @@ def run(eng: Engine, tokens: int, d_model: int, d_ff: int, iters: int = 20, warm
                  "nccl_plus_cublas_us": base, "cublas_gemm_us": gemm_cublas, "own_gemm_us": gemm_ours,
                  "nccl_reduce_scatter_us": comm_only, "speedup_vs_nccl_cublas": base / fused, "roofline_us": roof,
                  "fraction_of_roofline": roof / fused, "max_abs_diff_vs_baseline": err})
+    if fp8:
+        rows += run_fp8(eng, tokens, d_model, d_ff, x_local, w1, w2, h, iters, warmup, n_copy, link_gbs, flush)
+    return rows
+
+
+def _scaled_mm_us(a_q, b_q, iters, warmup, flush):
+    """cuBLASLt fp8 with ONE scale per tensor (torch._scaled_mm): the library's fp8 GEMM on this box; it has no
+    1x128 / 128x128 block-scaled form here, so this is a speed reference only, not the same arithmetic."""
+    one = torch.ones((), device="cuda")
+    a8, b8 = a_q.view(torch.float8_e4m3fn), b_q.view(torch.float8_e4m3fn)
+    try:
+        return _time(lambda: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), iters, warmup, flush)
+    except Exception:       # noqa: BLE001 - an unsupported shape or build leaves the reference out
+        return None
+
+
+def run_fp8(eng, tokens, d_model, d_ff, x_local, w1, w2, h, iters, warmup, n_copy, link_gbs, flush):
+    """Block-scaled fp8 (1x128 activations, 128x128 weights) forms of the two fused paths."""
+    world = eng.world
+    n1 = d_ff // world
+    m_local = tokens // world
+    rows = []
+    w1q, w1s = quant_blocks(w1)
+    w2q, w2s = quant_blocks(w2)
+    # ---- all-gather -> GEMM -------------------------------------------------------------------
+    ag = AllGatherGemmFp8(eng, tokens, d_model, n_copy=max(2, n_copy // 2))
+    ag.quantize_local(x_local)
+    y = torch.empty(tokens, n1, dtype=torch.bfloat16, device="cuda")
+    xg = torch.empty(tokens, d_model, dtype=torch.bfloat16, device="cuda")
+    xgq = torch.empty(tokens, d_model, dtype=torch.uint8, device="cuda")
+    xgs = torch.empty(tokens, d_model // 128, dtype=torch.float32, device="cuda")
+    y_ref = torch.empty_like(y)
+    xq_l, xs_l = ag.xq_local.clone(), ag.xs_local.clone()
+
+    def nccl_bf16():
+        dist.all_gather_into_tensor(xg, x_local)
+        torch.matmul(xg, w1.t(), out=y_ref)
+
+    def nccl_fp8_then_own_gemm():
+        dist.all_gather_into_tensor(xgq, xq_l)
+        dist.all_gather_into_tensor(xgs, xs_l)
+        gemm_fp8(xgq, xgs, w1q, w1s, out=y_ref)
+
+    fused = _time(lambda: ag(w1q, w1s, out=y), iters, warmup, flush)
+    check_status("ag_gemm_fp8")
+    fused_q = _time(lambda: ag(w1q, w1s, gelu=True, quant_out=True), iters, warmup, flush)
+    base = _time(nccl_bf16, iters, warmup, flush)
+    unfused = _time(nccl_fp8_then_own_gemm, iters, warmup, flush)
+    torch.cuda.synchronize()
+    err = (y.float() - y_ref.float()).abs().max().item()
+    own = _time(lambda: gemm_fp8(xgq, xgs, w1q, w1s, out=y_ref), iters, warmup, flush)
+    lt = _scaled_mm_us(xgq, w1q, iters, warmup, flush)
+    flops = 2.0 * tokens * n1 * d_model
+    comm_bytes = (world - 1) * m_local * (d_model + d_model // 128 * 4)
+    peak = flops / (lt * 1e-6) if lt else None
+    roof = max(flops / peak if peak else 0.0, comm_bytes / (link_gbs * 1e9)) * 1e6
+    rows.append({"op": "allgather_gemm_fp8", "n_gpus": world, "M": tokens, "N": n1, "K": d_model, "fused_us": fused,
+                 "fused_gelu_quant_out_us": fused_q, "nccl_bf16_plus_cublas_bf16_us": base, "nccl_fp8_plus_own_fp8_gemm_us": unfused,
+                 "own_fp8_gemm_us": own, "cublaslt_fp8_tensorwise_gemm_us": lt, "speedup_vs_nccl_cublas_bf16": base / fused,
+                 "speedup_vs_unfused_fp8": unfused / fused, "roofline_us": roof, "fraction_of_roofline": roof / fused,
+                 "roofline_note": "compute term at the measured cuBLASLt tensorwise-fp8 rate of the same shape",
+                 "max_abs_diff_vs_unfused": err})
+
+    # ---- GEMM -> reduce-scatter ---------------------------------------------------------------
+    rs = GemmReduceScatterFp8(eng, tokens, d_model)
+    hq, hs = quant_rows(h)
+    z = torch.empty(m_local, d_model, dtype=torch.bfloat16, device="cuda")
+    part = torch.empty(tokens, d_model, dtype=torch.bfloat16, device="cuda")
+    z_ref = torch.empty_like(z)
+
+    def nccl_bf16_rs():
+        torch.matmul(h, w2.t(), out=part)
+        dist.reduce_scatter_tensor(z_ref, part)
+
+    def own_gemm_then_nccl():
+        gemm_fp8(hq, hs, w2q, w2s, out=part)
+        dist.reduce_scatter_tensor(z_ref, part)
+
+    fused = _time(lambda: rs(hq, hs, w2q, w2s, out=z), iters, warmup, flush)
+    check_status("gemm_rs_fp8")
+    base = _time(nccl_bf16_rs, iters, warmup, flush)
+    unfused = _time(own_gemm_then_nccl, iters, warmup, flush)
+    own = _time(lambda: gemm_fp8(hq, hs, w2q, w2s, out=part), iters, warmup, flush)
+    lt = _scaled_mm_us(hq, w2q, iters, warmup, flush)
+    own_gemm_then_nccl()
+    rs(hq, hs, w2q, w2s, out=z)
+    torch.cuda.synchronize()
+    err = (z.float() - z_ref.float()).abs().max().item()
+    flops = 2.0 * tokens * d_model * n1
+    comm_bytes = (world - 1) * m_local * d_model * 2
+    peak = flops / (lt * 1e-6) if lt else None
+    roof = max(flops / peak if peak else 0.0, comm_bytes / (link_gbs * 1e9)) * 1e6
+    rows.append({"op": "gemm_reduce_scatter_fp8", "n_gpus": world, "M": tokens, "N": d_model, "K": n1, "fused_us": fused,
+                 "nccl_bf16_plus_cublas_bf16_us": base, "own_fp8_gemm_plus_nccl_us": unfused, "own_fp8_gemm_us": own,
+                 "cublaslt_fp8_tensorwise_gemm_us": lt, "speedup_vs_nccl_cublas_bf16": base / fused,
+                 "speedup_vs_unfused_fp8": unfused / fused, "roofline_us": roof, "fraction_of_roofline": roof / fused,
+                 "roofline_note": "compute term at the measured cuBLASLt tensorwise-fp8 rate of the same shape",
+                 "max_abs_diff_vs_unfused": err})
     return rows
 
 
@@ -118,6 +216,7 @@ def main():
     ap.add_argument("--d-ff", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--n-copy", type=int, default=16)
+    ap.add_argument("--no-fp8", action="store_true")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -125,7 +224,7 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
     os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
     eng = Engine(rank, world)
-    heap = 3 * args.tokens * args.d_model * 2 + (1 << 30)
+    heap = 5 * args.tokens * args.d_model * 2 + (1 << 30)
     eng.initEngine("cuda", heap_bytes=heap)
     eng.connect()
     peaks = {}
@@ -135,7 +234,7 @@ def main():
     except OSError:
         pass
     rows = run(eng, args.tokens, args.d_model, args.d_ff, iters=args.iters, n_copy=args.n_copy,
-               peak_tflops=float(peaks.get("bf16_tflops", 1590.0)))
+               peak_tflops=float(peaks.get("bf16_tflops", 1590.0)), fp8=not args.no_fp8)
     if rank == 0:
         for r in rows:
             print(json.dumps(r), flush=True)

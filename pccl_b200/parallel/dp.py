@@ -48,7 +48,14 @@ class ShardedDataParallel:
 
     def __init__(self, model: nn.Module, engine: Optional[Engine] = None, *, lr: float = 3e-4, betas=(0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, bucket_mb: float = 25.0, heap_bytes: int = 0,
-                 comm_blocks: Optional[int] = None, algo: str = "auto", group=None, fuse_optimizer: bool = True):
+                 comm_blocks: Optional[int] = None, algo: str = "auto", group=None, fuse_optimizer: bool = True,
+                 schedule: str = "auto", topology=None):
+        """``schedule``: "auto" asks the MILP synthesiser (pccl_b200.synth) for the reduce-scatter schedule of one
+        bucket on ``topology`` (default: this world behind an NVSwitch at the measured port bandwidth).  When the
+        optimum is the one-step direct exchange -- it is on NVSwitch -- the hand-written kernel that fuses that
+        exchange with scaling and AdamW runs it; a multi-step optimum (a ring or a partial mesh) is registered
+        with the engine and executed by the interpreter kernel, followed by the unfused optimizer.  "fused" and
+        "interpreter" force one or the other."""
         self.model = model
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.algo = algo
@@ -76,8 +83,30 @@ class ShardedDataParallel:
         self.comm_blocks = comm_blocks if comm_blocks else (128 if engine.world == 1 else 64)
         self.comm_stream = torch.cuda.Stream(priority=-1)
         self.step_count = 0
+        self._plan_schedule(int(bucket_mb * (1 << 20)), schedule, topology)
         self._build_buckets(params, int(bucket_mb * (1 << 20)) // 2)
         self._ready_events: Dict[int, torch.cuda.Event] = {}
+
+    # ------------------------------------------------------------------------------------------
+    def _plan_schedule(self, bucket_bytes: int, schedule: str, topology) -> None:
+        self.schedule = {"source": "none", "mode": "fused"}
+        self.interpreted = False
+        if self.world == 1:
+            return
+        if schedule not in ("auto", "fused", "interpreter"):
+            raise ValueError("ShardedDataParallel: schedule must be auto, fused or interpreter")
+        from ..synth import Topology, synthesize
+        topo = topology or Topology.nvswitch(self.world)
+        # deterministic, so every rank arrives at the same schedule without exchanging it
+        res = synthesize("reduce_scatter", topo, bucket_bytes, chunks=1, time_limit=10.0)
+        direct = res.steps_used == 1 and len(res.sends[0]) == self.world * (self.world - 1)
+        self.interpreted = schedule == "interpreter" or (schedule == "auto" and not direct)
+        self.schedule = {"source": "milp", "topology": topo.name, "steps": res.steps_used, "direct": direct,
+                         "objective_us": res.objective_seconds * 1e6, "lower_bound_us": res.lower_bound_seconds * 1e6,
+                         "mode": "interpreter" if self.interpreted else "fused"}
+        if self.interpreted:
+            self.engine.regOp("dp_grad_reduce_scatter", res.ir)
+            self.fuse_optimizer = False
 
     # ------------------------------------------------------------------------------------------
     def _build_buckets(self, params: List[nn.Parameter], cap_elems: int) -> None:
@@ -131,6 +160,8 @@ class ShardedDataParallel:
             b.exp_avg = torch.zeros_like(b.master)
             b.exp_avg_sq = torch.zeros_like(b.master)
             b.grad_shard = torch.empty_like(b.master)
+            if self.interpreted:
+                b.rs_out = eng.symmetric_tensor((shard,), torch.bfloat16, align=256)
             base += b.numel
         torch.cuda.synchronize()
 
@@ -162,6 +193,12 @@ class ShardedDataParallel:
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream())
         self.comm_stream.wait_event(ev)
+        if self.interpreted:
+            # the synthesised multi-step schedule, run by the interpreter kernel; scale and cast follow
+            self.engine.exeOp("dp_grad_reduce_scatter", b.grads, b.rs_out, width=4, lane=1, stream=self.comm_stream)
+            with torch.cuda.stream(self.comm_stream):
+                torch.mul(b.rs_out, 1.0 / self.world, out=b.grad_shard)
+            return
         if not self.fuse_optimizer:
             coll.reduce_scatter(self.engine, b.grads, b.grad_shard, scale=1.0 / self.world, algo=self.algo,
                                 blocks=self.comm_blocks, lane=1, stream=self.comm_stream)

@@ -149,6 +149,34 @@ def case_dp(eng, rank, world):
     return {"losses": lt.tolist()}
 
 
+def case_dp_milp_ring(eng, rank, world):
+    """Gradient reduce-scatter by a MILP-synthesised multi-step schedule (ring topology forced) that the
+    interpreter kernel executes: training proceeds and every rank ends with the same parameters."""
+    from pccl_b200.models import GPT, GPTConfig
+    from pccl_b200.parallel import ShardedDataParallel
+    from pccl_b200.synth import Topology
+    cfg = GPTConfig.tiny()
+    torch.manual_seed(0)
+    model = GPT(cfg, device="cuda")
+    dp = ShardedDataParallel(model, eng, lr=1e-3, bucket_mb=0.25, topology=Topology.ring(world))
+    assert dp.schedule["source"] == "milp"
+    if world > 2:
+        assert dp.interpreted and dp.schedule["steps"] > 1, dp.schedule
+    g = torch.Generator().manual_seed(5)
+    data = torch.randint(0, cfg.vocab_size, (2 * world, cfg.seq_len + 1), generator=g)
+    mine = data[2 * rank:2 * rank + 2].cuda()
+    losses = [float(dp.train_step(mine[:, :-1], mine[:, 1:])) for _ in range(3)]
+    torch.cuda.synchronize()
+    eng.raise_on_status(1, "interpreted reduce-scatter")
+    flat = dp.flat_params.float()
+    ref = flat.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(ref, flat), "ranks disagree on the parameters after the all-gather"
+    lt = torch.tensor(losses, device="cuda"); dist.all_reduce(lt); lt /= world
+    assert lt[-1] < lt[0], f"mean loss did not go down: {lt.tolist()}"
+    return {"losses": lt.tolist(), "schedule": dp.schedule}
+
+
 def case_fused_tp(eng, rank, world):
     """all-gather -> GEMM and GEMM -> reduce-scatter against gathered/reduced fp32 references."""
     from pccl_b200.ops import check_status
@@ -185,6 +213,47 @@ def case_fused_tp(eng, rank, world):
         ref = total[rank * M_local:(rank + 1) * M_local]
         err = (out.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
         assert err < 0.03, f"gemm_rs iteration {it}: {err}"
+        dist.barrier()
+    return {"ok": True}
+
+
+def case_fused_tp_fp8(eng, rank, world):
+    """Block-scaled fp8 forms of the two fused paths, chained like an MLP: AG->GEMM (+GELU, quantised output) -> GEMM->RS."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.fused_tp import AllGatherGemmFp8, GemmReduceScatterFp8
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, quant_blocks, quant_rows
+    M_local, K, N = 256, 1024, 512
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(23)
+    xs = [(torch.randn(M_local, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+    w1 = [(torch.randn(N, K, generator=g, device="cuda") * 0.05).bfloat16() for _ in range(world)]
+    w2 = [(torch.randn(K, N, generator=g, device="cuda") * 0.05).bfloat16() for _ in range(world)]
+    w1q, w1s = quant_blocks(w1[rank])
+    w2q, w2s = quant_blocks(w2[rank])
+    ag = AllGatherGemmFp8(eng, M, K, n_copy=4)
+    rs = GemmReduceScatterFp8(eng, M, K)
+    for it in range(3):
+        ag.quantize_local((xs[rank].float() * (it + 1)).bfloat16())
+        y = ag(w1q, w1s)
+        hq, hs = ag(w1q, w1s, gelu=True, quant_out=True)
+        z = rs(hq, hs, w2q, w2s)
+        torch.cuda.synchronize()
+        check_status("fused fp8")
+        X = torch.cat([dequant_rows(*quant_rows((x.float() * (it + 1)).bfloat16())) for x in xs])
+        assert torch.equal(dequant_rows(ag.xq_full, ag.xs_full), X), "gathered fp8 X differs"
+        ref = X @ dequant_blocks(w1q, w1s).t()
+        err = (y.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        assert err < 0.02, f"ag_gemm fp8 iteration {it}: {err}"
+        # second GEMM: every rank's partial from ITS quantised hidden activations, summed over ranks
+        mine = dequant_rows(hq, hs) @ dequant_blocks(w2q, w2s).t()
+        total = mine.clone()
+        dist.all_reduce(total)
+        refz = total[rank * M_local:(rank + 1) * M_local]
+        errz = (z.float() - refz).abs().max().item() / max(1.0, refz.abs().max().item())
+        assert errz < 0.03, f"gemm_rs fp8 iteration {it}: {errz}"
+        href = torch.nn.functional.gelu(ref, approximate="tanh")
+        errh = (dequant_rows(hq, hs) - href).abs().max().item() / max(1.0, href.abs().max().item())
+        assert errh < 0.07, f"quantised hidden iteration {it}: {errh}"
         dist.barrier()
     return {"ok": True}
 
