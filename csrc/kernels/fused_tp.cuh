@@ -42,17 +42,30 @@ __device__ __forceinline__ bool cta_peer_barrier(const World& W, int me, int lan
 // =================================================================================================
 // all-gather -> GEMM
 // =================================================================================================
+// Tile order of the all-gather GEMM: the rank's own rows first (they are there), then the remote rows
+// row block by row block -- block b of EVERY peer before block b+1 of any -- which is the order in which
+// the senders emit them, so the data keeps ahead of the tensor cores from the first remote tile on.
+// Within a row block consecutive tiles share the B panel (same n, different source rank).
 struct AgSched {
   int me, world, tiles_ml, tiles_n, first, stride;
   __device__ __forceinline__ bool get(int it, TileCoord* t) const {
     const long long idx = first + static_cast<long long>(it) * stride;
     const int per_panel = tiles_ml * tiles_n;
     if (idx >= static_cast<long long>(world) * per_panel) return false;
-    const int panel = static_cast<int>(idx / per_panel), r = static_cast<int>(idx % per_panel);
-    int src = me + panel;
+    if (idx < per_panel) {
+      const int r = static_cast<int>(idx);
+      t->m = me * tiles_ml + r % tiles_ml;
+      t->n = r / tiles_ml;
+      t->extra = me;
+      return true;
+    }
+    const long long j = idx - per_panel;
+    const int per_block = (world - 1) * tiles_n;
+    const int blk = static_cast<int>(j / per_block), rem = static_cast<int>(j % per_block);
+    int src = me + 1 + rem % (world - 1);
     if (src >= world) src -= world;
-    t->m = src * tiles_ml + r % tiles_ml;
-    t->n = r / tiles_ml;
+    t->m = src * tiles_ml + blk;
+    t->n = rem / (world - 1);
     t->extra = src;
     return true;
   }
@@ -82,53 +95,86 @@ struct AgGate {
   }
 };
 
-// Copy CTAs push this rank's rows into every peer's gathered buffer with plain 16-byte stores
-// (posted writes: no round trip per request, a handful of CTAs fills the NVLink port).  Peers are
-// served in the order in which they need the panel -- rank me-1 consumes it first, then me-2, ... --
-// so at any moment each receiver is fed by one sender.  A 128-row chunk is split across the copy
-// CTAs; each adds one to the receiver's counter for that chunk when its part has been written.
+// Copy CTAs send this rank's rows to every peer's gathered buffer, 128-row chunk by chunk; a chunk is
+// split across the copy CTAs and each adds one to the receivers' counter for that chunk when its part
+// has been written.
+//   With an NVLS multicast mapping of the heap: ONE multimem.st per 16 bytes reaches all peers (the
+//   switch replicates it), so a rank issues its rows once instead of world-1 times, and one
+//   multimem.red bumps the chunk counter on every receiver.  A few CTAs saturate the receivers' ports.
+//   Without it: plain 16-byte stores to each peer in turn (posted writes) and one counter update per peer.
+template <bool MC>
+__device__ __forceinline__ void push_store(char* dst, const dev::Vec16& v) {
+  if constexpr (MC) dev::multimem_st(dst, v);
+  else dev::st16(dst, v);
+}
+
+// Copies 16-byte vectors [lo, hi) of src to dst with the whole CTA; the loads of batch b+1 are issued
+// before the stores of batch b, so that a thread keeps 8 to 16 vectors in flight.
+template <bool MC>
+__device__ __forceinline__ void push_vecs(const char* src, char* dst, long long lo, long long hi) {
+  const long long nt = blockDim.x;
+  long long i = lo + threadIdx.x;
+  if (i + 7 * nt < hi) {
+    dev::Vec16 cur[8], nxt[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) cur[u] = dev::ld16(src + ((i + u * nt) << 4));
+    for (;;) {
+      const long long j = i + 8 * nt;
+      const bool more = j + 7 * nt < hi;
+      if (more) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) nxt[u] = dev::ld16(src + ((j + u * nt) << 4));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) push_store<MC>(dst + ((i + u * nt) << 4), cur[u]);
+      i = j;
+      if (!more) break;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) cur[u] = nxt[u];
+    }
+  }
+  for (; i < hi; i += nt) push_store<MC>(dst + (i << 4), dev::ld16(src + (i << 4)));
+}
+
 __device__ __forceinline__ void ag_push_role(const AgGemmArgs& A, const AgGemmRank& R) {
   const int me = R.rank, world = A.w.world, j = blockIdx.x;
   if (!cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 1, A.spin_ns, R.status)) return;
   const int chunks = A.M_local / BM;
   const long long row_bytes = static_cast<long long>(A.K) * (A.elem_bytes ? A.elem_bytes : 2);
-  const long long chunk_bytes = static_cast<long long>(BM) * row_bytes;
-  const long long nvec = chunk_bytes >> 4;
+  const long long nvec = (static_cast<long long>(BM) * row_bytes) >> 4;
+  const long long per = (nvec + A.n_copy - 1) / A.n_copy;
+  const long long lo = min(nvec, per * j), hi = min(nvec, per * (j + 1));
   // block-scaled operands: the 1 x 128 scales of a chunk (fp32 [128, K/128]) travel with it
   const long long svec = A.xs_off ? (static_cast<long long>(BM) * (A.K / 128) * 4) >> 4 : 0;
   const long long sper = (svec + A.n_copy - 1) / A.n_copy;
   const long long slo = min(svec, sper * j), shi = min(svec, sper * (j + 1));
-  const long long per = (nvec + A.n_copy - 1) / A.n_copy;
-  const long long lo = min(nvec, per * j), hi = min(nvec, per * (j + 1));
-  const int nt = blockDim.x;
-  for (int k = 1; k < world; ++k) {
-    int p = me - k;
-    if (p < 0) p += world;
-    for (int c = 0; c < chunks; ++c) {
-      const long long row0 = static_cast<long long>(me) * A.M_local + static_cast<long long>(c) * BM;
-      const long long off = static_cast<long long>(A.x_off) + row0 * row_bytes;
-      const char* src = A.w.heap[me] + off;
-      char* dst = A.w.heap[p] + off;
-      long long i = lo + threadIdx.x;
-      for (; i + 3 * nt < hi; i += 4 * nt) {
-        dev::Vec16 v0 = dev::ld16(src + (i << 4)), v1 = dev::ld16(src + ((i + nt) << 4));
-        dev::Vec16 v2 = dev::ld16(src + ((i + 2 * nt) << 4)), v3 = dev::ld16(src + ((i + 3 * nt) << 4));
-        dev::st16(dst + (i << 4), v0);
-        dev::st16(dst + ((i + nt) << 4), v1);
-        dev::st16(dst + ((i + 2 * nt) << 4), v2);
-        dev::st16(dst + ((i + 3 * nt) << 4), v3);
-      }
-      for (; i < hi; i += nt) dev::st16(dst + (i << 4), dev::ld16(src + (i << 4)));
-      if (svec) {
-        const long long soff = static_cast<long long>(A.xs_off) + row0 * (A.K / 128) * 4;
-        for (long long q = slo + threadIdx.x; q < shi; q += nt)
-          dev::st16(A.w.heap[p] + soff + (q << 4), dev::ld16(A.w.heap[me] + soff + (q << 4)));
-      }
+  const bool mc = A.w.mc_heap != nullptr && A.nvirt <= 1;
+  for (int c = 0; c < chunks; ++c) {
+    const long long row0 = static_cast<long long>(me) * A.M_local + static_cast<long long>(c) * BM;
+    const long long off = static_cast<long long>(A.x_off) + row0 * row_bytes;
+    const long long soff = static_cast<long long>(A.xs_off) + row0 * (A.K / 128) * 4;
+    const long long cnt_off = static_cast<long long>(A.ready_off) + static_cast<long long>(me * chunks + c) * 4;
+    if (mc) {
+      push_vecs<true>(A.w.heap[me] + off, A.w.mc_heap + off, lo, hi);
+      if (svec) push_vecs<true>(A.w.heap[me] + soff, A.w.mc_heap + soff, slo, shi);
       __syncthreads();                        // every thread's stores of this chunk part are issued
       if (threadIdx.x == 0) {
         __threadfence_system();
-        uint32_t* cnt = reinterpret_cast<uint32_t*>(A.w.heap[p] + A.ready_off) + (me * chunks + c);
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+        asm volatile("multimem.red.release.sys.global.add.u32 [%0], 1;" ::"l"(A.w.mc_heap + cnt_off) : "memory");
+      }
+    } else {
+      for (int k = 1; k < world; ++k) {
+        int p = me - k;
+        if (p < 0) p += world;
+        push_vecs<false>(A.w.heap[me] + off, A.w.heap[p] + off, lo, hi);
+        if (svec) push_vecs<false>(A.w.heap[me] + soff, A.w.heap[p] + soff, slo, shi);
+      }
+      __syncthreads();
+      if (threadIdx.x >= 1 && threadIdx.x < static_cast<uint32_t>(world)) {
+        int p = me - static_cast<int>(threadIdx.x);
+        if (p < 0) p += world;
+        __threadfence_system();
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(A.w.heap[p] + cnt_off) : "memory");
       }
     }
   }

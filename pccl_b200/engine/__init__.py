@@ -129,6 +129,7 @@ class Engine:
         """Exchange endpoint documents over an existing ``torch.distributed`` group, map every
         peer's heap and (on NVSwitch machines) bind the heap to an NVLS multicast object."""
         import torch.distributed as dist
+        self._group, self._connected_dist = group, True
         docs: List[Optional[str]] = [None] * self.world
         dist.all_gather_object(docs, self.exportEndpoint(), group=group)
         self._e.importEndpoints([d for d in docs if d is not None])
@@ -145,6 +146,18 @@ class Engine:
                 self._e.mcBind()
                 dist.barrier(group=group)
         dist.barrier(group=group)
+
+    def barrier(self) -> None:
+        """Host barrier over the ranks of this engine (device work of this rank is synchronised first).  Objects
+        that zero symmetric flags when they are built call it, so that no peer's first kernel can write
+        a flag that is cleared afterwards.  A no-op for a world of one or an engine not connected through
+        ``torch.distributed``."""
+        if self.world == 1 or not getattr(self, "_connected_dist", False):
+            return
+        import torch.distributed as dist
+        if self.device == "cuda":
+            torch.cuda.synchronize()
+        dist.barrier(group=self._group)
 
     # -- symmetric memory ------------------------------------------------------------------------
     def symmetric_tensor(self, shape: Sequence[int], dtype: torch.dtype, align: int = 256) -> torch.Tensor:

@@ -30,6 +30,7 @@ class AllGatherGemm:
         self.ready = eng.symmetric_tensor((rows_total // 128,), torch.int32)     # peers bump these counters
         self.ready.zero_()
         torch.cuda.synchronize()
+        eng.barrier()
         self.epoch = 0
         self.n_copy = n_copy if eng.world > 1 else 0
         self.ctas = ctas or C.sm_count()
@@ -63,6 +64,7 @@ class GemmReduceScatter:
         self.flags = eng.symmetric_tensor((eng.world, (m_local // 128) * (n // 256)), torch.int64)
         self.flags.zero_()
         torch.cuda.synchronize()
+        eng.barrier()
         self.epoch = 0
         self.ctas = ctas or C.sm_count()
 
@@ -101,6 +103,7 @@ class AllGatherGemmFp8:
         self.ready = eng.symmetric_tensor((rows_total // 128,), torch.int32)
         self.ready.zero_()
         torch.cuda.synchronize()
+        eng.barrier()
         self.epoch = 0
         self.n_copy = n_copy if eng.world > 1 else 0
         self.ctas = ctas or C.sm_count()
@@ -150,6 +153,7 @@ class GemmReduceScatterFp8:
         self.flags = eng.symmetric_tensor((eng.world, (m_local // 128) * (n // 256)), torch.int64)
         self.flags.zero_()
         torch.cuda.synchronize()
+        eng.barrier()
         self.epoch = 0
         self.ctas = ctas or C.sm_count()
 

@@ -2,6 +2,7 @@
 `ncu` captures (a few hundred MB on the device, a handful of launches):
 
     python -m pccl_b200.profile_targets ag_gemm   [--world 2 --rows 1024 --k 8192 --n 3584]
+    python -m pccl_b200.profile_targets ag_gemm_fp8 [--world 2 --rows 1024 --k 8192 --n 3584]
     python -m pccl_b200.profile_targets gemm_rs   [--world 2 --rows 1024 --k 3584 --n 8192]
     python -m pccl_b200.profile_targets allreduce [--world 4 --mbytes 64]
     python -m pccl_b200.profile_targets moe       [--world 2 --tokens 2048 --hidden 7168]
@@ -54,6 +55,39 @@ def ag_gemm(a):
                       torch.cuda.current_stream().cuda_stream)
     print({"op": "ag_gemm", "world": w, "M": M, "N": N, "K": K, "ctas_per_rank": ctas, "us": _timed(run, a.iters)})
     _check(st)
+
+
+def ag_gemm_fp8(a):
+    """The block-scaled fp8 all-gather GEMM, emulated ranks, next to the plain fp8 GEMM of one rank's shape on the
+    same number of CTAs (what the fused kernel would cost if the rows were already there)."""
+    from .ops.gemm import gemm_fp8, quant_blocks, quant_rows
+    w, ml, K, N = a.world, a.rows, a.k, a.n
+    M = ml * w
+    xs_off = DATA_OFF + M * K
+    ready_off = xs_off + M * (K // 128) * 4
+    heaps = [torch.zeros(ready_off + 4096, dtype=torch.uint8, device="cuda") for _ in range(w)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(w)]
+    ws = [quant_blocks((torch.randn(N, K, device="cuda") * 0.02).bfloat16()) for _ in range(w)]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(w)]
+    for r in range(w):
+        q, s_ = quant_rows(torch.randn(ml, K, device="cuda").bfloat16())
+        heaps[r][DATA_OFF:xs_off].view(M, K)[r * ml:(r + 1) * ml] = q
+        heaps[r][xs_off:ready_off].view(torch.float32).view(M, K // 128)[r * ml:(r + 1) * ml] = s_
+    ctas = (C.sm_count() // w) & ~1
+    ep = [0]
+
+    def run():
+        ep[0] += 1
+        C.ag_gemm_fp8(None, [h.data_ptr() for h in heaps], FLAG_OFF, DATA_OFF, xs_off, M, N, K, [x[0].data_ptr() for x in ws], K,
+                      [x[1].data_ptr() for x in ws], K // 128, [o.data_ptr() for o in outs], N, [], [], 0, 0, 0, ready_off, ep[0],
+                      a.n_copy if w > 1 else 0, ctas, 0, [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream)
+    fused = _timed(run, a.iters)
+    _check(st)
+    aq = heaps[0][DATA_OFF:xs_off].view(M, K)
+    a_s = heaps[0][xs_off:ready_off].view(torch.float32).view(M, K // 128)
+    plain = _timed(lambda: gemm_fp8(aq, a_s, ws[0][0], ws[0][1], out=outs[0], sms=ctas - (a.n_copy if w > 1 else 0)), a.iters)
+    print({"op": "ag_gemm_fp8", "world": w, "M": M, "N": N, "K": K, "ctas_per_rank": ctas, "us": fused,
+           "plain_fp8_gemm_one_rank_same_ctas_us": plain})
 
 
 def gemm_rs(a):
@@ -124,7 +158,7 @@ def moe(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("target", choices=["ag_gemm", "gemm_rs", "allreduce", "moe"])
+    ap.add_argument("target", choices=["ag_gemm", "ag_gemm_fp8", "gemm_rs", "allreduce", "moe"])
     ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--rows", type=int, default=1024, help="rows per rank")
     ap.add_argument("--k", type=int, default=0)
@@ -135,11 +169,11 @@ def main():
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
-    if a.target == "ag_gemm":
+    if a.target in ("ag_gemm", "ag_gemm_fp8"):
         a.k, a.n = a.k or 8192, a.n or 3584
     if a.target == "gemm_rs":
         a.k, a.n = a.k or 3584, a.n or 8192
-    {"ag_gemm": ag_gemm, "gemm_rs": gemm_rs, "allreduce": allreduce, "moe": moe}[a.target](a)
+    {"ag_gemm": ag_gemm, "ag_gemm_fp8": ag_gemm_fp8, "gemm_rs": gemm_rs, "allreduce": allreduce, "moe": moe}[a.target](a)
 
 
 if __name__ == "__main__":

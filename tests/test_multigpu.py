@@ -36,5 +36,10 @@ def test_case(case, tmp_path):
     _run(case, _world(), tmp_path)
 
 
+def test_cases_share_one_launch(tmp_path):
+    """The heap is handed back between cases, so a list of cases runs in one set of processes."""
+    _run("heap,coll_p2p", _world(), tmp_path)
+
+
 def test_collectives_without_nvls(tmp_path):
     _run("coll_p2p", _world(), tmp_path, env={"PCCL_TEST_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
