@@ -37,6 +37,29 @@ void bindGemm(py::module_& m) {
         py::arg("a"), py::arg("lda"), py::arg("sa"), py::arg("ld_sa"), py::arg("b"), py::arg("ldb"), py::arg("sb"), py::arg("ld_sb"),
         py::arg("d"), py::arg("ldd"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("flags"), py::arg("bias") = 0,
         py::arg("d2") = 0, py::arg("sms") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+  m.def("gemm_mx8",
+        [](uint64_t a, int64_t lda, uint64_t sa, int ld_sa, uint64_t b, int64_t ldb, uint64_t sb, int ld_sb, uint64_t d, int64_t ldd,
+           int M, int N, int K, uint32_t flags, uint64_t bias, uint64_t d2, int sms, uint64_t status, uint64_t stream) {
+          int err = gemmMx8(reinterpret_cast<const void*>(a), lda, reinterpret_cast<const uint8_t*>(sa), ld_sa,
+                            reinterpret_cast<const void*>(b), ldb, reinterpret_cast<const uint8_t*>(sb), ld_sb,
+                            reinterpret_cast<void*>(d), ldd, M, N, K, flags, reinterpret_cast<const void*>(bias),
+                            reinterpret_cast<void*>(d2), sms, reinterpret_cast<uint32_t*>(status),
+                            reinterpret_cast<cudaStream_t>(stream));
+          if (err != 0) throw std::runtime_error(std::string("gemm_mx8: ") + cudaErrorName(err) + " " + gemmMx8LastError());
+        },
+        py::arg("a"), py::arg("lda"), py::arg("sa"), py::arg("ld_sa"), py::arg("b"), py::arg("ldb"), py::arg("sb"), py::arg("ld_sb"),
+        py::arg("d"), py::arg("ldd"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("flags"), py::arg("bias") = 0,
+        py::arg("d2") = 0, py::arg("sms") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+  m.def("quant_mx8_rows", [](uint64_t x, uint64_t q, uint64_t s, long long rows, int k, uint64_t stream) {
+    int err = launchQuantMx8Rows(reinterpret_cast<const void*>(x), reinterpret_cast<void*>(q), reinterpret_cast<uint8_t*>(s), rows, k,
+                                 reinterpret_cast<cudaStream_t>(stream));
+    if (err != 0) throw std::runtime_error(std::string("quant_mx8_rows: ") + cudaErrorName(err));
+  });
+  m.def("quant_mx8_blocks", [](uint64_t w, uint64_t q, uint64_t s, int rows, int cols, uint64_t stream) {
+    int err = launchQuantMx8Blocks(reinterpret_cast<const void*>(w), reinterpret_cast<void*>(q), reinterpret_cast<uint8_t*>(s), rows, cols,
+                                   reinterpret_cast<cudaStream_t>(stream));
+    if (err != 0) throw std::runtime_error(std::string("quant_mx8_blocks: ") + cudaErrorName(err));
+  });
   m.def("adamw", [](uint64_t p, uint64_t mm, uint64_t v, uint64_t g, uint64_t pb, long long n, float lr, float b1, float b2,
                     float eps, float wd, int step, float grad_scale, uint64_t stream) {
     int err = launchAdamW(reinterpret_cast<float*>(p), reinterpret_cast<float*>(mm), reinterpret_cast<float*>(v),

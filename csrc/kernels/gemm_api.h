@@ -43,6 +43,16 @@ int gemmFp8(const void* A, int64_t lda, const float* sa, int ld_sa, const void* 
             cudaStream_t stream);
 const char* gemmFp8LastError();
 
+// fp8 with HARDWARE block scaling (tcgen05 kind::mxf8f6f4.block_scale): like gemmFp8, but the scales are UE8M0 bytes
+// (value 2^(byte - 127)): sa [M, ld_sa], sb [ceil(N/128), ld_sb], one byte per 128 values of K.
+int gemmMx8(const void* A, int64_t lda, const uint8_t* sa, int ld_sa, const void* B, int64_t ldb, const uint8_t* sb, int ld_sb,
+            void* D, int64_t ldd, int M, int N, int K, uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status,
+            cudaStream_t stream);
+// bf16 -> e4m3 with power-of-two scales: rows [rows, k] -> q + bytes [rows, k/128]; weights [rows, cols] -> q + bytes [rows/128, cols/128]
+int launchQuantMx8Rows(const void* x, void* q, uint8_t* scales, long long rows, int k, cudaStream_t stream);
+int launchQuantMx8Blocks(const void* w, void* q, uint8_t* scales, int rows, int cols, cudaStream_t stream);
+const char* gemmMx8LastError();
+
 const char* gemmLastError();
 
 }  // namespace pccl

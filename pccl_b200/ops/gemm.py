@@ -170,6 +170,80 @@ def gemm_fp8(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch
     return out
 
 
+def quant_rows_mx(x: torch.Tensor):
+    """bf16 [rows, K] -> (e4m3 bytes [rows, K], UE8M0 scale bytes [rows, K/128]): power-of-two scales for the
+    hardware block-scaled GEMM (``gemm_mx8``)."""
+    rows, k = x.shape
+    if k % 128 or not x.is_contiguous() or x.dtype != torch.bfloat16:
+        raise ValueError("quant_rows_mx: contiguous bf16 with K % 128 == 0")
+    q = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, k // 128), dtype=torch.uint8, device=x.device)
+    C.quant_mx8_rows(x.data_ptr(), q.data_ptr(), s.data_ptr(), rows, k, torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return q, s
+
+
+def quant_blocks_mx(w: torch.Tensor):
+    """bf16 [N, K] weights -> (e4m3 bytes, UE8M0 scale bytes [N/128, K/128])."""
+    n, k = w.shape
+    if n % 128 or k % 128 or not w.is_contiguous() or w.dtype != torch.bfloat16:
+        raise ValueError("quant_blocks_mx: contiguous bf16 with both sizes multiples of 128")
+    q = torch.empty((n, k), dtype=torch.uint8, device=w.device)
+    s = torch.empty((n // 128, k // 128), dtype=torch.uint8, device=w.device)
+    C.quant_mx8_blocks(w.data_ptr(), q.data_ptr(), s.data_ptr(), n, k, torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return q, s
+
+
+def ue8m0_to_float(s: torch.Tensor) -> torch.Tensor:
+    """2^(byte - 127) as fp32."""
+    return torch.exp2(s.float() - 127.0)
+
+
+def gemm_mx8(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, *,
+             out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+             bias: Optional[torch.Tensor] = None, gelu_inplace: bool = False, accumulate: bool = False,
+             sms: int = 0) -> torch.Tensor:
+    """``a @ b.T`` for e4m3 operands with power-of-two block scales applied by the tensor core
+    (tcgen05 ``kind::mxf8f6f4.block_scale``; csrc/kernels/gemm_mx8.cu): ``a_s`` uint8 [M, K/128], ``b_s`` uint8
+    [ceil(N/128), K/128], bytes in UE8M0 (``quant_rows_mx`` / ``quant_blocks_mx``)."""
+    for t, name in ((a_q, "a_q"), (b_q, "b_q")):
+        if not t.is_cuda or t.element_size() != 1 or t.dim() != 2 or t.stride(1) != 1 or t.stride(0) % 16 or t.data_ptr() % 16:
+            raise ValueError(f"gemm_mx8: {name} must be 2-D one-byte elements, unit inner stride, 16-byte aligned rows")
+    M, K = a_q.shape
+    N, Kb = b_q.shape
+    if K != Kb or K % 128:
+        raise ValueError("gemm_mx8: inner sizes must agree and be a multiple of 128")
+    if a_s.dtype != torch.uint8 or a_s.shape != (M, K // 128) or a_s.stride(1) != 1:
+        raise ValueError("gemm_mx8: a_s must be uint8 [M, K/128]")
+    if b_s.dtype != torch.uint8 or b_s.shape != ((N + 127) // 128, K // 128) or b_s.stride(1) != 1:
+        raise ValueError("gemm_mx8: b_s must be uint8 [ceil(N/128), K/128]")
+    if out is None:
+        ldd = (N + 7) // 8 * 8
+        store = torch.empty((M, ldd), dtype=out_dtype, device=a_q.device)
+        out = store[:, :N] if ldd != N else store
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError("gemm_mx8: out must be [M,N] bf16/fp32 with unit inner stride")
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= C.GEMM_OUT_F32
+    if accumulate:
+        flags |= C.GEMM_ACCUMULATE
+    if gelu_inplace:
+        flags |= C.GEMM_GELU_INPLACE
+    bias_ptr = 0
+    if bias is not None:
+        if bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous():
+            raise ValueError("gemm_mx8: bias must be a contiguous bf16 vector of length N")
+        flags |= C.GEMM_BIAS
+        bias_ptr = bias.data_ptr()
+    C.gemm_mx8(a_q.data_ptr(), a_q.stride(0), a_s.data_ptr(), a_s.stride(0), b_q.data_ptr(), b_q.stride(0), b_s.data_ptr(),
+               b_s.stride(0), out.data_ptr(), out.stride(0), M, N, K, flags, bias_ptr, 0, sms,
+               status_words(a_q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return out
+
+
 def dequant_rows(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     """fp32 values of a 1 x 128 block-scaled e4m3 tensor (reference for tests; tensor ops)."""
     v = q.view(torch.float8_e4m3fn).float()
@@ -209,10 +283,12 @@ if __name__ == "__main__":      # python -m pccl_b200.ops.gemm --m 4096 --n 4096
     ap.add_argument("--b-t", action="store_true")
     ap.add_argument("--pair", action="store_true")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 operands (1x128 / 128x128 scales)")
+    ap.add_argument("--mx", action="store_true", help="with --fp8: power-of-two scales applied by the tensor core")
     a_ = ap.parse_args()
     if a_.fp8:
-        Aq, As = quant_rows(torch.randn((a_.m, a_.k), device="cuda").bfloat16())
-        Bq, Bs = quant_blocks((torch.randn((a_.n, a_.k), device="cuda") * 0.02).bfloat16())
+        qr, qb, gemm_fp8 = (quant_rows_mx, quant_blocks_mx, gemm_mx8) if a_.mx else (quant_rows, quant_blocks, gemm_fp8)
+        Aq, As = qr(torch.randn((a_.m, a_.k), device="cuda").bfloat16())
+        Bq, Bs = qb((torch.randn((a_.n, a_.k), device="cuda") * 0.02).bfloat16())
         D = torch.empty((a_.m, a_.n), device="cuda", dtype=torch.bfloat16)
         torch.cuda.synchronize()
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(a_.iters + 1)]
@@ -223,7 +299,7 @@ if __name__ == "__main__":      # python -m pccl_b200.ops.gemm --m 4096 --n 4096
         torch.cuda.synchronize()
         check_status("gemm_fp8")
         ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(a_.iters)]
-        print({"fp8": True, "ms": ms, "tflops": [2 * a_.m * a_.n * a_.k / t / 1e9 for t in ms]})
+        print({"fp8": True, "mx": a_.mx, "ms": ms, "tflops": [2 * a_.m * a_.n * a_.k / t / 1e9 for t in ms]})
         raise SystemExit(0)
     A = torch.randn((a_.k, a_.m) if a_.a_t else (a_.m, a_.k), device="cuda").bfloat16()
     B = torch.randn((a_.k, a_.n) if a_.b_t else (a_.n, a_.k), device="cuda").bfloat16()

@@ -116,3 +116,39 @@ def test_fp8_gemm_bias_and_accumulate():
     gemm_fp8(aq, a_s, wq, w_s, out=out, bias=bias, accumulate=True)
     check_status("gemm_fp8")
     assert (out - (ref + bias.float()[None, :] + 1.0)).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item())
+
+
+def test_mx_quantisers_give_power_of_two_scales_that_cover_the_block():
+    from pccl_b200.ops.gemm import dequant_rows, quant_blocks_mx, quant_rows_mx, ue8m0_to_float
+    x = _rand((200, 512), 11, scale=3.0)
+    q, s = quant_rows_mx(x)
+    sc = ue8m0_to_float(s)
+    amax = x.float().view(200, 4, 128).abs().amax(-1)
+    assert torch.all(sc * 448.0 >= amax) and torch.all(sc * 224.0 < amax.clamp_min(1e-30) * 1.0000001)
+    back = dequant_rows(q, sc)
+    assert (back - x.float()).abs().max().item() <= 0.07 * x.float().abs().max().item()
+    w = _rand((256, 384), 12, scale=0.02)
+    qw, sw = quant_blocks_mx(w)
+    amaxw = w.float().view(2, 128, 3, 128).abs().amax((1, 3))
+    assert torch.all(ue8m0_to_float(sw) * 448.0 >= amaxw)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 256, 512), (256, 512, 1024), (384, 768, 2048), (1000, 640, 640), (72, 128, 256)])
+def test_mx_fp8_gemm_matches_fp32_reference_of_the_quantised_operands(M, N, K):
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, gemm_mx8, quant_blocks_mx, quant_rows_mx, ue8m0_to_float
+    a = _rand((M, K), 13)
+    w = _rand((N, K), 14, scale=0.02)
+    # magnitudes that differ per K block AND per row group / column block, so that a wrong scale index shows
+    a = (a.float() * torch.logspace(-2, 2, K // 128, device="cuda").repeat_interleave(128)[None, :]
+         * (1.0 + (torch.arange(M, device="cuda") // 32 % 4).float())[:, None]).bfloat16()
+    w = (w.float() * (1.0 + 3.0 * (torch.arange(N, device="cuda") // 128).float())[:, None]).bfloat16()
+    aq, a_s = quant_rows_mx(a)
+    wq, w_s = quant_blocks_mx(w)
+    out32 = gemm_mx8(aq, a_s, wq, w_s, out_dtype=torch.float32)
+    check_status("gemm_mx8")
+    ref = dequant_rows(aq, ue8m0_to_float(a_s)) @ dequant_blocks(wq, ue8m0_to_float(w_s)).t()
+    scale = max(1.0, ref.abs().max().item())
+    assert (out32 - ref).abs().max().item() <= 2e-3 * scale
+    out = gemm_mx8(aq, a_s, wq, w_s)
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * scale
