@@ -145,7 +145,7 @@ void bindFused(py::module_& m) {
                           int K, const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& w_scale, int ld_ws,
                           const std::vector<uint64_t>& d, int64_t ldd, const std::vector<uint64_t>& dq, const std::vector<uint64_t>& ds,
                           int64_t ldq, uint64_t bias, uint32_t flags, uint64_t ready_off, uint64_t epoch, int n_copy, int ctas,
-                          int flag_lane, const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream) {
+                          int flag_lane, const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream, bool mx) {
     AgGemmArgs A{};
     const int n = e ? 1 : static_cast<int>(heaps.size());
     A.w = e ? e->worldTable() : emuWorld2(heaps, flag_off);
@@ -167,11 +167,12 @@ void bindFused(py::module_& m) {
       A.r[r].rank = e ? e->rank() : r;
       h[r] = AgGemmHost{reinterpret_cast<const void*>(w.at(r)), ldw, false};
     }
-    check(launchAgGemmFp8(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "ag_gemm_fp8");
+    check(mx ? launchAgGemmMx8(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream))
+             : launchAgGemmFp8(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "ag_gemm_fp8");
   }, py::arg("engine").none(true), py::arg("heaps"), py::arg("flag_off"), py::arg("x_off"), py::arg("xs_off"), py::arg("M"), py::arg("N"),
      py::arg("K"), py::arg("w"), py::arg("ldw"), py::arg("w_scale"), py::arg("ld_ws"), py::arg("d"), py::arg("ldd"), py::arg("dq"),
      py::arg("ds"), py::arg("ldq"), py::arg("bias"), py::arg("flags"), py::arg("ready_off"), py::arg("epoch"), py::arg("n_copy"),
-     py::arg("ctas"), py::arg("flag_lane"), py::arg("status"), py::arg("spin_ns"), py::arg("stream"));
+     py::arg("ctas"), py::arg("flag_lane"), py::arg("status"), py::arg("spin_ns"), py::arg("stream"), py::arg("mx") = false);
   m.def("gemm_rs_fp8", [](Engine* e, const std::vector<uint64_t>& heaps, const std::vector<uint64_t>& y, int64_t ldy,
                           const std::vector<uint64_t>& y_scale, int ld_ys, const std::vector<uint64_t>& w, int64_t ldw,
                           const std::vector<uint64_t>& w_scale, int ld_ws, const std::vector<uint64_t>& out, int64_t ldo, int M, int N,

@@ -20,7 +20,7 @@ struct AgGemmRank {
   int rank;
   int pad;
   // block-scaled fp8 only
-  const float* w_scale;       // fp32 [N/128, ld_ws]: 128 x 128 scales of the W shard
+  const float* w_scale;       // fp32 [N/128, ld_ws]: 128 x 128 scales of the W shard (UE8M0 bytes when scale_bytes is 1)
   int ld_ws;
   int pad2;
   void* Dq;                   // when set, the output is quantised instead: e4m3 [M, ldq] ...
@@ -42,7 +42,9 @@ struct AgGemmArgs {
   uint64_t spin_ns;
   uint32_t flags;             // GEMM_BIAS, GEMM_GELU_INPLACE (fp8 path)
   int elem_bytes;             // 2 (bf16 X) or 1 (e4m3 X with scales at xs_off); 0 is read as 2
-  uint64_t xs_off;            // fp8: heap offset of the symmetric gathered scales, fp32 [M, K/128]
+  uint64_t xs_off;            // fp8: heap offset of the symmetric gathered scales [M, K/128]: fp32, or UE8M0 bytes (scale_bytes 1)
+  int scale_bytes;            // 4 (fp32 scales; 0 is read as 4) or 1 (UE8M0 bytes, hardware block scaling)
+  int pad3;
   AgGemmRank r[kMaxVirt];
 };
 
@@ -82,6 +84,8 @@ int launchGemmRs(GemmRsArgs& args, const GemmRsHost* host, int ctas, cudaStream_
 // 256; the scale fields of the argument structs must be filled.  Single-CTA tiles.
 int launchAgGemmFp8(AgGemmArgs& args, const AgGemmHost* host, int ctas, cudaStream_t stream);
 int launchGemmRsFp8(GemmRsArgs& args, const GemmRsHost* host, int ctas, cudaStream_t stream);
+// all-gather -> GEMM on the hardware block-scaled pipeline (UE8M0 scale bytes; N a multiple of 32; bf16 output)
+int launchAgGemmMx8(AgGemmArgs& args, const AgGemmHost* host, int ctas, cudaStream_t stream);
 const char* fusedLastError();
 
 }  // namespace pccl

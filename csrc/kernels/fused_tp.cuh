@@ -145,14 +145,15 @@ __device__ __forceinline__ void ag_push_role(const AgGemmArgs& A, const AgGemmRa
   const long long per = (nvec + A.n_copy - 1) / A.n_copy;
   const long long lo = min(nvec, per * j), hi = min(nvec, per * (j + 1));
   // block-scaled operands: the 1 x 128 scales of a chunk (fp32 [128, K/128]) travel with it
-  const long long svec = A.xs_off ? (static_cast<long long>(BM) * (A.K / 128) * 4) >> 4 : 0;
+  const int sbytes = A.scale_bytes ? A.scale_bytes : 4;
+  const long long svec = A.xs_off ? (static_cast<long long>(BM) * (A.K / 128) * sbytes) >> 4 : 0;
   const long long sper = (svec + A.n_copy - 1) / A.n_copy;
   const long long slo = min(svec, sper * j), shi = min(svec, sper * (j + 1));
   const bool mc = A.w.mc_heap != nullptr && A.nvirt <= 1;
   for (int c = 0; c < chunks; ++c) {
     const long long row0 = static_cast<long long>(me) * A.M_local + static_cast<long long>(c) * BM;
     const long long off = static_cast<long long>(A.x_off) + row0 * row_bytes;
-    const long long soff = static_cast<long long>(A.xs_off) + row0 * (A.K / 128) * 4;
+    const long long soff = static_cast<long long>(A.xs_off) + row0 * (A.K / 128) * sbytes;
     const long long cnt_off = static_cast<long long>(A.ready_off) + static_cast<long long>(me * chunks + c) * 4;
     if (mc) {
       push_vecs<true>(A.w.heap[me] + off, A.w.mc_heap + off, lo, hi);

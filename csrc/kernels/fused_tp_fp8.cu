@@ -18,6 +18,7 @@
 #include "fused_api.h"
 #include "fused_tp.cuh"
 #include "gemm_fp8_pipeline.cuh"
+#include "gemm_mx8_pipeline.cuh"
 #include "tensormap.h"
 
 namespace pccl {
@@ -95,6 +96,24 @@ __global__ void __launch_bounds__(gemm8::NUM_THREADS, 1) ag_gemm_fp8_kernel(cons
   }
 }
 
+// all-gather -> GEMM with hardware block scaling: e4m3 rows and their UE8M0 scale bytes are pushed, the tensor core
+// applies the scales (gemm_mx8_pipeline.cuh), 224-column tiles.
+__global__ void __launch_bounds__(gemmx::NUM_THREADS, 1) ag_gemm_mx8_kernel(const __grid_constant__ AgGemmArgs A) {
+  const AgGemmRank& R = A.r[blockIdx.y];
+  if (static_cast<int>(blockIdx.x) < A.n_copy) {
+    if (A.w.world > 1) ag_push_role(A, R);
+    return;
+  }
+  const int tiles_ml = A.M_local / gemmx::BM, tiles_n = (A.N + gemmx::BN - 1) / gemmx::BN;
+  AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy};
+  AgGate gate{reinterpret_cast<const uint32_t*>(A.w.heap[R.rank] + A.ready_off), R.rank,
+              static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>(A.n_copy), A.spin_ns};
+  gemmx::Scales sc{reinterpret_cast<const uint8_t*>(A.w.heap[R.rank] + A.xs_off), reinterpret_cast<const uint8_t*>(R.w_scale), A.K / 128,
+                   R.ld_ws, A.M, A.N};
+  gemm::StoreEpi epi{R.D, nullptr, static_cast<const __nv_bfloat16*>(R.bias), R.ldd, A.M, A.N, A.flags};
+  gemmx::run(&R.tmA, &R.tmB, A.K, sc, sched, gate, epi, R.status);
+}
+
 constexpr int kRs8StageBytes = gemm8::EPI_WARPS * 32 * kRsPitch;
 constexpr int kRs8Stages = 3;                      // 3 x 48 KiB of operands leave room for the staging rows
 constexpr int RS8_SMEM_BYTES = gemm8::smem_bytes(kRs8Stages) + kRs8StageBytes;
@@ -142,6 +161,36 @@ int launchAgGemmFp8(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_
   dim3 grid(ctas, nv);
   void* args[] = {&A};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), grid, dim3(gemm8::NUM_THREADS), args, gemm8::SMEM_BYTES, stream));
+}
+
+int launchAgGemmMx8(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_t stream) {
+  const int nv = A.nvirt > 1 ? A.nvirt : 1;
+  if (nv > kMaxVirt || A.M_local % gemmx::BM || A.M != A.M_local * A.w.world || A.K % 128 || A.N % 32 || !A.xs_off) {
+    g_err = "ag_gemm mx8: rows per rank % 128, K % 128, N % 32, and a gathered-scale buffer are required";
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  A.elem_bytes = 1;
+  A.scale_bytes = 1;
+  for (int v = 0; v < nv; ++v) {
+    const void* xg = A.w.heap[A.r[v].rank] + A.x_off;     // TMA reads local memory only
+    if (!makeTensorMap2D(&A.r[v].tmA, xg, TM_U8, A.K, A.M, A.K, gemmx::BK, gemmx::BM, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
+    if (host[v].b_mn || !A.r[v].w_scale || !A.r[v].D) {
+      g_err = "ag_gemm mx8: W is K-major with scale bytes; the output is bf16";
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+    if (!makeTensorMap2D(&A.r[v].tmB, host[v].W, TM_U8, A.K, A.N, host[v].ldw, gemmx::BK, gemmx::BN, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (A.w.world == 1) A.n_copy = 0;
+  if (ctas <= A.n_copy) { g_err = "ag_gemm mx8: need more CTAs than copy CTAs"; return static_cast<int>(cudaErrorInvalidValue); }
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(ag_gemm_mx8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemmx::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    set = true;
+  }
+  dim3 grid(ctas, nv);
+  void* args[] = {&A};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ag_gemm_mx8_kernel), grid, dim3(gemmx::NUM_THREADS), args, gemmx::SMEM_BYTES, stream));
 }
 
 int launchGemmRsFp8(GemmRsArgs& A, const GemmRsHost* host, int ctas, cudaStream_t stream) {

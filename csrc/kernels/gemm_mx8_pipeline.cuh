@@ -43,15 +43,17 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SF_BYTES = 512 + 1024;        // one scale image: A (128 rows) + B (up to 256 columns)
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * SF_BYTES + 1024 + 256;
+constexpr int SF_IMAGES = 4;                // scale images in shared memory: the builder runs up to four K groups ahead
+static_assert(STAGES <= 4, "the reuse of the TMEM scale words relies on the operand ring being no deeper than one K group");
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SF_IMAGES * SF_BYTES + 1024 + 256;
 
 struct Barriers {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t sf_full[2];
-  uint64_t sf_empty[2];
+  uint64_t sf_full[SF_IMAGES];
+  uint64_t sf_empty[SF_IMAGES];
   uint64_t drain;
   uint32_t tmem_base;
   uint32_t abort;
@@ -95,7 +97,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sf_smem = smem + STAGES * STAGE_BYTES;
-  Barriers* bar = reinterpret_cast<Barriers*>(sf_smem + 2 * SF_BYTES);
+  Barriers* bar = reinterpret_cast<Barriers*>(sf_smem + SF_IMAGES * SF_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
   const int num_kg = (num_kb + 3) / 4;
@@ -109,6 +111,8 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(&bar->tmem_full[a], 1);
       tc::mbar_init(&bar->tmem_empty[a], 4);
+    }
+    for (int a = 0; a < SF_IMAGES; ++a) {
       tc::mbar_init(&bar->sf_full[a], 1);
       tc::mbar_init(&bar->sf_empty[a], 1);
     }
@@ -169,12 +173,16 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
         tc::tc_fence_after();
         const uint32_t d_tmem = tmem + acc * 256;
         for (int kb = 0; kb < num_kb; ++kb) {
-          const uint32_t buf = g & 1;
+          // scale words of group g: TMEM buffer g & 1, shared-memory image g % SF_IMAGES.  The copy for group g+2 reuses
+          // the TMEM words of group g: by then stage 4(g+2)-1 has been issued, which needed the MMAs of stage 4(g+1)-1
+          // to have completed (the four-stage ring lets the issuer run at most four stages ahead of finished MMAs, and a
+          // group is four stages), so every MMA of group g is done
+          const uint32_t buf = g & 1, im = g % SF_IMAGES;
           const uint32_t tsfa = tmem + BN + 16 * buf, tsfb = tsfa + 4;
           if ((kb & 3) == 0) {
-            if (!tc::mbar_wait(&bar->sf_full[buf], (g >> 1) & 1, abort)) { ok = false; break; }
+            if (!tc::mbar_wait(&bar->sf_full[im], (g / SF_IMAGES) & 1, abort)) { ok = false; break; }
             tc::tc_fence_after();
-            const uint32_t img = tc::smem_u32(sf_smem + buf * SF_BYTES);
+            const uint32_t img = tc::smem_u32(sf_smem + im * SF_BYTES);
             tmem_cp_32x128b_x4(tsfa, sf_desc(img));
             tmem_cp_32x128b_x4(tsfb, sf_desc(img + 512));
             tmem_cp_32x128b_x4(tsfb + 4, sf_desc(img + 1024));
@@ -193,7 +201,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
           tc::mma_commit(&bar->empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
           if ((kb & 3) == 3 || kb == num_kb - 1) {
-            tc::mma_commit(&bar->sf_empty[buf]);       // the copies and MMAs that read this scale image have finished
+            tc::mma_commit(&bar->sf_empty[im]);        // the copies that read this scale image have finished
             ++g;
           }
         }
@@ -208,6 +216,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   } else if (warp == 2) {
     // ------------------------------------------------------------------ scale builder (whole warp)
     const int nblk = (sc.N + 127) / 128;
+    const bool aligned4 = ((sc.ld_sa | sc.ld_sb) & 3) == 0 && ((reinterpret_cast<uintptr_t>(sc.sa) | reinterpret_cast<uintptr_t>(sc.sb)) & 3) == 0;
     uint32_t g = 0;
     bool ok = true;
     TileCoord t;
@@ -219,20 +228,25 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       }
       const int row0 = t.m * BM, col0 = t.n * BN;
       for (int kg = 0; kg < num_kg; ++kg, ++g) {
-        const uint32_t buf = g & 1;
+        const uint32_t im = g % SF_IMAGES;
         int open = 1;
-        if (lane == 0) open = tc::mbar_wait(&bar->sf_empty[buf], ((g >> 1) & 1) ^ 1, abort) ? 1 : 0;
+        if (lane == 0) open = tc::mbar_wait(&bar->sf_empty[im], ((g / SF_IMAGES) & 1) ^ 1, abort) ? 1 : 0;
         if (!__shfl_sync(0xffffffffu, open, 0)) { ok = false; break; }
-        uint8_t* img = sf_smem + buf * SF_BYTES;
+        uint8_t* img = sf_smem + im * SF_BYTES;
         const int kb0 = kg * 4;
+        const bool wide = aligned4 && kb0 + 4 <= num_kb;     // four scale bytes in one load
 #pragma unroll
         for (int q = 0; q < 4; ++q) {               // A: rows 32 q + lane
           const int row = min(row0 + 32 * q + lane, sc.M - 1);
           const uint8_t* p = sc.sa + static_cast<long long>(row) * sc.ld_sa;
           uint32_t w = 0;
+          if (wide) {
+            w = __ldcg(reinterpret_cast<const uint32_t*>(p + kb0));
+          } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldcg(p + kb0 + j)) << (8 * j);
+            for (int j = 0; j < 4; ++j)
+              if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldcg(p + kb0 + j)) << (8 * j);
+          }
           *reinterpret_cast<uint32_t*>(img + lane * 16 + q * 4) = w;
         }
 #pragma unroll
@@ -240,14 +254,18 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
           const int blk = min((col0 + 32 * q + lane) >> 7, nblk - 1);
           const uint8_t* p = sc.sb + static_cast<long long>(blk) * sc.ld_sb;
           uint32_t w = 0;
+          if (wide) {
+            w = __ldg(reinterpret_cast<const uint32_t*>(p + kb0));
+          } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldg(p + kb0 + j)) << (8 * j);
+            for (int j = 0; j < 4; ++j)
+              if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldg(p + kb0 + j)) << (8 * j);
+          }
           *reinterpret_cast<uint32_t*>(img + 512 + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = w;
         }
         tc::fence_proxy_async_smem();                // the image is read by tcgen05.cp (async proxy)
         __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&bar->sf_full[buf]);
+        if (lane == 0) tc::mbar_arrive(&bar->sf_full[im]);
       }
     }
     if (!ok && lane == 0 && atomicExch(const_cast<uint32_t*>(&bar->abort), 1u) == 0) dev::report(status, ST_TIMEOUT, blockIdx.x, 3, 0);

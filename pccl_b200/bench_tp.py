@@ -171,6 +171,23 @@ def run_fp8(eng, tokens, d_model, d_ff, x_local, w1, w2, h, iters, warmup, n_cop
                  "roofline_note": "compute term at the measured cuBLASLt tensorwise-fp8 rate of the same shape",
                  "max_abs_diff_vs_unfused": err})
 
+    # ---- the same all-gather GEMM with power-of-two scales applied by the tensor core --------------
+    try:
+        from .ops.gemm import gemm_mx8, quant_blocks_mx
+        agx = AllGatherGemmFp8(eng, tokens, d_model, n_copy=max(2, n_copy // 2), mx=True)
+        agx.quantize_local(x_local)
+        wxq, wxs = quant_blocks_mx(w1)
+        fused_x = _time(lambda: agx(wxq, wxs, out=y), iters, warmup, flush)
+        check_status("ag_gemm_mx8")
+        own_x = _time(lambda: gemm_mx8(agx.xq_full, agx.xs_full, wxq, wxs, out=y_ref), iters, warmup, flush)
+        roof_x = max(flops / peak if peak else 0.0, (world - 1) * m_local * (d_model + d_model // 128) / (link_gbs * 1e9)) * 1e6
+        rows.append({"op": "allgather_gemm_mx8", "n_gpus": world, "M": tokens, "N": n1, "K": d_model, "fused_us": fused_x,
+                     "nccl_bf16_plus_cublas_bf16_us": base, "own_mx8_gemm_us": own_x, "cublaslt_fp8_tensorwise_gemm_us": lt,
+                     "speedup_vs_nccl_cublas_bf16": base / fused_x, "roofline_us": roof_x, "fraction_of_roofline": roof_x / fused_x,
+                     "note": "e4m3 with UE8M0 (power-of-two) 1x128 / 128x128 scales, tcgen05 kind::mxf8f6f4.block_scale"})
+    except Exception as e:      # noqa: BLE001 - the row is optional; the other rows must still be reported
+        rows.append({"op": "allgather_gemm_mx8", "n_gpus": world, "error": f"{type(e).__name__}: {e}"})
+
     # ---- GEMM -> reduce-scatter ---------------------------------------------------------------
     rs = GemmReduceScatterFp8(eng, tokens, d_model)
     hq, hs = quant_rows(h)

@@ -90,12 +90,15 @@ class AllGatherGemmFp8:
     With ``quant_out`` the result (after bias / GELU) is returned quantised the same way, ready for the
     second GEMM of the layer."""
 
-    def __init__(self, eng: Engine, rows_total: int, k: int, n_copy: int = 8, ctas: Optional[int] = None, flag_lane: int = 4):
+    def __init__(self, eng: Engine, rows_total: int, k: int, n_copy: int = 8, ctas: Optional[int] = None, flag_lane: int = 4,
+                 mx: bool = False):
+        """``mx``: power-of-two scale bytes (UE8M0) applied by the tensor core (``ops.gemm.quant_blocks_mx`` weights,
+        224-column tiles, bf16 output only) instead of fp32 scales applied by promotion."""
         if rows_total % (128 * eng.world) or k % 128:
             raise ValueError("AllGatherGemmFp8: rows per rank must be a multiple of 128 and K a multiple of 128")
-        self.eng, self.M, self.K = eng, rows_total, k
+        self.eng, self.M, self.K, self.mx = eng, rows_total, k, mx
         self.xq_full = eng.symmetric_tensor((rows_total, k), torch.uint8)
-        self.xs_full = eng.symmetric_tensor((rows_total, k // 128), torch.float32)
+        self.xs_full = eng.symmetric_tensor((rows_total, k // 128), torch.uint8 if mx else torch.float32)
         m_local = rows_total // eng.world
         self.m_local = m_local
         self.xq_local = self.xq_full[eng.rank * m_local:(eng.rank + 1) * m_local]
@@ -113,15 +116,18 @@ class AllGatherGemmFp8:
         """bf16 [M/world, K] -> this rank's rows of the gathered fp8 buffer and its scales (one kernel)."""
         if x.shape != (self.m_local, self.K) or x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise ValueError("AllGatherGemmFp8.quantize_local: contiguous bf16 [M/world, K]")
-        C.quant_fp8_rows(x.data_ptr(), self.xq_local.data_ptr(), self.xs_local.data_ptr(), self.m_local, self.K,
-                         torch.cuda.current_stream().cuda_stream)
+        quant = C.quant_mx8_rows if self.mx else C.quant_fp8_rows
+        quant(x.data_ptr(), self.xq_local.data_ptr(), self.xs_local.data_ptr(), self.m_local, self.K,
+              torch.cuda.current_stream().cuda_stream)
         count_launch()
 
     def __call__(self, wq: torch.Tensor, ws: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
                  quant_out: bool = False, out=None):
         n = wq.shape[0]
-        if wq.element_size() != 1 or wq.shape[1] != self.K or n % 256 or ws.shape != (n // 128, self.K // 128):
-            raise ValueError("AllGatherGemmFp8: wq e4m3 [N, K] with N % 256 == 0 and ws fp32 [N/128, K/128]")
+        if wq.element_size() != 1 or wq.shape[1] != self.K or n % (128 if self.mx else 256) or ws.shape != (n // 128, self.K // 128):
+            raise ValueError("AllGatherGemmFp8: wq e4m3 [N, K] with N % 256 == 0 (128 with mx) and ws [N/128, K/128]")
+        if ws.dtype != (torch.uint8 if self.mx else torch.float32) or (self.mx and (quant_out or gelu)):
+            raise ValueError("AllGatherGemmFp8: scales must be fp32 (uint8 with mx); mx has the plain bf16 epilogue only")
         d, dq, ds, ldd, ldq = [], [], [], 0, 0
         if quant_out:
             q = torch.empty((self.M, n), dtype=torch.uint8, device="cuda") if out is None else out[0]
@@ -135,7 +141,7 @@ class AllGatherGemmFp8:
                       [wq.data_ptr()], wq.stride(0), [ws.data_ptr()], ws.stride(0), d, ldd, dq, ds, ldq,
                       bias.data_ptr() if bias is not None else 0, C.GEMM_GELU_INPLACE if gelu else 0, self.eng.heap_offset(self.ready),
                       self.epoch, self.n_copy, self.ctas, self.flag_lane, [status_words().data_ptr()], 0,
-                      torch.cuda.current_stream().cuda_stream)
+                      torch.cuda.current_stream().cuda_stream, self.mx)
         count_launch()
         return result
 

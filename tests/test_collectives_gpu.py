@@ -279,6 +279,46 @@ def test_ag_gemm_fp8_emulated(native, world, quant_out):
             assert torch.equal(dequant_rows(gq, gs), X)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_ag_gemm_mx8_emulated(native, world):
+    """All-gather -> GEMM on the hardware block-scaled pipeline: e4m3 rows and UE8M0 scale bytes are gathered."""
+    from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, quant_blocks_mx, quant_rows_mx, ue8m0_to_float
+    M_local, K, N = 256, 1024, 640
+    M = M_local * world
+    g = torch.Generator(device="cuda").manual_seed(29)
+    xs = [(torch.randn(M_local, K, generator=g, device="cuda") * (0.5 + r)).bfloat16() for r in range(world)]
+    ws = [quant_blocks_mx((torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16()) for _ in range(world)]
+    x_off = DATA_OFF
+    xs_off = x_off + M * K
+    ready_off = xs_off + M * (K // 128)
+    heaps = [torch.zeros(ready_off + 4096, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ctas = 148 // world
+    for epoch in (1, 2):
+        X = []
+        for r in range(world):
+            q, s = quant_rows_mx((xs[r].float() * epoch).bfloat16())
+            X.append(dequant_rows(q, ue8m0_to_float(s)))
+            fq = heaps[r][x_off:x_off + M * K].view(M, K)
+            fs = heaps[r][xs_off:xs_off + M * (K // 128)].view(M, K // 128)
+            fq.zero_()
+            fs.zero_()
+            fq[r * M_local:(r + 1) * M_local] = q
+            fs[r * M_local:(r + 1) * M_local] = s
+        native.ag_gemm_fp8(None, [h.data_ptr() for h in heaps], FLAG_OFF, x_off, xs_off, M, N, K, [w[0].data_ptr() for w in ws], K,
+                           [w[1].data_ptr() for w in ws], K // 128, [o.data_ptr() for o in outs], N, [], [], 0, 0, 0, ready_off, epoch,
+                           4, ctas, 0, [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream, True)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        X = torch.cat(X)
+        for r in range(world):
+            ref = X @ dequant_blocks(ws[r][0], ue8m0_to_float(ws[r][1])).t()
+            assert (outs[r].float() - ref).abs().max().item() < 0.02 * max(1.0, ref.abs().max().item())
+            gs = heaps[r][xs_off:xs_off + M * (K // 128)].view(M, K // 128)
+            assert torch.equal(dequant_rows(heaps[r][x_off:x_off + M * K].view(M, K), ue8m0_to_float(gs)), X)
+
+
 @pytest.mark.parametrize("world,M_local", [(2, 128), (2, 256), (4, 128)])
 def test_gemm_rs_fp8_emulated(native, world, M_local):
     from pccl_b200.ops.gemm import dequant_blocks, dequant_rows, quant_blocks, quant_rows
