@@ -5,7 +5,7 @@
 // and nothing is promoted in registers (the exact-fp32-scale kernel of gemm_fp8_pipeline.cuh pays twice
 // the MMA time for that).
 //
-//   warp 0      TMA producer: 128 x 128 A and 224 x 128 B tiles (128-byte swizzle), 4 stages; `Gate` as in
+//   warp 0      TMA producer: 128 x 128 A and 224 x 128 B tiles (128-byte swizzle), 5 stages; `Gate` as in
 //               the other pipelines
 //   warp 1      MMA issuer: per stage four MMAs 128 x 224 x 32; every fourth stage it first copies the
 //               scale images of the next 512 values of K from shared memory into TMEM (tcgen05.cp
@@ -36,16 +36,17 @@ namespace gemmx {
 using gemm::TileCoord;
 
 constexpr int BM = 128, BN = 224, BK = 128, UMMA_K = 32;
-constexpr int STAGES = 4;
+constexpr int STAGES = 5;
 constexpr int A_BYTES = BM * BK;            // 16 KiB
 constexpr int B_BYTES = BN * BK;            // 28 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SF_BYTES = 512 + 1024;        // one scale image: A (128 rows) + B (up to 256 columns)
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 256;
-constexpr int SF_IMAGES = 4;                // scale images in shared memory: the builder runs up to four K groups ahead
-static_assert(STAGES <= 4, "the reuse of the TMEM scale words relies on the operand ring being no deeper than one K group");
+constexpr int SF_IMAGES = 2;                // scale images in shared memory (five 44 KiB stages leave room for two)
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SF_IMAGES * SF_BYTES + 1024 + 256;
+static_assert(SF_IMAGES == 2, "image and TMEM scale buffer of a K group must share their index (see the MMA issuer)");
+static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -173,12 +174,12 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
         tc::tc_fence_after();
         const uint32_t d_tmem = tmem + acc * 256;
         for (int kb = 0; kb < num_kb; ++kb) {
-          // scale words of group g: TMEM buffer g & 1, shared-memory image g % SF_IMAGES.  The copy for group g+2 reuses
-          // the TMEM words of group g: by then stage 4(g+2)-1 has been issued, which needed the MMAs of stage 4(g+1)-1
-          // to have completed (the four-stage ring lets the issuer run at most four stages ahead of finished MMAs, and a
-          // group is four stages), so every MMA of group g is done
+          // scale words of group g: TMEM buffer g & 1, shared-memory image g & 1.  The copy for group g+2 reuses the TMEM
+          // words of group g; its image is only written after sf_empty of group g, i.e. after every MMA of group g has
+          // finished, so the copy cannot overwrite scales that are still in use
           const uint32_t buf = g & 1, im = g % SF_IMAGES;
           const uint32_t tsfa = tmem + BN + 16 * buf, tsfb = tsfa + 4;
+          if (!tc::mbar_wait(&bar->full[stage], phase, abort)) { ok = false; break; }
           if ((kb & 3) == 0) {
             if (!tc::mbar_wait(&bar->sf_full[im], (g / SF_IMAGES) & 1, abort)) { ok = false; break; }
             tc::tc_fence_after();
@@ -187,7 +188,6 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
             tmem_cp_32x128b_x4(tsfb, sf_desc(img + 512));
             tmem_cp_32x128b_x4(tsfb + 4, sf_desc(img + 1024));
           }
-          if (!tc::mbar_wait(&bar->full[stage], phase, abort)) { ok = false; break; }
           tc::tc_fence_after();
           const uint32_t sa = tc::smem_u32(smem + stage * STAGE_BYTES), sb = sa + A_BYTES;
           const uint32_t sf = static_cast<uint32_t>(kb & 3);
@@ -215,58 +215,80 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
     }
   } else if (warp == 2) {
     // ------------------------------------------------------------------ scale builder (whole warp)
+    // The words of the NEXT group (also across a tile boundary) are fetched from global memory into registers while
+    // the MMAs of the current ones run; once the image buffer is free only the shared-memory writes remain.
     const int nblk = (sc.N + 127) / 128;
     const bool aligned4 = ((sc.ld_sa | sc.ld_sb) & 3) == 0 && ((reinterpret_cast<uintptr_t>(sc.sa) | reinterpret_cast<uintptr_t>(sc.sb)) & 3) == 0;
+    uint32_t wa[4], wb[8];
+    auto fetch = [&](const TileCoord& tt, int kg) {
+      const int row0 = tt.m * BM, col0 = tt.n * BN, kb0 = kg * 4;
+      const bool wide = aligned4 && kb0 + 4 <= num_kb;     // four scale bytes in one load
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {               // A: rows 32 q + lane
+        const int row = min(row0 + 32 * q + lane, sc.M - 1);
+        const uint8_t* p = sc.sa + static_cast<long long>(row) * sc.ld_sa;
+        uint32_t w = 0;
+        if (wide) {
+          w = __ldcg(reinterpret_cast<const uint32_t*>(p + kb0));     // may have been written by a peer: past L1
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldcg(p + kb0 + j)) << (8 * j);
+        }
+        wa[q] = w;
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {               // B: tile columns 32 q + lane
+        const int blk = min((col0 + 32 * q + lane) >> 7, nblk - 1);
+        const uint8_t* p = sc.sb + static_cast<long long>(blk) * sc.ld_sb;
+        uint32_t w = 0;
+        if (wide) {
+          w = __ldg(reinterpret_cast<const uint32_t*>(p + kb0));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldg(p + kb0 + j)) << (8 * j);
+        }
+        wb[q] = w;
+      }
+    };
+    auto gate_open = [&](const TileCoord& tt) {   // A's scales arrive with its rows: read them only behind the gate
+      int open = 1;
+      if (lane == 0) open = gate.wait(tt, abort) ? 1 : 0;
+      return __shfl_sync(0xffffffffu, open, 0) != 0;
+    };
     uint32_t g = 0;
     bool ok = true;
-    TileCoord t;
-    for (int it = 0; ok && sched.get(it, &t); ++it) {
-      {   // A's scales arrive with its rows: a gated tile's scales may only be read once the gate has opened
-        int open = 1;
-        if (lane == 0) open = gate.wait(t, abort) ? 1 : 0;
-        if (!__shfl_sync(0xffffffffu, open, 0)) { ok = false; break; }
-      }
-      const int row0 = t.m * BM, col0 = t.n * BN;
+    TileCoord t, tn;
+    bool have = sched.get(0, &t);
+    if (have) {
+      ok = gate_open(t);
+      if (ok) fetch(t, 0);
+    }
+    for (int it = 0; ok && have; ++it) {
+      const bool have_next = sched.get(it + 1, &tn);
       for (int kg = 0; kg < num_kg; ++kg, ++g) {
         const uint32_t im = g % SF_IMAGES;
         int open = 1;
         if (lane == 0) open = tc::mbar_wait(&bar->sf_empty[im], ((g / SF_IMAGES) & 1) ^ 1, abort) ? 1 : 0;
         if (!__shfl_sync(0xffffffffu, open, 0)) { ok = false; break; }
         uint8_t* img = sf_smem + im * SF_BYTES;
-        const int kb0 = kg * 4;
-        const bool wide = aligned4 && kb0 + 4 <= num_kb;     // four scale bytes in one load
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {               // A: rows 32 q + lane
-          const int row = min(row0 + 32 * q + lane, sc.M - 1);
-          const uint8_t* p = sc.sa + static_cast<long long>(row) * sc.ld_sa;
-          uint32_t w = 0;
-          if (wide) {
-            w = __ldcg(reinterpret_cast<const uint32_t*>(p + kb0));
-          } else {
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint32_t*>(img + lane * 16 + q * 4) = wa[q];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldcg(p + kb0 + j)) << (8 * j);
-          }
-          *reinterpret_cast<uint32_t*>(img + lane * 16 + q * 4) = w;
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {               // B: tile columns 32 q + lane
-          const int blk = min((col0 + 32 * q + lane) >> 7, nblk - 1);
-          const uint8_t* p = sc.sb + static_cast<long long>(blk) * sc.ld_sb;
-          uint32_t w = 0;
-          if (wide) {
-            w = __ldg(reinterpret_cast<const uint32_t*>(p + kb0));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (kb0 + j < num_kb) w |= static_cast<uint32_t>(__ldg(p + kb0 + j)) << (8 * j);
-          }
-          *reinterpret_cast<uint32_t*>(img + 512 + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = w;
-        }
+        for (int q = 0; q < 8; ++q) *reinterpret_cast<uint32_t*>(img + 512 + (q >> 2) * 512 + lane * 16 + (q & 3) * 4) = wb[q];
         tc::fence_proxy_async_smem();                // the image is read by tcgen05.cp (async proxy)
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&bar->sf_full[im]);
+        if (kg + 1 < num_kg) {
+          fetch(t, kg + 1);
+        } else if (have_next) {
+          if (!gate_open(tn)) { ok = false; break; }
+          fetch(tn, 0);
+        }
       }
+      t = tn;
+      have = have_next;
     }
     if (!ok && lane == 0 && atomicExch(const_cast<uint32_t*>(&bar->abort), 1u) == 0) dev::report(status, ST_TIMEOUT, blockIdx.x, 3, 0);
   } else if (warp >= 4) {
