@@ -56,6 +56,8 @@ int launchKind(const std::string& kind, const CollArgs& a, int blocks, int threa
   if (kind == "reduce_scatter") return launchReduceScatter(a, blocks, threads, s);
   if (kind == "allgather") return launchAllGather(a, blocks, threads, s);
   if (kind == "alltoall") return launchAllToAll(a, blocks, threads, s);
+  if (kind == "allreduce_fp8") return launchAllReduceFp8(a, blocks, threads, s);
+  if (kind == "reduce_scatter_fp8") return launchReduceScatterFp8(a, blocks, threads, s);
   throw std::runtime_error("unknown collective '" + kind + "'");
 }
 
@@ -63,9 +65,11 @@ int launchKind(const std::string& kind, const CollArgs& a, int blocks, int threa
 void collective(Engine& e, const std::string& kind, const std::string& algo, const std::string& dtype,
                 const std::string& redop, uint64_t in_off, uint64_t out_off, uint64_t count, int flag_lane,
                 float scale, const std::string& out_dtype, int blocks, int threads, uint64_t stream,
-                uint64_t local_in, uint64_t local_out, uint64_t spin_limit) {
+                uint64_t local_in, uint64_t local_out, uint64_t spin_limit, uint64_t s_in_off, uint64_t s_out_off) {
   CollArgs a = makeCollArgs(e.worldTable(), 1, e.rank(), algo, dtype, redop, in_off, out_off, count,
                             e.nextEpoch(flag_lane), flag_lane, scale, out_dtype, spin_limit);
+  a.s_in_off = s_in_off;
+  a.s_out_off = s_out_off;
   a.status[0] = reinterpret_cast<uint32_t*>(e.statusPtr(8 + flag_lane));
   a.local_in[0] = reinterpret_cast<const void*>(local_in);
   a.local_out[0] = reinterpret_cast<void*>(local_out);
@@ -87,9 +91,11 @@ void emuCollective(const std::string& kind, const std::vector<uint64_t>& heaps, 
                    const std::string& dtype, const std::string& redop, uint64_t in_off, uint64_t out_off, uint64_t count,
                    uint64_t epoch, int flag_lane, float scale, const std::string& out_dtype, int blocks, int threads,
                    uint64_t stream, const std::vector<uint64_t>& status, const std::vector<uint64_t>& local_in,
-                   const std::vector<uint64_t>& local_out, uint64_t spin_limit) {
+                   const std::vector<uint64_t>& local_out, uint64_t spin_limit, uint64_t s_in_off, uint64_t s_out_off) {
   World w = emuWorld(heaps, signal_off, flag_off);
   CollArgs a = makeCollArgs(w, w.world, 0, "p2p", dtype, redop, in_off, out_off, count, epoch, flag_lane, scale, out_dtype, spin_limit);
+  a.s_in_off = s_in_off;
+  a.s_out_off = s_out_off;
   for (int r = 0; r < w.world; ++r) {
     a.status[r] = reinterpret_cast<uint32_t*>(status.at(r));
     a.local_in[r] = local_in.empty() ? nullptr : reinterpret_cast<const void*>(local_in.at(r));
@@ -231,7 +237,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("collective", &collective, py::arg("engine"), py::arg("kind"), py::arg("algo"), py::arg("dtype"),
         py::arg("redop"), py::arg("in_off"), py::arg("out_off"), py::arg("count"), py::arg("flag_lane") = 0,
         py::arg("scale") = 1.0f, py::arg("out_dtype") = "", py::arg("blocks") = 32, py::arg("threads") = 512,
-        py::arg("stream") = 0, py::arg("local_in") = 0, py::arg("local_out") = 0, py::arg("spin_limit") = 0);
+        py::arg("stream") = 0, py::arg("local_in") = 0, py::arg("local_out") = 0, py::arg("spin_limit") = 0,
+        py::arg("s_in_off") = 0, py::arg("s_out_off") = 0);
   m.def("reduce_scatter_adamw", [](Engine& e, const std::string& algo, uint64_t in_off, uint64_t count, int flag_lane, float scale,
                                    uint64_t p, uint64_t mm, uint64_t v, uint64_t p_bf16, float lr, float b1, float b2, float eps,
                                    float wd, int step, int blocks, int threads, uint64_t stream) {
@@ -246,7 +253,10 @@ PYBIND11_MODULE(_C, m) {
     o.inv_sqrt_bc2 = 1.0f / std::sqrt(1.0f - std::pow(b2, static_cast<float>(step)));
     throwIfCuda(launchReduceScatterAdamW(a, o, blocks, threads, reinterpret_cast<cudaStream_t>(stream)), "reduce_scatter_adamw");
   });
-  m.def("emu_collective", &emuCollective);
+  m.def("emu_collective", &emuCollective, py::arg("kind"), py::arg("heaps"), py::arg("signal_off"), py::arg("flag_off"), py::arg("dtype"),
+        py::arg("redop"), py::arg("in_off"), py::arg("out_off"), py::arg("count"), py::arg("epoch"), py::arg("flag_lane"), py::arg("scale"),
+        py::arg("out_dtype"), py::arg("blocks"), py::arg("threads"), py::arg("stream"), py::arg("status"), py::arg("local_in"),
+        py::arg("local_out"), py::arg("spin_limit"), py::arg("s_in_off") = 0, py::arg("s_out_off") = 0);
   m.def("emu_program", &emuProgram);
   m.def("wait_timeout_probe", [](uint64_t flag, uint64_t spin_limit, uint64_t status, uint64_t stream) {
     throwIfCuda(launchWaitTimeoutProbe(reinterpret_cast<uint64_t*>(flag), spin_limit, reinterpret_cast<uint32_t*>(status),

@@ -85,6 +85,8 @@ struct CollArgs {
   // input and the reduce-scatter output are only touched by their own rank.
   const void* local_in[kMaxRanks];
   void* local_out[kMaxRanks];
+  // block-scaled fp8 collectives only: heap offsets of the fp32 scales (one per 128 values) of input and output
+  uint64_t s_in_off, s_out_off;
 };
 
 int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
@@ -98,6 +100,11 @@ struct AdamArgs {
   float lr, b1, b2, eps, wd, inv_bc1, inv_sqrt_bc2;
 };
 int launchReduceScatterAdamW(const CollArgs& a, const AdamArgs& o, int blocks, int threads, cudaStream_t stream);
+// Block-scaled fp8 (e4m3 payload + one fp32 scale per 128 values) all-reduce and reduce-scatter: every 128-value block is
+// dequantised, accumulated in fp32 over the ranks and re-quantised with a fresh scale (block maximum / 448), all inside
+// the transfer.  `count` = elements (AR: whole vector; RS: per shard), a multiple of 128.  Sum or max.  P2P only.
+int launchAllReduceFp8(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
+int launchReduceScatterFp8(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 int launchAllGather(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 int launchAllToAll(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 // Bounded-wait self test: waits on a flag nobody sets; must come back with ST_TIMEOUT.

@@ -443,6 +443,121 @@ int launchReduceScatterAdamW(const CollArgs& a, const AdamArgs& o, int blocks, i
   return static_cast<int>(cudaLaunchCooperativeKernel(kern, dim3(blocks), dim3(threads), args, 0, stream));
 }
 
+// ---------------------------------------------------------------------------------------------
+// block-scaled fp8 all-reduce / reduce-scatter: dequantise -> fp32 accumulate -> requantise, per 128-value block
+// ---------------------------------------------------------------------------------------------
+// 16 consecutive lanes own one block (8 bytes each); the block's scale is read by all of them (one broadcast load).
+template <bool ALL, uint32_t OP>
+__global__ void __launch_bounds__(512) reduce_fp8_kernel(const __grid_constant__ CollArgs A) {
+  __shared__ uint32_t s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = my_rank(A), n = A.w.world;
+  if (!peer_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const uint64_t nb = A.count >> 7;                       // blocks of the vector (AR) or of one shard (RS)
+  uint64_t lo, hi;                                        // input blocks this rank reduces
+  if (ALL) {
+    const uint64_t per = (nb + n - 1) / n;
+    lo = min(per * me, nb);
+    hi = min(per * (me + 1), nb);
+  } else {
+    lo = nb * me;
+    hi = nb * (me + 1);
+  }
+  const int sub = threadIdx.x & 15;
+  const uint64_t hw = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const uint64_t nhw = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 4;
+  const int slot = A.nvirt > 1 ? me : 0;
+  // every half-warp of a warp runs the same number of iterations (the shuffles below are warp-wide)
+  const uint64_t span = hi - lo;
+  const uint64_t iters = (span + nhw - 1) / nhw;
+  for (uint64_t it = 0; it < iters; ++it) {
+    const uint64_t b = lo + it * nhw + hw;
+    const bool live = b < hi;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = OP == RED_SUM ? 0.f : (OP == RED_MAX ? -INFINITY : INFINITY);
+    if (live) {
+      for (int g = 0; g < n; g += 8) {
+        uint2 q[8];
+        float sc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (g + k < n) {
+            int p = me + g + k;
+            if (p >= n) p -= n;
+            q[k] = *reinterpret_cast<const uint2*>(A.w.heap[p] + A.in_off + (b << 7) + sub * 8);
+            sc[k] = *reinterpret_cast<const float*>(A.w.heap[p] + A.s_in_off + (b << 2));
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (g + k < n) {
+            const uint32_t w[2] = {q[k].x, q[k].y};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w[h] >> (16 * j)) & 0xffffu), __NV_E4M3);
+                const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+                const float v0 = f.x * sc[k], v1 = f.y * sc[k];
+                float& a0 = acc[4 * h + 2 * j];
+                float& a1 = acc[4 * h + 2 * j + 1];
+                if (OP == RED_SUM) { a0 += v0; a1 += v1; }
+                else if (OP == RED_MAX) { a0 = fmaxf(a0, v0); a1 = fmaxf(a1, v1); }
+                else { a0 = fminf(a0, v0); a1 = fminf(a1, v1); }
+              }
+            }
+          }
+        }
+      }
+    }
+    float amax = 0.f;
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(acc[i]));
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!live) continue;
+    const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+    const float inv = 1.0f / scale;
+    uint32_t w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t l = __nv_cvt_float2_to_fp8x2(make_float2(acc[4 * h] * inv, acc[4 * h + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      uint32_t u = __nv_cvt_float2_to_fp8x2(make_float2(acc[4 * h + 2] * inv, acc[4 * h + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      w[h] = (l & 0xffffu) | (u << 16);
+    }
+    const uint2 out = make_uint2(w[0], w[1]);
+    if (ALL) {
+      for (int k = 0; k < n; ++k) {
+        int p = me + k;
+        if (p >= n) p -= n;
+        *reinterpret_cast<uint2*>(A.w.heap[p] + A.out_off + (b << 7) + sub * 8) = out;
+        if (sub == 0) *reinterpret_cast<float*>(A.w.heap[p] + A.s_out_off + (b << 2)) = scale;
+      }
+    } else {
+      const uint64_t ob = b - lo;
+      char* oq = A.local_out[slot] ? static_cast<char*>(A.local_out[slot]) : A.w.heap[me] + A.out_off;
+      *reinterpret_cast<uint2*>(oq + (ob << 7) + sub * 8) = out;
+      if (sub == 0) *reinterpret_cast<float*>(A.w.heap[me] + A.s_out_off + (ob << 2)) = scale;
+    }
+  }
+  peer_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+template <bool ALL>
+int launchReduceFp8(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
+  if (a.count % 128 || a.dtype != DT_FP8_E4M3) return static_cast<int>(cudaErrorInvalidValue);
+  if (a.redop == RED_SUM) return launchCoop(reduce_fp8_kernel<ALL, RED_SUM>, a, blocks, threads, stream);
+  if (a.redop == RED_MAX) return launchCoop(reduce_fp8_kernel<ALL, RED_MAX>, a, blocks, threads, stream);
+  if (a.redop == RED_MIN) return launchCoop(reduce_fp8_kernel<ALL, RED_MIN>, a, blocks, threads, stream);
+  return static_cast<int>(cudaErrorNotSupported);
+}
+
+int launchAllReduceFp8(const CollArgs& a, int blocks, int threads, cudaStream_t stream) { return launchReduceFp8<true>(a, blocks, threads, stream); }
+int launchReduceScatterFp8(const CollArgs& a, int blocks, int threads, cudaStream_t stream) { return launchReduceFp8<false>(a, blocks, threads, stream); }
+
 int launchAllGather(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
   return a.algo == ALGO_NVLS ? launchCoop(allgather_kernel<true>, a, blocks, threads, stream)
                              : launchCoop(allgather_kernel<false>, a, blocks, threads, stream);

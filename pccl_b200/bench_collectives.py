@@ -42,6 +42,30 @@ def bus_factor(kind: str, n: int) -> float:
     return 2.0 * (n - 1) / n if kind == "allreduce" else (n - 1) / n
 
 
+_PROGRAMS: Dict[str, List[str]] = {}
+
+
+def interp_programs(eng: Engine, kind: str) -> List[str]:
+    """Registers (once) the ``pccl_b200.lang`` programs the interpreter kernel is timed on: the NVLS and direct forms of
+    the collective and the MILP-synthesised schedule for this world behind an NVSwitch."""
+    if kind in _PROGRAMS:
+        return _PROGRAMS[kind]
+    from .lang import build
+    from .synth import Topology, synthesize
+    lang_kind = {"allreduce": "allreduce", "reduce_scatter": "reduce_scatter", "allgather": "allgather"}[kind]
+    names = []
+    if eng.has_nvls:
+        eng.regOp(f"bench_nvls_{kind}", build(f"nvls_{lang_kind}", eng.world, channels=2))
+        names.append(f"bench_nvls_{kind}")
+    eng.regOp(f"bench_direct_{kind}", build(f"direct_{lang_kind}", eng.world, channels=2))
+    names.append(f"bench_direct_{kind}")
+    res = synthesize(lang_kind, Topology.nvswitch(eng.world), 16 << 20, chunks=1, time_limit=10.0)
+    eng.regOp(f"bench_milp_{kind}", res.ir)
+    names.append(f"bench_milp_{kind}")
+    _PROGRAMS[kind] = names
+    return names
+
+
 def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: List[str], iters: Optional[int] = None) -> Dict:
     """`nbytes` = bytes of the full vector (all-reduce) or of the gathered/scattered whole (RS/AG)."""
     world = eng.world
@@ -62,6 +86,33 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
     outs = [pool_out[i * slot:i * slot + nbytes].view(dtype) for i in range(n_slots)]
     res = {"kind": kind, "dtype": str(dtype).replace("torch.", ""), "bytes": nbytes, "n_gpus": world}
     for impl in impls:
+        if impl == "interp":
+            # the same collective as a lowered pccl_b200.lang program run by the persistent interpreter kernel:
+            # best program and width (runtime CTA budget) for this size
+            if nbytes > (64 << 20):
+                continue
+            best = None
+            for name in interp_programs(eng, kind):
+                for width in (4, 16, 32):
+                    if kind == "allreduce":
+                        fn = lambda i, n_=name, w_=width: eng.exeOp(n_, ins[i], outs[i], width=w_)  # noqa: E731
+                    elif kind == "reduce_scatter":
+                        fn = lambda i, n_=name, w_=width: eng.exeOp(n_, ins[i], outs[i][:shard], width=w_)  # noqa: E731
+                    else:
+                        fn = lambda i, n_=name, w_=width: eng.exeOp(n_, ins[i][:shard], outs[i], width=w_)  # noqa: E731
+                    try:
+                        ms = _time(fn, n_slots, max(5, iters // 4), 3)
+                    except Exception as e:  # noqa: BLE001 - a program that does not fit the workspace is left out
+                        if eng.rank == 0:
+                            print(f"# interp {name} width {width} at {nbytes} bytes: {type(e).__name__}: {e}", flush=True)
+                        continue
+                    if best is None or ms < best[0]:
+                        best = (ms, name, width)
+            if best is not None:
+                alg = nbytes / (best[0] * 1e-3) / 1e9
+                res[impl] = {"us": best[0] * 1e3, "algbw_gbs": alg, "busbw_gbs": alg * bus_factor(kind, world),
+                             "program": best[1].replace("bench_", ""), "width": best[2]}
+            continue
         if impl == "nccl":
             if kind == "allreduce":
                 fn = lambda i: dist.all_reduce(ins[i])  # noqa: E731
@@ -105,9 +156,10 @@ def main() -> None:
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
-    os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
+    interp = "interp" in args.impls.split(",")
+    os.environ.setdefault("PCCL_WORKSPACE_MB", "1024" if interp else "64")      # scratch of the direct programs
     eng = Engine(rank, world)
-    eng.initEngine("cuda", heap_bytes=(2 * POOL_BYTES) + 4 * args.max_bytes + (512 << 20))
+    eng.initEngine("cuda", heap_bytes=(2 * POOL_BYTES) + 4 * args.max_bytes + (512 << 20) + ((2 << 30) if interp else 0))
     eng.connect()
     dtypes = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}
     rows = []

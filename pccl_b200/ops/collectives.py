@@ -92,6 +92,39 @@ def reduce_scatter_adamw(eng: Engine, grads: torch.Tensor, master: torch.Tensor,
     count_launch()
 
 
+def all_reduce_fp8(eng: Engine, q: torch.Tensor, s: torch.Tensor, out_q: Optional[torch.Tensor] = None,
+                   out_s: Optional[torch.Tensor] = None, op: str = "sum", blocks: Optional[int] = None, threads: int = 512,
+                   lane: int = 0, stream=None):
+    """All-reduce of a block-scaled fp8 vector: ``q`` e4m3 bytes (symmetric, n elements, n % 128 == 0) with ``s`` fp32
+    scales (symmetric, n / 128).  Every 128-value block is dequantised, accumulated in fp32 over the ranks and
+    re-quantised with a fresh scale inside the transfer; the result lands in ``out_q`` / ``out_s`` on every rank
+    (default: in place).  Returns ``(out_q, out_s)``."""
+    out_q = q if out_q is None else out_q
+    out_s = s if out_s is None else out_s
+    n = q.numel()
+    if q.element_size() != 1 or n % 128 or s.dtype != torch.float32 or s.numel() != n // 128:
+        raise ValueError("all_reduce_fp8: q must be one-byte elements (n % 128 == 0) and s fp32 with n / 128 entries")
+    st = (stream or torch.cuda.current_stream()).cuda_stream
+    C.collective(eng.raw, "allreduce_fp8", "p2p", "e4m3", op, eng.heap_offset(q), eng.heap_offset(out_q), n, lane, 1.0, "",
+                 _blocks(n // eng.world, blocks), threads, st, 0, 0, 0, eng.heap_offset(s), eng.heap_offset(out_s))
+    count_launch()
+    return out_q, out_s
+
+
+def reduce_scatter_fp8(eng: Engine, q: torch.Tensor, s: torch.Tensor, out_q: torch.Tensor, out_s: torch.Tensor, op: str = "sum",
+                       blocks: Optional[int] = None, threads: int = 512, lane: int = 0, stream=None):
+    """Reduce-scatter of a block-scaled fp8 vector (see ``all_reduce_fp8``): rank r receives blocks
+    [r * m, (r + 1) * m) with m = out_q.numel(); all four tensors are symmetric."""
+    m = out_q.numel()
+    if q.element_size() != 1 or m % 128 or q.numel() != m * eng.world or s.numel() != q.numel() // 128 or out_s.numel() != m // 128:
+        raise ValueError("reduce_scatter_fp8: shapes do not match world * shard with 128-value blocks")
+    st = (stream or torch.cuda.current_stream()).cuda_stream
+    C.collective(eng.raw, "reduce_scatter_fp8", "p2p", "e4m3", op, eng.heap_offset(q), eng.heap_offset(out_q), m, lane, 1.0, "",
+                 _blocks(m, blocks), threads, st, 0, 0, 0, eng.heap_offset(s), eng.heap_offset(out_s))
+    count_launch()
+    return out_q, out_s
+
+
 def all_gather(eng: Engine, inp: torch.Tensor, out: torch.Tensor, algo: str = "auto", blocks: Optional[int] = None,
                threads: int = 512, lane: int = 0, stream=None) -> torch.Tensor:
     """``out`` (symmetric, world * inp.numel()) receives every rank's ``inp`` at its rank's slot."""

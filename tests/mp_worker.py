@@ -86,6 +86,36 @@ def case_coll_nvls(eng, rank, world):
     return _coll_checks(eng, rank, world, "nvls")
 
 
+def case_coll_fp8(eng, rank, world):
+    """Block-scaled fp8 all-reduce and reduce-scatter through the Python API."""
+    from pccl_b200.ops import collectives as C
+    from pccl_b200.ops.gemm import dequant_rows, quant_rows
+    blocks = 64 * world
+    n = 128 * blocks
+    g = torch.Generator(device="cuda").manual_seed(41)
+    xs = [(torch.randn(blocks, 128, generator=g, device="cuda") * (1 + r)).bfloat16() for r in range(world)]
+    qs = [quant_rows(x) for x in xs]
+    ref = torch.stack([dequant_rows(q, s) for q, s in qs]).sum(0)
+    q = eng.symmetric_tensor((n,), torch.uint8); s = eng.symmetric_tensor((blocks,), torch.float32)
+    oq = eng.symmetric_tensor((n,), torch.uint8); os_ = eng.symmetric_tensor((blocks,), torch.float32)
+    rq = eng.symmetric_tensor((n // world,), torch.uint8); rs = eng.symmetric_tensor((blocks // world,), torch.float32)
+    for it in range(2):
+        q.copy_(qs[rank][0].view(-1)); s.copy_(qs[rank][1].view(-1))
+        torch.cuda.synchronize(); dist.barrier()
+        C.all_reduce_fp8(eng, q, s, oq, os_)
+        C.reduce_scatter_fp8(eng, q, s, rq, rs, lane=1)
+        torch.cuda.synchronize()
+        got = dequant_rows(oq.view(blocks, 128), os_.view(blocks, 1))
+        assert (got - ref).abs().max().item() <= 0.0625 * ref.abs().max().item() + 1e-6, "all_reduce_fp8"
+        assert torch.allclose(os_, ref.abs().amax(-1) / 448.0, rtol=1e-5, atol=0)
+        mine = ref[rank * (blocks // world):(rank + 1) * (blocks // world)]
+        got = dequant_rows(rq.view(blocks // world, 128), rs.view(blocks // world, 1))
+        assert (got - mine).abs().max().item() <= 0.0625 * mine.abs().max().item() + 1e-6, "reduce_scatter_fp8"
+        dist.barrier()
+    eng.raise_on_status(8, "fp8 all-reduce"); eng.raise_on_status(9, "fp8 reduce-scatter")
+    return {"ok": True}
+
+
 def case_interp(eng, rank, world):
     """Lowered programs through the interpreter kernel, including the NVLS ones."""
     from pccl_b200.lang import build

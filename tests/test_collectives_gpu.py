@@ -168,6 +168,48 @@ def test_interpreter_peer_never_arrives(native):
     assert torch.ones(4, device="cuda").sum().item() == 4.0
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("kind,redop", [("allreduce_fp8", "sum"), ("allreduce_fp8", "max"), ("reduce_scatter_fp8", "sum")])
+def test_fp8_block_scaled_reduce_emulated(native, world, kind, redop):
+    """Block-scaled fp8 all-reduce / reduce-scatter: dequantise, accumulate in fp32, requantise with a fresh scale."""
+    from pccl_b200.ops.gemm import dequant_rows, quant_rows
+    shard_blocks = 24
+    n = 128 * shard_blocks * world            # elements of the whole vector
+    g = torch.Generator(device="cuda").manual_seed(33)
+    xs = [(torch.randn(n // 128, 128, generator=g, device="cuda") * (1 + r)).bfloat16() for r in range(world)]
+    qs = [quant_rows(x) for x in xs]
+    q_in, s_in = DATA_OFF, DATA_OFF + n
+    q_out, s_out = s_in + (n // 128) * 4, s_in + (n // 128) * 4 + n
+    hs = [torch.zeros(s_out + (n // 128) * 4 + 256, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    for r in range(world):
+        hs[r][q_in:q_in + n] = qs[r][0].view(-1)
+        hs[r][s_in:s_in + (n // 128) * 4].view(torch.float32)[:] = qs[r][1].view(-1)
+    count = n if kind == "allreduce_fp8" else n // world
+    native.emu_collective(kind, [h.data_ptr() for h in hs], SIGNAL_OFF, FLAG_OFF, "e4m3", redop, q_in, q_out, count, 1, 2, 1.0, "",
+                          4, 256, torch.cuda.current_stream().cuda_stream, [s.data_ptr() for s in st], [], [], 0, s_in, s_out)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+    vals = torch.stack([dequant_rows(q, s) for q, s in qs])       # [world, n/128, 128] exact inputs
+    ref = vals.sum(0) if redop == "sum" else vals.amax(0)
+    for r in range(world):
+        if kind == "allreduce_fp8":
+            oq = hs[r][q_out:q_out + n].view(n // 128, 128)
+            os_ = hs[r][s_out:s_out + (n // 128) * 4].view(torch.float32).view(n // 128, 1)
+            want = ref
+        else:
+            m = n // world
+            oq = hs[r][q_out:q_out + m].view(m // 128, 128)
+            os_ = hs[r][s_out:s_out + (m // 128) * 4].view(torch.float32).view(m // 128, 1)
+            want = ref[r * shard_blocks:(r + 1) * shard_blocks]
+        # the fresh scale is the block maximum over 448, and the payload is the e4m3 rounding of value / scale
+        assert torch.allclose(os_.view(-1), want.abs().amax(-1) / 448.0, rtol=1e-5, atol=0)
+        got = dequant_rows(oq, os_)
+        assert (got - want).abs().max().item() <= 0.0625 * want.abs().max().item() + 1e-6
+        want_q = (want / os_).to(torch.float8_e4m3fn).float()
+        assert (oq.view(torch.float8_e4m3fn).float() - want_q).abs().max().item() <= 32.0     # at most one e4m3 step at the top of the range
+
+
 # ---------------------------------------------------------------------------------------------
 # fused collective + GEMM kernels, ranks emulated on one GPU
 # ---------------------------------------------------------------------------------------------

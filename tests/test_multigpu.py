@@ -31,7 +31,7 @@ def _world():
     return min(torch.cuda.device_count(), 8)
 
 
-@pytest.mark.parametrize("case", ["heap", "coll_p2p", "coll_nvls", "interp", "dp", "dp_milp_ring", "fused_tp", "fused_tp_fp8", "tp_mlp", "moe"])
+@pytest.mark.parametrize("case", ["heap", "coll_p2p", "coll_nvls", "coll_fp8", "interp", "dp", "dp_milp_ring", "fused_tp", "fused_tp_fp8", "tp_mlp", "moe"])
 def test_case(case, tmp_path):
     _run(case, _world(), tmp_path)
 
