@@ -125,6 +125,7 @@ void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
   peer_heaps_.assign(world_, nullptr);
   peer_heaps_[rank_] = heap_;
   lane_epochs_.assign(8, 0);
+  lane_launches_.assign(64, 0);
 
   configs_["host_id"] = host_id_;
   configs_["device"] = device_;
@@ -252,7 +253,8 @@ void Engine::rebind(int new_rank, int new_world) {
   peer_heaps_.assign(world_, nullptr);
   peer_heaps_[rank_] = mine;
   if (device_ == "cpu") std::memset(heap_ + layout_.signal_off, 0, layout_.num_signals * 8);
-  for (auto& kv : ops_) kv.second.epoch = 0;
+  for (auto& kv : ops_)
+    for (auto& v : kv.second.variants) v.second.epoch = 0;
 }
 
 void Engine::injectFault(const std::string& kind) {
@@ -269,11 +271,6 @@ void Engine::regOp(const std::string& name, const std::string& path_or_json) {
   std::lock_guard<std::mutex> g(mu_);
   if (ops_.count(name)) throw std::runtime_error("regOp: '" + name + "' is already registered");
   Op op;
-  op.slots_reserved = p.num_slots * static_cast<uint32_t>(max_width_);
-  if (initialized_ && next_slot_ + op.slots_reserved > layout_.num_signals)
-    throw std::runtime_error("regOp: out of signal words");
-  op.slot_base = next_slot_;
-  next_slot_ += op.slots_reserved;
   op.program = std::move(p);
   ops_.emplace(name, std::move(op));
 }
@@ -360,6 +357,19 @@ int Engine::exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, ui
   return exeOnCuda(op, in_ptr, out_ptr, in_bytes, dt, width, lane, stream);
 }
 
+// Signal words of a (program, width) pair are handed out at its first launch; every rank launches the same sequence
+// of (op, width) pairs, so every rank arrives at the same numbering.
+Engine::Op::Variant& Engine::variantFor(Op& op, int width) {
+  auto it = op.variants.find(width);
+  if (it != op.variants.end()) return it->second;
+  const uint32_t need = op.program.num_slots * static_cast<uint32_t>(width);
+  if (next_slot_ + need > layout_.num_signals) throw std::runtime_error("exeOp: out of signal words");
+  Op::Variant v;
+  v.slot_base = next_slot_;
+  next_slot_ += need;
+  return op.variants.emplace(width, v).first->second;
+}
+
 int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dt, int width, int lane) {
   const Program& p = op.program;
   uint64_t bb = p.blockBytesForInput(in_bytes);
@@ -374,7 +384,8 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
     throw std::runtime_error("exeOp: message needs " + std::to_string(m.buf_bytes[BUF_SCRATCH]) +
                              " bytes of scratch but a workspace lane half holds " + std::to_string(half) +
                              " (raise PCCL_WORKSPACE_MB or split the message)");
-  uint64_t scratch_off = lane * lane_bytes + (op.epoch & 1) * half;
+  Op::Variant& var = variantFor(op, width);
+  uint64_t scratch_off = lane * lane_bytes + (lane_launches_.at(lane)++ & 1) * half;
   CpuExecContext ctx;
   ctx.rank = rank_;
   ctx.world = world_;
@@ -392,8 +403,8 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   ctx.tcp = tcp_.get();
   ctx.tcp_scratch_key = tcp_key_;
   ctx.tcp_scratch_off = scratch_off;
-  ctx.slot_base = op.slot_base;
-  ctx.epoch = op.epoch;
+  ctx.slot_base = var.slot_base;
+  ctx.epoch = var.epoch;
   ctx.dtype = dt;
   ctx.redop = parseRedOp(p.redop);
   ctx.timeout_ms = timeout_ms_;
@@ -401,7 +412,7 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   ctx.trace = trace_;
   CpuExecResult res = runOnCpu(m, ctx);
   for (auto& ev : res.trace) spans_.push_back(Span{p.name, ev.stream, ev.pc, ev.op, ev.t0_ns, ev.t1_ns, ev.bytes});
-  op.epoch++;
+  var.epoch++;
   op.launches++;
   op.bytes += m.bytes_moved;
   op.nanos += res.nanos;
@@ -450,8 +461,9 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   InterpLaunch L{};
   L.w = worldTable();
   L.nvirt = 1;
-  L.slot_base = op.slot_base;
-  L.epoch = op.epoch;
+  Op::Variant& var = variantFor(op, width);
+  L.slot_base = var.slot_base;
+  L.epoch = var.epoch;
   L.dtype = dt;
   L.redop = parseRedOp(p.redop);
   L.spin_limit = spin_limit_;
@@ -467,12 +479,12 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   R.output_heap_off = heapOff(p.in_place ? in_ptr : out_ptr);
   if (p.remote_io && (R.input_heap_off < 0 || R.output_heap_off < 0))
     throw std::runtime_error("exeOp: this program lets peers touch the tensors, so both must come from the symmetric heap");
-  R.scratch_off = lane * lane_bytes + (op.epoch & 1) * half;
+  R.scratch_off = lane * lane_bytes + (lane_launches_.at(lane)++ & 1) * half;
   for (int b = 0; b < BUF_COUNT; ++b) R.buf_bytes[b] = c.m.buf_bytes[b];
   R.status = reinterpret_cast<uint32_t*>(statusPtr(lane));
   int err = launchInterpreter(L, 512, reinterpret_cast<cudaStream_t>(stream));
   if (err != 0) throw std::runtime_error(std::string("exeOp: kernel launch failed: ") + cudaErrorName(err));
-  op.epoch++;
+  var.epoch++;
   op.launches++;
   op.bytes += c.m.bytes_moved;
   return 0;

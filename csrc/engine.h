@@ -96,9 +96,11 @@ class Engine {
  private:
   struct Op {
     Program program;
-    uint32_t slot_base = 0;
-    uint32_t slots_reserved = 0;
-    uint64_t epoch = 0;
+    // A program is materialised per width (replicas of every channel); each width has its own signal words and
+    // its own launch count, because signals only ever count up: "launch e expects e * count + k" holds only
+    // among launches that use the same words the same way.
+    struct Variant { uint32_t slot_base = 0; uint64_t epoch = 0; };
+    std::map<int, Variant> variants;
     uint64_t launches = 0, bytes = 0, nanos = 0, timeouts = 0;
     struct DeviceCopy { Instr* instrs = nullptr; uint32_t* starts = nullptr; int n_streams = 0; Materialized m; };
     std::map<std::pair<uint64_t, int>, DeviceCopy> device_cache;
@@ -107,6 +109,7 @@ class Engine {
   void buildLayout(uint64_t heap_bytes);
   void setupPeers(const std::map<int, NodeMeta>& nodes);
   void dropPeers();
+  Op::Variant& variantFor(Op& op, int width);
   int exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane);
   int exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane, uint64_t stream);
 
@@ -128,6 +131,7 @@ class Engine {
   uint32_t next_slot_ = 0;
   std::mutex mu_;
   std::vector<uint64_t> lane_epochs_;
+  std::vector<uint64_t> lane_launches_;     // programs launched per workspace lane: picks the scratch half
   int timeout_ms_ = 30000;
   uint64_t spin_limit_ = kDefaultSpinLimit;
   bool bounds_check_ = true;

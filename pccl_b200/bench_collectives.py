@@ -106,6 +106,11 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
                         if eng.rank == 0:
                             print(f"# interp {name} width {width} at {nbytes} bytes: {type(e).__name__}: {e}", flush=True)
                         continue
+                    st = eng.check_status(0)
+                    if st[0] != 0:        # the kernel gave up (bounds check, time-out): not a timing
+                        if eng.rank == 0:
+                            print(f"# interp {name} width {width} at {nbytes} bytes: device status {list(st)}", flush=True)
+                        continue
                     if best is None or ms < best[0]:
                         best = (ms, name, width)
             if best is not None:

@@ -61,6 +61,28 @@ def _baseline_rank(rank, world, port, transport):
     return (torch.equal(y, ref), (y - ref).abs().max().item(), tcp)
 
 
+def _mixed_width_rank(rank, world, port):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, build
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("ring_allreduce", world, channels=2, device_type=DeviceType.CPU))
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.rand(6 * 1024, generator=g) for _ in range(world)]
+    errs = []
+    for it, width in enumerate([1, 3, 1, 2, 3, 3, 1]):     # the runtime CTA/thread budget changes from launch to launch
+        y = torch.empty_like(xs[rank])
+        e.exeOp("ar", xs[rank] + it, y, width=width)
+        errs.append((y - (sum(xs) + it * world)).abs().max().item())
+    e.exitCluster()
+    return max(errs)
+
+
+def test_one_op_may_run_at_a_different_width_on_every_launch():
+    res = run_ranks(_mixed_width_rank, 2, env={"PCCL_WORKSPACE_MB": "16"})
+    assert max(res.values() if isinstance(res, dict) else res) < 1e-5
+
+
 def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
     # ring allreduce (sum) of 4M fp32 per rank, uniform[-1,1) from seed 0, world 2, checked against torch sum
     for transport in ("shm", "tcp"):
