@@ -5,7 +5,7 @@
 //   add only; its ld_reduce never returns the loaded value and the scalar .red forms are malformed)
 //   include/plugins/cuda_executor/utils/vector_datatype.h:21-80 (packed register types)
 // — and adds what a kernel that talks to peers needs: system-scope release/acquire flag accesses,
-// waits that give up after a poll budget instead of hanging, min/max in-switch reductions for the
+// waits that give up after a time limit instead of hanging, min/max in-switch reductions for the
 // 16-bit types, fp32 accumulation for 16-bit in-switch sums, and typed 16-byte reduce helpers.
 #pragma once
 #include <cuda_bf16.h>

@@ -1,6 +1,6 @@
 // Blackwell (sm_100a) building blocks in inline PTX: mbarrier, TMA tile loads (never with cluster
 // multicast), tcgen05 tensor-core MMA with TMEM accumulators, and the shared-memory / instruction
-// descriptors the MMA takes.  Every wait is bounded: it returns false when its poll budget runs out
+// descriptors the MMA takes.  Every wait is bounded: it returns false when its time limit runs out
 // so that the caller can flag the error, drain its copies, free TMEM and leave.
 #pragma once
 #include <cuda.h>

@@ -74,11 +74,24 @@ def _compile(cmd, src: Path, hdr_mtime: float, verbose: bool, extra=()):
 _lock = threading.Lock()
 
 
-def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile whatever changed and link ``_C.so``.  Safe to call repeatedly."""
+SANITIZED_TARGET = ROOT / "build" / "sanitize" / "_C.so"
+
+
+def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False, sanitize: bool = False) -> Path:
+    """Compile whatever changed and link ``_C.so``.  Safe to call repeatedly.
+
+    ``sanitize=True`` builds a second copy, ``build/sanitize/_C.so``, whose HOST objects are compiled with
+    ``-fsanitize=address,undefined`` (the device objects are shared with the normal build).  Load it with
+    ``PCCL_NATIVE_LIB=<that path>`` and ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``; it is what the CPU test
+    suite uses to run the engine, daemon, transport and executor under the sanitizers."""
     with _lock:
         OBJ.mkdir(parents=True, exist_ok=True)
         cxx, nv = _flags()
+        target = TARGET
+        if sanitize:
+            cxx = [c for c in cxx if c != "-O2"] + ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined"]
+            target = SANITIZED_TARGET
+            target.parent.mkdir(parents=True, exist_ok=True)
         cc, cu = sources()
         hdr = _newest_header()
         if force:
@@ -94,17 +107,18 @@ def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False) -
             results = [j.result() for j in jobs]
         objs = [str(o) for o, _ in results]
         changed = any(c for _, c in results)
-        if changed or not TARGET.exists():
-            link = ["g++", "-shared", "-o", str(TARGET)] + objs + [
+        if changed or not target.exists():
+            link = ["g++", "-shared", "-o", str(target)] + objs + [
                 f"-L{CUDA_HOME}/lib64", "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+            if sanitize:
+                link += ["-fsanitize=address,undefined"]
             if verbose:
-                print("[pccl build] link", TARGET.name, flush=True)
+                print("[pccl build] link", target, flush=True)
             r = subprocess.run(link, capture_output=True, text=True)
             if r.returncode != 0:
                 raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-        return TARGET
+        return target
 
 
 if __name__ == "__main__":
-    build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas-info" in sys.argv)
-    print(TARGET)
+    print(build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas-info" in sys.argv, sanitize="--sanitize" in sys.argv))

@@ -10,6 +10,16 @@ _HERE = Path(__file__).resolve().parent
 
 
 def load():
+    override = os.environ.get("PCCL_NATIVE_LIB")
+    if override:
+        # an alternative build of the same extension (the sanitizer build of the host code, for one)
+        import importlib.util
+        import sys
+        spec = importlib.util.spec_from_file_location("pccl_b200._C", override)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        sys.modules["pccl_b200._C"] = mod
+        return mod
     so = _HERE / "_C.so"
     if not so.exists() or os.environ.get("PCCL_REBUILD") == "1":
         from . import _build

@@ -1,14 +1,15 @@
 """Data parallelism with bucketed gradient reduce-scatter overlapped with backward.
 
 Gradients live in flat bf16 buckets (25 MB by default) inside the symmetric heap.  The moment the
-last gradient of a bucket has been written (the weight-gradient GEMMs write there directly), the
-bucket's reduce-scatter kernel is queued on a side stream with a small CTA budget: each rank
-pull-reduces its 1/world slice from every peer over NVLink (or multimem.ld_reduce through the
-switch), multiplies by 1/world and stores fp32 -- reduction, scaling and cast in one pass, while
-backward keeps the other SMs.  The optimizer is sharded the same way (ZeRO-1): fused AdamW on the
-fp32 slice writes the new bf16 parameters into the flat parameter buffer, and an all-gather kernel
-pushes each slice to every rank.  With a world of one the same kernels run (the reduce-scatter
-degenerates to the scale/cast pass), so single-GPU and multi-GPU steps share one code path.
+last gradient of a bucket has been written (the weight-gradient GEMMs write there directly), ONE
+kernel is queued on a high-priority side stream: each rank reduces its 1/world slice of the bucket
+(multimem.ld_reduce through the switch, or loads from every peer over NVLink), multiplies by
+1/world and applies AdamW to its fp32 master slice -- reduction, scaling, cast and optimizer in one
+pass -- and writes the new bf16 parameters, which the bucket's all-gather kernel then pushes to
+every rank (ZeRO-1).  The kernels run as short, wide bursts (64 to 128 CTAs) that slip in between
+two GEMM kernels of backward.  With a world of one the same kernels run (the reduce-scatter
+degenerates to the scale/cast/update pass), so single-GPU and multi-GPU steps share one code path.
+``fuse_optimizer=False`` keeps the reduce-scatter (with scale and fp32 cast) and the optimizer apart.
 """
 from __future__ import annotations
 

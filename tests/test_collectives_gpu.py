@@ -155,7 +155,7 @@ def test_bounded_wait_returns_timeout_status(native):
 
 
 def test_interpreter_peer_never_arrives(native):
-    """Rank 1's streams are left out: rank 0 gives up after its poll budget and reports where."""
+    """Rank 1's streams are left out: rank 0 gives up after its time limit and reports where."""
     from pccl_b200.lang import build, to_schedule
     doc = json.dumps(to_schedule(build("ring_allreduce", 2)))
     hs, st = _heaps(2, 1 << 20)

@@ -1,0 +1,46 @@
+"""The host side of the native extension (engine, cluster daemon, TCP transport, CPU executor, bindings) under
+AddressSanitizer and UndefinedBehaviorSanitizer: a second build of the extension with instrumented host objects runs
+part of the CPU suite in a child process.  compute-sanitizer is not available for the device side; the kernels have
+their own bounds-checked mode and differential tests instead."""
+import os
+import shutil
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def _runtime(name):
+    r = subprocess.run(["gcc", f"-print-file-name={name}"], capture_output=True, text=True)
+    path = r.stdout.strip()
+    return path if r.returncode == 0 and os.path.isabs(path) and os.path.exists(path) else None
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc")
+def test_host_code_is_clean_under_asan_and_ubsan():
+    asan, stdcxx = _runtime("libasan.so"), _runtime("libstdc++.so")
+    if not asan or not stdcxx:
+        pytest.skip("the sanitizer runtime of this gcc is not installed")
+    sys.path.insert(0, ROOT)
+    from pccl_b200 import _build
+    lib = _build.build(verbose=False, sanitize=True)
+    env = dict(os.environ)
+    # libstdc++ is preloaded next to the sanitizer runtime: python itself does not link it, and the runtime's
+    # interceptor of __cxa_throw must find the real one when it initialises
+    env.update({"LD_PRELOAD": f"{asan} {stdcxx}", "PCCL_NATIVE_LIB": str(lib),
+                "ASAN_OPTIONS": "detect_leaks=0:halt_on_error=1", "UBSAN_OPTIONS": "print_stacktrace=1:halt_on_error=1"})
+    cmd = [sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider",
+           os.path.join(HERE, "test_native_common.py"),
+           os.path.join(HERE, "test_engine_cpu.py") + "::test_one_op_may_run_at_a_different_width_on_every_launch",
+           os.path.join(HERE, "test_engine_cpu.py") + "::test_regop_accepts_file_and_rejects_garbage",
+           os.path.join(HERE, "test_engine_cpu.py") + "::test_instruction_trace_is_chrome_trace_json",
+           os.path.join(HERE, "test_elastic_cpu.py") + "::test_survivors_run_in_the_resized_world",
+           os.path.join(HERE, "test_elastic_cpu.py") + "::test_wait_on_a_rank_that_never_launches_times_out"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500, cwd=ROOT)
+    text = r.stdout + r.stderr
+    assert "AddressSanitizer" not in text and "runtime error:" not in text, text[-6000:]
+    assert r.returncode == 0, text[-6000:]
+    assert " passed" in text
