@@ -118,6 +118,43 @@ def test_fused_and_unfused_optimizer_paths_agree():
     assert (flats[0] == flats[1]).float().mean().item() > 0.9       # identical except where atomics order / bf16 rounding of a gradient differs
 
 
+def test_dp_checkpoint_resume_matches_uninterrupted_training(tmp_path):
+    """torch.save of the sharded optimizer state and flat parameters after two steps, loaded into a differently
+    initialised trainer, continues like the run that was never interrupted."""
+    from pccl_b200.engine import Engine
+    from pccl_b200.models import GPT, GPTConfig
+    from pccl_b200.parallel import ShardedDataParallel
+    cfg = GPTConfig.tiny()
+    ids = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+
+    def make(seed):
+        torch.manual_seed(seed)
+        model = GPT(cfg, device="cuda")
+        eng = Engine(0, 1); eng.initEngine("cuda", heap_bytes=256 << 20)
+        return model, eng, ShardedDataParallel(model, eng, lr=1e-3, bucket_mb=0.5)
+
+    model, eng, dp = make(0)
+    for _ in range(2):
+        dp.train_step(ids, ids.roll(-1, 1))
+    torch.cuda.synchronize()
+    torch.save(dp.gather_full_state(), tmp_path / "ckpt.pt")
+    for _ in range(2):
+        last = float(dp.train_step(ids, ids.roll(-1, 1)))
+    torch.cuda.synchronize()
+    want = dp.flat_params.float().clone()
+    del dp, model, eng
+    model, eng, dp = make(1)            # other initial weights: everything has to come from the checkpoint
+    dp.load_full_state(torch.load(tmp_path / "ckpt.pt"))
+    assert dp.step_count == 2
+    for _ in range(2):
+        resumed = float(dp.train_step(ids, ids.roll(-1, 1)))
+    torch.cuda.synchronize()
+    got = dp.flat_params.float()
+    assert abs(resumed - last) <= 2e-2 * abs(last), (resumed, last)
+    assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    assert (got == want).float().mean().item() > 0.9
+
+
 @pytest.mark.parametrize("rows,D", [(37, 256), (4096, 2048), (600, 4096), (130, 8192)])
 def test_layernorm_kernels_match_fp32_reference(rows, D):
     from pccl_b200.nn import LayerNorm
