@@ -3,7 +3,9 @@ missing it is built in-tree, and if that fails the import error says why."""
 from __future__ import annotations
 
 import importlib
+import importlib.util
 import os
+import sys
 from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
@@ -13,8 +15,6 @@ def load():
     override = os.environ.get("PCCL_NATIVE_LIB")
     if override:
         # an alternative build of the same extension (the sanitizer build of the host code, for one)
-        import importlib.util
-        import sys
         spec = importlib.util.spec_from_file_location("pccl_b200._C", override)
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
