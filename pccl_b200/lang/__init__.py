@@ -6,8 +6,10 @@ from .verify import Report, VerificationError, port_load, verify
 from .lower import LoweringError, OPCODES, check_lowered_deadlock_free, lower, to_schedule
 from . import algorithms
 from .algorithms import ALGORITHMS, build
+from .cluster import Cluster
+from .operator import Operator
 
 __all__ = ["DirectedGraph", "BUFFER_KINDS", "Chunk", "CollectiveIR", "Device", "DeviceType", "Link",
            "PrimitiveOp", "PrimitiveOpType", "Report", "VerificationError", "port_load", "verify",
            "LoweringError", "OPCODES", "check_lowered_deadlock_free", "lower", "to_schedule",
-           "algorithms", "ALGORITHMS", "build"]
+           "algorithms", "ALGORITHMS", "build", "Cluster", "Operator"]

@@ -78,6 +78,26 @@ def _mixed_width_rank(rank, world, port):
     return max(errs)
 
 
+def _operator_rank(rank, world, port):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, Operator
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    op = Operator.from_algorithm("direct_allreduce", world, name="ar", channels=2, device_type=DeviceType.CPU).register(e)
+    g = torch.Generator().manual_seed(9)
+    xs = [torch.rand(4096, generator=g) for _ in range(world)]
+    y = torch.empty_like(xs[rank])
+    st = op(xs[rank], y, width=2)
+    e.exitCluster()
+    return st, (y - sum(xs)).abs().max().item()
+
+
+def test_operator_object_registers_and_runs_on_cpu_ranks():
+    res = run_ranks(_operator_rank, 2, env={"PCCL_WORKSPACE_MB": "16"})
+    for r in (0, 1):
+        assert res[r][0] == 0 and res[r][1] < 1e-5
+
+
 def test_one_op_may_run_at_a_different_width_on_every_launch():
     res = run_ranks(_mixed_width_rank, 2, env={"PCCL_WORKSPACE_MB": "16"})
     assert max(res.values() if isinstance(res, dict) else res) < 1e-5

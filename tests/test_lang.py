@@ -120,3 +120,34 @@ def test_lowering_rejects_missing_barrier_partner():
                                         [remap[d] for d in o.dependencies if d in remap], o.metadata)
     with pytest.raises(LoweringError):
         lower(ir2)
+
+
+def test_reference_module_names_resolve_and_cluster_operator_helpers_work(tmp_path):
+    import pccl.lang.chunk as chunk
+    import pccl.lang.cluster as cluster
+    import pccl.lang.operator as operator
+    import pccl.lang.topology as topology
+    from pccl.lang.utils.graph import DirectedGraph as DG
+    from pccl_b200.lang import Cluster, Operator, DirectedGraph, build, verify
+    assert DG is DirectedGraph and chunk.CollectiveIR is not None and topology.Topology is not None
+    assert cluster.Cluster is Cluster and operator.Operator is Operator
+    # a ring cluster stamped onto a ring program verifies; the same program on too small a cluster is refused
+    ir = Cluster.ring(4).apply(build("ring_allreduce", 4, channels=2))
+    verify(ir).raise_if_failed()
+    assert len(ir.links) == 8 and ir.attrs["cluster"] == "ring4"
+    with pytest.raises(ValueError):
+        Cluster.ring(2).apply(build("ring_allreduce", 4))
+    # cluster <-> synthesiser topology
+    topo = Cluster.nvswitch(8).to_topology()
+    assert topo.n == 8 and len(topo.link_bw) == 56
+    assert Cluster.from_topology(topology.Topology.ring(4)).world_size == 4
+    # operators: from the library, synthesised, saved as a schedule file
+    op = Operator.from_algorithm("direct_allreduce", 4)
+    doc = op.schedule()
+    assert doc["collective"] == "allreduce" and op.schedule() is doc
+    import json
+    assert json.load(open(op.save(str(tmp_path / "op.json"))))["world_size"] == 4
+    syn = Operator.synthesized("allgather", Cluster.ring(4).to_topology(), 1 << 20)
+    assert syn.collective == "allgather" and syn.ir.attrs["synthesized"]
+    with pytest.raises(RuntimeError):
+        op(None)                      # not registered with an engine
