@@ -459,6 +459,13 @@ ALGORITHMS = {
 
 
 def build(name: str, n: int, **kw) -> CollectiveIR:
+    """The library algorithm ``name`` for ``n`` ranks.  ``channels`` defaults to the environment variable
+    ``PCCL_CHANNELS`` (1 when unset)."""
     if name not in ALGORITHMS:
         raise KeyError(f"unknown algorithm {name!r}; have {sorted(ALGORITHMS)}")
+    if "channels" not in kw:
+        import os
+        env = os.environ.get("PCCL_CHANNELS", "")
+        if env.isdigit() and int(env) > 0:
+            kw["channels"] = int(env)
     return ALGORITHMS[name](n, **kw)

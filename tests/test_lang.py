@@ -151,3 +151,15 @@ def test_reference_module_names_resolve_and_cluster_operator_helpers_work(tmp_pa
     assert syn.collective == "allgather" and syn.ir.attrs["synthesized"]
     with pytest.raises(RuntimeError):
         op(None)                      # not registered with an engine
+
+
+def test_default_channel_count_comes_from_the_environment(monkeypatch):
+    from pccl_b200.lang import build, to_schedule
+
+    def streams(doc):
+        return doc["lowered"]["num_channels"]
+    monkeypatch.delenv("PCCL_CHANNELS", raising=False)
+    one = streams(to_schedule(build("ring_allreduce", 4)))
+    monkeypatch.setenv("PCCL_CHANNELS", "3")
+    assert streams(to_schedule(build("ring_allreduce", 4))) == 3 * one
+    assert streams(to_schedule(build("ring_allreduce", 4, channels=1))) == one      # an explicit argument wins
