@@ -99,3 +99,26 @@ def _run_synth(rank, world, port, coll, topo_kind):
 def test_synthesised_schedule_runs_on_cpu_ranks(coll, topo_kind):
     res = run_ranks(_run_synth, 4, args=(coll, topo_kind), env={"PCCL_WORKSPACE_MB": "32"})
     assert all(v < 1e-4 for v in res.values()), res
+
+
+def test_examples_compile_and_the_cpu_ones_run(tmp_path):
+    """Every example is at least importable Python; the synthesis example runs end to end on CPU."""
+    import glob
+    import json
+    import os
+    import py_compile
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "examples", "**", "*.py"), recursive=True))
+    assert len(files) >= 5
+    for f in files:
+        py_compile.compile(f, doraise=True, cfile=str(tmp_path / (os.path.basename(f) + "c")))
+    out = tmp_path / "ag.json"
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "collective", "synthesize.py"), "--topology", "ring", "--world", "4",
+                        "--collective", "allgather", "--mbytes", "1", "--out", str(out), "--cache-dir", str(tmp_path / "cache")],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rep = json.loads(r.stdout.strip().splitlines()[-1])
+    assert rep["steps"] == 2 and rep["cache_hits"] == 1 and rep["cache_misses"] == 1
+    assert json.load(open(out))["collective"] == "allgather"
