@@ -20,7 +20,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--topology", choices=["nvswitch", "ring"], default="nvswitch")
     ap.add_argument("--world", type=int, default=8)
-    ap.add_argument("--collective", choices=["allreduce", "reduce_scatter", "allgather"], default="allreduce")
+    ap.add_argument("--collective", choices=["allreduce", "reduce_scatter", "allgather", "alltoall"], default="allreduce")
     ap.add_argument("--mbytes", type=float, default=64.0)
     ap.add_argument("--chunks", type=int, default=1)
     ap.add_argument("--out", default="")

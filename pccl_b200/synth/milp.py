@@ -31,7 +31,7 @@ from scipy.optimize import Bounds, LinearConstraint, milp
 from scipy.sparse import lil_matrix
 
 from ..lang import Chunk, CollectiveIR, Device, DeviceType, Link, verify
-from ..lang.algorithms import allgather_conditions, allreduce_conditions, reduce_scatter_conditions
+from ..lang.algorithms import allgather_conditions, allreduce_conditions, alltoall_conditions, reduce_scatter_conditions
 from .topology import Topology
 
 
@@ -46,14 +46,21 @@ class SynthesisResult:
     lower_bound_seconds: float
 
 
-def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float, symmetric: bool, time_limit: float):
+def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float, symmetric: bool, time_limit: float,
+                     alltoall: bool = False):
+    """Spreading model.  All-gather: commodity (owner o, chunk c) starts on o and must reach everybody.  With
+    ``alltoall`` a commodity is (o, destination d, c): it must reach d only, other devices may relay it (they
+    receive it at most once).  Returns per step the transfers (o, c, u, v), or (o, d, c, u, v) for all-to-all."""
     n = topo.n
     # Times inside the model are in microseconds: in seconds the coefficients (1e-6) would sit below
     # the solver's feasibility tolerance and it would accept schedules that overrun a port.
     alpha = topo.alpha * 1e6
     chunk_bytes = chunk_bytes * 1e6
     owners = [0] if symmetric else list(range(n))
-    K = [(o, c) for o in owners for c in range(chunks)]
+    if alltoall:
+        K = [(o, c, d) for o in owners for d in range(n) if d != o for c in range(chunks)]
+    else:
+        K = [(o, c, None) for o in owners for c in range(chunks)]
     E = sorted(topo.link_bw)
     nK, nE, S = len(K), len(E), steps
     ix = lambda k, e, s: (k * nE + e) * S + s                     # noqa: E731
@@ -74,11 +81,12 @@ def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float
     ub[base_t:] = np.inf
     integrality = np.ones(nv)
     integrality[base_t:] = 0
-    for k, (o, c) in enumerate(K):
+    for k, (o, c, dest) in enumerate(K):
         for u in range(n):
             v0 = 1.0 if u == o else 0.0
             lb[ip(k, u, 0)] = ub[ip(k, u, 0)] = v0
-            lb[ip(k, u, S)] = 1.0                                    # everybody has it at the end
+            if dest is None or u == dest:
+                lb[ip(k, u, S)] = 1.0                                # everybody (all-to-all: the destination) has it at the end
         for s in range(S):
             for e, (u, v) in enumerate(E):
                 add({ix(k, e, s): 1.0, ip(k, u, s): -1.0}, -np.inf, 0.0)
@@ -99,7 +107,8 @@ def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float
                 for e, (a, b) in enumerate(E):
                     if b == v:
                         co[ix(k, e, s)] = 1.0
-            add(co, 1.0, 1.0)                                        # received exactly once
+            # received exactly once (all-to-all: a relay at most once, the destination exactly once)
+            add(co, 1.0 if (dest is None or v == dest) else 0.0, 1.0)
     for s in range(S):
         if symmetric:
             co = {base_t + s: 1.0, base_u + s: -alpha}
@@ -148,15 +157,15 @@ def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float
     if res.x is None:
         return None, res
     sends: List[List[Tuple[int, int, int, int]]] = [[] for _ in range(S)]
-    for k, (o, cidx) in enumerate(K):
+    for k, (o, cidx, dest) in enumerate(K):
         for s in range(S):
             for e, (u, v) in enumerate(E):
                 if res.x[ix(k, e, s)] > 0.5:
-                    if symmetric:
-                        for r in range(n):
-                            sends[s].append((r, cidx, (u + r) % n, (v + r) % n))
-                    else:
-                        sends[s].append((o, cidx, u, v))
+                    for r in (range(n) if symmetric else [0]):
+                        if dest is None:
+                            sends[s].append(((o + r) % n, cidx, (u + r) % n, (v + r) % n))
+                        else:
+                            sends[s].append(((o + r) % n, (dest + r) % n, cidx, (u + r) % n, (v + r) % n))
     return sends, res
 
 
@@ -183,6 +192,42 @@ def _build_allgather_ir(n: int, chunks: int, sends, name: str) -> CollectiveIR:
             new[(o, c, v)] = ir.copy(Chunk({o}, v, 1, org, "scratch", origin=org), Chunk({o}, v, 1, org, "output", origin=org),
                                      deps=[push], step=2 + 2 * s, channel=c)
         have.update(new)
+    return ir
+
+
+def _build_alltoall_ir(n: int, chunks: int, sends, name: str) -> CollectiveIR:
+    """Block d of rank o's input becomes block o of rank d's output.  Every hop lands in the receiver's scratch slot
+    of its (o, d, c) -- relays forward from there, the destination copies it into its output -- so nobody writes a
+    peer's input or output tensor and the program also runs on the host executor."""
+    blk = chunks
+    U = n * blk
+    ir = CollectiveIR(name, "alltoall", U, buffers={"input": U, "output": U, "scratch": n * U})
+    ir.attrs["block_units"] = blk
+    for r in range(n):
+        ir.add_device(Device(r, DeviceType.CUDA))
+    ir.fully_connect()
+    alltoall_conditions(ir, n, blk)
+    held: Dict[Tuple[int, int, int, int], Tuple[str, int, Optional[int]]] = {}     # (o, d, c, device) -> (buffer, unit, producing op)
+    for o in range(n):
+        for c in range(blk):
+            org = o * U + o * blk + c
+            ir.copy(Chunk({o}, o, 1, o * blk + c, "input", origin=org), Chunk({o}, o, 1, o * blk + c, "output", origin=org), step=0, channel=c)
+            for d in range(n):
+                if d != o:
+                    held[(o, d, c, o)] = ("input", d * blk + c, None)
+    for s, step_sends in enumerate(sends):
+        new = {}
+        for (o, d, c, u, v) in step_sends:
+            org = o * U + d * blk + c
+            buf, unit, op = held[(o, d, c, u)]
+            slot = o * U + d * blk + c
+            push = ir.copy(Chunk({o}, u, 1, unit, buf, origin=org), Chunk({o}, v, 1, slot, "scratch", origin=org),
+                           deps=[] if op is None else [op], step=1 + 2 * s, channel=c)
+            new[(o, d, c, v)] = ("scratch", slot, push)
+            if v == d:
+                ir.copy(Chunk({o}, v, 1, slot, "scratch", origin=org), Chunk({o}, v, 1, o * blk + c, "output", origin=org),
+                        deps=[push], step=2 + 2 * s, channel=c)
+        held.update(new)
     return ir
 
 
@@ -229,10 +274,11 @@ def _recv_unit(n: int, sh: int, v: int, o: int, c: int) -> int:
 
 def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, max_steps: Optional[int] = None,
                redop: str = "sum", time_limit: float = 20.0, check: bool = True) -> SynthesisResult:
-    """Synthesise a schedule for `collective` in {"allgather", "reduce_scatter", "allreduce"} moving `nbytes` per rank
-    (all-gather: bytes each rank contributes; reduce-scatter / all-reduce: bytes of the full vector)."""
+    """Synthesise a schedule for `collective` in {"allgather", "reduce_scatter", "allreduce", "alltoall"} moving `nbytes` per
+    rank (all-gather: bytes each rank contributes; reduce-scatter / all-reduce: bytes of the full vector; all-to-all:
+    bytes of a rank's whole input, i.e. n blocks)."""
     n = topo.n
-    if collective not in ("allgather", "reduce_scatter", "allreduce"):
+    if collective not in ("allgather", "reduce_scatter", "allreduce", "alltoall"):
         raise ValueError("synthesize: unsupported collective")
     shard_bytes = nbytes if collective == "allgather" else nbytes / n
     chunk_bytes = shard_bytes / chunks
@@ -241,7 +287,7 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
     steps_try = [max_steps] if max_steps else list(range(1, n + 1))
     best = None
     for S in steps_try:
-        sends, res = _solve_allgather(topo, chunks, S, chunk_bytes, symmetric, time_limit)
+        sends, res = _solve_allgather(topo, chunks, S, chunk_bytes, symmetric, time_limit, alltoall=collective == "alltoall")
         if sends is None:
             continue
         obj = float(res.fun) * 1e-6
@@ -259,6 +305,9 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
         total = obj
     elif collective == "reduce_scatter":
         ir = _build_reduce_scatter_ir(n, chunks, sends, name, redop)
+        total = obj
+    elif collective == "alltoall":
+        ir = _build_alltoall_ir(n, chunks, sends, name)
         total = obj
     else:
         ir = _compose_allreduce(n, chunks, sends, name, redop)

@@ -51,7 +51,7 @@ def test_asymmetric_topology_is_solved_without_the_rotation_shortcut():
     assert slow <= 1
 
 
-@pytest.mark.parametrize("coll", ["allgather", "reduce_scatter", "allreduce"])
+@pytest.mark.parametrize("coll", ["allgather", "reduce_scatter", "allreduce", "alltoall"])
 @pytest.mark.parametrize("topo", [Topology.nvswitch(4), Topology.ring(4, 50.0)])
 def test_synthesised_programs_verify_and_lower(coll, topo):
     r = synthesize(coll, topo, 1 << 20, chunks=2)
@@ -83,18 +83,30 @@ def _run_synth(rank, world, port, coll, topo_kind):
     e.regOp("s", ir)
     n = 5000
     g = torch.Generator().manual_seed(0)
-    per = {"allgather": n, "reduce_scatter": n * world, "allreduce": n}[coll]
+    per = {"allgather": n, "reduce_scatter": n * world, "allreduce": n, "alltoall": n * world}[coll]
     xs = [torch.randn(per, generator=g) for _ in range(world)]
-    out_n = {"allgather": n * world, "reduce_scatter": n, "allreduce": n}[coll]
+    out_n = {"allgather": n * world, "reduce_scatter": n, "allreduce": n, "alltoall": n * world}[coll]
     y = torch.zeros(out_n)
     e.exeOp("s", xs[rank], y, width=2)
     full = torch.stack(xs)
-    ref = {"allgather": torch.cat(xs), "reduce_scatter": full.sum(0)[rank * n:(rank + 1) * n], "allreduce": full.sum(0)}[coll]
+    ref = {"allgather": torch.cat(xs), "reduce_scatter": full.sum(0)[rank * n:(rank + 1) * n], "allreduce": full.sum(0),
+           "alltoall": torch.cat([x[rank * n:(rank + 1) * n] for x in xs])}[coll]
     e.exitCluster()
     return (y - ref).abs().max().item()
 
 
-@pytest.mark.parametrize("coll", ["allgather", "reduce_scatter", "allreduce"])
+def test_alltoall_on_a_switch_is_direct_and_on_a_ring_is_relayed():
+    sw = synthesize("alltoall", Topology.nvswitch(8), 8 << 20)
+    assert sw.steps_used == 1 and len(sw.sends[0]) == 56
+    assert all(v == d for (_o, d, _c, _u, v) in sw.sends[0])                       # every block goes straight to its destination
+    assert abs(sw.objective_seconds - sw.lower_bound_seconds) < 1e-9
+    rg = synthesize("alltoall", Topology.ring(6, 50.0), 6 << 20)
+    hops = sum(len(st) for st in rg.sends)
+    assert rg.steps_used == 3 and hops == 6 * (2 * 1 + 2 * 2 + 1 * 3)             # distances 1, 1, 2, 2, 3 around a ring of six
+    assert any(v != d for st in rg.sends for (_o, d, _c, _u, v) in st)              # some transfers end on a relay
+
+
+@pytest.mark.parametrize("coll", ["allgather", "reduce_scatter", "allreduce", "alltoall"])
 @pytest.mark.parametrize("topo_kind", ["switch", "ring"])
 def test_synthesised_schedule_runs_on_cpu_ranks(coll, topo_kind):
     res = run_ranks(_run_synth, 4, args=(coll, topo_kind), env={"PCCL_WORKSPACE_MB": "32"})
