@@ -90,6 +90,45 @@ def test_survivors_run_in_the_resized_world():
     assert res[0]["sum"] == 3.0 and res[1]["sum"] == 3.0
 
 
+def _recover(rank, world, port, next_port, cache_dir):
+    """The packaged flow: departure -> time-out -> resize -> new engine with re-synthesised schedules."""
+    import torch
+    from pccl_b200.engine import Engine, PcclTimeout
+    from pccl_b200.engine.elastic import cached_schedule, recover
+    from pccl_b200.lang import DeviceType, build
+    from pccl_b200.synth import ScheduleCache, Topology
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("direct_allreduce", world, device_type=DeviceType.CPU))
+    x = torch.full((512,), float(rank + 1)); y = torch.empty_like(x)
+    e.exeOp("ar", x, y)
+    if rank == 1:                            # a middle rank leaves: the survivors are renumbered 0, 1
+        e.exitCluster()
+        return {"left": True}
+    assert e.wait_for_departure(1, 8000)
+    try:
+        e.exeOp("ar", x, y)
+        second = "completed"
+    except PcclTimeout:
+        second = "timeout"
+    cache = ScheduleCache(cache_dir)
+    e2 = recover(e, f"127.0.0.1:{next_port}", {"ar": cached_schedule("allreduce", 1 << 16, lambda n: Topology.ring(n, 50.0), cache)})
+    y2 = torch.empty_like(x)
+    e2.exeOp("ar", x, y2)
+    out = {"second": second, "new_rank": e2.rank, "new_world": e2.world, "sum": y2[0].item(), "misses": cache.misses}
+    e2.exitCluster()
+    return out
+
+
+def test_recover_builds_the_new_world_with_resynthesised_schedules(tmp_path):
+    from _ranks import free_port
+    res = run_ranks(_recover, 3, args=(free_port(), str(tmp_path)), timeout=90,
+                    env={"PCCL_WORKSPACE_MB": "8", "PCCL_WAIT_TIMEOUT_MS": "1500", "PCCL_HEARTBEAT_MS": "100", "PCCL_HEARTBEAT_MISSES": "5"})
+    assert res[0]["second"] == res[2]["second"] == "timeout"
+    assert (res[0]["new_rank"], res[2]["new_rank"]) == (0, 1) and res[0]["new_world"] == res[2]["new_world"] == 2
+    assert res[0]["sum"] == res[2]["sum"] == 1.0 + 3.0          # ranks 0 and 2 of the old world
+    assert res[0]["misses"] + res[2]["misses"] >= 1             # the schedule for two ranks did not exist before
+
+
 def _never_joins(rank, world, port):
     import torch
     from pccl_b200.engine import Engine, PcclTimeout
