@@ -376,6 +376,132 @@ def ulysses_alltoall(n: int, channels: int = 1, device_type=DeviceType.CUDA) -> 
 
 
 # ---------------------------------------------------------------------------------------------
+# more ring / recursive algorithms (latency-optimal shapes for switchless or power-of-two worlds)
+# ---------------------------------------------------------------------------------------------
+def ring_reduce_scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum") -> CollectiveIR:
+    """Ring reduce-scatter: shard c starts on rank c+1 and travels the ring, every rank folding its own contribution
+    in, until it reaches its owner c after n-1 steps."""
+    sh = channels
+    ir = _new(f"ring_reduce_scatter_n{n}_c{channels}", "reduce_scatter", n, n * sh,
+              {"input": n * sh, "output": sh, "scratch": 2 * n * sh}, device_type, redop, block_units=sh)
+    reduce_scatter_conditions(ir, n, sh)
+    for ch in range(channels):
+        # running partial of shard c on rank r: the output when r owns c, else scratch unit c*sh+ch
+        def acc(r, c, ranks):
+            if r == c:
+                return Chunk(set(ranks), r, 1, ch, "output", origin=c * sh + ch)
+            return Chunk(set(ranks), r, 1, c * sh + ch, "scratch", origin=c * sh + ch)
+        last = {}
+        for r in range(n):
+            for c in range(n):
+                last[(r, c)] = ir.copy(Chunk({r}, r, 1, c * sh + ch, "input"), acc(r, c, {r}), step=0, channel=ch)
+        for s in range(n - 1):
+            new_last = {}
+            for r in range(n):
+                c, nxt = (r - 1 - s) % n, (r + 1) % n
+                have = {(r - k) % n for k in range(s + 1)}
+                slot = Chunk(set(have), nxt, 1, (n + c) * sh + ch, "scratch", origin=c * sh + ch)
+                push = ir.copy(acc(r, c, have), slot, deps=[last[(r, c)]], step=1 + 2 * s, channel=ch)
+                new_last[(nxt, c)] = ir.reduce(slot, acc(nxt, c, have | {nxt}), deps=[push, last[(nxt, c)]], step=2 + 2 * s, channel=ch)
+            last.update(new_last)
+    return ir
+
+
+def _log2_exact(n: int) -> int:
+    k = n.bit_length() - 1
+    if n < 1 or (1 << k) != n:
+        raise ValueError(f"this algorithm needs a power-of-two world, not {n}")
+    return k
+
+
+def recursive_doubling_allgather(n: int, channels: int = 1, device_type=DeviceType.CUDA) -> CollectiveIR:
+    """log2(n) exchange steps: at step k rank r swaps everything it holds (2^k blocks) with rank r xor 2^k."""
+    steps = _log2_exact(n)
+    sh = channels
+    ir = _new(f"recursive_doubling_allgather_n{n}_c{channels}", "allgather", n, sh,
+              {"input": sh, "output": n * sh, "scratch": n * sh}, device_type, block_units=sh)
+    allgather_conditions(ir, n, sh)
+    for ch in range(channels):
+        last = {}
+        held = {r: [r] for r in range(n)}
+        for r in range(n):
+            org = r * sh + ch
+            last[(r, r)] = ir.copy(Chunk({r}, r, 1, ch, "input", origin=org), Chunk({r}, r, 1, org, "output", origin=org), step=0, channel=ch)
+        for k in range(steps):
+            new_last, new_held = {}, {r: list(held[r]) for r in range(n)}
+            for r in range(n):
+                p = r ^ (1 << k)
+                for b in held[r]:
+                    org = b * sh + ch
+                    push = ir.copy(Chunk({b}, r, 1, org, "output", origin=org), Chunk({b}, p, 1, org, "scratch", origin=org),
+                                   deps=[last[(r, b)]], step=1 + 2 * k, channel=ch)
+                    new_last[(p, b)] = ir.copy(Chunk({b}, p, 1, org, "scratch", origin=org), Chunk({b}, p, 1, org, "output", origin=org),
+                                               deps=[push], step=2 + 2 * k, channel=ch)
+                    new_held[p].append(b)
+            last.update(new_last)
+            held = new_held
+    return ir
+
+
+def halving_doubling_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum") -> CollectiveIR:
+    """Recursive halving reduce-scatter followed by recursive doubling all-gather: 2 log2(n) steps, each rank
+    moves (n-1)/n of the vector per phase -- the bandwidth of the ring at the latency of a tree."""
+    steps = _log2_exact(n)
+    U = n * channels
+    ir = _new(f"halving_doubling_allreduce_n{n}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": max(1, 2 * steps) * U}, device_type, redop)
+    allreduce_conditions(ir, n, U)
+    for ch in range(channels):
+        unit = lambda c: c * channels + ch  # noqa: E731
+        last = {}
+        for r in range(n):
+            for c in range(n):
+                last[(r, c)] = ir.copy(Chunk({r}, r, 1, unit(c), "input"), Chunk({r}, r, 1, unit(c), "output"), step=0, channel=ch)
+        lo = {r: 0 for r in range(n)}
+        hi = {r: n for r in range(n)}
+        have = {r: {r} for r in range(n)}
+        # reduce-scatter by halving: keep the half of the current range on your side of the split, send the other
+        for k in range(steps):
+            d = n >> (k + 1)
+            new_last, new_have = {}, {}
+            ranges = {}
+            for r in range(n):
+                mid = (lo[r] + hi[r]) // 2
+                ranges[r] = (lo[r], mid) if (r & d) == 0 else (mid, hi[r])
+            for r in range(n):
+                p = r ^ d
+                send_lo, send_hi = ranges[p]            # the partner keeps this part of the (common) range
+                for c in range(send_lo, send_hi):
+                    slot = Chunk(set(have[r]), p, 1, k * U + unit(c), "scratch")
+                    push = ir.copy(Chunk(set(have[r]), r, 1, unit(c), "output"), slot, deps=[last[(r, c)]], step=1 + 2 * k, channel=ch)
+                    new_last[(p, c)] = ir.reduce(slot, Chunk(have[r] | have[p], p, 1, unit(c), "output"), deps=[push, last[(p, c)]],
+                                                 step=2 + 2 * k, channel=ch)
+                new_have[r] = have[r] | have[p]
+            last.update(new_last)
+            for r in range(n):
+                lo[r], hi[r] = ranges[r]
+            have = new_have
+        # all-gather by doubling: the ranges merge back in the opposite order
+        base = 1 + 2 * steps
+        everyone = _all(n)
+        for j, k in enumerate(reversed(range(steps))):
+            d = n >> (k + 1)
+            new_last = {}
+            new_lo, new_hi = dict(lo), dict(hi)
+            for r in range(n):
+                p = r ^ d
+                for c in range(lo[r], hi[r]):
+                    slot = Chunk(set(everyone), p, 1, (steps + j) * U + unit(c), "scratch")
+                    push = ir.copy(Chunk(set(everyone), r, 1, unit(c), "output"), slot, deps=[last[(r, c)], last[(p, c)]],
+                                   step=base + 2 * j, channel=ch)
+                    new_last[(p, c)] = ir.copy(slot, Chunk(set(everyone), p, 1, unit(c), "output"), deps=[push], step=base + 1 + 2 * j, channel=ch)
+                new_lo[p], new_hi[p] = min(new_lo[p], lo[r]), max(new_hi[p], hi[r])
+            last.update(new_last)
+            lo, hi = new_lo, new_hi
+    return ir
+
+
+# ---------------------------------------------------------------------------------------------
 # NVLS (in-switch) algorithms — GPU only, symmetric input/output bound to a multicast object
 # ---------------------------------------------------------------------------------------------
 def nvls_allreduce(n: int, channels: int = 1, redop: str = "sum") -> CollectiveIR:
@@ -455,6 +581,9 @@ ALGORITHMS = {
     "nvls_allreduce": nvls_allreduce,
     "nvls_reduce_scatter": nvls_reduce_scatter,
     "nvls_allgather": nvls_allgather,
+    "ring_reduce_scatter": ring_reduce_scatter,
+    "recursive_doubling_allgather": recursive_doubling_allgather,
+    "halving_doubling_allreduce": halving_doubling_allreduce,
 }
 
 
