@@ -203,6 +203,7 @@ PYBIND11_MODULE(_C, m) {
       .def("exeOp", &Engine::exeOp, py::arg("name"), py::arg("in_ptr"), py::arg("out_ptr"), py::arg("in_bytes"),
            py::arg("dtype"), py::arg("width") = 1, py::arg("lane") = 0, py::arg("stream") = 0,
            py::call_guard<py::gil_scoped_release>())
+      .def("prepareOp", &Engine::prepareOp, py::arg("name"), py::arg("width") = 1)
       .def("exportEndpoint", &Engine::exportEndpoint)
       .def("importEndpoints", &Engine::importEndpoints, py::call_guard<py::gil_scoped_release>())
       .def("joinCluster", &Engine::joinCluster, py::arg("master_endpoint"), py::arg("timeout_ms") = 60000,

@@ -342,9 +342,14 @@ std::vector<uint32_t> Engine::checkStatus(int lane) {
 int Engine::exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes,
                   const std::string& dtype, int width, int lane, uint64_t stream) {
   if (!initialized_) throw std::runtime_error("exeOp: call initEngine first");
-  auto it = ops_.find(name);
-  if (it == ops_.end()) throw std::runtime_error("exeOp: no op named '" + name + "'");
-  Op& op = it->second;
+  Op* found = nullptr;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = ops_.find(name);
+    if (it == ops_.end()) throw std::runtime_error("exeOp: no op named '" + name + "'");
+    found = &it->second;                 // std::map nodes are stable; ops are never unregistered
+  }
+  Op& op = *found;
   if (op.program.world != world_) throw std::runtime_error("exeOp: '" + name + "' was written for another world size");
   if (lane < 0 || lane >= layout_.lanes) throw std::runtime_error("exeOp: lane out of range");
   for (int r = 0; r < world_; ++r)
@@ -359,6 +364,16 @@ int Engine::exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, ui
 
 // Signal words of a (program, width) pair are handed out at its first launch; every rank launches the same sequence
 // of (op, width) pairs, so every rank arrives at the same numbering.
+void Engine::prepareOp(const std::string& name, int width) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("prepareOp: no op named '" + name + "'");
+  if (width < 1) width = 1;
+  if (width > max_width_) width = max_width_;
+  variantFor(it->second, width);
+}
+
+// (callers hold mu_)
 Engine::Op::Variant& Engine::variantFor(Op& op, int width) {
   auto it = op.variants.find(width);
   if (it != op.variants.end()) return it->second;
@@ -376,6 +391,7 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   if (bb % dtypeSize(dt)) throw std::runtime_error("exeOp: block size is not a whole number of elements");
   if (p.needs_multicast || p.remote_io) throw std::runtime_error("exeOp: this program needs GPU symmetric memory");
   auto key = std::make_pair(bb, width);
+  std::unique_lock<std::mutex> lock(mu_);      // bookkeeping is serialised; the execution itself is not
   auto hc = op.host_cache.find(key);
   if (hc == op.host_cache.end()) hc = op.host_cache.emplace(key, p.materialize(rank_, bb, width)).first;
   const Materialized& m = hc->second;
@@ -404,15 +420,16 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   ctx.tcp_scratch_key = tcp_key_;
   ctx.tcp_scratch_off = scratch_off;
   ctx.slot_base = var.slot_base;
-  ctx.epoch = var.epoch;
+  ctx.epoch = var.epoch++;
   ctx.dtype = dt;
   ctx.redop = parseRedOp(p.redop);
   ctx.timeout_ms = timeout_ms_;
   ctx.bounds_check = bounds_check_;
   ctx.trace = trace_;
+  lock.unlock();
   CpuExecResult res = runOnCpu(m, ctx);
+  lock.lock();
   for (auto& ev : res.trace) spans_.push_back(Span{p.name, ev.stream, ev.pc, ev.op, ev.t0_ns, ev.t1_ns, ev.bytes});
-  var.epoch++;
   op.launches++;
   op.bytes += m.bytes_moved;
   op.nanos += res.nanos;
@@ -433,6 +450,7 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   if (bb % dtypeSize(dt)) throw std::runtime_error("exeOp: block size is not a whole number of elements");
   if (p.needs_multicast && !mc_base_) throw std::runtime_error("exeOp: program needs NVLS multicast, which is not set up");
   auto key = std::make_pair(bb, width);
+  std::lock_guard<std::mutex> lock(mu_);       // the launch is asynchronous, so the whole call may hold the lock
   auto dc = op.device_cache.find(key);
   if (dc == op.device_cache.end()) {
     Op::DeviceCopy c;

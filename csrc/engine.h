@@ -51,6 +51,9 @@ class Engine {
   void regOp(const std::string& name, const std::string& path_or_json);
   // Returns an ExecStatus for CPU ranks (synchronous); 0 for CUDA ranks (asynchronous on `stream`;
   // call checkStatus() to synchronise and read the device status words).
+  // Hands the signal words of (op, width) out now.  exeOp does it at the first launch by itself; threads that launch
+  // DIFFERENT ops concurrently call this first, in one order on every rank, so that all ranks number the words alike.
+  void prepareOp(const std::string& name, int width);
   int exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes,
             const std::string& dtype, int width, int lane, uint64_t stream);
   std::string exportEndpoint();
@@ -109,7 +112,7 @@ class Engine {
   void buildLayout(uint64_t heap_bytes);
   void setupPeers(const std::map<int, NodeMeta>& nodes);
   void dropPeers();
-  Op::Variant& variantFor(Op& op, int width);
+  Op::Variant& variantFor(Op& op, int width);     // caller holds mu_
   int exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane);
   int exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane, uint64_t stream);
 

@@ -91,6 +91,12 @@ class Engine:
             program = json.dumps(program)
         self._e.regOp(name, program)
 
+    def prepareOp(self, name: str, width: int = 1) -> None:
+        """Reserve the signal words of ``name`` at ``width`` now.  Only needed when several host threads launch
+        different ops at the same time (communication-communication overlap on the host executor): every rank
+        prepares them in the same order first, so that all ranks number the words alike."""
+        self._e.prepareOp(name, int(width))
+
     def exeOp(self, name: str, input: torch.Tensor, output: Optional[torch.Tensor] = None, *,
               width: int = 1, lane: int = 0, stream: Optional["torch.cuda.Stream"] = None,
               check: Optional[bool] = None) -> int:

@@ -98,6 +98,48 @@ def test_operator_object_registers_and_runs_on_cpu_ranks():
         assert res[r][0] == 0 and res[r][1] < 1e-5
 
 
+def _overlap_rank(rank, world, port):
+    """Two collectives at once, from two host threads, on two workspace lanes."""
+    import threading
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, build
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("ring_allreduce", world, channels=2, device_type=DeviceType.CPU))
+    e.regOp("ag", build("ring_allgather", world, channels=2, device_type=DeviceType.CPU))
+    e.prepareOp("ar", 2); e.prepareOp("ag", 1)           # same order on every rank
+    g = torch.Generator().manual_seed(4)
+    xs = [torch.rand(64 * 1024, generator=g) for _ in range(world)]
+    errs = []
+
+    def allreduce():
+        for it in range(6):
+            y = torch.empty_like(xs[rank])
+            e.exeOp("ar", xs[rank] + it, y, width=2, lane=0)
+            errs.append((y - (sum(xs) + it * world)).abs().max().item())
+
+    def allgather():
+        for it in range(6):
+            y = torch.empty(world * 4096)
+            e.exeOp("ag", xs[rank][:4096] * (it + 1), y, width=1, lane=1)
+            errs.append((y - torch.cat([x[:4096] * (it + 1) for x in xs])).abs().max().item())
+
+    ts = [threading.Thread(target=allreduce), threading.Thread(target=allgather)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    st = e.stats()["ops"]
+    e.exitCluster()
+    return max(errs), st["ar"]["launches"], st["ag"]["launches"]
+
+
+def test_two_ops_overlap_on_two_lanes_from_two_threads():
+    res = run_ranks(_overlap_rank, 3, env={"PCCL_WORKSPACE_MB": "16"}, timeout=120)
+    for r in range(3):
+        assert res[r][0] < 1e-5 and res[r][1] == 6 and res[r][2] == 6, res[r]
+
+
 def test_one_op_may_run_at_a_different_width_on_every_launch():
     res = run_ranks(_mixed_width_rank, 2, env={"PCCL_WORKSPACE_MB": "16"})
     assert max(res.values() if isinstance(res, dict) else res) < 1e-5
