@@ -35,6 +35,7 @@ def test_host_code_is_clean_under_asan_and_ubsan():
     cmd = [sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider",
            os.path.join(HERE, "test_native_common.py"),
            os.path.join(HERE, "test_engine_cpu.py") + "::test_one_op_may_run_at_a_different_width_on_every_launch",
+           os.path.join(HERE, "test_engine_cpu.py") + "::test_two_ops_overlap_on_two_lanes_from_two_threads",
            os.path.join(HERE, "test_engine_cpu.py") + "::test_regop_accepts_file_and_rejects_garbage",
            os.path.join(HERE, "test_engine_cpu.py") + "::test_instruction_trace_is_chrome_trace_json",
            os.path.join(HERE, "test_elastic_cpu.py") + "::test_survivors_run_in_the_resized_world",
