@@ -98,6 +98,38 @@ def test_operator_object_registers_and_runs_on_cpu_ranks():
         assert res[r][0] == 0 and res[r][1] < 1e-5
 
 
+def _two_hosts_rank(rank, world, port):
+    """Ranks 0,1 pretend to sit on one host and ranks 2,3 on another: shared memory inside a host, TCP between them."""
+    import torch
+    from pccl_b200.engine import Engine, LaunchEnvironments
+    from pccl_b200.lang import DeviceType, build
+    LaunchEnvironments.setOverride("PCCL_HOST_ID", f"host{rank // 2}")
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("ring_allreduce", world, channels=1, device_type=DeviceType.CPU))
+    e.regOp("a2a", build("alltoall", world, channels=1, device_type=DeviceType.CPU))
+    g = torch.Generator().manual_seed(6)
+    xs = [torch.rand(8 * 1024, generator=g) for _ in range(world)]
+    y = torch.empty_like(xs[rank])
+    e.exeOp("ar", xs[rank], y)
+    err = (y - sum(xs)).abs().max().item()
+    z = torch.empty_like(xs[rank])
+    e.exeOp("a2a", xs[rank], z)
+    blk = xs[rank].numel() // world
+    err = max(err, (z - torch.cat([x[rank * blk:(rank + 1) * blk] for x in xs])).abs().max().item())
+    tcp = e.stats().get("tcp_bytes_sent", 0)
+    e.exitCluster()
+    return err, tcp
+
+
+def test_shared_memory_inside_a_host_and_tcp_between_hosts_in_one_collective():
+    res = run_ranks(_two_hosts_rank, 4, env={"PCCL_WORKSPACE_MB": "16"}, timeout=120)
+    for r in range(4):
+        assert res[r][0] < 1e-5
+    # in the ring 0-1-2-3-0 only the hops 1->2 and 3->0 cross hosts: those senders use TCP, ranks 0 and 2 send the ring
+    # traffic over shared memory (their all-to-all blocks for the other host still travel by TCP)
+    assert res[1][1] > res[0][1] > 0 and res[3][1] > res[2][1] > 0
+
+
 def _overlap_rank(rank, world, port):
     """Two collectives at once, from two host threads, on two workspace lanes."""
     import threading
