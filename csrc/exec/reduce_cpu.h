@@ -1,4 +1,5 @@
 // Typed element-wise reductions on host memory (dst = dst (op) src), used by the CPU executor.
+// (No counterpart in the reference: its CPU executor header is empty, include/plugins/cpu_executor/executor.h.)
 #pragma once
 #include <cstddef>
 #include <cstdint>

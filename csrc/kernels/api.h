@@ -1,4 +1,6 @@
 // Host-callable entry points of the sm_100a kernels.  Plain C++ types only (no torch headers):
+// (The reference ships no kernel: its only device code is three inline-PTX multimem helpers,
+// include/plugins/cuda_executor/utils/multimem.h:12-127, and register-packing types, vector_datatype.h:21-80.)
 // the Python layer passes raw device pointers and the CUDA stream handle.
 //
 // Multi-rank convention.  Every communication kernel takes a `World`: the table of all ranks'

@@ -1,3 +1,4 @@
+// Element-wise / row-wise kernels of the training path (AdamW, cross-entropy, LayerNorm).  No counterpart in the reference.
 // Host entry points of the memory-bound training kernels (elementwise.cu).
 #pragma once
 #include <cuda_runtime.h>

@@ -1,4 +1,5 @@
 // Host entry points of the kernels that fuse a collective into the tcgen05 GEMM (fused_tp.cu).
+// ("communication-computation overlap" is a feature bullet of the reference, README.md:1-9, with no code behind it.)
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

@@ -1,4 +1,5 @@
 // Host entry points of the tcgen05 GEMM family (defined in gemm_*.cu).  Raw pointers, no torch.
+// (The reference has no GEMM: cutlass and composable_kernel are empty submodules, .gitmodules:4-9.)
 #pragma once
 #include <cuda_runtime.h>
 
