@@ -31,3 +31,25 @@ def test_every_kernel_source_targets_sm_100a_only():
     for src in cu:
         text = open(src).read()
         assert "wgmma" not in text and "__CUDA_ARCH__ <" not in text, src
+
+
+def test_collective_algorithm_choice_follows_the_measured_crossovers():
+    """`auto` picks the in-switch (NVLS) or the peer-to-peer kernel from measured cross-overs; no GPU is needed to check the rule."""
+    from pccl_b200.ops import collectives as C
+
+    class FakeEngine:
+        def __init__(self, world, nvls):
+            self.world, self.has_nvls = world, nvls
+
+    e8, e4, e2, plain = FakeEngine(8, True), FakeEngine(4, True), FakeEngine(2, True), FakeEngine(8, False)
+    assert C._algo(e8, "auto", "bf16", "sum", 1 << 20) == "nvls"
+    assert C._algo(plain, "auto", "bf16", "sum", 1 << 20) == "p2p"               # no multicast object: peer loads
+    assert C._algo(e8, "auto", "bf16", "sum", (1 << 20) + 8) == "p2p"            # multimem needs 16-byte vectors
+    assert C._algo(e2, "auto", "f32", "sum", 4 << 20) == "nvls" and C._algo(e2, "auto", "f32", "sum", 16 << 20) == "p2p"
+    assert C._algo(e4, "auto", "bf16", "sum", 32 << 20, "reduce_scatter") == "p2p"      # 128 MiB in total on four GPUs
+    assert C._algo(e8, "auto", "bf16", "sum", 32 << 20, "reduce_scatter") == "nvls"
+    assert C._algo(e8, "p2p", "bf16", "sum", 1 << 20) == "p2p"
+    import pytest
+    with pytest.raises(RuntimeError):
+        C._algo(plain, "nvls", "bf16", "sum", 1 << 20)
+    assert C._blocks(1 << 10, None) == 1 and C._blocks(64 << 20, None) == 128 and C._blocks(1 << 20, 7) == 7
