@@ -140,7 +140,9 @@ class Engine:
         dist.all_gather_object(docs, self.exportEndpoint(), group=group)
         self._e.importEndpoints([d for d in docs if d is not None])
         if nvls is None:
-            nvls = os.environ.get("PCCL_NVLS", "1") != "0"
+            # PCCL_NVLS=0 or PCCL_TRANSPORT=p2p keep the heap off the multicast object: every kernel then takes its
+            # peer-to-peer form
+            nvls = os.environ.get("PCCL_NVLS", "1") != "0" and os.environ.get("PCCL_TRANSPORT", "") != "p2p"
         if self.device == "cuda" and nvls and self.world > 1:
             flags = [None] * self.world
             dist.all_gather_object(flags, bool(self._e.multicastSupported()), group=group)
