@@ -130,6 +130,16 @@ def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float
                         if b == u:
                             co[ix(k, e, s)] = -chunk_bytes / topo.ingress_bw[u]
                 add(co, 0.0, np.inf)
+        for links, cap in getattr(topo, "shared_caps", []):
+            if symmetric:
+                raise ValueError("shared capacities need the general (non-rotation-symmetric) model")
+            co = {base_t + s: 1.0, base_u + s: -alpha}
+            members = set(links)
+            for k in range(nK):
+                for e, (a, b) in enumerate(E):
+                    if (a, b) in members:
+                        co[ix(k, e, s)] = -chunk_bytes / cap
+            add(co, 0.0, np.inf)
         for e, (a, b) in enumerate(E):
             co = {base_t + s: 1.0, base_u + s: -alpha}
             mult = 1.0

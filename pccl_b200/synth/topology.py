@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import hashlib
 import json
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, field
 from typing import Dict, List, Optional, Tuple
 
 
@@ -22,6 +22,9 @@ class Topology:
     alpha: float = 4.0e-6                            # seconds per step (launch + flag round trip)
     name: str = "custom"
     rotation_symmetric: bool = False                 # relabelling r -> r+1 (mod n) maps the topology onto itself
+    # Extra shared capacities: (directed links that share it, bytes/s).  A host's network card is one: every flow that
+    # leaves the host goes through it, whichever GPU sends and whichever remote GPU receives.
+    shared_caps: List[Tuple[Tuple[Tuple[int, int], ...], float]] = field(default_factory=list)
 
     @staticmethod
     def nvswitch(n: int, port_gbs: float = 770.0, alpha: float = 4.0e-6) -> "Topology":
@@ -51,8 +54,30 @@ class Topology:
                   for a in range(n) for b in range(n) if a != b)
         return Topology(n, links, list(port), list(port), alpha, "measured", sym)
 
+    @staticmethod
+    def two_level(hosts: int, per_host: int, intra_gbs: float = 770.0, nic_gbs: float = 50.0, alpha: float = 4.0e-6,
+                  inter_alpha: float = 12.0e-6) -> "Topology":
+        """``hosts`` machines of ``per_host`` GPUs: inside a machine every pair at the NVSwitch port rate, between
+        machines every pair at the network card's rate, and one card per machine and direction shared by all of its
+        GPUs' remote flows.  Rank r sits on host r // per_host."""
+        n = hosts * per_host
+        intra, nic = intra_gbs * 1e9, nic_gbs * 1e9
+        host = lambda r: r // per_host  # noqa: E731
+        links = {(a, b): (intra if host(a) == host(b) else nic) for a in range(n) for b in range(n) if a != b}
+        caps = []
+        for h in range(hosts):
+            out = tuple((a, b) for (a, b) in sorted(links) if host(a) == h and host(b) != h)
+            inn = tuple((a, b) for (a, b) in sorted(links) if host(b) == h and host(a) != h)
+            if out:
+                caps.append((out, nic))
+                caps.append((inn, nic))
+        t = Topology(n, links, [intra] * n, [intra] * n, max(alpha, inter_alpha) if hosts > 1 else alpha,
+                     f"hosts{hosts}x{per_host}", False, caps)
+        return t
+
     def fingerprint(self) -> str:
         doc = {"n": self.n, "links": sorted((a, b, round(v / 1e9)) for (a, b), v in self.link_bw.items()),
+               "shared": sorted((sorted(ls), round(c / 1e9)) for ls, c in self.shared_caps),
                "egress": [round(v / 1e9) for v in self.egress_bw], "ingress": [round(v / 1e9) for v in self.ingress_bw],
                "alpha_us": round(self.alpha * 1e6, 1)}
         return hashlib.sha1(json.dumps(doc, sort_keys=True).encode()).hexdigest()[:16]

@@ -62,6 +62,53 @@ def test_synthesised_programs_verify_and_lower(coll, topo):
     assert r.ir.attrs["synthesized"] and r.ir.attrs["topology"] == topo.fingerprint()
 
 
+def test_two_hosts_sharing_a_network_card_send_every_block_across_once():
+    topo = Topology.two_level(2, 2, intra_gbs=770.0, nic_gbs=50.0)
+    assert len(topo.shared_caps) == 4 and not topo.rotation_symmetric
+    host = lambda r: r // 2  # noqa: E731
+    ag = synthesize("allgather", topo, 64 << 20)
+    cross = [(o, u, v) for st in ag.sends for (o, _c, u, v) in st if host(u) != host(v)]
+    assert len(cross) == 4 and sorted(o for o, _u, _v in cross) == [0, 1, 2, 3]      # a direct exchange would cross 8 times
+    assert ag.steps_used == 2
+    # without the shared card every pair has its own 50 GB/s and the one-step direct exchange wins
+    loose = Topology.two_level(2, 2)
+    loose.shared_caps = []
+    assert synthesize("allgather", loose, 64 << 20).steps_used == 1
+    a2a = synthesize("alltoall", topo, 64 << 20)
+    assert sum(1 for st in a2a.sends for tr in st if host(tr[3]) != host(tr[4])) == 8       # nothing to save: every block is unique
+    assert verify(synthesize("allreduce", topo, 64 << 20).ir).ok
+
+
+def _two_host_synth(rank, world, port, how):
+    """Two pretended hosts of two ranks: shared memory inside, TCP between.  Returns the error and the TCP bytes sent."""
+    import torch
+    from pccl_b200.engine import Engine, LaunchEnvironments
+    from pccl_b200.lang import DeviceType, build
+    from pccl_b200.synth import Topology, synthesize
+    LaunchEnvironments.setOverride("PCCL_HOST_ID", f"host{rank // 2}")
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    ir = synthesize("allgather", Topology.two_level(2, 2), 64 << 20).ir if how == "milp" else build("direct_allgather", world, device_type=DeviceType.CPU)
+    e.regOp("ag", ir)
+    n = 16 * 1024
+    g = torch.Generator().manual_seed(2)
+    xs = [torch.rand(n, generator=g) for _ in range(world)]
+    y = torch.empty(n * world)
+    e.exeOp("ag", xs[rank], y)
+    tcp = e.stats().get("tcp_bytes_sent", 0)
+    e.exitCluster()
+    return (y - torch.cat(xs)).abs().max().item(), tcp
+
+
+def test_schedule_for_two_hosts_halves_the_network_traffic_of_the_direct_exchange():
+    got = {}
+    for how in ("milp", "direct"):
+        res = run_ranks(_two_host_synth, 4, args=(how,), env={"PCCL_WORKSPACE_MB": "16"}, timeout=120)
+        assert all(res[r][0] == 0.0 for r in range(4)), res
+        got[how] = sum(res[r][1] for r in range(4))
+    payload = 16 * 1024 * 4
+    assert got["direct"] >= 8 * payload and 4 * payload <= got["milp"] < 0.6 * got["direct"], got
+
+
 def test_schedule_cache_roundtrip(tmp_path):
     cache = ScheduleCache(str(tmp_path))
     topo = Topology.nvswitch(4)
