@@ -501,6 +501,93 @@ def halving_doubling_allreduce(n: int, channels: int = 1, device_type=DeviceType
     return ir
 
 
+def hierarchical_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum",
+                           per_host: int = 2) -> CollectiveIR:
+    """All-reduce for ``n / per_host`` hosts of ``per_host`` ranks (rank r on host r // per_host): reduce-scatter inside
+    each host, all-reduce of every part among the ranks with the same local index (one per host), all-gather inside
+    each host.  Only the middle phase crosses hosts, and it moves 2 (hosts-1)/n of the vector per rank."""
+    L = per_host
+    if L < 1 or n % L:
+        raise ValueError(f"hierarchical_allreduce: {n} ranks do not split into hosts of {L}")
+    H = n // L
+    U = n * channels
+    ir = _new(f"hierarchical_allreduce_n{n}_h{H}x{L}_c{channels}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": (L + H + 1) * U}, device_type, redop)
+    allreduce_conditions(ir, n, U)
+    rank_of = lambda g, l: g * L + l  # noqa: E731
+    for ch in range(channels):
+        unit = lambda c: c * channels + ch  # noqa: E731      chunk c = l * H + h: part l, sub-chunk h
+        last, have = {}, {}
+        for r in range(n):
+            for c in range(n):
+                last[(r, c)] = ir.copy(Chunk({r}, r, 1, unit(c), "input"), Chunk({r}, r, 1, unit(c), "output"), step=0, channel=ch)
+                have[(r, c)] = {r}
+        # A: inside a host, local rank l collects part l
+        new_last, new_have = {}, {}
+        for g in range(H):
+            for l in range(L):
+                owner = rank_of(g, l)
+                for lp in range(L):
+                    if lp == l:
+                        continue
+                    src = rank_of(g, lp)
+                    for h in range(H):
+                        c = l * H + h
+                        slot = Chunk({src}, owner, 1, (lp * n + c) * channels + ch, "scratch")
+                        push = ir.copy(Chunk({src}, src, 1, unit(c), "output"), slot, deps=[last[(src, c)]], step=1, channel=ch)
+                        got = new_have.get((owner, c), {owner}) | {src}
+                        new_last[(owner, c)] = ir.reduce(slot, Chunk(set(got), owner, 1, unit(c), "output"),
+                                                         deps=[push, new_last.get((owner, c), last[(owner, c)])], step=2, channel=ch)
+                        new_have[(owner, c)] = got
+        last.update(new_last)
+        have.update(new_have)
+        # B1: among the hosts, rank (g, l) collects sub-chunk g of part l
+        new_last, new_have = {}, {}
+        for l in range(L):
+            for g in range(H):
+                owner, c = rank_of(g, l), l * H + g
+                for gp in range(H):
+                    if gp == g:
+                        continue
+                    src = rank_of(gp, l)
+                    slot = Chunk(set(have[(src, c)]), owner, 1, ((L + gp) * n + c) * channels + ch, "scratch")
+                    push = ir.copy(Chunk(set(have[(src, c)]), src, 1, unit(c), "output"), slot, deps=[last[(src, c)]], step=3, channel=ch)
+                    got = new_have.get((owner, c), have[(owner, c)]) | have[(src, c)]
+                    new_last[(owner, c)] = ir.reduce(slot, Chunk(set(got), owner, 1, unit(c), "output"),
+                                                     deps=[push, new_last.get((owner, c), last[(owner, c)])], step=4, channel=ch)
+                    new_have[(owner, c)] = got
+        last.update(new_last)
+        have.update(new_have)
+        everyone = _all(n)
+        gather_slot = lambda c: ((L + H) * n + c) * channels + ch  # noqa: E731
+
+        def hand_over(src, dst, c, step):
+            slot = Chunk(set(everyone), dst, 1, gather_slot(c), "scratch")
+            push = ir.copy(Chunk(set(everyone), src, 1, unit(c), "output"), slot, deps=[last[(src, c)], last[(dst, c)]], step=step, channel=ch)
+            return ir.copy(slot, Chunk(set(everyone), dst, 1, unit(c), "output"), deps=[push], step=step + 1, channel=ch)
+        # B2: the finished sub-chunks go back to the other hosts
+        new_last = {}
+        for l in range(L):
+            for g in range(H):
+                c = l * H + g
+                for gp in range(H):
+                    if gp != g:
+                        new_last[(rank_of(gp, l), c)] = hand_over(rank_of(g, l), rank_of(gp, l), c, 5)
+        last.update(new_last)
+        # C: inside a host, every rank hands its finished part to its neighbours
+        new_last = {}
+        for g in range(H):
+            for l in range(L):
+                for lp in range(L):
+                    if lp == l:
+                        continue
+                    for h in range(H):
+                        c = l * H + h
+                        new_last[(rank_of(g, lp), c)] = hand_over(rank_of(g, l), rank_of(g, lp), c, 7)
+        last.update(new_last)
+    return ir
+
+
 # ---------------------------------------------------------------------------------------------
 # NVLS (in-switch) algorithms — GPU only, symmetric input/output bound to a multicast object
 # ---------------------------------------------------------------------------------------------
@@ -584,6 +671,7 @@ ALGORITHMS = {
     "ring_reduce_scatter": ring_reduce_scatter,
     "recursive_doubling_allgather": recursive_doubling_allgather,
     "halving_doubling_allreduce": halving_doubling_allreduce,
+    "hierarchical_allreduce": hierarchical_allreduce,
 }
 
 

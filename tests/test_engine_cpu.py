@@ -130,6 +130,36 @@ def test_shared_memory_inside_a_host_and_tcp_between_hosts_in_one_collective():
     assert res[1][1] > res[0][1] > 0 and res[3][1] > res[2][1] > 0
 
 
+def _hier_rank(rank, world, port, algo):
+    import torch
+    from pccl_b200.engine import Engine, LaunchEnvironments
+    from pccl_b200.lang import DeviceType, build
+    LaunchEnvironments.setOverride("PCCL_HOST_ID", f"host{rank // 2}")
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    kw = {"per_host": 2} if algo == "hierarchical_allreduce" else {}
+    e.regOp("ar", build(algo, world, channels=1, device_type=DeviceType.CPU, **kw))
+    g = torch.Generator().manual_seed(8)
+    xs = [torch.rand(32 * 1024, generator=g) for _ in range(world)]
+    y = torch.empty_like(xs[rank])
+    e.exeOp("ar", xs[rank], y)
+    tcp = e.stats().get("tcp_bytes_sent", 0)
+    e.exitCluster()
+    return (y - sum(xs)).abs().max().item(), tcp
+
+
+def test_hierarchical_allreduce_sends_less_over_the_network_than_the_direct_one():
+    """Four ranks on two pretended hosts: only the middle phase of the hierarchical algorithm uses TCP."""
+    sent = {}
+    for algo in ("hierarchical_allreduce", "direct_allreduce"):
+        res = run_ranks(_hier_rank, 4, args=(algo,), env={"PCCL_WORKSPACE_MB": "16"}, timeout=120)
+        assert all(res[r][0] < 1e-5 for r in range(4)), (algo, res)
+        sent[algo] = sum(res[r][1] for r in range(4))
+    vector = 32 * 1024 * 4
+    # hierarchical: each rank sends 2 * (hosts - 1) / n of the vector across = 1/2 vector per rank; direct: 2 * 2/4 = 1 vector per rank
+    assert sent["hierarchical_allreduce"] <= 0.6 * sent["direct_allreduce"], sent
+    assert sent["hierarchical_allreduce"] >= 4 * vector // 2
+
+
 def _overlap_rank(rank, world, port):
     """Two collectives at once, from two host threads, on two workspace lanes."""
     import threading
@@ -191,7 +221,7 @@ def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
     ("ring_allreduce", {}), ("direct_allreduce", {}), ("oneshot_allreduce", {}), ("tree_allreduce", {}),
     ("direct_reduce_scatter", {}), ("direct_allgather", {}), ("ring_allgather", {}), ("ring_kv_rotation", {}),
     ("alltoall", {}), ("ulysses_alltoall", {}), ("ring_reduce_scatter", {}), ("recursive_doubling_allgather", {}),
-    ("halving_doubling_allreduce", {})])
+    ("halving_doubling_allreduce", {}), ("hierarchical_allreduce", {"per_host": 2})])
 def test_algorithms_on_cpu_ranks_shm(algo, kwargs):
     res = run_ranks(_collective_rank, 4, args=(algo, "shm", "float32", 1000 + 17, 2, 2, kwargs),
                     env={"PCCL_WORKSPACE_MB": "16"})
