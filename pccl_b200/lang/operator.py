@@ -35,6 +35,19 @@ class Operator:
         res = synthesize(collective, topology, nbytes, **kw)
         return cls(name or res.ir.name, res.ir, check=False)     # the synthesiser verified it
 
+    @classmethod
+    def best(cls, collective: str, topology, nbytes: int, name: Optional[str] = None, **kw) -> "Operator":
+        """The cheapest program for ``collective`` on ``topology`` at this size under the cost model
+        (``pccl_b200.synth.choose``; ``include_milp=True`` also prices a synthesised schedule)."""
+        from ..synth import choose
+        ranked = choose(collective, topology, nbytes, **kw)
+        if not ranked:
+            raise ValueError(f"no library algorithm for {collective} fits this topology (try include_milp=True)")
+        chosen, est, ir = ranked[0]
+        op = cls(name or chosen, ir, check=False)
+        op.estimate = est
+        return op
+
     @property
     def collective(self) -> str:
         return self.ir.collective

@@ -168,3 +168,14 @@ def test_default_channel_count_comes_from_the_environment(monkeypatch):
     monkeypatch.setenv("PCCL_CHANNELS", "3")
     assert streams(to_schedule(build("ring_allreduce", 4))) == 3 * one
     assert streams(to_schedule(build("ring_allreduce", 4, channels=1))) == one      # an explicit argument wins
+
+
+def test_operator_best_picks_by_the_cost_model():
+    from pccl_b200.lang import Operator
+    from pccl_b200.synth import Topology
+    assert Operator.best("allreduce", Topology.nvswitch(8), 1 << 10).name == "oneshot_allreduce"
+    assert Operator.best("allreduce", Topology.nvswitch(8), 64 << 20).name == "direct_allreduce"
+    with pytest.raises(ValueError):
+        Operator.best("alltoall", Topology.ring(4), 1 << 20)
+    op = Operator.best("alltoall", Topology.ring(4), 1 << 20, include_milp=True)
+    assert op.name.startswith("milp_alltoall") and op.estimate.steps >= 2 and op.schedule()["collective"] == "alltoall"
