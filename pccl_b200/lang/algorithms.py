@@ -501,6 +501,50 @@ def halving_doubling_allreduce(n: int, channels: int = 1, device_type=DeviceType
     return ir
 
 
+def hierarchical_allgather(n: int, channels: int = 1, device_type=DeviceType.CUDA, per_host: int = 2) -> CollectiveIR:
+    """All-gather for hosts of ``per_host`` ranks: every rank first swaps its shard with the ranks of the same local
+    index on the other hosts (the only traffic between hosts: each shard crosses once per remote host), then the
+    ranks of a host hand one another everything they hold."""
+    L = per_host
+    if L < 1 or n % L:
+        raise ValueError(f"hierarchical_allgather: {n} ranks do not split into hosts of {L}")
+    H = n // L
+    sh = channels
+    ir = _new(f"hierarchical_allgather_n{n}_h{H}x{L}_c{channels}", "allgather", n, sh,
+              {"input": sh, "output": n * sh, "scratch": n * sh}, device_type, block_units=sh)
+    allgather_conditions(ir, n, sh)
+    rank_of = lambda g, l: g * L + l  # noqa: E731
+    for ch in range(channels):
+        last = {}
+        for r in range(n):
+            org = r * sh + ch
+            last[(r, r)] = ir.copy(Chunk({r}, r, 1, ch, "input", origin=org), Chunk({r}, r, 1, org, "output", origin=org), step=0, channel=ch)
+
+        def hand_over(src, dst, b, step):
+            org = b * sh + ch
+            push = ir.copy(Chunk({b}, src, 1, org, "output", origin=org), Chunk({b}, dst, 1, org, "scratch", origin=org),
+                           deps=[last[(src, b)]], step=step, channel=ch)
+            return ir.copy(Chunk({b}, dst, 1, org, "scratch", origin=org), Chunk({b}, dst, 1, org, "output", origin=org),
+                           deps=[push], step=step + 1, channel=ch)
+        new_last = {}
+        for l in range(L):                       # between hosts, same local index
+            for g in range(H):
+                for gp in range(H):
+                    if gp != g:
+                        new_last[(rank_of(gp, l), rank_of(g, l))] = hand_over(rank_of(g, l), rank_of(gp, l), rank_of(g, l), 1)
+        last.update(new_last)
+        new_last = {}
+        for g in range(H):                       # inside a host: rank (g, l) holds the shards of local index l from every host
+            for l in range(L):
+                for lp in range(L):
+                    if lp == l:
+                        continue
+                    for gg in range(H):
+                        new_last[(rank_of(g, lp), rank_of(gg, l))] = hand_over(rank_of(g, l), rank_of(g, lp), rank_of(gg, l), 3)
+        last.update(new_last)
+    return ir
+
+
 def hierarchical_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum",
                            per_host: int = 2) -> CollectiveIR:
     """All-reduce for ``n / per_host`` hosts of ``per_host`` ranks (rank r on host r // per_host): reduce-scatter inside
@@ -672,6 +716,7 @@ ALGORITHMS = {
     "recursive_doubling_allgather": recursive_doubling_allgather,
     "halving_doubling_allreduce": halving_doubling_allreduce,
     "hierarchical_allreduce": hierarchical_allreduce,
+    "hierarchical_allgather": hierarchical_allgather,
 }
 
 

@@ -221,7 +221,8 @@ def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
     ("ring_allreduce", {}), ("direct_allreduce", {}), ("oneshot_allreduce", {}), ("tree_allreduce", {}),
     ("direct_reduce_scatter", {}), ("direct_allgather", {}), ("ring_allgather", {}), ("ring_kv_rotation", {}),
     ("alltoall", {}), ("ulysses_alltoall", {}), ("ring_reduce_scatter", {}), ("recursive_doubling_allgather", {}),
-    ("halving_doubling_allreduce", {}), ("hierarchical_allreduce", {"per_host": 2})])
+    ("halving_doubling_allreduce", {}), ("hierarchical_allreduce", {"per_host": 2}),
+    ("hierarchical_allgather", {"per_host": 2})])
 def test_algorithms_on_cpu_ranks_shm(algo, kwargs):
     res = run_ranks(_collective_rank, 4, args=(algo, "shm", "float32", 1000 + 17, 2, 2, kwargs),
                     env={"PCCL_WORKSPACE_MB": "16"})

@@ -57,7 +57,7 @@ def test_ir_builder_and_reference_api():
 @pytest.mark.parametrize("n", [2, 3, 4, 8])
 def test_every_algorithm_verifies_and_lowers(name, n):
     if (name in ("recursive_doubling_allgather", "halving_doubling_allreduce") and n & (n - 1)) or \
-            (name == "hierarchical_allreduce" and n % 2):
+            (name in ("hierarchical_allreduce", "hierarchical_allgather") and n % 2):
         with pytest.raises(ValueError):
             build(name, n)
         return
