@@ -33,7 +33,8 @@ def reference_arm() -> None:
     probe = os.path.join(ROOT, "baseline", "_ref")
     if os.path.isdir(probe) and os.listdir(probe):
         why += " (a partial install exists under baseline/_ref but exposes no runnable path)"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also under torch.distributed.run
+        print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
 def main() -> None:
