@@ -53,3 +53,26 @@ def test_collective_algorithm_choice_follows_the_measured_crossovers():
     with pytest.raises(RuntimeError):
         C._algo(plain, "nvls", "bf16", "sum", 1 << 20)
     assert C._blocks(1 << 10, None) == 1 and C._blocks(64 << 20, None) == 128 and C._blocks(1 << 20, 7) == 7
+
+
+def test_clock_sampler_reads_a_stand_in_for_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler only READS clocks and throttle reasons; here it reads a script that prints what the tool would."""
+    import stat
+    import time
+    fake = tmp_path / "nvidia-smi"
+    lines = ["#!/bin/sh", "for i in 1 2 3 4 5 6; do",
+             "  echo '1410, 1965, 950.12, Not Active, Not Active, Not Active, Active'",
+             "  echo '1395, 1965, 990.00, Not Active, Not Active, Not Active, Not Active'",
+             "  sleep 0.05", "done", "sleep 5", ""]
+    fake.write_text(chr(10).join(lines))
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    from pccl_b200.utils import ClockSampler
+    s = ClockSampler(0, period_ms=50).start()
+    time.sleep(0.6)
+    out = s.stop()
+    assert out["samples"] >= 4 and out["sm_max_mhz"] == 1965.0 and 1395.0 <= out["sm_mhz"] <= 1410.0
+    assert out["reasons"] == ["sw_power_cap"]
+    # without the tool the sampler stays silent instead of failing the benchmark
+    monkeypatch.setenv("PATH", str(tmp_path / "nowhere"))
+    assert ClockSampler(0).start().stop()["sm_mhz"] is None
