@@ -201,7 +201,12 @@ def test_cost_model_ranks_algorithms_the_way_the_topology_demands():
     names = [n for n, _e, _ir in ranked]
     assert names[0] == "hierarchical_allreduce" and "direct_allreduce" in names and "shared capacity" in ranked[-1][1].busiest
     ag = choose("allgather", hosts, 64 << 20, include_milp=True)
-    assert ag[0][0].startswith("milp_allgather") and ag[0][1].seconds < 0.75 * ag[1][1].seconds
+    by_name = {n: e for n, e, _ir in ag}
+    # the synthesiser finds the two-level form by itself: the hand-written hierarchical gather costs the same
+    # to a few per cent, and every flat form pays for crossing the hosts' shared link more than once
+    assert ag[0][0].startswith("milp_allgather") and ag[1][0] == "hierarchical_allgather"
+    assert ag[1][1].seconds < 1.05 * ag[0][1].seconds
+    assert ag[0][1].seconds < 0.75 * min(by_name["ring_allgather"].seconds, by_name["direct_allgather"].seconds)
     # the model prices the transfer step of the synthesiser's schedule at the synthesiser's objective; the local
     # staging copies around it (which the MILP does not model) come on top
     r = synthesize("allgather", sw, 16 << 20)
