@@ -75,22 +75,26 @@ _lock = threading.Lock()
 
 
 SANITIZED_TARGET = ROOT / "build" / "sanitize" / "_C.so"
+THREAD_SANITIZED_TARGET = ROOT / "build" / "sanitize-thread" / "_C.so"
+_SANITIZERS = {"address": ("address,undefined", SANITIZED_TARGET), "thread": ("thread", THREAD_SANITIZED_TARGET)}
 
 
-def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False, sanitize: bool = False) -> Path:
+def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False, sanitize=False) -> Path:
     """Compile whatever changed and link ``_C.so``.  Safe to call repeatedly.
 
-    ``sanitize=True`` builds a second copy, ``build/sanitize/_C.so``, whose HOST objects are compiled with
-    ``-fsanitize=address,undefined`` (the device objects are shared with the normal build).  Load it with
-    ``PCCL_NATIVE_LIB=<that path>`` and ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``; it is what the CPU test
-    suite uses to run the engine, daemon, transport and executor under the sanitizers."""
+    ``sanitize=True`` (or ``"address"``) builds a second copy, ``build/sanitize/_C.so``, whose HOST objects are
+    compiled with ``-fsanitize=address,undefined``; ``sanitize="thread"`` builds ``build/sanitize-thread/_C.so`` with
+    ``-fsanitize=thread``.  The device objects are shared with the normal build.  Load such a copy with
+    ``PCCL_NATIVE_LIB=<that path>`` and ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)`` (``libtsan.so`` for the
+    thread build); it is what the CPU test suite uses to run the engine, daemon, transport and executor under the
+    sanitizers."""
     with _lock:
         OBJ.mkdir(parents=True, exist_ok=True)
         cxx, nv = _flags()
         target = TARGET
         if sanitize:
-            cxx = [c for c in cxx if c != "-O2"] + ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined"]
-            target = SANITIZED_TARGET
+            fsan, target = _SANITIZERS["address" if sanitize is True else sanitize]
+            cxx = [c for c in cxx if c != "-O2"] + ["-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={fsan}"]
             target.parent.mkdir(parents=True, exist_ok=True)
         cc, cu = sources()
         hdr = _newest_header()
@@ -111,7 +115,7 @@ def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False, s
             link = ["g++", "-shared", "-o", str(target)] + objs + [
                 f"-L{CUDA_HOME}/lib64", "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
             if sanitize:
-                link += ["-fsanitize=address,undefined"]
+                link += [f"-fsanitize={fsan}"]
             if verbose:
                 print("[pccl build] link", target, flush=True)
             r = subprocess.run(link, capture_output=True, text=True)
@@ -121,4 +125,4 @@ def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False, s
 
 
 if __name__ == "__main__":
-    print(build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas-info" in sys.argv, sanitize="--sanitize" in sys.argv))
+    print(build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas-info" in sys.argv, sanitize="thread" if "--sanitize-thread" in sys.argv else "--sanitize" in sys.argv))
