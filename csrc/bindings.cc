@@ -211,6 +211,7 @@ PYBIND11_MODULE(_C, m) {
       .def("exitCluster", &Engine::exitCluster, py::call_guard<py::gil_scoped_release>())
       .def("stats", &Engine::stats)
       .def("trace", &Engine::trace)
+      .def("ingestDeviceTrace", &Engine::ingestDeviceTrace, py::arg("name"), py::arg("in_bytes"), py::arg("width"), py::arg("stamps"))
       .def("deviceKind", &Engine::deviceKind)
       .def("heapBase", &Engine::heapBase)
       .def("heapBytes", &Engine::heapBytes)

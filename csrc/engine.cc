@@ -52,6 +52,8 @@ Engine::~Engine() {
       if (dc.second.instrs) cudaFree(dc.second.instrs);
       if (dc.second.starts) cudaFree(dc.second.starts);
     }
+  for (auto& t : dtrace_)
+    if (t.words) cudaFree(t.words);
   dropPeers();
   if (tcp_) tcp_->shutdown();
   if (heap_) {
@@ -450,7 +452,7 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   if (bb % dtypeSize(dt)) throw std::runtime_error("exeOp: block size is not a whole number of elements");
   if (p.needs_multicast && !mc_base_) throw std::runtime_error("exeOp: program needs NVLS multicast, which is not set up");
   auto key = std::make_pair(bb, width);
-  std::lock_guard<std::mutex> lock(mu_);       // the launch is asynchronous, so the whole call may hold the lock
+  std::unique_lock<std::mutex> lock(mu_);      // the launch is asynchronous, so the whole call may hold the lock
   auto dc = op.device_cache.find(key);
   if (dc == op.device_cache.end()) {
     Op::DeviceCopy c;
@@ -500,15 +502,68 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   R.scratch_off = lane * lane_bytes + (lane_launches_.at(lane)++ & 1) * half;
   for (int b = 0; b < BUF_COUNT; ++b) R.buf_bytes[b] = c.m.buf_bytes[b];
   R.status = reinterpret_cast<uint32_t*>(statusPtr(lane));
+  size_t n_instr = 0;
+  if (trace_) {
+    for (auto& s : c.m.streams) n_instr += s.size();
+    if (dtrace_.size() <= static_cast<size_t>(lane)) dtrace_.resize(lane + 1);
+    DeviceTrace& t = dtrace_[lane];
+    if (t.cap < 2 * n_instr) {
+      if (t.words) cudaFree(t.words);
+      t.words = nullptr;
+      t.cap = 0;
+      cudaCheck(cudaMalloc(&t.words, 2 * n_instr * sizeof(uint64_t)), "cudaMalloc(trace)");
+      t.cap = 2 * n_instr;
+    }
+    cudaCheck(cudaMemsetAsync(t.words, 0, 2 * n_instr * sizeof(uint64_t), reinterpret_cast<cudaStream_t>(stream)), "clearing the trace");
+    R.trace = t.words;
+  }
   int err = launchInterpreter(L, 512, reinterpret_cast<cudaStream_t>(stream));
   if (err != 0) throw std::runtime_error(std::string("exeOp: kernel launch failed: ") + cudaErrorName(err));
   var.epoch++;
   op.launches++;
   op.bytes += c.m.bytes_moved;
+  if (trace_) {
+    // Read the stamps back without the lock: the kernel may be waiting for a peer whose matching launch
+    // on another lane of this engine needs the lock first.
+    uint64_t* words = R.trace;
+    lock.unlock();
+    cudaCheck(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)), "traced launch");
+    std::vector<uint64_t> stamps(2 * n_instr);
+    cudaCheck(cudaMemcpy(stamps.data(), words, stamps.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost), "reading the trace");
+    lock.lock();
+    addDeviceSpans(p.name, c.m, stamps);
+  }
   return 0;
 }
 
+void Engine::addDeviceSpans(const std::string& name, const Materialized& m, const std::vector<uint64_t>& stamps) {
+  size_t flat = 0;
+  for (size_t s = 0; s < m.streams.size(); ++s)
+    for (size_t pc = 0; pc < m.streams[s].size(); ++pc, ++flat) {
+      const Instr& in = m.streams[s][pc];
+      if (2 * flat + 1 >= stamps.size()) return;
+      uint64_t t0 = stamps[2 * flat], t1 = stamps[2 * flat + 1];
+      if (in.op == OP_END || t0 == 0 || t1 < t0) continue;      // never reached (a failed stream stops early)
+      bool moves = in.op == OP_COPY || in.op == OP_REDUCE || in.op == OP_MM_LD_REDUCE || in.op == OP_MM_ST;
+      spans_.push_back(Span{name, static_cast<uint32_t>(s), static_cast<uint32_t>(pc), in.op, t0, t1, moves ? in.bytes : 0});
+    }
+}
+
+void Engine::ingestDeviceTrace(const std::string& name, uint64_t in_bytes, int width, const std::vector<uint64_t>& stamps) {
+  std::lock_guard<std::mutex> lock(mu_);
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("ingestDeviceTrace: no operator named '" + name + "'");
+  const Program& p = it->second.program;
+  Materialized m = p.materialize(rank_, p.blockBytesForInput(in_bytes), width);
+  size_t n = 0;
+  for (auto& s : m.streams) n += s.size();
+  if (stamps.size() != 2 * n)
+    throw std::runtime_error("ingestDeviceTrace: " + std::to_string(stamps.size()) + " stamps for " + std::to_string(n) + " instructions");
+  addDeviceSpans(name, m, stamps);
+}
+
 std::string Engine::trace() {
+  std::lock_guard<std::mutex> lock(mu_);
   static const char* names[] = {"NOP", "COPY", "REDUCE", "NOTIFY", "WAIT", "MM_LD_REDUCE", "MM_ST", "BARRIER", "END"};
   Json events = Json::array();
   for (auto& s : spans_) {

@@ -61,9 +61,14 @@ class Engine {
   void joinCluster(const std::string& master_endpoint, int timeout_ms = 60000);
   void exitCluster();
   std::string stats();
-  // Chrome-trace ("traceEvents") JSON of the CPU executor's instructions recorded while PCCL_TRACE=1;
+  // Chrome-trace ("traceEvents") JSON of the instructions recorded while PCCL_TRACE=1: the CPU executor's
+  // with host timestamps, the interpreter kernel's with the device's %globaltimer (a traced GPU launch is
+  // followed by a synchronize of its stream, so tracing is for inspection, not for timed runs or graph capture);
   // clears the record.
   std::string trace();
+  // Adds the spans of one interpreter launch from its raw stamp buffer (two %globaltimer words per instruction
+  // of this rank's streams at `width`, streams back to back): for buffers captured outside exeOp.
+  void ingestDeviceTrace(const std::string& name, uint64_t in_bytes, int width, const std::vector<uint64_t>& stamps);
 
   // symmetric heap
   const std::string& deviceKind() const { return device_; }
@@ -115,6 +120,8 @@ class Engine {
   Op::Variant& variantFor(Op& op, int width);     // caller holds mu_
   int exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane);
   int exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane, uint64_t stream);
+  // Turns the interpreter kernel's stamps (two words per instruction, streams back to back) into spans; caller holds mu_.
+  void addDeviceSpans(const std::string& name, const Materialized& m, const std::vector<uint64_t>& stamps);
 
   int rank_, world_;
   bool initialized_ = false;
@@ -141,6 +148,9 @@ class Engine {
   bool trace_ = false;
   struct Span { std::string op; uint32_t stream, pc, opcode; uint64_t t0, t1, bytes; };
   std::vector<Span> spans_;
+  // Device trace buffers, one per workspace lane (two %globaltimer words per instruction), grown on demand.
+  struct DeviceTrace { uint64_t* words = nullptr; size_t cap = 0; };
+  std::vector<DeviceTrace> dtrace_;
   int max_width_ = 32;
 };
 

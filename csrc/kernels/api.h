@@ -47,6 +47,8 @@ struct InterpRank {
   uint64_t scratch_off;           // offset of this launch's scratch lane inside the heap
   uint64_t buf_bytes[BUF_COUNT];
   uint32_t* status;               // [0]=status code, [1]=stream, [2]=pc, [3]=detail
+  uint64_t* trace;                // nullptr, or two words per instruction of this rank (indexed like `instrs`):
+                                  // %globaltimer when the CTA began it and when all its threads had finished it
 };
 
 struct InterpLaunch {

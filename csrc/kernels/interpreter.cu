@@ -10,6 +10,8 @@
 //   MM_LD_REDUCE / MM_ST in-switch reduction / multicast store through the NVLS mapping
 // A wait that runs out of polls writes ST_TIMEOUT with the stream and pc into the status words and
 // the CTA leaves; sibling CTAs notice the status word and leave too.  Nothing traps or spins forever.
+// With a trace buffer attached, thread 0 stamps %globaltimer around every instruction (the end stamp
+// after a CTA barrier, so it covers the slowest thread); the host turns the stamps into trace events.
 #include <cooperative_groups.h>
 
 #include "api.h"
@@ -126,6 +128,7 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
   const int me = R.rank;
   uint64_t* my_sig = reinterpret_cast<uint64_t*>(W.heap[me] + W.signal_off) + L.slot_base;
   const Instr* prog = R.instrs + R.stream_start[stream];
+  uint64_t* const trace = R.trace ? R.trace + 2ull * R.stream_start[stream] : nullptr;
 
   // Address of (rank q, buffer b, offset) or nullptr when q's buffer b is not reachable.
   auto resolve = [&](int q, uint32_t b, uint64_t off) -> char* {
@@ -145,6 +148,7 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
     const Instr in = prog[pc];
     if (in.op == OP_END) break;
     uint32_t fail = 0;
+    if (trace && threadIdx.x == 0) trace[2ull * pc] = global_timer_ns();
     switch (in.op) {
       case OP_NOP: break;
       case OP_COPY:
@@ -220,6 +224,10 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
         break;
       }
       default: fail = ST_BAD_OP;
+    }
+    if (trace) {                // uniform over the CTA: the pointer is a launch argument
+      __syncthreads();
+      if (threadIdx.x == 0) trace[2ull * pc + 1] = global_timer_ns();
     }
     if (fail) {
       if (threadIdx.x == 0) report(R.status, fail, static_cast<uint32_t>(stream), pc, in.op);

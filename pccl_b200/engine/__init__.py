@@ -250,9 +250,10 @@ class Engine:
         return json.loads(self._e.stats())
 
     def trace(self, path: Optional[str] = None) -> Dict:
-        """Instruction-level Chrome trace of the CPU executor (recorded while ``PCCL_TRACE=1``); written
-        to ``path`` when given (open it in chrome://tracing or Perfetto).  GPU launches are timed with
-        ``timed_exeOp``."""
+        """Instruction-level Chrome trace (recorded while ``PCCL_TRACE=1``); written to ``path`` when given
+        (open it in chrome://tracing or Perfetto).  The CPU executor stamps host time; the interpreter
+        kernel stamps ``%globaltimer`` around every instruction, and a traced GPU launch is followed by a
+        synchronize of its stream, so trace to look at a schedule and time with ``timed_exeOp``."""
         doc = json.loads(self._e.trace())
         if path:
             with open(path, "w") as f:

@@ -294,3 +294,31 @@ def test_instruction_trace_is_chrome_trace_json(tmp_path):
     assert ev and ev[0]["ph"] == "X" and ev[0]["name"] == "COPY" and ev[0]["args"]["bytes"] == 4000
     assert json.loads((tmp_path / "t.json").read_text())["traceEvents"] == ev
     assert e.trace()["traceEvents"] == []       # reading clears the record
+
+
+def test_device_stamps_become_trace_events():
+    """The interpreter kernel leaves two timer words per instruction; the engine pairs them with the program it
+    launched.  Here the stamp buffer is made by hand: reached instructions get spans, END and the unreached do not."""
+    import re
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import build
+    e = Engine(0, 2); e.initEngine("cpu")
+    e.regOp("ar", build("ring_allreduce", 2))
+    in_bytes = 4 * 4096
+    with pytest.raises(RuntimeError) as err:
+        e._e.ingestDeviceTrace("ar", in_bytes, 1, [0])
+    n = int(re.search(r"for (\d+) instructions", str(err.value)).group(1))
+    assert n >= 6
+    stamps = []
+    for i in range(n):
+        reached = i < n - 3                   # the last instructions never ran (a stream that gave up early)
+        stamps += [1_000_000 + 100 * i, 1_000_000 + 100 * i + 40] if reached else [0, 0]
+    e._e.ingestDeviceTrace("ar", in_bytes, 1, stamps)
+    ev = e.trace()["traceEvents"]
+    assert 0 < len(ev) <= n - 3 and all(x["name"] != "END" and x["cat"] == "ar" and x["dur"] == pytest.approx(0.04) for x in ev)
+    assert [x["ts"] for x in ev] == sorted(x["ts"] for x in ev)
+    moved = [x for x in ev if x["name"] in ("COPY", "REDUCE")]
+    assert moved and all(x["args"]["bytes"] == in_bytes // 2 for x in moved)
+    assert all(x["args"]["bytes"] == 0 for x in ev if x["name"] in ("NOTIFY", "WAIT"))
+    with pytest.raises(RuntimeError, match="no operator"):
+        e._e.ingestDeviceTrace("nope", in_bytes, 1, stamps)
