@@ -698,6 +698,181 @@ def nvls_allgather(n: int, channels: int = 1) -> CollectiveIR:
     return ir
 
 
+# ---------------------------------------------------------------------------------------------
+# rooted and point-to-point programs
+# ---------------------------------------------------------------------------------------------
+def _check_rank(n: int, **ranks) -> None:
+    for what, r in ranks.items():
+        if not 0 <= r < n:
+            raise ValueError(f"{what}={r} is not a rank of a world of {n}")
+
+
+def _ack(ir: CollectiveIR, consumer: int, producer: int, after: int, step: int, ch: int) -> int:
+    """The consumer tells the producer that it has taken the data out of its workspace, and the producer waits for
+    that before it ends.  In the symmetric collectives every rank needs something from every other rank in every
+    launch, so nobody gets ahead; a rank that ONLY sends could otherwise run two launches ahead and overwrite a
+    workspace half (the halves alternate by launch) that the receiver of the launch before last still reads."""
+    nt = ir.notify(consumer, producer, deps=[after], step=step, channel=ch)
+    return ir.get_notified(consumer, producer, deps=[nt], step=step, channel=ch)
+
+
+def send_recv(n: int, channels: int = 1, device_type=DeviceType.CUDA, src: int = 0, dst: int = 1) -> CollectiveIR:
+    """Point to point: rank ``src``'s input becomes rank ``dst``'s output.  The sender stores into the receiver's
+    workspace and the receiver copies out, so neither tensor needs to come from the symmetric heap; the other
+    ranks have empty programs."""
+    _check_rank(n, src=src, dst=dst)
+    U = channels
+    ir = _new(f"send_recv_n{n}_c{channels}_{src}to{dst}", "send_recv", n, U,
+              {"input": U, "output": U, "scratch": U}, device_type)
+    ir.attrs.update(src=src, dst=dst)
+    ir.set_precondition([Chunk({src}, src, U, 0, "input")])
+    ir.set_postcondition([Chunk({src}, dst, U, 0, "output")])
+    for ch in range(channels):
+        if src == dst:
+            ir.copy(Chunk({src}, src, 1, ch, "input"), Chunk({src}, src, 1, ch, "output"), step=0, channel=ch)
+            continue
+        push = ir.copy(Chunk({src}, src, 1, ch, "input"), Chunk({src}, dst, 1, ch, "scratch", origin=ch),
+                       step=0, channel=ch)
+        took = ir.copy(Chunk({src}, dst, 1, ch, "scratch", origin=ch), Chunk({src}, dst, 1, ch, "output"),
+                       deps=[push], step=1, channel=ch)
+        _ack(ir, dst, src, took, 2, ch)
+    return ir
+
+
+def broadcast(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int = 0, tree: bool = False) -> CollectiveIR:
+    """``root``'s input reaches every rank's output.  Default: the root stores to every peer in one step (on a switch
+    its port is the limit either way and one hop is the shortest path); ``tree=True`` relays along a binomial tree,
+    log2(n) rounds in which every holder sends once, for links where the root's fan-out is the bottleneck."""
+    _check_rank(n, root=root)
+    U = channels
+    ir = _new(f"broadcast_n{n}_c{channels}_r{root}{'_tree' if tree else ''}", "broadcast", n, U,
+              {"input": U, "output": U, "scratch": U}, device_type)
+    ir.attrs["root"] = root
+    ir.set_precondition([Chunk({root}, root, U, 0, "input")])
+    ir.set_postcondition([Chunk({root}, r, U, 0, "output") for r in range(n)])
+    real = lambda v: (v + root) % n        # the tree is laid over ranks counted from the root
+    for ch in range(channels):
+        got = {root: ir.copy(Chunk({root}, root, 1, ch, "input"), Chunk({root}, root, 1, ch, "output"), step=0, channel=ch)}
+        if not tree:
+            for v in range(1, n):
+                d = real(v)
+                push = ir.copy(Chunk({root}, root, 1, ch, "input"), Chunk({root}, d, 1, ch, "scratch", origin=ch),
+                               step=0, channel=ch)
+                took = ir.copy(Chunk({root}, d, 1, ch, "scratch", origin=ch), Chunk({root}, d, 1, ch, "output"),
+                               deps=[push], step=1, channel=ch)
+                _ack(ir, d, root, took, 2, ch)
+            continue
+        dist = 1
+        while dist * 2 < n:
+            dist *= 2
+        step = 1
+        parent = {}
+        while dist >= 1:
+            for v in range(0, n, 2 * dist):
+                if v + dist >= n:
+                    continue
+                a, b = real(v), real(v + dist)
+                push = ir.copy(Chunk({root}, a, 1, ch, "output"), Chunk({root}, b, 1, ch, "scratch", origin=ch),
+                               deps=[got[a]], step=step, channel=ch)
+                got[b] = ir.copy(Chunk({root}, b, 1, ch, "scratch", origin=ch), Chunk({root}, b, 1, ch, "output"),
+                                 deps=[push], step=step + 1, channel=ch)
+                parent[b] = a
+            dist //= 2
+            step += 2
+        for b, a in parent.items():         # after the last round, so that no parent's later sends wait for an ack
+            _ack(ir, b, a, got[b], step, ch)
+    return ir
+
+
+def reduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum", root: int = 0) -> CollectiveIR:
+    """Rooted reduction along a binomial tree: log2(n) rounds, after which ``root``'s output holds the reduction of
+    every rank's input.  The other ranks accumulate in their workspace; their outputs are left alone."""
+    _check_rank(n, root=root)
+    U = channels
+    levels = max(1, (n - 1).bit_length())
+    ir = _new(f"reduce_n{n}_c{channels}_r{root}", "reduce", n, U,
+              {"input": U, "output": U, "scratch": U * (levels + 1)}, device_type, redop)
+    ir.attrs["root"] = root
+    ir.set_precondition([Chunk({r}, r, U, 0, "input") for r in range(n)])
+    ir.set_postcondition([Chunk(_all(n), root, U, 0, "output")])
+    real = lambda v: (v + root) % n
+
+    def acc(r: int, have, ch: int) -> Chunk:        # where rank r keeps its partial result
+        if r == root:
+            return Chunk(have, r, 1, ch, "output")
+        return Chunk(have, r, 1, levels * U + ch, "scratch", origin=ch)
+    for ch in range(channels):
+        last, have = {}, {}
+        for r in range(n):
+            have[r] = {r}
+            last[r] = ir.copy(Chunk({r}, r, 1, ch, "input"), acc(r, {r}, ch), step=0, channel=ch)
+        lvl, dist, step = 0, 1, 1
+        while dist < n:
+            for v in range(0, n, 2 * dist):
+                if v + dist >= n:
+                    continue
+                a, b = real(v), real(v + dist)
+                slot = lvl * U + ch
+                push = ir.copy(acc(b, have[b], ch), Chunk(have[b], a, 1, slot, "scratch", origin=ch),
+                               deps=[last[b]], step=step, channel=ch)
+                last[a] = ir.reduce(Chunk(have[b], a, 1, slot, "scratch", origin=ch), acc(a, have[a] | have[b], ch),
+                                    deps=[push, last[a]], step=step + 1, channel=ch)
+                _ack(ir, a, b, last[a], step + 2, ch)        # b has sent its only message: waiting costs it nothing
+                have[a] = have[a] | have[b]
+            dist *= 2
+            lvl += 1
+            step += 2
+    return ir
+
+
+def scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int = 0) -> CollectiveIR:
+    """Block d of ``root``'s input becomes rank d's output."""
+    _check_rank(n, root=root)
+    blk = channels
+    ir = _new(f"scatter_n{n}_c{channels}_r{root}", "scatter", n, n * blk,
+              {"input": n * blk, "output": blk, "scratch": blk}, device_type, block_units=blk)
+    ir.attrs["root"] = root
+    ir.set_precondition([Chunk({root}, root, n * blk, 0, "input")])
+    ir.set_postcondition([Chunk({root}, d, blk, 0, "output", origin=d * blk) for d in range(n)])
+    for ch in range(channels):
+        acks = []
+        for k in range(n):
+            d = (root + k) % n
+            src = Chunk({root}, root, 1, d * blk + ch, "input")
+            if d == root:
+                ir.copy(src, Chunk({root}, d, 1, ch, "output", origin=d * blk + ch), step=0, channel=ch)
+                continue
+            push = ir.copy(src, Chunk({root}, d, 1, ch, "scratch", origin=d * blk + ch), step=0, channel=ch)
+            took = ir.copy(Chunk({root}, d, 1, ch, "scratch", origin=d * blk + ch),
+                           Chunk({root}, d, 1, ch, "output", origin=d * blk + ch), deps=[push], step=1, channel=ch)
+            acks.append((d, took))
+        for d, took in acks:                # after all the sends
+            _ack(ir, d, root, took, 2, ch)
+    return ir
+
+
+def gather(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int = 0) -> CollectiveIR:
+    """Rank s's input becomes block s of ``root``'s output."""
+    _check_rank(n, root=root)
+    blk = channels
+    ir = _new(f"gather_n{n}_c{channels}_r{root}", "gather", n, blk,
+              {"input": blk, "output": n * blk, "scratch": n * blk}, device_type, block_units=blk)
+    ir.attrs["root"] = root
+    ir.set_precondition([Chunk({s}, s, blk, 0, "input", origin=s * blk) for s in range(n)])
+    ir.set_postcondition([Chunk({s}, root, blk, s * blk, "output", origin=s * blk) for s in range(n)])
+    for ch in range(channels):
+        for s in range(n):
+            src = Chunk({s}, s, 1, ch, "input", origin=s * blk + ch)
+            if s == root:
+                ir.copy(src, Chunk({s}, root, 1, s * blk + ch, "output", origin=s * blk + ch), step=0, channel=ch)
+                continue
+            push = ir.copy(src, Chunk({s}, root, 1, s * blk + ch, "scratch", origin=s * blk + ch), step=0, channel=ch)
+            took = ir.copy(Chunk({s}, root, 1, s * blk + ch, "scratch", origin=s * blk + ch),
+                           Chunk({s}, root, 1, s * blk + ch, "output", origin=s * blk + ch), deps=[push], step=1, channel=ch)
+            _ack(ir, root, s, took, 2, ch)
+    return ir
+
+
 ALGORITHMS = {
     "ring_allreduce": ring_allreduce,
     "ring_allgather": ring_allgather,
@@ -717,6 +892,11 @@ ALGORITHMS = {
     "halving_doubling_allreduce": halving_doubling_allreduce,
     "hierarchical_allreduce": hierarchical_allreduce,
     "hierarchical_allgather": hierarchical_allgather,
+    "send_recv": send_recv,
+    "broadcast": broadcast,
+    "reduce": reduce,
+    "scatter": scatter,
+    "gather": gather,
 }
 
 

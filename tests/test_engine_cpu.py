@@ -21,10 +21,14 @@ def _collective_rank(rank, world, port, algo, transport, dtype_name, n_elems, ch
     g = torch.Generator().manual_seed(0)
     coll = ir.collective
     per_rank = {"allreduce": n_elems, "reduce_scatter": n_elems * world, "allgather": n_elems,
-                "alltoall": n_elems * world}[coll]
+                "alltoall": n_elems * world, "send_recv": n_elems, "broadcast": n_elems, "reduce": n_elems,
+                "scatter": n_elems * world, "gather": n_elems}[coll]
     xs = [((torch.rand(per_rank, generator=g) * 2 - 1) * 4).to(dtype) for _ in range(world)]
     out_elems = {"allreduce": n_elems, "reduce_scatter": n_elems, "allgather": n_elems * world,
-                 "alltoall": n_elems * world}[coll]
+                 "alltoall": n_elems * world, "send_recv": n_elems, "broadcast": n_elems, "reduce": n_elems,
+                 "scatter": n_elems, "gather": n_elems * world}[coll]
+    root = ir.attrs.get("root", 0)
+    untouched = torch.full((out_elems,), -777.0)
     errs = []
     for it in range(3):     # repeated launches exercise the epoch-counting signals and scratch halves
         x = (xs[rank].float() + it).to(dtype)
@@ -37,8 +41,18 @@ def _collective_rank(rank, world, port, algo, transport, dtype_name, n_elems, ch
             ref = torch.stack(full).sum(0)[rank * n_elems:(rank + 1) * n_elems]
         elif coll == "allgather":
             ref = torch.cat(full)
-        else:
+        elif coll == "alltoall":
             ref = torch.cat([f[rank * n_elems:(rank + 1) * n_elems] for f in full])
+        elif coll == "send_recv":           # only the receiver's output is written
+            ref = full[ir.attrs["src"]] if rank == ir.attrs["dst"] else untouched
+        elif coll == "broadcast":
+            ref = full[root]
+        elif coll == "reduce":
+            ref = torch.stack(full).sum(0) if rank == root else untouched
+        elif coll == "scatter":
+            ref = full[root][rank * n_elems:(rank + 1) * n_elems]
+        else:
+            ref = torch.cat(full) if rank == root else untouched
         errs.append((y.float() - ref).abs().max().item())
     st = e.stats()
     e.exitCluster()
@@ -222,7 +236,9 @@ def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
     ("direct_reduce_scatter", {}), ("direct_allgather", {}), ("ring_allgather", {}), ("ring_kv_rotation", {}),
     ("alltoall", {}), ("ulysses_alltoall", {}), ("ring_reduce_scatter", {}), ("recursive_doubling_allgather", {}),
     ("halving_doubling_allreduce", {}), ("hierarchical_allreduce", {"per_host": 2}),
-    ("hierarchical_allgather", {"per_host": 2})])
+    ("hierarchical_allgather", {"per_host": 2}),
+    ("send_recv", {"src": 2, "dst": 1}), ("broadcast", {"root": 1}), ("broadcast", {"root": 3, "tree": True}),
+    ("reduce", {"root": 2}), ("scatter", {"root": 1}), ("gather", {"root": 3})])
 def test_algorithms_on_cpu_ranks_shm(algo, kwargs):
     res = run_ranks(_collective_rank, 4, args=(algo, "shm", "float32", 1000 + 17, 2, 2, kwargs),
                     env={"PCCL_WORKSPACE_MB": "16"})
@@ -322,3 +338,34 @@ def test_device_stamps_become_trace_events():
     assert all(x["args"]["bytes"] == 0 for x in ev if x["name"] in ("NOTIFY", "WAIT"))
     with pytest.raises(RuntimeError, match="no operator"):
         e._e.ingestDeviceTrace("nope", in_bytes, 1, stamps)
+
+
+def _runahead_rank(rank, world, port):
+    """A sender that is never slowed down by its own work against a receiver that dawdles before every launch."""
+    import time
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, build
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("p2p", build("send_recv", world, channels=1, device_type=DeviceType.CPU, src=0, dst=1))
+    bad = 0
+    t0 = time.monotonic()
+    for it in range(6):
+        if rank == 1:
+            time.sleep(0.15)
+        x = torch.full((2048,), float(it + 1))
+        y = torch.zeros(2048)
+        e.exeOp("p2p", x, y)
+        if rank == 1:
+            bad += int((y != it + 1).any())
+    took = time.monotonic() - t0
+    e.exitCluster()
+    return bad, took
+
+
+def test_a_rank_that_only_sends_cannot_overrun_the_receivers_workspace():
+    """Workspace halves alternate by launch, so a sender two launches ahead would overwrite data its receiver has not
+    taken yet: the rooted programs end with an acknowledgement, which holds the sender to at most one launch ahead."""
+    res = run_ranks(_runahead_rank, 2, env={"PCCL_WORKSPACE_MB": "8"})
+    assert res[1][0] == 0
+    assert res[0][1] > 0.5          # the sender was held back by the receiver's pace (6 x 0.15 s)
