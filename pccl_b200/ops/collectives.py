@@ -150,3 +150,67 @@ def all_to_all(eng: Engine, inp: torch.Tensor, out: torch.Tensor, blocks: Option
                  _blocks(nbytes * eng.world, blocks), threads, s, inp.data_ptr(), 0, 0)
     count_launch()
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Rooted and point-to-point collectives: library programs of pccl_b200.lang run by the engine (the
+# interpreter kernel on a CUDA engine, the host executor on a CPU engine).  Data travels through the
+# engine's workspace, so the tensors may be ordinary ones.  Every rank makes every call.
+# ---------------------------------------------------------------------------------------------
+def _library_op(eng: Engine, algo: str, **kw) -> str:
+    """Registers ``lang.build(algo, world, **kw)`` with the engine on first use and returns its name."""
+    from ..lang import DeviceType, build
+    name = "lib." + algo + "".join(f".{k}={v}" for k, v in sorted(kw.items()))
+    done = eng.__dict__.setdefault("_library_ops", set())
+    if name not in done:
+        dev = DeviceType.CUDA if eng.device == "cuda" else DeviceType.CPU
+        eng.regOp(name, build(algo, eng.world, device_type=dev, **kw))
+        done.add(name)
+    return name
+
+
+def _run_library_op(eng: Engine, name: str, inp: torch.Tensor, out: torch.Tensor, width: int, lane: int, stream) -> None:
+    eng.exeOp(name, inp, out, width=width, lane=lane, stream=stream)
+    if inp.is_cuda:
+        count_launch()
+
+
+def broadcast(eng: Engine, t: torch.Tensor, root: int = 0, out: Optional[torch.Tensor] = None, tree: bool = False,
+              channels: int = 1, width: int = 1, lane: int = 0, stream=None) -> torch.Tensor:
+    """``t`` of rank ``root`` reaches ``out`` (default: ``t`` itself, in place) on every rank."""
+    out = t if out is None else out
+    _run_library_op(eng, _library_op(eng, "broadcast", root=root, tree=tree, channels=channels), t, out, width, lane, stream)
+    return out
+
+
+def reduce(eng: Engine, inp: torch.Tensor, out: torch.Tensor, root: int = 0, op: str = "sum", channels: int = 1,
+           width: int = 1, lane: int = 0, stream=None) -> torch.Tensor:
+    """The reduction of every rank's ``inp`` lands in ``out`` of rank ``root``; the other ranks' ``out`` is not written."""
+    _run_library_op(eng, _library_op(eng, "reduce", root=root, redop=op, channels=channels), inp, out, width, lane, stream)
+    return out
+
+
+def scatter(eng: Engine, inp: torch.Tensor, out: torch.Tensor, root: int = 0, channels: int = 1, width: int = 1,
+            lane: int = 0, stream=None) -> torch.Tensor:
+    """Block d of ``root``'s ``inp`` (world * out.numel() elements; only read on the root) becomes rank d's ``out``."""
+    if inp.numel() != out.numel() * eng.world:
+        raise ValueError("scatter: inp must hold world blocks of out's size (on every rank, although only the root's is read)")
+    _run_library_op(eng, _library_op(eng, "scatter", root=root, channels=channels), inp, out, width, lane, stream)
+    return out
+
+
+def gather(eng: Engine, inp: torch.Tensor, out: torch.Tensor, root: int = 0, channels: int = 1, width: int = 1,
+           lane: int = 0, stream=None) -> torch.Tensor:
+    """Rank s's ``inp`` becomes block s of ``root``'s ``out`` (world * inp.numel() elements; only written on the root)."""
+    if out.numel() != inp.numel() * eng.world:
+        raise ValueError("gather: out must hold world blocks of inp's size (on every rank, although only the root's is written)")
+    _run_library_op(eng, _library_op(eng, "gather", root=root, channels=channels), inp, out, width, lane, stream)
+    return out
+
+
+def send_recv(eng: Engine, inp: torch.Tensor, out: torch.Tensor, src: int, dst: int, channels: int = 1, width: int = 1,
+              lane: int = 0, stream=None) -> torch.Tensor:
+    """``inp`` of rank ``src`` becomes ``out`` of rank ``dst``.  All ranks call it (the others run an empty program),
+    so it can sit in a sequence of collectives without a separate group."""
+    _run_library_op(eng, _library_op(eng, "send_recv", src=src, dst=dst, channels=channels), inp, out, width, lane, stream)
+    return out

@@ -369,3 +369,52 @@ def test_a_rank_that_only_sends_cannot_overrun_the_receivers_workspace():
     res = run_ranks(_runahead_rank, 2, env={"PCCL_WORKSPACE_MB": "8"})
     assert res[1][0] == 0
     assert res[0][1] > 0.5          # the sender was held back by the receiver's pace (6 x 0.15 s)
+
+
+def _rooted_api_rank(rank, world, port):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.ops import collectives as C
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    n = 3000 + 5
+    mine = torch.arange(n, dtype=torch.float32) + 1000 * rank
+    errs = {}
+    for it in range(2):                              # the second round reuses the registered programs
+        t = mine.clone() + it
+        C.broadcast(e, t, root=1)
+        errs["broadcast"] = (t - (torch.arange(n) + 1000 + it)).abs().max().item()
+        out = torch.full((n,), -1.0)
+        C.reduce(e, mine + it, out, root=2)
+        want = sum(torch.arange(n, dtype=torch.float32) + 1000 * r + it for r in range(world)) if rank == 2 else torch.full((n,), -1.0)
+        errs["reduce"] = (out - want).abs().max().item()
+        big = torch.arange(n * world, dtype=torch.float32) + 7 * rank + it
+        part = torch.zeros(n)
+        C.scatter(e, big, part, root=0)
+        errs["scatter"] = (part - (torch.arange(n * world, dtype=torch.float32) + it)[rank * n:(rank + 1) * n]).abs().max().item()
+        allv = torch.full((n * world,), -1.0)
+        C.gather(e, mine + it, allv, root=1, width=2)
+        want = torch.cat([torch.arange(n, dtype=torch.float32) + 1000 * r + it for r in range(world)]) if rank == 1 else torch.full((n * world,), -1.0)
+        errs["gather"] = (allv - want).abs().max().item()
+        got = torch.full((n,), -1.0)
+        C.send_recv(e, mine + it, got, src=2, dst=0)
+        want = torch.arange(n, dtype=torch.float32) + 2000 + it if rank == 0 else torch.full((n,), -1.0)
+        errs["send_recv"] = (got - want).abs().max().item()
+        if max(errs.values()) > 0:
+            break
+    ops = sorted(k for k in e.stats()["ops"] if k.startswith("lib."))
+    e.exitCluster()
+    return errs, ops
+
+
+def test_rooted_collectives_through_the_ops_api_on_cpu_ranks():
+    res = run_ranks(_rooted_api_rank, 3, env={"PCCL_WORKSPACE_MB": "16"}, timeout=120)
+    for r in range(3):
+        errs, ops = res[r]
+        assert max(errs.values()) == 0, (r, errs)
+        assert len(ops) == 5            # one registration per (program, arguments), reused by the second round
+    with pytest.raises(ValueError):
+        from pccl_b200.ops import collectives as C
+
+        class _E:
+            world = 4
+        C.scatter(_E(), torch.zeros(7), torch.zeros(2))
