@@ -739,6 +739,31 @@ def send_recv(n: int, channels: int = 1, device_type=DeviceType.CUDA, src: int =
     return ir
 
 
+def ring_shift(n: int, channels: int = 1, device_type=DeviceType.CUDA, shift: int = 1) -> CollectiveIR:
+    """Permutation: rank r's input becomes the output of rank (r + shift) mod n.  One hop of ring attention's KV
+    rotation when the attention of a block is computed between two hops; each receiver acknowledges, because a
+    rank's sends depend on nothing that its receiver does."""
+    U = channels
+    shift %= n
+    ir = _new(f"ring_shift_n{n}_c{channels}_s{shift}", "permute", n, U, {"input": U, "output": U, "scratch": U}, device_type)
+    ir.attrs["shift"] = shift
+    ir.set_precondition([Chunk({r}, r, U, 0, "input", origin=r * U) for r in range(n)])
+    ir.set_postcondition([Chunk({r}, (r + shift) % n, U, 0, "output", origin=r * U) for r in range(n)])
+    for ch in range(channels):
+        for r in range(n):
+            d = (r + shift) % n
+            org = r * U + ch
+            if d == r:
+                ir.copy(Chunk({r}, r, 1, ch, "input", origin=org), Chunk({r}, r, 1, ch, "output", origin=org), step=0, channel=ch)
+                continue
+            push = ir.copy(Chunk({r}, r, 1, ch, "input", origin=org), Chunk({r}, d, 1, ch, "scratch", origin=org),
+                           step=0, channel=ch)
+            took = ir.copy(Chunk({r}, d, 1, ch, "scratch", origin=org), Chunk({r}, d, 1, ch, "output", origin=org),
+                           deps=[push], step=1, channel=ch)
+            _ack(ir, d, r, took, 2, ch)
+    return ir
+
+
 def broadcast(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int = 0, tree: bool = False) -> CollectiveIR:
     """``root``'s input reaches every rank's output.  Default: the root stores to every peer in one step (on a switch
     its port is the limit either way and one hop is the shortest path); ``tree=True`` relays along a binomial tree,
@@ -781,6 +806,54 @@ def broadcast(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int 
             step += 2
         for b, a in parent.items():         # after the last round, so that no parent's later sends wait for an ack
             _ack(ir, b, a, got[b], step, ch)
+    return ir
+
+
+def scatter_allgather_broadcast(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int = 0) -> CollectiveIR:
+    """Broadcast of a long vector in two steps: the root sends piece d to rank d, then every rank sends its piece to
+    all the others.  The root's port carries the vector once instead of n-1 times, and so does every other port."""
+    _check_rank(n, root=root)
+    sh = channels
+    U = n * sh
+    ir = _new(f"scatter_allgather_broadcast_n{n}_c{channels}_r{root}", "broadcast", n, U,
+              {"input": U, "output": U, "scratch": U}, device_type)
+    ir.attrs["root"] = root
+    ir.set_precondition([Chunk({root}, root, U, 0, "input")])
+    ir.set_postcondition([Chunk({root}, r, U, 0, "output") for r in range(n)])
+    for ch in range(channels):
+        have = {}
+        for k in range(n):                  # step 0-1: piece d -> rank d
+            d = (root + k) % n
+            u = d * sh + ch
+            if d == root:
+                for v in range(n):          # the root keeps everything
+                    own = ir.copy(Chunk({root}, root, 1, v * sh + ch, "input"), Chunk({root}, root, 1, v * sh + ch, "output"),
+                                  step=0, channel=ch)
+                    if v == root:
+                        have[root] = own
+                continue
+            push = ir.copy(Chunk({root}, root, 1, u, "input"), Chunk({root}, d, 1, u, "scratch", origin=u), step=0, channel=ch)
+            have[d] = ir.copy(Chunk({root}, d, 1, u, "scratch", origin=u), Chunk({root}, d, 1, u, "output"),
+                              deps=[push], step=1, channel=ch)
+            _ack(ir, d, root, have[d], 4, ch)           # the root receives nothing else from d
+        for d in range(n):                  # step 2-3: every other rank hands its piece round (the root has them all)
+            if d == root:
+                continue
+            u = d * sh + ch
+            for k in range(1, n):
+                e = (d + k) % n
+                if e == root:
+                    continue
+                push = ir.copy(Chunk({root}, d, 1, u, "output"), Chunk({root}, e, 1, u, "scratch", origin=u),
+                               deps=[have[d]], step=2, channel=ch)
+                ir.copy(Chunk({root}, e, 1, u, "scratch", origin=u), Chunk({root}, e, 1, u, "output"),
+                        deps=[push], step=3, channel=ch)
+        for e in range(n):                  # the root's own piece reaches the others from the root
+            if e == root:
+                continue
+            u = root * sh + ch
+            push = ir.copy(Chunk({root}, root, 1, u, "input"), Chunk({root}, e, 1, u, "scratch", origin=u), step=2, channel=ch)
+            ir.copy(Chunk({root}, e, 1, u, "scratch", origin=u), Chunk({root}, e, 1, u, "output"), deps=[push], step=3, channel=ch)
     return ir
 
 
@@ -893,7 +966,9 @@ ALGORITHMS = {
     "hierarchical_allreduce": hierarchical_allreduce,
     "hierarchical_allgather": hierarchical_allgather,
     "send_recv": send_recv,
+    "ring_shift": ring_shift,
     "broadcast": broadcast,
+    "scatter_allgather_broadcast": scatter_allgather_broadcast,
     "reduce": reduce,
     "scatter": scatter,
     "gather": gather,

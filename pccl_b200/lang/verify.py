@@ -69,8 +69,36 @@ def _accesses(ir: CollectiveIR, op) -> Tuple[List[tuple], List[tuple]]:
     return reads, writes
 
 
+def relaunch_hazards(ir: CollectiveIR) -> List[Tuple[int, int]]:
+    """Pairs (s, r) such that rank s writes into rank r's workspace but nothing rank s executes depends on anything
+    rank r executes.
+
+    The engine alternates between two halves of the workspace from launch to launch and never clears a signal, so a
+    program is run again without any barrier between launches.  That is safe as long as a writer cannot get two
+    launches ahead of the rank it writes to.  If some op of s depends on some op of r, then s ends launch L+1 only
+    after r has begun it, hence after r has finished launch L, and the half that s overwrites in launch L+2 is no
+    longer read.  A rank that only ever sends has no such tie and needs an acknowledgement from its receiver."""
+    if not ir.ops:
+        return []
+    anc = ir.op_dag.reachability()
+    index = anc["__index__"]
+    mask_of: Dict[int, int] = {}
+    reach_of: Dict[int, int] = {}
+    for op in ir.ops.values():
+        e = op.executor
+        mask_of[e] = mask_of.get(e, 0) | (1 << index[op.op_id])
+        reach_of[e] = reach_of.get(e, 0) | anc[op.op_id]
+    pairs = set()
+    for op in ir.ops.values():
+        _reads, writes = _accesses(ir, op)
+        for dev, buf, _off, _size in writes:
+            if buf == "scratch" and dev != op.executor:
+                pairs.add((op.executor, dev))
+    return sorted((s, r) for s, r in pairs if not (reach_of.get(s, 0) & mask_of.get(r, 0)))
+
+
 def verify(ir: CollectiveIR, check_races: bool = True, check_remote_scratch_only: bool = False,
-           check_annotations: bool = True) -> Report:
+           check_annotations: bool = True, check_relaunch: bool = True) -> Report:
     errors: List[str] = []
     if not ir.validate_dag():
         return Report(False, ["op DAG has a cycle"], len(ir.ops), 0, 0.0, {})
@@ -227,6 +255,13 @@ def verify(ir: CollectiveIR, check_races: bool = True, check_remote_scratch_only
                                       f"({'write' if aw else 'read'}/{'write' if bw else 'read'}) with no ordering")
             if len(errors) > 32:
                 break
+
+    # ---- repeated launches ----------------------------------------------------------------------
+    if check_relaunch and not errors:
+        for s_, r_ in relaunch_hazards(ir)[:8]:
+            errors.append(f"relaunch: rank {s_} writes into rank {r_}'s workspace but waits for nothing from rank {r_}: "
+                          f"launched repeatedly it can overwrite data that rank {r_} has not taken yet "
+                          f"(end with an acknowledgement: NOTIFY from {r_}, GET_NOTIFIED on {s_})")
 
     return Report(not errors, errors, len(ir.ops), ir.num_steps(), ir.op_dag.critical_path(), traffic)
 

@@ -175,11 +175,24 @@ def _run_library_op(eng: Engine, name: str, inp: torch.Tensor, out: torch.Tensor
         count_launch()
 
 
-def broadcast(eng: Engine, t: torch.Tensor, root: int = 0, out: Optional[torch.Tensor] = None, tree: bool = False,
+def broadcast(eng: Engine, t: torch.Tensor, root: int = 0, out: Optional[torch.Tensor] = None, algo: str = "direct",
               channels: int = 1, width: int = 1, lane: int = 0, stream=None) -> torch.Tensor:
-    """``t`` of rank ``root`` reaches ``out`` (default: ``t`` itself, in place) on every rank."""
+    """``t`` of rank ``root`` reaches ``out`` (default: ``t`` itself, in place) on every rank.  ``algo``: ``"direct"``
+    (the root stores to every peer: shortest, right for small messages), ``"tree"`` (binomial relay), ``"scatter_allgather"``
+    (the root's port carries the vector once: right for long vectors), or ``"auto"``: the cheapest of the three by the
+    cost model on an NVSwitch of this world's size."""
     out = t if out is None else out
-    _run_library_op(eng, _library_op(eng, "broadcast", root=root, tree=tree, channels=channels), t, out, width, lane, stream)
+    if algo == "auto":
+        from ..synth import Topology, choose
+        ranked = choose("broadcast", Topology.nvswitch(eng.world), t.numel() * t.element_size(), channels=channels, root=root)
+        algo = {"broadcast": "direct", "broadcast[tree]": "tree"}.get(ranked[0][0], "scatter_allgather") if ranked else "direct"
+    if algo == "scatter_allgather":
+        name = _library_op(eng, "scatter_allgather_broadcast", root=root, channels=channels)
+    elif algo in ("direct", "tree"):
+        name = _library_op(eng, "broadcast", root=root, tree=(algo == "tree"), channels=channels)
+    else:
+        raise ValueError(f"broadcast: unknown algo {algo!r}")
+    _run_library_op(eng, name, t, out, width, lane, stream)
     return out
 
 
@@ -213,4 +226,12 @@ def send_recv(eng: Engine, inp: torch.Tensor, out: torch.Tensor, src: int, dst: 
     """``inp`` of rank ``src`` becomes ``out`` of rank ``dst``.  All ranks call it (the others run an empty program),
     so it can sit in a sequence of collectives without a separate group."""
     _run_library_op(eng, _library_op(eng, "send_recv", src=src, dst=dst, channels=channels), inp, out, width, lane, stream)
+    return out
+
+
+def ring_shift(eng: Engine, inp: torch.Tensor, out: torch.Tensor, shift: int = 1, channels: int = 1, width: int = 1,
+               lane: int = 0, stream=None) -> torch.Tensor:
+    """``inp`` of rank r becomes ``out`` of rank (r + shift) mod world: one hop of a ring (the KV rotation of ring
+    attention, when a block's attention is computed between hops)."""
+    _run_library_op(eng, _library_op(eng, "ring_shift", shift=shift % eng.world, channels=channels), inp, out, width, lane, stream)
     return out

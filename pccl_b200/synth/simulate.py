@@ -89,27 +89,36 @@ def estimate(ir: CollectiveIR, topo: Topology, nbytes: int, memory_gbs: float = 
     return Estimate(total, len(per_step), remote_total, worst, per_step)
 
 
+# Forms of one library algorithm that are priced separately.
+_VARIANTS = {"broadcast": ({"tree": False}, {"tree": True})}
+
+
 def choose(collective: str, topo: Topology, nbytes: int, channels: int = 1, include_milp: bool = False,
            nvls: bool = False, **build_kw) -> List[Tuple[str, Estimate, CollectiveIR]]:
     """Library algorithms of ``collective`` that run on ``topo`` (and, with ``include_milp``, the synthesised schedule),
     cheapest first: ``[(name, estimate, ir), ...]``.  NVLS programs are priced only when ``nvls`` says the machine has
     a multicast-capable switch."""
+    import inspect
     out = []
     for name, gen in sorted(ALGORITHMS.items()):
         if name.startswith("nvls_") and not nvls:
             continue
-        import inspect
         accepted = inspect.signature(gen).parameters
         kw = {k: v for k, v in build_kw.items() if k in accepted}      # per_host, redop, device_type: only where they apply
-        try:
-            ir = gen(topo.n, channels=channels, **kw)
-        except (ValueError, TypeError):
-            continue                                     # the world does not fit this algorithm (power of two, hosts, ...)
-        if ir.collective != collective or ir.attrs.get("use"):
-            continue
-        est = estimate(ir, topo, nbytes)
-        if est is not None:
-            out.append((name, est, ir))
+        for variant in _VARIANTS.get(name, ({},)):
+            if any(k in kw for k in variant):
+                if any(kw[k] != v for k, v in variant.items() if k in kw):
+                    continue                             # the caller fixed this argument to another value
+            try:
+                ir = gen(topo.n, channels=channels, **{**variant, **kw})
+            except (ValueError, TypeError):
+                continue                                 # the world does not fit this algorithm (power of two, hosts, ...)
+            if ir.collective != collective or ir.attrs.get("use"):
+                continue
+            est = estimate(ir, topo, nbytes)
+            if est is not None:
+                label = name + "".join(f"[{k}]" for k, v in variant.items() if v is True)
+                out.append((label, est, ir))
     if include_milp:
         from .milp import synthesize
         res = synthesize(collective, topo, nbytes, chunks=channels, time_limit=20.0)

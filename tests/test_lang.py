@@ -48,7 +48,8 @@ def test_ir_builder_and_reference_api():
     ir.set_postcondition([Chunk({0, 1}, 0, 1, 0, "output")])
     assert ir.validate_dag() and ir.validate_topology()
     assert [o.op_id for o in ir.get_operation_sequence()][-1] == c
-    assert verify(ir).ok
+    assert verify(ir, check_relaunch=False).ok        # rank 1 only sends: fine for one launch
+    assert any("relaunch" in e for e in verify(ir).errors)
     with pytest.raises(ValueError):
         ir.create_operation(PrimitiveOpType.COPY, dependencies=[999])
 
@@ -179,3 +180,30 @@ def test_operator_best_picks_by_the_cost_model():
         Operator.best("alltoall", Topology.ring(4), 1 << 20)
     op = Operator.best("alltoall", Topology.ring(4), 1 << 20, include_milp=True)
     assert op.name.startswith("milp_alltoall") and op.estimate.steps >= 2 and op.schedule()["collective"] == "alltoall"
+
+
+def test_verifier_rejects_a_sender_that_nothing_holds_back():
+    """Run again and again, a rank that only sends gets ahead of its receiver and overwrites workspace that is still
+    being read; the verifier wants a tie from the receiver back to the sender."""
+    from pccl_b200.lang import relaunch_hazards
+
+    def program(ack: bool) -> CollectiveIR:
+        ir = CollectiveIR("one_way", "send_recv", units=1, buffers={"input": 1, "output": 1, "scratch": 1})
+        ir.add_device(Device(0, DeviceType.CPU)); ir.add_device(Device(1, DeviceType.CPU))
+        ir.add_link(Link(0, 1))
+        ir.set_precondition([Chunk({0}, 0, 1, 0, "input")])
+        ir.set_postcondition([Chunk({0}, 1, 1, 0, "output")])
+        push = ir.copy(Chunk({0}, 0, 1, 0, "input"), Chunk({0}, 1, 1, 0, "scratch"))
+        took = ir.copy(Chunk({0}, 1, 1, 0, "scratch"), Chunk({0}, 1, 1, 0, "output"), deps=[push])
+        if ack:
+            ir.get_notified(1, 0, deps=[ir.notify(1, 0, deps=[took])])
+        return ir
+    bare = program(False)
+    assert relaunch_hazards(bare) == [(0, 1)]
+    rep = verify(bare)
+    assert not rep.ok and "relaunch" in rep.errors[0]
+    assert verify(bare, check_relaunch=False).ok          # a program that is launched once may leave it out
+    assert verify(program(True)).ok and relaunch_hazards(program(True)) == []
+    # the library's one-way programs carry the acknowledgement
+    for name in ("send_recv", "broadcast", "reduce", "scatter", "gather"):
+        assert relaunch_hazards(build(name, 4)) == []

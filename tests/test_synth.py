@@ -181,6 +181,10 @@ def test_examples_compile_and_the_cpu_ones_run(tmp_path):
     rep = json.loads(r.stdout.strip().splitlines()[-1])
     assert rep["steps"] == 2 and rep["cache_hits"] == 1 and rep["cache_misses"] == 1
     assert json.load(open(out))["collective"] == "allgather"
+    # ring attention and Ulysses over CPU ranks against attention over the whole sequence
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "collective", "context_parallel.py"), "--world", "2",
+                        "--heads", "4", "--seq", "64", "--dim", "16"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "matches attention over the whole sequence" in r.stdout, r.stdout[-1000:] + r.stderr[-2000:]
 
 
 def test_cost_model_ranks_algorithms_the_way_the_topology_demands():
