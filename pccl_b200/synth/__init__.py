@@ -3,5 +3,7 @@ from .topology import Topology, probe_topology
 from .milp import SynthesisResult, synthesize
 from .cache import ScheduleCache
 from .simulate import Estimate, choose, estimate
+from .local_node import GpuInfo, LocalNode, TopologyCache
 
-__all__ = ["Topology", "probe_topology", "SynthesisResult", "synthesize", "ScheduleCache", "Estimate", "choose", "estimate"]
+__all__ = ["Topology", "probe_topology", "SynthesisResult", "synthesize", "ScheduleCache", "Estimate", "choose", "estimate",
+           "GpuInfo", "LocalNode", "TopologyCache"]

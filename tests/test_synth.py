@@ -216,3 +216,70 @@ def test_cost_model_ranks_algorithms_the_way_the_topology_demands():
     r = synthesize("allgather", sw, 16 << 20)
     e = estimate(r.ir, sw, 16 << 20)
     assert abs(max(e.per_step) - r.objective_seconds) <= 1e-3 * r.objective_seconds and e.seconds > r.objective_seconds
+
+
+def test_local_node_from_a_stand_in_sysfs_and_cuda(tmp_path, monkeypatch):
+    """Host description (include/topology/local_node.h in the reference is empty) from a made-up sysfs tree and CUDA
+    runtime: NUMA nodes, each GPU's NUMA node by PCI address, peer access -> nominal topology."""
+    from types import SimpleNamespace
+    from pccl_b200.synth import LocalNode
+    from pccl_b200.synth.local_node import parse_cpu_list
+    assert parse_cpu_list("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11] and parse_cpu_list("") == []
+    sysfs, proc = tmp_path / "sys", tmp_path / "proc"
+    for node, cpus in ((0, "0-3"), (1, "4-7")):
+        d = sysfs / "devices" / "system" / "node" / f"node{node}"
+        d.mkdir(parents=True)
+        (d / "cpulist").write_text(cpus + "\n")
+    for i in range(4):
+        d = sysfs / "bus" / "pci" / "devices" / f"0000:{0x1b + i:02x}:00.0"
+        d.mkdir(parents=True)
+        (d / "numa_node").write_text(f"{i // 2}\n")
+    (proc / "sys" / "kernel" / "random").mkdir(parents=True)
+    (proc / "sys" / "kernel" / "random" / "boot_id").write_text("1234-abcd\n")
+    monkeypatch.delenv("PCCL_HOST_ID", raising=False)
+
+    class Cuda:
+        def __init__(self, reach):
+            self.reach = reach
+
+        def device_count(self):
+            return 4
+
+        def get_device_properties(self, i):
+            return SimpleNamespace(name="B200", multi_processor_count=148, total_memory=180 << 30, pci_domain_id=0,
+                                   pci_bus_id=0x1b + i, pci_device_id=0)
+
+        def can_device_access_peer(self, a, b):
+            return self.reach(a, b)
+    node = LocalNode.probe(str(sysfs), str(proc), Cuda(lambda a, b: True))
+    assert node.host_id == "1234-abcd" and node.cpus == 8 and node.numa_cpus == {0: [0, 1, 2, 3], 1: [4, 5, 6, 7]}
+    assert [g.numa_node for g in node.gpus] == [0, 0, 1, 1] and node.gpus[2].pci_bus_id == "0000:1d:00.0"
+    assert node.cpus_near(3) == [4, 5, 6, 7] and node.fully_peered()
+    topo = node.to_topology()
+    assert topo.name == "nvswitch4" and topo.rotation_symmetric
+    assert LocalNode.from_json(node.to_json()) == node
+    # two islands of two GPUs: peer access inside, a host bridge between
+    split = LocalNode.probe(str(sysfs), str(proc), Cuda(lambda a, b: a // 2 == b // 2))
+    t2 = split.to_topology(port_gbs=770.0, pcie_gbs=50.0)
+    assert not split.fully_peered() and t2.link_bw[(0, 1)] == 770e9 and t2.link_bw[(0, 2)] == 50e9
+    # no GPU, no sysfs: still a description, no topology
+    bare = LocalNode.probe(str(tmp_path / "nothing"), str(tmp_path / "nothing"), SimpleNamespace(device_count=lambda: 0))
+    assert bare.gpus == [] and bare.to_topology() is None and bare.cpus >= 1 and bare.host_id == "unknown"
+
+
+def test_topology_cache_measures_once_per_host(tmp_path):
+    from pccl_b200.synth import TopologyCache
+    cache = TopologyCache(str(tmp_path))
+    calls = []
+
+    def measure():
+        calls.append(1)
+        return Topology.two_level(2, 2)
+    a = cache.get_or_measure("boot-1", 4, measure)
+    b = cache.get_or_measure("boot-1", 4, measure)
+    assert len(calls) == 1 and cache.hits == 1 and cache.misses == 1
+    assert a.fingerprint() == b.fingerprint() and b.shared_caps == a.shared_caps and b.link_bw == a.link_bw
+    cache.get_or_measure("boot-2", 4, measure)            # another boot of the host measures again
+    assert len(calls) == 2
+    (tmp_path / "topology_boot_1_4.json").write_text("{broken")
+    assert cache.load("boot-1", 4) is None                # a damaged file reads as a miss
