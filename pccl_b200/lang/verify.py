@@ -97,6 +97,29 @@ def relaunch_hazards(ir: CollectiveIR) -> List[Tuple[int, int]]:
     return sorted((s, r) for s, r in pairs if not (reach_of.get(s, 0) & mask_of.get(r, 0)))
 
 
+def add_acknowledgements(ir: CollectiveIR) -> int:
+    """Closes every relaunch hazard of ``ir`` in place and returns how many it closed: for a pair (s, r) the receiver r
+    sends a NOTIFY to s once everything that consumes s's writes on r has run, and s ends with the matching
+    GET_NOTIFIED.  A program that has none is left as it is."""
+    added = 0
+    for s_, r_ in relaunch_hazards(ir):
+        pushes = []
+        for op in ir.ops.values():
+            if op.executor != s_:
+                continue
+            _reads, writes = _accesses(ir, op)
+            if any(buf == "scratch" and dev == r_ for dev, buf, _o, _n in writes):
+                pushes.append(op)
+        consumers = sorted({c for p in pushes for c in ir.op_dag.get_successors(p.op_id) if ir.ops[c].executor == r_})
+        after = consumers or [p.op_id for p in pushes]
+        last = max(pushes, key=lambda o: (o.step, o.op_id))
+        step = max(ir.ops[o].step for o in after) + 1
+        nt = ir.notify(r_, s_, deps=after, step=step, channel=last.channel)
+        ir.get_notified(r_, s_, deps=[nt], step=step, channel=last.channel)
+        added += 1
+    return added
+
+
 def verify(ir: CollectiveIR, check_races: bool = True, check_remote_scratch_only: bool = False,
            check_annotations: bool = True, check_relaunch: bool = True) -> Report:
     errors: List[str] = []

@@ -47,16 +47,22 @@ class SynthesisResult:
 
 
 def _solve_allgather(topo: Topology, chunks: int, steps: int, chunk_bytes: float, symmetric: bool, time_limit: float,
-                     alltoall: bool = False):
+                     alltoall: bool = False, only_owner: Optional[int] = None):
     """Spreading model.  All-gather: commodity (owner o, chunk c) starts on o and must reach everybody.  With
     ``alltoall`` a commodity is (o, destination d, c): it must reach d only, other devices may relay it (they
-    receive it at most once).  Returns per step the transfers (o, c, u, v), or (o, d, c, u, v) for all-to-all."""
+    receive it at most once).  With ``only_owner`` the chunks of that one rank are the only commodities: a broadcast
+    (the rotation shortcut does not apply to it).  Returns per step the transfers (o, c, u, v), or (o, d, c, u, v) for
+    all-to-all."""
     n = topo.n
     # Times inside the model are in microseconds: in seconds the coefficients (1e-6) would sit below
     # the solver's feasibility tolerance and it would accept schedules that overrun a port.
     alpha = topo.alpha * 1e6
     chunk_bytes = chunk_bytes * 1e6
-    owners = [0] if symmetric else list(range(n))
+    if only_owner is not None:
+        symmetric = False
+        owners = [only_owner]
+    else:
+        owners = [0] if symmetric else list(range(n))
     if alltoall:
         K = [(o, c, d) for o in owners for d in range(n) if d != o for c in range(chunks)]
     else:
@@ -205,6 +211,34 @@ def _build_allgather_ir(n: int, chunks: int, sends, name: str) -> CollectiveIR:
     return ir
 
 
+def _build_broadcast_ir(n: int, chunks: int, sends, name: str, root: int) -> CollectiveIR:
+    """The root's vector in ``chunks`` pieces; every hop lands in the receiver's scratch slot of the piece and is copied
+    into its output, from where it may be forwarded.  Ranks that only send get an acknowledgement at the end."""
+    from ..lang import add_acknowledgements
+    U = chunks
+    ir = CollectiveIR(name, "broadcast", U, buffers={"input": U, "output": U, "scratch": U})
+    ir.attrs["block_units"] = U
+    ir.attrs["root"] = root
+    for r in range(n):
+        ir.add_device(Device(r, DeviceType.CUDA))
+    ir.fully_connect()
+    ir.set_precondition([Chunk({root}, root, U, 0, "input")])
+    ir.set_postcondition([Chunk({root}, r, U, 0, "output") for r in range(n)])
+    have: Dict[Tuple[int, int], int] = {}
+    for c in range(U):
+        have[(c, root)] = ir.copy(Chunk({root}, root, 1, c, "input"), Chunk({root}, root, 1, c, "output"), step=0, channel=c)
+    for s, step_sends in enumerate(sends):
+        new = {}
+        for (_o, c, u, v) in step_sends:
+            push = ir.copy(Chunk({root}, u, 1, c, "output"), Chunk({root}, v, 1, c, "scratch", origin=c),
+                           deps=[have[(c, u)]], step=1 + 2 * s, channel=c)
+            new[(c, v)] = ir.copy(Chunk({root}, v, 1, c, "scratch", origin=c), Chunk({root}, v, 1, c, "output"),
+                                  deps=[push], step=2 + 2 * s, channel=c)
+        have.update(new)
+    add_acknowledgements(ir)
+    return ir
+
+
 def _build_alltoall_ir(n: int, chunks: int, sends, name: str) -> CollectiveIR:
     """Block d of rank o's input becomes block o of rank d's output.  Every hop lands in the receiver's scratch slot
     of its (o, d, c) -- relays forward from there, the destination copies it into its output -- so nobody writes a
@@ -283,21 +317,25 @@ def _recv_unit(n: int, sh: int, v: int, o: int, c: int) -> int:
 
 
 def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, max_steps: Optional[int] = None,
-               redop: str = "sum", time_limit: float = 20.0, check: bool = True) -> SynthesisResult:
-    """Synthesise a schedule for `collective` in {"allgather", "reduce_scatter", "allreduce", "alltoall"} moving `nbytes` per
-    rank (all-gather: bytes each rank contributes; reduce-scatter / all-reduce: bytes of the full vector; all-to-all:
-    bytes of a rank's whole input, i.e. n blocks)."""
+               redop: str = "sum", time_limit: float = 20.0, check: bool = True, root: int = 0) -> SynthesisResult:
+    """Synthesise a schedule for `collective` in {"allgather", "reduce_scatter", "allreduce", "alltoall", "broadcast"}
+    moving `nbytes` per rank (all-gather: bytes each rank contributes; reduce-scatter / all-reduce: bytes of the full
+    vector; all-to-all: bytes of a rank's whole input, i.e. n blocks; broadcast: bytes of ``root``'s vector, which
+    travels in ``chunks`` pieces -- with as many pieces as ranks the solver finds the scatter + all-gather form)."""
     n = topo.n
-    if collective not in ("allgather", "reduce_scatter", "allreduce", "alltoall"):
+    if collective not in ("allgather", "reduce_scatter", "allreduce", "alltoall", "broadcast"):
         raise ValueError("synthesize: unsupported collective")
-    shard_bytes = nbytes if collective == "allgather" else nbytes / n
+    if not 0 <= root < n:
+        raise ValueError("synthesize: root is not a rank of the topology")
+    shard_bytes = nbytes if collective in ("allgather", "broadcast") else nbytes / n
     chunk_bytes = shard_bytes / chunks
     symmetric = topo.rotation_symmetric
     result = None
     steps_try = [max_steps] if max_steps else list(range(1, n + 1))
     best = None
     for S in steps_try:
-        sends, res = _solve_allgather(topo, chunks, S, chunk_bytes, symmetric, time_limit, alltoall=collective == "alltoall")
+        sends, res = _solve_allgather(topo, chunks, S, chunk_bytes, symmetric, time_limit, alltoall=collective == "alltoall",
+                                      only_owner=root if collective == "broadcast" else None)
         if sends is None:
             continue
         obj = float(res.fun) * 1e-6
@@ -319,6 +357,9 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
     elif collective == "alltoall":
         ir = _build_alltoall_ir(n, chunks, sends, name)
         total = obj
+    elif collective == "broadcast":
+        ir = _build_broadcast_ir(n, chunks, sends, name, root)
+        total = obj
     else:
         ir = _compose_allreduce(n, chunks, sends, name, redop)
         total = 2 * obj
@@ -329,6 +370,8 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
     lb = topo.alpha + (n - 1) * shard_bytes / min(min(topo.ingress_bw), min(topo.egress_bw))
     if collective == "allreduce":
         lb *= 2
+    if collective == "broadcast":       # the vector has to leave the root and to enter every other rank once
+        lb = topo.alpha + shard_bytes / min(topo.egress_bw[root], min(b for r, b in enumerate(topo.ingress_bw) if r != root))
     return SynthesisResult(ir, total, len(sends), [], sends, str(res.message), lb)
 
 

@@ -283,3 +283,45 @@ def test_topology_cache_measures_once_per_host(tmp_path):
     assert len(calls) == 2
     (tmp_path / "topology_boot_1_4.json").write_text("{broken")
     assert cache.load("boot-1", 4) is None                # a damaged file reads as a miss
+
+
+def test_broadcast_in_pieces_becomes_scatter_then_allgather():
+    """One piece can only be relayed along a tree; with as many pieces as ranks the solver finds the two-step form in
+    which the root's port carries the vector once."""
+    from pccl_b200.lang import relaunch_hazards
+    topo = Topology.nvswitch(4)
+    nbytes = 64 << 20
+    tree = synthesize("broadcast", topo, nbytes, chunks=1, root=1)
+    assert tree.steps_used == 2 and [len(s) for s in tree.sends] == [1, 2]          # binomial: 1 -> a, then 1 -> b and a -> c
+    assert all(o == 1 for st in tree.sends for (o, _c, _u, _v) in st)
+    pieces = synthesize("broadcast", topo, nbytes, chunks=4, root=1)
+    assert pieces.steps_used == 2 and len(pieces.sends[0]) == 3 and len(pieces.sends[1]) == 9
+    assert all(u == 1 for (_o, _c, u, _v) in pieces.sends[0])                       # step one: the root hands out pieces
+    assert pieces.objective_seconds < 0.8 * tree.objective_seconds
+    assert pieces.lower_bound_seconds <= pieces.objective_seconds
+    for r in (tree, pieces):
+        assert verify(r.ir).ok and relaunch_hazards(r.ir) == [] and check_lowered_deadlock_free(lower(r.ir))
+    with pytest.raises(ValueError):
+        synthesize("broadcast", topo, nbytes, root=4)
+
+
+def _run_synth_broadcast(rank, world, port):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.synth import Topology, synthesize
+    ir = synthesize("broadcast", Topology.nvswitch(world), 1 << 20, chunks=world, root=2).ir
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("b", ir)
+    errs = []
+    for it in range(3):
+        x = torch.arange(4099, dtype=torch.float32) + 100 * rank + it
+        y = torch.zeros(4099)
+        e.exeOp("b", x, y)
+        errs.append((y - (torch.arange(4099, dtype=torch.float32) + 200 + it)).abs().max().item())
+    e.exitCluster()
+    return max(errs)
+
+
+def test_synthesised_broadcast_runs_on_cpu_ranks():
+    res = run_ranks(_run_synth_broadcast, 4, env={"PCCL_WORKSPACE_MB": "16"}, timeout=180)
+    assert all(v == 0.0 for v in res.values()), res
