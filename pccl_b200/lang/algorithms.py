@@ -18,7 +18,7 @@ Conventions
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 from .ir import Chunk, CollectiveIR, Device, DeviceType, PrimitiveOpType
 

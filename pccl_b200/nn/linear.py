@@ -7,7 +7,6 @@ copy.  Operands are never transposed in memory: dx and dW use the kernel's MN-ma
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -11,8 +11,6 @@ the gathered activations that the forward kernels leave behind.
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
 import torch.nn as nn
 

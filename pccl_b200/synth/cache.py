@@ -8,7 +8,7 @@ import json
 import os
 from typing import Optional
 
-from ..lang import CollectiveIR, to_schedule
+from ..lang import to_schedule
 from .milp import synthesize
 from .topology import Topology
 

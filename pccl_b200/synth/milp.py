@@ -30,7 +30,7 @@ import numpy as np
 from scipy.optimize import Bounds, LinearConstraint, milp
 from scipy.sparse import lil_matrix
 
-from ..lang import Chunk, CollectiveIR, Device, DeviceType, Link, verify
+from ..lang import Chunk, CollectiveIR, Device, DeviceType, verify
 from ..lang.algorithms import allgather_conditions, allreduce_conditions, alltoall_conditions, reduce_scatter_conditions
 from .topology import Topology
 

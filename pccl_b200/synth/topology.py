@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import hashlib
 import json
-from dataclasses import dataclass, field, field
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 

@@ -1,7 +1,6 @@
 """Failure detection and elastic membership on CPU ranks.  Every failure is made on the host: a rank
 that exits, a rank whose control connection is dropped, a rank that goes silent, a rank that never
 joins a collective.  No GPU takes part."""
-import os
 import time
 
 import pytest

@@ -1,6 +1,5 @@
 """Multi-process CPU ranks: lang -> JSON schedule -> C++ engine -> CPU executor over shm and TCP."""
 import json
-import os
 
 import pytest
 import torch

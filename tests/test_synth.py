@@ -4,7 +4,7 @@ import json
 
 import pytest
 
-from pccl_b200.lang import check_lowered_deadlock_free, lower, to_schedule, verify
+from pccl_b200.lang import check_lowered_deadlock_free, lower, verify
 from pccl_b200.synth import ScheduleCache, Topology, synthesize
 
 from _ranks import run_ranks
