@@ -116,6 +116,45 @@ def case_coll_fp8(eng, rank, world):
     return {"ok": True}
 
 
+def case_rooted(eng, rank, world):
+    """Rooted and point-to-point library programs through the interpreter kernel (ordinary device tensors: the data
+    travels through the engine's workspace).  Run on demand, it is not in the list of test_multigpu.py:
+    `python -m torch.distributed.run --nproc-per-node N tests/mp_worker.py rooted out.json`."""
+    from pccl_b200.ops import collectives as C
+    n = 48 * 1024 + 8
+    base = torch.arange(n, dtype=torch.float32, device="cuda")
+    mine = base + 1000 * rank
+    root = world - 1
+    for it in range(3):
+        for algo in ("direct", "tree", "scatter_allgather"):
+            t = mine + it
+            C.broadcast(eng, t, root=root, algo=algo, width=2)
+            torch.cuda.synchronize()
+            assert torch.equal(t, base + 1000 * root + it), f"broadcast {algo}"
+        out = torch.full((n,), -1.0, device="cuda")
+        C.reduce(eng, mine + it, out, root=root, channels=2)
+        torch.cuda.synchronize()
+        want = sum(base + 1000 * r + it for r in range(world)) if rank == root else torch.full((n,), -1.0, device="cuda")
+        assert torch.allclose(out, want, rtol=1e-6), "reduce"
+        big = torch.arange(n * world, dtype=torch.float32, device="cuda") + 7 * rank + it
+        part = torch.zeros(n, device="cuda")
+        C.scatter(eng, big, part, root=0)
+        allv = torch.full((n * world,), -1.0, device="cuda")
+        C.gather(eng, mine + it, allv, root=root)
+        got = torch.full((n,), -1.0, device="cuda")
+        C.send_recv(eng, mine + it, got, src=0, dst=world - 1)
+        nxt = torch.zeros(n, device="cuda")
+        C.ring_shift(eng, mine + it, nxt, shift=1)
+        torch.cuda.synchronize()
+        assert torch.equal(part, (torch.arange(n * world, dtype=torch.float32, device="cuda") + it)[rank * n:(rank + 1) * n]), "scatter"
+        want = torch.cat([base + 1000 * r + it for r in range(world)]) if rank == root else torch.full((n * world,), -1.0, device="cuda")
+        assert torch.equal(allv, want), "gather"
+        assert torch.equal(got, base + it if rank == world - 1 else torch.full((n,), -1.0, device="cuda")), "send_recv"
+        assert torch.equal(nxt, base + 1000 * ((rank - 1) % world) + it), "ring_shift"
+    eng.raise_on_status(0, "rooted programs")
+    return {"ok": True}
+
+
 def case_interp(eng, rank, world):
     """Lowered programs through the interpreter kernel, including the NVLS ones."""
     from pccl_b200.lang import build
