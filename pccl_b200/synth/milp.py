@@ -310,6 +310,42 @@ def _build_reduce_scatter_ir(n: int, chunks: int, sends, name: str, redop: str) 
     return ir
 
 
+def _build_reduce_ir(n: int, chunks: int, sends, name: str, redop: str, root: int) -> CollectiveIR:
+    """A broadcast schedule run backwards: where the broadcast sent piece c from u to v, v now hands its partial of
+    piece c to u, which folds it in; the root ends with the reduction of everybody's vector in its output.  Scratch:
+    block 0 holds a rank's running partials, block 1 + v the partials received from rank v."""
+    from ..lang import add_acknowledgements
+    U = chunks
+    ir = CollectiveIR(name, "reduce", U, redop, buffers={"input": U, "output": U, "scratch": (n + 1) * U})
+    ir.attrs["block_units"] = U
+    ir.attrs["root"] = root
+    for r in range(n):
+        ir.add_device(Device(r, DeviceType.CUDA))
+    ir.fully_connect()
+    everyone = set(range(n))
+    ir.set_precondition([Chunk({r}, r, U, 0, "input") for r in range(n)])
+    ir.set_postcondition([Chunk(everyone, root, U, 0, "output")])
+
+    def acc_chunk(c, d, ranks):
+        return Chunk(set(ranks), d, 1, c, "output") if d == root else Chunk(set(ranks), d, 1, c, "scratch", origin=c)
+    acc_op: Dict[Tuple[int, int], int] = {}
+    acc_set: Dict[Tuple[int, int], set] = {}
+    for d in range(n):
+        for c in range(U):
+            acc_op[(c, d)] = ir.copy(Chunk({d}, d, 1, c, "input"), acc_chunk(c, d, {d}), step=0, channel=c)
+            acc_set[(c, d)] = {d}
+    S = len(sends)
+    for rs, s in enumerate(reversed(range(S))):
+        for (_o, c, u, v) in sends[s]:
+            rslot = Chunk(set(acc_set[(c, v)]), u, 1, (1 + v) * U + c, "scratch", origin=c)
+            push = ir.copy(acc_chunk(c, v, acc_set[(c, v)]), rslot, deps=[acc_op[(c, v)]], step=1 + 2 * rs, channel=c)
+            merged = acc_set[(c, u)] | acc_set[(c, v)]
+            acc_op[(c, u)] = ir.reduce(rslot, acc_chunk(c, u, merged), deps=[push, acc_op[(c, u)]], step=2 + 2 * rs, channel=c)
+            acc_set[(c, u)] = merged
+    add_acknowledgements(ir)
+    return ir
+
+
 def _recv_unit(n: int, sh: int, v: int, o: int, c: int) -> int:
     """Scratch unit on a receiver for the partial of shard (o, c) sent by device v.  Scratch blocks
     (of `sh` units): [0, n) running partials per shard, [n, n + n*n) one receive slot per (sender, shard)."""
@@ -318,16 +354,17 @@ def _recv_unit(n: int, sh: int, v: int, o: int, c: int) -> int:
 
 def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, max_steps: Optional[int] = None,
                redop: str = "sum", time_limit: float = 20.0, check: bool = True, root: int = 0) -> SynthesisResult:
-    """Synthesise a schedule for `collective` in {"allgather", "reduce_scatter", "allreduce", "alltoall", "broadcast"}
-    moving `nbytes` per rank (all-gather: bytes each rank contributes; reduce-scatter / all-reduce: bytes of the full
+    """Synthesise a schedule for `collective` in {"allgather", "reduce_scatter", "allreduce", "alltoall", "broadcast",
+    "reduce"} (a rooted reduce is the broadcast's schedule run backwards) moving `nbytes` per rank (all-gather: bytes each rank contributes; reduce-scatter / all-reduce: bytes of the full
     vector; all-to-all: bytes of a rank's whole input, i.e. n blocks; broadcast: bytes of ``root``'s vector, which
     travels in ``chunks`` pieces -- with as many pieces as ranks the solver finds the scatter + all-gather form)."""
     n = topo.n
-    if collective not in ("allgather", "reduce_scatter", "allreduce", "alltoall", "broadcast"):
+    if collective not in ("allgather", "reduce_scatter", "allreduce", "alltoall", "broadcast", "reduce"):
         raise ValueError("synthesize: unsupported collective")
     if not 0 <= root < n:
         raise ValueError("synthesize: root is not a rank of the topology")
-    shard_bytes = nbytes if collective in ("allgather", "broadcast") else nbytes / n
+    rooted = collective in ("broadcast", "reduce")
+    shard_bytes = nbytes if (collective == "allgather" or rooted) else nbytes / n
     chunk_bytes = shard_bytes / chunks
     symmetric = topo.rotation_symmetric
     result = None
@@ -335,7 +372,7 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
     best = None
     for S in steps_try:
         sends, res = _solve_allgather(topo, chunks, S, chunk_bytes, symmetric, time_limit, alltoall=collective == "alltoall",
-                                      only_owner=root if collective == "broadcast" else None)
+                                      only_owner=root if rooted else None)
         if sends is None:
             continue
         obj = float(res.fun) * 1e-6
@@ -360,6 +397,9 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
     elif collective == "broadcast":
         ir = _build_broadcast_ir(n, chunks, sends, name, root)
         total = obj
+    elif collective == "reduce":
+        ir = _build_reduce_ir(n, chunks, sends, name, redop, root)
+        total = obj
     else:
         ir = _compose_allreduce(n, chunks, sends, name, redop)
         total = 2 * obj
@@ -370,7 +410,7 @@ def synthesize(collective: str, topo: Topology, nbytes: int, chunks: int = 1, ma
     lb = topo.alpha + (n - 1) * shard_bytes / min(min(topo.ingress_bw), min(topo.egress_bw))
     if collective == "allreduce":
         lb *= 2
-    if collective == "broadcast":       # the vector has to leave the root and to enter every other rank once
+    if rooted:                          # the vector has to leave (enter) the root and to enter (leave) every other rank once
         lb = topo.alpha + shard_bytes / min(topo.egress_bw[root], min(b for r, b in enumerate(topo.ingress_bw) if r != root))
     return SynthesisResult(ir, total, len(sends), [], sends, str(res.message), lb)
 

@@ -325,3 +325,38 @@ def _run_synth_broadcast(rank, world, port):
 def test_synthesised_broadcast_runs_on_cpu_ranks():
     res = run_ranks(_run_synth_broadcast, 4, env={"PCCL_WORKSPACE_MB": "16"}, timeout=180)
     assert all(v == 0.0 for v in res.values()), res
+
+
+def test_rooted_reduce_is_the_broadcast_run_backwards():
+    from pccl_b200.lang import relaunch_hazards
+    topo = Topology.nvswitch(4)
+    b = synthesize("broadcast", topo, 16 << 20, chunks=4, root=3)
+    r = synthesize("reduce", topo, 16 << 20, chunks=4, root=3)
+    assert r.steps_used == b.steps_used == 2 and abs(r.objective_seconds - b.objective_seconds) < 1e-9
+    assert r.ir.collective == "reduce" and r.ir.attrs["root"] == 3
+    assert verify(r.ir).ok and relaunch_hazards(r.ir) == [] and check_lowered_deadlock_free(lower(r.ir))
+    ring = synthesize("reduce", Topology.ring(4, 50.0), 1 << 20, chunks=2, root=0, redop="max")
+    assert verify(ring.ir).ok and ring.ir.redop == "max"
+
+
+def _run_synth_reduce(rank, world, port):
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.synth import Topology, synthesize
+    ir = synthesize("reduce", Topology.nvswitch(world), 1 << 20, chunks=world, root=1).ir
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("r", ir)
+    errs = []
+    for it in range(3):
+        x = torch.arange(4099, dtype=torch.float32) + 100 * rank + it
+        y = torch.full((4099,), -5.0)
+        e.exeOp("r", x, y, width=2)
+        want = sum(torch.arange(4099, dtype=torch.float32) + 100 * r + it for r in range(world)) if rank == 1 else torch.full((4099,), -5.0)
+        errs.append((y - want).abs().max().item())
+    e.exitCluster()
+    return max(errs)
+
+
+def test_synthesised_reduce_runs_on_cpu_ranks():
+    res = run_ranks(_run_synth_reduce, 4, env={"PCCL_WORKSPACE_MB": "16"}, timeout=180)
+    assert all(v == 0.0 for v in res.values()), res
