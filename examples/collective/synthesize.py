@@ -20,15 +20,17 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--topology", choices=["nvswitch", "ring"], default="nvswitch")
     ap.add_argument("--world", type=int, default=8)
-    ap.add_argument("--collective", choices=["allreduce", "reduce_scatter", "allgather", "alltoall"], default="allreduce")
+    ap.add_argument("--collective", choices=["allreduce", "reduce_scatter", "allgather", "alltoall", "broadcast", "reduce"], default="allreduce")
     ap.add_argument("--mbytes", type=float, default=64.0)
-    ap.add_argument("--chunks", type=int, default=1)
+    ap.add_argument("--chunks", type=int, default=1, help="pieces per shard (broadcast / reduce: pieces of the vector; try --chunks = --world)")
+    ap.add_argument("--root", type=int, default=0, help="broadcast / reduce only")
     ap.add_argument("--out", default="")
     ap.add_argument("--cache-dir", default="")
     a = ap.parse_args()
     topo = Topology.nvswitch(a.world) if a.topology == "nvswitch" else Topology.ring(a.world)
     nbytes = int(a.mbytes * (1 << 20))
-    res = synthesize(a.collective, topo, nbytes, chunks=a.chunks, time_limit=20.0)
+    rooted = {"root": a.root} if a.collective in ("broadcast", "reduce") else {}
+    res = synthesize(a.collective, topo, nbytes, chunks=a.chunks, time_limit=20.0, **rooted)
     doc = to_schedule(res.ir)
     assert check_lowered_deadlock_free(doc["lowered"])
     report = {"program": res.ir.name, "steps": res.steps_used, "transfers_per_step": [len(s) for s in res.sends],
@@ -37,8 +39,8 @@ def main():
               "links_in_cluster": len(Cluster.from_topology(topo).links)}
     if a.cache_dir:                         # the on-disk cache that a trainer would consult at start-up
         cache = ScheduleCache(a.cache_dir)
-        cache.get_or_synthesize(a.collective, topo, nbytes, chunks=a.chunks)
-        cache.get_or_synthesize(a.collective, topo, nbytes, chunks=a.chunks)
+        cache.get_or_synthesize(a.collective, topo, nbytes, chunks=a.chunks, **rooted)
+        cache.get_or_synthesize(a.collective, topo, nbytes, chunks=a.chunks, **rooted)
         report["cache_hits"], report["cache_misses"] = cache.hits, cache.misses
     if a.out:
         with open(a.out, "w") as f:

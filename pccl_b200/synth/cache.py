@@ -34,15 +34,17 @@ class ScheduleCache:
     def size_bucket(nbytes: int) -> int:
         return max(0, int(nbytes).bit_length() - 1)        # floor(log2)
 
-    def key(self, collective: str, topo: Topology, nbytes: int, chunks: int) -> str:
+    def key(self, collective: str, topo: Topology, nbytes: int, chunks: int, root: Optional[int] = None) -> str:
         text = f"{collective}|{topo.n}|{self.size_bucket(nbytes)}|{chunks}|{topo.fingerprint()}"
+        if root is not None:                 # rooted collectives: one schedule per root
+            text += f"|root{root}"
         return f"{_fnv1a(text):016x}"
 
     def path(self, key: str) -> str:
         return os.path.join(self.dir, f"{key}.json")
 
     def get_or_synthesize(self, collective: str, topo: Topology, nbytes: int, chunks: int = 1, **kw) -> dict:
-        k = self.key(collective, topo, nbytes, chunks)
+        k = self.key(collective, topo, nbytes, chunks, kw.get("root") if collective in ("broadcast", "reduce") else None)
         p = self.path(k)
         if os.path.exists(p):
             self.hits += 1

@@ -118,6 +118,11 @@ def test_schedule_cache_roundtrip(tmp_path):
     c = cache.get_or_synthesize("reduce_scatter", Topology.ring(4), 3 << 20)
     assert cache.misses == 2 and c["name"] != a["name"]
     assert json.loads(json.dumps(a))["lowered"]["num_ranks"] == 4
+    # rooted collectives: one entry per root
+    r1 = cache.get_or_synthesize("broadcast", topo, 1 << 20, root=1)
+    r2 = cache.get_or_synthesize("broadcast", topo, 1 << 20, root=2)
+    assert cache.misses == 4 and r1["attrs"]["root"] == 1 and r2["attrs"]["root"] == 2
+    assert cache.get_or_synthesize("broadcast", topo, 1 << 20, root=1) == r1 and cache.hits == 2
 
 
 def _run_synth(rank, world, port, coll, topo_kind):
