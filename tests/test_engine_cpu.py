@@ -419,3 +419,31 @@ def test_rooted_collectives_through_the_ops_api_on_cpu_ranks():
         class _E:
             world = 4
         C.scatter(_E(), torch.zeros(7), torch.zeros(2))
+
+
+def _traced_rank(rank, world, port):
+    import torch
+    from pccl_b200.engine import Engine, LaunchEnvironments
+    from pccl_b200.lang import DeviceType, build
+    LaunchEnvironments.setOverride("PCCL_TRACE", "1")
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("ring_allreduce", world, device_type=DeviceType.CPU))
+    x = torch.ones(4096); y = torch.zeros(4096)
+    e.exeOp("ar", x, y)
+    doc = e.trace()
+    e.exitCluster()
+    return doc
+
+
+def test_traces_of_all_ranks_merge_into_one_document(tmp_path):
+    from pccl_b200.utils.trace import merge_traces, summarize
+    res = run_ranks(_traced_rank, 2, env={"PCCL_WORKSPACE_MB": "8"})
+    merged = merge_traces([res[0], res[1]], out=str(tmp_path / "all.json"), align=True)
+    ev = merged["traceEvents"]
+    assert {e["pid"] for e in ev} == {0, 1}
+    assert sorted(e["args"]["name"] for e in ev if e["ph"] == "M") == ["rank 0", "rank 1"]
+    for pid in (0, 1):
+        assert min(e["ts"] for e in ev if e["ph"] == "X" and e["pid"] == pid) == 0.0
+    stats = summarize(str(tmp_path / "all.json"))
+    assert stats["COPY"]["count"] >= 4 and stats["REDUCE"]["count"] == 2 and stats["REDUCE"]["bytes"] == 2 * 8192
+    assert stats["WAIT"]["bytes"] == 0 and stats["COPY"]["gbs"] > 0
