@@ -155,6 +155,29 @@ def case_rooted(eng, rank, world):
     return {"ok": True}
 
 
+def case_trace(eng, rank, world):
+    """Device-side instruction trace of the interpreter kernel.  Run on demand with PCCL_TRACE=1 in the environment
+    (the engine reads it when it is initialised): `PCCL_TRACE=1 python -m torch.distributed.run --nproc-per-node N
+    tests/mp_worker.py trace out.json`."""
+    from pccl_b200.lang import build
+    from pccl_b200.utils.trace import summarize
+    eng.regOp("traced_ar", build("direct_allreduce", world, channels=2))
+    n = 1 << 20
+    x = eng.symmetric_tensor((n,), torch.float32); y = eng.symmetric_tensor((n,), torch.float32)
+    x.fill_(float(rank + 1))
+    torch.cuda.synchronize(); dist.barrier()
+    eng.exeOp("traced_ar", x, y, width=2)
+    torch.cuda.synchronize()
+    assert torch.all(y == world * (world + 1) / 2)
+    doc = eng.trace()
+    ev = [e for e in doc["traceEvents"] if e["ph"] == "X"]
+    assert ev, "no device stamps came back (was PCCL_TRACE=1 set before the engine was initialised?)"
+    assert all(e["dur"] >= 0 and e["pid"] == rank for e in ev)
+    stats = summarize(doc)
+    assert stats["REDUCE"]["count"] >= 1 and stats["COPY"]["bytes"] > 0
+    return {"events": len(ev), "copy_gbs": stats["COPY"]["gbs"]}
+
+
 def case_interp(eng, rank, world):
     """Lowered programs through the interpreter kernel, including the NVLS ones."""
     from pccl_b200.lang import build
