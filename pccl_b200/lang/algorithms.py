@@ -898,6 +898,41 @@ def reduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = 
     return ir
 
 
+def reduce_scatter_gather_reduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, redop: str = "sum",
+                                 root: int = 0) -> CollectiveIR:
+    """Rooted reduction of a long vector in two steps: piece d is reduced on rank d (every rank sends it its
+    contribution), then every rank hands its reduced piece to the root.  Every port carries the vector about once,
+    where the tree form sends the whole vector log2(n) times in a row.  Scratch: block 0 holds a rank's own reduced
+    piece (on the root: the pieces that come back), block 1 + r the contribution received from rank r."""
+    _check_rank(n, root=root)
+    sh = channels
+    U = n * sh
+    ir = _new(f"reduce_scatter_gather_reduce_n{n}_c{channels}_r{root}", "reduce", n, U,
+              {"input": U, "output": U, "scratch": (n + 1) * U}, device_type, redop)
+    ir.attrs["root"] = root
+    ir.set_precondition([Chunk({r}, r, U, 0, "input") for r in range(n)])
+    ir.set_postcondition([Chunk(_all(n), root, U, 0, "output")])
+    for ch in range(channels):
+        for d in range(n):
+            u = d * sh + ch
+
+            def acc(ranks):
+                return Chunk(set(ranks), d, 1, u, "output") if d == root else Chunk(set(ranks), d, 1, u, "scratch", origin=u)
+            last = ir.copy(Chunk({d}, d, 1, u, "input"), acc({d}), step=0, channel=ch)
+            have = {d}
+            for k in range(1, n):
+                r = (d + k) % n
+                slot = Chunk({r}, d, 1, (1 + r) * U + u, "scratch", origin=u)
+                push = ir.copy(Chunk({r}, r, 1, u, "input"), slot, step=0, channel=ch)
+                last = ir.reduce(slot, acc(have | {r}), deps=[push, last], step=k, channel=ch)
+                have = have | {r}
+            if d != root:
+                back = ir.copy(acc(have), Chunk(set(have), root, 1, u, "scratch", origin=u), deps=[last], step=n, channel=ch)
+                ir.copy(Chunk(set(have), root, 1, u, "scratch", origin=u), Chunk(set(have), root, 1, u, "output"),
+                        deps=[back], step=n + 1, channel=ch)
+    return ir
+
+
 def scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA, root: int = 0) -> CollectiveIR:
     """Block d of ``root``'s input becomes rank d's output."""
     _check_rank(n, root=root)
@@ -970,6 +1005,7 @@ ALGORITHMS = {
     "broadcast": broadcast,
     "scatter_allgather_broadcast": scatter_allgather_broadcast,
     "reduce": reduce,
+    "reduce_scatter_gather_reduce": reduce_scatter_gather_reduce,
     "scatter": scatter,
     "gather": gather,
 }

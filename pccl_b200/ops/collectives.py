@@ -196,10 +196,19 @@ def broadcast(eng: Engine, t: torch.Tensor, root: int = 0, out: Optional[torch.T
     return out
 
 
-def reduce(eng: Engine, inp: torch.Tensor, out: torch.Tensor, root: int = 0, op: str = "sum", channels: int = 1,
-           width: int = 1, lane: int = 0, stream=None) -> torch.Tensor:
-    """The reduction of every rank's ``inp`` lands in ``out`` of rank ``root``; the other ranks' ``out`` is not written."""
-    _run_library_op(eng, _library_op(eng, "reduce", root=root, redop=op, channels=channels), inp, out, width, lane, stream)
+def reduce(eng: Engine, inp: torch.Tensor, out: torch.Tensor, root: int = 0, op: str = "sum", algo: str = "tree",
+           channels: int = 1, width: int = 1, lane: int = 0, stream=None) -> torch.Tensor:
+    """The reduction of every rank's ``inp`` lands in ``out`` of rank ``root``; the other ranks' ``out`` is not written.
+    ``algo``: ``"tree"`` (binomial, log2(world) hops of the whole vector: small messages), ``"pieces"`` (piece d is reduced
+    on rank d and handed to the root: long vectors), or ``"auto"`` (the cheaper of the two by the cost model)."""
+    if algo == "auto":
+        from ..synth import Topology, choose
+        ranked = choose("reduce", Topology.nvswitch(eng.world), inp.numel() * inp.element_size(), channels=channels, root=root)
+        algo = "pieces" if ranked and ranked[0][0] == "reduce_scatter_gather_reduce" else "tree"
+    if algo not in ("tree", "pieces"):
+        raise ValueError(f"reduce: unknown algo {algo!r}")
+    name = _library_op(eng, "reduce" if algo == "tree" else "reduce_scatter_gather_reduce", root=root, redop=op, channels=channels)
+    _run_library_op(eng, name, inp, out, width, lane, stream)
     return out
 
 

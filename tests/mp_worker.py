@@ -131,11 +131,12 @@ def case_rooted(eng, rank, world):
             C.broadcast(eng, t, root=root, algo=algo, width=2)
             torch.cuda.synchronize()
             assert torch.equal(t, base + 1000 * root + it), f"broadcast {algo}"
-        out = torch.full((n,), -1.0, device="cuda")
-        C.reduce(eng, mine + it, out, root=root, channels=2)
-        torch.cuda.synchronize()
-        want = sum(base + 1000 * r + it for r in range(world)) if rank == root else torch.full((n,), -1.0, device="cuda")
-        assert torch.allclose(out, want, rtol=1e-6), "reduce"
+        for algo in ("tree", "pieces"):
+            out = torch.full((n,), -1.0, device="cuda")
+            C.reduce(eng, mine + it, out, root=root, algo=algo, channels=2)
+            torch.cuda.synchronize()
+            want = sum(base + 1000 * r + it for r in range(world)) if rank == root else torch.full((n,), -1.0, device="cuda")
+            assert torch.allclose(out, want, rtol=1e-6), f"reduce {algo}"
         big = torch.arange(n * world, dtype=torch.float32, device="cuda") + 7 * rank + it
         part = torch.zeros(n, device="cuda")
         C.scatter(eng, big, part, root=0)

@@ -238,7 +238,7 @@ def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
     ("hierarchical_allgather", {"per_host": 2}),
     ("send_recv", {"src": 2, "dst": 1}), ("broadcast", {"root": 1}), ("broadcast", {"root": 3, "tree": True}),
     ("reduce", {"root": 2}), ("scatter", {"root": 1}), ("gather", {"root": 3}),
-    ("scatter_allgather_broadcast", {"root": 2})])
+    ("scatter_allgather_broadcast", {"root": 2}), ("reduce_scatter_gather_reduce", {"root": 1})])
 def test_algorithms_on_cpu_ranks_shm(algo, kwargs):
     res = run_ranks(_collective_rank, 4, args=(algo, "shm", "float32", 1000 + 17, 2, 2, kwargs),
                     env={"PCCL_WORKSPACE_MB": "16"})
@@ -384,10 +384,11 @@ def _rooted_api_rank(rank, world, port):
             t = mine.clone() + it
             C.broadcast(e, t, root=1, algo=algo)
             errs["broadcast_" + algo] = (t - (torch.arange(n) + 1000 + it)).abs().max().item()
-        out = torch.full((n,), -1.0)
-        C.reduce(e, mine + it, out, root=2)
-        want = sum(torch.arange(n, dtype=torch.float32) + 1000 * r + it for r in range(world)) if rank == 2 else torch.full((n,), -1.0)
-        errs["reduce"] = (out - want).abs().max().item()
+        for algo in ("tree", "pieces", "auto"):
+            out = torch.full((n,), -1.0)
+            C.reduce(e, mine + it, out, root=2, algo=algo)
+            want = sum(torch.arange(n, dtype=torch.float32) + 1000 * r + it for r in range(world)) if rank == 2 else torch.full((n,), -1.0)
+            errs["reduce_" + algo] = (out - want).abs().max().item()
         big = torch.arange(n * world, dtype=torch.float32) + 7 * rank + it
         part = torch.zeros(n)
         C.scatter(e, big, part, root=0)
@@ -412,7 +413,7 @@ def test_rooted_collectives_through_the_ops_api_on_cpu_ranks():
     for r in range(3):
         errs, ops = res[r]
         assert max(errs.values()) == 0, (r, errs)
-        assert len(ops) == 7            # one registration per (program, arguments), reused by the second round and by "auto"
+        assert len(ops) == 8            # one registration per (program, arguments), reused by the second round and by "auto"
     with pytest.raises(ValueError):
         from pccl_b200.ops import collectives as C
 
