@@ -33,20 +33,36 @@ def wait_for_resize(engine: Engine, survivors: int, timeout_s: float = 10.0) -> 
 
 
 def recover(engine: Engine, next_master: str, programs: Dict[str, ProgramFactory], *, device: Optional[str] = None,
-            heap_bytes: int = 0, timeout_s: float = 10.0) -> Engine:
+            heap_bytes: int = 0, timeout_s: float = 10.0, spares: int = 0) -> Engine:
     """Called by every survivor once ``engine.alive_ranks()`` has shrunk.  Returns the engine of the new world with
     ``programs`` registered (``{name: factory(new_world)}``).  ``next_master`` is the endpoint ("host:port") on which
-    the new rank 0 serves the new cluster; the old cluster is left."""
+    the new rank 0 serves the new cluster; the old cluster is left.
+
+    ``spares``: processes that stood by and now take the ranks after the survivors' (``join_as_spare``), so that a job
+    can go on at its old size: the replacement that the reference's ReplaceOld / BeReplaced events stand for
+    (include/cluster/daemon.h:16-25), done by forming the new world instead of patching the old one."""
     alive = engine.alive_ranks()
     if engine.rank not in alive:
         raise PcclError("recover: this rank is not among the survivors")
     mapping = wait_for_resize(engine, len(alive), timeout_s)
-    new_rank, new_world = mapping[engine.rank], len(mapping)
+    new_rank, new_world = mapping[engine.rank], len(mapping) + int(spares)
     dev = device or engine.device
     engine.exitCluster()
     fresh = Engine(new_rank, new_world)
     fresh.initEngine(dev, heap_bytes) if heap_bytes else fresh.initEngine(dev)
     fresh.joinCluster(next_master)
+    for name, factory in programs.items():
+        fresh.regOp(name, factory(new_world))
+    return fresh
+
+
+def join_as_spare(next_master: str, new_rank: int, new_world: int, programs: Dict[str, ProgramFactory], *,
+                  device: str = "auto", heap_bytes: int = 0, timeout_ms: int = 60000) -> Engine:
+    """The stand-by's side of ``recover(..., spares=k)``: wait for the new world's master (the connection is retried
+    until ``timeout_ms``), join as ``new_rank`` (survivors come first, spares after them) and register the programs."""
+    fresh = Engine(new_rank, new_world)
+    fresh.initEngine(device, heap_bytes) if heap_bytes else fresh.initEngine(device)
+    fresh.joinCluster(next_master, timeout_ms)
     for name, factory in programs.items():
         fresh.regOp(name, factory(new_world))
     return fresh
@@ -62,4 +78,4 @@ def cached_schedule(collective: str, nbytes: int, topology_of: Callable[[int], o
     return factory
 
 
-__all__ = ["recover", "wait_for_resize", "cached_schedule"]
+__all__ = ["recover", "join_as_spare", "wait_for_resize", "cached_schedule"]

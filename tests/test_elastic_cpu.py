@@ -164,3 +164,40 @@ def test_join_times_out_when_a_rank_is_missing():
         e.joinCluster(f"127.0.0.1:{free_port()}", 700)
     assert time.time() - t0 < 5
     e.exitCluster()
+
+
+def _recover_with_spare(rank, nprocs, port, next_port):
+    """Three ranks and a stand-by process; rank 1 leaves, the stand-by takes the last rank of a new world of three."""
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.engine.elastic import join_as_spare, recover
+    from pccl_b200.lang import DeviceType, build
+    world = nprocs - 1
+    programs = {"ar": lambda n: build("direct_allreduce", n, device_type=DeviceType.CPU)}
+    value = float(10 * (rank + 1))
+    x = torch.full((512,), value); y = torch.empty_like(x)
+    if rank == world:                        # the stand-by: joins whenever the new world's master appears
+        e2 = join_as_spare(f"127.0.0.1:{next_port}", world - 1, world, programs, device="cpu", timeout_ms=60000)
+    else:
+        e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+        e.regOp("ar", programs["ar"](world))
+        e.exeOp("ar", x, y)
+        assert y[0].item() == 10.0 + 20.0 + 30.0
+        if rank == 1:
+            e.exitCluster()
+            return {"left": True}
+        assert e.wait_for_departure(1, 8000)
+        e2 = recover(e, f"127.0.0.1:{next_port}", programs, spares=1)
+    e2.exeOp("ar", x, y)
+    out = {"new_rank": e2.rank, "new_world": e2.world, "sum": y[0].item()}
+    e2.exitCluster()
+    return out
+
+
+def test_a_stand_by_process_takes_the_place_of_a_rank_that_left():
+    from _ranks import free_port
+    res = run_ranks(_recover_with_spare, 4, args=(free_port(),), timeout=120,
+                    env={"PCCL_WORKSPACE_MB": "8", "PCCL_WAIT_TIMEOUT_MS": "3000", "PCCL_HEARTBEAT_MS": "100", "PCCL_HEARTBEAT_MISSES": "5"})
+    assert res[1] == {"left": True}
+    assert [res[r]["new_rank"] for r in (0, 2, 3)] == [0, 1, 2] and all(res[r]["new_world"] == 3 for r in (0, 2, 3))
+    assert all(res[r]["sum"] == 10.0 + 30.0 + 40.0 for r in (0, 2, 3))       # old ranks 0 and 2, and the stand-by
