@@ -207,3 +207,15 @@ def test_verifier_rejects_a_sender_that_nothing_holds_back():
     # the library's one-way programs carry the acknowledgement
     for name in ("send_recv", "broadcast", "reduce", "scatter", "gather"):
         assert relaunch_hazards(build(name, 4)) == []
+
+
+def test_every_module_is_reachable_under_the_reference_package_name():
+    import importlib
+    import pccl
+    import pccl_b200.synth
+    assert importlib.import_module("pccl.synth") is pccl_b200.synth and pccl_b200.synth.__spec__.name == "pccl_b200.synth"
+    assert importlib.import_module("pccl.engine.elastic").join_as_spare is not None
+    assert importlib.import_module("pccl.synth.local_node").LocalNode is pccl_b200.synth.LocalNode
+    assert importlib.import_module("pccl.lang.chunk").CollectiveIR is pccl.lang.CollectiveIR      # the package's own files win
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("pccl.no_such_module")
