@@ -161,7 +161,7 @@ void emuProgram(const std::string& schedule_json, const std::vector<uint64_t>& h
       R.input_heap_off = p.remote_io ? heapOff(inputs.at(r)) : -1;
       R.output_heap_off = p.remote_io ? heapOff(p.in_place ? inputs.at(r) : outputs.at(r)) : -1;
       R.scratch_off = scratch_off;
-      for (int b = 0; b < BUF_COUNT; ++b) R.buf_bytes[b] = m.buf_bytes[b];
+      for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) R.buf_bytes[b] = m.buf_bytes[b];
       R.status = reinterpret_cast<uint32_t*>(status.at(r));
     }
     throwIfCuda(launchInterpreter(L, 256, reinterpret_cast<cudaStream_t>(stream)), "interpreter launch");

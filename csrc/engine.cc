@@ -270,6 +270,8 @@ void Engine::regOp(const std::string& name, const std::string& path_or_json) {
   size_t i = path_or_json.find_first_not_of(" \t\r\n");
   Json doc = (i != std::string::npos && path_or_json[i] == '{') ? Json::parse(path_or_json) : Json::parseFile(path_or_json);
   Program p = Program::fromJson(doc);
+  PCCL_DLOG_DEBUG("regOp '%s': %s for %d ranks, %d channels, %u signal slots", name.c_str(), p.collective.c_str(), p.world,
+                  p.channels, p.num_slots);
   std::lock_guard<std::mutex> g(mu_);
   if (ops_.count(name)) throw std::runtime_error("regOp: '" + name + "' is already registered");
   Op op;
@@ -344,6 +346,8 @@ std::vector<uint32_t> Engine::checkStatus(int lane) {
 int Engine::exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes,
                   const std::string& dtype, int width, int lane, uint64_t stream) {
   if (!initialized_) throw std::runtime_error("exeOp: call initEngine first");
+  PCCL_DLOG_TRACE("exeOp '%s': %llu bytes of %s, width %d, lane %d", name.c_str(), static_cast<unsigned long long>(in_bytes),
+                  dtype.c_str(), width, lane);
   Op* found = nullptr;
   {
     std::lock_guard<std::mutex> g(mu_);
@@ -410,7 +414,7 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   ctx.local[BUF_INPUT] = reinterpret_cast<char*>(in_ptr);
   ctx.local[BUF_OUTPUT] = reinterpret_cast<char*>(p.in_place ? in_ptr : out_ptr);
   ctx.local[BUF_SCRATCH] = heap_ + scratch_off;
-  for (int b = 0; b < BUF_COUNT; ++b) ctx.local_bytes[b] = m.buf_bytes[b];
+  for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) ctx.local_bytes[b] = m.buf_bytes[b];
   ctx.peer_scratch.assign(world_, nullptr);
   ctx.peer_signals.assign(world_, nullptr);
   for (int r = 0; r < world_; ++r) {
@@ -500,7 +504,7 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   if (p.remote_io && (R.input_heap_off < 0 || R.output_heap_off < 0))
     throw std::runtime_error("exeOp: this program lets peers touch the tensors, so both must come from the symmetric heap");
   R.scratch_off = lane * lane_bytes + (lane_launches_.at(lane)++ & 1) * half;
-  for (int b = 0; b < BUF_COUNT; ++b) R.buf_bytes[b] = c.m.buf_bytes[b];
+  for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) R.buf_bytes[b] = c.m.buf_bytes[b];
   R.status = reinterpret_cast<uint32_t*>(statusPtr(lane));
   size_t n_instr = 0;
   if (trace_) {

@@ -49,7 +49,7 @@ Program Program::fromJson(const Json& doc) {
   p.buf_units[BUF_INPUT] = bufs["input"].asInt(p.units);
   p.buf_units[BUF_OUTPUT] = bufs["output"].asInt(p.units);
   p.buf_units[BUF_SCRATCH] = bufs["scratch"].asInt(0);
-  for (int b = 0; b < BUF_COUNT; ++b)
+  for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b)
     if (p.buf_units[b] % p.block_units)
       throw std::runtime_error("schedule: buffer sizes must be multiples of block_units");
   const Json& low = doc["lowered"];
@@ -117,7 +117,7 @@ Materialized Program::materialize(int rank, uint64_t bb, int width) const {
   m.num_slots = num_slots * width;
   const uint64_t bu = static_cast<uint64_t>(block_units);
   const uint64_t ub = alignUp((bb + bu - 1) / bu, 16);
-  for (int b = 0; b < BUF_COUNT; ++b) m.buf_bytes[b] = static_cast<uint64_t>(buf_units[b]) / bu * bb;
+  for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) m.buf_bytes[b] = static_cast<uint64_t>(buf_units[b]) / bu * bb;
   auto start = [&](int64_t u) { return (u / bu) * bb + std::min<uint64_t>((u % bu) * ub, bb); };
   auto stop = [&](int64_t last) { return (last / bu) * bb + std::min<uint64_t>((last % bu + 1) * ub, bb); };
   m.streams.resize(static_cast<size_t>(channels) * width);
