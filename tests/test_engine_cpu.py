@@ -7,16 +7,25 @@ import torch
 from _ranks import run_ranks
 
 
-def _collective_rank(rank, world, port, algo, transport, dtype_name, n_elems, channels, width, kwargs):
-    import torch
+def _collective_rank(rank, world, port, algos, transport, dtype_name, n_elems, channels, width):
+    """Every (algorithm, arguments) of ``algos`` in one set of ranks: three launches each, against torch."""
     from pccl_b200.engine import Engine
-    from pccl_b200.lang import DeviceType, build
-    dtype = getattr(torch, dtype_name)
     e = Engine(rank, world)
     e.initEngine("cpu")
     e.joinCluster(f"127.0.0.1:{port}")
+    out = {}
+    for i, (algo, kwargs) in enumerate(algos):
+        out[f"{algo}{kwargs or ''}"] = _one_collective(e, f"op{i}", rank, world, algo, dtype_name, n_elems, channels, width, kwargs)
+    e.exitCluster()
+    return out
+
+
+def _one_collective(e, name, rank, world, algo, dtype_name, n_elems, channels, width, kwargs):
+    import torch
+    from pccl_b200.lang import DeviceType, build
+    dtype = getattr(torch, dtype_name)
     ir = build(algo, world, channels=channels, device_type=DeviceType.CPU, **kwargs)
-    e.regOp("op", ir)
+    e.regOp(name, ir)
     g = torch.Generator().manual_seed(0)
     coll = ir.collective
     per_rank = {"allreduce": n_elems, "reduce_scatter": n_elems * world, "allgather": n_elems,
@@ -32,7 +41,7 @@ def _collective_rank(rank, world, port, algo, transport, dtype_name, n_elems, ch
     for it in range(3):     # repeated launches exercise the epoch-counting signals and scratch halves
         x = (xs[rank].float() + it).to(dtype)
         y = torch.full((out_elems,), -777, dtype=dtype)
-        e.exeOp("op", x, y, width=width)
+        e.exeOp(name, x, y, width=width)
         full = [(v.float() + it).to(dtype).float() for v in xs]
         if coll == "allreduce":
             ref = torch.stack(full).sum(0)
@@ -54,8 +63,7 @@ def _collective_rank(rank, world, port, algo, transport, dtype_name, n_elems, ch
             ref = torch.cat(full) if rank == root else untouched
         errs.append((y.float() - ref).abs().max().item())
     st = e.stats()
-    e.exitCluster()
-    return {"err": max(errs), "launches": st["ops"]["op"]["launches"], "tcp": st.get("tcp_bytes_sent", 0)}
+    return {"err": max(errs), "launches": st["ops"][name]["launches"], "tcp": st.get("tcp_bytes_sent", 0)}
 
 
 def _baseline_rank(rank, world, port, transport):
@@ -230,28 +238,36 @@ def test_baseline_config_ring_allreduce_4m_fp32_world2_shm_and_tcp():
             assert (res[r][2] > 0) == (transport == "tcp")
 
 
-@pytest.mark.parametrize("algo,kwargs", [
+_SYMMETRIC = [
     ("ring_allreduce", {}), ("direct_allreduce", {}), ("oneshot_allreduce", {}), ("tree_allreduce", {}),
     ("direct_reduce_scatter", {}), ("direct_allgather", {}), ("ring_allgather", {}), ("ring_kv_rotation", {}),
     ("alltoall", {}), ("ulysses_alltoall", {}), ("ring_reduce_scatter", {}), ("recursive_doubling_allgather", {}),
     ("halving_doubling_allreduce", {}), ("hierarchical_allreduce", {"per_host": 2}),
-    ("hierarchical_allgather", {"per_host": 2}),
+    ("hierarchical_allgather", {"per_host": 2})]
+_ROOTED = [
     ("send_recv", {"src": 2, "dst": 1}), ("broadcast", {"root": 1}), ("broadcast", {"root": 3, "tree": True}),
     ("reduce", {"root": 2}), ("scatter", {"root": 1}), ("gather", {"root": 3}),
-    ("scatter_allgather_broadcast", {"root": 2}), ("reduce_scatter_gather_reduce", {"root": 1})])
-def test_algorithms_on_cpu_ranks_shm(algo, kwargs):
-    res = run_ranks(_collective_rank, 4, args=(algo, "shm", "float32", 1000 + 17, 2, 2, kwargs),
-                    env={"PCCL_WORKSPACE_MB": "16"})
-    for r, v in res.items():
-        assert v["err"] < 1e-4 and v["launches"] == 3, (algo, r, v)
+    ("scatter_allgather_broadcast", {"root": 2}), ("reduce_scatter_gather_reduce", {"root": 1})]
 
 
-@pytest.mark.parametrize("algo", ["ring_allreduce", "direct_reduce_scatter", "alltoall"])
-def test_algorithms_on_cpu_ranks_tcp_bf16(algo):
-    res = run_ranks(_collective_rank, 3, args=(algo, "tcp", "bfloat16", 4096 + 8, 1, 1, {}),
-                    env={"PCCL_WORKSPACE_MB": "16", "PCCL_TRANSPORT": "tcp"})
-    for r, v in res.items():
-        assert v["err"] <= 0.26 and v["tcp"] > 0, (algo, r, v)   # bf16 rounding of sums up to ~24
+@pytest.mark.parametrize("algos", [_SYMMETRIC, _ROOTED], ids=["symmetric", "rooted"])
+def test_algorithms_on_cpu_ranks_shm(algos):
+    """One set of four ranks runs the whole group, one program after the other (starting ranks is what costs time)."""
+    res = run_ranks(_collective_rank, 4, args=(algos, "shm", "float32", 1000 + 17, 2, 2),
+                    env={"PCCL_WORKSPACE_MB": "16"}, timeout=300)
+    for r, per_algo in res.items():
+        assert len(per_algo) == len(algos)
+        for label, v in per_algo.items():
+            assert v["err"] < 1e-4 and v["launches"] == 3, (label, r, v)
+
+
+def test_algorithms_on_cpu_ranks_tcp_bf16():
+    algos = [("ring_allreduce", {}), ("direct_reduce_scatter", {}), ("alltoall", {})]
+    res = run_ranks(_collective_rank, 3, args=(algos, "tcp", "bfloat16", 4096 + 8, 1, 1),
+                    env={"PCCL_WORKSPACE_MB": "16", "PCCL_TRANSPORT": "tcp"}, timeout=300)
+    for r, per_algo in res.items():
+        for label, v in per_algo.items():
+            assert v["err"] <= 0.26 and v["tcp"] > 0, (label, r, v)   # bf16 rounding of sums up to ~24
 
 
 def test_regop_accepts_file_and_rejects_garbage(tmp_path):
