@@ -141,6 +141,44 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
     return res
 
 
+def bench_rooted(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, iters: Optional[int] = None, root: int = 0) -> Dict:
+    """Broadcast or rooted reduce of a vector of `nbytes`: the library programs run by the interpreter kernel (every
+    form, best width) next to NCCL's.  Bandwidth is bytes of the vector over time."""
+    es = torch.empty((), dtype=dtype).element_size()
+    n = max(eng.world * 16 // es, nbytes // es // (eng.world * 16 // es) * (eng.world * 16 // es))
+    nbytes = n * es
+    if iters is None:
+        iters = 100 if nbytes <= (1 << 20) else (30 if nbytes <= (64 << 20) else 10)
+    n_slots = max(1, min(32, (256 << 20) // nbytes))            # rotate through more than the L2 holds
+    xs = [torch.ones(n, dtype=dtype, device="cuda") for _ in range(n_slots)]
+    ys = [torch.empty(n, dtype=dtype, device="cuda") for _ in range(n_slots)]
+    res = {"kind": kind, "dtype": str(dtype).replace("torch.", ""), "bytes": nbytes, "n_gpus": eng.world, "root": root}
+    forms = ("direct", "tree", "scatter_allgather") if kind == "broadcast" else ("tree", "pieces")
+    best = None
+    for form in forms:
+        for width in (4, 16):
+            if kind == "broadcast":
+                fn = lambda i, f=form, w=width: C.broadcast(eng, xs[i], root=root, out=ys[i], algo=f, channels=2, width=w)  # noqa: E731
+            else:
+                fn = lambda i, f=form, w=width: C.reduce(eng, xs[i], ys[i], root=root, algo=f, channels=2, width=w)  # noqa: E731
+            try:
+                ms = _time(fn, n_slots, iters, 3)
+            except Exception as e:  # noqa: BLE001 - a form that does not fit the workspace at this size is left out
+                if eng.rank == 0:
+                    print(f"# {kind} {form} width {width} at {nbytes} bytes: {type(e).__name__}: {e}", flush=True)
+                continue
+            if eng.check_status(0)[0] != 0:
+                continue
+            if best is None or ms < best[0]:
+                best = (ms, form, width)
+    if best is not None:
+        res["interp"] = {"us": best[0] * 1e3, "algbw_gbs": nbytes / (best[0] * 1e-3) / 1e9, "form": best[1], "width": best[2]}
+    nccl = (lambda i: dist.broadcast(xs[i], root)) if kind == "broadcast" else (lambda i: dist.reduce(xs[i], root))
+    ms = _time(nccl, n_slots, iters, 3)
+    res["nccl"] = {"us": ms * 1e3, "algbw_gbs": nbytes / (ms * 1e-3) / 1e9}
+    return res
+
+
 def quick_micro(eng: Engine) -> Dict:
     """Three all-reduce sizes, ours against NCCL; cheap enough to ride along with bench.py."""
     out = []
@@ -161,7 +199,7 @@ def main() -> None:
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
-    interp = "interp" in args.impls.split(",")
+    interp = "interp" in args.impls.split(",") or any(k in ("broadcast", "reduce") for k in args.kinds.split(","))
     os.environ.setdefault("PCCL_WORKSPACE_MB", "1024" if interp else "64")      # scratch of the direct programs
     eng = Engine(rank, world)
     eng.initEngine("cuda", heap_bytes=(2 * POOL_BYTES) + 4 * args.max_bytes + (512 << 20) + ((2 << 30) if interp else 0))
@@ -172,7 +210,12 @@ def main() -> None:
         for dn in args.dtypes.split(","):
             nbytes = args.min_bytes
             while nbytes <= args.max_bytes:
-                r = bench_size(eng, kind, dtypes[dn], nbytes, args.impls.split(","))
+                if kind in ("broadcast", "reduce"):
+                    if nbytes > (64 << 20):          # the programs stage through the workspace
+                        break
+                    r = bench_rooted(eng, kind, dtypes[dn], nbytes)
+                else:
+                    r = bench_size(eng, kind, dtypes[dn], nbytes, args.impls.split(","))
                 rows.append(r)
                 if rank == 0:
                     print(json.dumps(r), flush=True)
