@@ -48,6 +48,23 @@ class Cluster:
                 c.links.append(Link(a, b, bw, topo.alpha))
         return c
 
+    @staticmethod
+    def from_local_node(node=None, port_gbs: float = 770.0, pcie_gbs: float = 50.0) -> "Cluster":
+        """The GPUs of this host as a cluster: ``node`` is a ``pccl_b200.synth.LocalNode`` (probed when omitted); pairs
+        with peer access get the port rate, the others a host bridge's; each device carries its SM count as
+        ``compute_capability`` and nothing is measured.  Refuses a host without GPUs."""
+        if node is None:
+            from ..synth.local_node import LocalNode
+            node = LocalNode.probe()
+        topo = node.to_topology(port_gbs, pcie_gbs)
+        if topo is None:
+            raise ValueError("this host has no GPUs to make a cluster of")
+        c = Cluster.from_topology(topo)
+        c.name = f"host_{len(node.gpus)}gpu"
+        for d, g in zip(c.devices, node.gpus):
+            d.compute_capability = g.sm_count
+        return c
+
     # -- use -------------------------------------------------------------------------------------
     @property
     def world_size(self) -> int:

@@ -263,6 +263,10 @@ def test_local_node_from_a_stand_in_sysfs_and_cuda(tmp_path, monkeypatch):
     topo = node.to_topology()
     assert topo.name == "nvswitch4" and topo.rotation_symmetric
     assert LocalNode.from_json(node.to_json()) == node
+    from pccl_b200.lang import Cluster, build, verify
+    cl = Cluster.from_local_node(node)
+    assert cl.world_size == 4 and len(cl.links) == 12 and cl.devices[0].compute_capability == 148
+    verify(cl.apply(build("direct_allreduce", 4))).raise_if_failed()
     # two islands of two GPUs: peer access inside, a host bridge between
     split = LocalNode.probe(str(sysfs), str(proc), Cuda(lambda a, b: a // 2 == b // 2))
     t2 = split.to_topology(port_gbs=770.0, pcie_gbs=50.0)
@@ -270,6 +274,8 @@ def test_local_node_from_a_stand_in_sysfs_and_cuda(tmp_path, monkeypatch):
     # no GPU, no sysfs: still a description, no topology
     bare = LocalNode.probe(str(tmp_path / "nothing"), str(tmp_path / "nothing"), SimpleNamespace(device_count=lambda: 0))
     assert bare.gpus == [] and bare.to_topology() is None and bare.cpus >= 1 and bare.host_id == "unknown"
+    with pytest.raises(ValueError):
+        Cluster.from_local_node(bare)
 
 
 def test_topology_cache_measures_once_per_host(tmp_path):
