@@ -38,6 +38,8 @@ def test_host_code_is_clean_under_asan_and_ubsan():
            os.path.join(HERE, "test_engine_cpu.py") + "::test_two_ops_overlap_on_two_lanes_from_two_threads",
            os.path.join(HERE, "test_engine_cpu.py") + "::test_regop_accepts_file_and_rejects_garbage",
            os.path.join(HERE, "test_engine_cpu.py") + "::test_instruction_trace_is_chrome_trace_json",
+           os.path.join(HERE, "test_engine_cpu.py") + "::test_device_stamps_become_trace_events",
+           os.path.join(HERE, "test_engine_cpu.py") + "::test_a_rank_that_only_sends_cannot_overrun_the_receivers_workspace",
            os.path.join(HERE, "test_elastic_cpu.py") + "::test_survivors_run_in_the_resized_world",
            os.path.join(HERE, "test_elastic_cpu.py") + "::test_wait_on_a_rank_that_never_launches_times_out"]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500, cwd=ROOT)
