@@ -87,9 +87,34 @@ class Engine:
             if check:
                 verify(program).raise_if_failed()
             program = to_schedule(program)
+        elif check:
+            self._check_document(program)
         if isinstance(program, dict):
             program = json.dumps(program)
         self._e.regOp(name, program)
+
+    @staticmethod
+    def _check_document(program) -> None:
+        """A schedule document carries the op DAG it was lowered from: a sender that nothing holds back (unsafe to launch
+        repeatedly) is refused here too.  Anything that does not parse is left to the native loader's error message."""
+        from ..lang import VerificationError, relaunch_hazards
+        try:
+            doc = program
+            if isinstance(program, str):
+                if program.lstrip().startswith("{"):
+                    doc = json.loads(program)
+                else:
+                    with open(program) as f:
+                        doc = json.load(f)
+            if not isinstance(doc, dict) or not doc.get("ops"):
+                return
+            hazards = relaunch_hazards(CollectiveIR.from_dict(doc))
+        except (OSError, ValueError, KeyError, TypeError, AttributeError):
+            return
+        if hazards:
+            s_, r_ = hazards[0]
+            raise VerificationError(f"relaunch: rank {s_} writes into rank {r_}'s workspace but waits for nothing from it "
+                                    f"(pccl.lang.add_acknowledgements closes this; check=False registers the program as it is)")
 
     def prepareOp(self, name: str, width: int = 1) -> None:
         """Reserve the signal words of ``name`` at ``width`` now.  Only needed when several host threads launch

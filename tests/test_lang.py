@@ -219,3 +219,24 @@ def test_every_module_is_reachable_under_the_reference_package_name():
     assert importlib.import_module("pccl.lang.chunk").CollectiveIR is pccl.lang.CollectiveIR      # the package's own files win
     with pytest.raises(ModuleNotFoundError):
         importlib.import_module("pccl.no_such_module")
+
+
+def test_regop_checks_schedule_documents_too(tmp_path):
+    import json as _json
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import VerificationError, add_acknowledgements, to_schedule
+    ir = CollectiveIR("one_way", "send_recv", units=1, buffers={"input": 1, "output": 1, "scratch": 1})
+    ir.add_device(Device(0, DeviceType.CPU)); ir.add_device(Device(1, DeviceType.CPU)); ir.add_link(Link(0, 1))
+    ir.set_precondition([Chunk({0}, 0, 1, 0, "input")]); ir.set_postcondition([Chunk({0}, 1, 1, 0, "output")])
+    push = ir.copy(Chunk({0}, 0, 1, 0, "input"), Chunk({0}, 1, 1, 0, "scratch"))
+    ir.copy(Chunk({0}, 1, 1, 0, "scratch"), Chunk({0}, 1, 1, 0, "output"), deps=[push])
+    doc = to_schedule(ir)
+    path = tmp_path / "one_way.json"
+    path.write_text(_json.dumps(doc))
+    e = Engine(0, 2); e.initEngine("cpu")
+    for form in (doc, _json.dumps(doc), str(path)):
+        with pytest.raises(VerificationError, match="relaunch"):
+            e.regOp("bad", form)
+    e.regOp("as_it_is", doc, check=False)
+    assert add_acknowledgements(ir) == 1
+    e.regOp("good", to_schedule(ir))
