@@ -11,6 +11,14 @@ parameter all-gather -- tokens/s of the whole job.
 Rank 0 prints one JSON line.  `value` is timed on the device (CUDA events, max over ranks) with the
 batch already resident; `e2e` repeats the measurement through the public API with, every step, the
 host->device copy of that step's token ids from pinned memory and a device->host read of the loss.
+The same line carries
+  * `baseline_ddp`: the same model, batch and step count in plain PyTorch (torch.nn + DistributedDataParallel with
+    25 MB buckets + fused AdamW: NCCL, cuBLAS, cuDNN) measured in the same launch right after the framework's own
+    steps; `vs_baseline` is value / the recorded tokens/s of that baseline on this GPU pool (same N);
+  * `headline` (N >= 2): this library's headline metric -- all-reduce / reduce-scatter / all-gather bus GB/s at
+    1 MB .. 1 GB with algo="auto" next to NCCL, and the fused tensor-parallel all-gather+GEMM and
+    GEMM+reduce-scatter kernels next to NCCL+cuBLAS (sequential and stream-overlapped) at TP = N.
+`--impl ddp` times only the PyTorch baseline and prints it in the same format.
 `--impl reference` reports that the reference (napplesty/pccl) cannot be built or run.
 """
 from __future__ import annotations
@@ -37,12 +45,47 @@ def reference_arm() -> None:
         print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
+def ddp_arm(args, rank: int, world: int, local: int) -> None:
+    """The PyTorch baseline alone, in the framework's output format (impl = "ddp")."""
+    import torch
+    import torch.distributed as dist
+    from pccl_b200.baselines.ddp_gpt import measure
+    from pccl_b200.models import GPTConfig
+    from pccl_b200.utils import ClockSampler
+    cfg = GPTConfig.gpt_1p3b() if args.model == "gpt-1.3b" else GPTConfig.tiny()
+    sampler = ClockSampler(local).start()
+    r = measure(cfg, world, rank, local, args.batch, args.steps, args.warmup, precision=args.ddp_precision, zero=args.ddp_zero)
+    clocks = sampler.stop()
+    if rank == 0:
+        print(json.dumps({
+            "impl": "ddp", "metric": "tokens/s, data-parallel GPT-1.3B training in plain PyTorch (DistributedDataParallel, "
+            "25 MB buckets, fused AdamW)", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
+            "config": {"model": args.model, "params": r["params"], "global_batch": world * args.batch, "seq_len": cfg.seq_len,
+                       "parallelism": f"dp{world}", "precision": r["precision"], "optimizer": r["optimizer"], "wrapper": r["wrapper"],
+                       "l2": "no flush: each step streams >20 GB of weights/activations, far above the 126 MB L2"},
+            "e2e": {"value": r.get("e2e_tokens_per_s"), "unit": "tokens/s", "ms_per_step": r.get("e2e_ms_per_step"),
+                    "h2d_bytes_per_step": args.batch * (cfg.seq_len + 1) * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": 0, "model_tflops_per_gpu": cfg.flops_per_token() * r["tokens_per_s"] / world / 1e12,
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
+            "final_loss": r["final_loss"]}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ddp"])
+    ap.add_argument("--ddp-precision", default="bf16", choices=["bf16", "amp"],
+                    help="PyTorch baseline: bf16 parameters and optimizer state (fastest) or fp32 parameters under autocast")
+    ap.add_argument("--ddp-zero", action="store_true", help="PyTorch baseline: ZeroRedundancyOptimizer around fused AdamW")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the in-launch PyTorch DDP baseline")
+    ap.add_argument("--no-headline", action="store_true", help="skip the collective / fused-TP headline block at N > 1")
     ap.add_argument("--batch", type=int, default=int(os.environ.get("PCCL_BENCH_BATCH", "8")), help="sequences per GPU per step")
     ap.add_argument("--model", default="gpt-1.3b", choices=["gpt-1.3b", "tiny"])
     ap.add_argument("--bucket-mb", type=float, default=25.0)
@@ -70,6 +113,10 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=__import__("datetime").timedelta(seconds=180))
 
+    if args.impl == "ddp":
+        ddp_arm(args, rank, world, local)
+        return
+
     from pccl_b200.engine import Engine
     from pccl_b200.models import GPT, GPTConfig
     from pccl_b200.ops import check_status, launch_count
@@ -82,9 +129,11 @@ def main() -> None:
     n_params = sum(p.numel() for p in model.parameters())
     os.environ.setdefault("PCCL_WORKSPACE_MB", "256")
     eng = Engine(rank, world)
-    eng.initEngine("cuda", heap_bytes=int(4.4 * n_params) + (1 << 30))
+    # gradient + parameter buckets (2 x 2 bytes per parameter), and room for the headline block's 1 GB collectives
+    eng.initEngine("cuda", heap_bytes=max(int(4.4 * n_params) + (1 << 30), (3 << 30) if world > 1 else 0))
     if world > 1:
         eng.connect()
+    heap_mark = eng.symmetric_mark()
     dp = ShardedDataParallel(model, eng, lr=1e-4, bucket_mb=args.bucket_mb, comm_blocks=args.comm_blocks, algo=args.algo)
 
     B, S = args.batch, cfg.seq_len
@@ -144,14 +193,32 @@ def main() -> None:
     clocks = sampler.stop()
     check_status("end-to-end steps")
 
-    micro = None
-    if world > 1 and not args.no_micro:
+    grad_rs_schedule = dp.schedule
+    # ---- the library's headline metric and the PyTorch baseline, in the same launch -----------------------
+    # The training state is released first: its buckets give the symmetric heap back to the 1 GB collectives,
+    # and the baseline gets the device memory.
+    del dp, model, dev_batches, loss
+    import gc
+    gc.collect()                      # the wrapper's hook closures form cycles
+    torch.cuda.empty_cache()
+    eng.symmetric_reset(heap_mark)
+    head = None
+    if world > 1 and not args.no_headline and not args.no_micro:
         try:
-            from pccl_b200.bench_collectives import quick_micro
-            micro = quick_micro(eng)
-        except Exception as e:  # noqa: BLE001 - the headline number must still be printed
-            micro = {"error": f"{type(e).__name__}: {e}"}
+            from pccl_b200.bench_headline import headline
+            head = headline(eng)
+        except Exception as e:  # noqa: BLE001 - the training number must still be printed
+            head = {"error": f"{type(e).__name__}: {e}"}
+    baseline = None
+    if not args.no_baseline:
+        try:
+            from pccl_b200.baselines.ddp_gpt import measure
+            baseline = measure(cfg, world, rank, local, B, min(args.steps, 10), 3, precision=args.ddp_precision, e2e=False)
+        except Exception as e:  # noqa: BLE001
+            baseline = {"error": f"{type(e).__name__}: {e}"}
 
+    from pccl_b200.baselines.ddp_gpt import recorded
+    recorded_ddp = recorded(world) if args.model == "gpt-1.3b" and B == 8 else None
     tokens = world * B * S * args.steps
     value = tokens / (dev_ms / 1e3)
     e2e_value = tokens / (max(e2e_ms, wall_ms) / 1e3)
@@ -161,13 +228,14 @@ def main() -> None:
             "metric": "tokens/s, data-parallel GPT-1.3B training (bf16, 25 MB gradient buckets, reduce-scatter fused "
                       "with scale/cast and overlapped with backward)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / recorded_ddp) if recorded_ddp else None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": "gpt-1.3b (24 layers, d=2048, 16 heads, vocab 50257)" if args.model == "gpt-1.3b" else "tiny",
                        "params": n_params, "global_batch": world * B, "seq_len": S, "parallelism": f"dp{world}",
                        "bucket_mb": args.bucket_mb, "optimizer": "sharded AdamW (ZeRO-1) + parameter all-gather",
                        "transport": "nvls" if eng.has_nvls else ("p2p" if world > 1 else "local"),
-                       "grad_rs_schedule": dp.schedule,
+                       "grad_rs_schedule": grad_rs_schedule,
                        "l2": "no flush: each step streams >20 GB of weights/activations, far above the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": max(e2e_ms, wall_ms) / args.steps,
                     "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4},
@@ -176,12 +244,19 @@ def main() -> None:
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
             "final_loss": final_loss,
         }
-        if micro is not None:
-            out["micro"] = micro
+        out["baseline"] = {"what": "PyTorch DistributedDataParallel (NCCL, 25 MB buckets) + cuBLAS/cuDNN eager model + fused AdamW, "
+                                   "same model, batch and sequence length, on this GPU pool", "recorded_tokens_per_s": recorded_ddp,
+                           "source": "pccl_b200/baselines/ddp_gpt1p3b_b200.json (bench.py --impl ddp)"}
+        if baseline is not None:
+            out["baseline_ddp"] = baseline
+            if "tokens_per_s" in baseline:
+                out["baseline_ddp"]["ratio_ours_over_ddp_same_launch"] = value / baseline["tokens_per_s"]
+        if head is not None:
+            out["headline"] = head
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
-    del dp, model, eng          # unbind and unmap the symmetric heap while every rank is still here
+    del eng          # unbind and unmap the symmetric heap while every rank is still here
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -224,5 +224,12 @@ bool recvFd(int sock, int* fd_out, uint64_t* tag) {
   return true;
 }
 
+long peerUid(int sock) {
+  ucred cr{};
+  socklen_t len = sizeof(cr);
+  if (::getsockopt(sock, SOL_SOCKET, SO_PEERCRED, &cr, &len) != 0 || len != sizeof(cr)) return -1;
+  return static_cast<long>(cr.uid);
+}
+
 }  // namespace wire
 }  // namespace pccl

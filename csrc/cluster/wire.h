@@ -42,6 +42,7 @@ int unixListen(const std::string& abstract_name);
 int unixConnect(const std::string& abstract_name, int timeout_ms);
 bool sendFd(int sock, int fd_to_send, uint64_t tag);
 bool recvFd(int sock, int* fd_out, uint64_t* tag);
+long peerUid(int sock);      // user id of the process at the other end of an AF_UNIX socket (SO_PEERCRED); -1 if unknown
 
 }  // namespace wire
 }  // namespace pccl

@@ -8,6 +8,8 @@
 #include <stdexcept>
 
 #include "../cluster/wire.h"
+#include "../common/env.h"
+#include "../common/hex.h"
 #include "../common/json.h"
 #include "../common/log.h"
 
@@ -43,9 +45,13 @@ Driver& drv() {
   static Driver d;
   static std::once_flag once;
   std::call_once(once, [] {
-    void* lib = ::dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    // PCCL_CUDA_DRIVER_LIB names another library with the same entry points: the CPU tests point it at a
+    // stand-in driver that backs "device" allocations with memfd pages, which exercises handle passing,
+    // peer mapping and the multicast bookkeeping on a machine without a GPU.
+    std::string libname = LaunchEnvironments::getStr("PCCL_CUDA_DRIVER_LIB", "libcuda.so.1");
+    void* lib = ::dlopen(libname.c_str(), RTLD_NOW | RTLD_GLOBAL);
     if (!lib) {
-      d.why = "libcuda.so.1 not found (no NVIDIA driver on this machine)";
+      d.why = libname + " not found (no NVIDIA driver on this machine)";
       return;
     }
     using GetProc = CUresult (*)(const char*, void**, int, cuuint64_t, CUdriverProcAddressQueryResult*);
@@ -126,10 +132,6 @@ CudaDevice::~CudaDevice() {
   if (server_fd_ >= 0) wire::shutdownFd(server_fd_);
   if (server_.joinable()) server_.join();
   wire::closeFd(server_fd_);
-  try {
-    multicastRelease();
-  } catch (...) {
-  }
   std::map<void*, Alloc> allocs;
   {
     std::lock_guard<std::mutex> g(mu_);
@@ -227,48 +229,94 @@ void* CudaDevice::allocateIpcBuffer(size_t bytes, std::string* handle) {
   h.set("id", a.id);
   h.set("pid", static_cast<int64_t>(::getpid()));
   h.set("sock", sock_name_);
+  h.set("token", token_);
   h.set("device", static_cast<int>(dev));
   if (handle) *handle = h.dump();
   return ptr;
 }
 
+// The handle-passing socket lives in the abstract AF_UNIX namespace, which every process of the network
+// namespace can reach, and allocation ids are small integers.  So a request is served only when (a) the
+// kernel says the peer runs under our own user id (SO_PEERCRED) and (b) it carries the 128-bit random token
+// that travels in the handle document (which peers receive over the job's own rendezvous).  Anything else
+// gets an answer without a descriptor.
 void CudaDevice::startFdServer() {
   std::lock_guard<std::mutex> g(mu_);
   if (serving_.load()) return;
-  sock_name_ = "pccl-vmm-" + std::to_string(::getpid()) + "-" + std::to_string(reinterpret_cast<uintptr_t>(this) & 0xffff);
+  unsigned char rnd[16];
+  bool have = false;
+  if (FILE* f = std::fopen("/dev/urandom", "rb")) {
+    have = std::fread(rnd, 1, sizeof(rnd), f) == sizeof(rnd);
+    std::fclose(f);
+  }
+  if (!have) throw std::runtime_error("cuda device: no random source for the handle token");
+  token_ = encodeHex(rnd, sizeof(rnd));
+  sock_name_ = "pccl-vmm-" + std::to_string(::getpid()) + "-" + token_.substr(0, 8);
   server_fd_ = wire::unixListen(sock_name_);
   if (server_fd_ < 0) throw std::runtime_error("cuda device: cannot create the handle-passing socket");
   serving_.store(true);
   server_ = std::thread([this] { fdServerLoop(); });
 }
 
+namespace {
+struct FdRequest {
+  uint64_t id;
+  char token[32];     // hex digits of the 128-bit token
+};
+bool sameToken(const char* a, const std::string& b) {
+  if (b.size() != 32) return false;
+  unsigned char diff = 0;
+  for (int i = 0; i < 32; ++i) diff |= static_cast<unsigned char>(a[i] ^ b[i]);   // no early exit
+  return diff == 0;
+}
+}  // namespace
+
 void CudaDevice::fdServerLoop() {
   while (serving_.load()) {
     int c = wire::acceptOne(server_fd_, 100);
     if (c < 0) continue;
-    uint64_t id = 0;
-    if (wire::recvAll(c, &id, sizeof(id))) {
+    FdRequest rq{};
+    if (wire::recvAll(c, &rq, sizeof(rq))) {
       int fd = -1;
-      {
+      long uid = wire::peerUid(c);
+      bool trusted = uid >= 0 && static_cast<uid_t>(uid) == ::geteuid() && sameToken(rq.token, token_);
+      if (trusted) {
         std::lock_guard<std::mutex> g(mu_);
-        auto it = exported_fds_.find(id);
+        auto it = exported_fds_.find(rq.id);
         if (it != exported_fds_.end()) fd = it->second;
+      } else {
+        refused_.fetch_add(1);
+        PCCL_LOG_WARN("cuda device: refused a memory-handle request (peer uid %ld, token %s)", uid,
+                      sameToken(rq.token, token_) ? "ok" : "wrong");
       }
-      wire::sendFd(c, fd, id);
+      wire::sendFd(c, fd, rq.id);
     }
     wire::closeFd(c);
   }
 }
 
-static int fetchFd(const std::string& sock, uint64_t id) {
+static int fetchFd(const std::string& sock, uint64_t id, const std::string& token) {
   int c = wire::unixConnect(sock, 10000);
   if (c < 0) throw std::runtime_error("cuda device: cannot reach peer handle socket " + sock);
+  FdRequest rq{};
+  rq.id = id;
+  std::memcpy(rq.token, token.data(), std::min<size_t>(token.size(), sizeof(rq.token)));
   int fd = -1;
   uint64_t tag = 0;
-  bool ok = wire::sendAll(c, &id, sizeof(id)) && wire::recvFd(c, &fd, &tag);
+  bool ok = wire::sendAll(c, &rq, sizeof(rq)) && wire::recvFd(c, &fd, &tag);
   wire::closeFd(c);
   if (!ok || fd < 0 || tag != id) throw std::runtime_error("cuda device: peer did not hand over the memory handle");
   return fd;
+}
+
+bool CudaDevice::probeFdServer(const std::string& sock, uint64_t id, const std::string& token) {
+  try {
+    int fd = fetchFd(sock, id, token);
+    ::close(fd);
+    return true;
+  } catch (const std::exception&) {
+    return false;
+  }
 }
 
 void* CudaDevice::mapBuffer(const std::string& handle) {
@@ -276,7 +324,7 @@ void* CudaDevice::mapBuffer(const std::string& handle) {
   Json h = Json::parse(handle);
   size_t size = static_cast<size_t>(h["size"].asInt());
   uint64_t id = static_cast<uint64_t>(h["id"].asInt());
-  int fd = fetchFd(h["sock"].asString(), id);
+  int fd = fetchFd(h["sock"].asString(), id, h["token"].asString());
   Alloc a;
   CUresult r = drv().MemImportFromShareableHandle(&a.handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
                                                   CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
@@ -308,7 +356,6 @@ void CudaDevice::deallocate(void* ptr) {
     allocs_.erase(it);
     exported_fds_.erase(a.id);
   }
-  if (ptr == mc_local_) multicastRelease();
   CUdeviceptr p = reinterpret_cast<CUdeviceptr>(ptr);
   drv().MemUnmap(p, a.bytes);
   drv().MemAddressFree(p, a.bytes);
@@ -343,8 +390,9 @@ size_t CudaDevice::multicastGranularity(int num_devices, size_t bytes, bool reco
   return g;
 }
 
-std::string CudaDevice::multicastCreate(size_t bytes, int num_devices) {
+std::string CudaDevice::multicastCreate(size_t bytes, int num_devices, McObject* mc) {
   if (!multicastSupported()) throw std::runtime_error("cuda device: multicast is not supported here");
+  if (mc->handle) throw std::runtime_error("cuda device: this owner already holds a multicast object");
   CUmulticastObjectProp p{};
   p.numDevices = static_cast<unsigned>(num_devices);
   p.size = bytes;
@@ -361,36 +409,41 @@ std::string CudaDevice::multicastCreate(size_t bytes, int num_devices) {
   {
     std::lock_guard<std::mutex> g(mu_);
     exported_fds_[id] = fd;
-    mc_handle_ = h;
-    mc_bytes_ = bytes;
   }
+  mc->handle = h;
+  mc->bytes = bytes;
+  mc->export_id = id;
   startFdServer();
   Json j = Json::object();
   j.set("size", static_cast<uint64_t>(bytes));
   j.set("id", id);
   j.set("pid", static_cast<int64_t>(::getpid()));
   j.set("sock", sock_name_);
+  j.set("token", token_);
   j.set("num_devices", num_devices);
   return j.dump();
 }
 
-void CudaDevice::multicastJoin(const std::string& handle) {
+void CudaDevice::multicastJoin(const std::string& handle, McObject* mc) {
   Json j = Json::parse(handle);
   size_t bytes = static_cast<size_t>(j["size"].asInt());
-  if (j["pid"].asInt() != static_cast<int64_t>(::getpid()) || mc_handle_ == 0) {
-    int fd = fetchFd(j["sock"].asString(), static_cast<uint64_t>(j["id"].asInt()));
+  const bool mine = j["pid"].asInt() == static_cast<int64_t>(::getpid()) && mc->handle != 0 &&
+                    mc->export_id == static_cast<uint64_t>(j["id"].asInt());
+  if (!mine) {
+    if (mc->handle) throw std::runtime_error("cuda device: this owner already holds a multicast object");
+    int fd = fetchFd(j["sock"].asString(), static_cast<uint64_t>(j["id"].asInt()), j["token"].asString());
     CUmemGenericAllocationHandle h;
     CUresult r = drv().MemImportFromShareableHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
                                                     CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
     ::close(fd);
     check(r, "cuMemImportFromShareableHandle(multicast)");
-    mc_handle_ = h;
-    mc_bytes_ = bytes;
+    mc->handle = h;
+    mc->bytes = bytes;
   }
-  check(drv().MulticastAddDevice(mc_handle_, currentDevice()), "cuMulticastAddDevice");
+  check(drv().MulticastAddDevice(mc->handle, currentDevice()), "cuMulticastAddDevice");
 }
 
-void* CudaDevice::multicastBind(void* local_ptr) {
+void* CudaDevice::multicastBind(void* local_ptr, McObject* mc) {
   Alloc a;
   {
     std::lock_guard<std::mutex> g(mu_);
@@ -398,30 +451,36 @@ void* CudaDevice::multicastBind(void* local_ptr) {
     if (it == allocs_.end()) throw std::runtime_error("cuda device: multicastBind of an unknown allocation");
     a = it->second;
   }
-  if (a.bytes < mc_bytes_) throw std::runtime_error("cuda device: allocation smaller than the multicast object");
-  check(drv().MulticastBindMem(mc_handle_, 0, a.handle, 0, mc_bytes_, 0), "cuMulticastBindMem");
-  mc_bound_ = true;
-  mc_local_ = local_ptr;
-  mc_va_ = mapHandle(mc_handle_, mc_bytes_);
-  return mc_va_;
+  if (!mc->handle) throw std::runtime_error("cuda device: multicastBind before multicastJoin");
+  if (a.bytes < mc->bytes) throw std::runtime_error("cuda device: allocation smaller than the multicast object");
+  check(drv().MulticastBindMem(mc->handle, 0, a.handle, 0, mc->bytes, 0), "cuMulticastBindMem");
+  mc->bound = true;
+  mc->local = local_ptr;
+  mc->va = mapHandle(mc->handle, mc->bytes);
+  return mc->va;
 }
 
-void CudaDevice::multicastRelease() {
-  if (!drv().ok || mc_handle_ == 0) return;
-  if (mc_va_) {
-    CUdeviceptr p = reinterpret_cast<CUdeviceptr>(mc_va_);
-    drv().MemUnmap(p, mc_bytes_);
-    drv().MemAddressFree(p, mc_bytes_);
-    mc_va_ = nullptr;
+void CudaDevice::multicastRelease(McObject* mc) {
+  if (!drv().ok || !mc || mc->handle == 0) return;
+  if (mc->va) {
+    CUdeviceptr p = reinterpret_cast<CUdeviceptr>(mc->va);
+    drv().MemUnmap(p, mc->bytes);
+    drv().MemAddressFree(p, mc->bytes);
   }
-  if (mc_bound_) {
+  if (mc->bound) {
     CUdevice dev;
-    if (drv().CtxGetDevice(&dev) == CUDA_SUCCESS) drv().MulticastUnbind(mc_handle_, dev, 0, mc_bytes_);
-    mc_bound_ = false;
+    if (drv().CtxGetDevice(&dev) == CUDA_SUCCESS) drv().MulticastUnbind(mc->handle, dev, 0, mc->bytes);
   }
-  drv().MemRelease(mc_handle_);
-  mc_handle_ = 0;
-  mc_local_ = nullptr;
+  drv().MemRelease(mc->handle);
+  if (mc->export_id) {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = exported_fds_.find(mc->export_id);
+    if (it != exported_fds_.end()) {
+      if (it->second >= 0) ::close(it->second);
+      exported_fds_.erase(it);
+    }
+  }
+  *mc = McObject{};
 }
 
 void registerCudaDevice() {

@@ -35,16 +35,34 @@ class CudaDevice : public DeviceBase {
   void unmapBuffer(void* ptr) override;
 
   // ---- NVLS multicast ------------------------------------------------------------------------
+  // The state of one multicast object lives with its owner (an Engine), not with the device: the
+  // device object is process-wide, and several engines of one process (the old and the new engine
+  // around an elastic recovery, a world-of-one helper engine, a test fixture) each bind their own
+  // heap.  Releasing one object must leave every other mapping alone.
+  struct McObject {
+    unsigned long long handle = 0;
+    size_t bytes = 0;
+    void* va = nullptr;        // multicast address of the bound heap
+    bool bound = false;
+    void* local = nullptr;     // the allocation that is bound
+    uint64_t export_id = 0;    // creator side: id under which the fd server hands the object out
+  };
   bool multicastSupported();
   size_t multicastGranularity(int num_devices, size_t bytes, bool recommended = false);
   // Rank 0: create the object for `num_devices` GPUs; returns a handle document for the others.
-  std::string multicastCreate(size_t bytes, int num_devices);
+  std::string multicastCreate(size_t bytes, int num_devices, McObject* mc);
   // Every rank (rank 0 passes its own document): import and add this process's device.
-  void multicastJoin(const std::string& handle);
+  void multicastJoin(const std::string& handle, McObject* mc);
   // After every rank has joined: bind the local allocation `local_ptr` (from allocateIpcBuffer)
   // and map the object; returns the multicast address of the heap.
-  void* multicastBind(void* local_ptr);
-  void multicastRelease();
+  void* multicastBind(void* local_ptr, McObject* mc);
+  // Unmaps, unbinds and releases `mc` only; a second call is a no-op.
+  void multicastRelease(McObject* mc);
+
+  // Asks the handle server at `sock` for allocation `id` with `token`; true when a descriptor came back (it is
+  // closed again).  For tests of the server's checks.
+  static bool probeFdServer(const std::string& sock, uint64_t id, const std::string& token);
+  uint64_t refusedRequests() const { return refused_.load(); }
 
   size_t allocatedSize(void* ptr);
   int deviceOrdinal();
@@ -70,12 +88,8 @@ class CudaDevice : public DeviceBase {
   int server_fd_ = -1;
   std::thread server_;
   std::atomic<bool> serving_{false};
-  // multicast state
-  unsigned long long mc_handle_ = 0;
-  size_t mc_bytes_ = 0;
-  void* mc_va_ = nullptr;
-  bool mc_bound_ = false;
-  void* mc_local_ = nullptr;
+  std::atomic<uint64_t> refused_{0};
+  std::string token_;                      // 128 random bits; a request for an fd must carry them
 };
 
 void registerCudaDevice();   // idempotent; registers even without a GPU (allocatorAvailable()==false)

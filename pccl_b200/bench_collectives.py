@@ -15,27 +15,34 @@ from typing import Dict, List, Optional
 import torch
 import torch.distributed as dist
 
-from .engine import Engine
+from .engine import Engine, dtype_name
 from .ops import collectives as C
 
 POOL_BYTES = 320 << 20
 
 
-def _time(fn_at, n_slots: int, iters: int, warmup: int) -> float:
-    """Median-free mean of `iters` back-to-back calls (events bracket the whole train of calls)."""
+def _time(fn_at, n_slots: int, iters: int, warmup: int, trains: int = 1) -> float:
+    """Milliseconds per call: a train of `iters` back-to-back calls between two CUDA events, maximum over the
+    ranks; with `trains` > 1 the median of that many trains (one slow train, e.g. a clock dip, does not decide)."""
     for i in range(warmup):
         fn_at(i % n_slots)
-    torch.cuda.synchronize()
-    dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(iters):
-        fn_at((warmup + i) % n_slots)
-    b.record()
-    b.synchronize()
-    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    per_train = []
+    k = warmup
+    for _ in range(max(1, trains)):
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _i in range(iters):
+            fn_at(k % n_slots)
+            k += 1
+        b.record()
+        b.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_train.append(float(t.item()))
+    per_train.sort()
+    return per_train[len(per_train) // 2]
 
 
 def bus_factor(kind: str, n: int) -> float:
@@ -66,7 +73,8 @@ def interp_programs(eng: Engine, kind: str) -> List[str]:
     return names
 
 
-def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: List[str], iters: Optional[int] = None) -> Dict:
+def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: List[str], iters: Optional[int] = None,
+               trains: int = 1) -> Dict:
     """`nbytes` = bytes of the full vector (all-reduce) or of the gathered/scattered whole (RS/AG)."""
     world = eng.world
     es = torch.empty((), dtype=dtype).element_size()
@@ -134,9 +142,15 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
                 fn = lambda i, a=impl: C.reduce_scatter(eng, ins[i], outs[i][:shard], algo=a)  # noqa: E731
             else:
                 fn = lambda i, a=impl: C.all_gather(eng, ins[i][:shard], outs[i], algo=a)  # noqa: E731
-        ms = _time(fn, n_slots, iters, warmup)
+        ms = _time(fn, n_slots, iters, warmup, trains)
         alg = nbytes / (ms * 1e-3) / 1e9
         res[impl] = {"us": ms * 1e3, "algbw_gbs": alg, "busbw_gbs": alg * bus_factor(kind, world)}
+        if impl == "auto":          # what `algo="auto"` resolved to at this size
+            per_rank = nbytes if kind == "allreduce" else nbytes // world
+            if kind == "allgather":
+                res[impl]["algo"] = "nvls" if (eng.has_nvls and per_rank % 16 == 0 and per_rank < (4 << 20)) else "p2p"
+            else:
+                res[impl]["algo"] = C._algo(eng, "auto", dtype_name(dtype), "sum", per_rank, kind)
     eng.symmetric_reset(mark)
     return res
 
