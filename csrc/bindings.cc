@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <map>
 
 #include "base/registry.h"
 #include "common/clock.h"
@@ -290,6 +291,36 @@ PYBIND11_MODULE(_C, m) {
     return py::bytes(s);
   });
   utils.def("fnv1a", [](const std::string& s) { return fnv1a(s); });
+  // The CUDA device plugin by itself (no engine, no CUDA runtime call): what the CPU tests drive against a stand-in
+  // driver library (PCCL_CUDA_DRIVER_LIB).  Multicast objects are kept here under small integer ids.
+  auto cudaDev = [] {
+    registerCudaDevice();
+    return static_cast<CudaDevice*>(getDev("cuda").get());
+  };
+  static std::map<int, CudaDevice::McObject> mc_objects;
+  static int mc_next = 1;
+  utils.def("cuda_device_available", [cudaDev] { return cudaDev()->allocatorAvailable(); });
+  utils.def("cuda_device_alloc", [cudaDev](uint64_t bytes) {
+    std::string handle;
+    void* p = cudaDev()->allocateIpcBuffer(bytes, &handle);
+    return py::make_tuple(reinterpret_cast<uint64_t>(p), handle);
+  });
+  utils.def("cuda_device_map", [cudaDev](const std::string& handle) { return reinterpret_cast<uint64_t>(cudaDev()->mapBuffer(handle)); },
+            py::call_guard<py::gil_scoped_release>());
+  utils.def("cuda_device_free", [cudaDev](uint64_t ptr) { cudaDev()->deallocate(reinterpret_cast<void*>(ptr)); });
+  utils.def("cuda_fd_probe", &CudaDevice::probeFdServer, py::call_guard<py::gil_scoped_release>());
+  utils.def("cuda_fd_refused", [cudaDev] { return cudaDev()->refusedRequests(); });
+  utils.def("cuda_mc_new", [] { mc_objects[mc_next] = CudaDevice::McObject{}; return mc_next++; });
+  utils.def("cuda_mc_create", [cudaDev](int id, uint64_t bytes, int n) { return cudaDev()->multicastCreate(bytes, n, &mc_objects.at(id)); });
+  utils.def("cuda_mc_join", [cudaDev](int id, const std::string& h) { cudaDev()->multicastJoin(h, &mc_objects.at(id)); });
+  utils.def("cuda_mc_bind", [cudaDev](int id, uint64_t ptr) {
+    return reinterpret_cast<uint64_t>(cudaDev()->multicastBind(reinterpret_cast<void*>(ptr), &mc_objects.at(id)));
+  });
+  utils.def("cuda_mc_release", [cudaDev](int id) { cudaDev()->multicastRelease(&mc_objects.at(id)); });
+  utils.def("cuda_mc_state", [](int id) {
+    const auto& m = mc_objects.at(id);
+    return py::make_tuple(static_cast<uint64_t>(m.handle), reinterpret_cast<uint64_t>(m.va), m.bound);
+  });
   utils.def("now_nanos", &nowNanos);
   utils.def("launch_timestamp", &launchTimestamp);
   utils.def("log", [](const std::string& level, const std::string& msg) {

@@ -60,7 +60,8 @@ Engine::~Engine() {
     auto dev = getDev(device_);
     if (dev) {
       try {
-        if (device_ == "cuda") static_cast<CudaDevice*>(dev.get())->multicastRelease();
+        // only the multicast object that THIS engine created or joined: other engines of the process keep theirs
+        if (device_ == "cuda") static_cast<CudaDevice*>(dev.get())->multicastRelease(&mc_);
         dev->deallocate(heap_);
       } catch (...) {
       }
@@ -76,6 +77,9 @@ void Engine::buildLayout(uint64_t heap_bytes) {
   if (L.lanes < 1) L.lanes = 1;
   L.signal_off = L.workspace_bytes;
   L.num_signals = 65536;
+  L.finish_base = static_cast<uint32_t>(L.num_signals) - kMaxLanes;
+  L.turn_base = L.finish_base - kMaxLanes * kMaxRanks;
+  if (L.lanes > kMaxLanes) L.lanes = kMaxLanes;
   L.flag_off = L.signal_off + L.num_signals * 8;
   L.flag_bytes = alignUp(8ull * kMaxBlocksPerColl * kMaxRanks * 8, 256 * 1024);
   L.status_off = L.flag_off + L.flag_bytes;
@@ -99,6 +103,8 @@ void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
   bounds_check_ = LaunchEnvironments::getBool("PCCL_BOUNDS_CHECK", true);
   trace_ = LaunchEnvironments::getBool("PCCL_TRACE", false);
   max_width_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_MAX_SMS", 32));
+  exec_delay_us_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_EXEC_DELAY_US", 0));
+  exec_delay_rank_ = static_cast<int>(LaunchEnvironments::getInt("PCCL_EXEC_DELAY_RANK", -1));
   host_id_ = readHostId();
   buildLayout(heap_bytes);
   if (device_ == "cuda" && world_ > 1) {
@@ -247,14 +253,31 @@ bool Engine::waitForDeparture(int rank, int timeout_ms) { return cluster_ && clu
 
 void Engine::rebind(int new_rank, int new_world) {
   // Peers are re-mapped by the next importEndpoints/joinCluster; registered programs of the old
-  // world size stay registered but cannot run (their world differs).
+  // world size stay registered but cannot run (their world differs).  Everything that counts launches
+  // starts again from zero: signal words, barrier flags, status, lane and program epochs -- on a CUDA
+  // engine after the device has drained, and with the old world's multicast object released (connect()
+  // builds a new one for the new world).
+  if (new_world < 1 || new_rank < 0 || new_rank >= new_world || new_world > kMaxRanks)
+    throw std::runtime_error("rebind: need 0 <= rank < world <= the compiled maximum");
+  std::lock_guard<std::mutex> g(mu_);
   dropPeers();
   char* mine = heap_;
   rank_ = new_rank;
   world_ = new_world;
   peer_heaps_.assign(world_, nullptr);
   peer_heaps_[rank_] = mine;
-  if (device_ == "cpu") std::memset(heap_ + layout_.signal_off, 0, layout_.num_signals * 8);
+  const uint64_t ctl = layout_.user_off - layout_.signal_off;
+  if (device_ == "cuda") {
+    cudaCheck(cudaDeviceSynchronize(), "rebind: draining the device");
+    if (auto dev = getDev("cuda")) static_cast<CudaDevice*>(dev.get())->multicastRelease(&mc_);
+    mc_base_ = nullptr;
+    cudaCheck(cudaMemset(heap_ + layout_.signal_off, 0, ctl), "rebind: clearing the signal area");
+    cudaCheck(cudaDeviceSynchronize(), "rebind");
+  } else if (heap_) {
+    std::memset(heap_ + layout_.signal_off, 0, ctl);
+  }
+  lane_epochs_.assign(lane_epochs_.size(), 0);
+  lane_launches_.assign(lane_launches_.size(), 0);
   for (auto& kv : ops_)
     for (auto& v : kv.second.variants) v.second.epoch = 0;
 }
@@ -316,12 +339,12 @@ std::string Engine::mcCreate() {
   auto* dev = static_cast<CudaDevice*>(getDev("cuda").get());
   size_t gran = dev->multicastGranularity(world_, layout_.total);
   if (layout_.total % gran) throw std::runtime_error("mcCreate: heap size is not a multiple of the multicast granularity");
-  return dev->multicastCreate(layout_.total, world_);
+  return dev->multicastCreate(layout_.total, world_, &mc_);
 }
 
-void Engine::mcJoin(const std::string& handle) { static_cast<CudaDevice*>(getDev("cuda").get())->multicastJoin(handle); }
+void Engine::mcJoin(const std::string& handle) { static_cast<CudaDevice*>(getDev("cuda").get())->multicastJoin(handle, &mc_); }
 
-void Engine::mcBind() { mc_base_ = static_cast<CudaDevice*>(getDev("cuda").get())->multicastBind(heap_); }
+void Engine::mcBind() { mc_base_ = static_cast<CudaDevice*>(getDev("cuda").get())->multicastBind(heap_, &mc_); }
 
 uint64_t Engine::nextEpoch(int lane) {
   if (lane < 0 || lane >= static_cast<int>(lane_epochs_.size())) throw std::runtime_error("nextEpoch: bad lane");
@@ -384,7 +407,7 @@ Engine::Op::Variant& Engine::variantFor(Op& op, int width) {
   auto it = op.variants.find(width);
   if (it != op.variants.end()) return it->second;
   const uint32_t need = op.program.num_slots * static_cast<uint32_t>(width);
-  if (next_slot_ + need > layout_.num_signals) throw std::runtime_error("exeOp: out of signal words");
+  if (next_slot_ + need > layout_.turn_base) throw std::runtime_error("exeOp: out of signal words");
   Op::Variant v;
   v.slot_base = next_slot_;
   next_slot_ += need;
@@ -407,8 +430,12 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
                              " bytes of scratch but a workspace lane half holds " + std::to_string(half) +
                              " (raise PCCL_WORKSPACE_MB or split the message)");
   Op::Variant& var = variantFor(op, width);
-  uint64_t scratch_off = lane * lane_bytes + (lane_launches_.at(lane)++ & 1) * half;
+  const uint64_t launch_no = lane_launches_.at(lane)++;
+  uint64_t scratch_off = lane * lane_bytes + (launch_no & 1) * half;
   CpuExecContext ctx;
+  ctx.turn_slot = world_ > 1 ? static_cast<int64_t>(layout_.turn_base) + lane * kMaxRanks : -1;
+  ctx.launch_no = launch_no;
+  if (exec_delay_rank_ == rank_) ctx.delay_us = exec_delay_us_;
   ctx.rank = rank_;
   ctx.world = world_;
   ctx.local[BUF_INPUT] = reinterpret_cast<char*>(in_ptr);
@@ -503,7 +530,13 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   R.output_heap_off = heapOff(p.in_place ? in_ptr : out_ptr);
   if (p.remote_io && (R.input_heap_off < 0 || R.output_heap_off < 0))
     throw std::runtime_error("exeOp: this program lets peers touch the tensors, so both must come from the symmetric heap");
-  R.scratch_off = lane * lane_bytes + (lane_launches_.at(lane)++ & 1) * half;
+  const uint64_t launch_no = lane_launches_.at(lane)++;
+  R.scratch_off = lane * lane_bytes + (launch_no & 1) * half;
+  if (world_ > 1) {
+    L.turn_slot = layout_.turn_base + static_cast<uint32_t>(lane) * kMaxRanks;
+    L.finish_slot = layout_.finish_base + static_cast<uint32_t>(lane);
+    L.launch_no = launch_no;
+  }
   for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) R.buf_bytes[b] = c.m.buf_bytes[b];
   R.status = reinterpret_cast<uint32_t*>(statusPtr(lane));
   size_t n_instr = 0;

@@ -40,7 +40,11 @@ struct HeapLayout {
   uint64_t user_off = 0;
   uint64_t total = 0;
   int lanes = 2;
+  // The last signal words are not handed to programs: kMaxLanes x kMaxRanks "launches finished" counters and
+  // kMaxLanes "streams ended" counters of the workspace turn-taking (kernels/api.h, InterpLaunch).
+  uint32_t turn_base = 0, finish_base = 0;
 };
+constexpr int kMaxLanes = 8;
 
 class Engine {
  public:
@@ -132,6 +136,7 @@ class Engine {
   std::string heap_handle_;
   std::vector<char*> peer_heaps_;
   void* mc_base_ = nullptr;
+  CudaDevice::McObject mc_;                 // this engine's NVLS multicast object (none until mcCreate / mcJoin)
   uint64_t user_top_ = 0;
   std::map<std::string, std::string> configs_;
   std::unique_ptr<ClusterManager> cluster_;
@@ -152,6 +157,7 @@ class Engine {
   struct DeviceTrace { uint64_t* words = nullptr; size_t cap = 0; };
   std::vector<DeviceTrace> dtrace_;
   int max_width_ = 32;
+  int exec_delay_us_ = 0, exec_delay_rank_ = -1;   // testing aid: PCCL_EXEC_DELAY_US on rank PCCL_EXEC_DELAY_RANK
 };
 
 }  // namespace pccl

@@ -55,6 +55,7 @@ void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext&
   for (size_t pc = 0; pc < prog.size(); ++pc) {
     if (sh.status.load(std::memory_order_relaxed) != ST_OK) return;
     const Instr& in = prog[pc];
+    if (ctx.delay_us > 0 && in.op != OP_END) std::this_thread::sleep_for(std::chrono::microseconds(ctx.delay_us));
     struct Stamp {
       std::vector<TraceEvent>* out; uint32_t stream, pc, op; uint64_t bytes, t0;
       ~Stamp() { if (out) out->push_back(TraceEvent{stream, pc, op, t0, monotonicNanos(), bytes}); }
@@ -129,6 +130,18 @@ void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext&
 CpuExecResult runOnCpu(const Materialized& m, const CpuExecContext& ctx) {
   Shared sh;
   uint64_t t0 = monotonicNanos();
+  if (ctx.turn_slot >= 0 && ctx.launch_no >= 2) {
+    std::atomic<uint64_t>* mine = ctx.peer_signals[ctx.rank];
+    for (int r = 0; r < ctx.world; ++r)
+      if (r != ctx.rank && !waitFor(&mine[ctx.turn_slot + r], ctx.launch_no - 1, ctx, sh)) {
+        CpuExecResult bad;
+        bad.status = ST_TIMEOUT;
+        bad.failed_stream = -1;
+        bad.failed_pc = -1;
+        bad.nanos = monotonicNanos() - t0;
+        return bad;
+      }
+  }
   std::vector<std::thread> threads;
   std::vector<std::vector<TraceEvent>> traces(ctx.trace ? m.streams.size() : 0);
   auto tr = [&](size_t i) { return ctx.trace ? &traces[i] : nullptr; };
@@ -136,6 +149,14 @@ CpuExecResult runOnCpu(const Materialized& m, const CpuExecContext& ctx) {
     threads.emplace_back([&, i] { runStream(m.streams[i], static_cast<int>(i), ctx, sh, tr(i)); });
   if (!m.streams.empty()) runStream(m.streams[0], 0, ctx, sh, tr(0));
   for (auto& t : threads) t.join();
+  if (ctx.turn_slot >= 0 && sh.status.load() == ST_OK) {
+    const uint32_t word = static_cast<uint32_t>(ctx.turn_slot + ctx.rank);
+    for (int q = 0; q < ctx.world; ++q) {
+      if (q == ctx.rank) continue;
+      if (ctx.peer_signals[q]) ctx.peer_signals[q][word].fetch_add(1, std::memory_order_release);
+      else if (!ctx.tcp || !ctx.tcp->signal(q, word, 1)) sh.fail(ST_PEER_GONE, -1, -1);
+    }
+  }
   CpuExecResult r;
   for (auto& v : traces) r.trace.insert(r.trace.end(), v.begin(), v.end());
   r.status = sh.status.load();

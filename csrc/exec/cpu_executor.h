@@ -32,6 +32,13 @@ struct CpuExecContext {
   int timeout_ms = 30000;
   bool bounds_check = true;
   bool trace = false;                // record one TraceEvent per executed instruction
+  // Workspace turn-taking (see InterpLaunch in kernels/api.h): before the launch every peer must have finished
+  // launch_no - 2 on this lane; after it this rank adds one to its word on every peer.  turn_slot < 0: off.
+  int64_t turn_slot = -1;
+  uint64_t launch_no = 0;
+  // Testing aid (PCCL_EXEC_DELAY_US with PCCL_EXEC_DELAY_RANK): sleep this long before every instruction, which
+  // makes one rank lag behind the others deterministically.
+  int delay_us = 0;
 };
 
 struct TraceEvent {

@@ -51,11 +51,23 @@ struct InterpRank {
                                   // %globaltimer when the CTA began it and when all its threads had finished it
 };
 
+constexpr uint32_t kNoTurnSlot = 0xffffffffu;
+
 struct InterpLaunch {
   World w;
   int nvirt;                      // 1, or world for single-GPU emulation
   uint32_t slot_base;
   uint64_t epoch;
+  // Workspace turn-taking.  Launches on one workspace lane alternate between the lane's two scratch halves, so
+  // launch n reuses the half of launch n - 2.  Programs differ in which ranks they tie together, so a rank may
+  // run ahead of a peer across a program that does not involve both.  Every rank therefore publishes "I have
+  // finished n launches on this lane" to all peers when its last stream ends, and before a launch touches any
+  // scratch it waits until every peer has finished launch n - 2.  Words turn_slot + r (absolute signal indices)
+  // count rank r's finished launches; finish_slot counts this rank's streams that have ended (wraps to zero).
+  // kNoTurnSlot switches the protocol off (single-launch emulation).
+  uint32_t turn_slot = kNoTurnSlot;
+  uint32_t finish_slot = 0;
+  uint64_t launch_no = 0;         // 0-based launch number on the lane
   uint32_t dtype, redop;
   uint64_t spin_limit;
   int bounds_check;

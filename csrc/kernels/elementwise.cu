@@ -1,6 +1,7 @@
 // Memory-bound training kernels that sit next to the GEMMs: fused AdamW on a flat fp32 shard with
 // the bf16 parameter write-back, and softmax cross-entropy forward+backward in one pass over the
 // logits (the row is staged in shared memory: read once, gradient written once, in place).
+#include <atomic>
 #include <cuda_bf16.h>
 
 #include "elementwise_api.h"
@@ -70,7 +71,7 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_m
 
 __global__ void __launch_bounds__(512) cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
                                                             float* __restrict__ loss, int vocab, long long ld, float grad_scale,
-                                                            long long ignore_index) {
+                                                            long long ignore_index, uint32_t* __restrict__ status) {
   extern __shared__ __align__(16) uint8_t ce_smem[];
   __nv_bfloat16* row_s = reinterpret_cast<__nv_bfloat16*>(ce_smem);
   __shared__ float scratch[32];
@@ -97,8 +98,18 @@ __global__ void __launch_bounds__(512) cross_entropy_kernel(__nv_bfloat16* __res
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += __expf(__bfloat162float(row_s[i]) - mx);
   sum = block_reduce(sum, scratch, false);
   const float lse = mx + __logf(sum);
-  const bool ignored = tgt == ignore_index;
-  if (threadIdx.x == 0) loss[row] = ignored ? 0.f : lse - __bfloat162float(row_s[tgt]);
+  // A target outside [0, vocab) never indexes the staged row: the row is handled like an ignored one (loss 0,
+  // zero gradient), and unless it is the ignore value itself the first such row is recorded in the status words.
+  const bool valid = tgt >= 0 && tgt < static_cast<long long>(vocab);
+  const bool ignored = tgt == ignore_index || !valid;
+  if (threadIdx.x == 0) {
+    loss[row] = ignored ? 0.f : lse - __bfloat162float(row_s[tgt]);
+    if (!valid && tgt != ignore_index && status && atomicCAS(status, 0u, static_cast<uint32_t>(ST_BOUNDS)) == 0u) {
+      status[1] = static_cast<uint32_t>(row);
+      status[2] = static_cast<uint32_t>(tgt);
+      status[3] = 0xCEu;          // detail: cross-entropy target out of range
+    }
+  }
   const float scale = ignored ? 0.f : grad_scale;
   const float inv = 1.f / sum;
   for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
@@ -131,19 +142,32 @@ int launchAdamW(float* p, float* m, float* v, const float* g, void* p_bf16, long
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace {
+constexpr int kMaxDevices = 64;
+// The shared-memory opt-in of cross_entropy_kernel is a per-device function attribute.
+std::atomic<bool> g_ce_attr[kMaxDevices];
+
+cudaError_t ensureCrossEntropyAttr() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (g_ce_attr[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(cross_entropy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e == cudaSuccess) g_ce_attr[dev].store(true, std::memory_order_release);
+  return e;
+}
+}  // namespace
+
 int launchCrossEntropy(void* logits, const long long* targets, float* loss, long long rows, int vocab, long long ld,
-                       float grad_scale, long long ignore_index, cudaStream_t stream) {
+                       float grad_scale, long long ignore_index, uint32_t* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
   size_t smem = (static_cast<size_t>(vocab) * 2 + 15) / 16 * 16;
   if (smem > 200 * 1024 || ld % 8 || reinterpret_cast<uintptr_t>(logits) % 16) return static_cast<int>(cudaErrorInvalidValue);
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(cross_entropy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    set = true;
-  }
+  cudaError_t e = ensureCrossEntropyAttr();
+  if (e != cudaSuccess) return static_cast<int>(e);
   cross_entropy_kernel<<<static_cast<unsigned>(rows), 512, smem, stream>>>(static_cast<__nv_bfloat16*>(logits), targets, loss, vocab, ld,
-                                                                          grad_scale, ignore_index);
+                                                                          grad_scale, ignore_index, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -177,9 +201,9 @@ __global__ void __launch_bounds__(1024) noalloc_mean_kernel(float* __restrict__ 
   }
 }
 
-constexpr int kMaxDevices = 64;
+// Written without a lock: two host threads that make the FIRST call on one device at the same time both resolve
+// and store the same address, which is harmless.
 float* g_noalloc_ptr[kMaxDevices] = {nullptr};
-bool g_noalloc_attr[kMaxDevices] = {false};
 int g_noalloc_cuda_error = 0;
 
 }  // namespace
@@ -204,14 +228,12 @@ extern "C" int pccl_cross_entropy_mean_noalloc(void* logits, const long long* ta
     if (e != cudaSuccess || !p) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
     g_noalloc_ptr[dev] = static_cast<float*>(p);
   }
-  if (!g_noalloc_attr[dev]) {
-    e = cudaFuncSetAttribute(cross_entropy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
-    g_noalloc_attr[dev] = true;
-  }
+  e = ensureCrossEntropyAttr();
+  if (e != cudaSuccess) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }
   const float scale = 1.0f / static_cast<float>(rows);
+  // no ignore value of its own: every target outside [0, vocab) (the customary -100 included) makes an ignored row
   cross_entropy_kernel<<<static_cast<unsigned>(rows), 512, smem, stream>>>(static_cast<__nv_bfloat16*>(logits), targets,
-                                                                          g_noalloc_ptr[dev], vocab, ld, scale, -(1ll << 62));
+                                                                          g_noalloc_ptr[dev], vocab, ld, scale, -(1ll << 62), nullptr);
   noalloc_mean_kernel<<<1, 1024, 0, stream>>>(mean_loss, rows, scale);
   e = cudaGetLastError();
   if (e != cudaSuccess) { g_noalloc_cuda_error = static_cast<int>(e); return PCCL_NOALLOC_CUDA_ERROR; }

@@ -18,6 +18,7 @@ enum GemmFlags : uint32_t {
   GEMM_BIAS = 1u << 5,        // D = A*B^T + bias[n] (bf16 bias)
   GEMM_GELU_INPLACE = 1u << 6,  // D = gelu_tanh(A*B^T (+bias)); no separate pre-activation
   GEMM_PAIR = 1u << 7,        // CTA pairs (cta_group::2, 256 x 256 tiles) instead of single CTAs (128 x 256)
+  GEMM_ADD_D2 = 1u << 8,      // D = A*B^T (+bias) + D2 (bf16, D's layout, read only): a residual connection; not with GEMM_GELU
 };
 
 // D[M,N] (ldd) = A * B^T.  K-major operands: A is [M,K] with row stride lda, B is [N,K] with row
@@ -27,6 +28,13 @@ enum GemmFlags : uint32_t {
 // null) receives ST_TIMEOUT if a pipeline wait runs out.
 int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
              uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status, cudaStream_t stream);
+
+// D[M,N] = (A * B^T) .* gelu_tanh'(pre[M,N]) in bf16, and colsum[n] += sum_m D[m,n] (fp32, may be null): the
+// backward of "linear -> GELU -> linear" between the second layer's input gradient and the first layer's output
+// gradient, with the first layer's bias gradient as a by-product.  `pre` has D's row stride.  CTA pairs; M a multiple
+// of 256 and N a multiple of 256; flags: GEMM_A_MN / GEMM_B_MN only.
+int gemmBf16Dgelu(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, const void* pre, float* colsum,
+                  int M, int N, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream);
 
 // Grouped GEMM for expert layers: group g multiplies rows [row_off[g], row_off[g+1]) of A [*, K] with
 // the g-th [N, K] block of B (stacked [groups*N, K]) into the same rows of D [*, N].  `row_off`

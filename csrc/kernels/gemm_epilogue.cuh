@@ -13,6 +13,67 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.0f + tanhf(u));
 }
 
+// d/dx of gelu_tanh
+__device__ __forceinline__ float dgelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float x2 = x * x;
+  const float t = tanhf(k0 * (x + k1 * x * x2));
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k0 * (1.0f + 3.0f * k1 * x2);
+}
+
+// Sums v[0..31] of the 32 lanes column by column: afterwards lane l holds (in v[0]) the sum over the warp of v[l].
+// A butterfly that halves the number of live values per step: 31 shuffles instead of 32 five-step reductions.
+__device__ __forceinline__ void warp_transpose_sum32(float* v, int lane) {
+#pragma unroll
+  for (int s = 16; s >= 1; s >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int i = 0; i < s; ++i) {
+      const float send = upper ? v[i] : v[i + s];
+      const float keep = upper ? v[i + s] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+    }
+  }
+}
+
+// Backward of a GELU that sits between two linear layers, fused into the GEMM that produces the gradient of the
+// activation: D = (A * B^T) .* gelu'(pre), and the column sums of D (the bias gradient of the first layer) are added
+// to `colsum` (fp32, zeroed by the caller).  Full tiles only (M % 128 == 0, N % 256 == 0); `pre` has D's layout.
+struct DgeluEpi {
+  static constexpr bool kRow128 = false;
+  __nv_bfloat16* D;
+  const __nv_bfloat16* pre;
+  float* colsum;
+  long long ldd;
+  int M, N;
+
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.m * BM; }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * BN; }
+  __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
+
+  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
+    const int row = t.m * BM + row_in_tile, col = t.n * BN + col_in_tile;
+    const long long at = static_cast<long long>(row) * ldd + col;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      float x[8];
+      dev::unpack<DT_BF16>(dev::ld16(pre + at + i), x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i + j] = __uint_as_float(r[i + j]) * dgelu_tanh(x[j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) dev::st16(D + at + i, dev::pack<DT_BF16>(v + i));
+    if (colsum) {
+      const int lane = threadIdx.x & 31;       // an epilogue warp holds 32 consecutive rows, one per lane
+      warp_transpose_sum32(v, lane);
+      atomicAdd(colsum + col + lane, v[0]);
+    }
+  }
+};
+
 struct StoreEpi {
   static constexpr bool kRow128 = false;   // takes 32-column strips
   void* D;
@@ -61,6 +122,16 @@ struct StoreEpi {
     }
     __nv_bfloat16* d = static_cast<__nv_bfloat16*>(D) + static_cast<long long>(row) * ldd + col;
     if (full) {
+      if (flags & GEMM_ADD_D2) {        // D = A*B^T (+bias) + D2: the residual connection around a linear layer
+        const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(D2) + static_cast<long long>(row) * ldd + col;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          float f[8];
+          dev::unpack<DT_BF16>(dev::ld16(res + i), f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i + j] += f[j];
+        }
+      }
       if (flags & GEMM_GELU_INPLACE) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
@@ -88,6 +159,7 @@ struct StoreEpi {
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         if (col + i >= N) continue;
+        if (flags & GEMM_ADD_D2) v[i] += __bfloat162float((static_cast<const __nv_bfloat16*>(D2) + static_cast<long long>(row) * ldd + col)[i]);
         float x = (flags & GEMM_ACCUMULATE) ? v[i] + __bfloat162float(d[i]) : v[i];
         d[i] = __float2bfloat16_rn(x);
         if (flags & GEMM_GELU)

@@ -29,25 +29,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ---- CTA-pair kernel ---------------------------------------------------------------------------------
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, class Epi = StoreEpi>
 __global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, StoreEpi epi, int K,
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi epi, int K,
                       uint32_t* status) {
   GroupedSched sched{(epi.M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.N + gemm2::BN - 1) / gemm2::BN,
                      static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
   NoGate gate;
   const int cta = static_cast<int>(tc::cluster_ctarank());
-  gemm2::PairEpi<StoreEpi> pe{epi, cta};
+  gemm2::PairEpi<Epi> pe{epi, cta};
   gemm2::PairGate<NoGate> pg{gate, cta};
   gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, pg, pe, status);
 }
 
 thread_local std::string g_err;
 
-template <bool A_MN, bool B_MN>
-int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const StoreEpi& epi, int K, int grid, uint32_t* status, cudaStream_t stream) {
+template <bool A_MN, bool B_MN, class Epi = StoreEpi>
+int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, int K, int grid, uint32_t* status, cudaStream_t stream) {
   static bool attr_set = false;
-  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, Epi>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -93,6 +93,10 @@ int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, in
     g_err = "gemmBf16: strides must be multiples of 8 elements and pointers 16-byte aligned";
     return static_cast<int>(cudaErrorInvalidValue);
   }
+  if ((flags & GEMM_ADD_D2) && (!D2 || (flags & (GEMM_OUT_F32 | GEMM_GELU)))) {
+    g_err = "gemmBf16: the residual input needs D2 and a bf16 D, and excludes the GELU side output";
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
   if ((flags & GEMM_GELU) && (!D2 || (flags & GEMM_OUT_F32))) {
     g_err = "gemmBf16: the GELU side output needs D2 and a bf16 D";
     return static_cast<int>(cudaErrorInvalidValue);
@@ -125,6 +129,32 @@ int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, in
   int grid = tiles < n_sm ? tiles : n_sm;
   if (a_mn) return b_mn ? launch<true, true>(ta, tb, epi, K, grid, status, stream) : launch<true, false>(ta, tb, epi, K, grid, status, stream);
   return b_mn ? launch<false, true>(ta, tb, epi, K, grid, status, stream) : launch<false, false>(ta, tb, epi, K, grid, status, stream);
+}
+
+int gemmBf16Dgelu(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, const void* pre, float* colsum,
+                  int M, int N, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda | ldb | ldd) % 8 || M % 256 || N % 256 ||
+      (reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D) | reinterpret_cast<uintptr_t>(pre)) % 16) {
+    g_err = "gemmBf16Dgelu: M and N must be multiples of 256, strides multiples of 8 elements, pointers 16-byte aligned";
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const bool a_mn = flags & GEMM_A_MN, b_mn = flags & GEMM_B_MN;
+  if (a_mn) {
+    g_err = "gemmBf16Dgelu: an MN-major A operand is not built";
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  CUtensorMap pa, pb;
+  if (!makeTensorMap2D(&pa, A, TM_BF16, K, M, lda, BK, 128, &g_err)) return static_cast<int>(cudaErrorInvalidValue);
+  if (!b_mn ? !makeTensorMap2D(&pb, B, TM_BF16, K, N, ldb, BK, 128, &g_err) : !makeTensorMap2D(&pb, B, TM_BF16, N, K, ldb, 64, BK, &g_err))
+    return static_cast<int>(cudaErrorInvalidValue);
+  DgeluEpi epi{static_cast<__nv_bfloat16*>(D), static_cast<const __nv_bfloat16*>(pre), colsum, ldd, M, N};
+  int pair_tiles = (M / 256) * (N / 256);
+  int n_sm = deviceSmCount();
+  if (sms > 0 && sms < n_sm) n_sm = sms;
+  int grid = 2 * (pair_tiles < n_sm / 2 ? pair_tiles : n_sm / 2);
+  return b_mn ? launchPair<false, true, DgeluEpi>(pa, pb, epi, K, grid, status, stream)
+              : launchPair<false, false, DgeluEpi>(pa, pb, epi, K, grid, status, stream);
 }
 
 }  // namespace pccl

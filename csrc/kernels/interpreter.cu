@@ -119,14 +119,36 @@ __device__ __forceinline__ void mm_st_range(char* mc_dst, const char* src, uint6
 __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ InterpLaunch L) {
   const InterpRank& R = L.r[blockIdx.y];
   const int stream = blockIdx.x;
-  if (stream >= R.n_streams) return;
+  const bool turns = L.turn_slot != kNoTurnSlot;
+  // a rank without instructions still takes its turn on the lane (one CTA that only runs the hand-shake)
+  const int n_workers = turns && R.n_streams == 0 ? 1 : R.n_streams;
+  if (stream >= n_workers) return;
   __shared__ uint32_t s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
 
   const World& W = L.w;
   const int me = R.rank;
-  uint64_t* my_sig = reinterpret_cast<uint64_t*>(W.heap[me] + W.signal_off) + L.slot_base;
+  uint64_t* const sig0 = reinterpret_cast<uint64_t*>(W.heap[me] + W.signal_off);
+  uint64_t* my_sig = sig0 + L.slot_base;
+  if (turns && L.launch_no >= 2) {
+    // nobody may still be using the scratch half of launch_no - 2 when this launch starts to write it
+    if (threadIdx.x == 0) {
+      for (int q = 0; q < W.world; ++q)
+        if (q != me && !wait_ge(sig0 + L.turn_slot + q, L.launch_no - 1, L.spin_limit, R.status)) { s_fail = ST_TIMEOUT; break; }
+    }
+    __syncthreads();
+    if (s_fail) {
+      if (threadIdx.x == 0) report(R.status, ST_TIMEOUT, static_cast<uint32_t>(stream), 0xffffu, OP_WAIT);
+      return;
+    }
+  }
+  if (R.n_streams == 0) {
+    if (threadIdx.x == 0)
+      for (int q = 0; q < W.world; ++q)
+        if (q != me) red_add_release_sys(reinterpret_cast<uint64_t*>(W.heap[q] + W.signal_off) + L.turn_slot + me, 1);
+    return;
+  }
   const Instr* prog = R.instrs + R.stream_start[stream];
   uint64_t* const trace = R.trace ? R.trace + 2ull * R.stream_start[stream] : nullptr;
 
@@ -234,6 +256,18 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
       return;
     }
   }
+  if (turns) {
+    // the last stream of this rank to end tells every peer that the rank has left this launch's scratch half
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      unsigned int* fin = reinterpret_cast<unsigned int*>(sig0 + L.finish_slot);
+      if (atomicInc(fin, static_cast<unsigned int>(n_workers - 1)) == static_cast<unsigned int>(n_workers - 1)) {
+        for (int q = 0; q < W.world; ++q)
+          if (q != me) red_add_release_sys(reinterpret_cast<uint64_t*>(W.heap[q] + W.signal_off) + L.turn_slot + me, 1);
+      }
+    }
+  }
 }
 
 __global__ void wait_timeout_probe_kernel(uint64_t* flag, uint64_t spin_limit, uint32_t* status) {
@@ -247,6 +281,7 @@ __global__ void wait_timeout_probe_kernel(uint64_t* flag, uint64_t spin_limit, u
 int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream) {
   int max_streams = 0;
   for (int v = 0; v < L.nvirt; ++v) max_streams = L.r[v].n_streams > max_streams ? L.r[v].n_streams : max_streams;
+  if (max_streams == 0 && L.turn_slot != kNoTurnSlot) max_streams = 1;      // the lane's hand-shake still runs
   if (max_streams == 0) return 0;
   dim3 grid(max_streams, L.nvirt), block(threads);
   void* args[] = {const_cast<InterpLaunch*>(&L)};

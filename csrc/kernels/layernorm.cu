@@ -4,6 +4,12 @@
 // share of dgamma / dbeta in registers across all of its rows and writes one partial row at the end;
 // a second small kernel adds the partial rows.  (PyTorch's stock backward takes two kernels and ~230 us
 // per call at 16384 x 2048; this takes ~60 us.)
+//
+// Both directions can carry the residual connection that surrounds the norm in a pre-norm transformer block:
+// forward takes `delta` and computes s = x + delta (stored, it is the next residual stream) and y = LN(s) in one
+// pass; backward adds the gradient that arrives on the residual stream (`dres`) to the norm's input gradient, and
+// can emit the column sums of that total -- the bias gradient of the linear layer that produced `delta` -- next
+// to dgamma / dbeta.  That removes the separate element-wise add kernels and one pass per bias gradient.
 #include <cuda_bf16.h>
 
 #include "elementwise_api.h"
@@ -44,7 +50,8 @@ __device__ __forceinline__ void block_sum2(float a, float b, float* scratch, flo
 }
 
 template <int MAXV>
-__global__ void __launch_bounds__(256) ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+__global__ void __launch_bounds__(256) ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                                                     __nv_bfloat16* __restrict__ sum_out, const __nv_bfloat16* __restrict__ gamma,
                                                      const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
                                                      float* __restrict__ mean, float* __restrict__ rstd, int D, float eps) {
   __shared__ float scratch[8];
@@ -57,6 +64,16 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(const __nv_bfloat16* __rest
     const int v = threadIdx.x + j * 256;
     if (v < nvec) {
       unpack<DT_BF16>(ld16(x + row * D + v * 8), f[j]);
+      if (delta) {
+        // the norm sees the sum as it is stored (rounded to bf16), so that backward, which re-reads it, agrees
+        float d[8];
+        unpack<DT_BF16>(ld16(delta + row * D + v * 8), d);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[j][k] += d[k];
+        const Vec16 r = pack<DT_BF16>(f[j]);
+        st16(sum_out + row * D + v * 8, r);
+        unpack<DT_BF16>(r, f[j]);
+      }
 #pragma unroll
       for (int k = 0; k < 8; ++k) s += f[j][k];
     }
@@ -90,16 +107,17 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(const __nv_bfloat16* __rest
 template <int MAXV>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                      const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean,
-                                                     const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
-                                                     float* __restrict__ part_g, float* __restrict__ part_b, long long rows, int D) {
+                                                     const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dres,
+                                                     __nv_bfloat16* __restrict__ dx, float* __restrict__ part_g,
+                                                     float* __restrict__ part_b, float* __restrict__ part_c, long long rows, int D) {
   __shared__ float scratch[16];
   const int nvec = D >> 3;
-  float g[MAXV][8], ag[MAXV][8], ab[MAXV][8];
+  float g[MAXV][8], ag[MAXV][8], ab[MAXV][8], ac[MAXV][8];
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
     const int v = threadIdx.x + j * 256;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) { ag[j][k] = 0.f; ab[j][k] = 0.f; g[j][k] = 0.f; }
+    for (int k = 0; k < 8; ++k) { ag[j][k] = 0.f; ab[j][k] = 0.f; ac[j][k] = 0.f; g[j][k] = 0.f; }
     if (v < nvec) unpack<DT_BF16>(ld16(gamma + v * 8), g[j]);
   }
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -135,6 +153,16 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
         float o[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = rs * (dg[j][k] - m1 - xh[j][k] * m2);
+        if (dres) {
+          float r[8];
+          unpack<DT_BF16>(ld16(dres + row * D + v * 8), r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] += r[k];
+        }
+        if (part_c) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) ac[j][k] += o[k];
+        }
         st16(dx + row * D + v * 8, pack<DT_BF16>(o));
       }
     }
@@ -147,64 +175,134 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
       float* pb = part_b + static_cast<long long>(blockIdx.x) * D + v * 8;
       st16(pg, pack<DT_F32>(ag[j])); st16(pg + 4, pack<DT_F32>(ag[j] + 4));
       st16(pb, pack<DT_F32>(ab[j])); st16(pb + 4, pack<DT_F32>(ab[j] + 4));
+      if (part_c) {
+        float* pc = part_c + static_cast<long long>(blockIdx.x) * D + v * 8;
+        st16(pc, pack<DT_F32>(ac[j])); st16(pc + 4, pack<DT_F32>(ac[j] + 4));
+      }
     }
   }
 }
 
-// 32 columns x 8 partial-row lanes per CTA: the partial rows are summed eight at a time in parallel
-__global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ part_g, const float* __restrict__ part_b,
-                                                            __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta,
-                                                            int nparts, int D) {
-  __shared__ float sg[8][33], sb[8][33];
-  const int col = blockIdx.x * 32 + (threadIdx.x & 31), lane8 = threadIdx.x >> 5;
-  float g = 0.f, b = 0.f;
+// Adds the partial rows of up to three arrays [nparts, D] column by column into bf16 vectors of length D.  A CTA owns
+// 32 columns; its 32 warps each walk every 32nd partial row, so the rows are read 32 at a time with full coalescing.
+struct ReduceJob {
+  const float* part[3];
+  __nv_bfloat16* out[3];
+  int n;
+};
+
+__global__ void __launch_bounds__(1024) partial_rows_reduce_kernel(ReduceJob job, int nparts, int D) {
+  __shared__ float sm[3][32][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
+  float acc[3] = {0.f, 0.f, 0.f};
   if (col < D) {
-    for (int p = lane8; p < nparts; p += 8) {
-      g += part_g[static_cast<long long>(p) * D + col];
-      b += part_b[static_cast<long long>(p) * D + col];
+    for (int p = warp; p < nparts; p += 32) {
+#pragma unroll
+      for (int a = 0; a < 3; ++a)
+        if (a < job.n) acc[a] += job.part[a][static_cast<long long>(p) * D + col];
     }
   }
-  sg[lane8][threadIdx.x & 31] = g;
-  sb[lane8][threadIdx.x & 31] = b;
-  __syncthreads();
-  if (lane8 == 0 && col < D) {
 #pragma unroll
-    for (int k = 1; k < 8; ++k) { g += sg[k][threadIdx.x]; b += sb[k][threadIdx.x]; }
-    dgamma[col] = __float2bfloat16_rn(g);
-    dbeta[col] = __float2bfloat16_rn(b);
+  for (int a = 0; a < 3; ++a) sm[a][warp][lane] = acc[a];
+  __syncthreads();
+  if (warp < job.n && col < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t += sm[warp][k][lane];
+    job.out[warp][col] = __float2bfloat16_rn(t);
+  }
+}
+
+// Column sums of a bf16 matrix [rows, N] (row stride ld): the bias gradient of a linear layer whose output gradient
+// comes from elsewhere.  A CTA owns 256 columns (one 16-byte vector per lane, 8 warps = 8 rows at a time) and a block
+// of rows; it writes one partial row, which partial_rows_reduce_kernel adds up.
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long ld, long long rows, int N,
+                                                             int rows_per_part, float* __restrict__ part) {
+  __shared__ float sm[8][256 + 8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_part;
+  const long long r1 = r0 + rows_per_part < rows ? r0 + rows_per_part : rows;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < N) {
+    long long r = r0 + warp;
+    for (; r + 8 < r1; r += 16) {          // two independent loads in flight
+      float a[8], b[8];
+      const Vec16 va = ld16(x + r * ld + col), vb = ld16(x + (r + 8) * ld + col);
+      unpack<DT_BF16>(va, a);
+      unpack<DT_BF16>(vb, b);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += a[k] + b[k];
+    }
+    for (; r < r1; r += 8) {
+      float a[8];
+      unpack<DT_BF16>(ld16(x + r * ld + col), a);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += a[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) sm[warp][lane * 8 + k] = acc[k];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sm[w][threadIdx.x];
+    part[static_cast<long long>(blockIdx.y) * N + c] = t;
   }
 }
 
 }  // namespace
 
-int launchLayerNormFwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, long long rows, int D,
-                       float eps, cudaStream_t stream) {
+int launchLayerNormFwd(const void* x, const void* delta, void* sum_out, const void* gamma, const void* beta, void* y, float* mean,
+                       float* rstd, long long rows, int D, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (D % 8 || D > 8192) return static_cast<int>(cudaErrorInvalidValue);
+  if (D % 8 || D > 8192 || (delta && !sum_out)) return static_cast<int>(cudaErrorInvalidValue);
   auto X = static_cast<const __nv_bfloat16*>(x); auto G = static_cast<const __nv_bfloat16*>(gamma);
   auto B = static_cast<const __nv_bfloat16*>(beta); auto Y = static_cast<__nv_bfloat16*>(y);
+  auto DL = static_cast<const __nv_bfloat16*>(delta); auto S = static_cast<__nv_bfloat16*>(sum_out);
   const unsigned grid = static_cast<unsigned>(rows);
-  if (D <= 2048) ln_fwd_kernel<1><<<grid, 256, 0, stream>>>(X, G, B, Y, mean, rstd, D, eps);
-  else if (D <= 4096) ln_fwd_kernel<2><<<grid, 256, 0, stream>>>(X, G, B, Y, mean, rstd, D, eps);
-  else ln_fwd_kernel<4><<<grid, 256, 0, stream>>>(X, G, B, Y, mean, rstd, D, eps);
+  if (D <= 2048) ln_fwd_kernel<1><<<grid, 256, 0, stream>>>(X, DL, S, G, B, Y, mean, rstd, D, eps);
+  else if (D <= 4096) ln_fwd_kernel<2><<<grid, 256, 0, stream>>>(X, DL, S, G, B, Y, mean, rstd, D, eps);
+  else ln_fwd_kernel<4><<<grid, 256, 0, stream>>>(X, DL, S, G, B, Y, mean, rstd, D, eps);
   return static_cast<int>(cudaGetLastError());
 }
 
-int layerNormBwdParts(long long rows) { return static_cast<int>(rows < 148 * 8 ? rows : 148 * 8); }
+int layerNormBwdParts(long long rows) { return static_cast<int>(rows < 148 * 4 ? rows : 148 * 4); }
 
-int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx, void* dgamma,
-                       void* dbeta, float* partials, long long rows, int D, cudaStream_t stream) {
+int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres, void* dx,
+                       void* dgamma, void* dbeta, void* dcolsum, float* partials, long long rows, int D, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D % 8 || D > 8192) return static_cast<int>(cudaErrorInvalidValue);
   const int parts = layerNormBwdParts(rows);
   float* pg = partials;
   float* pb = partials + static_cast<long long>(parts) * D;
+  float* pc = dcolsum ? partials + 2ll * parts * D : nullptr;
   auto DY = static_cast<const __nv_bfloat16*>(dy); auto X = static_cast<const __nv_bfloat16*>(x);
   auto G = static_cast<const __nv_bfloat16*>(gamma); auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (D <= 2048) ln_bwd_kernel<1><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DX, pg, pb, rows, D);
-  else if (D <= 4096) ln_bwd_kernel<2><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DX, pg, pb, rows, D);
-  else ln_bwd_kernel<4><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DX, pg, pb, rows, D);
-  ln_bwd_reduce_kernel<<<(D + 31) / 32, 256, 0, stream>>>(pg, pb, static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta), parts, D);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  if (D <= 2048) ln_bwd_kernel<1><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
+  else if (D <= 4096) ln_bwd_kernel<2><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
+  else ln_bwd_kernel<4><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
+  ReduceJob job{{pg, pb, pc}, {static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta), static_cast<__nv_bfloat16*>(dcolsum)},
+                dcolsum ? 3 : 2};
+  partial_rows_reduce_kernel<<<(D + 31) / 32, 1024, 0, stream>>>(job, parts, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int colSumParts(long long rows) { return static_cast<int>((rows + 255) / 256 < 64 ? (rows + 255) / 256 : 64); }
+
+int launchColSum(const void* x, long long ld, long long rows, int N, void* out_bf16, float* partials, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  if (N % 8 || ld % 8 || reinterpret_cast<uintptr_t>(x) % 16) return static_cast<int>(cudaErrorInvalidValue);
+  const int parts = colSumParts(rows);
+  const int rows_per_part = static_cast<int>((rows + parts - 1) / parts);
+  dim3 grid((N + 255) / 256, parts);
+  colsum_partial_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ld, rows, N, rows_per_part, partials);
+  ReduceJob job{{partials, nullptr, nullptr}, {static_cast<__nv_bfloat16*>(out_bf16), nullptr, nullptr}, 1};
+  partial_rows_reduce_kernel<<<(N + 31) / 32, 1024, 0, stream>>>(job, parts, N);
   return static_cast<int>(cudaGetLastError());
 }
 

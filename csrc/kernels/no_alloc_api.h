@@ -15,7 +15,12 @@
 //     that device current) -- make that first call outside any stream capture;
 //   * it calls no cudaMalloc / cudaFree and no allocating library routine;
 //   * all calls on a device share the array: two calls that overlap on the GPU (different streams)
-//     race on it.  Nothing in it needs to start at zero: every launch rewrites the rows it then sums.
+//     race on it.  Nothing in it needs to start at zero: every launch rewrites the rows it then sums;
+//   * targets must lie in [0, vocab).  There is no ignore value to pass: a target outside that range (the
+//     customary -100 included) makes an ignored row -- its loss is 0, its gradient is all zeros, nothing outside the
+//     row is read -- and the mean is still taken over all `rows`;
+//   * the per-device set-up state is written without a lock: two host threads that make the first call on one
+//     device at the same moment both store the same values, which is harmless.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -33,7 +38,7 @@ enum {
 };
 
 // logits: device, bf16 [rows, vocab] with row stride `ld` elements (multiple of 8, base 16-byte aligned)
-// targets: device, int64 [rows]; mean_loss: device, one float (output)
+// targets: device, int64 [rows], each in [0, vocab) (anything else: ignored row, see above); mean_loss: device, one float (output)
 // Asynchronous on `stream`.  Returns one of the codes above.
 __attribute__((visibility("default")))
 int pccl_cross_entropy_mean_noalloc(void* logits, const long long* targets, float* mean_loss, long long rows, int vocab,

@@ -26,17 +26,6 @@ NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
-def _cutlass_include() -> list:
-    """CuTe/CUTLASS headers vendored in site-packages (used by kernels that include them)."""
-    import site
-    for sp in site.getsitepackages():
-        for rel in ("flashinfer/data/cutlass/include", "tilelang/3rdparty/cutlass/include"):
-            p = Path(sp) / rel
-            if p.exists():
-                return [f"-I{p}"]
-    return []
-
-
 def _flags():
     import pybind11
     inc = [f"-I{CSRC}", f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
@@ -108,7 +97,7 @@ def build(verbose: bool = True, force: bool = False, ptxas_info: bool = False, s
         with ThreadPoolExecutor(max_workers=max(2, (os.cpu_count() or 4))) as ex:
             for s in cc:
                 jobs.append(ex.submit(_compile, cxx, s, hdr, verbose))
-            extra = _cutlass_include() + (["-Xptxas", "-v"] if ptxas_info else [])
+            extra = ["-Xptxas", "-v"] if ptxas_info else []
             for s in cu:
                 jobs.append(ex.submit(_compile, nv, s, hdr, verbose, extra))
             results = [j.result() for j in jobs]

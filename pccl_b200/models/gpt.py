@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..nn.linear import Embedding, Linear, LinearGelu, _LinearFn
+from ..nn.linear import Embedding, Linear, LinearGelu, _LinearFn, mlp
 from ..nn.loss import fused_cross_entropy
 from ..nn.norm import LayerNorm
 
@@ -65,13 +65,20 @@ class Block(nn.Module):
         self.fc1 = LinearGelu(d, cfg.mlp_ratio * d, device=device)
         self.fc2 = Linear(cfg.mlp_ratio * d, d, device=device, init_std=0.02 / math.sqrt(2 * cfg.n_layer))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], prev_bias: Optional[torch.Tensor]):
+        """The residual stream travels as ``(x, delta)``: the sum is formed inside the LayerNorm kernel that needs it.
+        Returns the block's own ``(x, delta, bias of the layer that made delta)`` for the next norm to finish."""
         B, T, D = x.shape
-        qkv = self.qkv(self.ln1(x)).view(B, T, 3, self.n_head, D // self.n_head)
+        if delta is None:
+            h = self.ln1(x)
+        else:
+            x, h = self.ln1.add_norm(x, delta, prev_bias)
+        qkv = self.qkv(h).view(B, T, 3, self.n_head, D // self.n_head)
         q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))    # unbind: one stacked gradient, no zero-fills
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        x = x + self.proj(a.transpose(1, 2).reshape(B, T, D))
-        return x + self.fc2(self.fc1(self.ln2(x)))
+        d_attn = self.proj(a.transpose(1, 2).reshape(B, T, D), defer_bias_grad=True)
+        x, h = self.ln2.add_norm(x, d_attn, self.proj.bias)
+        return x, mlp(h, self.fc1, self.fc2, defer_fc2_bias_grad=True), self.fc2.bias
 
 
 class GPT(nn.Module):
@@ -91,9 +98,10 @@ class GPT(nn.Module):
         B, T = ids.shape
         pos = torch.arange(T, device=ids.device)
         x = self.wte(ids) + self.wpe(pos)[None]
+        delta, prev_bias = None, None
         for blk in self.blocks:
-            x = blk(x)
-        x = self.ln_f(x)
+            x, delta, prev_bias = blk(x, delta, prev_bias)
+        _, x = self.ln_f.add_norm(x, delta, prev_bias)
         w = self.wte.weight if self.cfg.tie_embeddings else self.lm_head.weight
         return _LinearFn.apply(x, w, None)          # [B, T, vocab]; rows padded to a multiple of 8
 

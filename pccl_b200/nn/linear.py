@@ -12,7 +12,8 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
-from ..ops.gemm import gemm
+from ..ops.elementwise import colsum
+from ..ops.gemm import gemm, gemm_dgelu
 
 
 def _as_operand(t: torch.Tensor) -> torch.Tensor:
@@ -47,7 +48,10 @@ def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor) -> O
 def _bias_grad(dy2: torch.Tensor, bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if bias is None:
         return None
-    db = dy2.sum(0, dtype=torch.float32).to(bias.dtype)
+    if dy2.shape[1] % 8 == 0 and dy2.is_cuda:
+        db = colsum(dy2)
+    else:
+        db = dy2.sum(0, dtype=torch.float32).to(bias.dtype)
     mg = _grad_target(bias)
     if mg is None:
         return db
@@ -60,12 +64,20 @@ def _bias_grad(dy2: torch.Tensor, bias: Optional[torch.Tensor]) -> Optional[torc
 
 
 class _LinearFn(torch.autograd.Function):
+    """y = x W^T + b (+ residual).  ``defer_bias_grad``: the bias gradient is produced elsewhere (by the fused
+    residual-add + LayerNorm that consumes y, which sums the same rows anyway), so backward skips it."""
+
     @staticmethod
-    def forward(ctx, x, weight, bias):
+    def forward(ctx, x, weight, bias, residual=None, defer_bias_grad=False):
         x2 = _as_operand(x)
-        y = gemm(x2, weight, bias=bias)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, weight.shape[0])
+        y = gemm(x2, weight, bias=bias, residual=res2)
         ctx.save_for_backward(x2, weight, bias)
         ctx.x_shape = x.shape
+        ctx.defer_bias_grad = defer_bias_grad
+        ctx.has_residual = residual is not None
         return y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -74,8 +86,8 @@ class _LinearFn(torch.autograd.Function):
         dy2 = _as_operand(dy)
         dx = gemm(dy2, weight, b_t=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         dw = _weight_grad(dy2, x2, weight)
-        db = _bias_grad(dy2, bias)
-        return dx, dw, db
+        db = None if ctx.defer_bias_grad else _bias_grad(dy2, bias)
+        return dx, dw, db, (dy if ctx.has_residual else None), None
 
 
 class _LinearGeluFn(torch.autograd.Function):
@@ -101,6 +113,55 @@ class _LinearGeluFn(torch.autograd.Function):
         return dx, dw, db
 
 
+class _MlpFn(torch.autograd.Function):
+    """out = gelu_tanh(x W1^T + b1) W2^T + b2 as one autograd node, so that backward can fuse across the two layers:
+    the GEMM that turns the output gradient into the activation gradient applies gelu' in its epilogue and sums the
+    columns of its result (the first bias gradient) on the way out -- no GELU-backward kernel, no separate reduction,
+    and the activation gradient never visits memory."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, defer_b2_grad=False):
+        x2 = _as_operand(x)
+        act = torch.empty((x2.shape[0], w1.shape[0]), dtype=torch.bfloat16, device=x.device)
+        pre = gemm(x2, w1, bias=b1, gelu_out=act)
+        out = gemm(act, w2, bias=b2)
+        ctx.save_for_backward(x2, w1, b1, w2, b2, pre, act)
+        ctx.x_shape = x.shape
+        ctx.defer_b2_grad = defer_b2_grad
+        return out.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dz):
+        x2, w1, b1, w2, b2, pre, act = ctx.saved_tensors
+        dz2 = _as_operand(dz)
+        rows, n1 = pre.shape
+        if rows % 256 == 0 and n1 % 256 == 0:
+            sums = torch.zeros(n1, dtype=torch.float32, device=pre.device) if b1 is not None else None
+            dy2 = gemm_dgelu(dz2, w2, pre, b_t=True, colsum=sums)
+            db1 = _deliver_bias(b1, sums.to(b1.dtype)) if b1 is not None else None
+        else:
+            dact = gemm(dz2, w2, b_t=True)
+            dy2 = torch.ops.aten.gelu_backward(dact, pre, approximate="tanh")
+            db1 = _bias_grad(dy2, b1)
+        dw2 = _weight_grad(dz2, act, w2)
+        db2 = None if ctx.defer_b2_grad else _bias_grad(dz2, b2)
+        dx = gemm(dy2, w1, b_t=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw1 = _weight_grad(dy2, x2, w1)
+        return dx, dw1, db1, dw2, db2, None
+
+
+def _deliver_bias(bias: torch.Tensor, db: torch.Tensor) -> Optional[torch.Tensor]:
+    mg = _grad_target(bias)
+    if mg is None:
+        return db
+    if getattr(bias, "_pccl_written", False):
+        mg.add_(db)
+    else:
+        mg.copy_(db)
+    _finish_main_grad(bias)
+    return None
+
+
 class Linear(nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=torch.bfloat16,
                  init_std: float = 0.02):
@@ -112,8 +173,15 @@ class Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
         nn.init.normal_(self.weight, std=init_std)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return _LinearFn.apply(x, self.weight, self.bias)
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, defer_bias_grad: bool = False) -> torch.Tensor:
+        """``residual`` is added in the GEMM epilogue.  ``defer_bias_grad=True`` promises that the consumer of the output
+        (``LayerNorm.add_norm(..., prev_bias=self.bias)``) produces this layer's bias gradient."""
+        return _LinearFn.apply(x, self.weight, self.bias, residual, defer_bias_grad)
+
+
+def mlp(x: torch.Tensor, fc1: "Linear", fc2: "Linear", defer_fc2_bias_grad: bool = False) -> torch.Tensor:
+    """``fc2(gelu_tanh(fc1(x)))`` with the two layers' backward passes fused (see ``_MlpFn``)."""
+    return _MlpFn.apply(x, fc1.weight, fc1.bias, fc2.weight, fc2.bias, defer_fc2_bias_grad)
 
 
 class LinearGelu(Linear):

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from .._native import C
-from .gemm import count_launch
+from .gemm import count_launch, status_words
 
 
 def adamw_step(master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, grad: torch.Tensor,
@@ -26,7 +26,9 @@ def adamw_step(master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Te
 def cross_entropy_(logits: torch.Tensor, targets: torch.Tensor, *, grad_scale: float = 1.0,
                    ignore_index: int = -100) -> torch.Tensor:
     """Per-row losses of ``logits`` (bf16 [rows, vocab], row stride a multiple of 8); the logits are
-    replaced in place by ``(softmax - onehot) * grad_scale``."""
+    replaced in place by ``(softmax - onehot) * grad_scale``.  Targets must lie in [0, vocab) or equal
+    ``ignore_index``; any other value yields an ignored row (loss 0, zero gradient) and sets the device status
+    words, so the next ``check_status`` raises."""
     if logits.dtype != torch.bfloat16 or logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("cross_entropy_: bf16 [rows, vocab] logits with unit inner stride expected")
     rows, vocab = logits.shape
@@ -35,6 +37,20 @@ def cross_entropy_(logits: torch.Tensor, targets: torch.Tensor, *, grad_scale: f
         raise ValueError("cross_entropy_: int64 targets, one per row")
     loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
     C.cross_entropy(logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), rows, vocab, logits.stride(0), grad_scale,
-                    ignore_index, torch.cuda.current_stream().cuda_stream)
+                    ignore_index, status_words(logits.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     count_launch()
     return loss
+
+
+def colsum(x: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """Column sums (fp32 accumulation) of a bf16 matrix [rows, N] with unit inner stride, as bf16 [N]: the bias gradient of
+    a linear layer.  Two short kernels (partial rows, then their sum) that run near memory bandwidth."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1 or x.stride(0) % 8 or x.shape[1] % 8 or x.data_ptr() % 16:
+        raise ValueError("colsum: bf16 [rows, N] with unit inner stride, N and the row stride multiples of 8, 16-byte aligned")
+    rows, n = x.shape
+    if out is None:
+        out = torch.empty(n, dtype=torch.bfloat16, device=x.device)
+    partials = torch.empty(C.colsum_parts(rows) * n, dtype=torch.float32, device=x.device)
+    C.colsum(x.data_ptr(), x.stride(0), rows, n, out.data_ptr(), partials.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    count_launch(2)
+    return out

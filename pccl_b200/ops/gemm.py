@@ -56,11 +56,13 @@ def _check(t: torch.Tensor, name: str) -> None:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          bias: Optional[torch.Tensor] = None, gelu_out: Optional[torch.Tensor] = None,
-         accumulate: bool = False, sms: int = 0, pair: Optional[bool] = None) -> torch.Tensor:
+         accumulate: bool = False, sms: int = 0, pair: Optional[bool] = None,
+         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = op(a) @ op(b)`` with ``op(a) = a.T if a_t else a`` (a: [M,K] or [K,M]) and
     ``op(b) = b if b_t else b.T`` (b: [N,K], or [K,N] when ``b_t``).  So the default is the linear
     layer form ``a @ b.T``.  ``bias`` (bf16 [N]) is added; ``gelu_out`` receives gelu_tanh(out).
-    ``pair`` selects the CTA-pair kernel (cta_group::2, 256 x 256 tiles); default from PCCL_GEMM_PAIR."""
+    ``pair`` selects the CTA-pair kernel (cta_group::2, 256 x 256 tiles); default from PCCL_GEMM_PAIR.
+    ``residual`` (bf16, out's shape and strides) is added in the epilogue: ``out = a @ b.T + bias + residual``."""
     _check(a, "a")
     _check(b, "b")
     M, K = (a.shape[1], a.shape[0]) if a_t else (a.shape[0], a.shape[1])
@@ -96,8 +98,39 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
             raise ValueError("gemm: gelu_out must match out")
         flags |= C.GEMM_GELU
         d2 = gelu_out.data_ptr()
+    if residual is not None:
+        if gelu_out is not None or out.dtype != torch.bfloat16 or residual.dtype != torch.bfloat16 or residual.shape != out.shape \
+                or residual.stride() != out.stride() or residual.data_ptr() % 16:
+            raise ValueError("gemm: residual must be bf16 with out's shape and strides (and excludes gelu_out)")
+        flags |= C.GEMM_ADD_D2
+        d2 = residual.data_ptr()
     C.gemm_bf16(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), M, N, K, flags,
                 bias_ptr, d2, sms, status_words(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    count_launch()
+    return out
+
+
+def gemm_dgelu(a: torch.Tensor, b: torch.Tensor, pre: torch.Tensor, *, b_t: bool = False, colsum: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None, sms: int = 0) -> torch.Tensor:
+    """``out = (a @ op(b)) * gelu_tanh'(pre)`` in one kernel (the GELU derivative is applied in the GEMM epilogue), and,
+    when ``colsum`` (fp32 [N], zeroed by the caller) is given, ``colsum += out.sum(0)``.  This is the step of an MLP's
+    backward pass that turns the gradient of the second layer's input into the gradient of the first layer's output;
+    the column sums are the first layer's bias gradient.  M and N must be multiples of 256."""
+    _check(a, "a")
+    _check(b, "b")
+    M, K = a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_t else (b.shape[0], b.shape[1])
+    if K != Kb or pre.shape != (M, N) or pre.dtype != torch.bfloat16 or pre.stride(1) != 1:
+        raise ValueError("gemm_dgelu: shapes of a, b and pre do not match")
+    if out is None:
+        out = torch.empty_strided((M, N), pre.stride(), dtype=torch.bfloat16, device=a.device)
+    if out.stride() != pre.stride() or out.dtype != torch.bfloat16:
+        raise ValueError("gemm_dgelu: out must have pre's strides")
+    if colsum is not None and (colsum.dtype != torch.float32 or colsum.numel() != N or not colsum.is_contiguous()):
+        raise ValueError("gemm_dgelu: colsum must be a contiguous fp32 vector of length N")
+    C.gemm_bf16_dgelu(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(), out.stride(0), pre.data_ptr(),
+                      colsum.data_ptr() if colsum is not None else 0, M, N, K, C.GEMM_B_MN if b_t else 0, sms,
+                      status_words(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     count_launch()
     return out
 

@@ -537,3 +537,30 @@ def test_moe_route_and_plan_kernels_match_tensor_ops(native):
     assert ((rows >= off[flat]) & (rows < off[flat + 1])).all()
     assert torch.equal(rows.sort().values, ref_rows.sort().values)
     del moe, eng
+
+
+@pytest.mark.parametrize("algo", ["ring_allreduce", "direct_allreduce", "direct_reduce_scatter", "direct_allgather", "alltoall"])
+def test_engine_regop_exeop_on_a_cuda_engine_with_alternating_widths(native, algo):
+    """The public path initEngine("cuda") -> regOp -> exeOp on a world of one: the program is materialised per width,
+    every (program, width) pair gets its own signal words and launch count, the scratch half alternates per launch, and
+    the interpreter kernel runs it on the GPU.  A world of one keeps every wait inside one launch."""
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import build
+    eng = Engine(0, 1)
+    eng.initEngine("cuda", heap_bytes=64 << 20)
+    eng.regOp("op", build(algo, 1, channels=2))
+    n = 3 * 8192 + 16
+    for it, width in enumerate([1, 4, 1, 4, 2, 4]):
+        x = torch.arange(n, device="cuda", dtype=torch.float32) + it
+        y = torch.full((n,), -1.0, device="cuda")
+        eng.exeOp("op", x, y, width=width, check=True)
+        assert torch.equal(y, x), (algo, it, width)
+    st = eng.stats()
+    assert st["ops"]["op"]["launches"] == 6 and st["device"] == "cuda" and st["signals_used"] > 0
+    # a symmetric (heap) tensor works as well, and in place
+    z = eng.symmetric_tensor((n,), torch.float32)
+    z.copy_(torch.arange(n, device="cuda", dtype=torch.float32))
+    if algo.endswith("allreduce"):
+        eng.exeOp("op", z, width=2, check=True)
+        assert torch.equal(z, torch.arange(n, device="cuda", dtype=torch.float32))
+    del eng

@@ -464,3 +464,70 @@ def test_traces_of_all_ranks_merge_into_one_document(tmp_path):
     stats = summarize(str(tmp_path / "all.json"))
     assert stats["COPY"]["count"] >= 4 and stats["REDUCE"]["count"] == 2 and stats["REDUCE"]["bytes"] == 2 * 8192
     assert stats["WAIT"]["bytes"] == 0 and stats["COPY"]["gbs"] > 0
+
+
+def _interleaved_rank(rank, world, port):
+    """all-reduce, then a send between two OTHER ranks, then the all-reduce again, on one workspace lane; one rank is
+    slowed down before every instruction."""
+    import torch
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, build
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("ring_allreduce", world, channels=1, device_type=DeviceType.CPU))
+    e.regOp("p2p", build("send_recv", world, channels=1, device_type=DeviceType.CPU, src=0, dst=1))
+    g = torch.Generator().manual_seed(11)
+    xs = [torch.rand(3 * 4096, generator=g) for _ in range(world)]
+    errs = []
+    for it in range(4):
+        y = torch.zeros_like(xs[rank])
+        e.exeOp("ar", xs[rank] + it, y)
+        errs.append((y - (sum(xs) + it * world)).abs().max().item())
+        z = torch.zeros(64)
+        e.exeOp("p2p", torch.full((64,), float(it)), z)        # ranks other than 0 and 1 run an empty program
+        if rank == 1:
+            errs.append((z - it).abs().max().item())
+    e.exitCluster()
+    return max(errs)
+
+
+def test_programs_interleaved_on_one_lane_do_not_overrun_a_slow_ranks_scratch():
+    """The scratch half of launch n is the half of launch n - 2.  Between two all-reduces sits a program that does not
+    involve rank 2, so nothing in the programs themselves keeps rank 2 from starting the second all-reduce while the
+    slowed-down rank still reads the first one's scratch; the engine's per-lane turn-taking does."""
+    res = run_ranks(_interleaved_rank, 3, env={"PCCL_WORKSPACE_MB": "8", "PCCL_EXEC_DELAY_US": "3000", "PCCL_EXEC_DELAY_RANK": "0"},
+                    timeout=300)
+    for r in range(3):
+        assert res[r] < 1e-5, res
+
+
+def _rebind_rank(rank, world, port):
+    """Launch, rebind to the same world (every counter starts over), reconnect, launch again."""
+    import torch
+    from _ranks import free_port  # noqa: F401
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import DeviceType, build
+    e = Engine(rank, world); e.initEngine("cpu"); e.joinCluster(f"127.0.0.1:{port}")
+    e.regOp("ar", build("ring_allreduce", world, channels=1, device_type=DeviceType.CPU))
+    xs = [torch.arange(2048, dtype=torch.float32) * (r + 1) for r in range(world)]
+    errs = []
+    for it in range(3):
+        y = torch.zeros(2048)
+        e.exeOp("ar", xs[rank], y)
+        errs.append((y - sum(xs)).abs().max().item())
+    docs_before = e.exportEndpoint()
+    e.exitCluster()
+    e.rebind(rank, world)
+    e.joinCluster(f"127.0.0.1:{port + 1}")
+    for it in range(3):                      # after a rebind the signal words were cleared and the epochs restarted
+        y = torch.zeros(2048)
+        st = e.exeOp("ar", xs[rank] + it, y)
+        errs.append(float(st))
+        errs.append((y - (sum(xs) + it * world)).abs().max().item())
+    e.exitCluster()
+    return max(errs), len(docs_before) > 0
+
+
+def test_rebind_restarts_every_counter_and_the_engine_runs_again():
+    res = run_ranks(_rebind_rank, 2, env={"PCCL_WORKSPACE_MB": "8"})
+    for r in (0, 1):
+        assert res[r][0] < 1e-5, res

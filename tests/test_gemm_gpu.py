@@ -152,3 +152,50 @@ def test_mx_fp8_gemm_matches_fp32_reference_of_the_quantised_operands(M, N, K):
     assert (out32 - ref).abs().max().item() <= 2e-3 * scale
     out = gemm_mx8(aq, a_s, wq, w_s)
     assert (out.float() - ref).abs().max().item() <= 1e-2 * scale
+
+
+def test_gemm_residual_epilogue_adds_the_residual_stream():
+    """out = a @ b.T + bias + residual in the GEMM epilogue (full and ragged tiles)."""
+    from pccl_b200.ops import gemm, check_status
+    for (M, N, K) in [(512, 1024, 256), (300, 264, 128)]:
+        a, b = _rand((M, K), 21), _rand((N, K), 22, 0.05)
+        bias, res = _rand((N,), 23), _rand((M, N), 24)
+        out = gemm(a, b, bias=bias, residual=res)
+        check_status("gemm residual")
+        ref = a.float() @ b.float().t() + bias.float() + res.float()
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("b_t", [True, False])
+def test_gemm_dgelu_epilogue_and_column_sums(b_t):
+    """(a @ op(b)) * gelu_tanh'(pre) with the column sums of the result, against fp32 PyTorch."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.gemm import gemm_dgelu
+    M, N, K = 512, 768, 256
+    a = _rand((M, K), 31)
+    b = _rand((K, N) if b_t else (N, K), 32, 0.05)
+    pre = _rand((M, N), 33, 1.5)
+    sums = torch.zeros(N, dtype=torch.float32, device="cuda")
+    out = gemm_dgelu(a, b, pre, b_t=b_t, colsum=sums)
+    check_status("gemm dgelu")
+    prod = a.float() @ (b.float() if b_t else b.float().t())
+    x = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(x, approximate="tanh").backward(prod)
+    ref = x.grad
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    assert (sums - ref.sum(0)).abs().max().item() <= 2e-2 * max(1.0, ref.sum(0).abs().max().item())
+    # without column sums the product is the same
+    out2 = gemm_dgelu(a, b, pre, b_t=b_t)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("rows,N", [(16384, 2048), (1000, 520), (37, 8)])
+def test_colsum_kernel_matches_torch(rows, N):
+    from pccl_b200.ops.elementwise import colsum
+    x = _rand((rows, N), 41)
+    got = colsum(x)
+    ref = x.float().sum(0)
+    assert (got.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+    view = _rand((rows, N + 24), 42)[:, 8:8 + N] if N % 8 == 0 and N > 8 else None     # a column slice of a wider buffer
+    if view is not None and view.data_ptr() % 16 == 0:
+        assert (colsum(view).float() - view.float().sum(0)).abs().max().item() <= 1e-2 * max(1.0, view.float().sum(0).abs().max().item())

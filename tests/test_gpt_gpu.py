@@ -45,7 +45,8 @@ def test_gpt_forward_backward_matches_fp32_reference():
     ref_loss, ref_grads = _reference_loss(model, ids, tgt)
     assert abs(loss.item() - ref_loss) < 0.02 * ref_loss
     for name in ("blocks.0.qkv.weight", "blocks.1.fc1.weight", "blocks.1.fc2.weight", "blocks.0.proj.bias", "wte.weight",
-                 "wpe.weight", "blocks.1.ln2.weight"):
+                 "wpe.weight", "blocks.1.ln2.weight", "blocks.0.fc1.bias", "blocks.1.fc2.bias", "blocks.0.fc2.bias", "blocks.1.qkv.bias",
+                 "blocks.0.ln1.weight", "ln_f.bias"):
         got = dict(model.named_parameters())[name].grad.float()
         ref = ref_grads[name]
         denom = ref.abs().max().item() + 1e-8
@@ -68,6 +69,30 @@ def test_fused_cross_entropy_matches_torch():
     loss.backward()
     assert abs(loss.item() - ref.item()) < 1e-3
     assert (x.grad.float() - ref_in.grad).abs().max().item() < 2e-5 + 0.01 * ref_in.grad.abs().max().item()
+
+
+def test_cross_entropy_reports_a_target_outside_the_vocabulary_instead_of_indexing_with_it():
+    """An out-of-range target is never used as an index: its row gets loss 0 and a zero gradient, the first such
+    row is written to the device status words, and ``ignore_index`` itself stays silent."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.elementwise import cross_entropy_
+    import pytest as _pt
+    torch.manual_seed(5)
+    rows, vocab = 32, 512
+    x = (torch.randn(rows, vocab, device="cuda") * 2).bfloat16()
+    tgt = torch.randint(0, vocab, (rows,), device="cuda")
+    tgt[5] = -100
+    check_status("before")
+    quiet = cross_entropy_(x.clone(), tgt, grad_scale=1.0, ignore_index=-100)
+    check_status("ignore_index is not an error")
+    assert quiet[5].item() == 0.0
+    tgt[9] = vocab + 3
+    y = x.clone()
+    loss = cross_entropy_(y, tgt, grad_scale=1.0, ignore_index=-100)
+    assert loss[9].item() == 0.0 and int(y[9].abs().sum()) == 0 and loss[8].item() > 0.0
+    with _pt.raises(RuntimeError, match="device status"):
+        check_status("cross entropy with a bad target")
+    check_status("cleared")
 
 
 def test_adamw_kernel_matches_torch():
@@ -176,3 +201,59 @@ def test_layernorm_kernels_match_fp32_reference(rows, D):
     assert (x.grad.float() - xr.grad).abs().max().item() < 0.03 * max(1.0, xr.grad.abs().max().item())
     assert (ln.weight.grad.float() - wr.grad).abs().max().item() < 0.02 * max(1.0, wr.grad.abs().max().item())
     assert (ln.bias.grad.float() - br.grad).abs().max().item() < 0.02 * max(1.0, br.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("rows,D", [(512, 2048), (300, 256), (64, 4096)])
+def test_fused_residual_add_layernorm_matches_fp32_reference(rows, D):
+    """(x, delta) -> (x + delta, LN(x + delta)) forward, and backward with the gradient on the residual stream added in
+    and the producing layer's bias gradient (column sums of d delta) as a by-product."""
+    from pccl_b200.nn import LayerNorm
+    torch.manual_seed(7)
+    ln = LayerNorm(D, device="cuda")
+    with torch.no_grad():
+        ln.weight.copy_((1 + 0.1 * torch.randn(D, device="cuda")).bfloat16())
+        ln.bias.copy_((0.1 * torch.randn(D, device="cuda")).bfloat16())
+    x = torch.randn(rows, D, device="cuda").bfloat16().requires_grad_(True)
+    delta = torch.randn(rows, D, device="cuda").bfloat16().requires_grad_(True)
+    prev_bias = torch.zeros(D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    s, y = ln.add_norm(x, delta, prev_bias)
+    gs, gy = torch.randn(rows, D, device="cuda").bfloat16(), torch.randn(rows, D, device="cuda").bfloat16()
+    torch.autograd.backward([s, y], [gs, gy])
+    xr, dr = x.detach().float().requires_grad_(True), delta.detach().float().requires_grad_(True)
+    wr, br = ln.weight.detach().float().requires_grad_(True), ln.bias.detach().float().requires_grad_(True)
+    # the norm sees the stored (bf16-rounded) sum; gradients pass straight through the rounding
+    sr = (xr + dr) + ((xr + dr).detach().bfloat16().float() - (xr + dr).detach())
+    yr = F.layer_norm(sr, (D,), wr, br, ln.eps)
+    torch.autograd.backward([sr, yr], [gs.float(), gy.float()])
+    assert (s.float() - sr).abs().max().item() <= 1e-6
+    assert (y.float() - yr).abs().max().item() <= 3e-2
+    tol = 3e-2 * max(1.0, xr.grad.abs().max().item())
+    assert (x.grad.float() - xr.grad).abs().max().item() <= tol
+    assert x.grad.data_ptr() == delta.grad.data_ptr() or torch.equal(x.grad, delta.grad)
+    for got, ref in ((ln.weight.grad, wr.grad), (ln.bias.grad, br.grad), (prev_bias.grad, dr.grad.sum(0))):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_fused_mlp_backward_matches_fp32_reference():
+    """fc2(gelu(fc1(x))) as one autograd node (GELU derivative and first bias gradient inside the GEMM epilogue)."""
+    from pccl_b200.nn import Linear, mlp
+    torch.manual_seed(8)
+    rows, d, h = 512, 256, 1024
+    fc1, fc2 = Linear(d, h, device="cuda"), Linear(h, d, device="cuda")
+    with torch.no_grad():
+        fc1.bias.copy_((0.1 * torch.randn(h, device="cuda")).bfloat16())
+        fc2.bias.copy_((0.1 * torch.randn(d, device="cuda")).bfloat16())
+    x = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.randn(rows, d, device="cuda").bfloat16()
+    mlp(x, fc1, fc2).backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    P = {n: p.detach().float().requires_grad_(True) for n, p in (("w1", fc1.weight), ("b1", fc1.bias), ("w2", fc2.weight), ("b2", fc2.bias))}
+    out = F.linear(F.gelu(F.linear(xr, P["w1"], P["b1"]), approximate="tanh"), P["w2"], P["b2"])
+    out.backward(g.float())
+    for got, ref, name in ((x.grad, xr.grad, "dx"), (fc1.weight.grad, P["w1"].grad, "dw1"), (fc1.bias.grad, P["b1"].grad, "db1"),
+                           (fc2.weight.grad, P["w2"].grad, "dw2"), (fc2.bias.grad, P["b2"].grad, "db2")):
+        assert (got.float() - ref).abs().max().item() <= 5e-2 * max(1e-3, ref.abs().max().item()), name
+    # the second bias gradient can be left to the consumer of the output
+    fc2.bias.grad = None
+    mlp(x, fc1, fc2, defer_fc2_bias_grad=True).backward(g)
+    assert fc2.bias.grad is None

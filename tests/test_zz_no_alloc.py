@@ -51,6 +51,30 @@ def test_no_alloc_cross_entropy_matches_regular_entry_point_twice():
         assert torch.equal(a, b), f"call {call}: gradients differ from the regular entry point"
 
 
+def test_no_alloc_cross_entropy_treats_out_of_range_targets_as_ignored_rows():
+    """A target outside [0, vocab) -- the customary -100, a negative, one past the end -- must not be used as an index:
+    such rows get loss 0 and an all-zero gradient, the others are unchanged, and the mean is over all rows."""
+    from pccl_b200.ops.elementwise import cross_entropy_
+    lib, fn = _lib()
+    torch.manual_seed(1)
+    rows, vocab = 64, 1000
+    store = (torch.randn(rows, vocab, device="cuda") * 2).bfloat16()
+    tgt = torch.randint(0, vocab, (rows,), device="cuda")
+    bad = torch.tensor([3, 17, 40, 63], device="cuda")
+    tgt_bad = tgt.clone()
+    tgt_bad[bad] = torch.tensor([-100, -1, vocab, 1 << 40], device="cuda")
+    a, b = store.clone(), store.clone()
+    good = torch.ones(rows, dtype=torch.bool, device="cuda")
+    good[bad] = False
+    ref_rows = cross_entropy_(a, tgt, grad_scale=1.0 / rows, ignore_index=-(1 << 62))
+    out = torch.zeros(1, device="cuda")
+    assert fn(b.data_ptr(), tgt_bad.data_ptr(), out.data_ptr(), rows, vocab, vocab, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(a[good], b[good]) and int(b[bad].abs().sum()) == 0
+    want = ref_rows[good].sum().item() / rows
+    assert abs(out.item() - want) <= 1e-4 * max(1.0, abs(want))
+
+
 def test_no_alloc_cross_entropy_rejects_what_it_cannot_hold():
     lib, fn = _lib()
     x = torch.zeros(8, 16, device="cuda", dtype=torch.bfloat16)
