@@ -91,6 +91,7 @@ def main() -> None:
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the gradient/optimizer kernels (0 = automatic)")
     ap.add_argument("--algo", default="auto", choices=["auto", "nvls", "p2p"])
+    ap.add_argument("--unfused-blocks", action="store_true", help="every layer its own autograd node (comparison run)")
     ap.add_argument("--no-micro", action="store_true", help="skip the collective micro-benchmarks at N > 1")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -124,6 +125,7 @@ def main() -> None:
     from pccl_b200.utils import ClockSampler
 
     cfg = GPTConfig.gpt_1p3b() if args.model == "gpt-1.3b" else GPTConfig.tiny()
+    cfg.fuse_blocks = not args.unfused_blocks
     torch.manual_seed(1234)            # same initial weights on every rank
     model = GPT(cfg, device="cuda")
     n_params = sum(p.numel() for p in model.parameters())

@@ -183,6 +183,110 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
   }
 }
 
+// Backward for D = NV * 256 <= 2048 with one WARP per row: a lane keeps NV 16-byte vectors of x, dy (and dres) of its
+// row in flight at once (up to 12 KiB per warp), the row statistics need only warp shuffles (no CTA barrier per row),
+// and the column sums (dgamma, dbeta, bias gradient) are accumulated in shared memory that is private to the warp:
+// 8 warps x 3 arrays x D floats, laid out as two planes of 4-float halves so that consecutive lanes touch consecutive
+// 16-byte words (no bank conflicts).  At the end the CTA adds its 8 private copies and writes one partial row per
+// array; with one CTA per SM that leaves at most 148 partial rows for the reduce kernel.
+template <int NV>
+__global__ void __launch_bounds__(256, 1) ln_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                             const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean,
+                                                             const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dres,
+                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ part_g,
+                                                             float* __restrict__ part_b, float* __restrict__ part_c, long long rows) {
+  constexpr int D = NV * 256;
+  constexpr int HALF = D / 8;                 // float4 slots per plane
+  extern __shared__ __align__(16) float ln_acc[];          // [8 warps][3 arrays][2 planes][D / 8][4], then gamma (bf16 [D])
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 8 * 3 * D / 4; i += 256) reinterpret_cast<float4*>(ln_acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  Vec16* gq = reinterpret_cast<Vec16*>(ln_acc + 8 * 3 * D);      // read per use: keeps 4 * NV registers free
+  for (int i = threadIdx.x; i < D / 8; i += 256) gq[i] = ld16(gamma + i * 8);
+  __syncthreads();
+  float4* acc_g = reinterpret_cast<float4*>(ln_acc + (warp * 3 + 0) * D);
+  float4* acc_b = reinterpret_cast<float4*>(ln_acc + (warp * 3 + 1) * D);
+  float4* acc_c = reinterpret_cast<float4*>(ln_acc + (warp * 3 + 2) * D);
+  const float inv_d = 1.0f / D;
+  for (long long row = static_cast<long long>(blockIdx.x) * 8 + warp; row < rows; row += static_cast<long long>(gridDim.x) * 8) {
+    const long long base = row * D + lane * 8;
+    Vec16 vx[NV], vd[NV], vr[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      vx[j] = ld16(x + base + j * 256);
+      vd[j] = ld16(dy + base + j * 256);
+      if (dres) vr[j] = ld16(dres + base + j * 256);
+    }
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float xf[8], df[8], gf[8];
+      unpack<DT_BF16>(vx[j], xf);
+      unpack<DT_BF16>(vd[j], df);
+      unpack<DT_BF16>(gq[j * 32 + lane], gf);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float dg = df[k] * gf[k];
+        s1 += dg;
+        s2 += dg * ((xf[k] - mu) * rs);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    const float m1 = s1 * inv_d, m2 = s2 * inv_d;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float xf[8], df[8], gf[8], of[8];
+      unpack<DT_BF16>(vx[j], xf);
+      unpack<DT_BF16>(vd[j], df);
+      unpack<DT_BF16>(gq[j * 32 + lane], gf);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        xf[k] = (xf[k] - mu) * rs;
+        of[k] = rs * (df[k] * gf[k] - m1 - xf[k] * m2);
+      }
+      if (dres) {
+        float rf[8];
+        unpack<DT_BF16>(vr[j], rf);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) of[k] += rf[k];
+      }
+      st16(dx + base + j * 256, pack<DT_BF16>(of));
+      const int vec = j * 32 + lane;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float4 a = acc_g[h * HALF + vec], b = acc_b[h * HALF + vec];
+        a.x += df[4 * h] * xf[4 * h]; a.y += df[4 * h + 1] * xf[4 * h + 1]; a.z += df[4 * h + 2] * xf[4 * h + 2]; a.w += df[4 * h + 3] * xf[4 * h + 3];
+        b.x += df[4 * h]; b.y += df[4 * h + 1]; b.z += df[4 * h + 2]; b.w += df[4 * h + 3];
+        acc_g[h * HALF + vec] = a;
+        acc_b[h * HALF + vec] = b;
+        if (part_c) {
+          float4 c = acc_c[h * HALF + vec];
+          c.x += of[4 * h]; c.y += of[4 * h + 1]; c.z += of[4 * h + 2]; c.w += of[4 * h + 3];
+          acc_c[h * HALF + vec] = c;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int narr = part_c ? 3 : 2;
+  for (int i = threadIdx.x; i < narr * (D / 4); i += 256) {
+    const int arr = i / (D / 4), idx = i % (D / 4);
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float4 v = reinterpret_cast<const float4*>(ln_acc + (w * 3 + arr) * D)[idx];
+      t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+    }
+    const int h = idx / HALF, vec = idx % HALF;
+    float* dst = (arr == 0 ? part_g : (arr == 1 ? part_b : part_c)) + static_cast<long long>(blockIdx.x) * D + vec * 8 + h * 4;
+    *reinterpret_cast<float4*>(dst) = t;
+  }
+}
+
 // Adds the partial rows of up to three arrays [nparts, D] column by column into bf16 vectors of length D.  A CTA owns
 // 32 columns; its 32 warps each walk every 32nd partial row, so the rows are read 32 at a time with full coalescing.
 struct ReduceJob {
@@ -227,13 +331,16 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (col < N) {
     long long r = r0 + warp;
-    for (; r + 8 < r1; r += 16) {          // two independent loads in flight
-      float a[8], b[8];
+    for (; r + 24 < r1; r += 32) {         // four independent loads in flight
+      float a[8], b[8], c[8], d[8];
       const Vec16 va = ld16(x + r * ld + col), vb = ld16(x + (r + 8) * ld + col);
+      const Vec16 vc = ld16(x + (r + 16) * ld + col), vd = ld16(x + (r + 24) * ld + col);
       unpack<DT_BF16>(va, a);
       unpack<DT_BF16>(vb, b);
+      unpack<DT_BF16>(vc, c);
+      unpack<DT_BF16>(vd, d);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += a[k] + b[k];
+      for (int k = 0; k < 8; ++k) acc[k] += (a[k] + b[k]) + (c[k] + d[k]);
     }
     for (; r < r1; r += 8) {
       float a[8];
@@ -270,7 +377,7 @@ int launchLayerNormFwd(const void* x, const void* delta, void* sum_out, const vo
   return static_cast<int>(cudaGetLastError());
 }
 
-int layerNormBwdParts(long long rows) { return static_cast<int>(rows < 148 * 4 ? rows : 148 * 4); }
+int layerNormBwdParts(long long rows) { return static_cast<int>(rows < 148 * 8 ? rows : 148 * 8); }
 
 int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres, void* dx,
                        void* dgamma, void* dbeta, void* dcolsum, float* partials, long long rows, int D, cudaStream_t stream) {
@@ -283,12 +390,29 @@ int launchLayerNormBwd(const void* dy, const void* x, const void* gamma, const f
   auto DY = static_cast<const __nv_bfloat16*>(dy); auto X = static_cast<const __nv_bfloat16*>(x);
   auto G = static_cast<const __nv_bfloat16*>(gamma); auto DX = static_cast<__nv_bfloat16*>(dx);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
-  if (D <= 2048) ln_bwd_kernel<1><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
+  int nparts = parts;
+  const int nv = D / 256;
+  if (D % 256 == 0 && (nv == 1 || nv == 2 || nv == 4 || nv == 8)) {
+    // one warp per row, one CTA per SM
+    const int grid = static_cast<int>(rows < 148 * 8 ? (rows + 7) / 8 : 148);
+    const size_t smem = 8ull * 3 * D * sizeof(float) + static_cast<size_t>(D) * 2;
+    cudaError_t e = cudaSuccess;
+    auto go = [&](auto kern) {
+      if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e == cudaSuccess) kern<<<grid, 256, smem, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows);
+    };
+    if (nv == 1) go(ln_bwd_warp_kernel<1>);
+    else if (nv == 2) go(ln_bwd_warp_kernel<2>);
+    else if (nv == 4) go(ln_bwd_warp_kernel<4>);
+    else go(ln_bwd_warp_kernel<8>);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    nparts = grid;
+  } else if (D <= 2048) ln_bwd_kernel<1><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
   else if (D <= 4096) ln_bwd_kernel<2><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
   else ln_bwd_kernel<4><<<parts, 256, 0, stream>>>(DY, X, G, mean, rstd, DR, DX, pg, pb, pc, rows, D);
   ReduceJob job{{pg, pb, pc}, {static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta), static_cast<__nv_bfloat16*>(dcolsum)},
                 dcolsum ? 3 : 2};
-  partial_rows_reduce_kernel<<<(D + 31) / 32, 1024, 0, stream>>>(job, parts, D);
+  partial_rows_reduce_kernel<<<(D + 31) / 32, 1024, 0, stream>>>(job, nparts, D);
   return static_cast<int>(cudaGetLastError());
 }
 

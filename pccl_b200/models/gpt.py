@@ -30,6 +30,10 @@ class GPTConfig:
     vocab_size: int = 50257
     mlp_ratio: int = 4
     tie_embeddings: bool = True
+    # Residual adds inside the LayerNorm kernels, the MLP as one autograd node (GELU backward and bias gradients in
+    # GEMM epilogues), bias gradients of proj / fc2 as a by-product of the next norm's backward.  False keeps every
+    # layer a separate node with element-wise PyTorch kernels between them (for comparison and debugging).
+    fuse_blocks: bool = True
 
     @staticmethod
     def gpt_1p3b() -> "GPTConfig":
@@ -58,6 +62,7 @@ class Block(nn.Module):
         super().__init__()
         d = cfg.d_model
         self.n_head = cfg.n_head
+        self.fuse = cfg.fuse_blocks
         self.ln1 = LayerNorm(d, device=device)
         self.qkv = Linear(d, 3 * d, device=device)
         self.proj = Linear(d, d, device=device, init_std=0.02 / math.sqrt(2 * cfg.n_layer))
@@ -69,6 +74,12 @@ class Block(nn.Module):
         """The residual stream travels as ``(x, delta)``: the sum is formed inside the LayerNorm kernel that needs it.
         Returns the block's own ``(x, delta, bias of the layer that made delta)`` for the next norm to finish."""
         B, T, D = x.shape
+        if not self.fuse:
+            qkv = self.qkv(self.ln1(x)).view(B, T, 3, self.n_head, D // self.n_head)
+            q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = x + self.proj(a.transpose(1, 2).reshape(B, T, D))
+            return x + self.fc2(self.fc1(self.ln2(x))), None, None
         if delta is None:
             h = self.ln1(x)
         else:
@@ -101,7 +112,7 @@ class GPT(nn.Module):
         delta, prev_bias = None, None
         for blk in self.blocks:
             x, delta, prev_bias = blk(x, delta, prev_bias)
-        _, x = self.ln_f.add_norm(x, delta, prev_bias)
+        x = self.ln_f(x) if delta is None else self.ln_f.add_norm(x, delta, prev_bias)[1]
         w = self.wte.weight if self.cfg.tie_embeddings else self.lm_head.weight
         return _LinearFn.apply(x, w, None)          # [B, T, vocab]; rows padded to a multiple of 8
 

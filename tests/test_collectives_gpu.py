@@ -547,7 +547,7 @@ def test_engine_regop_exeop_on_a_cuda_engine_with_alternating_widths(native, alg
     from pccl_b200.engine import Engine
     from pccl_b200.lang import build
     eng = Engine(0, 1)
-    eng.initEngine("cuda", heap_bytes=64 << 20)
+    eng.initEngine("cuda", heap_bytes=512 << 20)       # the default 256 MiB workspace and some room for tensors
     eng.regOp("op", build(algo, 1, channels=2))
     n = 3 * 8192 + 16
     for it, width in enumerate([1, 4, 1, 4, 2, 4]):
