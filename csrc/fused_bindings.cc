@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "engine.h"
+#include "common/env.h"
 #include "kernels/fused_api.h"
 #include "kernels/gemm_api.h"
 #include "kernels/moe_api.h"
@@ -116,6 +117,7 @@ void bindFused(py::module_& m) {
     A.M = M; A.N = N; A.K = K; A.M_local = M / e.world();
     A.x_off = x_off; A.epoch = epoch; A.bar_epoch = e.nextEpoch(flag_lane); A.n_copy = n_copy; A.flag_lane = flag_lane;
     A.spin_ns = kDefaultSpinLimit;
+    A.tail_tiles = static_cast<int>(LaunchEnvironments::getInt("PCCL_AG_TAIL", -1));     // -1: from the cost model
     A.flags = bias ? GEMM_BIAS : 0;
     A.r[0].D = reinterpret_cast<void*>(d); A.r[0].ldd = ldd; A.r[0].bias = reinterpret_cast<const void*>(bias);
     A.ready_off = ready; A.r[0].status = reinterpret_cast<uint32_t*>(status);
@@ -202,7 +204,7 @@ void bindFused(py::module_& m) {
   m.def("emu_ag_gemm", [](const std::vector<uint64_t>& heaps, uint64_t flag_off, uint64_t x_off, int M, int N, int K,
                           const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& d, int64_t ldd,
                           uint64_t ready_off, uint64_t epoch, int n_copy, int ctas,
-                          const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream) {
+                          const std::vector<uint64_t>& status, uint64_t spin_ns, uint64_t stream, int tail_tiles) {
     AgGemmArgs A{};
     A.ready_off = ready_off;
     A.w = emuWorld2(heaps, flag_off);
@@ -210,6 +212,7 @@ void bindFused(py::module_& m) {
     A.nvirt = n;
     A.M = M; A.N = N; A.K = K; A.M_local = M / n;
     A.x_off = x_off; A.epoch = epoch; A.bar_epoch = epoch; A.n_copy = n_copy; A.flag_lane = 0; A.spin_ns = spin_ns ? spin_ns : kDefaultSpinLimit;
+    A.tail_tiles = tail_tiles;
     std::vector<AgGemmHost> h(n);
     for (int r = 0; r < n; ++r) {
       A.r[r].D = reinterpret_cast<void*>(d.at(r)); A.r[r].ldd = ldd;
@@ -218,7 +221,12 @@ void bindFused(py::module_& m) {
       h[r] = AgGemmHost{reinterpret_cast<const void*>(w.at(r)), ldw, false};
     }
     check(launchAgGemm(A, h.data(), ctas, reinterpret_cast<cudaStream_t>(stream)), "emu_ag_gemm");
-  });
+  }, py::arg("heaps"), py::arg("flag_off"), py::arg("x_off"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("w"), py::arg("ldw"),
+     py::arg("d"), py::arg("ldd"), py::arg("ready_off"), py::arg("epoch"), py::arg("n_copy"), py::arg("ctas"), py::arg("status"),
+     py::arg("spin_ns"), py::arg("stream"), py::arg("tail_tiles") = -1);
+  // time attribution of the fused kernels: a zeroed device buffer of PROBE_WORDS u64 per CTA, or 0 to switch it off
+  m.def("fused_set_probe", [](uint64_t ptr) { setFusedProbe(reinterpret_cast<unsigned long long*>(ptr)); });
+  m.attr("PROBE_WORDS") = kProbeWords;
   m.def("emu_gemm_rs", [](const std::vector<uint64_t>& heaps, const std::vector<uint64_t>& y, int64_t ldy,
                           const std::vector<uint64_t>& w, int64_t ldw, const std::vector<uint64_t>& out, int64_t ldo, int M,
                           int N, int K, uint64_t stage_off, uint64_t flag_off2, uint64_t epoch, int ctas,

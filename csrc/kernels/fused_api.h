@@ -12,6 +12,17 @@ namespace pccl {
 
 constexpr int kMaxVirt = 4;   // ranks that one launch can emulate on a single GPU (tests)
 
+// Opt-in time attribution of the fused kernels.  With a probe buffer set (device memory, kProbeWords u64 per CTA of the
+// largest grid, zeroed by the caller), every CTA adds up where it waited, in nanoseconds of %globaltimer:
+//   [0] all-gather GEMM: waiting for a remote chunk's counter before a tile's loads (AgGate)
+//   [1] GEMM reduce-scatter: waiting for the peers' partial tiles before an own tile (tile_begin)
+//   [2] GEMM reduce-scatter: waiting for staged rows to leave shared memory (per strip / per tile)
+//   [3] GEMM reduce-scatter: waiting for a peer tile's writes to complete before its flag is released (tile_done)
+//   [4] %globaltimer when the CTA started, [5] when it ended, [6] duration of the copy role, [7] tiles computed
+// The probes cost a few timer reads per tile; they are for attribution runs, not for timed ones.
+constexpr int kProbeWords = 8;
+void setFusedProbe(unsigned long long* device_buffer);
+
 struct AgGemmRank {
   CUtensorMap tmA, tmB;       // filled by launchAgGemm
   void* D;                    // [M, N] bf16 output (local)
@@ -45,7 +56,8 @@ struct AgGemmArgs {
   int elem_bytes;             // 2 (bf16 X) or 1 (e4m3 X with scales at xs_off); 0 is read as 2
   uint64_t xs_off;            // fp8: heap offset of the symmetric gathered scales [M, K/128]: fp32, or UE8M0 bytes (scale_bytes 1)
   int scale_bytes;            // 4 (fp32 scales; 0 is read as 4) or 1 (UE8M0 bytes, hardware block scaling)
-  int pad3;
+  int tail_tiles;             // tiles at the end of the tile order that the copy CTAs compute once their rows are sent
+  unsigned long long* probe;  // null, or kProbeWords x u64 per CTA (see setFusedProbe)
   AgGemmRank r[kMaxVirt];
 };
 
@@ -74,6 +86,7 @@ struct GemmRsArgs {
   uint64_t flag_off2;         // heap offset of the symmetric tile flags uint64 [world][M_local/128 * N/256], zeroed once
   uint64_t epoch;
   uint64_t spin_ns;
+  unsigned long long* probe;  // null, or kProbeWords x u64 per CTA (see setFusedProbe)
   GemmRsRank r[kMaxVirt];
 };
 

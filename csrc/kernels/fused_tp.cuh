@@ -46,12 +46,15 @@ __device__ __forceinline__ bool cta_peer_barrier(const World& W, int me, int lan
 // row block by row block -- block b of EVERY peer before block b+1 of any -- which is the order in which
 // the senders emit them, so the data keeps ahead of the tensor cores from the first remote tile on.
 // Within a row block consecutive tiles share the B panel (same n, different source rank).
+// [begin, end) is the slice of that order which this group of CTAs works through (`first` + it * `stride` inside it):
+// the GEMM CTAs take everything but the last `tail` tiles, the copy CTAs take the tail once their rows are sent.
 struct AgSched {
   int me, world, tiles_ml, tiles_n, first, stride;
+  long long begin, end;
   __device__ __forceinline__ bool get(int it, TileCoord* t) const {
-    const long long idx = first + static_cast<long long>(it) * stride;
+    const long long idx = begin + first + static_cast<long long>(it) * stride;
     const int per_panel = tiles_ml * tiles_n;
-    if (idx >= static_cast<long long>(world) * per_panel) return false;
+    if (idx >= end || idx >= static_cast<long long>(world) * per_panel) return false;
     if (idx < per_panel) {
       const int r = static_cast<int>(idx);
       t->m = me * tiles_ml + r % tiles_ml;
@@ -76,11 +79,17 @@ struct AgGate {
   int me;
   uint32_t target;         // epoch * copy CTAs
   uint64_t spin_ns;
+  unsigned long long* probe = nullptr;     // this CTA's probe words, or null
   __device__ __forceinline__ bool wait(const TileCoord& t, const volatile uint32_t* abort) const {
+    if (probe) atomicAdd(probe + 7, 1ull);
     if (t.extra == me) return true;
     const uint32_t* f = ready + t.m;
     if (dev::ld_acquire_sys_u32(f) < target) {
       const uint64_t t0 = dev::global_timer_ns();
+      struct Tally {
+        unsigned long long* p; uint64_t t0;
+        __device__ ~Tally() { if (p) atomicAdd(p, static_cast<unsigned long long>(dev::global_timer_ns() - t0)); }
+      } tally{probe, t0};
       for (uint32_t i = 1;; ++i) {
         if (dev::ld_acquire_sys_u32(f) >= target) break;
         if ((i & 31) == 0) {
@@ -138,6 +147,11 @@ __device__ __forceinline__ void push_vecs(const char* src, char* dst, long long 
 
 __device__ __forceinline__ void ag_push_role(const AgGemmArgs& A, const AgGemmRank& R) {
   const int me = R.rank, world = A.w.world, j = blockIdx.x;
+  const uint64_t push_t0 = A.probe ? dev::global_timer_ns() : 0;
+  struct PushTally {
+    unsigned long long* p; uint64_t t0;
+    __device__ ~PushTally() { if (p && threadIdx.x == 0) p[6] = dev::global_timer_ns() - t0; }
+  } push_tally{A.probe ? A.probe + static_cast<long long>(blockIdx.y * gridDim.x + blockIdx.x) * kProbeWords : nullptr, push_t0};
   if (!cta_peer_barrier(A.w, me, A.flag_lane, j, 4 * A.bar_epoch + 1, A.spin_ns, R.status)) return;
   const int chunks = A.M_local / BM;
   const long long row_bytes = static_cast<long long>(A.K) * (A.elem_bytes ? A.elem_bytes : 2);
@@ -212,6 +226,7 @@ struct RsEpiT {
   const GemmRsRank* R;
   uint8_t* stage;      // this warp's 32 x 144 B staging rows
   int me, tiles_ml, tiles_n;
+  unsigned long long* probe = nullptr;     // this CTA's probe words, or null
 
   __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.m * BM; }
   __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * BN; }
@@ -228,11 +243,13 @@ struct RsEpiT {
     if (t.extra != me) return;
     // our own rows: the peers' partials of this tile must be in our staging slots
     const int lane = threadIdx.x & 31;
+    const uint64_t t0 = probe ? dev::global_timer_ns() : 0;
     if (lane < A->w.world && lane != me) {
       if (!dev::wait_ge(tile_flag(me, lane, tile_local_index(t)), A->epoch, A->spin_ns, nullptr))
         dev::report(R->status, ST_TIMEOUT, blockIdx.x, 4, static_cast<uint32_t>(lane));
     }
     __syncwarp();
+    if (probe && lane == 0 && (threadIdx.x >> 5) == 2) atomicAdd(probe + 1, static_cast<unsigned long long>(dev::global_timer_ns() - t0));
   }
 
   __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
@@ -255,7 +272,9 @@ struct RsEpiT {
                     ((static_cast<long long>(me) * A->M_local + row_local) * A->N + (col - 32)) * 2;
         tc::bulk_store_s2g(dst, stage + lane * kRsPitch, 128);
         tc::bulk_commit();
+        const uint64_t t0 = probe ? dev::global_timer_ns() : 0;
         tc::bulk_wait_read<0>();      // the staging row may be overwritten by the next strip
+        if (probe && lane == 0 && (threadIdx.x >> 5) == 2) atomicAdd(probe + 2, static_cast<unsigned long long>(dev::global_timer_ns() - t0));
       }
       return;
     }
@@ -279,16 +298,56 @@ struct RsEpiT {
 
   __device__ __forceinline__ void tile_done(const TileCoord& t, const volatile uint32_t*) {
     if (t.extra == me) return;
+    const uint64_t t0 = probe ? dev::global_timer_ns() : 0;
     tc::bulk_wait<0>();                  // this lane's rows have been written to the owner
     tc::fence_proxy_async();
     asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");   // the epilogue warps
     if ((threadIdx.x >> 5) == 2 && (threadIdx.x & 31) == 0) {
       __threadfence_system();
       dev::st_release_sys(tile_flag(t.extra, me, tile_local_index(t)), A->epoch);
+      if (probe) {
+        atomicAdd(probe + 3, static_cast<unsigned long long>(dev::global_timer_ns() - t0));
+        atomicAdd(probe + 7, 1ull);
+      }
     }
   }
 };
 using RsEpi = RsEpiT<4>;
+
+// The same protocol with whole rows staged: a warp keeps 32 rows x 256 columns (512 bytes per row) of a peer-owned tile
+// in shared memory and sends each row with ONE 512-byte bulk copy when the tile's last strip is packed, instead of a
+// 128-byte copy and a full drain after every 64 columns.  Four times fewer, four times larger writes on NVLink, and the
+// epilogue never waits inside a tile.  Needs 64 KiB of staging, which the CTA-pair kernel makes room for by running a
+// five-stage operand ring (gemm2::run<..., 5>).
+constexpr int kRsRowBytes = BN * 2;                          // 512
+constexpr int kRsRowStageBytes = 4 * 32 * kRsRowBytes;       // four epilogue warps: 64 KiB
+struct RsEpiRow : RsEpiT<4> {
+  __device__ __forceinline__ void attach_smem(uint8_t* p) { stage = p + ((static_cast<int>(threadIdx.x >> 5) - 2) & 3) * (32 * kRsRowBytes); }
+
+  __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
+    if (t.extra == me) {
+      RsEpiT<4>::strip(t, row_in_tile, col_in_tile, r);
+      return;
+    }
+    const int lane = threadIdx.x & 31;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    uint8_t* srow = stage + lane * kRsRowBytes;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) *reinterpret_cast<dev::Vec16*>(srow + (col_in_tile + i) * 2) = dev::pack<DT_BF16>(v + i);
+    if (col_in_tile == BN - 32) {
+      const int owner = t.extra;
+      const long long row_local = static_cast<long long>(t.m - owner * tiles_ml) * BM + row_in_tile;
+      char* dst = A->w.heap[owner] + A->stage_off +
+                  ((static_cast<long long>(me) * A->M_local + row_local) * A->N + static_cast<long long>(t.n) * BN) * 2;
+      tc::fence_proxy_async_smem();       // this lane's own stores to its row, before the bulk copy reads them
+      tc::bulk_store_s2g(dst, srow, kRsRowBytes);
+      tc::bulk_commit();
+    }
+  }
+  // tile_done (inherited) waits for the copies, so the rows are free again before the next tile's first strip
+};
 
 }  // namespace fused
 }  // namespace pccl

@@ -83,7 +83,8 @@ __global__ void __launch_bounds__(gemm8::NUM_THREADS, 1) ag_gemm_fp8_kernel(cons
     return;
   }
   const int tiles_ml = A.M_local / gemm8::BM, tiles_n = A.N / gemm8::BN;
-  AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy};
+  AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy, 0,
+                static_cast<long long>(A.w.world) * tiles_ml * tiles_n};
   AgGate gate{reinterpret_cast<const uint32_t*>(A.w.heap[R.rank] + A.ready_off), R.rank,
               static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>(A.n_copy), A.spin_ns};
   gemm8::Scales sc{reinterpret_cast<const float*>(A.w.heap[R.rank] + A.xs_off), R.w_scale, A.K / 128, R.ld_ws, A.M, A.N};
@@ -105,7 +106,8 @@ __global__ void __launch_bounds__(gemmx::NUM_THREADS, 1) ag_gemm_mx8_kernel(cons
     return;
   }
   const int tiles_ml = A.M_local / gemmx::BM, tiles_n = (A.N + gemmx::BN - 1) / gemmx::BN;
-  AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy};
+  AgSched sched{R.rank, A.w.world, tiles_ml, tiles_n, static_cast<int>(blockIdx.x) - A.n_copy, static_cast<int>(gridDim.x) - A.n_copy, 0,
+                static_cast<long long>(A.w.world) * tiles_ml * tiles_n};
   AgGate gate{reinterpret_cast<const uint32_t*>(A.w.heap[R.rank] + A.ready_off), R.rank,
               static_cast<uint32_t>(A.epoch) * static_cast<uint32_t>(A.n_copy), A.spin_ns};
   gemmx::Scales sc{reinterpret_cast<const uint8_t*>(A.w.heap[R.rank] + A.xs_off), reinterpret_cast<const uint8_t*>(R.w_scale), A.K / 128,

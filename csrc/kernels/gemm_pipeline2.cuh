@@ -40,12 +40,15 @@ struct Barriers {
 
 // `sched` enumerates pair tiles: t.m indexes 256-row blocks.  Epi sees per-CTA coordinates through
 // a_row0 / b_row0 (which must add cta_rank * 128) and strip(t, row_in_cta_tile, col, r).
-template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi>
+// NSTAGES (<= STAGES) shortens the operand ring; an epilogue that needs a large staging area of its own (the
+// reduce-scatter epilogue stages whole 512-byte rows) gives up one stage for it.
+template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES>
 __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* tmB, int K, const Sched& sched,
                                     const Gate& gate, Epi& epi, uint32_t* status) {
+  static_assert(NSTAGES >= 2 && NSTAGES <= STAGES, "ring length");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  Barriers* bar = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + NSTAGES * STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = tc::cluster_ctarank();
   const bool leader = cta == 0;
@@ -53,7 +56,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   volatile uint32_t* abort = &bar->abort;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NSTAGES; ++s) {
       tc::mbar_init(&bar->full[s], 1);
       tc::mbar_init(&bar->empty[s], 1);
     }
@@ -77,7 +80,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  epi.attach_smem(smem + EPI_SMEM_OFFSET);
+  epi.attach_smem(smem + NSTAGES * STAGE_BYTES + 256);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -108,7 +111,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
 #pragma unroll
             for (int j = 0; j < HALF_N / 64; ++j) tc::tma_load_2d_pair(sb + j * (64 * BK * 2), tmB, full_leader, col0 + j * 64, k0);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok && atomicExch(const_cast<uint32_t*>(&bar->abort), 1u) == 0) dev::report(status, ST_TIMEOUT, blockIdx.x, 0, 0);
@@ -139,7 +142,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
             tc::mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
           }
           tc::mma_commit_pair(&bar->empty[stage], 3);       // frees the stage in both CTAs
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         tc::mma_commit_pair(&bar->tmem_full[acc], 3);       // accumulator ready in both CTAs

@@ -226,6 +226,49 @@ def run_fp8(eng, tokens, d_model, d_ff, x_local, w1, w2, h, iters, warmup, n_cop
     return rows
 
 
+def probe_fused(eng: Engine, tokens: int, d_model: int, d_ff: int, n_copy: int):
+    """One launch of each bf16 fused kernel with the wait-time probes on (csrc/kernels/fused_api.h: setFusedProbe):
+    per rank, the mean and maximum over CTAs of the nanoseconds spent in each kind of wait, the spread of CTA start
+    times, and the kernel's span from the first CTA's start to the last CTA's end."""
+    from ._native import C
+    world, rank = eng.world, eng.rank
+    n1, m_local = d_ff // world, tokens // world
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    w1 = (torch.randn(n1, d_model, generator=g, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(d_model, n1, generator=g, device="cuda") * 0.02).bfloat16()
+    h = (torch.randn(tokens, n1, generator=g, device="cuda") * 0.5).bfloat16()
+    ag = AllGatherGemm(eng, tokens, d_model, n_copy=n_copy)
+    ag.x_local.normal_()
+    rs = GemmReduceScatter(eng, tokens, d_model)
+    ctas = C.sm_count()
+    buf = torch.zeros(ctas * C.PROBE_WORDS, dtype=torch.int64, device="cuda")
+    rows = []
+    for name, fn in (("allgather_gemm", lambda: ag(w1)), ("gemm_reduce_scatter", lambda: rs(h, w2))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.zero_()
+        C.fused_set_probe(buf.data_ptr())
+        fn()
+        torch.cuda.synchronize()
+        C.fused_set_probe(0)
+        p = buf.view(ctas, C.PROBE_WORDS).double().cpu()
+        live = p[:, 4] > 0
+        start, end = p[live, 4], p[live, 5]
+        rec = {"op": name + "_probe", "rank": rank, "n_gpus": world, "ctas": int(live.sum()),
+               "span_us": float(end.max() - start.min()) / 1e3, "start_spread_us": float(start.max() - start.min()) / 1e3}
+        for i, key in ((0, "gate_wait"), (1, "own_tile_wait"), (2, "stage_drain_wait"), (3, "tile_done_wait"), (6, "copy_role")):
+            col = p[live, i] / 1e3
+            rec[key + "_us_mean"] = float(col.mean())
+            rec[key + "_us_max"] = float(col.max())
+        rec["tiles_max_per_cta"] = float(p[live, 7].max())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, rec)
+        rows += gathered if rank == 0 else []
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=8192)
@@ -234,6 +277,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--n-copy", type=int, default=16)
     ap.add_argument("--no-fp8", action="store_true")
+    ap.add_argument("--probe", action="store_true", help="after the timed runs, one launch of each bf16 fused kernel with the "
+                    "in-kernel wait-time probes on; prints where the CTAs waited")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -252,6 +297,8 @@ def main():
         pass
     rows = run(eng, args.tokens, args.d_model, args.d_ff, iters=args.iters, n_copy=args.n_copy,
                peak_tflops=float(peaks.get("bf16_tflops", 1590.0)), fp8=not args.no_fp8)
+    if args.probe:
+        rows += probe_fused(eng, args.tokens, args.d_model, args.d_ff, args.n_copy)
     if rank == 0:
         for r in rows:
             print(json.dumps(r), flush=True)

@@ -213,8 +213,10 @@ def test_fp8_block_scaled_reduce_emulated(native, world, kind, redop):
 # ---------------------------------------------------------------------------------------------
 # fused collective + GEMM kernels, ranks emulated on one GPU
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("world", [2, 4])
-def test_ag_gemm_emulated(native, world):
+@pytest.mark.parametrize("world,tail", [(2, -1), (4, -1), (2, 0), (2, 2), (2, 100), (4, 5)])
+def test_ag_gemm_emulated(native, world, tail):
+    """`tail`: tiles at the end of the tile order that the copy CTAs compute after sending their rows (-1: cost model,
+    0: none, a number beyond the tile count: all of them)."""
     M_local, K, N = 256, 512, 520
     M = M_local * world
     g = torch.Generator(device="cuda").manual_seed(9)
@@ -233,7 +235,7 @@ def test_ag_gemm_emulated(native, world):
             full[r * M_local:(r + 1) * M_local] = xs[r] * epoch
         native.emu_ag_gemm([h.data_ptr() for h in heaps], FLAG_OFF, x_off, M, N, K, [w.data_ptr() for w in ws], K,
                            [o.data_ptr() for o in outs], N, ready_off, epoch, 4, ctas,
-                           [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream)
+                           [s.data_ptr() for s in st], 0, torch.cuda.current_stream().cuda_stream, tail)
         torch.cuda.synchronize()
         assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
         X = torch.cat(xs).float() * epoch
@@ -244,9 +246,9 @@ def test_ag_gemm_emulated(native, world):
             assert torch.equal(gathered.float(), X)
 
 
-@pytest.mark.parametrize("world,M_local", [(2, 128), (2, 256), (4, 128)])
+@pytest.mark.parametrize("world,M_local", [(2, 128), (2, 256), (4, 128), (2, 512)])
 def test_gemm_rs_emulated(native, world, M_local):
-    K, N = 448, 512     # 256 rows per rank and an even CTA count take the CTA-pair pipeline
+    K, N = 448, 512     # 256 rows per rank and an even CTA count take the CTA-pair pipeline (whole rows staged per tile)
     M = M_local * world
     g = torch.Generator(device="cuda").manual_seed(10)
     ys = [(torch.randn(M, K, generator=g, device="cuda") * 0.5).bfloat16() for _ in range(world)]
