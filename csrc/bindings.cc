@@ -74,6 +74,8 @@ void collective(Engine& e, const std::string& kind, const std::string& algo, con
   a.status[0] = reinterpret_cast<uint32_t*>(e.statusPtr(8 + flag_lane));
   a.local_in[0] = reinterpret_cast<const void*>(local_in);
   a.local_out[0] = reinterpret_cast<void*>(local_out);
+  if (flag_lane >= 0 && flag_lane < kLlLanes && e.layout().ll_off && LaunchEnvironments::getBool("PCCL_LL", true))
+    a.ll_off = e.layout().ll_off + static_cast<uint64_t>(flag_lane) * kLlLaneBytes;
   throwIfCuda(launchKind(kind, a, blocks, threads, reinterpret_cast<cudaStream_t>(stream)), kind.c_str());
 }
 
@@ -92,11 +94,12 @@ void emuCollective(const std::string& kind, const std::vector<uint64_t>& heaps, 
                    const std::string& dtype, const std::string& redop, uint64_t in_off, uint64_t out_off, uint64_t count,
                    uint64_t epoch, int flag_lane, float scale, const std::string& out_dtype, int blocks, int threads,
                    uint64_t stream, const std::vector<uint64_t>& status, const std::vector<uint64_t>& local_in,
-                   const std::vector<uint64_t>& local_out, uint64_t spin_limit, uint64_t s_in_off, uint64_t s_out_off) {
+                   const std::vector<uint64_t>& local_out, uint64_t spin_limit, uint64_t s_in_off, uint64_t s_out_off, uint64_t ll_off) {
   World w = emuWorld(heaps, signal_off, flag_off);
   CollArgs a = makeCollArgs(w, w.world, 0, "p2p", dtype, redop, in_off, out_off, count, epoch, flag_lane, scale, out_dtype, spin_limit);
   a.s_in_off = s_in_off;
   a.s_out_off = s_out_off;
+  a.ll_off = ll_off;
   for (int r = 0; r < w.world; ++r) {
     a.status[r] = reinterpret_cast<uint32_t*>(status.at(r));
     a.local_in[r] = local_in.empty() ? nullptr : reinterpret_cast<const void*>(local_in.at(r));
@@ -143,6 +146,7 @@ void emuProgram(const std::string& schedule_json, const std::vector<uint64_t>& h
       R.rank = r;
       R.n_streams = static_cast<int>(starts.size());
       if (!flat.empty()) {
+        flat.resize(flat.size() + kInstrPad, Instr{});      // the kernel reads whole chunks: no-ops behind the last stream
         Instr* di = nullptr;
         uint32_t* ds = nullptr;
         throwIfCuda(cudaMalloc(&di, flat.size() * sizeof(Instr)), "cudaMalloc");
@@ -259,7 +263,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("emu_collective", &emuCollective, py::arg("kind"), py::arg("heaps"), py::arg("signal_off"), py::arg("flag_off"), py::arg("dtype"),
         py::arg("redop"), py::arg("in_off"), py::arg("out_off"), py::arg("count"), py::arg("epoch"), py::arg("flag_lane"), py::arg("scale"),
         py::arg("out_dtype"), py::arg("blocks"), py::arg("threads"), py::arg("stream"), py::arg("status"), py::arg("local_in"),
-        py::arg("local_out"), py::arg("spin_limit"), py::arg("s_in_off") = 0, py::arg("s_out_off") = 0);
+        py::arg("local_out"), py::arg("spin_limit"), py::arg("s_in_off") = 0, py::arg("s_out_off") = 0, py::arg("ll_off") = 0);
+  m.attr("LL_LANE_BYTES") = kLlLaneBytes;
+  m.attr("LL_MAX_BYTES") = kLlMaxBytes;
   m.def("emu_program", &emuProgram);
   m.def("wait_timeout_probe", [](uint64_t flag, uint64_t spin_limit, uint64_t status, uint64_t stream) {
     throwIfCuda(launchWaitTimeoutProbe(reinterpret_cast<uint64_t*>(flag), spin_limit, reinterpret_cast<uint32_t*>(status),

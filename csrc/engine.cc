@@ -84,7 +84,8 @@ void Engine::buildLayout(uint64_t heap_bytes) {
   L.flag_bytes = alignUp(8ull * kMaxBlocksPerColl * kMaxRanks * 8, 256 * 1024);
   L.status_off = L.flag_off + L.flag_bytes;
   L.status_bytes = 4096;
-  L.user_off = alignUp(L.status_off + L.status_bytes, 2 * kMiB);
+  L.ll_off = alignUp(L.status_off + L.status_bytes, 4096);
+  L.user_off = alignUp(L.ll_off + kLlLanes * kLlLaneBytes, 2 * kMiB);
   L.total = alignUp(std::max(heap_bytes, L.user_off), 2 * kMiB);
   user_top_ = L.user_off;
 }
@@ -495,6 +496,7 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
       flat.insert(flat.end(), s.begin(), s.end());
     }
     c.n_streams = static_cast<int>(starts.size());
+    flat.resize(flat.size() + kInstrPad, Instr{});      // the kernel reads whole chunks: no-ops behind the last stream
     cudaCheck(cudaMalloc(&c.instrs, flat.size() * sizeof(Instr)), "cudaMalloc(instructions)");
     cudaCheck(cudaMalloc(&c.starts, starts.size() * sizeof(uint32_t)), "cudaMalloc(stream table)");
     cudaCheck(cudaMemcpy(c.instrs, flat.data(), flat.size() * sizeof(Instr), cudaMemcpyHostToDevice), "upload instructions");

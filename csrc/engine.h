@@ -37,6 +37,7 @@ struct HeapLayout {
   uint64_t signal_off = 0, num_signals = 0;
   uint64_t flag_off = 0, flag_bytes = 0;
   uint64_t status_off = 0, status_bytes = 0;
+  uint64_t ll_off = 0;                       // low-latency all-reduce receive areas, kLlLanes x kLlLaneBytes
   uint64_t user_off = 0;
   uint64_t total = 0;
   int lanes = 2;

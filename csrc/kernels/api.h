@@ -52,6 +52,9 @@ struct InterpRank {
 };
 
 constexpr uint32_t kNoTurnSlot = 0xffffffffu;
+// The interpreter reads instructions a chunk of this many at a time; the array that InterpRank::instrs points to must
+// be followed by that many readable (no-op) instructions.
+constexpr uint32_t kInstrPad = 32;
 
 struct InterpLaunch {
   World w;
@@ -103,7 +106,18 @@ struct CollArgs {
   void* local_out[kMaxRanks];
   // block-scaled fp8 collectives only: heap offsets of the fp32 scales (one per 128 values) of input and output
   uint64_t s_in_off, s_out_off;
+  // Heap offset of the low-latency receive area of this flag lane (kLlLaneBytes: two epochs x kMaxRanks sources x
+  // kLlSlotBytes), or 0 when the heap has none.  All-reduces of at most kLlMaxBytes then take the flag-in-data path.
+  uint64_t ll_off;
 };
+
+// Low-latency all-reduce: every rank stores each 4-byte word of its input into every peer's receive slot as an 8-byte
+// packet {word, launch number} -- the flag travels with the data in one store, so there is no barrier before or after --
+// and reduces its own slots as the packets arrive.  Two receive areas alternate by launch parity.
+constexpr uint64_t kLlMaxBytes = 64ull << 10;
+constexpr uint64_t kLlSlotBytes = 2 * kLlMaxBytes;
+constexpr uint64_t kLlLaneBytes = 2ull * kMaxRanks * kLlSlotBytes;
+constexpr int kLlLanes = 4;
 
 int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t stream);
 int launchReduceScatter(const CollArgs& a, int blocks, int threads, cudaStream_t stream);

@@ -183,6 +183,72 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------
+// low-latency all-reduce (flag in the data): <= kLlMaxBytes, a multiple of 4 bytes; input and output may be any local
+// tensors (also the same one); no barrier, one kernel, every wait bounded
+// ---------------------------------------------------------------------------------------------
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ uint32_t ll_reduce_word(uint32_t a, uint32_t b) {
+  if constexpr (DT == DT_F32) {
+    return __float_as_uint(red1<OP>(__uint_as_float(a), __uint_as_float(b)));
+  } else {
+    // two 16-bit values per word: reduce in fp32, round once per step (the sum of at most 16 ranks)
+    float a0 = load1<DT>(reinterpret_cast<const char*>(&a)), a1 = load1<DT>(reinterpret_cast<const char*>(&a) + 2);
+    float b0 = load1<DT>(reinterpret_cast<const char*>(&b)), b1 = load1<DT>(reinterpret_cast<const char*>(&b) + 2);
+    uint32_t r;
+    store1<DT>(reinterpret_cast<char*>(&r), red1<OP>(a0, b0));
+    store1<DT>(reinterpret_cast<char*>(&r) + 2, red1<OP>(a1, b1));
+    return r;
+  }
+}
+
+template <uint32_t DT, uint32_t OP>
+__global__ void __launch_bounds__(512) allreduce_ll_kernel(const __grid_constant__ CollArgs A) {
+  const int me = my_rank(A), n = A.w.world;
+  const int slot = A.nvirt > 1 ? me : 0;
+  const uint32_t words = static_cast<uint32_t>(A.count * (DT == DT_F32 ? 4 : 2) / 4);
+  const uint32_t flag = static_cast<uint32_t>(A.epoch);                   // never 0: epochs start at 1
+  const uint64_t area = A.ll_off + (A.epoch & 1) * (static_cast<uint64_t>(kMaxRanks) * kLlSlotBytes);
+  const uint32_t* in = reinterpret_cast<const uint32_t*>(A.local_in[slot] ? A.local_in[slot] : A.w.heap[me] + A.in_off);
+  uint32_t* out = reinterpret_cast<uint32_t*>(A.local_out[slot] ? static_cast<char*>(A.local_out[slot]) : A.w.heap[me] + A.out_off);
+  const uint32_t stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
+  // 1. every word to every peer's slot for this rank, flag attached (8-byte stores are single transactions)
+  for (uint32_t w = first; w < words; w += stride) {
+    const uint64_t pkt = (static_cast<uint64_t>(flag) << 32) | in[w];
+    for (int k = 1; k < n; ++k) {
+      int p = me + k;
+      if (p >= n) p -= n;
+      uint64_t* dst = reinterpret_cast<uint64_t*>(A.w.heap[p] + area + static_cast<uint64_t>(me) * kLlSlotBytes) + w;
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(pkt) : "memory");
+    }
+  }
+  // 2. own word plus the peers' packets as they arrive
+  bool failed = false;
+  for (uint32_t w = first; w < words && !failed; w += stride) {
+    uint32_t acc = in[w];
+    for (int k = 1; k < n; ++k) {
+      int p = me - k;
+      if (p < 0) p += n;
+      const uint64_t* src = reinterpret_cast<const uint64_t*>(A.w.heap[me] + area + static_cast<uint64_t>(p) * kLlSlotBytes) + w;
+      uint64_t pkt = ld_relaxed_sys(src);
+      if (static_cast<uint32_t>(pkt >> 32) != flag) {
+        const uint64_t t0 = global_timer_ns();
+        for (uint32_t i = 1;; ++i) {
+          pkt = ld_relaxed_sys(src);
+          if (static_cast<uint32_t>(pkt >> 32) == flag) break;
+          if ((i & 63) == 0 && global_timer_ns() - t0 > A.spin_limit) { failed = true; break; }
+        }
+        if (failed) {
+          report(A.status[slot], ST_TIMEOUT, blockIdx.x, static_cast<uint32_t>(p), 0x11u);
+          break;
+        }
+      }
+      acc = ll_reduce_word<DT, OP>(acc, static_cast<uint32_t>(pkt));
+    }
+    if (!failed) out[w] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // reduce-scatter with epilogue: out_r[i] = cast(scale * reduce_p in_p[r*count + i])
 // ---------------------------------------------------------------------------------------------
 template <uint32_t DT, uint32_t OP, bool NVLS, bool OUT_F32>
@@ -407,6 +473,20 @@ int launchCoop(K kernel, const CollArgs& a, int blocks, int threads, cudaStream_
 int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t stream) {
   const bool nvls = a.algo == ALGO_NVLS;
   const uint64_t bytes = a.count * dtypeSize(a.dtype);
+  // Up to 64 KiB: flag-in-data packets, no barrier at all (needs the low-latency area and whole 4-byte words).
+  if (a.ll_off && bytes <= kLlMaxBytes && bytes % 4 == 0 && a.w.world > 1 && a.w.world <= kMaxRanks &&
+      (a.dtype == DT_F32 || a.dtype == DT_BF16 || a.dtype == DT_F16) && (a.redop == RED_SUM || a.redop == RED_MAX || a.redop == RED_MIN)) {
+    const int words = static_cast<int>(bytes / 4);
+    int ll_blocks = (words + threads - 1) / threads;
+    if (ll_blocks > 32) ll_blocks = 32;
+#define PCCL_LL(DT_, OP_) return launchCoop(allreduce_ll_kernel<DT_, OP_>, a, ll_blocks, threads, stream);
+    switch (a.dtype) {
+      case DT_F32: switch (a.redop) { case RED_SUM: PCCL_LL(DT_F32, RED_SUM) case RED_MAX: PCCL_LL(DT_F32, RED_MAX) default: PCCL_LL(DT_F32, RED_MIN) }
+      case DT_BF16: switch (a.redop) { case RED_SUM: PCCL_LL(DT_BF16, RED_SUM) case RED_MAX: PCCL_LL(DT_BF16, RED_MAX) default: PCCL_LL(DT_BF16, RED_MIN) }
+      default: switch (a.redop) { case RED_SUM: PCCL_LL(DT_F16, RED_SUM) case RED_MAX: PCCL_LL(DT_F16, RED_MAX) default: PCCL_LL(DT_F16, RED_MIN) }
+    }
+#undef PCCL_LL
+  }
   // One-shot below 256 KiB when the output does not alias the input: one barrier pair, no second hop.
   const bool oneshot = bytes <= (256u << 10) && a.in_off != a.out_off;
 #define PCCL_AR(DT_, OP_)                                                                              \

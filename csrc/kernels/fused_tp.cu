@@ -134,15 +134,17 @@ int launchAgGemm(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_t s
   if (pair && (A.n_copy & 1)) A.n_copy += 1;
   A.probe = g_probe;
   if (A.tail_tiles < 0 && A.n_copy > 0) {
-    // Size of the tail from a cost model: the copy CTAs are busy for about t_copy (the rank's rows to every peer's port at
-    // ~600 GB/s), a tile takes t_tile at ~1.5 PFLOP/s over the whole GPU; the tail makes both groups finish together:
+    // Size of the tail from a cost model: the copy CTAs are busy for about t_copy (a copy CTA was measured to push about
+    // 6.6 GB/s: 24 KiB in flight against a few microseconds of store round trip), a tile takes t_tile at ~1.5 PFLOP/s over
+    // the whole GPU; the tail makes both groups finish together:
     //   (T - R) / G = t_copy / t_tile + R / C   with T tiles, G GEMM groups, C copy groups.
     const int unit = pair ? 2 : 1;
     const double T = static_cast<double>(A.w.world) * (A.M_local / (BM * unit)) * ((A.N + BN - 1) / BN);
     const double C = A.n_copy / unit, G = (ctas - A.n_copy) / unit;
     const double t_tile = 2.0 * BM * unit * BN * A.K / (1.5e15 / (148.0 / unit));
-    const double bytes = static_cast<double>(A.w.world - 1) * A.M_local * A.K * (A.elem_bytes ? A.elem_bytes : 2);
-    const double t_copy = bytes / 600e9 + 20e-6;
+    const bool mc = A.w.mc_heap != nullptr && A.nvirt <= 1;      // one multicast store reaches every peer
+    const double bytes = static_cast<double>(mc ? 1 : A.w.world - 1) * A.M_local * A.K * (A.elem_bytes ? A.elem_bytes : 2);
+    const double t_copy = bytes / (6.6e9 * A.n_copy) + 20e-6;
     double Rt = (T - G * t_copy / t_tile) * C / (G + C);
     A.tail_tiles = Rt > 0 ? static_cast<int>(Rt) : 0;
   }

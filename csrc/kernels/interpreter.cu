@@ -67,6 +67,45 @@ __device__ __forceinline__ void reduce_range_f(char* dst, const char* src, uint6
     store1<DT>(dst + b, red1<OP>(load1<DT>(dst + b), load1<DT>(src + b)));
 }
 
+// dst = dst (op) src[0] (op) ... (op) src[k-1] in ONE pass: the destination is read and written once and the loads of
+// all sources of a vector are in flight together (a chain of two-operand reduces makes a pass per source).
+constexpr int kMaxFused = 8;
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ void reduce_n_range_f(char* dst, char* const* src, int k, uint64_t bytes) {
+  constexpr int N = Lanes<DT>::n;
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  const uint64_t nvec = bytes >> 4;
+  for (uint64_t i = tid; i < nvec; i += nt) {
+    Vec16 v[kMaxFused + 1];
+    v[0] = ld16(dst + (i << 4));
+#pragma unroll
+    for (int s = 0; s < kMaxFused; ++s)
+      if (s < k) v[s + 1] = ld16(src[s] + (i << 4));
+    float acc[N];
+    unpack<DT>(v[0], acc);
+#pragma unroll
+    for (int s = 0; s < kMaxFused; ++s) {
+      if (s < k) {
+        float f[N];
+        unpack<DT>(v[s + 1], f);
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] = red1<OP>(acc[e], f[e]);
+      }
+    }
+    st16(dst + (i << 4), pack<DT>(acc));
+  }
+}
+
+template <uint32_t OP>
+__device__ __forceinline__ bool reduce_n_dispatch(uint32_t dt, char* dst, char* const* src, int k, uint64_t bytes) {
+  switch (dt) {
+    case DT_F32: reduce_n_range_f<DT_F32, OP>(dst, src, k, bytes); return true;
+    case DT_BF16: reduce_n_range_f<DT_BF16, OP>(dst, src, k, bytes); return true;
+    case DT_F16: reduce_n_range_f<DT_F16, OP>(dst, src, k, bytes); return true;
+    default: return false;
+  }
+}
+
 template <typename T, uint32_t OP>
 __device__ __forceinline__ void reduce_range_i(char* dst, const char* src, uint64_t bytes) {
   T* d = reinterpret_cast<T*>(dst);
@@ -97,9 +136,17 @@ __device__ __forceinline__ bool reduce_dispatch(uint32_t dt, char* dst, const ch
 
 template <uint32_t DT, uint32_t OP>
 __device__ __forceinline__ void mm_ld_reduce_range(char* dst, const char* mc_src, uint64_t bytes) {
-  const uint64_t nvec = bytes >> 4;
-  for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x)
-    st16(dst + (i << 4), multimem_ld_reduce<DT, OP>(mc_src + (i << 4)));
+  const uint64_t nvec = bytes >> 4, nt = blockDim.x;
+  uint64_t i = threadIdx.x;
+  for (; i + 3 * nt < nvec; i += 4 * nt) {       // four in-switch reductions in flight per thread
+    const Vec16 a = multimem_ld_reduce<DT, OP>(mc_src + (i << 4)), b = multimem_ld_reduce<DT, OP>(mc_src + ((i + nt) << 4));
+    const Vec16 c = multimem_ld_reduce<DT, OP>(mc_src + ((i + 2 * nt) << 4)), d = multimem_ld_reduce<DT, OP>(mc_src + ((i + 3 * nt) << 4));
+    st16(dst + (i << 4), a);
+    st16(dst + ((i + nt) << 4), b);
+    st16(dst + ((i + 2 * nt) << 4), c);
+    st16(dst + ((i + 3 * nt) << 4), d);
+  }
+  for (; i < nvec; i += nt) st16(dst + (i << 4), multimem_ld_reduce<DT, OP>(mc_src + (i << 4)));
 }
 
 __device__ __forceinline__ bool mm_ld_reduce_dispatch(uint32_t dt, uint32_t op, char* dst, const char* mc, uint64_t bytes) {
@@ -112,8 +159,17 @@ __device__ __forceinline__ bool mm_ld_reduce_dispatch(uint32_t dt, uint32_t op, 
 }
 
 __device__ __forceinline__ void mm_st_range(char* mc_dst, const char* src, uint64_t bytes) {
-  const uint64_t nvec = bytes >> 4;
-  for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) multimem_st(mc_dst + (i << 4), ld16(src + (i << 4)));
+  const uint64_t nvec = bytes >> 4, nt = blockDim.x;
+  uint64_t i = threadIdx.x;
+  for (; i + 3 * nt < nvec; i += 4 * nt) {
+    const Vec16 a = ld16(src + (i << 4)), b = ld16(src + ((i + nt) << 4));
+    const Vec16 c = ld16(src + ((i + 2 * nt) << 4)), d = ld16(src + ((i + 3 * nt) << 4));
+    multimem_st(mc_dst + (i << 4), a);
+    multimem_st(mc_dst + ((i + nt) << 4), b);
+    multimem_st(mc_dst + ((i + 2 * nt) << 4), c);
+    multimem_st(mc_dst + ((i + 3 * nt) << 4), d);
+  }
+  for (; i < nvec; i += nt) multimem_st(mc_dst + (i << 4), ld16(src + (i << 4)));
 }
 
 __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ InterpLaunch L) {
@@ -166,8 +222,26 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
     return ho < 0 ? nullptr : W.mc_heap + ho + off;
   };
 
+  // The stream is read through shared memory, kChunk instructions at a time (the CTA loads a chunk with 16-byte
+  // vectors; a thread then reads its instruction from shared memory instead of 64 bytes of global memory each).
+  constexpr uint32_t kChunk = kInstrPad;
+  __shared__ __align__(16) Instr s_prog[kChunk];
+  uint32_t chunk_base = 0x80000000u;                   // "no chunk loaded": pc - chunk_base is then far above kChunk
+  auto fetch = [&](uint32_t pc) -> const Instr& {       // uniform over the CTA
+    if (pc - chunk_base >= kChunk) {
+      __syncthreads();                                   // everybody is done with the previous chunk
+      chunk_base = pc;
+      // the host pads the instruction array with kInstrPad no-ops, so a whole chunk can always be read
+      const Vec16* g = reinterpret_cast<const Vec16*>(prog + pc);
+      Vec16* sm = reinterpret_cast<Vec16*>(s_prog);
+      for (uint32_t i = threadIdx.x; i < kChunk * 4; i += blockDim.x) sm[i] = g[i];
+      __syncthreads();
+    }
+    return s_prog[pc - chunk_base];
+  };
+
   for (uint32_t pc = 0;; ++pc) {
-    const Instr in = prog[pc];
+    const Instr in = fetch(pc);
     if (in.op == OP_END) break;
     uint32_t fail = 0;
     if (trace && threadIdx.x == 0) trace[2ull * pc] = global_timer_ns();
@@ -189,12 +263,50 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
           if (in.op == OP_COPY) {
             if (s != d) copy_range(d, s, in.bytes);
           } else {
+            // Fold the reduces that follow into this one when they have the same destination ("WAIT; REDUCE" pairs: the
+            // waits are taken first, which only delays this stream): one pass over the destination instead of one per source.
+            char* srcs[kMaxFused];
+            srcs[0] = s;
+            int k = 1;
+            uint32_t j = pc + 1;
+            const bool fusable = !trace && (L.dtype == DT_F32 || L.dtype == DT_BF16 || L.dtype == DT_F16) &&
+                                 ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | in.bytes) & 15) == 0;
+            while (fusable && k < kMaxFused && !fail) {
+              const uint32_t idx = j - chunk_base;
+              if (idx + 1 >= kChunk) break;                      // look only inside the chunk that is in shared memory
+              const Instr& a = s_prog[idx];
+              const bool waits = a.op == OP_WAIT && s_prog[idx + 1].op == OP_REDUCE;
+              if (!waits && a.op != OP_REDUCE) break;
+              const Instr& r = waits ? s_prog[idx + 1] : a;
+              if (r.dst_rank != in.dst_rank || r.dst_buf != in.dst_buf || r.dst_off != in.dst_off || r.bytes != in.bytes) break;
+              if (L.bounds_check && r.src_off + r.bytes > R.buf_bytes[r.src_buf]) break;      // left to the plain path, which reports it
+              char* sp = resolve(r.src_rank, r.src_buf, r.src_off);
+              if (!sp || (reinterpret_cast<uintptr_t>(sp) & 15)) break;
+              if (waits) {
+                if (threadIdx.x == 0 && !wait_ge(my_sig + a.slot, L.epoch * a.count + a.value, L.spin_limit, R.status)) s_fail = ST_TIMEOUT;
+                __syncthreads();
+                if (s_fail) { fail = s_fail; pc = j; break; }
+              }
+              srcs[k++] = sp;
+              j += waits ? 2 : 1;
+            }
+            if (fail) break;
             bool ok = false;
-            switch (L.redop) {
-              case RED_SUM: ok = reduce_dispatch<RED_SUM>(L.dtype, d, s, in.bytes); break;
-              case RED_MAX: ok = reduce_dispatch<RED_MAX>(L.dtype, d, s, in.bytes); break;
-              case RED_MIN: ok = reduce_dispatch<RED_MIN>(L.dtype, d, s, in.bytes); break;
-              case RED_PROD: ok = reduce_dispatch<RED_PROD>(L.dtype, d, s, in.bytes); break;
+            if (k > 1) {
+              switch (L.redop) {
+                case RED_SUM: ok = reduce_n_dispatch<RED_SUM>(L.dtype, d, srcs, k, in.bytes); break;
+                case RED_MAX: ok = reduce_n_dispatch<RED_MAX>(L.dtype, d, srcs, k, in.bytes); break;
+                case RED_MIN: ok = reduce_n_dispatch<RED_MIN>(L.dtype, d, srcs, k, in.bytes); break;
+                case RED_PROD: ok = reduce_n_dispatch<RED_PROD>(L.dtype, d, srcs, k, in.bytes); break;
+              }
+              pc = j - 1;                                        // the folded instructions are done
+            } else {
+              switch (L.redop) {
+                case RED_SUM: ok = reduce_dispatch<RED_SUM>(L.dtype, d, s, in.bytes); break;
+                case RED_MAX: ok = reduce_dispatch<RED_MAX>(L.dtype, d, s, in.bytes); break;
+                case RED_MIN: ok = reduce_dispatch<RED_MIN>(L.dtype, d, s, in.bytes); break;
+                case RED_PROD: ok = reduce_dispatch<RED_PROD>(L.dtype, d, s, in.bytes); break;
+              }
             }
             if (!ok) fail = ST_UNSUPPORTED;
           }

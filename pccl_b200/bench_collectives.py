@@ -97,11 +97,11 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
         if impl == "interp":
             # the same collective as a lowered pccl_b200.lang program run by the persistent interpreter kernel:
             # best program and width (runtime CTA budget) for this size
-            if nbytes > (64 << 20):
-                continue
             best = None
             for name in interp_programs(eng, kind):
-                for width in (4, 16, 32):
+                if nbytes > (64 << 20) and "nvls" not in name:      # the direct forms stage through the workspace
+                    continue
+                for width in ((4, 16, 32) if nbytes <= (64 << 20) else (32,)):
                     if kind == "allreduce":
                         fn = lambda i, n_=name, w_=width: eng.exeOp(n_, ins[i], outs[i], width=w_)  # noqa: E731
                     elif kind == "reduce_scatter":

@@ -48,6 +48,40 @@ def test_allreduce_emulated(native, world, dtype, count):
             assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype,redop", [(torch.float32, "sum"), (torch.bfloat16, "sum"), (torch.bfloat16, "max")])
+@pytest.mark.parametrize("count", [2, 1024, 16 * 1024])
+def test_allreduce_low_latency_path_emulated(native, world, dtype, redop, count):
+    """All-reduce of up to 64 KiB with the flag travelling in the data (8-byte packets {word, launch number}): no barrier,
+    out of place and in place, several launches on alternating receive areas."""
+    es = torch.empty((), dtype=dtype).element_size()
+    size = (count * es + 255) // 256 * 256
+    ll_off = DATA_OFF + 2 * size
+    hs = [torch.zeros(ll_off + native.LL_LANE_BYTES, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    g = torch.Generator(device="cuda").manual_seed(1)
+    xs = [torch.randn(count, generator=g, device="cuda").to(dtype) for _ in range(world)]
+    for epoch in (1, 2, 3, 4):
+        in_place = epoch == 4
+        for r in range(world):
+            _view(hs[r], 0, count, dtype).copy_(xs[r] * epoch)
+        native.emu_collective("allreduce", [h.data_ptr() for h in hs], SIGNAL_OFF, FLAG_OFF, NAMES[dtype], redop,
+                              DATA_OFF, DATA_OFF if in_place else DATA_OFF + size, count, epoch, 0, 1.0, "", 4, 256,
+                              torch.cuda.current_stream().cuda_stream, [s.data_ptr() for s in st], [], [], 0, 0, 0, ll_off)
+        torch.cuda.synchronize()
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        stack = torch.stack([(x * epoch).float() for x in xs])
+        ref = stack.sum(0) if redop == "sum" else stack.max(0).values
+        tol = 1e-5 * world if dtype == torch.float32 else 0.04 * world
+        for r in range(world):
+            got = _view(hs[r], 0 if in_place else size, count, dtype).float()
+            assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item()), (epoch, r)
+        # the packets of this launch are in the receive area of its parity: the path was taken
+        slot = native.LL_LANE_BYTES // 2 // native.MAX_RANKS                      # rank 1's packets in rank 0's area
+        first = hs[0][ll_off + (epoch & 1) * (native.LL_LANE_BYTES // 2) + slot:][:8].view(torch.int64)[0].item()
+        assert first >> 32 == epoch, "the low-latency path was not taken"
+
+
 @pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("redop", ["max", "min"])
 def test_allreduce_minmax_in_place(native, world, redop):

@@ -19,7 +19,11 @@ def _run(case, nproc, tmp_path, env=None, timeout=600):
            "--master-port", str(free_port()), os.path.join(HERE, "mp_worker.py"), case, str(out)]
     e = dict(os.environ)
     e.update(env or {})
-    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=timeout)
+    for attempt in range(3):
+        r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=timeout)
+        if out.exists() or "EADDRINUSE" not in r.stderr:
+            break
+        cmd[cmd.index("--master-port") + 1] = str(free_port())      # the port was taken between the probe and the launch
     results = json.loads(out.read_text()) if out.exists() else None
     assert results is not None, f"workers left no result file\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
     for rank, res in enumerate(results):
