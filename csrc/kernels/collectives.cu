@@ -479,7 +479,14 @@ int launchAllReduce(const CollArgs& a, int blocks, int threads, cudaStream_t str
     const int words = static_cast<int>(bytes / 4);
     int ll_blocks = (words + threads - 1) / threads;
     if (ll_blocks > 32) ll_blocks = 32;
-#define PCCL_LL(DT_, OP_) return launchCoop(allreduce_ll_kernel<DT_, OP_>, a, ll_blocks, threads, stream);
+    // One rank per launch: at most 32 CTAs, which wait only on other GPUs, so a plain launch will do (it costs less on
+    // the host than a cooperative one, and this path is about latency).  Emulated ranks share a GPU: cooperative.
+#define PCCL_LL(DT_, OP_)                                                            \
+    if (a.nvirt <= 1) {                                                              \
+      allreduce_ll_kernel<DT_, OP_><<<ll_blocks, threads, 0, stream>>>(a);           \
+      return static_cast<int>(cudaGetLastError());                                   \
+    }                                                                                \
+    return launchCoop(allreduce_ll_kernel<DT_, OP_>, a, ll_blocks, threads, stream);
     switch (a.dtype) {
       case DT_F32: switch (a.redop) { case RED_SUM: PCCL_LL(DT_F32, RED_SUM) case RED_MAX: PCCL_LL(DT_F32, RED_MAX) default: PCCL_LL(DT_F32, RED_MIN) }
       case DT_BF16: switch (a.redop) { case RED_SUM: PCCL_LL(DT_BF16, RED_SUM) case RED_MAX: PCCL_LL(DT_BF16, RED_MAX) default: PCCL_LL(DT_BF16, RED_MIN) }

@@ -149,6 +149,31 @@ __device__ __forceinline__ void mm_ld_reduce_range(char* dst, const char* mc_src
   for (; i < nvec; i += nt) st16(dst + (i << 4), multimem_ld_reduce<DT, OP>(mc_src + (i << 4)));
 }
 
+// in-switch reduction handed straight to a multicast store: the reduced vector never visits local memory on its way
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ void mm_reduce_bcast_range(char* mc_dst, const char* mc_src, uint64_t bytes) {
+  const uint64_t nvec = bytes >> 4, nt = blockDim.x;
+  uint64_t i = threadIdx.x;
+  for (; i + 3 * nt < nvec; i += 4 * nt) {
+    const Vec16 a = multimem_ld_reduce<DT, OP>(mc_src + (i << 4)), b = multimem_ld_reduce<DT, OP>(mc_src + ((i + nt) << 4));
+    const Vec16 c = multimem_ld_reduce<DT, OP>(mc_src + ((i + 2 * nt) << 4)), d = multimem_ld_reduce<DT, OP>(mc_src + ((i + 3 * nt) << 4));
+    multimem_st(mc_dst + (i << 4), a);
+    multimem_st(mc_dst + ((i + nt) << 4), b);
+    multimem_st(mc_dst + ((i + 2 * nt) << 4), c);
+    multimem_st(mc_dst + ((i + 3 * nt) << 4), d);
+  }
+  for (; i < nvec; i += nt) multimem_st(mc_dst + (i << 4), multimem_ld_reduce<DT, OP>(mc_src + (i << 4)));
+}
+
+__device__ __forceinline__ bool mm_reduce_bcast_dispatch(uint32_t dt, uint32_t op, char* mc_dst, const char* mc_src, uint64_t bytes) {
+#define PCCL_MM(DT_, OP_) if (dt == DT_ && op == OP_) { mm_reduce_bcast_range<DT_, OP_>(mc_dst, mc_src, bytes); return true; }
+  PCCL_MM(DT_F32, RED_SUM)
+  PCCL_MM(DT_BF16, RED_SUM) PCCL_MM(DT_BF16, RED_MAX) PCCL_MM(DT_BF16, RED_MIN)
+  PCCL_MM(DT_F16, RED_SUM) PCCL_MM(DT_F16, RED_MAX) PCCL_MM(DT_F16, RED_MIN)
+#undef PCCL_MM
+  return false;
+}
+
 __device__ __forceinline__ bool mm_ld_reduce_dispatch(uint32_t dt, uint32_t op, char* dst, const char* mc, uint64_t bytes) {
 #define PCCL_MM(DT_, OP_) if (dt == DT_ && op == OP_) { mm_ld_reduce_range<DT_, OP_>(dst, mc, bytes); return true; }
   PCCL_MM(DT_F32, RED_SUM)
@@ -313,6 +338,20 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
         } else if (in.op == OP_MM_LD_REDUCE) {
           char* mc = resolve_mc(in.src_buf, in.src_off);
           char* d = resolve(me, in.dst_buf, in.dst_off);
+          // "reduce my slice in the switch, then multicast it from where it landed": when the next instruction stores
+          // exactly this result to the same place on every rank, the two become one loop (the multicast store also
+          // writes this rank's own copy)
+          const uint32_t nidx = pc + 1 - chunk_base;
+          if (!trace && mc && d && nidx < kChunk && s_prog[nidx].op == OP_MM_ST && s_prog[nidx].src_buf == in.dst_buf &&
+              s_prog[nidx].src_off == in.dst_off && s_prog[nidx].dst_buf == in.dst_buf && s_prog[nidx].dst_off == in.dst_off &&
+              s_prog[nidx].bytes == in.bytes) {
+            char* mcd = resolve_mc(in.dst_buf, in.dst_off);
+            if (mcd && !((reinterpret_cast<uintptr_t>(mc) | reinterpret_cast<uintptr_t>(mcd) | in.bytes) & 15) &&
+                mm_reduce_bcast_dispatch(L.dtype, L.redop, mcd, mc, in.bytes)) {
+              ++pc;
+              break;
+            }
+          }
           if (!mc || !d || ((reinterpret_cast<uintptr_t>(mc) | reinterpret_cast<uintptr_t>(d) | in.bytes) & 15) ||
               !mm_ld_reduce_dispatch(L.dtype, L.redop, d, mc, in.bytes))
             fail = ST_UNSUPPORTED;

@@ -151,6 +151,8 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
                 res[impl]["algo"] = "nvls" if (eng.has_nvls and per_rank % 16 == 0 and per_rank < (4 << 20)) else "p2p"
             else:
                 res[impl]["algo"] = C._algo(eng, "auto", dtype_name(dtype), "sum", per_rank, kind)
+                if kind == "allreduce" and nbytes <= (64 << 10) and nbytes % 4 == 0 and os.environ.get("PCCL_LL", "1") != "0":
+                    res[impl]["algo"] = "ll"          # flag-in-data packets, no barrier (csrc/kernels/collectives.cu)
     eng.symmetric_reset(mark)
     return res
 
