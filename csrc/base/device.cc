@@ -23,6 +23,8 @@ void RemoteCommunicatorBase::unregBuffer(uint32_t) { throw na("unregBuffer"); }
 void RemoteCommunicatorBase::regRemoteHandle(int, const std::string&) { throw na("regRemoteHandle"); }
 void RemoteCommunicatorBase::connect(int) { throw na("connect"); }
 void RemoteCommunicatorBase::disconnect(int) { throw na("disconnect"); }
+bool RemoteCommunicatorBase::put(int, uint32_t, uint64_t, const void*, uint64_t) { return false; }
+bool RemoteCommunicatorBase::signal(int, uint32_t, uint64_t) { return false; }
 
 namespace {
 std::mutex& mu() { static std::mutex m; return m; }

@@ -43,6 +43,13 @@ class RemoteCommunicatorBase {
   virtual void regRemoteHandle(int peer, const std::string& handle);
   virtual void connect(int peer);
   virtual void disconnect(int peer);
+  // Data plane.  put: `bytes` from local `src` into the peer's registered buffer `remote_key` at `remote_off`.
+  // signal: add `add` to the peer's signal word `slot`; it becomes visible after every put issued before it to the
+  // same peer.  Both return false when the peer cannot be reached (the executor reports ST_PEER_GONE).
+  virtual bool put(int peer, uint32_t remote_key, uint64_t remote_off, const void* src, uint64_t bytes);
+  virtual bool signal(int peer, uint32_t slot, uint64_t add);
+  virtual uint64_t bytesSent() const { return 0; }
+  virtual uint64_t bytesReceived() const { return 0; }
 };
 
 class DeviceBase : public AllocatorBase, public IpcCommunicatorBase, public RemoteCommunicatorBase {

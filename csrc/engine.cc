@@ -56,6 +56,7 @@ Engine::~Engine() {
     if (t.words) cudaFree(t.words);
   dropPeers();
   if (tcp_) tcp_->shutdown();
+  if (verbs_) verbs_->shutdown();
   if (heap_) {
     auto dev = getDev(device_);
     if (dev) {
@@ -150,10 +151,25 @@ void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
     tcp_->setSignals(reinterpret_cast<std::atomic<uint64_t>*>(heap_ + layout_.signal_off),
                      static_cast<uint32_t>(layout_.num_signals));
     configs_["remote.tcp.buffer.cpu.key"] = std::to_string(tcp_key_);
+    remote_ = tcp_.get();
+    remote_key_ = tcp_key_;
   }
   std::string why;
-  configs_["remote.verbs.available"] = verbsAvailable(&why) ? "1" : "0";
+  const bool have_verbs = VerbsTransport::probe(&why);
+  configs_["remote.verbs.available"] = have_verbs ? "1" : "0";
   configs_["remote.verbs.note"] = why;
+  if (device_ == "cpu" && LaunchEnvironments::getEnv("PCCL_TRANSPORT") == "verbs") {
+    // asked for by name: without a usable device this is an error, not a silent fall-back
+    if (!have_verbs) throw std::runtime_error("initEngine: PCCL_TRANSPORT=verbs, but " + why);
+    verbs_ = std::make_unique<VerbsTransport>(rank_, world_);
+    verbs_->activate();
+    verbs_key_ = verbs_->regBuffer(heap_, layout_.total);
+    verbs_->setSignalRegion(verbs_key_, layout_.signal_off, static_cast<uint32_t>(layout_.num_signals));
+    configs_["remote.verbs.endpoint"] = verbs_->endpoint();
+    configs_["remote.verbs.buffer.cpu.key"] = std::to_string(verbs_key_);
+    remote_ = verbs_.get();
+    remote_key_ = verbs_key_;
+  }
   initialized_ = true;
   PCCL_LOG_INFO("engine: rank %d/%d on %s, heap %llu MiB", rank_, world_, device_.c_str(),
                 static_cast<unsigned long long>(layout_.total / kMiB));
@@ -179,6 +195,9 @@ void Engine::dropPeers() {
   }
   if (tcp_)
     for (int r = 0; r < world_; ++r) tcp_->disconnect(r);
+  if (verbs_)
+    for (int r = 0; r < world_; ++r)
+      if (r != rank_) verbs_->disconnect(r);
 }
 
 void Engine::setupPeers(const std::map<int, NodeMeta>& nodes) {
@@ -194,13 +213,20 @@ void Engine::setupPeers(const std::map<int, NodeMeta>& nodes) {
     };
     if (get("device") != device_) throw std::runtime_error("setupPeers: rank " + std::to_string(r) + " runs on a different device kind");
     bool same_host = get("host_id") == host_id_;
-    bool use_tcp = device_ == "cpu" && (forced == "tcp" || !same_host);
+    bool use_tcp = device_ == "cpu" && (forced == "tcp" || forced == "verbs" || !same_host);
     if (!use_tcp) {
       if (!same_host) throw std::runtime_error("setupPeers: CUDA ranks on different hosts need a network transport that this build lacks");
       if (!peer_heaps_[r]) peer_heaps_[r] = static_cast<char*>(dev->mapBuffer(get("ipc." + device_ + ".handle")));
     } else {
-      tcp_->regRemoteHandle(r, get("remote.tcp.endpoint"));
-      tcp_->connect(r);
+      if (verbs_) {
+        std::string ep = get("remote.verbs.endpoint");
+        if (ep.empty()) throw std::runtime_error("setupPeers: rank " + std::to_string(r) + " published no verbs endpoint");
+        verbs_->regRemoteHandle(r, ep);
+        verbs_->connect(r);
+      } else {
+        tcp_->regRemoteHandle(r, get("remote.tcp.endpoint"));
+        tcp_->connect(r);
+      }
     }
   }
 }
@@ -450,8 +476,8 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
     ctx.peer_scratch[r] = peer_heaps_[r] + scratch_off;
     ctx.peer_signals[r] = reinterpret_cast<std::atomic<uint64_t>*>(peer_heaps_[r] + layout_.signal_off);
   }
-  ctx.tcp = tcp_.get();
-  ctx.tcp_scratch_key = tcp_key_;
+  ctx.tcp = remote_;
+  ctx.tcp_scratch_key = remote_key_;
   ctx.tcp_scratch_off = scratch_off;
   ctx.slot_base = var.slot_base;
   ctx.epoch = var.epoch++;
@@ -638,6 +664,11 @@ std::string Engine::stats() {
   j.set("multicast", mc_base_ != nullptr);
   j.set("log_file", Logger::get().path());
   j.set("log_errors", Logger::get().count(LogLevel::Error));
+  if (verbs_) {
+    j.set("verbs_bytes_sent", verbs_->bytesSent());
+    for (int r = 0; r < world_; ++r)
+      if (r != rank_) j.set("verbs_qp_state." + std::to_string(r), verbs_->queuePairState(r));
+  }
   if (tcp_) {
     j.set("tcp_bytes_sent", tcp_->bytesSent());
     j.set("tcp_bytes_received", tcp_->bytesReceived());

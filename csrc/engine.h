@@ -29,6 +29,7 @@
 #include "kernels/api.h"
 #include "mem/cuda_device.h"
 #include "transport/tcp_transport.h"
+#include "transport/verbs_transport.h"
 
 namespace pccl {
 
@@ -143,6 +144,12 @@ class Engine {
   std::unique_ptr<ClusterManager> cluster_;
   std::unique_ptr<TcpTransport> tcp_;
   uint32_t tcp_key_ = 0;
+  // InfiniBand / RoCE data plane (PCCL_TRANSPORT=verbs on CPU ranks): used instead of tcp_ for peers that are reached
+  // over the network; remote_ points at whichever of the two carries remote PUT / SIGNAL traffic.
+  std::unique_ptr<VerbsTransport> verbs_;
+  uint32_t verbs_key_ = 0;
+  RemoteCommunicatorBase* remote_ = nullptr;
+  uint32_t remote_key_ = 0;
   std::map<std::string, Op> ops_;
   uint32_t next_slot_ = 0;
   std::mutex mu_;

@@ -23,7 +23,7 @@ struct CpuExecContext {
   uint64_t local_bytes[BUF_COUNT] = {0, 0, 0};
   std::vector<char*> peer_scratch;                         // per rank; nullptr = reach it over TCP
   std::vector<std::atomic<uint64_t>*> peer_signals;        // per rank; nullptr = over TCP
-  TcpTransport* tcp = nullptr;
+  RemoteCommunicatorBase* tcp = nullptr;              // the data plane for peers that cannot be mapped (TCP or verbs)
   uint32_t tcp_scratch_key = 0;
   uint64_t tcp_scratch_off = 0;      // lane offset inside the peer's registered workspace
   uint32_t slot_base = 0;            // first signal slot of this op

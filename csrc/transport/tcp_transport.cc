@@ -178,33 +178,4 @@ void TcpTransport::readerLoop(int fd) {
   }
 }
 
-bool verbsAvailable(std::string* why) {
-  if (LaunchEnvironments::has("PCCL_DISABLE_IB")) {
-    if (why) *why = "disabled by PCCL_DISABLE_IB";
-    return false;
-  }
-  void* lib = ::dlopen("libibverbs.so.1", RTLD_NOW | RTLD_LOCAL);
-  if (!lib) lib = ::dlopen("libibverbs.so", RTLD_NOW | RTLD_LOCAL);
-  if (!lib) {
-    if (why) *why = "libibverbs is not installed";
-    return false;
-  }
-  using GetList = void** (*)(int*);
-  using FreeList = void (*)(void**);
-  auto get = reinterpret_cast<GetList>(::dlsym(lib, "ibv_get_device_list"));
-  auto fre = reinterpret_cast<FreeList>(::dlsym(lib, "ibv_free_device_list"));
-  int n = 0;
-  if (get) {
-    void** l = get(&n);
-    if (l && fre) fre(l);
-  }
-  ::dlclose(lib);
-  if (n <= 0) {
-    if (why) *why = "no verbs device present";
-    return false;
-  }
-  if (why) *why = "verbs devices present, but no verbs data path is built in this image (header infiniband/verbs.h absent)";
-  return false;
-}
-
 }  // namespace pccl

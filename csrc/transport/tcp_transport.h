@@ -32,11 +32,11 @@ class TcpTransport : public RemoteCommunicatorBase {
   void disconnect(int peer) override;
 
   void setSignals(std::atomic<uint64_t>* signals, uint32_t count) { signals_ = signals; num_signals_ = count; }
-  bool put(int peer, uint32_t remote_key, uint64_t remote_off, const void* src, uint64_t bytes);
-  bool signal(int peer, uint32_t slot, uint64_t add);
+  bool put(int peer, uint32_t remote_key, uint64_t remote_off, const void* src, uint64_t bytes) override;
+  bool signal(int peer, uint32_t slot, uint64_t add) override;
   void shutdown();
-  uint64_t bytesSent() const { return bytes_sent_.load(); }
-  uint64_t bytesReceived() const { return bytes_recv_.load(); }
+  uint64_t bytesSent() const override { return bytes_sent_.load(); }
+  uint64_t bytesReceived() const override { return bytes_recv_.load(); }
   void setAdvertisedHost(const std::string& h) { host_ = h; }
 
  private:
@@ -60,11 +60,5 @@ class TcpTransport : public RemoteCommunicatorBase {
   uint32_t num_signals_ = 0;
   std::atomic<uint64_t> bytes_sent_{0}, bytes_recv_{0};
 };
-
-// InfiniBand/RoCE probe.  The verbs plugin of the reference (include/plugins/rdma_executor/utils/
-// rdma_utils.h:15-319) dlopen()s libibverbs; the header infiniband/verbs.h is not installed here
-// and GPUs of one box talk over NVLink, so only availability detection is kept: when verbs is
-// absent or PCCL_DISABLE_IB is set, remote peers use TcpTransport.
-bool verbsAvailable(std::string* why);
 
 }  // namespace pccl
