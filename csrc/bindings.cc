@@ -238,6 +238,12 @@ PYBIND11_MODULE(_C, m) {
       .def("rebind", &Engine::rebind)
       .def("injectFault", &Engine::injectFault)
       .def("nextEpoch", &Engine::nextEpoch)
+      .def("mixedHosts", &Engine::mixedHosts)
+      .def("startResident", &Engine::startResident, py::arg("width") = 4)
+      .def("enqueueOp", &Engine::enqueueOp, py::arg("name"), py::arg("in_ptr"), py::arg("out_ptr"), py::arg("in_bytes"), py::arg("dtype"),
+           py::arg("lane") = 0, py::arg("stream") = 0, py::call_guard<py::gil_scoped_release>())
+      .def("waitOp", &Engine::waitOp, py::arg("ticket"), py::arg("timeout_ms") = 0, py::call_guard<py::gil_scoped_release>())
+      .def("stopResident", &Engine::stopResident, py::call_guard<py::gil_scoped_release>())
       .def_property_readonly("rank", &Engine::rank)
       .def_property_readonly("world", &Engine::world);
 

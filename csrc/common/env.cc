@@ -111,6 +111,7 @@ void registerBuiltinOptions() {
   L::registerOpt("PCCL_GEMM_PAIR", "0: single-CTA GEMM tiles instead of CTA pairs");
   L::registerOpt("PCCL_CACHE_DIR", "directory of the synthesised-schedule cache (default ~/.cache/pccl_b200)");
   L::registerOpt("PCCL_MAX_SMS", "upper bound on CTAs a collective may use (default 32)");
+  L::registerOpt("PCCL_RESIDENT_IDLE_MS", "the resident interpreter kernel leaves after this long without work (default 20)");
   L::registerOpt("PCCL_IBVERBS_LIB", "library to load the verbs API from (default libibverbs.so.1; tests name a stand-in)");
   L::registerOpt("PCCL_LL", "0 keeps all-reduces of up to 64 KiB off the flag-in-data (low-latency) path (default 1)");
   L::registerOpt("PCCL_AG_TAIL", "all-gather GEMM: tiles left to the copy CTAs once their rows are sent (default -1: from a cost model; 0: none)");

@@ -3,7 +3,9 @@
 #include <cuda_runtime.h>
 #include <unistd.h>
 
+#include <chrono>
 #include <cstring>
+#include <thread>
 #include <fstream>
 #include <stdexcept>
 
@@ -34,6 +36,56 @@ std::string readHostId() {
 void cudaCheck(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string("engine: ") + what + ": " + cudaGetErrorString(e));
 }
+
+// Device-memory copies and reductions for the host-driven executor.  Worker threads are short-lived, so streams come
+// from a small pool; every call makes the engine's device current in the calling thread first.
+class CudaMemOps : public MemOps {
+ public:
+  explicit CudaMemOps(int device) : device_(device) {}
+  ~CudaMemOps() override {
+    for (cudaStream_t s : pool_) cudaStreamDestroy(s);
+  }
+  bool copy(void* dst, const void* src, uint64_t bytes) override {
+    Lease l(this);
+    return l.s && cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, l.s) == cudaSuccess && cudaStreamSynchronize(l.s) == cudaSuccess;
+  }
+  bool reduce(void* dst, const void* src, uint64_t bytes, uint32_t dtype, uint32_t redop) override {
+    Lease l(this);
+    return l.s && launchDeviceReduce(dst, src, bytes, dtype, redop, l.s) == 0 && cudaStreamSynchronize(l.s) == cudaSuccess;
+  }
+  const void* toHost(const void* src, uint64_t bytes) override {
+    thread_local std::vector<char> buf;
+    if (buf.size() < bytes) buf.resize(bytes);
+    Lease l(this);
+    if (!l.s || cudaMemcpyAsync(buf.data(), src, bytes, cudaMemcpyDeviceToHost, l.s) != cudaSuccess || cudaStreamSynchronize(l.s) != cudaSuccess)
+      return nullptr;
+    return buf.data();
+  }
+
+ private:
+  struct Lease {
+    CudaMemOps* o;
+    cudaStream_t s = nullptr;
+    explicit Lease(CudaMemOps* ops) : o(ops) {
+      if (cudaSetDevice(o->device_) != cudaSuccess) return;
+      std::lock_guard<std::mutex> g(o->mu_);
+      if (!o->pool_.empty()) {
+        s = o->pool_.back();
+        o->pool_.pop_back();
+      } else if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) {
+        s = nullptr;
+      }
+    }
+    ~Lease() {
+      if (!s) return;
+      std::lock_guard<std::mutex> g(o->mu_);
+      o->pool_.push_back(s);
+    }
+  };
+  int device_;
+  std::mutex mu_;
+  std::vector<cudaStream_t> pool_;
+};
 }  // namespace
 
 Engine::Engine(int rank, int world) : rank_(rank), world_(world) {
@@ -43,6 +95,10 @@ Engine::Engine(int rank, int world) : rank_(rank), world_(world) {
 }
 
 Engine::~Engine() {
+  try {
+    stopResident();
+  } catch (...) {
+  }
   try {
     exitCluster();
   } catch (...) {
@@ -57,6 +113,10 @@ Engine::~Engine() {
   dropPeers();
   if (tcp_) tcp_->shutdown();
   if (verbs_) verbs_->shutdown();
+  device_mem_ops_.reset();
+  if (shadow_stream_) cudaStreamDestroy(static_cast<cudaStream_t>(shadow_stream_));
+  if (shadow_) cudaFreeHost(shadow_);
+  delete[] host_signals_;
   if (heap_) {
     auto dev = getDev(device_);
     if (dev) {
@@ -154,6 +214,15 @@ void Engine::initEngine(const std::string& device, uint64_t heap_bytes) {
     remote_ = tcp_.get();
     remote_key_ = tcp_key_;
   }
+  if (device_ == "cuda" && world_ > 1) {
+    // a listening socket only; the shadow of the workspace and the host signal words are made when a peer turns out
+    // to live on another host (ensureMixedHostResources)
+    cudaCheck(cudaGetDevice(&cuda_ordinal_), "cudaGetDevice");
+    tcp_ = std::make_unique<TcpTransport>();
+    tcp_->setAdvertisedHost(LaunchEnvironments::getStr("PCCL_TCP_HOST", "127.0.0.1"));
+    configs_["remote.tcp.endpoint"] = tcp_->activate();
+    configs_["remote.tcp.buffer.cuda.key"] = "0";
+  }
   std::string why;
   const bool have_verbs = VerbsTransport::probe(&why);
   configs_["remote.verbs.available"] = have_verbs ? "1" : "0";
@@ -215,8 +284,12 @@ void Engine::setupPeers(const std::map<int, NodeMeta>& nodes) {
     bool same_host = get("host_id") == host_id_;
     bool use_tcp = device_ == "cpu" && (forced == "tcp" || forced == "verbs" || !same_host);
     if (!use_tcp) {
-      if (!same_host) throw std::runtime_error("setupPeers: CUDA ranks on different hosts need a network transport that this build lacks");
-      if (!peer_heaps_[r]) peer_heaps_[r] = static_cast<char*>(dev->mapBuffer(get("ipc." + device_ + ".handle")));
+      if (!same_host) {
+        if (!tcp_) throw std::runtime_error("setupPeers: rank " + std::to_string(r) + " is on another host and this engine has no network transport");
+        mixed_hosts_ = true;               // reached through the host shadow of the workspace over TCP
+      } else if (!peer_heaps_[r]) {
+        peer_heaps_[r] = static_cast<char*>(dev->mapBuffer(get("ipc." + device_ + ".handle")));
+      }
     } else {
       if (verbs_) {
         std::string ep = get("remote.verbs.endpoint");
@@ -229,6 +302,42 @@ void Engine::setupPeers(const std::map<int, NodeMeta>& nodes) {
       }
     }
   }
+  if (device_ == "cuda" && mixed_hosts_) {
+    // every signal of the host-driven executor travels over TCP, so every peer needs a connection, also those whose
+    // heap is mapped over NVLink
+    ensureMixedHostResources();
+    for (auto& kv : nodes) {
+      int r = kv.first;
+      if (r == rank_ || r < 0 || r >= world_) continue;
+      auto it = kv.second.endpoint_configs_.find("remote.tcp.endpoint");
+      if (it == kv.second.endpoint_configs_.end()) throw std::runtime_error("setupPeers: rank " + std::to_string(r) + " published no TCP endpoint");
+      tcp_->regRemoteHandle(r, it->second);
+      tcp_->connect(r);
+    }
+  }
+}
+
+void Engine::ensureMixedHostResources() {
+  if (shadow_) return;
+  cudaCheck(cudaHostAlloc(reinterpret_cast<void**>(&shadow_), layout_.workspace_bytes, cudaHostAllocDefault), "pinned shadow of the workspace");
+  host_signals_ = new std::atomic<uint64_t>[layout_.num_signals]();
+  cudaStream_t s = nullptr;
+  cudaCheck(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "shadow stream");
+  shadow_stream_ = s;
+  tcp_key_ = tcp_->regBuffer(shadow_, layout_.workspace_bytes);          // the first registration: key 0, as published
+  tcp_->setSignals(host_signals_, static_cast<uint32_t>(layout_.num_signals));
+  // receiver thread: bytes that arrived in the shadow go on to the same offset of the device heap before the next frame
+  // (so before the SIGNAL that follows them) is read
+  tcp_->setPutHook([this](uint32_t key, uint64_t off, uint64_t bytes) {
+    if (key != tcp_key_ || off + bytes > layout_.workspace_bytes) return;
+    cudaStream_t st = static_cast<cudaStream_t>(shadow_stream_);
+    if (cudaSetDevice(cuda_ordinal_) != cudaSuccess || cudaMemcpyAsync(heap_ + off, shadow_ + off, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+      PCCL_LOG_ERROR("engine: copying %llu received bytes to the device failed", static_cast<unsigned long long>(bytes));
+  });
+  device_mem_ops_ = std::make_unique<CudaMemOps>(cuda_ordinal_);
+  remote_ = tcp_.get();
+  remote_key_ = tcp_key_;
 }
 
 void Engine::importEndpoints(const std::vector<std::string>& docs) {
@@ -348,6 +457,9 @@ void Engine::resetSymmetric(uint64_t mark) {
 }
 
 World Engine::worldTable() const {
+  if (mixed_hosts_)
+    throw std::runtime_error("this kernel addresses every peer's memory directly, but the ranks of this world span several hosts "
+                             "(use a program through exeOp: it runs on the host-driven executor)");
   World w{};
   w.world = world_;
   for (int r = 0; r < world_; ++r) w.heap[r] = peer_heaps_[r];
@@ -409,12 +521,13 @@ int Engine::exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, ui
   if (op.program.world != world_) throw std::runtime_error("exeOp: '" + name + "' was written for another world size");
   if (lane < 0 || lane >= layout_.lanes) throw std::runtime_error("exeOp: lane out of range");
   for (int r = 0; r < world_; ++r)
-    if (r != rank_ && !peer_heaps_[r] && !(tcp_ && device_ == "cpu"))
+    if (r != rank_ && !peer_heaps_[r] && !(tcp_ && (device_ == "cpu" || mixed_hosts_)))
       throw std::runtime_error("exeOp: peers are not connected (joinCluster/importEndpoints first)");
   uint32_t dt = parseDType(dtype);
   if (width < 1) width = 1;
   if (width > max_width_) width = max_width_;
   if (device_ == "cpu") return exeOnCpu(op, in_ptr, out_ptr, in_bytes, dt, width, lane);
+  if (mixed_hosts_) return exeOnCudaHost(op, in_ptr, out_ptr, in_bytes, dt, width, lane, stream);
   return exeOnCuda(op, in_ptr, out_ptr, in_bytes, dt, width, lane, stream);
 }
 
@@ -500,6 +613,67 @@ int Engine::exeOnCpu(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byte
   if (res.status == ST_TIMEOUT) op.timeouts++;
   if (res.status != ST_OK)
     PCCL_LOG_ERROR("exeOp '%s': status %u at stream %d pc %d", p.name.c_str(), res.status, res.failed_stream, res.failed_pc);
+  return static_cast<int>(res.status);
+}
+
+// CUDA engine whose peers are partly on other hosts: the same materialised streams as the CPU executor runs, walked by
+// host threads; COPY and REDUCE act on device memory (peers of this host through their NVLink mapping), a COPY to a
+// peer on another host goes device -> host -> TCP -> the peer's host shadow -> the peer's device, NOTIFY / WAIT use
+// host signal words fed by TCP.  Synchronous: the inputs are awaited on `stream`, the outputs are complete on return.
+int Engine::exeOnCudaHost(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dt, int width, int lane,
+                          uint64_t stream) {
+  const Program& p = op.program;
+  uint64_t bb = p.blockBytesForInput(in_bytes);
+  if (bb % dtypeSize(dt)) throw std::runtime_error("exeOp: block size is not a whole number of elements");
+  if (p.needs_multicast || p.remote_io)
+    throw std::runtime_error("exeOp: this program needs every rank on one NVSwitch; the ranks of this world span several hosts");
+  cudaCheck(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)), "waiting for the inputs");
+  auto key = std::make_pair(bb, width);
+  std::unique_lock<std::mutex> lock(mu_);
+  auto hc = op.host_cache.find(key);
+  if (hc == op.host_cache.end()) hc = op.host_cache.emplace(key, p.materialize(rank_, bb, width)).first;
+  const Materialized& m = hc->second;
+  uint64_t lane_bytes = layout_.workspace_bytes / layout_.lanes, half = lane_bytes / 2 / 4096 * 4096;
+  if (m.buf_bytes[BUF_SCRATCH] > half) throw std::runtime_error("exeOp: message needs more scratch than a workspace lane half holds (raise PCCL_WORKSPACE_MB)");
+  Op::Variant& var = variantFor(op, width);
+  const uint64_t launch_no = lane_launches_.at(lane)++;
+  uint64_t scratch_off = lane * lane_bytes + (launch_no & 1) * half;
+  CpuExecContext ctx;
+  ctx.turn_slot = static_cast<int64_t>(layout_.turn_base) + lane * kMaxRanks;
+  ctx.launch_no = launch_no;
+  ctx.rank = rank_;
+  ctx.world = world_;
+  ctx.local[BUF_INPUT] = reinterpret_cast<char*>(in_ptr);
+  ctx.local[BUF_OUTPUT] = reinterpret_cast<char*>(p.in_place ? in_ptr : out_ptr);
+  ctx.local[BUF_SCRATCH] = heap_ + scratch_off;
+  for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) ctx.local_bytes[b] = m.buf_bytes[b];
+  ctx.peer_scratch.assign(world_, nullptr);
+  ctx.peer_signals.assign(world_, nullptr);
+  for (int r = 0; r < world_; ++r)
+    if (peer_heaps_[r]) ctx.peer_scratch[r] = peer_heaps_[r] + scratch_off;
+  ctx.peer_signals[rank_] = host_signals_;
+  ctx.tcp = tcp_.get();
+  ctx.tcp_scratch_key = tcp_key_;
+  ctx.tcp_scratch_off = scratch_off;
+  ctx.slot_base = var.slot_base;
+  ctx.epoch = var.epoch++;
+  ctx.dtype = dt;
+  ctx.redop = parseRedOp(p.redop);
+  ctx.timeout_ms = timeout_ms_;
+  ctx.bounds_check = bounds_check_;
+  ctx.mem = device_mem_ops_.get();
+  lock.unlock();
+  CpuExecResult res = runOnCpu(m, ctx);
+  lock.lock();
+  op.launches++;
+  op.bytes += m.bytes_moved;
+  op.nanos += res.nanos;
+  if (res.status == ST_TIMEOUT) op.timeouts++;
+  if (res.status != ST_OK) {
+    uint32_t st[4] = {res.status, static_cast<uint32_t>(res.failed_stream), static_cast<uint32_t>(res.failed_pc), 0};
+    cudaMemcpy(reinterpret_cast<void*>(statusPtr(lane)), st, sizeof(st), cudaMemcpyHostToDevice);
+    PCCL_LOG_ERROR("exeOp '%s' (host-driven): status %u at stream %d pc %d", p.name.c_str(), res.status, res.failed_stream, res.failed_pc);
+  }
   return static_cast<int>(res.status);
 }
 
@@ -601,6 +775,172 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   return 0;
 }
 
+// ---- resident executor ---------------------------------------------------------------------------------------------
+void Engine::startResident(int width) {
+  if (!initialized_ || device_ != "cuda") throw std::runtime_error("startResident: a CUDA engine is needed");
+  if (mixed_hosts_) throw std::runtime_error("startResident: the ranks of this world span several hosts");
+  std::lock_guard<std::mutex> g(mu_);
+  if (rq_host_) throw std::runtime_error("startResident: already started");
+  if (width < 1) width = 1;
+  if (width > max_width_) width = max_width_;
+  void* hp = nullptr;
+  cudaCheck(cudaHostAlloc(&hp, sizeof(ResidentQueue), cudaHostAllocMapped), "resident queue");
+  std::memset(hp, 0, sizeof(ResidentQueue));
+  rq_host_ = static_cast<ResidentQueue*>(hp);
+  void* dp = nullptr;
+  cudaCheck(cudaHostGetDevicePointer(&dp, hp, 0), "resident queue (device view)");
+  rq_dev_ = static_cast<ResidentQueue*>(dp);
+  rq_host_->idle_ns = static_cast<uint64_t>(LaunchEnvironments::getInt("PCCL_RESIDENT_IDLE_MS", 20)) * 1000000ull;
+  cudaCheck(cudaMalloc(reinterpret_cast<void**>(&rctl_), sizeof(ResidentCtl)), "resident control block");
+  cudaCheck(cudaMemset(rctl_, 0, sizeof(ResidentCtl)), "resident control block");
+  cudaStream_t s = nullptr;
+  cudaCheck(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "resident stream");
+  resident_stream_ = s;
+  resident_width_ = width;
+  launchResidentKernel();
+}
+
+void Engine::launchResidentKernel() {
+  cudaStream_t s = static_cast<cudaStream_t>(resident_stream_);
+  cudaCheck(cudaStreamSynchronize(s), "resident kernel (previous run)");       // it has left: running == 0
+  rq_host_->stop = 0;
+  rq_host_->running = 1;
+  std::atomic_thread_fence(std::memory_order_seq_cst);
+  // every program of a launch may have up to width x channels streams; the grid must hold the widest registered one,
+  // which is checked per enqueue -- here the grid is sized for the budget
+  int err = launchResident(rq_dev_, rctl_, rq_host_->completed, resident_width_ * kResidentChannels, 512, s);
+  if (err != 0) {
+    rq_host_->running = 0;
+    throw std::runtime_error(std::string("startResident: kernel launch failed: ") + cudaErrorName(err));
+  }
+  resident_launches_++;
+}
+
+uint64_t Engine::enqueueOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, const std::string& dtype, int lane,
+                           uint64_t stream) {
+  if (!rq_host_) throw std::runtime_error("enqueueOp: call startResident first");
+  if (stream) cudaCheck(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)), "enqueueOp: waiting for the inputs");
+  std::unique_lock<std::mutex> lock(mu_);
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("enqueueOp: no op named '" + name + "'");
+  Op& op = it->second;
+  const Program& p = op.program;
+  if (p.world != world_) throw std::runtime_error("enqueueOp: '" + name + "' was written for another world size");
+  if (lane < 0 || lane >= layout_.lanes) throw std::runtime_error("enqueueOp: lane out of range");
+  const int width = resident_width_;
+  const uint32_t dt = parseDType(dtype);
+  uint64_t bb = p.blockBytesForInput(in_bytes);
+  if (bb % dtypeSize(dt)) throw std::runtime_error("enqueueOp: block size is not a whole number of elements");
+  if (p.needs_multicast && !mc_base_) throw std::runtime_error("enqueueOp: program needs NVLS multicast, which is not set up");
+  auto key = std::make_pair(bb, width);
+  auto dc = op.device_cache.find(key);
+  if (dc == op.device_cache.end()) {
+    Op::DeviceCopy c;
+    c.m = p.materialize(rank_, bb, width);
+    std::vector<Instr> flat;
+    std::vector<uint32_t> starts;
+    for (auto& st : c.m.streams) {
+      starts.push_back(static_cast<uint32_t>(flat.size()));
+      flat.insert(flat.end(), st.begin(), st.end());
+    }
+    c.n_streams = static_cast<int>(starts.size());
+    flat.resize(flat.size() + kInstrPad, Instr{});
+    cudaCheck(cudaMalloc(&c.instrs, flat.size() * sizeof(Instr)), "cudaMalloc(instructions)");
+    cudaCheck(cudaMalloc(&c.starts, (starts.size() + 1) * sizeof(uint32_t)), "cudaMalloc(stream table)");
+    cudaCheck(cudaMemcpy(c.instrs, flat.data(), flat.size() * sizeof(Instr), cudaMemcpyHostToDevice), "upload instructions");
+    if (!starts.empty()) cudaCheck(cudaMemcpy(c.starts, starts.data(), starts.size() * sizeof(uint32_t), cudaMemcpyHostToDevice), "upload stream table");
+    dc = op.device_cache.emplace(key, std::move(c)).first;
+  }
+  const Op::DeviceCopy& c = dc->second;
+  if (c.n_streams > resident_width_ * kResidentChannels)
+    throw std::runtime_error("enqueueOp: '" + name + "' has more streams than the resident kernel has CTAs (fewer channels, or a wider kernel)");
+  uint64_t lane_bytes = layout_.workspace_bytes / layout_.lanes, half = lane_bytes / 2 / 4096 * 4096;
+  if (c.m.buf_bytes[BUF_SCRATCH] > half) throw std::runtime_error("enqueueOp: message needs more scratch than a workspace lane half holds");
+  // room in the ring
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms_);
+  while (rq_host_->tail - rq_host_->completed >= kResidentSlots) {
+    if (std::chrono::steady_clock::now() >= deadline) throw std::runtime_error("enqueueOp: the resident queue stayed full");
+    std::this_thread::yield();
+  }
+  auto heapOff = [&](uint64_t ptr) -> long long {
+    uint64_t base = reinterpret_cast<uint64_t>(heap_);
+    return (ptr >= base && ptr < base + layout_.total) ? static_cast<long long>(ptr - base) : -1;
+  };
+  ResidentDesc d{};
+  d.w = worldTable();
+  Op::Variant& var = variantFor(op, width);
+  d.slot_base = var.slot_base;
+  d.epoch = var.epoch++;
+  d.dtype = dt;
+  d.redop = parseRedOp(p.redop);
+  d.spin_limit = spin_limit_;
+  d.bounds_check = bounds_check_ ? 1 : 0;
+  d.r.rank = rank_;
+  d.r.n_streams = c.n_streams;
+  d.r.instrs = c.instrs;
+  d.r.stream_start = c.starts;
+  d.r.input = reinterpret_cast<char*>(in_ptr);
+  d.r.output = reinterpret_cast<char*>(p.in_place ? in_ptr : out_ptr);
+  d.r.input_heap_off = heapOff(in_ptr);
+  d.r.output_heap_off = heapOff(p.in_place ? in_ptr : out_ptr);
+  if (p.remote_io && (d.r.input_heap_off < 0 || d.r.output_heap_off < 0))
+    throw std::runtime_error("enqueueOp: this program lets peers touch the tensors, so both must come from the symmetric heap");
+  const uint64_t launch_no = lane_launches_.at(lane)++;
+  d.r.scratch_off = lane * lane_bytes + (launch_no & 1) * half;
+  for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) d.r.buf_bytes[b] = c.m.buf_bytes[b];
+  d.r.status = reinterpret_cast<uint32_t*>(statusPtr(lane));
+  d.r.trace = nullptr;
+  d.turn_slot = kNoTurnSlot;
+  if (world_ > 1) {
+    d.turn_slot = layout_.turn_base + static_cast<uint32_t>(lane) * kMaxRanks;
+    d.finish_slot = layout_.finish_base + static_cast<uint32_t>(lane);
+    d.launch_no = launch_no;
+  }
+  const uint64_t ticket = rq_host_->tail + 1;
+  std::memcpy(const_cast<ResidentDesc*>(&rq_host_->slots[rq_host_->tail % kResidentSlots]), &d, sizeof(d));
+  std::atomic_thread_fence(std::memory_order_release);
+  rq_host_->tail = ticket;
+  std::atomic_thread_fence(std::memory_order_seq_cst);
+  // the kernel may have left for lack of work (before or just after this write): start it again; a kernel that is
+  // still there simply finds the descriptor
+  if (rq_host_->running == 0) launchResidentKernel();
+  op.launches++;
+  op.bytes += c.m.bytes_moved;
+  resident_ops_++;
+  return ticket;
+}
+
+bool Engine::waitOp(uint64_t ticket, int timeout_ms) {
+  if (!rq_host_) throw std::runtime_error("waitOp: the resident executor is not running");
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms > 0 ? timeout_ms : timeout_ms_);
+  for (int spins = 0; rq_host_->completed < ticket; ++spins) {
+    if ((spins & 255) == 255) {
+      if (rq_host_->running == 0 && rq_host_->completed < ticket && rq_host_->tail >= ticket) {
+        std::lock_guard<std::mutex> g(mu_);
+        if (rq_host_->running == 0 && rq_host_->completed < ticket) launchResidentKernel();     // it left between our write and its last look
+      }
+      if (std::chrono::steady_clock::now() >= deadline) return false;
+    }
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
+  return true;
+}
+
+void Engine::stopResident() {
+  std::lock_guard<std::mutex> g(mu_);
+  if (!rq_host_) return;
+  rq_host_->stop = 1;
+  std::atomic_thread_fence(std::memory_order_seq_cst);
+  cudaStreamSynchronize(static_cast<cudaStream_t>(resident_stream_));
+  cudaStreamDestroy(static_cast<cudaStream_t>(resident_stream_));
+  resident_stream_ = nullptr;
+  cudaFree(rctl_);
+  rctl_ = nullptr;
+  cudaFreeHost(rq_host_);
+  rq_host_ = rq_dev_ = nullptr;
+  resident_width_ = 0;
+}
+
 void Engine::addDeviceSpans(const std::string& name, const Materialized& m, const std::vector<uint64_t>& stamps) {
   size_t flat = 0;
   for (size_t s = 0; s < m.streams.size(); ++s)
@@ -662,6 +1002,10 @@ std::string Engine::stats() {
   j.set("workspace_bytes", layout_.workspace_bytes);
   j.set("signals_used", static_cast<uint64_t>(next_slot_));
   j.set("multicast", mc_base_ != nullptr);
+  j.set("mixed_hosts", mixed_hosts_);
+  j.set("resident_width", resident_width_);
+  j.set("resident_kernel_launches", resident_launches_);
+  j.set("resident_ops", resident_ops_);
   j.set("log_file", Logger::get().path());
   j.set("log_errors", Logger::get().count(LogLevel::Error));
   if (verbs_) {

@@ -62,6 +62,19 @@ class Engine {
   void prepareOp(const std::string& name, int width);
   int exeOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes,
             const std::string& dtype, int width, int lane, uint64_t stream);
+  // ---- resident executor (CUDA engines): a kernel that stays on the GPU and takes launches from a host-filled queue ----
+  // Counterpart of the reference's ring buffer between executor kinds and of its completed / total operator counters
+  // (include/base/operator.h:7-17, 31-38).  startResident launches the kernel with `width` CTAs (cooperatively: it is
+  // refused when they cannot all be resident); enqueueOp writes one descriptor -- no kernel launch -- and returns a
+  // ticket; waitOp blocks until the kernel has finished that ticket.  The program runs at the resident width.  The
+  // tensors must be complete when enqueueOp is called (it synchronises `stream` first when one is given) and must stay
+  // alive until the ticket is done.  The kernel leaves by itself after PCCL_RESIDENT_IDLE_MS without work (default 20)
+  // and is started again by the next enqueueOp, so device-wide synchronisation never waits longer than that.
+  void startResident(int width);
+  uint64_t enqueueOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, const std::string& dtype, int lane,
+                     uint64_t stream);
+  bool waitOp(uint64_t ticket, int timeout_ms);
+  void stopResident();
   std::string exportEndpoint();
   void importEndpoints(const std::vector<std::string>& docs);
   void joinCluster(const std::string& master_endpoint, int timeout_ms = 60000);
@@ -103,6 +116,7 @@ class Engine {
   bool waitForDeparture(int rank, int timeout_ms);
   void rebind(int new_rank, int new_world);   // adopt a ResizeWorld result (drops peer mappings)
   void injectFault(const std::string& kind);  // host-side fault injection for tests
+  bool mixedHosts() const { return mixed_hosts_; }   // CUDA ranks on more than one host: programs only, host-driven
   int rank() const { return rank_; }
   int world() const { return world_; }
   uint64_t nextEpoch(int flag_lane);          // per-lane launch counter for hand-written collectives
@@ -150,6 +164,26 @@ class Engine {
   uint32_t verbs_key_ = 0;
   RemoteCommunicatorBase* remote_ = nullptr;
   uint32_t remote_key_ = 0;
+  // CUDA ranks that do not all share one host (the reference pairs every communicator device with every memory device,
+  // csrc/engine.cc:52-95): peers on this host keep their NVLink mapping for data, peers elsewhere are reached over the
+  // host/TCP transport through a pinned host shadow of the workspace, and every signal travels over TCP into host
+  // signal words.  Programs then run on the host-driven executor (instruction streams on host threads, bytes on the GPU).
+  // resident executor state
+  ResidentQueue* rq_host_ = nullptr;      // pinned host memory
+  ResidentQueue* rq_dev_ = nullptr;       // the same memory as the device sees it
+  ResidentCtl* rctl_ = nullptr;
+  void* resident_stream_ = nullptr;
+  int resident_width_ = 0;
+  uint64_t resident_launches_ = 0, resident_ops_ = 0;
+  void launchResidentKernel();            // caller holds mu_
+  bool mixed_hosts_ = false;
+  int cuda_ordinal_ = 0;
+  char* shadow_ = nullptr;
+  std::atomic<uint64_t>* host_signals_ = nullptr;
+  void* shadow_stream_ = nullptr;
+  std::unique_ptr<MemOps> device_mem_ops_;
+  void ensureMixedHostResources();
+  int exeOnCudaHost(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, uint32_t dtype, int width, int lane, uint64_t stream);
   std::map<std::string, Op> ops_;
   uint32_t next_slot_ = 0;
   std::mutex mu_;

@@ -72,13 +72,27 @@ void runStream(const std::vector<Instr>& prog, int stream, const CpuExecContext&
         if (!s || !d) { sh.fail(ST_BOUNDS, stream, static_cast<int>(pc)); return; }
         if (src_tcp || (dst_tcp && in.op == OP_REDUCE)) { sh.fail(ST_UNSUPPORTED, stream, static_cast<int>(pc)); return; }
         if (dst_tcp) {
-          if (!ctx.tcp || !ctx.tcp->put(in.dst_rank, ctx.tcp_scratch_key, ctx.tcp_scratch_off + in.dst_off, s, in.bytes)) {
+          // the transport reads host memory: device bytes are staged in pieces
+          bool ok = ctx.tcp != nullptr;
+          const uint64_t piece = ctx.mem ? (4ull << 20) : in.bytes;
+          for (uint64_t o = 0; ok && o < in.bytes; o += piece) {
+            const uint64_t n = in.bytes - o < piece ? in.bytes - o : piece;
+            const void* h = ctx.mem ? ctx.mem->toHost(s + o, n) : s + o;
+            ok = h && ctx.tcp->put(in.dst_rank, ctx.tcp_scratch_key, ctx.tcp_scratch_off + in.dst_off + o, h, n);
+          }
+          if (!ok) {
             sh.fail(ST_PEER_GONE, stream, static_cast<int>(pc));
             return;
           }
         } else if (in.op == OP_COPY) {
-          if (s != d) std::memmove(d, s, in.bytes);
-        } else if (!reduceInto(d, s, in.bytes, ctx.dtype, ctx.redop)) {
+          if (s != d) {
+            if (ctx.mem) {
+              if (!ctx.mem->copy(d, s, in.bytes)) { sh.fail(ST_UNSUPPORTED, stream, static_cast<int>(pc)); return; }
+            } else {
+              std::memmove(d, s, in.bytes);
+            }
+          }
+        } else if (ctx.mem ? !ctx.mem->reduce(d, s, in.bytes, ctx.dtype, ctx.redop) : !reduceInto(d, s, in.bytes, ctx.dtype, ctx.redop)) {
           sh.fail(ST_UNSUPPORTED, stream, static_cast<int>(pc));
           return;
         }

@@ -17,6 +17,17 @@
 
 namespace pccl {
 
+// How the executor touches the buffers of a launch.  Null means plain host memory (memmove, host reduce).  A CUDA
+// engine whose peers are partly on other hosts runs its programs with this executor too -- the instruction streams
+// walk on host threads, the bytes stay on the device -- and supplies copies and reductions that act on device memory.
+struct MemOps {
+  virtual ~MemOps() = default;
+  virtual bool copy(void* dst, const void* src, uint64_t bytes) = 0;
+  virtual bool reduce(void* dst, const void* src, uint64_t bytes, uint32_t dtype, uint32_t redop) = 0;
+  // host-readable copy of `bytes` at `src`, valid until the calling thread's next call
+  virtual const void* toHost(const void* src, uint64_t bytes) = 0;
+};
+
 struct CpuExecContext {
   int rank = 0, world = 1;
   char* local[BUF_COUNT] = {nullptr, nullptr, nullptr};   // input, output, scratch (this launch's lane)
@@ -39,6 +50,7 @@ struct CpuExecContext {
   // Testing aid (PCCL_EXEC_DELAY_US with PCCL_EXEC_DELAY_RANK): sleep this long before every instruction, which
   // makes one rank lag behind the others deterministically.
   int delay_us = 0;
+  MemOps* mem = nullptr;
 };
 
 struct TraceEvent {

@@ -13,6 +13,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstdint>
 
 #include "../base/instr.h"
@@ -79,6 +80,44 @@ struct InterpLaunch {
 
 // grid = (max n_streams, nvirt); cooperative launch.  Returns a cudaError_t as int.
 int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream);
+// ---- resident interpreter: launches queued by the host, taken by a kernel that stays on the GPU ----------------------
+struct alignas(16) ResidentDesc { // what InterpLaunch carries, for this rank only; copied with 16-byte vector loads
+  World w;
+  InterpRank r;
+  uint64_t epoch;
+  uint64_t spin_limit;
+  uint64_t launch_no;
+  uint32_t slot_base;
+  uint32_t dtype, redop;
+  int bounds_check;
+  uint32_t turn_slot, finish_slot;
+  uint64_t pad;
+};
+static_assert(sizeof(ResidentDesc) % 16 == 0, "ResidentDesc is copied in 16-byte vectors");
+constexpr uint32_t kResidentSlots = 64;
+constexpr int kResidentChannels = 4;        // the resident grid holds width x this many CTAs (streams = channels x width)
+struct ResidentQueue {           // pinned, mapped host memory: written by the host, polled by the kernel
+  volatile uint64_t tail;        // host: descriptors published so far
+  volatile uint64_t completed;   // device: descriptors finished so far
+  volatile uint32_t stop;        // host: leave now
+  volatile uint32_t running;     // host sets 1 before a launch, the kernel clears it when it leaves
+  uint64_t idle_ns;              // leave after this long without work
+  uint64_t pad[4];               // the descriptors start on a 16-byte boundary (offset 64)
+  ResidentDesc slots[kResidentSlots];
+};
+static_assert(offsetof(ResidentQueue, slots) % 16 == 0, "queued descriptors are read with 16-byte vector loads");
+struct ResidentCtl {             // device memory: CTA 0's decision and the descriptor for the other CTAs
+  uint32_t run;
+  uint32_t pad[3];
+  ResidentDesc desc;
+};
+static_assert(offsetof(ResidentCtl, desc) % 16 == 0, "the descriptor copy is written with 16-byte vector stores");
+// Cooperative launch of `ctas` CTAs that serve the queue from descriptor `head` on.
+int launchResident(ResidentQueue* queue_device_view, ResidentCtl* ctl, uint64_t head, int ctas, int threads, cudaStream_t stream);
+
+// dst = dst (redop) src over `bytes` of device memory: the REDUCE instruction as a kernel of its own, for the
+// host-driven executor of engines whose peers are partly reached over the network.
+int launchDeviceReduce(void* dst, const void* src, uint64_t bytes, uint32_t dtype, uint32_t redop, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // K1-K4, K10: hand-written collectives over the symmetric heap (offsets are heap-relative)

@@ -197,9 +197,10 @@ __device__ __forceinline__ void mm_st_range(char* mc_dst, const char* src, uint6
   for (; i < nvec; i += nt) multimem_st(mc_dst + (i << 4), ld16(src + (i << 4)));
 }
 
-__global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ InterpLaunch L) {
-  const InterpRank& R = L.r[blockIdx.y];
-  const int stream = blockIdx.x;
+// One CTA runs stream `stream` of rank R.  LaunchT is InterpLaunch (a kernel argument) or ResidentDesc (a queued launch
+// read from memory): both carry the world table and the per-launch scalars under the same names.
+template <class LaunchT>
+__device__ __forceinline__ void interp_body(const LaunchT& L, const InterpRank& R, const int stream) {
   const bool turns = L.turn_slot != kNoTurnSlot;
   // a rank without instructions still takes its turn on the lane (one CTA that only runs the hand-shake)
   const int n_workers = turns && R.n_streams == 0 ? 1 : R.n_streams;
@@ -421,6 +422,84 @@ __global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ Int
   }
 }
 
+__global__ void __launch_bounds__(512) interp_kernel(const __grid_constant__ InterpLaunch L) {
+  interp_body(L, L.r[blockIdx.y], static_cast<int>(blockIdx.x));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Resident form: the kernel stays on the GPU and takes launches from a queue that the host fills, so that a collective
+// costs a 300-byte write to pinned memory instead of a kernel launch.  This is the device half of the reference's
+// mirrored ring buffer between executors (include/base/operator.h:7-17: producer_buffer_, consumer_buffer_, head_,
+// tail_) and of its completed_operator / total_operator counters (operator.h:31-38).  CTA 0 polls the queue's tail
+// (host memory, read over PCIe), copies the next descriptor into device memory, the grid synchronises, every CTA runs
+// its stream of the program, the grid synchronises again and CTA 0 publishes the completion count.  The kernel leaves by
+// itself when the host says stop or when nothing has arrived for `idle_ns` (the host then launches it again on the next
+// submission), so it can never spin without bound.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t ld_volatile_u64(const volatile uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(512) resident_kernel(ResidentQueue* q, ResidentCtl* ctl, uint64_t head) {
+  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+  for (;;) {
+    if (blockIdx.x == 0 && threadIdx.x < 32) {
+      uint32_t run = 1;
+      if (threadIdx.x == 0) {
+        const uint64_t t0 = global_timer_ns();
+        while (ld_volatile_u64(&q->tail) <= head) {
+          if (ld_volatile_u32(const_cast<const uint32_t*>(&q->stop)) != 0 || global_timer_ns() - t0 > q->idle_ns) { run = 0; break; }
+          __nanosleep(100);
+        }
+      }
+      run = __shfl_sync(0xffffffffu, run, 0);
+      if (run) {
+        // the descriptor crosses PCIe once, 16 bytes per lane, all loads in flight together
+        const Vec16* src = reinterpret_cast<const Vec16*>(&q->slots[head % kResidentSlots]);
+        Vec16* dst = reinterpret_cast<Vec16*>(&ctl->desc);
+        for (uint32_t i = threadIdx.x; i < sizeof(ResidentDesc) / 16; i += 32) dst[i] = ld16(reinterpret_cast<const char*>(src + i));
+      }
+      __syncwarp();
+      if (threadIdx.x == 0) {
+        ctl->run = run;
+        __threadfence();
+      }
+    }
+    grid.sync();
+    if (*const_cast<volatile uint32_t*>(&ctl->run) == 0) break;
+    interp_body(ctl->desc, ctl->desc.r, static_cast<int>(blockIdx.x));
+    grid.sync();
+    ++head;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      __threadfence_system();
+      asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(&q->completed), "l"(head) : "memory");
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(&q->running), "r"(0u) : "memory");
+  }
+}
+
+__global__ void __launch_bounds__(512) device_reduce_kernel(char* dst, const char* src, uint64_t bytes, uint32_t dtype, uint32_t redop,
+                                                            uint32_t* bad) {
+  // each CTA takes a 16-byte aligned slice
+  const uint64_t per = ((bytes + gridDim.x - 1) / gridDim.x + 15) & ~15ull;
+  const uint64_t lo = per * blockIdx.x;
+  if (lo >= bytes) return;
+  const uint64_t n = bytes - lo < per ? bytes - lo : per;
+  bool ok = false;
+  switch (redop) {
+    case RED_SUM: ok = reduce_dispatch<RED_SUM>(dtype, dst + lo, src + lo, n); break;
+    case RED_MAX: ok = reduce_dispatch<RED_MAX>(dtype, dst + lo, src + lo, n); break;
+    case RED_MIN: ok = reduce_dispatch<RED_MIN>(dtype, dst + lo, src + lo, n); break;
+    case RED_PROD: ok = reduce_dispatch<RED_PROD>(dtype, dst + lo, src + lo, n); break;
+  }
+  if (!ok && threadIdx.x == 0) *bad = 1;
+}
+
 __global__ void wait_timeout_probe_kernel(uint64_t* flag, uint64_t spin_limit, uint32_t* status) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     if (!wait_ge(flag, 1, spin_limit, nullptr)) report(status, ST_TIMEOUT, 0, 0, OP_WAIT);
@@ -439,6 +518,27 @@ int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream) {
   // Streams wait on one another, so every CTA must be resident: a cooperative launch refuses
   // (instead of hanging) when the grid does not fit.
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(interp_kernel), grid, block, args, 0, stream));
+}
+
+int launchResident(ResidentQueue* queue_device_view, ResidentCtl* ctl, uint64_t head, int ctas, int threads, cudaStream_t stream) {
+  void* args[] = {&queue_device_view, &ctl, &head};
+  return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(resident_kernel), dim3(ctas), dim3(threads), args, 0, stream));
+}
+
+int launchDeviceReduce(void* dst, const void* src, uint64_t bytes, uint32_t dtype, uint32_t redop, cudaStream_t stream) {
+  if (bytes == 0) return 0;
+  static uint32_t* bad = nullptr;                   // sticky "unsupported dtype / op" word, checked by the caller's status read
+  if (!bad) {
+    cudaError_t e = cudaMalloc(&bad, sizeof(uint32_t));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaMemset(bad, 0, sizeof(uint32_t));
+  }
+  const uint32_t es = dtypeSize(dtype);
+  if (bytes % es) return static_cast<int>(cudaErrorInvalidValue);
+  int blocks = static_cast<int>((bytes + (256u << 10) - 1) / (256u << 10));
+  if (blocks > 64) blocks = 64;
+  device_reduce_kernel<<<blocks, 512, 0, stream>>>(static_cast<char*>(dst), static_cast<const char*>(src), bytes, dtype, redop, bad);
+  return static_cast<int>(cudaGetLastError());
 }
 
 int launchWaitTimeoutProbe(uint64_t* flag, uint64_t spin_limit, uint32_t* status, cudaStream_t stream) {

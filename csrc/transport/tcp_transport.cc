@@ -165,8 +165,10 @@ void TcpTransport::readerLoop(int fd) {
         sink.resize(n);
         dst = sink.data();
       }
+      const bool real = dst != sink.data() || n == 0;
       if (n && !wire::recvAll(fd, dst, n)) break;
       bytes_recv_.fetch_add(n);
+      if (real && n && put_hook_) put_hook_(ph.key, ph.off, n);
     } else if (h.kind == kSignal && h.length == sizeof(SigHead)) {
       SigHead sh;
       if (!wire::recvAll(fd, &sh, sizeof(sh))) break;

@@ -9,6 +9,7 @@
 // without InfiniBand and by CPU ranks when PCCL_TRANSPORT=tcp.
 #pragma once
 #include <atomic>
+#include <functional>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -32,6 +33,10 @@ class TcpTransport : public RemoteCommunicatorBase {
   void disconnect(int peer) override;
 
   void setSignals(std::atomic<uint64_t>* signals, uint32_t count) { signals_ = signals; num_signals_ = count; }
+  // Called by the receiver thread after the bytes of a PUT have landed in the registered buffer and before the next
+  // frame of that connection is read -- so before the SIGNAL that follows the PUT takes effect.  A CUDA engine uses it
+  // to move the bytes from its host shadow of the workspace on to the device.
+  void setPutHook(std::function<void(uint32_t key, uint64_t off, uint64_t bytes)> hook) { put_hook_ = std::move(hook); }
   bool put(int peer, uint32_t remote_key, uint64_t remote_off, const void* src, uint64_t bytes) override;
   bool signal(int peer, uint32_t slot, uint64_t add) override;
   void shutdown();
@@ -56,6 +61,7 @@ class TcpTransport : public RemoteCommunicatorBase {
   std::map<int, std::string> endpoints_;
   std::map<int, std::shared_ptr<Conn>> conns_;
   std::vector<Region> regions_;
+  std::function<void(uint32_t, uint64_t, uint64_t)> put_hook_;
   std::atomic<uint64_t>* signals_ = nullptr;
   uint32_t num_signals_ = 0;
   std::atomic<uint64_t> bytes_sent_{0}, bytes_recv_{0};

@@ -146,6 +146,35 @@ class Engine:
                 raise exc(f"exeOp('{name}') finished with status {STATUS_NAMES.get(st, st)}")
         return st
 
+    # -- resident executor: one kernel that stays on the GPU and takes launches from a queue -----------------------
+    def start_resident(self, width: int = 4) -> None:
+        """Launch the resident interpreter kernel with ``width`` CTAs per channel.  From then on ``enqueue`` hands it a
+        registered program without a kernel launch (a descriptor written to pinned memory); ``wait`` blocks until a
+        ticket is done.  The kernel leaves by itself after ``PCCL_RESIDENT_IDLE_MS`` without work and comes back with
+        the next ``enqueue``."""
+        self._e.startResident(int(width))
+
+    def enqueue(self, name: str, input: torch.Tensor, output: Optional[torch.Tensor] = None, *, lane: int = 0,
+                stream: Optional["torch.cuda.Stream"] = None, sync_inputs: bool = True) -> int:
+        """Queue one run of program ``name`` for the resident kernel; returns its ticket.  With ``sync_inputs`` the
+        producing stream (default: the current one) is synchronised first, because the resident kernel is not ordered
+        behind any stream.  Keep the tensors alive until ``wait(ticket)`` has returned."""
+        if not input.is_cuda or not input.is_contiguous() or (output is not None and not output.is_contiguous()):
+            raise PcclError("enqueue needs contiguous CUDA tensors")
+        out = input if output is None else output
+        sh = (stream or torch.cuda.current_stream()).cuda_stream if sync_inputs else 0
+        if sync_inputs and sh == 0:
+            torch.cuda.current_stream().synchronize()
+        return self._e.enqueueOp(name, input.data_ptr(), out.data_ptr(), input.numel() * input.element_size(),
+                                 dtype_name(input.dtype), int(lane), int(sh))
+
+    def wait(self, ticket: int, timeout_ms: int = 0) -> None:
+        if not self._e.waitOp(int(ticket), int(timeout_ms)):
+            raise PcclTimeout(f"resident executor: ticket {ticket} did not finish in time")
+
+    def stop_resident(self) -> None:
+        self._e.stopResident()
+
     def exportEndpoint(self) -> str:
         return self._e.exportEndpoint()
 
@@ -168,7 +197,7 @@ class Engine:
             # PCCL_NVLS=0 or PCCL_TRANSPORT=p2p keep the heap off the multicast object: every kernel then takes its
             # peer-to-peer form
             nvls = os.environ.get("PCCL_NVLS", "1") != "0" and os.environ.get("PCCL_TRANSPORT", "") != "p2p"
-        if self.device == "cuda" and nvls and self.world > 1:
+        if self.device == "cuda" and nvls and self.world > 1 and not self._e.mixedHosts():
             flags = [None] * self.world
             dist.all_gather_object(flags, bool(self._e.multicastSupported()), group=group)
             if all(flags):

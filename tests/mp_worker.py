@@ -440,6 +440,86 @@ def case_moe(eng, rank, world):
     return {"ok": True}
 
 
+def case_mixed_hosts(eng, rank, world):
+    """CUDA ranks that do not share one host (emulated: every rank, or every pair of ranks, claims its own host id).
+    Peers of the same "host" keep their NVLink mapping for data; the others are reached over the host/TCP transport
+    through a pinned host shadow of the workspace; programs run on the host-driven executor.  A second engine is built
+    for this, the worker's own engine is not touched."""
+    from pccl_b200.engine import Engine, LaunchEnvironments
+    from pccl_b200.lang import build
+    per_host = 2 if world >= 4 and world % 2 == 0 else 1
+    LaunchEnvironments.setOverride("PCCL_HOST_ID", f"emulated-host-{rank // per_host}")
+    e2 = Engine(rank, world)
+    try:
+        e2.initEngine("cuda", heap_bytes=512 << 20)
+        e2.connect(nvls=False)
+    finally:
+        LaunchEnvironments.setOverride("PCCL_HOST_ID", "")
+    st = e2.stats()
+    assert st["mixed_hosts"] and not st["multicast"], st
+    n = 96 * 1024
+    g = torch.Generator(device="cuda").manual_seed(21)
+    xs = [torch.randn(n, generator=g, device="cuda") for _ in range(world)]
+    info = {}
+    e2.regOp("ring", build("ring_allreduce", world, channels=2))
+    e2.regOp("hier", build("hierarchical_allreduce", world, channels=1, per_host=per_host))
+    e2.regOp("ag", build("direct_allgather", world, channels=1))
+    for it in range(3):
+        for name in ("ring", "hier"):
+            y = torch.full((n,), -1.0, device="cuda")
+            stc = e2.exeOp(name, xs[rank] + it, y, width=2)
+            assert stc == 0, (name, stc)
+            ref = torch.stack(xs).sum(0) + it * world
+            assert torch.allclose(y, ref, rtol=1e-5, atol=1e-4), f"{name} launch {it}: {(y - ref).abs().max().item()}"
+        out = torch.zeros(world * 4096, device="cuda")
+        assert e2.exeOp("ag", xs[rank][:4096].contiguous() + it, out) == 0
+        assert torch.equal(out, torch.cat([x[:4096] + it for x in xs])), "allgather"
+    st = e2.stats()
+    info["tcp_bytes_sent"] = st.get("tcp_bytes_sent", 0)
+    assert info["tcp_bytes_sent"] > n * 4 // world
+    # kernels that address every peer directly are refused on such a world instead of dereferencing an unmapped peer
+    from pccl_b200.ops import collectives as C
+    t = e2.symmetric_tensor((1024,), torch.float32)
+    try:
+        C.all_reduce(e2, t)
+        raise AssertionError("a direct kernel ran on a world that spans hosts")
+    except RuntimeError as ex:
+        assert "span several hosts" in str(ex)
+    torch.cuda.synchronize(); dist.barrier()
+    del e2
+    return info
+
+
+def case_resident(eng, rank, world):
+    """The resident interpreter kernel on every rank: a run of all-reduces and all-gathers queued without a kernel
+    launch each; the ranks' kernels wait on one another through the usual signal words (each on its own GPU)."""
+    from pccl_b200.lang import build
+    eng.regOp("res_ar", build("direct_allreduce", world, channels=2))
+    eng.regOp("res_ag", build("direct_allgather", world, channels=1))
+    n = 256 * 1024
+    xs = [torch.full((n,), float(rank + 1) * (i + 1), device="cuda") for i in range(12)]
+    ys = [torch.zeros(n, device="cuda") for _ in range(12)]
+    gs = [torch.zeros(world * 1024, device="cuda") for _ in range(12)]
+    torch.cuda.synchronize(); dist.barrier()
+    eng.start_resident(width=4)
+    tickets = []
+    for i in range(12):
+        tickets.append(eng.enqueue("res_ar", xs[i], ys[i], sync_inputs=False))
+        tickets.append(eng.enqueue("res_ag", xs[i][:1024], gs[i], sync_inputs=False))
+    eng.wait(tickets[-1], timeout_ms=30000)
+    st = eng.check_status(0)
+    assert st[0] == 0, list(st)
+    for i in range(12):
+        want = sum(float(r + 1) * (i + 1) for r in range(world))
+        assert torch.all(ys[i] == want), f"all-reduce {i}"
+        ref = torch.cat([torch.full((1024,), float(r + 1) * (i + 1), device="cuda") for r in range(world)])
+        assert torch.equal(gs[i], ref), f"all-gather {i}"
+    stats = eng.stats()
+    dist.barrier()
+    eng.stop_resident()
+    return {"resident_kernel_launches": stats["resident_kernel_launches"], "resident_ops": stats["resident_ops"]}
+
+
 def case_overlap(eng, rank, world):
     """Two collectives at once on two CUDA streams with disjoint CTA budgets and separate flag lanes (an all-reduce on
     lane 0, an all-gather on lane 1), against the same two back to back on one stream.  Checks both results and

@@ -600,3 +600,44 @@ def test_engine_regop_exeop_on_a_cuda_engine_with_alternating_widths(native, alg
         eng.exeOp("op", z, width=2, check=True)
         assert torch.equal(z, torch.arange(n, device="cuda", dtype=torch.float32))
     del eng
+
+
+def test_resident_executor_takes_queued_launches_without_a_kernel_launch_each(native):
+    """startResident -> enqueue x N -> wait: the interpreter kernel stays on the GPU and takes its work from a queue in
+    pinned host memory (a world of one keeps every wait inside the one kernel).  It leaves by itself when idle and is
+    started again by the next submission."""
+    import time
+    from pccl_b200.engine import Engine
+    from pccl_b200.lang import build
+    eng = Engine(0, 1)
+    eng.initEngine("cuda", heap_bytes=512 << 20)
+    eng.regOp("ar", build("ring_allreduce", 1, channels=2))
+    eng.regOp("ag", build("direct_allgather", 1, channels=1))
+    eng.start_resident(width=2)
+    n = 64 * 1024
+    xs = [torch.arange(n, device="cuda", dtype=torch.float32) + i for i in range(24)]
+    ys = [torch.full((n,), -1.0, device="cuda") for _ in range(24)]
+    torch.cuda.current_stream().synchronize()
+    t0 = time.perf_counter()
+    tickets = [eng.enqueue("ar" if i % 3 else "ag", xs[i], ys[i], sync_inputs=False) for i in range(24)]
+    eng.wait(tickets[-1], timeout_ms=20000)
+    per_op_us = (time.perf_counter() - t0) / 24 * 1e6
+    for i in range(24):
+        assert torch.equal(ys[i], xs[i]), i
+    st = eng.stats()
+    assert st["resident_ops"] == 24 and st["resident_kernel_launches"] >= 1
+    first_launches = st["resident_kernel_launches"]
+    assert first_launches <= 3, st            # not one launch per operation
+    assert eng.check_status(0)[0] == 0
+    # idle: the kernel leaves (a device-wide synchronize returns), the next submission brings it back
+    time.sleep(0.1)
+    torch.cuda.synchronize()
+    y = torch.zeros(n, device="cuda")
+    eng.wait(eng.enqueue("ar", xs[3], y), timeout_ms=20000)
+    assert torch.equal(y, xs[3])
+    assert eng.stats()["resident_kernel_launches"] > first_launches
+    eng.stop_resident()
+    eng.exeOp("ar", xs[5], y, check=True)          # the launch-per-call path still works afterwards
+    assert torch.equal(y, xs[5])
+    print(f"resident executor: {per_op_us:.1f} us per queued operation (host clock, 24 operations)")
+    del eng
