@@ -68,8 +68,9 @@ void bindFused(py::module_& m) {
       a.out[r] = out.empty() ? nullptr : reinterpret_cast<void*>(out.at(r));
       a.status[r] = reinterpret_cast<uint32_t*>(status.at(r));
     }
-    int err = kind == "dispatch" ? launchMoeDispatch(a, blocks, reinterpret_cast<cudaStream_t>(stream))
-                                 : launchMoeCombine(a, blocks, reinterpret_cast<cudaStream_t>(stream));
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int err = kind == "dispatch" ? launchMoeDispatch(a, blocks, st)
+              : kind == "combine_dot" ? launchMoeCombineDot(a, blocks, st) : launchMoeCombine(a, blocks, st);
     check(err, kind.c_str());
   }, py::arg("kind"), py::arg("engine").none(true), py::arg("heaps"), py::arg("flag_off"), py::arg("tokens"), py::arg("hidden"),
      py::arg("topk"), py::arg("experts_per_rank"), py::arg("recv_q_off"), py::arg("recv_s_off"), py::arg("y_off"), py::arg("epoch"),

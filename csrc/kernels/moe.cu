@@ -104,9 +104,12 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const __grid_constant
       char* dq = base + A.recv_q_off + row * H;
       char* ds = base + A.recv_s_off + row * G * 4;
       for (int v = threadIdx.x; v < qvec; v += blockDim.x) st16(dq + v * 16, *reinterpret_cast<const Vec16*>(q + v * 16));
+      // With gate weights attached, destination k receives p[t,k] * x[t] (the gradient of an expert's output row in
+      // the backward pass): the e4m3 payload is the same for every destination, only the block scales are multiplied.
+      const float pk = A.probs[slot] ? A.probs[slot][t * A.topk + k] : 1.0f;
       if (threadIdx.x < svec) {
-        if ((G & 3) == 0) st16(ds + threadIdx.x * 16, *reinterpret_cast<const Vec16*>(reinterpret_cast<uint8_t*>(s) + threadIdx.x * 16));
-        else for (int i = threadIdx.x * 4; i < min(G, threadIdx.x * 4 + 4); ++i) reinterpret_cast<float*>(ds)[i] = s[i];
+        if ((G & 3) == 0 && !A.probs[slot]) st16(ds + threadIdx.x * 16, *reinterpret_cast<const Vec16*>(reinterpret_cast<uint8_t*>(s) + threadIdx.x * 16));
+        else for (int i = threadIdx.x * 4; i < min(G, threadIdx.x * 4 + 4); ++i) reinterpret_cast<float*>(ds)[i] = s[i] * pk;
       }
     }
   }
@@ -164,6 +167,67 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __grid_constant_
       }
       st16(out + static_cast<long long>(t) * H + v0 * 8, pack<DT_BF16>(acc0));
       if (v1 < nvec) st16(out + static_cast<long long>(t) * H + v1 * 8, pack<DT_BF16>(acc1));
+    }
+  }
+  moe_barrier(A, me, 4 * A.epoch + 2, &s_fail);
+}
+
+// dot[t,k] = <g[t], y[rank of expert (t,k)][dst_rows[t,k]]>: the gradient of the gate weight of an assignment, which is
+// the upstream gradient of the token times the expert's output row.  The rows are pulled like in the combine.
+__global__ void __launch_bounds__(256) moe_combine_dot_kernel(const __grid_constant__ MoeArgs A) {
+  __shared__ uint32_t s_fail;
+  __shared__ float part[8][8];
+  if (threadIdx.x == 0) s_fail = 0;
+  const int me = A.nvirt > 1 ? static_cast<int>(blockIdx.y) : A.rank;
+  const int slot = A.nvirt > 1 ? me : 0;
+  const int H = A.hidden, nvec = H >> 3;
+  if (!moe_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
+  const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(A.x[slot]);
+  float* dot = static_cast<float*>(A.out[slot]);
+  for (int t = blockIdx.x; t < A.tokens; t += gridDim.x) {
+    const char* src[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      src[k] = nullptr;
+      if (k < A.topk) {
+        const int e = A.expert_ids[slot][t * A.topk + k];
+        const long long row = A.dst_rows[slot][t * A.topk + k];
+        if (e >= 0 && row >= 0) src[k] = A.w.heap[e / A.experts_per_rank] + A.y_off + row * H * 2;
+      }
+    }
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      Vec16 a[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (src[k]) a[k] = ld16(src[k] + v * 16);
+      float gf[8];
+      unpack<DT_BF16>(ld16(g + static_cast<long long>(t) * H + v * 8), gf);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (src[k]) {
+          float f[8];
+          unpack<DT_BF16>(a[k], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[k] += gf[j] * f[j];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], o);
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) part[threadIdx.x >> 5][k] = acc[k];
+    }
+    __syncthreads();
+    if (threadIdx.x < static_cast<uint32_t>(A.topk)) {
+      float sum = 0.f;
+      for (int w = 0; w < 8; ++w) sum += part[w][threadIdx.x];
+      dot[t * A.topk + threadIdx.x] = sum;
     }
   }
   moe_barrier(A, me, 4 * A.epoch + 2, &s_fail);
@@ -416,6 +480,7 @@ int launchMoeDispatch(const MoeArgs& a, int blocks, cudaStream_t stream) {
 }
 
 int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream) { return coop(moe_combine_kernel, a, blocks, 0, stream); }
+int launchMoeCombineDot(const MoeArgs& a, int blocks, cudaStream_t stream) { return coop(moe_combine_dot_kernel, a, blocks, 0, stream); }
 
 int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, cudaStream_t stream) {
   if (hidden % 128) return static_cast<int>(cudaErrorInvalidValue);

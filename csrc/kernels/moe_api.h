@@ -32,8 +32,11 @@ struct MoeArgs {
   uint32_t* status[kMaxRanks];
 };
 
-// fp8 (e4m3, one fp32 scale per 128 values) quantisation fused with the push to the experts' ranks.
+// fp8 (e4m3, one fp32 scale per 128 values) quantisation fused with the push to the experts' ranks.  With `probs` set,
+// destination k of token t receives probs[t,k] * x[t] (the backward pass sends gate-weighted output gradients this way).
 int launchMoeDispatch(const MoeArgs& a, int blocks, cudaStream_t stream);
+// out (fp32 [tokens, topk]) = <x[t], y[rank of expert (t,k)][dst_rows[t,k]]>: gradients of the gate weights.
+int launchMoeCombineDot(const MoeArgs& a, int blocks, cudaStream_t stream);
 // out[t] = sum_k probs[t,k] * y[rank of expert (t,k)][dst_rows[t,k]]: pulls the rows over NVLink.
 int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream);
 // bf16 rows from fp8 rows + scales, for rows [0, *n_rows) (device count).

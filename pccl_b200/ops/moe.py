@@ -137,8 +137,27 @@ class MoEExchange:
                        [st.data_ptr()], self.blocks, 0, torch.cuda.current_stream().cuda_stream)
         count_launch()
 
-    def dispatch(self, x: torch.Tensor, ids: torch.Tensor, plan: Dict[str, torch.Tensor]) -> None:
-        self._exchange("dispatch", x, ids, plan["rows"], None, None)
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor, plan: Dict[str, torch.Tensor], probs: Optional[torch.Tensor] = None) -> None:
+        """Rows of ``x`` go to the ranks of their experts (e4m3 + block scales).  With ``probs`` destination k of token t
+        receives ``probs[t, k] * x[t]`` (how the backward pass sends gate-weighted output gradients)."""
+        self._exchange("dispatch", x, ids, plan["rows"], probs, None)
+
+    def received(self, plan: Dict[str, torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The rows that the last dispatch delivered to this rank, as bf16 [cap, hidden] (rows past the plan's count are
+        not written)."""
+        if out is None:
+            out = torch.empty((self.cap, self.H), dtype=torch.bfloat16, device="cuda")
+        C.moe_dequant(self.recv_q.data_ptr(), self.recv_s.data_ptr(), out.data_ptr(), plan["n_rows"].data_ptr(), self.cap,
+                      self.H, torch.cuda.current_stream().cuda_stream)
+        count_launch()
+        return out
+
+    def combine_dot(self, g: torch.Tensor, ids: torch.Tensor, plan: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """``dot[t, k] = <g[t], y row of assignment (t, k)>`` (fp32 [tokens, topk]): with ``g`` the upstream gradient and
+        the expert outputs of the forward pass still in ``self.y``, the gradient of the gate weights."""
+        out = torch.zeros((self.T, self.K), dtype=torch.float32, device="cuda")
+        self._exchange("combine_dot", g, ids, plan["rows"], None, out)
+        return out
 
     def experts(self, w1: torch.Tensor, w2: torch.Tensor, plan: Dict[str, torch.Tensor]) -> None:
         """w1: [experts_per_rank * d_ff, hidden], w2: [experts_per_rank * hidden, d_ff]; result in self.y."""

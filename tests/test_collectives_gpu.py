@@ -641,3 +641,50 @@ def test_resident_executor_takes_queued_launches_without_a_kernel_launch_each(na
     assert torch.equal(y, xs[5])
     print(f"resident executor: {per_op_us:.1f} us per queued operation (host clock, 24 operations)")
     del eng
+
+
+def test_moe_layer_backward_matches_dense_reference(native):
+    """The expert-parallel layer as an autograd node (world of one): gradients of the input, the gate logits and both
+    expert weights against a dense fp32 reference that sees the same e4m3 round trips as the kernels."""
+    from pccl_b200.engine import Engine
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.moe import MoEExchange
+    from pccl_b200.parallel.ep import _MoEFn
+    torch.manual_seed(16)
+    T, H, Fd, E, Kt = 256, 512, 256, 8, 2
+    eng = Engine(0, 1)
+    eng.initEngine("cuda", heap_bytes=512 << 20)
+    moe = MoEExchange(eng, T, H, E, Kt)
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True)
+    logits = torch.randn(T, E, device="cuda").requires_grad_(True)
+    w1 = (torch.randn(E * Fd, H, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(E * H, Fd, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    g = (torch.randn(T, H, device="cuda") * 0.1).bfloat16()
+    out = _MoEFn.apply(x, logits, w1, w2, moe)
+    out.backward(g)
+    check_status("moe backward")
+
+    def e4m3_round_trip(t):      # what a row looks like after the dispatch (1 x 128 blocks)
+        q = t.view(t.shape[0], -1, 128)
+        sc = (q.abs().amax(-1, keepdim=True) / 448.0).clamp_min(1e-30)
+        return ((q / sc).to(torch.float8_e4m3fn).float() * sc).view_as(t)
+
+    xr = x.detach().float().requires_grad_(True)
+    lr = logits.detach().float().requires_grad_(True)
+    w1r, w2r = w1.detach().float().requires_grad_(True), w2.detach().float().requires_grad_(True)
+    pf = torch.softmax(lr, -1)
+    p, ids = pf.topk(Kt, -1)
+    xs = xr + (e4m3_round_trip(xr.detach()) - xr.detach())            # straight-through: forward sees the quantised rows
+    ref = torch.zeros(T, H, device="cuda")
+    for e in range(E):
+        y = torch.nn.functional.gelu(xs @ w1r[e * Fd:(e + 1) * Fd].t(), approximate="tanh") @ w2r[e * H:(e + 1) * H].t()
+        for k in range(Kt):
+            m = (ids[:, k] == e).float()[:, None]
+            ref = ref + m * p[:, k, None] * y
+    ref.backward(g.float())
+    assert (out.float() - ref.detach()).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+    for got, want, name, tol in ((x.grad, xr.grad, "dx", 0.08), (logits.grad, lr.grad, "dlogits", 0.08), (w1.grad, w1r.grad, "dw1", 0.08),
+                                 (w2.grad, w2r.grad, "dw2", 0.08)):
+        err = (got.float() - want).abs().max().item()
+        assert err <= tol * max(1e-6, want.abs().max().item()), (name, err, want.abs().max().item())
+    del moe, eng
