@@ -6,6 +6,9 @@
     python -m pccl_b200.profile_targets gemm_rs   [--world 2 --rows 1024 --k 3584 --n 8192]
     python -m pccl_b200.profile_targets allreduce [--world 4 --mbytes 64]
     python -m pccl_b200.profile_targets moe       [--world 2 --tokens 2048 --hidden 7168]
+    python -m pccl_b200.profile_targets train_kernels   (GEMM with the GELU-backward epilogue, LayerNorm backward with
+                                                         the residual and bias-gradient extras, column sums; GPT-1.3B shapes)
+    python -m pccl_b200.profile_targets grouped_gemm [--tokens 8192 --hidden 7168]   (expert FFN, 32 experts)
 
 Each prints device times (CUDA events) of its launches and raises if a kernel reported a status.
 """
@@ -156,9 +159,49 @@ def moe(a):
     _check(st)
 
 
+def train_kernels(a):
+    """The fused kernels of the training step at the GPT-1.3B shapes (16384 tokens, d = 2048, d_ff = 8192)."""
+    from .nn.norm import _ln_backward, _ln_forward
+    from .ops.elementwise import colsum
+    from .ops.gemm import gemm, gemm_dgelu
+    T, D, H = 16384, 2048, 8192
+    r = lambda *s: torch.randn(*s, device="cuda").bfloat16()  # noqa: E731
+    dz, w2, pre = r(T, D), r(D, H) * 0.02, r(T, H)
+    out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    sums = torch.zeros(H, device="cuda")
+    print({"op": "gemm_dgelu_colsum", "M": T, "N": H, "K": D, "us": _timed(lambda: gemm_dgelu(dz, w2, pre, b_t=True, colsum=sums, out=out), a.iters)})
+    print({"op": "gemm_plain_same_shape", "us": _timed(lambda: gemm(dz, w2, b_t=True, out=out), a.iters)})
+    x, delta, g = r(T, D), r(T, D), r(T, D)
+    gamma, beta = torch.ones(D, device="cuda", dtype=torch.bfloat16), torch.zeros(D, device="cuda", dtype=torch.bfloat16)
+    s, _, mean, rstd = _ln_forward(x, delta, gamma, beta, 1e-5)
+    print({"op": "ln_fwd_add", "rows": T, "D": D, "us": _timed(lambda: _ln_forward(x, delta, gamma, beta, 1e-5), a.iters)})
+    print({"op": "ln_bwd_add_colsum", "rows": T, "D": D, "us": _timed(lambda: _ln_backward(g, s, gamma, mean, rstd, delta, True), a.iters)})
+    q = r(T, 3 * D)
+    print({"op": "colsum", "rows": T, "N": 3 * D, "us": _timed(lambda: colsum(q), a.iters)})
+    from .ops import check_status
+    check_status("train kernels")
+
+
+def grouped_gemm(a):
+    """Expert FFN of the MoE layer: 32 experts, rows spread unevenly, 7168 -> 2048 (GELU) -> 7168."""
+    from .ops.moe import grouped_gemm as gg
+    E, H, Fd, rows = 32, a.hidden, 2048, a.tokens
+    cuts = torch.sort(torch.randint(0, rows, (E - 1,), device="cuda")).values
+    row_off = torch.cat([torch.zeros(1, device="cuda", dtype=torch.long), cuts, torch.tensor([rows], device="cuda")]).to(torch.int32)
+    x = torch.randn(rows, H, device="cuda").bfloat16()
+    w1 = (torch.randn(E * Fd, H, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(E * H, Fd, device="cuda") * 0.02).bfloat16()
+    h = torch.empty(rows, Fd, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty(rows, H, device="cuda", dtype=torch.bfloat16)
+    print({"op": "grouped_gemm_up_gelu", "rows": rows, "N": Fd, "K": H, "experts": E, "us": _timed(lambda: gg(x, w1, row_off, Fd, out=h, gelu=True), a.iters)})
+    print({"op": "grouped_gemm_down", "rows": rows, "N": H, "K": Fd, "experts": E, "us": _timed(lambda: gg(h, w2, row_off, H, out=y), a.iters)})
+    from .ops import check_status
+    check_status("grouped gemm")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("target", choices=["ag_gemm", "ag_gemm_fp8", "gemm_rs", "allreduce", "moe"])
+    ap.add_argument("target", choices=["ag_gemm", "ag_gemm_fp8", "gemm_rs", "allreduce", "moe", "train_kernels", "grouped_gemm"])
     ap.add_argument("--world", type=int, default=2)
     ap.add_argument("--rows", type=int, default=1024, help="rows per rank")
     ap.add_argument("--k", type=int, default=0)
@@ -173,7 +216,8 @@ def main():
         a.k, a.n = a.k or 8192, a.n or 3584
     if a.target == "gemm_rs":
         a.k, a.n = a.k or 3584, a.n or 8192
-    {"ag_gemm": ag_gemm, "ag_gemm_fp8": ag_gemm_fp8, "gemm_rs": gemm_rs, "allreduce": allreduce, "moe": moe}[a.target](a)
+    {"ag_gemm": ag_gemm, "ag_gemm_fp8": ag_gemm_fp8, "gemm_rs": gemm_rs, "allreduce": allreduce, "moe": moe,
+     "train_kernels": train_kernels, "grouped_gemm": grouped_gemm}[a.target](a)
 
 
 if __name__ == "__main__":
