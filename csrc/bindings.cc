@@ -239,6 +239,28 @@ PYBIND11_MODULE(_C, m) {
       .def("injectFault", &Engine::injectFault)
       .def("nextEpoch", &Engine::nextEpoch)
       .def("mixedHosts", &Engine::mixedHosts)
+      .def("materializedStreams", [](Engine& e, const std::string& name, uint64_t in_bytes, int width) {
+        uint64_t bb[BUF_COUNT] = {0, 0, 0};
+        auto streams = e.materializedStreams(name, in_bytes, width, bb);
+        py::list out;
+        for (auto& s : streams) {
+          py::list one;
+          for (auto& in : s)
+            one.append(py::make_tuple(in.op, in.src_rank, in.dst_rank, in.src_buf, in.dst_buf, in.slot, in.value, in.count, in.src_off,
+                                      in.dst_off, in.bytes));
+          out.append(one);
+        }
+        return py::make_tuple(out, py::make_tuple(bb[0], bb[1], bb[2]));
+      }, py::arg("name"), py::arg("in_bytes"), py::arg("width") = 1)
+      .def("opInfo", &Engine::opInfo)
+      .def("planLaunch", [](Engine& e, const std::string& name, uint64_t in_bytes, int width, int lane) {
+        Engine::LaunchPlan L = e.planLaunch(name, in_bytes, width, lane);
+        py::dict d;
+        d["slot_base"] = L.slot_base; d["turn_slot"] = L.turn_slot; d["finish_slot"] = L.finish_slot; d["epoch"] = L.epoch;
+        d["launch_no"] = L.launch_no; d["scratch_off"] = L.scratch_off; d["spin_limit"] = L.spin_limit; d["status_ptr"] = L.status_ptr;
+        d["signal_off"] = L.signal_off; d["mc_base"] = L.mc_base;
+        return d;
+      }, py::arg("name"), py::arg("in_bytes"), py::arg("width") = 1, py::arg("lane") = 0)
       .def("startResident", &Engine::startResident, py::arg("width") = 4)
       .def("enqueueOp", &Engine::enqueueOp, py::arg("name"), py::arg("in_ptr"), py::arg("out_ptr"), py::arg("in_bytes"), py::arg("dtype"),
            py::arg("lane") = 0, py::arg("stream") = 0, py::call_guard<py::gil_scoped_release>())
@@ -283,6 +305,7 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("sm_count", &deviceSmCount);
   m.attr("MAX_RANKS") = kMaxRanks;
+  m.attr("NO_TURN_SLOT") = kNoTurnSlot;
   m.attr("MAX_BLOCKS_PER_COLL") = kMaxBlocksPerColl;
 
   bindGemm(m);

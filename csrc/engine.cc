@@ -775,6 +775,64 @@ int Engine::exeOnCuda(Op& op, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_byt
   return 0;
 }
 
+// ---- hooks for run-time compiled kernels ----------------------------------------------------------------------------
+std::vector<std::vector<Instr>> Engine::materializedStreams(const std::string& name, uint64_t in_bytes, int width, uint64_t* buf_bytes) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("materializedStreams: no op named '" + name + "'");
+  const Program& p = it->second.program;
+  if (width < 1) width = 1;
+  if (width > max_width_) width = max_width_;
+  Materialized m = p.materialize(rank_, p.blockBytesForInput(in_bytes), width);
+  if (buf_bytes)
+    for (int b = 0; b < static_cast<int>(BUF_COUNT); ++b) buf_bytes[b] = m.buf_bytes[b];
+  return m.streams;
+}
+
+std::map<std::string, std::string> Engine::opInfo(const std::string& name) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("opInfo: no op named '" + name + "'");
+  const Program& p = it->second.program;
+  return {{"name", p.name}, {"collective", p.collective}, {"redop", p.redop}, {"world", std::to_string(p.world)},
+          {"channels", std::to_string(p.channels)}, {"in_place", p.in_place ? "1" : "0"}, {"needs_multicast", p.needs_multicast ? "1" : "0"},
+          {"remote_io", p.remote_io ? "1" : "0"}};
+}
+
+Engine::LaunchPlan Engine::planLaunch(const std::string& name, uint64_t in_bytes, int width, int lane) {
+  if (!initialized_ || device_ != "cuda") throw std::runtime_error("planLaunch: a CUDA engine is needed");
+  if (mixed_hosts_) throw std::runtime_error("planLaunch: the ranks of this world span several hosts");
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = ops_.find(name);
+  if (it == ops_.end()) throw std::runtime_error("planLaunch: no op named '" + name + "'");
+  Op& op = it->second;
+  if (op.program.world != world_) throw std::runtime_error("planLaunch: '" + name + "' was written for another world size");
+  if (lane < 0 || lane >= layout_.lanes) throw std::runtime_error("planLaunch: lane out of range");
+  if (op.program.needs_multicast && !mc_base_) throw std::runtime_error("planLaunch: program needs NVLS multicast, which is not set up");
+  if (width < 1) width = 1;
+  if (width > max_width_) width = max_width_;
+  for (int r = 0; r < world_; ++r)
+    if (r != rank_ && !peer_heaps_[r]) throw std::runtime_error("planLaunch: peers are not connected");
+  Materialized m = op.program.materialize(rank_, op.program.blockBytesForInput(in_bytes), width);
+  uint64_t lane_bytes = layout_.workspace_bytes / layout_.lanes, half = lane_bytes / 2 / 4096 * 4096;
+  if (m.buf_bytes[BUF_SCRATCH] > half) throw std::runtime_error("planLaunch: message needs more scratch than a workspace lane half holds");
+  Op::Variant& var = variantFor(op, width);
+  LaunchPlan L{};
+  L.slot_base = var.slot_base;
+  L.epoch = var.epoch++;
+  L.launch_no = lane_launches_.at(lane)++;
+  L.scratch_off = lane * lane_bytes + (L.launch_no & 1) * half;
+  L.turn_slot = world_ > 1 ? layout_.turn_base + static_cast<uint32_t>(lane) * kMaxRanks : kNoTurnSlot;
+  L.finish_slot = layout_.finish_base + static_cast<uint32_t>(lane);
+  L.spin_limit = spin_limit_;
+  L.status_ptr = statusPtr(lane);
+  L.signal_off = layout_.signal_off;
+  L.mc_base = reinterpret_cast<uint64_t>(mc_base_);
+  op.launches++;
+  op.bytes += m.bytes_moved;
+  return L;
+}
+
 // ---- resident executor ---------------------------------------------------------------------------------------------
 void Engine::startResident(int width) {
   if (!initialized_ || device_ != "cuda") throw std::runtime_error("startResident: a CUDA engine is needed");

@@ -70,6 +70,17 @@ class Engine {
   // tensors must be complete when enqueueOp is called (it synchronises `stream` first when one is given) and must stay
   // alive until the ticket is done.  The kernel leaves by itself after PCCL_RESIDENT_IDLE_MS without work (default 20)
   // and is started again by the next enqueueOp, so device-wide synchronisation never waits longer than that.
+  // ---- hooks for kernels compiled at run time for one program (pccl_b200/jit.py) ----------------------------------------
+  // The instruction streams of this rank for (program, message size, width), as the executors would run them.
+  std::vector<std::vector<Instr>> materializedStreams(const std::string& name, uint64_t in_bytes, int width, uint64_t* buf_bytes);
+  // Everything a launch of (program, width) on `lane` needs besides the tensors, with the same book-keeping as exeOp:
+  // the variant's signal range and launch number, the lane's scratch half and turn-taking words.
+  struct LaunchPlan {
+    uint32_t slot_base, turn_slot, finish_slot;
+    uint64_t epoch, launch_no, scratch_off, spin_limit, status_ptr, signal_off, mc_base;
+  };
+  LaunchPlan planLaunch(const std::string& name, uint64_t in_bytes, int width, int lane);
+  std::map<std::string, std::string> opInfo(const std::string& name);     // collective, redop, world, channels, in_place, ...
   void startResident(int width);
   uint64_t enqueueOp(const std::string& name, uint64_t in_ptr, uint64_t out_ptr, uint64_t in_bytes, const std::string& dtype, int lane,
                      uint64_t stream);

@@ -490,6 +490,46 @@ def case_mixed_hosts(eng, rank, world):
     return info
 
 
+def case_jit(eng, rank, world):
+    """Programs compiled at run time for this world (NVRTC), launched next to the interpreter on the same lane."""
+    from pccl_b200.jit import JitOp
+    from pccl_b200.lang import build
+    names = {"jit_direct_ar": "direct_allreduce", "jit_direct_rs": "direct_reduce_scatter", "jit_ag": "direct_allgather"}
+    if eng.has_nvls:
+        names["jit_nvls_ar"] = "nvls_allreduce"
+    for name, algo in names.items():
+        eng.regOp(name, build(algo, world, channels=2))
+    ops = {name: JitOp(eng, name) for name in names}
+    n = world * 2 * 8192
+    g = torch.Generator(device="cuda").manual_seed(33)
+    xs = [torch.randn(n, generator=g, device="cuda") for _ in range(world)]
+    x = eng.symmetric_tensor((n,), torch.float32)
+    y = eng.symmetric_tensor((n,), torch.float32)
+    total = torch.stack(xs).sum(0)
+    for it in range(3):
+        for name in [k for k in names if k.endswith("_ar")]:
+            x.copy_(xs[rank] + it); y.fill_(-1.0)
+            torch.cuda.synchronize(); dist.barrier()
+            ops[name](x, y, width=2)
+            torch.cuda.synchronize()
+            assert torch.allclose(y, total + it * world, rtol=1e-5, atol=1e-4), f"{name} launch {it}"
+            y.fill_(-1.0)
+            eng.exeOp(name, x, y, width=2)                      # interpreter launch of the same program in between
+            torch.cuda.synchronize()
+            assert torch.allclose(y, total + it * world, rtol=1e-5, atol=1e-4), f"{name} interpreted {it}"
+        shard = torch.full((n // world,), -1.0, device="cuda")
+        x.copy_(xs[rank] + it)
+        torch.cuda.synchronize(); dist.barrier()
+        ops["jit_direct_rs"](x, shard, width=2)
+        gath = torch.zeros(n, device="cuda")
+        ops["jit_ag"](xs[rank][: n // world].contiguous(), gath)
+        torch.cuda.synchronize()
+        assert torch.allclose(shard, (total + it * world)[rank * (n // world):(rank + 1) * (n // world)], rtol=1e-5, atol=1e-4), "reduce-scatter"
+        assert torch.equal(gath, torch.cat([v[: n // world] for v in xs])), "all-gather"
+    eng.raise_on_status(0, "jit")
+    return {"compiled": {k: v.compiled for k, v in ops.items()}}
+
+
 def case_resident(eng, rank, world):
     """The resident interpreter kernel on every rank: a run of all-reduces and all-gathers queued without a kernel
     launch each; the ranks' kernels wait on one another through the usual signal words (each on its own GPU)."""

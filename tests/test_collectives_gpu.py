@@ -688,3 +688,36 @@ def test_moe_layer_backward_matches_dense_reference(native):
         err = (got.float() - want).abs().max().item()
         assert err <= tol * max(1e-6, want.abs().max().item()), (name, err, want.abs().max().item())
     del moe, eng
+
+
+def test_run_time_compiled_program_launches_and_mixes_with_the_interpreter(native):
+    """JitOp on a world of one: the generated kernel (NVRTC -> cubin -> driver launch) gives the program's result, at two
+    widths and two sizes, interleaved with interpreter launches of the same program on the same lane."""
+    from pccl_b200.engine import Engine
+    from pccl_b200.jit import JitOp
+    from pccl_b200.lang import build
+    eng = Engine(0, 1)
+    eng.initEngine("cuda", heap_bytes=512 << 20)
+    eng.regOp("ar", build("ring_allreduce", 1, channels=2))
+    eng.regOp("ag", build("direct_allgather", 1, channels=1))
+    ar, ag = JitOp(eng, "ar"), JitOp(eng, "ag")
+    for it, (n, width) in enumerate([(4096, 1), (4096, 2), (3 * 8192 + 16, 2), (4096, 1)]):
+        x = torch.arange(n, device="cuda", dtype=torch.float32) + it
+        y = torch.full((n,), -1.0, device="cuda")
+        ar(x, y, width=width)
+        torch.cuda.synchronize()
+        assert torch.equal(y, x), (it, n, width)
+        y.fill_(-1)
+        eng.exeOp("ar", x, y, width=width, check=True)          # the interpreter on the same signal range and lane
+        assert torch.equal(y, x)
+        g = torch.zeros(n, device="cuda")
+        ag(x, g)
+        torch.cuda.synchronize()
+        assert torch.equal(g, x)
+    assert ar.compiled == 3 and eng.check_status(0)[0] == 0      # (4096, 1) was compiled once
+    xb = torch.randn(8192, device="cuda").bfloat16()
+    yb = torch.zeros_like(xb)
+    ar(xb, yb, width=2)
+    torch.cuda.synchronize()
+    assert torch.equal(xb, yb)
+    del ar, ag, eng

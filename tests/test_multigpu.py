@@ -35,7 +35,7 @@ def _world():
     return min(torch.cuda.device_count(), 8)
 
 
-@pytest.mark.parametrize("case", ["heap", "coll_p2p", "coll_nvls", "coll_fp8", "interp", "rooted", "overlap", "mixed_hosts", "resident", "dp", "dp_milp_ring", "fused_tp",
+@pytest.mark.parametrize("case", ["heap", "coll_p2p", "coll_nvls", "coll_fp8", "interp", "rooted", "overlap", "mixed_hosts", "resident", "jit", "dp", "dp_milp_ring", "fused_tp",
                                   "fused_tp_fp8", "tp_mlp", "moe"])
 def test_case(case, tmp_path):
     _run(case, _world(), tmp_path)
