@@ -231,7 +231,11 @@ def main() -> None:
                       "with scale/cast and overlapped with backward)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": (value / recorded_ddp) if recorded_ddp else None,
+            "vs_baseline": (value / recorded_ddp) if recorded_ddp else (
+                value / baseline["tokens_per_s"] if baseline and baseline.get("tokens_per_s") else None),
+            "vs_baseline_source": ("recorded PyTorch DDP tokens/s for this N on this GPU pool" if recorded_ddp else
+                                   ("PyTorch DDP measured in this launch (no recorded number for this N)"
+                                    if baseline and baseline.get("tokens_per_s") else None)),
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": "gpt-1.3b (24 layers, d=2048, 16 heads, vocab 50257)" if args.model == "gpt-1.3b" else "tiny",
                        "params": n_params, "global_batch": world * B, "seq_len": S, "parallelism": f"dp{world}",
