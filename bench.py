@@ -91,6 +91,8 @@ def main() -> None:
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the gradient/optimizer kernels (0 = automatic)")
     ap.add_argument("--algo", default="auto", choices=["auto", "nvls", "p2p"])
+    ap.add_argument("--bucket-timing", action="store_true",
+                    help="after the timed runs, one extra step with CUDA events around every gradient bucket's kernels (key dp_timing)")
     ap.add_argument("--unfused-blocks", action="store_true", help="every layer its own autograd node (comparison run)")
     ap.add_argument("--no-micro", action="store_true", help="skip the collective micro-benchmarks at N > 1")
     args = ap.parse_args()
@@ -196,6 +198,11 @@ def main() -> None:
     check_status("end-to-end steps")
 
     grad_rs_schedule = dp.schedule
+    dp_timing = None
+    if args.bucket_timing:
+        b = dev_batches[0]
+        dp_timing = dp.timed_step(b[:, :-1], b[:, 1:])
+        barrier()
     # ---- the library's headline metric and the PyTorch baseline, in the same launch -----------------------
     # The training state is released first: its buckets give the symmetric heap back to the 1 GB collectives,
     # and the baseline gets the device memory.
@@ -257,6 +264,8 @@ def main() -> None:
             out["baseline_ddp"] = baseline
             if "tokens_per_s" in baseline:
                 out["baseline_ddp"]["ratio_ours_over_ddp_same_launch"] = value / baseline["tokens_per_s"]
+        if dp_timing is not None:
+            out["dp_timing"] = dp_timing
         if head is not None:
             out["headline"] = head
         print(json.dumps(out))

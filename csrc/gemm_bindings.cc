@@ -32,6 +32,15 @@ void bindGemm(py::module_& m) {
                                   reinterpret_cast<uint32_t*>(status), reinterpret_cast<cudaStream_t>(stream));
           if (err != 0) throw std::runtime_error(std::string("gemm_bf16_dgelu: ") + cudaErrorName(err) + " " + gemmLastError());
         });
+  m.def("gemm_bf16_dual",
+        [](uint64_t a0, int64_t lda0, uint64_t b0, int64_t ldb0, uint64_t d0, int64_t ldd0, int M0, int N0, bool acc0, uint64_t a1, int64_t lda1,
+           uint64_t b1, int64_t ldb1, uint64_t d1, int64_t ldd1, int M1, int N1, bool acc1, int K, uint32_t flags, int sms, uint64_t status,
+           uint64_t stream) {
+          GemmProblem p0{reinterpret_cast<const void*>(a0), lda0, reinterpret_cast<const void*>(b0), ldb0, reinterpret_cast<void*>(d0), ldd0, M0, N0, acc0};
+          GemmProblem p1{reinterpret_cast<const void*>(a1), lda1, reinterpret_cast<const void*>(b1), ldb1, reinterpret_cast<void*>(d1), ldd1, M1, N1, acc1};
+          int err = gemmBf16Dual(p0, p1, K, flags, sms, reinterpret_cast<uint32_t*>(status), reinterpret_cast<cudaStream_t>(stream));
+          if (err != 0) throw std::runtime_error(std::string("gemm_bf16_dual: ") + cudaErrorName(err) + " " + gemmLastError());
+        });
   m.def("gemm_fp8",
         [](uint64_t a, int64_t lda, uint64_t sa, int ld_sa, uint64_t b, int64_t ldb, uint64_t sb, int ld_sb, uint64_t d, int64_t ldd,
            int M, int N, int K, uint32_t flags, uint64_t bias, uint64_t d2, int sms, uint64_t status, uint64_t stream) {

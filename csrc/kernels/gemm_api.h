@@ -36,6 +36,18 @@ int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, in
 int gemmBf16Dgelu(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, const void* pre, float* colsum,
                   int M, int N, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream);
 
+// Two GEMMs of the same K and operand forms as ONE launch: their tiles form one list for the persistent CTA pairs, so the
+// partly filled last wave is paid once instead of twice (the two weight-gradient GEMMs of an MLP: 256 + 256 tiles on 74
+// CTA pairs take 7 rounds instead of 4 + 4).  bf16 or fp32 output; `accumulate` per problem.
+struct GemmProblem {
+  const void* A; int64_t lda;
+  const void* B; int64_t ldb;
+  void* D; int64_t ldd;
+  int M, N;
+  bool accumulate;
+};
+int gemmBf16Dual(const GemmProblem& p0, const GemmProblem& p1, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream);
+
 // Grouped GEMM for expert layers: group g multiplies rows [row_off[g], row_off[g+1]) of A [*, K] with
 // the g-th [N, K] block of B (stacked [groups*N, K]) into the same rows of D [*, N].  `row_off`
 // (groups+1 int32) lives on the device, so no host synchronisation is needed to know the sizes.

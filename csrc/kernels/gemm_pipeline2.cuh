@@ -11,6 +11,7 @@
 // waits as gemm_pipeline.cuh; every thread of both CTAs reaches the closing cluster barrier.
 #pragma once
 #include <cstdlib>
+#include <type_traits>
 #include <utility>
 
 #include "gemm_pipeline.cuh"
@@ -38,11 +39,21 @@ struct Barriers {
   uint32_t abort;
 };
 
+// An epilogue may declare `static constexpr bool kVarN = true` and `int tile_n(const TileCoord&)`: the tile then spans only
+// that many of the BN accumulator columns (a multiple of 16).  The MMA is issued with that N -- each CTA contributes the
+// first tile_n / 2 rows of its B box -- and the epilogue is handed only the strips below it, so a ragged last tile costs
+// tensor time in proportion to its width.  `int b_box(const TileCoord&)` then picks one of several B descriptors (`tmB` is an
+// array) whose boxes hold 128 >> b_box rows, so a narrow tile does not fetch rows it will not multiply.
+template <class E, class = void> struct HasVarN : std::false_type {};
+template <class E> struct HasVarN<E, std::void_t<decltype(E::kVarN)>> : std::true_type {};
+
 // `sched` enumerates pair tiles: t.m indexes 256-row blocks.  Epi sees per-CTA coordinates through
 // a_row0 / b_row0 (which must add cta_rank * 128) and strip(t, row_in_cta_tile, col, r).
 // NSTAGES (<= STAGES) shortens the operand ring; an epilogue that needs a large staging area of its own (the
 // reduce-scatter epilogue stages whole 512-byte rows) gives up one stage for it.
-template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES>
+// NPROB > 1: `tmA` / `tmB` are arrays of that many descriptors and a tile's `extra` field says which pair it loads from --
+// several GEMMs with the same K walked as one tile list (fewer idle CTAs in the last wave than one launch per GEMM).
+template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES, int NPROB = 1>
 __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* tmB, int K, const Sched& sched,
                                     const Gate& gate, Epi& epi, uint32_t* status) {
   static_assert(NSTAGES >= 2 && NSTAGES <= STAGES, "ring length");
@@ -67,8 +78,10 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
     tc::mbar_init(&bar->drain, 1);
     bar->abort = 0;
     tc::fence_barrier_init();
-    tc::tma_prefetch_desc(tmA);
-    tc::tma_prefetch_desc(tmB);
+    for (int q = 0; q < NPROB; ++q) {
+      tc::tma_prefetch_desc(tmA + q);
+      tc::tma_prefetch_desc(tmB + q);
+    }
   }
   __syncthreads();
   tc::cluster_sync();                 // the peer's barriers are initialised before anything signals them
@@ -92,24 +105,32 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       for (int it = 0; ok && sched.get(it, &t); ++it) {
         if (!gate.wait(t, abort)) { ok = false; break; }
         const int row0 = epi.a_row0(t), col0 = epi.b_row0(t);        // already offset by this CTA's half
+        const CUtensorMap* const tmA_t = NPROB > 1 ? tmA + t.extra : tmA;
+        const CUtensorMap* tmB_t = NPROB > 1 ? tmB + t.extra : tmB;
+        uint32_t stage_tx = 2 * STAGE_BYTES;
+        if constexpr (HasVarN<Epi>::value) {
+          const int sel = epi.b_box(t);
+          tmB_t = tmB + sel;
+          stage_tx = 2 * (A_BYTES + (B_BYTES >> sel));
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!tc::mbar_wait(&bar->empty[stage], phase ^ 1, abort)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           const uint32_t full_leader = tc::mapa(tc::smem_u32(&bar->full[stage]), 0);
-          if (leader) tc::mbar_arrive_expect_tx(&bar->full[stage], 2 * STAGE_BYTES);   // both CTAs' bytes
+          if (leader) tc::mbar_arrive_expect_tx(&bar->full[stage], stage_tx);   // both CTAs' bytes
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tc::tma_load_2d_pair(sa, tmA, full_leader, k0, row0);
+            tc::tma_load_2d_pair(sa, tmA_t, full_leader, k0, row0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tc::tma_load_2d_pair(sa + j * (64 * BK * 2), tmA, full_leader, row0 + j * 64, k0);
+            for (int j = 0; j < BM / 64; ++j) tc::tma_load_2d_pair(sa + j * (64 * BK * 2), tmA_t, full_leader, row0 + j * 64, k0);
           }
           if constexpr (!B_MN) {
-            tc::tma_load_2d_pair(sb, tmB, full_leader, k0, col0);
+            tc::tma_load_2d_pair(sb, tmB_t, full_leader, k0, col0);
           } else {
 #pragma unroll
-            for (int j = 0; j < HALF_N / 64; ++j) tc::tma_load_2d_pair(sb + j * (64 * BK * 2), tmB, full_leader, col0 + j * 64, k0);
+            for (int j = 0; j < HALF_N / 64; ++j) tc::tma_load_2d_pair(sb + j * (64 * BK * 2), tmB_t, full_leader, col0 + j * 64, k0);
           }
           if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -131,6 +152,8 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
         if (!tc::mbar_wait(&bar->tmem_empty[acc], acc_phase ^ 1, abort)) { ok = false; break; }
         tc::tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
+        uint32_t idesc_t = idesc;
+        if constexpr (HasVarN<Epi>::value) idesc_t = tc::make_idesc(1, 1, A_MN, B_MN, PAIR_M, static_cast<uint32_t>(epi.tile_n(t)));
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!tc::mbar_wait(&bar->full[stage], phase, abort)) { ok = false; break; }
           tc::tc_fence_after();
@@ -139,7 +162,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t da = tc::smem_desc_sw128(sa + k * A_KSTEP, A_LBO, SBO);
             uint64_t db = tc::smem_desc_sw128(sb + k * B_KSTEP, B_LBO, SBO);
-            tc::mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+            tc::mma_f16_pair(d_tmem, da, db, idesc_t, (kb | k) != 0);
           }
           tc::mma_commit_pair(&bar->empty[stage], 3);       // frees the stage in both CTAs
           if (++stage == NSTAGES) { stage = 0; phase ^= 1; }
@@ -164,8 +187,10 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       tc::tc_fence_after();
       const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       epi.tile_begin(t);
+      int n_strips = BN / 32;
+      if constexpr (HasVarN<Epi>::value) n_strips = (epi.tile_n(t) + 31) / 32;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < n_strips; ++c) {
         uint32_t r[32];
         tc::tmem_ld_32x32(taddr + c * 32, r);
         tc::tmem_ld_wait();

@@ -42,6 +42,51 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, pg, pe, status);
 }
 
+// ---- two GEMMs with one K as one tile list ---------------------------------------------------------------------------
+struct DualMaps { CUtensorMap a[2], b[2]; };
+
+struct DualSched {
+  int tiles_m[2], tiles_n[2], first, stride;
+  __device__ __forceinline__ bool get(int it, TileCoord* t) const {
+    long long idx = first + static_cast<long long>(it) * stride;
+    const long long n0 = static_cast<long long>(tiles_m[0]) * tiles_n[0];
+    const int q = idx >= n0 ? 1 : 0;
+    if (q) idx -= n0;
+    if (idx >= static_cast<long long>(tiles_m[q]) * tiles_n[q]) return false;
+    const int per_group = GroupedSched::GROUP_M * tiles_n[q];
+    const int g = static_cast<int>(idx / per_group), r = static_cast<int>(idx % per_group);
+    const int gm = min(GroupedSched::GROUP_M, tiles_m[q] - g * GroupedSched::GROUP_M);
+    t->m = g * GroupedSched::GROUP_M + r % gm;
+    t->n = r / gm;
+    t->extra = q;
+    return true;
+  }
+};
+
+struct DualEpi {
+  static constexpr bool kRow128 = false;
+  StoreEpi e[2];
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return e[t.extra].a_row0(t); }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return e[t.extra].b_row0(t); }
+  __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
+  __device__ __forceinline__ void strip(const TileCoord& t, int row, int col, uint32_t* r) { e[t.extra].strip(t, row, col, r); }
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
+gemm_bf16_pair_dual_kernel(const __grid_constant__ DualMaps maps, DualEpi epi, int K, uint32_t* status) {
+  DualSched sched{{(epi.e[0].M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.e[1].M + gemm2::PAIR_M - 1) / gemm2::PAIR_M},
+                  {(epi.e[0].N + gemm2::BN - 1) / gemm2::BN, (epi.e[1].N + gemm2::BN - 1) / gemm2::BN},
+                  static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
+  NoGate gate;
+  const int cta = static_cast<int>(tc::cluster_ctarank());
+  gemm2::PairEpi<DualEpi> pe{epi, cta};
+  gemm2::PairGate<NoGate> pg{gate, cta};
+  gemm2::run<A_MN, B_MN, DualSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<DualEpi>, gemm2::STAGES, 2>(maps.a, maps.b, K, sched, pg, pe, status);
+}
+
 thread_local std::string g_err;
 
 template <bool A_MN, bool B_MN, class Epi = StoreEpi>
@@ -155,6 +200,56 @@ int gemmBf16Dgelu(const void* A, int64_t lda, const void* B, int64_t ldb, void* 
   int grid = 2 * (pair_tiles < n_sm / 2 ? pair_tiles : n_sm / 2);
   return b_mn ? launchPair<false, true, DgeluEpi>(pa, pb, epi, K, grid, status, stream)
               : launchPair<false, false, DgeluEpi>(pa, pb, epi, K, grid, status, stream);
+}
+
+int gemmBf16Dual(const GemmProblem& p0, const GemmProblem& p1, int K, uint32_t flags, int sms, uint32_t* status, cudaStream_t stream) {
+  const GemmProblem* ps[2] = {&p0, &p1};
+  const bool a_mn = flags & GEMM_A_MN, b_mn = flags & GEMM_B_MN;
+  if (K <= 0) return 0;
+  DualMaps maps;
+  DualEpi epi;
+  for (int q = 0; q < 2; ++q) {
+    const GemmProblem& p = *ps[q];
+    if (p.M <= 0 || p.N <= 0 || (p.lda | p.ldb | p.ldd) % 8 ||
+        (reinterpret_cast<uintptr_t>(p.A) | reinterpret_cast<uintptr_t>(p.B) | reinterpret_cast<uintptr_t>(p.D)) % 16) {
+      g_err = "gemmBf16Dual: sizes must be positive, strides multiples of 8 elements, pointers 16-byte aligned";
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+    if (!a_mn ? !makeTensorMap2D(&maps.a[q], p.A, TM_BF16, K, p.M, p.lda, BK, 128, &g_err) : !makeTensorMap2D(&maps.a[q], p.A, TM_BF16, p.M, K, p.lda, 64, BK, &g_err))
+      return static_cast<int>(cudaErrorInvalidValue);
+    if (!b_mn ? !makeTensorMap2D(&maps.b[q], p.B, TM_BF16, K, p.N, p.ldb, BK, 128, &g_err) : !makeTensorMap2D(&maps.b[q], p.B, TM_BF16, p.N, K, p.ldb, 64, BK, &g_err))
+      return static_cast<int>(cudaErrorInvalidValue);
+    epi.e[q] = StoreEpi{p.D, nullptr, nullptr, p.ldd, p.M, p.N, (flags & GEMM_OUT_F32) | (p.accumulate ? GEMM_ACCUMULATE : 0u)};
+  }
+  const long long tiles = static_cast<long long>((p0.M + 255) / 256) * ((p0.N + 255) / 256) + static_cast<long long>((p1.M + 255) / 256) * ((p1.N + 255) / 256);
+  int n_sm = deviceSmCount();
+  if (sms > 0 && sms < n_sm) n_sm = sms;
+  const int grid = 2 * static_cast<int>(tiles < n_sm / 2 ? tiles : n_sm / 2);
+  static bool attr_set[4] = {false, false, false, false};      // per kernel: the four instantiations share one function type
+  bool& attr = attr_set[(a_mn ? 2 : 0) | (b_mn ? 1 : 0)];
+  auto go = [&](auto kern) {
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      attr = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(gemm2::NUM_THREADS);
+    cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int Kc = K;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, maps, epi, Kc, status));
+  };
+  if (a_mn) return b_mn ? go(gemm_bf16_pair_dual_kernel<true, true>) : go(gemm_bf16_pair_dual_kernel<true, false>);
+  return b_mn ? go(gemm_bf16_pair_dual_kernel<false, true>) : go(gemm_bf16_pair_dual_kernel<false, false>);
 }
 
 }  // namespace pccl

@@ -306,24 +306,31 @@ __global__ void __launch_bounds__(256) quant_blocks_kernel(const __nv_bfloat16* 
 // ---------------------------------------------------------------------------------------------
 using namespace gemm;
 
+// Both schedulers walk the concatenated per-group tile lists.  A role asks for its tiles in increasing order, so each keeps a
+// cursor (group, tiles before it) instead of scanning the groups from the start for every tile: the scan is a chain of
+// dependent loads, and the MMA warp's share of it would sit between two tiles with the tensor cores idle.
 struct GroupedSched {
   const int* row_off;    // groups + 1
   int groups, tiles_n, first, stride;
   int tile_rows;         // 128 (single CTA) or 256 (CTA pair)
+  mutable int cur_g = 0;
+  mutable long long cur_base = 0;
   // Tile `idx` of the concatenated per-group tile lists -> (group, m-tile inside group, n-tile).
   __device__ __forceinline__ bool get(int it, TileCoord* t) const {
-    long long idx = first + static_cast<long long>(it) * stride;
-    for (int g = 0; g < groups; ++g) {
-      const int rows = row_off[g + 1] - row_off[g];
+    const long long idx = first + static_cast<long long>(it) * stride;
+    while (cur_g < groups) {
+      const int rows = row_off[cur_g + 1] - row_off[cur_g];
       const int tm = (rows + tile_rows - 1) / tile_rows;
       const long long tiles = static_cast<long long>(tm) * tiles_n;
-      if (idx < tiles) {
-        t->m = static_cast<int>(idx % tm);
-        t->n = static_cast<int>(idx / tm);
-        t->extra = g;
+      if (idx - cur_base < tiles) {
+        const int local = static_cast<int>(idx - cur_base);
+        t->m = local % tm;
+        t->n = local / tm;
+        t->extra = cur_g;
         return true;
       }
-      idx -= tiles;
+      cur_base += tiles;
+      ++cur_g;
     }
     return false;
   }
@@ -380,6 +387,102 @@ gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   gemm2::PairEpi<GroupedEpi> pe{epi, cta};
   gemm2::PairGate<NoGate> pg{gate, cta};
   gemm2::run<false, false>(&tmA, &tmB, K, sched, pg, pe, status);
+}
+
+// The same product with the operands exchanged: the weights of a group are the M side of the tile (whole 256-row tiles, their
+// count is a multiple of 256) and the group's rows are the N side, whose extent the MMA instruction takes per tile in steps
+// of 16.  A group of 520 rows then costs 2 + 8/256 tiles of tensor time per weight tile, where the row-major form above pays
+// for 3: with a few hundred rows per expert that is a fifth of the whole product.  The accumulator arrives transposed (lane =
+// output feature, column = row of the group), so a warp stores 32 consecutive features of one row per instruction.
+struct RaggedSched {
+  const int* row_off;
+  int groups, tiles_f, first, stride;        // tiles_f = N / 256 weight tiles per group
+  mutable int cur_g = 0;
+  mutable long long cur_base = 0;
+  __device__ __forceinline__ bool get(int it, TileCoord* t) const {
+    const long long idx = first + static_cast<long long>(it) * stride;
+    while (cur_g < groups) {
+      const int rows = row_off[cur_g + 1] - row_off[cur_g];
+      const int tr = (rows + 255) / 256;
+      const long long tiles = static_cast<long long>(tr) * tiles_f;
+      if (idx - cur_base < tiles) {
+        const int local = static_cast<int>(idx - cur_base);
+        t->m = local / tr;                     // weight tile; the row tiles of one weight tile are neighbours in the list
+        t->n = local % tr;
+        t->extra = cur_g;
+        return true;
+      }
+      cur_base += tiles;
+      ++cur_g;
+    }
+    return false;
+  }
+};
+
+struct RaggedEpi {
+  static constexpr bool kVarN = true;
+  __nv_bfloat16* D;
+  long long ldd;
+  const int* row_off;
+  int N;             // output features per group
+  uint32_t flags;
+  int cta;
+  __device__ __forceinline__ int tile_n(const TileCoord& t) const {
+    const int left = row_off[t.extra + 1] - row_off[t.extra] - t.n * 256;
+    return left >= 256 ? 256 : ((left + 15) & ~15);
+  }
+  // A operand: this CTA's 128 weight rows; B operand: this CTA's half of the tile's rows
+  // descriptor whose box holds 128 >> b_box rows: the smallest that covers this CTA's tile_n / 2 rows
+  __device__ __forceinline__ int b_box(const TileCoord& t) const {
+    const int half = tile_n(t) >> 1;
+    return half > 64 ? 0 : half > 32 ? 1 : half > 16 ? 2 : half > 8 ? 3 : 4;
+  }
+  __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.extra * N + t.m * 256 + cta * 128; }
+  __device__ __forceinline__ int b_row0(const TileCoord& t) const { return row_off[t.extra] + t.n * 256 + cta * (tile_n(t) >> 1); }
+  __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
+  // The lane holds 32 rows of ONE feature; its neighbours hold the next features of the same rows.  Two exchange steps
+  // (lane ^ 1, lane ^ 2) regroup that into 4 consecutive features of one row per lane, so a strip leaves as 8 stores of 8 bytes
+  // per lane instead of 32 of 2: lanes 4q..4q+3 then cover rows 4j+0..3 of features 4q..4q+3.
+  __device__ __forceinline__ void strip(const TileCoord& t, int feat_in_cta, int col0, uint32_t* r) {
+    const int lane = feat_in_cta & 31;
+    const int feat4 = t.m * 256 + cta * 128 + (feat_in_cta & ~3);
+    const int row0 = row_off[t.extra] + t.n * 256 + col0;
+    const int n_valid = row_off[t.extra + 1] - row0;          // rows of this strip that belong to the group (may exceed 32)
+    const bool gelu = flags & GEMM_GELU_INPLACE;
+    const bool odd1 = lane & 1, odd2 = lane & 2;
+    uint32_t p[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float a = __uint_as_float(r[2 * j]), b = __uint_as_float(r[2 * j + 1]);
+      if (gelu) { a = gelu_tanh(a); b = gelu_tanh(b); }
+      const float got = __shfl_xor_sync(0xffffffffu, odd1 ? a : b, 1);
+      // even lane: row 2j, features (f, f+1) = (own a, neighbour's a); odd lane: row 2j+1, features (f-1, f) = (neighbour's b, own b)
+      const __nv_bfloat162 v = odd1 ? __floats2bfloat162_rn(got, b) : __floats2bfloat162_rn(a, got);
+      p[j] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, odd2 ? p[2 * m] : p[2 * m + 1], 2);
+      // bit 1 clear: keeps pair-row 2m, features +0..1 own, +2..3 from lane ^ 2; bit 1 set: keeps pair-row 2m+1
+      const uint2 out = odd2 ? make_uint2(got, p[2 * m + 1]) : make_uint2(p[2 * m], got);
+      const int row = 2 * (2 * m + (odd2 ? 1 : 0)) + (odd1 ? 1 : 0);
+      if (row < n_valid)
+        *reinterpret_cast<uint2*>(D + static_cast<long long>(row0 + row) * ldd + feat4) = out;
+    }
+  }
+};
+
+struct RaggedMaps { CUtensorMap x[5]; };     // boxes of 128, 64, 32, 16, 8 rows
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_grouped_ragged_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ RaggedMaps tmX, RaggedEpi epi, int groups, int K,
+                           uint32_t* status) {
+  RaggedSched sched{epi.row_off, groups, epi.N / 256, static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
+  NoGate gate;
+  epi.cta = static_cast<int>(tc::cluster_ctarank());
+  gemm2::run<false, false>(&tmW, tmX.x, K, sched, gate, epi, status);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -534,6 +637,24 @@ int gemmGroupedBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void
   int n_sm = deviceSmCount();
   if (sms > 0 && sms < n_sm) n_sm = sms;
   GroupedEpi epi{static_cast<__nv_bfloat16*>(D), ldd, row_off, N, flags};
+  static const bool ragged_on = !(std::getenv("PCCL_GROUPED_RAGGED") && std::getenv("PCCL_GROUPED_RAGGED")[0] == '0');
+  if (N % 256 == 0 && n_sm >= 2 && ragged_on) {
+    // operands exchanged: weights on the M side, the groups' rows on an N side that is cut to the rows there are
+    CUtensorMap tw;
+    RaggedMaps tx;
+    if (!makeTensorMap2D(&tw, B, TM_BF16, K, static_cast<uint64_t>(groups) * N, ldb, BK, 128, &err)) return static_cast<int>(cudaErrorInvalidValue);
+    for (int i = 0; i < 5; ++i)
+      if (!makeTensorMap2D(&tx.x[i], A, TM_BF16, K, max_rows, lda, BK, 128 >> i, &err)) return static_cast<int>(cudaErrorInvalidValue);
+    static bool set3 = false;
+    if (!set3) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_grouped_ragged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      set3 = true;
+    }
+    RaggedEpi repi{static_cast<__nv_bfloat16*>(D), ldd, row_off, N, flags, 0};
+    return static_cast<int>(gemm2::launch_pairs(gemm_grouped_ragged_kernel, dim3(n_sm & ~1), NUM_THREADS, gemm2::SMEM_BYTES, stream, false, tw, tx,
+                                                repi, groups, K, status));
+  }
   if (N % 256 == 0 && n_sm >= 2) {       // CTA pairs: each CTA loads 128 of the 256 B rows of a tile
     if (!makeTensorMap2D(&tb, B, TM_BF16, K, static_cast<uint64_t>(groups) * N, ldb, BK, 128, &err)) return static_cast<int>(cudaErrorInvalidValue);
     static bool set2 = false;

@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 
 from ..ops.elementwise import colsum
-from ..ops.gemm import gemm, gemm_dgelu
+from ..ops.gemm import gemm, gemm_dgelu, gemm_dual
 
 
 def _as_operand(t: torch.Tensor) -> torch.Tensor:
@@ -43,6 +43,23 @@ def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor) -> O
     gemm(dy2, x2, a_t=True, b_t=True, out=mg, accumulate=bool(getattr(weight, "_pccl_written", False)))
     _finish_main_grad(weight)
     return None
+
+
+def _weight_grad_pair(dy_a: torch.Tensor, x_a: torch.Tensor, w_a: torch.Tensor, dy_b: torch.Tensor, x_b: torch.Tensor, w_b: torch.Tensor):
+    """The weight gradients of two layers over the same rows as one launch (``gemm_dual``)."""
+    mg_a, mg_b = _grad_target(w_a), _grad_target(w_b)
+    if (mg_a is None) != (mg_b is None) or dy_a.shape[0] != dy_b.shape[0] or (mg_a is not None and mg_a.dtype != mg_b.dtype):
+        return _weight_grad(dy_a, x_a, w_a), _weight_grad(dy_b, x_b, w_b)
+    if mg_a is None:
+        ga = torch.empty((dy_a.shape[1], x_a.shape[1]), dtype=torch.bfloat16, device=dy_a.device)
+        gb = torch.empty((dy_b.shape[1], x_b.shape[1]), dtype=torch.bfloat16, device=dy_b.device)
+        gemm_dual(dy_a, x_a, ga, dy_b, x_b, gb, a_t=True, b_t=True)
+        return ga, gb
+    gemm_dual(dy_a, x_a, mg_a, dy_b, x_b, mg_b, a_t=True, b_t=True, accumulate0=bool(getattr(w_a, "_pccl_written", False)),
+              accumulate1=bool(getattr(w_b, "_pccl_written", False)))
+    _finish_main_grad(w_a)
+    _finish_main_grad(w_b)
+    return None, None
 
 
 def _bias_grad(dy2: torch.Tensor, bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -143,10 +160,9 @@ class _MlpFn(torch.autograd.Function):
             dact = gemm(dz2, w2, b_t=True)
             dy2 = torch.ops.aten.gelu_backward(dact, pre, approximate="tanh")
             db1 = _bias_grad(dy2, b1)
-        dw2 = _weight_grad(dz2, act, w2)
         db2 = None if ctx.defer_b2_grad else _bias_grad(dz2, b2)
         dx = gemm(dy2, w1, b_t=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
-        dw1 = _weight_grad(dy2, x2, w1)
+        dw1, dw2 = _weight_grad_pair(dy2, x2, w1, dz2, act, w2)          # both weight gradients in one launch
         return dx, dw1, db1, dw2, db2, None
 
 

@@ -110,6 +110,29 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     return out
 
 
+def gemm_dual(a0: torch.Tensor, b0: torch.Tensor, out0: torch.Tensor, a1: torch.Tensor, b1: torch.Tensor, out1: torch.Tensor, *,
+              a_t: bool = False, b_t: bool = False, accumulate0: bool = False, accumulate1: bool = False, sms: int = 0) -> None:
+    """Two GEMMs ``out_i (+)= op(a_i) @ op(b_i)`` with one reduction length and operand form, as a single launch: their tiles
+    form one list for the persistent CTA pairs, so the partly filled last wave is paid once (the two weight-gradient GEMMs
+    of an MLP are the case in mind)."""
+    for t, name in ((a0, "a0"), (b0, "b0"), (a1, "a1"), (b1, "b1")):
+        _check(t, name)
+    dims = []
+    for a, b, out in ((a0, b0, out0), (a1, b1, out1)):
+        M, K = (a.shape[1], a.shape[0]) if a_t else (a.shape[0], a.shape[1])
+        N, Kb = (b.shape[1], b.shape[0]) if b_t else (b.shape[0], b.shape[1])
+        if K != Kb or out.shape != (M, N) or out.stride(1) != 1 or out.dtype != out0.dtype or out.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("gemm_dual: shapes do not match, or the outputs differ in dtype")
+        dims.append((M, N, K))
+    if dims[0][2] != dims[1][2]:
+        raise ValueError("gemm_dual: both products must have the same inner dimension")
+    flags = (C.GEMM_A_MN if a_t else 0) | (C.GEMM_B_MN if b_t else 0) | (C.GEMM_OUT_F32 if out0.dtype == torch.float32 else 0)
+    C.gemm_bf16_dual(a0.data_ptr(), a0.stride(0), b0.data_ptr(), b0.stride(0), out0.data_ptr(), out0.stride(0), dims[0][0], dims[0][1], accumulate0,
+                     a1.data_ptr(), a1.stride(0), b1.data_ptr(), b1.stride(0), out1.data_ptr(), out1.stride(0), dims[1][0], dims[1][1], accumulate1,
+                     dims[0][2], flags, sms, status_words(a0.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    count_launch()
+
+
 def gemm_dgelu(a: torch.Tensor, b: torch.Tensor, pre: torch.Tensor, *, b_t: bool = False, colsum: Optional[torch.Tensor] = None,
                out: Optional[torch.Tensor] = None, sms: int = 0) -> torch.Tensor:
     """``out = (a @ op(b)) * gelu_tanh'(pre)`` in one kernel (the GELU derivative is applied in the GEMM epilogue), and,

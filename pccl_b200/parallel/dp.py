@@ -87,6 +87,9 @@ class ShardedDataParallel:
         self._plan_schedule(int(bucket_mb * (1 << 20)), schedule, topology)
         self._build_buckets(params, int(bucket_mb * (1 << 20)) // 2)
         self._ready_events: Dict[int, torch.cuda.Event] = {}
+        # opt-in per-bucket timing (CUDA events on both streams); see timed_step()
+        self._timing = False
+        self._marks: Dict[str, object] = {}
 
     # ------------------------------------------------------------------------------------------
     def _plan_schedule(self, bucket_bytes: int, schedule: str, topology) -> None:
@@ -191,9 +194,22 @@ class ShardedDataParallel:
         p._pccl_ready()
 
     def _launch_reduce(self, b: _Bucket) -> None:
-        ev = torch.cuda.Event()
+        ev = torch.cuda.Event(enable_timing=self._timing)
         ev.record(torch.cuda.current_stream())
         self.comm_stream.wait_event(ev)
+        if self._timing:
+            marks = {"ready": ev, "start": torch.cuda.Event(enable_timing=True), "reduced": torch.cuda.Event(enable_timing=True),
+                     "done": torch.cuda.Event(enable_timing=True)}
+            self._marks[b.index] = marks
+            marks["start"].record(self.comm_stream)
+            try:
+                self._launch_reduce_inner(b, marks["reduced"])
+            finally:
+                marks["done"].record(self.comm_stream)
+            return
+        self._launch_reduce_inner(b, None)
+
+    def _launch_reduce_inner(self, b: _Bucket, reduced_mark) -> None:
         if self.interpreted:
             # the synthesised multi-step schedule, run by the interpreter kernel; scale and cast follow
             self.engine.exeOp("dp_grad_reduce_scatter", b.grads, b.rs_out, width=4, lane=1, stream=self.comm_stream)
@@ -209,6 +225,8 @@ class ShardedDataParallel:
         coll.reduce_scatter_adamw(self.engine, b.grads, b.master, b.exp_avg, b.exp_avg_sq, dst, lr=self.lr, betas=self.betas,
                                   eps=self.eps, weight_decay=self.weight_decay if b.decay else 0.0, step=self.step_count,
                                   scale=1.0 / self.world, algo=self.algo, blocks=self.comm_blocks, lane=1, stream=self.comm_stream)
+        if reduced_mark is not None:
+            reduced_mark.record(self.comm_stream)
         if self.world > 1:
             # every gradient of the bucket exists, so backward no longer reads these parameters on any rank
             # that has reached this point; the all-gather's entry barrier waits for the others
@@ -258,6 +276,47 @@ class ShardedDataParallel:
         loss.backward()
         self.optimizer_step()
         return loss.detach()
+
+    def timed_step(self, inputs: torch.Tensor, targets: torch.Tensor) -> Dict[str, object]:
+        """One training step with CUDA events around forward, backward and every bucket's kernels on the communication
+        stream.  Returns, in milliseconds from the start of the step: ``forward_end``, ``backward_end``, ``step_end`` (after
+        the join with the communication stream) and per bucket ``ready`` (its last gradient was written), ``start``,
+        ``reduced`` (reduce-scatter + AdamW done; equals ``start`` where the mode does not fuse them) and ``done``
+        (parameter all-gather done).  ``exposed_ms`` is what the step waits for after backward has ended;
+        ``comm_busy_ms`` is the time the communication stream spent in these kernels."""
+        if not self.fuse_optimizer or self.interpreted:
+            raise RuntimeError("timed_step covers the fused reduce-scatter + AdamW + all-gather mode")
+        ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+        t0, t_fwd, t_bwd, t_end = ev(), ev(), ev(), ev()
+        self._timing, self._marks = True, {}
+        try:
+            cur = torch.cuda.current_stream()
+            t0.record(cur)
+            self.zero_grad()
+            loss = self.model(inputs, targets)
+            t_fwd.record(cur)
+            loss.backward()
+            t_bwd.record(cur)
+            self.optimizer_step()
+            t_end.record(cur)
+            torch.cuda.synchronize()
+        finally:
+            self._timing = False
+        at = lambda e: t0.elapsed_time(e)  # noqa: E731
+        rows = []
+        for b in self.buckets:
+            m = self._marks.get(b.index)
+            if m is None:
+                continue
+            rows.append({"bucket": b.index, "mbytes": b.numel * 2 / 2**20, "ready": at(m["ready"]), "start": at(m["start"]),
+                         "reduced": at(m["reduced"]), "done": at(m["done"])})
+        rows.sort(key=lambda r: r["ready"])
+        self._marks = {}
+        busy = sum(r["done"] - r["start"] for r in rows)
+        return {"loss": float(loss.detach()), "forward_end": at(t_fwd), "backward_end": at(t_bwd), "step_end": at(t_end),
+                "exposed_ms": at(t_end) - at(t_bwd), "comm_busy_ms": busy,
+                "reduce_ms": sum(r["reduced"] - r["start"] for r in rows), "allgather_ms": sum(r["done"] - r["reduced"] for r in rows),
+                "queue_delay_ms_max": max((r["start"] - r["ready"] for r in rows), default=0.0), "buckets": rows}
 
     def gather_full_state(self) -> Dict[str, torch.Tensor]:
         """Checkpoint helper: this rank's optimizer shards plus the (replicated) bf16 parameters."""

@@ -508,15 +508,19 @@ def case_jit(eng, rank, world):
     total = torch.stack(xs).sum(0)
     for it in range(3):
         for name in [k for k in names if k.endswith("_ar")]:
+            res = x if ops[name].in_place else y                # the in-switch program reduces in place
             x.copy_(xs[rank] + it); y.fill_(-1.0)
             torch.cuda.synchronize(); dist.barrier()
             ops[name](x, y, width=2)
             torch.cuda.synchronize()
-            assert torch.allclose(y, total + it * world, rtol=1e-5, atol=1e-4), f"{name} launch {it}"
-            y.fill_(-1.0)
+            assert torch.allclose(res, total + it * world, rtol=1e-5, atol=1e-4), f"{name} launch {it}"
+            dist.barrier()
+            x.copy_(xs[rank] + it); y.fill_(-1.0)
+            torch.cuda.synchronize(); dist.barrier()
             eng.exeOp(name, x, y, width=2)                      # interpreter launch of the same program in between
             torch.cuda.synchronize()
-            assert torch.allclose(y, total + it * world, rtol=1e-5, atol=1e-4), f"{name} interpreted {it}"
+            assert torch.allclose(res, total + it * world, rtol=1e-5, atol=1e-4), f"{name} interpreted {it}"
+            dist.barrier()
         shard = torch.full((n // world,), -1.0, device="cuda")
         x.copy_(xs[rank] + it)
         torch.cuda.synchronize(); dist.barrier()

@@ -451,22 +451,27 @@ def test_fp8_quantisers_match_reference(native):
     assert (deq.view(256, 384) - w.float()).abs().max().item() <= 0.07 * w.float().abs().max().item()
 
 
-def test_grouped_gemm_matches_per_group_reference(native):
+@pytest.mark.parametrize("N,gelu", [(384, False), (512, False), (768, True)])
+def test_grouped_gemm_matches_per_group_reference(native, N, gelu):
+    """N = 384 takes the single-CTA row-major kernel; multiples of 256 take the CTA-pair kernel with the operands exchanged,
+    whose tiles end where a group's rows end (group sizes around and off the multiples of 16 and 256)."""
     from pccl_b200.ops import check_status
     from pccl_b200.ops.moe import grouped_gemm
     torch.manual_seed(4)
-    K, N = 512, 384
-    sizes = [130, 0, 257, 5, 128, 64]
+    K = 512
+    sizes = [130, 0, 257, 5, 128, 64, 513, 16, 300, 1]
     off = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
     total = int(off[-1])
     a = (torch.randn(total + 200, K, device="cuda") * 0.5).bfloat16()
     b = (torch.randn(len(sizes) * N, K, device="cuda") * 0.1).bfloat16()
     out = torch.full((total + 200, N), 7.0, device="cuda", dtype=torch.bfloat16)
-    grouped_gemm(a, b, off, N, out=out)
+    grouped_gemm(a, b, off, N, out=out, gelu=gelu)
     check_status("grouped gemm")
     for g, n in enumerate(sizes):
         lo = int(off[g])
         ref = a[lo:lo + n].float() @ b[g * N:(g + 1) * N].float().t()
+        if gelu:
+            ref = torch.nn.functional.gelu(ref, approximate="tanh")
         assert (out[lo:lo + n].float() - ref).abs().max().item() < 0.05 if n else True
     assert torch.all(out[total:] == 7.0)        # rows past the last group are untouched
 

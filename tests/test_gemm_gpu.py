@@ -189,6 +189,35 @@ def test_gemm_dgelu_epilogue_and_column_sums(b_t):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("shapes", [((512, 256), (256, 768)), ((304, 520), (1032, 136)), ((2048, 8192), (8192, 2048))])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_dual_two_weight_gradients_one_launch(shapes, out_dtype):
+    """Two dW = dy^T x products of one row count as a single launch, fresh and accumulating, against fp32 PyTorch."""
+    from pccl_b200.ops import check_status
+    from pccl_b200.ops.gemm import gemm_dual
+    rows = 1024
+    (m0, n0), (m1, n1) = shapes
+    dy0, x0 = _rand((rows, m0), 51, 0.1), _rand((rows, n0), 52)
+    dy1, x1 = _rand((rows, m1), 53, 0.1), _rand((rows, n1), 54)
+    o0 = torch.full((m0, n0), 3.0, dtype=out_dtype, device="cuda")
+    o1 = torch.full((m1, n1), -2.0, dtype=out_dtype, device="cuda")
+    gemm_dual(dy0, x0, o0, dy1, x1, o1, a_t=True, b_t=True, accumulate1=True)
+    check_status("gemm dual")
+    r0 = dy0.float().t() @ x0.float()
+    r1 = dy1.float().t() @ x1.float() - 2.0
+    for got, ref in ((o0, r0), (o1, r1)):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    # the plain (K-major) operand forms go through the same scheduler
+    a0, b0 = _rand((m0, 192), 55), _rand((n0, 192), 56)
+    a1, b1 = _rand((m1, 192), 57), _rand((n1, 192), 58)
+    p0 = torch.empty((m0, n0), dtype=out_dtype, device="cuda")
+    p1 = torch.empty((m1, n1), dtype=out_dtype, device="cuda")
+    gemm_dual(a0, b0, p0, a1, b1, p1)
+    check_status("gemm dual k-major")
+    for got, ref in ((p0, a0.float() @ b0.float().t()), (p1, a1.float() @ b1.float().t())):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
 @pytest.mark.parametrize("rows,N", [(16384, 2048), (1000, 520), (37, 8)])
 def test_colsum_kernel_matches_torch(rows, N):
     from pccl_b200.ops.elementwise import colsum

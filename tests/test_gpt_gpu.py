@@ -143,6 +143,35 @@ def test_fused_and_unfused_optimizer_paths_agree():
     assert (flats[0] == flats[1]).float().mean().item() > 0.9       # identical except where atomics order / bf16 rounding of a gradient differs
 
 
+def test_timed_step_reports_every_bucket_and_trains_like_train_step():
+    """The opt-in per-bucket timing takes the same step as train_step and returns ordered, non-negative spans."""
+    from pccl_b200.engine import Engine
+    from pccl_b200.models import GPT, GPTConfig
+    from pccl_b200.parallel import ShardedDataParallel
+    cfg = GPTConfig.tiny()
+    ids = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len), device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    flats = []
+    for timed in (False, True):
+        torch.manual_seed(0)
+        model = GPT(cfg, device="cuda")
+        eng = Engine(0, 1); eng.initEngine("cuda", heap_bytes=256 << 20)
+        dp = ShardedDataParallel(model, eng, lr=1e-3, bucket_mb=0.5)
+        dp.train_step(ids, ids.roll(-1, 1))
+        if timed:
+            rep = dp.timed_step(ids, ids.roll(-1, 1))
+            assert len(rep["buckets"]) == len(dp.buckets) and math.isfinite(rep["loss"])
+            assert 0 < rep["forward_end"] < rep["backward_end"] <= rep["step_end"]
+            for row in rep["buckets"]:
+                assert row["ready"] <= row["start"] + 1e-3 and row["start"] <= row["reduced"] <= row["done"] <= rep["step_end"] + 1e-3
+            assert rep["exposed_ms"] >= 0 and rep["comm_busy_ms"] > 0
+        else:
+            dp.train_step(ids, ids.roll(-1, 1))
+        torch.cuda.synchronize()
+        flats.append(dp.flat_params.float().clone())
+        del dp, model, eng
+    assert (flats[0] - flats[1]).abs().max().item() <= 2e-2 * flats[1].abs().max().item()
+
+
 def test_dp_checkpoint_resume_matches_uninterrupted_training(tmp_path):
     """torch.save of the sharded optimizer state and flat parameters after two steps, loaded into a differently
     initialised trainer, continues like the run that was never interrupted."""
