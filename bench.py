@@ -168,10 +168,14 @@ def main() -> None:
     sampler = ClockSampler(local).start()
     launches0 = launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = []
     e0.record()
     for i in range(args.steps):
         b = dev_batches[i % 2]
         loss = dp.train_step(b[:, :-1], b[:, 1:])
+        if args.bucket_timing:                 # one more event per step: the per-step series goes into dp_timing
+            marks.append(torch.cuda.Event(enable_timing=True))
+            marks[-1].record()
     e1.record()
     barrier()
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -202,6 +206,22 @@ def main() -> None:
     if args.bucket_timing:
         b = dev_batches[0]
         dp_timing = dp.timed_step(b[:, :-1], b[:, 1:])
+        again = dp.timed_step(b[:, :-1], b[:, 1:])          # directly behind the first: no idle gap before it
+        dp_timing["second_timed_step"] = {k: v for k, v in again.items() if k != "buckets"}
+        prev = e0
+        series = []
+        for m in marks:
+            series.append(prev.elapsed_time(m))
+            prev = m
+        dp_timing["step_ms_series"] = series
+        mine = {"rank": rank, "forward_ms": dp_timing["forward_end"], "backward_ms": dp_timing["backward_end"] - dp_timing["forward_end"],
+                "sm_mhz": clocks["sm_mhz"], "step_ms_mean": sum(series) / max(1, len(series))}
+        if world > 1:
+            every = [None] * world
+            dist.all_gather_object(every, mine)
+            dp_timing["ranks"] = every
+        else:
+            dp_timing["ranks"] = [mine]
         barrier()
     # ---- the library's headline metric and the PyTorch baseline, in the same launch -----------------------
     # The training state is released first: its buckets give the symmetric heap back to the 1 GB collectives,

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_rs_kernel(const __grid_co
 }
 
 // shared memory of the CTA-pair reduce-scatter kernel: five operand stages, barriers, 64 KiB of row staging
-constexpr int RS_PAIR_SMEM_BYTES = 5 * gemm2::STAGE_BYTES + 1024 + 256 + kRsRowStageBytes;
+constexpr int RS_PAIR_SMEM_BYTES = 5 * gemm2::STAGE_BYTES + 1024 + gemm2::BAR_BYTES + kRsRowStageBytes;
 static_assert(RS_PAIR_SMEM_BYTES <= 227 * 1024, "reduce-scatter pair kernel: shared memory");
 
 unsigned long long* g_probe = nullptr;

@@ -75,5 +75,8 @@ int launchQuantMx8Blocks(const void* w, void* q, uint8_t* scales, int rows, int 
 const char* gemmMx8LastError();
 
 const char* gemmLastError();
+// Tile scheduling of the CTA-pair kernels: 1 = tiles are handed out at run time (an atomic counter per stream), 0 = fixed
+// round-robin lists, -1 = what the environment says (PCCL_GEMM_DYNAMIC, default 1).
+void gemmSetDynamic(int mode);
 
 }  // namespace pccl

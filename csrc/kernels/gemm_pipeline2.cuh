@@ -26,18 +26,26 @@ constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KiB
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int EPI_SMEM_OFFSET = STAGES * STAGE_BYTES + 256;
+constexpr int BAR_BYTES = 512;     // barriers and the tile-index ring, between the operand ring and an epilogue's staging area
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+constexpr int EPI_SMEM_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;
 
+constexpr int SCHED_SLOTS = 4;     // tile indices in flight between the roles (dynamic scheduling)
 struct Barriers {
   uint64_t full[STAGES];        // used in the leader: both CTAs' loads of the stage have landed
   uint64_t empty[STAGES];       // per CTA: the MMAs that read this stage have retired
   uint64_t tmem_full[2];        // per CTA: accumulator ready
   uint64_t tmem_empty[2];       // used in the leader: both CTAs' epilogues have drained the accumulator
   uint64_t drain;
+  uint64_t sched_full[SCHED_SLOTS];    // per CTA: the slot holds the tile index of iteration it (it % SCHED_SLOTS)
+  uint64_t sched_empty[SCHED_SLOTS];   // used in the leader: every role of both CTAs has read the slot
+  uint64_t inbox_full[SCHED_SLOTS];    // used in the peer: the leader has stored the index into `inbox`
+  int32_t sched_tile[SCHED_SLOTS];     // per CTA: tile index, or -1 for "no more tiles"; written by this CTA's producer
+  int32_t inbox[SCHED_SLOTS];          // used in the peer: written by the leader's producer, read by the peer's producer
   uint32_t tmem_base;
   uint32_t abort;
 };
+static_assert(sizeof(Barriers) <= BAR_BYTES, "barriers overrun their area");
 
 // An epilogue may declare `static constexpr bool kVarN = true` and `int tile_n(const TileCoord&)`: the tile then spans only
 // that many of the BN accumulator columns (a multiple of 16).  The MMA is issued with that N -- each CTA contributes the
@@ -53,7 +61,14 @@ template <class E> struct HasVarN<E, std::void_t<decltype(E::kVarN)>> : std::tru
 // reduce-scatter epilogue stages whole 512-byte rows) gives up one stage for it.
 // NPROB > 1: `tmA` / `tmB` are arrays of that many descriptors and a tile's `extra` field says which pair it loads from --
 // several GEMMs with the same K walked as one tile list (fewer idle CTAs in the last wave than one launch per GEMM).
-template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES, int NPROB = 1>
+//
+// DYN: tiles are handed out at run time instead of round-robin.  `sched` then has `counter` (a zeroed word in global memory
+// that the launch leaves zeroed), `total` (tiles) and `at(index, &tile)`.  The leader's producer thread draws the next
+// index with an atomic add and publishes it through a four-slot ring in both CTAs' shared memory; the other roles (the
+// peer's producer, the MMA thread, the eight epilogue warps) read it from there, so all of them walk the same tile list in
+// the same order.  A CTA pair that starts late -- its SMs were still held by another kernel, a collective on a second
+// stream for instance -- then simply takes fewer tiles, where the round-robin list would make the whole GEMM wait for it.
+template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES, int NPROB = 1, bool DYN = false>
 __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* tmB, int K, const Sched& sched,
                                     const Gate& gate, Epi& epi, uint32_t* status) {
   static_assert(NSTAGES >= 2 && NSTAGES <= STAGES, "ring length");
@@ -76,6 +91,11 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       tc::mbar_init(&bar->tmem_empty[a], 8);      // four epilogue warps in each CTA of the pair
     }
     tc::mbar_init(&bar->drain, 1);
+    for (int q = 0; q < SCHED_SLOTS; ++q) {
+      tc::mbar_init(&bar->sched_full[q], 1);
+      tc::mbar_init(&bar->sched_empty[q], 10);    // MMA thread + peer's producer + four epilogue warps in each CTA
+      tc::mbar_init(&bar->inbox_full[q], 1);
+    }
     bar->abort = 0;
     tc::fence_barrier_init();
     for (int q = 0; q < NPROB; ++q) {
@@ -93,7 +113,29 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
-  epi.attach_smem(smem + NSTAGES * STAGE_BYTES + 256);
+  epi.attach_smem(smem + NSTAGES * STAGE_BYTES + BAR_BYTES);
+
+  // Tile of iteration `it` for a role that READS the ring (every role but the leader's producer).  `warp_wide`: all lanes
+  // of a warp call this together and lane 0 releases the slot.  Returns 1 (tile), 0 (end of the list) or -1 (gave up).
+  auto ring_tile = [&](int it, TileCoord* t, bool warp_wide) -> int {
+    if constexpr (DYN) {
+      const int q = it & (SCHED_SLOTS - 1);
+      if (!tc::mbar_wait(&bar->sched_full[q], (it / SCHED_SLOTS) & 1, abort)) return -1;     // published inside this CTA
+      const int32_t v = *reinterpret_cast<volatile int32_t*>(&bar->sched_tile[q]);
+      if (warp_wide) __syncwarp();
+      // the slot goes back to the leader; the zero that is added to the address is computed from the value read (in a
+      // form the compiler cannot fold), so the arrive cannot be issued before that read has returned
+      if (!warp_wide || lane == 0) {
+        uint32_t zero;
+        asm volatile("and.b32 %0, %1, 0;" : "=r"(zero) : "r"(v));
+        tc::mbar_arrive_cluster_relaxed(tc::mapa(tc::smem_u32(&bar->sched_empty[q]) + zero, 0));
+      }
+      if (v < 0) return 0;
+      return sched.at(v, t) ? 1 : 0;
+    } else {
+      return sched.get(it, t) ? 1 : 0;
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -102,7 +144,45 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       uint32_t phase = 0;
       bool ok = true;
       TileCoord t;
-      for (int it = 0; ok && sched.get(it, &t); ++it) {
+      // dynamic scheduling, leader: the index for the next iteration is drawn one iteration ahead, so the atomic's latency
+      // hides behind this tile's loads.  Every producer draws exactly one index past the end; whoever draws the very last
+      // one of the launch (total + pairs - 1) puts the counter back to zero for the next launch on this stream.
+      uint32_t drawn = 0;
+      const uint32_t n_pairs = gridDim.x >> 1;
+      if constexpr (DYN) {
+        if (leader) drawn = atomicAdd(sched.counter, 1u);
+      }
+      for (int it = 0; ok; ++it) {
+        if constexpr (DYN) {
+          if (leader) {
+            const int q = it & (SCHED_SLOTS - 1);
+            if (!tc::mbar_wait(&bar->sched_empty[q], ((it / SCHED_SLOTS) & 1) ^ 1, abort)) { ok = false; break; }   // no data comes with it
+            const uint32_t cur = drawn;        // drawn one iteration ago: nothing has waited for the atomic until here
+            if (cur == sched.total + n_pairs - 1) atomicExch(sched.counter, 0u);
+            const int32_t v = cur < sched.total ? static_cast<int32_t>(cur) : -1;
+            bar->sched_tile[q] = v;
+            tc::mbar_arrive(&bar->sched_full[q]);                                          // this CTA's readers
+            tc::st_shared_cluster_u32(tc::mapa(tc::smem_u32(&bar->inbox[q]), 1), static_cast<uint32_t>(v));
+            tc::mbar_arrive_cluster(tc::mapa(tc::smem_u32(&bar->inbox_full[q]), 1));     // the peer's producer
+            if (v < 0 || !sched.at(v, &t)) break;
+            drawn = atomicAdd(sched.counter, 1u);
+          } else {
+            // the peer's producer: index out of the inbox (cluster-scope acquire), into this CTA's slot for its epilogue warps
+            const int q = it & (SCHED_SLOTS - 1);
+            if (!tc::mbar_wait_cluster(&bar->inbox_full[q], (it / SCHED_SLOTS) & 1, abort)) { ok = false; break; }
+            const int32_t v = *reinterpret_cast<volatile int32_t*>(&bar->inbox[q]);
+            bar->sched_tile[q] = v;
+            tc::mbar_arrive(&bar->sched_full[q]);
+            {                                                                                 // the inbox slot may be written again
+              uint32_t zero;
+              asm volatile("and.b32 %0, %1, 0;" : "=r"(zero) : "r"(v));
+              tc::mbar_arrive_cluster_relaxed(tc::mapa(tc::smem_u32(&bar->sched_empty[q]) + zero, 0));
+            }
+            if (v < 0 || !sched.at(v, &t)) break;
+          }
+        } else {
+          if (!sched.get(it, &t)) break;
+        }
         if (!gate.wait(t, abort)) { ok = false; break; }
         const int row0 = epi.a_row0(t), col0 = epi.b_row0(t);        // already offset by this CTA's half
         const CUtensorMap* const tmA_t = NPROB > 1 ? tmA + t.extra : tmA;
@@ -148,7 +228,10 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       TileCoord t;
-      for (int it = 0; ok && sched.get(it, &t); ++it) {
+      for (int it = 0; ok; ++it) {
+        const int got = ring_tile(it, &t, false);
+        if (got < 0) ok = false;
+        if (got <= 0) break;
         if (!tc::mbar_wait(&bar->tmem_empty[acc], acc_phase ^ 1, abort)) { ok = false; break; }
         tc::tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
@@ -182,7 +265,10 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
     uint32_t acc_phase = 0;
     bool ok = true;
     TileCoord t;
-    for (int it = 0; ok && sched.get(it, &t); ++it) {
+    for (int it = 0; ok; ++it) {
+      const int got = ring_tile(it, &t, true);
+      if (got < 0) ok = false;
+      if (got <= 0) break;
       if (!tc::mbar_wait(&bar->tmem_full[acc], acc_phase, abort)) { ok = false; break; }
       tc::tc_fence_after();
       const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;

@@ -4,8 +4,11 @@
 // .gitmodules:4-9); this is the "computation" half of its "communication & computation" claim.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <map>
 #include <mutex>
 #include <string>
+#include <utility>
 
 #include "gemm_api.h"
 #include "gemm_epilogue.cuh"
@@ -29,17 +32,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ---- CTA-pair kernel ---------------------------------------------------------------------------------
-template <bool A_MN, bool B_MN, class Epi = StoreEpi>
+// GroupedSched's order, handed out tile by tile at run time (gemm2::run, DYN): `counter` is a zeroed word that belongs to
+// the launching stream.
+struct DynGroupedSched {
+  int tiles_m, tiles_n;
+  uint32_t* counter;
+  uint32_t total;
+  __device__ __forceinline__ bool at(int idx, TileCoord* t) const {
+    const int per_group = GroupedSched::GROUP_M * tiles_n;
+    const int g = idx / per_group, r = idx % per_group;
+    const int gm = min(GroupedSched::GROUP_M, tiles_m - g * GroupedSched::GROUP_M);
+    t->m = g * GroupedSched::GROUP_M + r % gm;
+    t->n = r / gm;
+    t->extra = 0;
+    return true;
+  }
+};
+
+template <bool A_MN, bool B_MN, class Epi = StoreEpi, bool DYN = false>
 __global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi epi, int K,
-                      uint32_t* status) {
-  GroupedSched sched{(epi.M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.N + gemm2::BN - 1) / gemm2::BN,
-                     static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
+                      uint32_t* status, uint32_t* counter) {
+  const int tiles_m = (epi.M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, tiles_n = (epi.N + gemm2::BN - 1) / gemm2::BN;
   NoGate gate;
   const int cta = static_cast<int>(tc::cluster_ctarank());
   gemm2::PairEpi<Epi> pe{epi, cta};
   gemm2::PairGate<NoGate> pg{gate, cta};
-  gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, pg, pe, status);
+  if constexpr (DYN) {
+    DynGroupedSched sched{tiles_m, tiles_n, counter, static_cast<uint32_t>(tiles_m * tiles_n)};
+    gemm2::run<A_MN, B_MN, DynGroupedSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<Epi>, gemm2::STAGES, 1, true>(&tmA, &tmB, K, sched, pg, pe, status);
+  } else {
+    GroupedSched sched{tiles_m, tiles_n, static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
+    gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, pg, pe, status);
+  }
 }
 
 // ---- two GEMMs with one K as one tile list ---------------------------------------------------------------------------
@@ -47,8 +72,10 @@ struct DualMaps { CUtensorMap a[2], b[2]; };
 
 struct DualSched {
   int tiles_m[2], tiles_n[2], first, stride;
-  __device__ __forceinline__ bool get(int it, TileCoord* t) const {
-    long long idx = first + static_cast<long long>(it) * stride;
+  uint32_t* counter;       // dynamic scheduling: see DynGroupedSched; null = round-robin
+  uint32_t total;
+  __device__ __forceinline__ bool get(int it, TileCoord* t) const { return at(first + static_cast<long long>(it) * stride, t); }
+  __device__ __forceinline__ bool at(long long idx, TileCoord* t) const {
     const long long n0 = static_cast<long long>(tiles_m[0]) * tiles_n[0];
     const int q = idx >= n0 ? 1 : 0;
     if (q) idx -= n0;
@@ -74,25 +101,86 @@ struct DualEpi {
   __device__ __forceinline__ void strip(const TileCoord& t, int row, int col, uint32_t* r) { e[t.extra].strip(t, row, col, r); }
 };
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool DYN>
 __global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
-gemm_bf16_pair_dual_kernel(const __grid_constant__ DualMaps maps, DualEpi epi, int K, uint32_t* status) {
+gemm_bf16_pair_dual_kernel(const __grid_constant__ DualMaps maps, DualEpi epi, int K, uint32_t* status, uint32_t* counter) {
   DualSched sched{{(epi.e[0].M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.e[1].M + gemm2::PAIR_M - 1) / gemm2::PAIR_M},
                   {(epi.e[0].N + gemm2::BN - 1) / gemm2::BN, (epi.e[1].N + gemm2::BN - 1) / gemm2::BN},
-                  static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
+                  static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1), counter, 0u};
+  sched.total = static_cast<uint32_t>(sched.tiles_m[0] * sched.tiles_n[0] + sched.tiles_m[1] * sched.tiles_n[1]);
   NoGate gate;
   const int cta = static_cast<int>(tc::cluster_ctarank());
   gemm2::PairEpi<DualEpi> pe{epi, cta};
   gemm2::PairGate<NoGate> pg{gate, cta};
-  gemm2::run<A_MN, B_MN, DualSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<DualEpi>, gemm2::STAGES, 2>(maps.a, maps.b, K, sched, pg, pe, status);
+  gemm2::run<A_MN, B_MN, DualSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<DualEpi>, gemm2::STAGES, 2, DYN>(maps.a, maps.b, K, sched, pg, pe, status);
 }
 
 thread_local std::string g_err;
 
+// The zeroed counter word that dynamic tile scheduling of launches on `stream` uses (kernels on one stream run one after
+// the other, and each leaves the word zeroed).  One 128-byte line per stream out of a pool made on first use; a null
+// pointer (pool used up, or PCCL_GEMM_DYNAMIC=0) selects the round-robin kernels.
+int g_dynamic = -1;      // -1: PCCL_GEMM_DYNAMIC decides (default on); 0 / 1: set by gemmSetDynamic
+
+uint32_t* tileCounterFor(cudaStream_t stream) {
+  static const bool env_off = std::getenv("PCCL_GEMM_DYNAMIC") && std::getenv("PCCL_GEMM_DYNAMIC")[0] == '0';
+  if (g_dynamic == 0 || (g_dynamic < 0 && env_off)) return nullptr;
+  constexpr int kPool = 64, kStride = 32;          // words
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, uint32_t*> by_stream;
+  static std::map<int, std::pair<uint32_t*, int>> pools;      // device -> (base, used)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = by_stream.find({dev, stream});
+  if (it != by_stream.end()) return it->second;
+  auto& pool = pools[dev];
+  if (!pool.first) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    uint32_t* base = nullptr;
+    if (cudaMalloc(&base, kPool * kStride * sizeof(uint32_t)) != cudaSuccess) return nullptr;
+    if (cudaMemset(base, 0, kPool * kStride * sizeof(uint32_t)) != cudaSuccess) return nullptr;
+    pool = {base, 0};
+  }
+  if (pool.second >= kPool) return nullptr;
+  uint32_t* p = pool.first + static_cast<size_t>(pool.second++) * kStride;
+  by_stream[{dev, stream}] = p;
+  return p;
+}
+
+template <class Kern>
+int setPairSmem(Kern kern, bool* done) {
+  if (*done) return 0;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  *done = true;
+  return 0;
+}
+
 template <bool A_MN, bool B_MN, class Epi = StoreEpi>
 int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, int K, int grid, uint32_t* status, cudaStream_t stream) {
-  static bool attr_set = false;
-  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, Epi>;
+  static bool attr_set = false, attr_set_dyn = false;
+  uint32_t* counter = tileCounterFor(stream);
+  if (counter) {
+    auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, Epi, true>;
+    if (int e = setPairSmem(kern, &attr_set_dyn)) return e;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(gemm2::NUM_THREADS);
+    cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int Kc = K;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, tb, epi, Kc, status, counter));
+  }
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, Epi, false>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -111,7 +199,7 @@ int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, int
   cfg.attrs = at;
   cfg.numAttrs = 1;
   int Kc = K;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, tb, epi, Kc, status));
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, tb, epi, Kc, status, static_cast<uint32_t*>(nullptr)));
 }
 
 template <bool A_MN, bool B_MN>
@@ -130,6 +218,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreEpi& epi, in
 }  // namespace
 
 const char* gemmLastError() { return g_err.c_str(); }
+
+void gemmSetDynamic(int mode) { g_dynamic = mode < 0 ? -1 : (mode ? 1 : 0); }
 
 int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
              uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status, cudaStream_t stream) {
@@ -225,14 +315,11 @@ int gemmBf16Dual(const GemmProblem& p0, const GemmProblem& p1, int K, uint32_t f
   int n_sm = deviceSmCount();
   if (sms > 0 && sms < n_sm) n_sm = sms;
   const int grid = 2 * static_cast<int>(tiles < n_sm / 2 ? tiles : n_sm / 2);
-  static bool attr_set[4] = {false, false, false, false};      // per kernel: the four instantiations share one function type
-  bool& attr = attr_set[(a_mn ? 2 : 0) | (b_mn ? 1 : 0)];
+  static bool attr_set[8] = {false, false, false, false, false, false, false, false};   // per kernel: the instantiations share one function type
+  uint32_t* counter = tileCounterFor(stream);
+  bool& attr = attr_set[(counter ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0)];
   auto go = [&](auto kern) {
-    if (!attr) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      attr = true;
-    }
+    if (int e = setPairSmem(kern, &attr)) return e;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(gemm2::NUM_THREADS);
@@ -246,10 +333,14 @@ int gemmBf16Dual(const GemmProblem& p0, const GemmProblem& p1, int K, uint32_t f
     cfg.attrs = at;
     cfg.numAttrs = 1;
     int Kc = K;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, maps, epi, Kc, status));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, maps, epi, Kc, status, counter));
   };
-  if (a_mn) return b_mn ? go(gemm_bf16_pair_dual_kernel<true, true>) : go(gemm_bf16_pair_dual_kernel<true, false>);
-  return b_mn ? go(gemm_bf16_pair_dual_kernel<false, true>) : go(gemm_bf16_pair_dual_kernel<false, false>);
+  if (counter) {
+    if (a_mn) return b_mn ? go(gemm_bf16_pair_dual_kernel<true, true, true>) : go(gemm_bf16_pair_dual_kernel<true, false, true>);
+    return b_mn ? go(gemm_bf16_pair_dual_kernel<false, true, true>) : go(gemm_bf16_pair_dual_kernel<false, false, true>);
+  }
+  if (a_mn) return b_mn ? go(gemm_bf16_pair_dual_kernel<true, true, false>) : go(gemm_bf16_pair_dual_kernel<true, false, false>);
+  return b_mn ? go(gemm_bf16_pair_dual_kernel<false, true, false>) : go(gemm_bf16_pair_dual_kernel<false, false, false>);
 }
 
 }  // namespace pccl

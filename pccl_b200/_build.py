@@ -33,6 +33,8 @@ def _flags():
     cxx = ["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function"] + inc
     nv = [NVCC, "-std=c++17", "-O3", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC",
           "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"] + ARCH_FLAGS + inc
+    for d in filter(None, os.environ.get("PCCL_NVCC_DEFINES", "").split(",")):       # e.g. PCCL_NVCC_DEFINES=NAME=1,OTHER
+        nv.append(f"-D{d}")
     if os.environ.get("PCCL_DEBUG", "0") not in ("", "0"):       # the reference's debug build (setup.py:78-81): PCCL_DLOG_* become real
         cxx.append("-DPCCL_DEBUG")
         nv.append("-DPCCL_DEBUG")

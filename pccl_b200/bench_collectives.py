@@ -66,6 +66,9 @@ def interp_programs(eng: Engine, kind: str) -> List[str]:
         names.append(f"bench_nvls_{kind}")
     eng.regOp(f"bench_direct_{kind}", build(f"direct_{lang_kind}", eng.world, channels=2))
     names.append(f"bench_direct_{kind}")
+    # the same exchange on symmetric buffers: peers' inputs are read (outputs written) in place, nothing is staged
+    eng.regOp(f"bench_pull_{kind}", build(f"direct_{lang_kind}", eng.world, channels=2, direct=True))
+    names.append(f"bench_pull_{kind}")
     res = synthesize(lang_kind, Topology.nvswitch(eng.world), 16 << 20, chunks=1, time_limit=10.0)
     eng.regOp(f"bench_milp_{kind}", res.ir)
     names.append(f"bench_milp_{kind}")
@@ -99,7 +102,7 @@ def bench_size(eng: Engine, kind: str, dtype: torch.dtype, nbytes: int, impls: L
             # best program and width (runtime CTA budget) for this size
             best = None
             for name in interp_programs(eng, kind):
-                if nbytes > (64 << 20) and "nvls" not in name:      # the direct forms stage through the workspace
+                if nbytes > (64 << 20) and "nvls" not in name and "pull" not in name:   # the staged forms need that much workspace
                     continue
                 for width in ((4, 16, 32) if nbytes <= (64 << 20) else (32,)):
                     if kind == "allreduce":

@@ -183,14 +183,18 @@ def direct_reduce_scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA
                           redop: str = "sum", direct: bool = False) -> CollectiveIR:
     """Every rank sends shard d to rank d in one step; d folds the n contributions.
 
-    ``direct=True`` is the pull form: rank d reads its shard straight out of every peer's
-    (symmetric) input and reduces in registers; no scratch traffic."""
+    ``direct=True`` is the pull form for symmetric inputs: rank d reads its shard straight out of every peer's input and
+    reduces in registers; no scratch traffic.  A barrier before the reads says that every input is complete, one after
+    them that every peer has finished reading this rank's input (which the caller may then overwrite)."""
     sh = channels
     ir = _new(f"direct_reduce_scatter_n{n}_c{channels}{'_pull' if direct else ''}", "reduce_scatter",
               n, n * sh, {"input": n * sh, "output": sh, "scratch": 0 if direct else n * sh},
               device_type, redop, block_units=sh)
     reduce_scatter_conditions(ir, n, sh)
     for ch in range(channels):
+        bars = ([ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, metadata={"step": 0, "channel": ch})
+                 for r in range(n)] if direct else [])
+        last = []
         for d in range(n):
             acc = ir.copy(Chunk({d}, d, 1, d * sh + ch, "input"),
                           Chunk({d}, d, 1, ch, "output", origin=d * sh + ch), step=0, channel=ch)
@@ -200,7 +204,7 @@ def direct_reduce_scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA
                 if direct:
                     acc = ir.reduce(Chunk({r}, r, 1, d * sh + ch, "input"),
                                     Chunk(have | {r}, d, 1, ch, "output", origin=d * sh + ch),
-                                    deps=[acc], step=k, channel=ch, executor=d)
+                                    deps=[acc] + (bars if k == 1 else []), step=k, channel=ch, executor=d)
                 else:
                     push = ir.copy(Chunk({r}, r, 1, d * sh + ch, "input"),
                                    Chunk({r}, d, 1, r * sh + ch, "scratch", origin=d * sh + ch),
@@ -209,17 +213,26 @@ def direct_reduce_scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA
                                     Chunk(have | {r}, d, 1, ch, "output", origin=d * sh + ch),
                                     deps=[acc, push], step=k, channel=ch)
                 have = have | {r}
+            last.append(acc)
+        if direct:
+            for r in range(n):
+                ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, last, {"step": n, "channel": ch})
     return ir
 
 
 def direct_allgather(n: int, channels: int = 1, device_type=DeviceType.CUDA,
                      direct: bool = False) -> CollectiveIR:
+    """``direct=True``: for symmetric outputs every rank stores its shard straight into each peer's output, between a
+    barrier that says the outputs may be written and one that says every store has landed."""
     sh = channels
     ir = _new(f"direct_allgather_n{n}_c{channels}{'_sym' if direct else ''}", "allgather", n, sh,
               {"input": sh, "output": n * sh, "scratch": 0 if direct else n * sh}, device_type,
               block_units=sh)
     allgather_conditions(ir, n, sh)
     for ch in range(channels):
+        bars = ([ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, metadata={"step": 0, "channel": ch})
+                 for r in range(n)] if direct else [])
+        stores = []
         for r in range(n):
             org = r * sh + ch
             src = Chunk({r}, r, 1, ch, "input", origin=org)
@@ -227,11 +240,14 @@ def direct_allgather(n: int, channels: int = 1, device_type=DeviceType.CUDA,
             for k in range(1, n):
                 d = (r + k) % n
                 if direct:
-                    ir.copy(src, Chunk({r}, d, 1, org, "output", origin=org), step=0, channel=ch)
+                    stores.append(ir.copy(src, Chunk({r}, d, 1, org, "output", origin=org), deps=bars, step=1, channel=ch))
                 else:
                     push = ir.copy(src, Chunk({r}, d, 1, org, "scratch", origin=org), step=0, channel=ch)
                     ir.copy(Chunk({r}, d, 1, org, "scratch", origin=org),
                             Chunk({r}, d, 1, org, "output", origin=org), deps=[push], step=1, channel=ch)
+        if direct:
+            for r in range(n):
+                ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, stores, {"step": 2, "channel": ch})
     return ir
 
 
@@ -241,35 +257,49 @@ def direct_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, red
 
     Scratch is n+1 images of the vector: image r receives rank r's contribution (each unit keeps its
     position inside the image, so source and target slices have the same length whatever the
-    message size), image n receives the gathered results."""
+    message size), image n receives the gathered results.
+
+    ``direct=True`` is the form for symmetric inputs and outputs, with no scratch at all: rank d reduces its slice
+    straight out of every peer's input into its own output and stores the result into every peer's output, between an
+    entry barrier (inputs complete, outputs free) and an exit barrier (every store has landed, every read is over)."""
     sh = channels
     U = n * sh
-    ir = _new(f"direct_allreduce_n{n}_c{channels}", "allreduce", n, U,
-              {"input": U, "output": U, "scratch": (n + 1) * U}, device_type, redop)
+    ir = _new(f"direct_allreduce_n{n}_c{channels}{'_pull' if direct else ''}", "allreduce", n, U,
+              {"input": U, "output": U, "scratch": 0 if direct else (n + 1) * U}, device_type, redop)
     allreduce_conditions(ir, n, U)
     for ch in range(channels):
+        bars = ([ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, metadata={"step": 0, "channel": ch})
+                 for r in range(n)] if direct else [])
+        stores = []
         for d in range(n):
             u = d * sh + ch
             acc = ir.copy(Chunk({d}, d, 1, u, "input"), Chunk({d}, d, 1, u, "output"), step=0, channel=ch)
             have = {d}
             for k in range(1, n):
                 r = (d + k) % n
-                push = ir.copy(Chunk({r}, r, 1, u, "input"),
-                               Chunk({r}, d, 1, r * U + u, "scratch", origin=u), step=0, channel=ch)
-                acc = ir.reduce(Chunk({r}, d, 1, r * U + u, "scratch", origin=u),
-                                Chunk(have | {r}, d, 1, u, "output"), deps=[acc, push], step=k, channel=ch)
+                if direct:
+                    acc = ir.reduce(Chunk({r}, r, 1, u, "input"), Chunk(have | {r}, d, 1, u, "output"),
+                                    deps=[acc] + (bars if k == 1 else []), step=k, channel=ch, executor=d)
+                else:
+                    push = ir.copy(Chunk({r}, r, 1, u, "input"),
+                                   Chunk({r}, d, 1, r * U + u, "scratch", origin=u), step=0, channel=ch)
+                    acc = ir.reduce(Chunk({r}, d, 1, r * U + u, "scratch", origin=u),
+                                    Chunk(have | {r}, d, 1, u, "output"), deps=[acc, push], step=k, channel=ch)
                 have = have | {r}
             for k in range(1, n):
                 t = (d + k) % n
                 if direct:
-                    ir.copy(Chunk(_all(n), d, 1, u, "output"), Chunk(_all(n), t, 1, u, "output"),
-                            deps=[acc], step=n, channel=ch)
+                    stores.append(ir.copy(Chunk(_all(n), d, 1, u, "output"), Chunk(_all(n), t, 1, u, "output"),
+                                          deps=[acc], step=n, channel=ch))
                 else:
                     push = ir.copy(Chunk(_all(n), d, 1, u, "output"),
                                    Chunk(_all(n), t, 1, n * U + u, "scratch", origin=u),
                                    deps=[acc], step=n, channel=ch)
                     ir.copy(Chunk(_all(n), t, 1, n * U + u, "scratch", origin=u),
                             Chunk(_all(n), t, 1, u, "output"), deps=[push], step=n + 1, channel=ch)
+        if direct:
+            for r in range(n):
+                ir.create_operation(PrimitiveOpType.BARRIER, None, None, r, r, stores, {"step": n + 1, "channel": ch})
     return ir
 
 

@@ -51,7 +51,8 @@ def all_reduce(eng: Engine, inp: torch.Tensor, out: Optional[torch.Tensor] = Non
     a = _algo(eng, algo, dt, op, nbytes)
     s = (stream or torch.cuda.current_stream()).cuda_stream
     C.collective(eng.raw, "allreduce", a, dt, op, eng.heap_offset(inp), eng.heap_offset(out), inp.numel(), lane, 1.0, "",
-                 _blocks(nbytes if (nbytes <= (256 << 10) and out is not inp) else nbytes // eng.world, blocks), threads, s, 0, 0, 0)
+                 _blocks(nbytes if (nbytes <= ((64 << 10) if a == "nvls" else (256 << 10)) and out is not inp) else nbytes // eng.world, blocks),
+                 threads, s, 0, 0, 0)
     count_launch()
     return out
 

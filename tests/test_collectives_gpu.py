@@ -178,6 +178,38 @@ def test_interpreter_runs_lowered_programs(native, algo, world, width):
             assert (ys[r] - ref).abs().max().item() < 1e-4, (algo, r)
 
 
+@pytest.mark.parametrize("algo", ["direct_allreduce", "direct_reduce_scatter", "direct_allgather"])
+@pytest.mark.parametrize("world,width", [(2, 1), (4, 2), (8, 2)])
+def test_interpreter_runs_pull_forms_on_symmetric_buffers(native, algo, world, width):
+    """``direct=True``: peers' inputs are read and peers' outputs written in place (same heap offset on every rank), no
+    scratch; three launches in a row with changing inputs, so a rank that ran ahead of the barriers would be seen."""
+    from pccl_b200.lang import build, to_schedule
+    ir = build(algo, world, channels=2, direct=True)
+    assert ir.buffers["scratch"] == 0
+    doc = json.dumps(to_schedule(ir))
+    n = 2048 + 8
+    coll = ir.collective
+    n_in = {"allreduce": n, "reduce_scatter": n * world, "allgather": n}[coll]
+    n_out = {"allreduce": n, "reduce_scatter": n, "allgather": n * world}[coll]
+    hs, st = _heaps(world, 4 << 20)
+    in_off, out_off = DATA_OFF + (1 << 20), DATA_OFF + (2 << 20)
+    g = torch.Generator(device="cuda").manual_seed(14)
+    for epoch in range(3):
+        xs = [torch.randn(n_in, generator=g, device="cuda") for _ in range(world)]
+        for r in range(world):
+            _view(hs[r], in_off - DATA_OFF, n_in, torch.float32).copy_(xs[r])
+            _view(hs[r], out_off - DATA_OFF, n_out, torch.float32).fill_(-5.0)
+        native.emu_program(doc, [h.data_ptr() for h in hs], SIGNAL_OFF, [h.data_ptr() + in_off for h in hs],
+                           [h.data_ptr() + out_off for h in hs], n_in * 4, "f32", width, DATA_OFF, 0, epoch,
+                           0, [s.data_ptr() for s in st], [], torch.cuda.current_stream().cuda_stream)
+        assert all(s[0].item() == 0 for s in st), [s.tolist() for s in st]
+        full = torch.stack(xs)
+        for r in range(world):
+            got = _view(hs[r], out_off - DATA_OFF, n_out, torch.float32)
+            ref = full.sum(0) if coll == "allreduce" else (full.sum(0)[r * n:(r + 1) * n] if coll == "reduce_scatter" else torch.cat(xs))
+            assert (got - ref).abs().max().item() < 1e-4, (algo, r, epoch)
+
+
 def test_bounded_wait_returns_timeout_status(native):
     """A wait on a flag nobody sets comes back with ST_TIMEOUT; the context stays usable."""
     flag = torch.zeros(1, dtype=torch.int64, device="cuda")
