@@ -41,12 +41,12 @@ __device__ __forceinline__ void interp_body(const LaunchT& L, const InterpRank& 
   const int me = R.rank;
   uint64_t* const sig0 = reinterpret_cast<uint64_t*>(W.heap[me] + W.signal_off);
   uint64_t* my_sig = sig0 + L.slot_base;
-  if (turns && L.launch_no >= 2) {
-    // nobody may still be using the scratch half of launch_no - 2 when this launch starts to write it
-    if (threadIdx.x == 0) {
-      for (int q = 0; q < W.world; ++q)
-        if (q != me && !wait_ge(sig0 + L.turn_slot + q, L.launch_no - 1, L.spin_limit, R.status)) { s_fail = ST_TIMEOUT; break; }
-    }
+  if (turns && L.launch_no >= 2 && R.buf_bytes[BUF_SCRATCH] != 0) {
+    // nobody may still be using the scratch half of launch_no - 2 when this launch starts to write it (a launch that
+    // moves nothing through scratch has nothing to wait for); one thread per peer, so the checks overlap
+    if (threadIdx.x < static_cast<uint32_t>(W.world) && static_cast<int>(threadIdx.x) != me &&
+        !wait_ge(sig0 + L.turn_slot + threadIdx.x, L.launch_no - 1, L.spin_limit, R.status))
+      s_fail = ST_TIMEOUT;
     __syncthreads();
     if (s_fail) {
       if (threadIdx.x == 0) report(R.status, ST_TIMEOUT, static_cast<uint32_t>(stream), 0xffffu, OP_WAIT);
@@ -238,15 +238,17 @@ __device__ __forceinline__ void interp_body(const LaunchT& L, const InterpRank& 
   }
   if (turns) {
     // the last stream of this rank to end tells every peer that the rank has left this launch's scratch half
+    // (one thread per peer: the releases go out together instead of one behind the other)
+    __shared__ uint32_t s_last;
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence_system();
       unsigned int* fin = reinterpret_cast<unsigned int*>(sig0 + L.finish_slot);
-      if (atomicInc(fin, static_cast<unsigned int>(n_workers - 1)) == static_cast<unsigned int>(n_workers - 1)) {
-        for (int q = 0; q < W.world; ++q)
-          if (q != me) red_add_release_sys(reinterpret_cast<uint64_t*>(W.heap[q] + W.signal_off) + L.turn_slot + me, 1);
-      }
+      s_last = atomicInc(fin, static_cast<unsigned int>(n_workers - 1)) == static_cast<unsigned int>(n_workers - 1) ? 1u : 0u;
     }
+    __syncthreads();
+    if (s_last && threadIdx.x < static_cast<uint32_t>(W.world) && static_cast<int>(threadIdx.x) != me)
+      red_add_release_sys(reinterpret_cast<uint64_t*>(W.heap[threadIdx.x] + W.signal_off) + L.turn_slot + me, 1);
   }
 }
 

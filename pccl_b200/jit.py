@@ -86,6 +86,8 @@ def generate(streams: List[List[Tuple]], rank: int, world: int, dtype: str, redo
         raise PcclError(f"jit: no generated form for dtype {dtype!r} / reduction {redop!r} (use exeOp)")
     DT, RED = _DT[dtype], _RED[redop]
     n_workers = max(1, len(streams))
+    uses_scratch = any(ins[0] != OP["END"] and BUF_SCRATCH in (ins[3], ins[4]) and ins[0] in (OP["COPY"], OP["REDUCE"], OP["MM_LD_REDUCE"], OP["MM_ST"])
+                       for prog in streams for ins in prog)
     out = [_PROLOGUE, f'extern "C" __global__ void __launch_bounds__(512) {name}(const JitArgs a) {{',
            "  __shared__ unsigned int s_fail;",
            f"  const int me = {rank};",
@@ -95,10 +97,10 @@ def generate(streams: List[List[Tuple]], rank: int, world: int, dtype: str, redo
            "  unsigned long long* const sig0 = reinterpret_cast<unsigned long long*>(a.heap[me] + a.signal_off);",
            "  unsigned long long* const my_sig = sig0 + a.slot_base;",
            "  const bool turns = a.turn_slot != 0xffffffffu;",
-           "  if (turns && a.launch_no >= 2) {",
-           "    if (threadIdx.x == 0)",
-           f"      for (int q = 0; q < {world}; ++q)",
-           "        if (q != me && !wait_ge(sig0 + a.turn_slot + q, a.launch_no - 1, a.spin_limit, a.status)) { s_fail = ST_TIMEOUT; break; }",
+           # a program that moves nothing through scratch has no scratch half to wait for; one thread per peer otherwise
+           f"  if (turns && a.launch_no >= 2 && {'true' if uses_scratch else 'false'}) {{",
+           f"    if (threadIdx.x < {world}u && threadIdx.x != {rank}u && !wait_ge(sig0 + a.turn_slot + threadIdx.x, a.launch_no - 1, a.spin_limit, a.status))",
+           "      s_fail = ST_TIMEOUT;",
            "    __syncthreads();",
            "    if (s_fail) { if (threadIdx.x == 0) report(a.status, ST_TIMEOUT, blockIdx.x, 0xffffu, OP_WAIT); return; }",
            "  }",
@@ -193,14 +195,17 @@ def generate(streams: List[List[Tuple]], rank: int, world: int, dtype: str, redo
         out.append("    } break;")
     out += ["    default: break;", "  }",
             "  if (turns) {",
+            "    __shared__ unsigned int s_last;",
             "    __syncthreads();",
             "    if (threadIdx.x == 0) {",
             "      __threadfence_system();",
             "      unsigned int* fin = reinterpret_cast<unsigned int*>(sig0 + a.finish_slot);",
-            f"      if (atomicInc(fin, {n_workers - 1}u) == {n_workers - 1}u)",
-            f"        for (int q = 0; q < {world}; ++q)",
-            "          if (q != me) red_add_release_sys(reinterpret_cast<uint64_t*>(a.heap[q] + a.signal_off) + a.turn_slot + me, 1);",
-            "    }", "  }", "}"]
+            f"      s_last = atomicInc(fin, {n_workers - 1}u) == {n_workers - 1}u ? 1u : 0u;",
+            "    }",
+            "    __syncthreads();",
+            f"    if (s_last && threadIdx.x < {world}u && threadIdx.x != {rank}u)",
+            "      red_add_release_sys(reinterpret_cast<uint64_t*>(a.heap[threadIdx.x] + a.signal_off) + a.turn_slot + me, 1);",
+            "  }", "}"]
     return "\n".join(out)
 
 
