@@ -117,6 +117,9 @@ void registerBuiltinOptions() {
   L::registerOpt("PCCL_AG_TAIL", "all-gather GEMM: tiles left to the copy CTAs once their rows are sent (default -1: from a cost model; 0: none)");
   L::registerOpt("PCCL_EXEC_DELAY_US", "testing aid: the CPU executor of rank PCCL_EXEC_DELAY_RANK sleeps this long before every instruction");
   L::registerOpt("PCCL_EXEC_DELAY_RANK", "testing aid: the rank that PCCL_EXEC_DELAY_US slows down (default none)");
+  L::registerOpt("PCCL_HANDLE_TYPE", "fabric: also export GPU heap allocations as fabric handles inside the handle document (needs an IMEX channel; falls back to POSIX descriptors)");
+  L::registerOpt("PCCL_GEMM_DYNAMIC", "0: the CTA-pair GEMM kernels walk fixed round-robin tile lists instead of drawing tiles at run time");
+  L::registerOpt("PCCL_GROUPED_RAGGED", "0: the grouped GEMM keeps rows on the M side of the tile even when the output features are a multiple of 256");
   L::registerOpt("PCCL_CUDA_DRIVER_LIB", "library to load the CUDA driver API from (default libcuda.so.1; tests name a stand-in)");
   L::registerOpt("PCCL_CHANNELS", "default channel count of schedules generated by pccl.lang.build (default 1)");
   L::registerOpt("PCCL_SPIN_LIMIT", "bounded-wait budget of device-side waits, in nanoseconds (default 2e9)");

@@ -110,12 +110,22 @@ CUdevice currentDevice() {
   return dev;
 }
 
-CUmemAllocationProp allocProp(CUdevice dev) {
+// PCCL_HANDLE_TYPE=fabric asks for allocations that can ALSO be exported as fabric handles (64 opaque bytes that travel
+// in the handle document itself and are valid across the hosts of one NVLink domain, where a file descriptor is not);
+// the reference exports them whenever the platform has them (csrc/plugins/cuda_executor/device.cc:105-112, 156-196).
+// Where the driver refuses such an allocation (no IMEX channel: any single NVSwitch box) the POSIX descriptor alone is used.
+bool wantFabric() {
+  const char* v = std::getenv("PCCL_HANDLE_TYPE");
+  return v && std::string(v) == "fabric";
+}
+
+CUmemAllocationProp allocProp(CUdevice dev, bool fabric = false) {
   CUmemAllocationProp p{};
   p.type = CU_MEM_ALLOCATION_TYPE_PINNED;
   p.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
   p.location.id = dev;
-  p.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  p.requestedHandleTypes = static_cast<CUmemAllocationHandleType>(
+      CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR | (fabric ? CU_MEM_HANDLE_TYPE_FABRIC : 0));
   return p;
 }
 
@@ -200,16 +210,32 @@ void* CudaDevice::allocateIpcBuffer(size_t bytes, std::string* handle) {
   if (gran < (2u << 20)) gran = 2u << 20;
   size_t size = alignUp(bytes, gran);
   Alloc a;
-  check(drv().MemCreate(&a.handle, size, &prop, 0), "cuMemCreate");
+  bool fabric = wantFabric();
+  if (fabric) {
+    CUmemAllocationProp fprop = allocProp(dev, true);
+    if (drv().MemCreate(&a.handle, size, &fprop, 0) != CUDA_SUCCESS) {
+      PCCL_LOG_WARN("cuda device: the driver refused an allocation with fabric handles; using POSIX descriptors only");
+      fabric = false;
+    }
+  }
+  if (!fabric) check(drv().MemCreate(&a.handle, size, &prop, 0), "cuMemCreate");
   a.bytes = size;
   a.id = next_id_.fetch_add(1);
   void* ptr = nullptr;
+  std::string fabric_hex;
   try {
     ptr = mapHandle(a.handle, size);
     int fd = -1;
     check(drv().MemExportToShareableHandle(&fd, a.handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
           "cuMemExportToShareableHandle");
     a.fd = fd;
+    if (fabric) {
+      CUmemFabricHandle fh{};
+      if (drv().MemExportToShareableHandle(&fh, a.handle, CU_MEM_HANDLE_TYPE_FABRIC, 0) == CUDA_SUCCESS)
+        fabric_hex = encodeHex(fh.data, sizeof(fh.data));
+      else
+        PCCL_LOG_WARN("cuda device: exporting the fabric handle failed; peers will use the POSIX descriptor");
+    }
   } catch (...) {
     if (ptr) {
       drv().MemUnmap(reinterpret_cast<CUdeviceptr>(ptr), size);
@@ -231,6 +257,7 @@ void* CudaDevice::allocateIpcBuffer(size_t bytes, std::string* handle) {
   h.set("sock", sock_name_);
   h.set("token", token_);
   h.set("device", static_cast<int>(dev));
+  if (!fabric_hex.empty()) h.set("fabric", fabric_hex);
   if (handle) *handle = h.dump();
   return ptr;
 }
@@ -324,12 +351,24 @@ void* CudaDevice::mapBuffer(const std::string& handle) {
   Json h = Json::parse(handle);
   size_t size = static_cast<size_t>(h["size"].asInt());
   uint64_t id = static_cast<uint64_t>(h["id"].asInt());
-  int fd = fetchFd(h["sock"].asString(), id, h["token"].asString());
   Alloc a;
-  CUresult r = drv().MemImportFromShareableHandle(&a.handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
-                                                  CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
-  ::close(fd);
-  check(r, "cuMemImportFromShareableHandle");
+  bool imported = false;
+  if (wantFabric() && h.contains("fabric")) {
+    // the 64 bytes came with the document: no descriptor to fetch, and the owner may be on another host of the domain
+    CUmemFabricHandle fh{};
+    if (decodeHex(fh.data, sizeof(fh.data), h["fabric"].asString()) &&
+        drv().MemImportFromShareableHandle(&a.handle, &fh, CU_MEM_HANDLE_TYPE_FABRIC) == CUDA_SUCCESS)
+      imported = true;
+    else
+      PCCL_LOG_WARN("cuda device: importing the fabric handle failed; asking the owner for a POSIX descriptor");
+  }
+  if (!imported) {
+    int fd = fetchFd(h["sock"].asString(), id, h["token"].asString());
+    CUresult r = drv().MemImportFromShareableHandle(&a.handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                                    CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+    ::close(fd);
+    check(r, "cuMemImportFromShareableHandle");
+  }
   a.bytes = size;
   a.imported = true;
   void* ptr = nullptr;

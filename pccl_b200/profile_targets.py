@@ -163,7 +163,7 @@ def train_kernels(a):
     """The fused kernels of the training step at the GPT-1.3B shapes (16384 tokens, d = 2048, d_ff = 8192)."""
     from .nn.norm import _ln_backward, _ln_forward
     from .ops.elementwise import colsum
-    from .ops.gemm import gemm, gemm_dgelu
+    from .ops.gemm import gemm, gemm_dgelu, gemm_dual
     T, D, H = 16384, 2048, 8192
     r = lambda *s: torch.randn(*s, device="cuda").bfloat16()  # noqa: E731
     dz, w2, pre = r(T, D), r(D, H) * 0.02, r(T, H)
@@ -171,6 +171,12 @@ def train_kernels(a):
     sums = torch.zeros(H, device="cuda")
     print({"op": "gemm_dgelu_colsum", "M": T, "N": H, "K": D, "us": _timed(lambda: gemm_dgelu(dz, w2, pre, b_t=True, colsum=sums, out=out), a.iters)})
     print({"op": "gemm_plain_same_shape", "us": _timed(lambda: gemm(dz, w2, b_t=True, out=out), a.iters)})
+    act, xin, dy1 = r(T, H), r(T, D), r(T, H)
+    dw1, dw2 = torch.empty(H, D, device="cuda", dtype=torch.bfloat16), torch.empty(D, H, device="cuda", dtype=torch.bfloat16)
+    print({"op": "gemm_dual_two_weight_gradients", "K": T, "shapes": [[H, D], [D, H]],
+           "us": _timed(lambda: gemm_dual(dy1, xin, dw1, dz, act, dw2, a_t=True, b_t=True), a.iters)})
+    print({"op": "gemm_weight_gradients_two_launches",
+           "us": _timed(lambda: (gemm(dy1, xin, a_t=True, b_t=True, out=dw1), gemm(dz, act, a_t=True, b_t=True, out=dw2)), a.iters)})
     x, delta, g = r(T, D), r(T, D), r(T, D)
     gamma, beta = torch.ones(D, device="cuda", dtype=torch.bfloat16), torch.zeros(D, device="cuda", dtype=torch.bfloat16)
     s, _, mean, rstd = _ln_forward(x, delta, gamma, beta, 1e-5)
@@ -183,11 +189,18 @@ def train_kernels(a):
 
 
 def grouped_gemm(a):
-    """Expert FFN of the MoE layer: 32 experts, rows spread unevenly, 7168 -> 2048 (GELU) -> 7168."""
+    """Expert FFN of the MoE layer: 32 experts, 7168 -> 2048 (GELU) -> 7168; rows spread unevenly, or (--balanced) the way a
+    router with many tokens spreads them: the mean per expert give or take a few per cent."""
     from .ops.moe import grouped_gemm as gg
     E, H, Fd, rows = 32, a.hidden, 2048, a.tokens
-    cuts = torch.sort(torch.randint(0, rows, (E - 1,), device="cuda")).values
-    row_off = torch.cat([torch.zeros(1, device="cuda", dtype=torch.long), cuts, torch.tensor([rows], device="cuda")]).to(torch.int32)
+    if a.balanced:
+        sizes = (torch.randn(E) * 0.04 * rows / E + rows / E).round().clamp(min=1).long()
+        sizes[-1] = max(1, rows - int(sizes[:-1].sum()))
+        row_off = torch.cat([torch.zeros(1, dtype=torch.long), sizes.cumsum(0)]).to(torch.int32).cuda()
+        rows = int(row_off[-1])
+    else:
+        cuts = torch.sort(torch.randint(0, rows, (E - 1,), device="cuda")).values
+        row_off = torch.cat([torch.zeros(1, device="cuda", dtype=torch.long), cuts, torch.tensor([rows], device="cuda")]).to(torch.int32)
     x = torch.randn(rows, H, device="cuda").bfloat16()
     w1 = (torch.randn(E * Fd, H, device="cuda") * 0.02).bfloat16()
     w2 = (torch.randn(E * H, Fd, device="cuda") * 0.02).bfloat16()
@@ -211,6 +224,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--balanced", action="store_true", help="grouped_gemm: expert sizes near the mean instead of random cuts")
     a = ap.parse_args()
     if a.target in ("ag_gemm", "ag_gemm_fp8"):
         a.k, a.n = a.k or 8192, a.n or 3584

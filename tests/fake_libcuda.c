@@ -1,10 +1,14 @@
 /* Stand-in for the CUDA driver's virtual-memory and multicast entry points, for tests on machines without a GPU.
  * "Device memory" is a memfd; a shareable handle is a duplicate of that descriptor; mapping is mmap.  It keeps
  * enough book-keeping (live handles, bindings, mappings) for a test to see what the code under test released.
+ * A fabric handle (type 8) is 64 bytes naming the slot; importing one works in the process that made it and in its forked
+ * children, which is what a test needs.  FAKE_CUDA_NO_FABRIC=1 makes allocations that ask for fabric handles fail, as a
+ * machine without an IMEX channel does.
  * Only what csrc/mem/cuda_device.cc resolves by name is here. */
 #define _GNU_SOURCE
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -18,6 +22,8 @@ typedef unsigned long long Handle;
 #define MAXH 256
 static struct { int fd; size_t size; int live; int is_mc; int bound; int devices; } g_h[MAXH];
 static int g_maps = 0;
+static int g_fabric_exports = 0, g_fabric_imports = 0;
+#define TYPE_FABRIC 8
 
 static int slot_new(void) {
   for (int i = 1; i < MAXH; ++i)
@@ -31,7 +37,9 @@ CUresult cuDeviceGetAttribute(int* v, int attr, CUdevice d) { (void)attr; (void)
 CUresult cuMemGetAllocationGranularity(size_t* g, const void* prop, int flags) { (void)prop; (void)flags; *g = 2u << 20; return 0; }
 
 CUresult cuMemCreate(Handle* h, size_t size, const void* prop, unsigned long long flags) {
-  (void)prop; (void)flags;
+  (void)flags;
+  /* CUmemAllocationProp starts with { int type; int requestedHandleTypes; ... } */
+  if (prop && (((const int*)prop)[1] & TYPE_FABRIC) && getenv("FAKE_CUDA_NO_FABRIC")) return 801;
   int i = slot_new();
   if (!i) return 2;
   g_h[i].fd = memfd_create("fake-cuda", MFD_CLOEXEC);
@@ -70,15 +78,34 @@ CUresult cuMemUnmap(CUdeviceptr p, size_t size) {
 }
 CUresult cuMemSetAccess(CUdeviceptr p, size_t size, const void* desc, size_t n) { (void)p; (void)size; (void)desc; (void)n; return 0; }
 CUresult cuMemExportToShareableHandle(void* out, Handle h, int type, unsigned long long flags) {
-  (void)type; (void)flags;
+  (void)flags;
   if (h == 0 || h >= MAXH || !g_h[h].live) return 1;
+  if (type == TYPE_FABRIC) {
+    memset(out, 0, 64);
+    memcpy(out, "FAKEFABR", 8);
+    memcpy((char*)out + 8, &h, sizeof(h));
+    ++g_fabric_exports;
+    return 0;
+  }
   int fd = dup(g_h[h].fd);
   if (fd < 0) return 2;
   *(int*)out = fd;
   return 0;
 }
 CUresult cuMemImportFromShareableHandle(Handle* h, void* os_handle, int type) {
-  (void)type;
+  if (type == TYPE_FABRIC) {
+    Handle src = 0;
+    if (memcmp(os_handle, "FAKEFABR", 8) != 0) return 1;
+    memcpy(&src, (const char*)os_handle + 8, sizeof(src));
+    if (src == 0 || src >= MAXH || !g_h[src].live) return 1;
+    int j = slot_new();
+    if (!j) return 2;
+    g_h[j].fd = dup(g_h[src].fd);
+    g_h[j].size = g_h[src].size;
+    *h = (Handle)j;
+    ++g_fabric_imports;
+    return 0;
+  }
   int fd = (int)(intptr_t)os_handle;
   struct stat st;
   if (fstat(fd, &st) != 0) return 1;
@@ -121,3 +148,5 @@ int fake_cuda_handle_alive(Handle h) { return h > 0 && h < MAXH && g_h[h].live; 
 int fake_cuda_handle_bound(Handle h) { return h > 0 && h < MAXH && g_h[h].live ? g_h[h].bound : -1; }
 int fake_cuda_live_handles(void) { int n = 0; for (int i = 1; i < MAXH; ++i) n += g_h[i].live; return n; }
 int fake_cuda_mappings(void) { return g_maps; }
+int fake_cuda_fabric_exports(void) { return g_fabric_exports; }
+int fake_cuda_fabric_imports(void) { return g_fabric_imports; }

@@ -24,7 +24,7 @@ def fake_driver(tmp_path_factory):
     return str(out)
 
 
-def _run(fake_driver, body, timeout=120):
+def _run(fake_driver, body, timeout=120, extra_env=None):
     code = textwrap.dedent("""
         import ctypes, json, os, sys
         sys.path.insert(0, %r)
@@ -34,7 +34,7 @@ def _run(fake_driver, body, timeout=120):
         fake.fake_cuda_handle_alive.argtypes = [ctypes.c_ulonglong]
         fake.fake_cuda_handle_bound.argtypes = [ctypes.c_ulonglong]
     """ % ROOT) + textwrap.dedent(body)
-    env = dict(os.environ, PCCL_CUDA_DRIVER_LIB=fake_driver)
+    env = dict(os.environ, PCCL_CUDA_DRIVER_LIB=fake_driver, **(extra_env or {}))
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     return json.loads(r.stdout.strip().splitlines()[-1])
@@ -117,3 +117,46 @@ def test_memory_handle_reaches_another_process_only_with_the_token_and_the_same_
         assert out["refused"] >= 3
     else:
         assert out["refused"] >= 2
+
+
+_FABRIC_BODY = """
+    import multiprocessing as mp
+    size = 2 << 20
+    ptr, handle = U.cuda_device_alloc(size)
+    ctypes.memmove(ptr, b"pccl-heap", 9)
+    doc = json.loads(handle)
+
+    def peer(handle, q):
+        try:
+            from pccl_b200._native import C as C2
+            f2 = ctypes.CDLL(os.environ["PCCL_CUDA_DRIVER_LIB"])
+            p = C2.utils.cuda_device_map(handle)
+            q.put([ctypes.string_at(p, 9).decode(), f2.fake_cuda_fabric_imports()])
+        except Exception as e:
+            q.put(["failed: " + str(e)[:120], -1])
+
+    ctx = mp.get_context("fork")
+    q = ctx.Queue()
+    p = ctx.Process(target=peer, args=(handle, q)); p.start(); got = q.get(timeout=60); p.join()
+    U.cuda_device_free(ptr)
+    print(json.dumps({"has_fabric": "fabric" in doc, "fabric_len": len(doc.get("fabric", "")), "exports": fake.fake_cuda_fabric_exports(),
+                      "peer_read": got[0], "peer_fabric_imports": got[1], "has_sock": bool(doc.get("sock"))}))
+"""
+
+
+def test_fabric_handle_travels_in_the_handle_document_when_asked_for(fake_driver):
+    """PCCL_HANDLE_TYPE=fabric: the allocation is exported as 64 opaque bytes inside the handle document and a peer maps
+    it from those, without asking the owner's descriptor server; the POSIX descriptor stays available next to it."""
+    out = _run(fake_driver, _FABRIC_BODY, extra_env={"PCCL_HANDLE_TYPE": "fabric"})
+    assert out["has_fabric"] and out["fabric_len"] == 128 and out["exports"] == 1 and out["has_sock"]
+    assert out["peer_read"] == "pccl-heap" and out["peer_fabric_imports"] == 1
+
+
+def test_fabric_request_falls_back_to_descriptors_where_the_driver_refuses(fake_driver):
+    """A driver without an IMEX channel refuses allocations that ask for fabric handles: the plugin allocates again
+    without them and peers map through the descriptor server, as they do by default."""
+    out = _run(fake_driver, _FABRIC_BODY, extra_env={"PCCL_HANDLE_TYPE": "fabric", "FAKE_CUDA_NO_FABRIC": "1"})
+    assert not out["has_fabric"] and out["exports"] == 0
+    assert out["peer_read"] == "pccl-heap" and out["peer_fabric_imports"] == 0
+    out = _run(fake_driver, _FABRIC_BODY)                      # not asked for: nothing changes
+    assert not out["has_fabric"] and out["peer_read"] == "pccl-heap"
