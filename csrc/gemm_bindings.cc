@@ -124,4 +124,5 @@ void bindGemm(py::module_& m) {
   m.attr("GEMM_BIAS") = static_cast<uint32_t>(GEMM_BIAS);
   m.attr("GEMM_PAIR") = static_cast<uint32_t>(GEMM_PAIR);
   m.attr("GEMM_ADD_D2") = static_cast<uint32_t>(GEMM_ADD_D2);
+  m.attr("GEMM_ROW_STORES") = static_cast<uint32_t>(GEMM_ROW_STORES);
 }

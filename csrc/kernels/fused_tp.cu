@@ -162,12 +162,13 @@ int launchAgGemm(AgGemmArgs& A, const AgGemmHost* host, int ctas, cudaStream_t s
   auto k00 = ag_gemm_kernel<false, false>; auto k10 = ag_gemm_kernel<true, false>;
   auto k01 = ag_gemm_kernel<false, true>;  auto k11 = ag_gemm_kernel<true, true>;
   auto kern = which == 0 ? k00 : which == 1 ? k10 : which == 2 ? k01 : k11;
+  const int smem_bytes = pair ? gemm2::SMEM_BYTES : SMEM_BYTES;      // the pair pipeline's ring and barrier area are its own
   if (!set[which]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     set[which] = true;
   }
-  if (pair) return static_cast<int>(gemm2::launch_pairs(kern, grid, NUM_THREADS, SMEM_BYTES, stream, true, A));
+  if (pair) return static_cast<int>(gemm2::launch_pairs(kern, grid, NUM_THREADS, smem_bytes, stream, true, A));
   void* args[] = {&A};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), grid, dim3(NUM_THREADS), args, SMEM_BYTES, stream));
 }

@@ -19,6 +19,8 @@ enum GemmFlags : uint32_t {
   GEMM_GELU_INPLACE = 1u << 6,  // D = gelu_tanh(A*B^T (+bias)); no separate pre-activation
   GEMM_PAIR = 1u << 7,        // CTA pairs (cta_group::2, 256 x 256 tiles) instead of single CTAs (128 x 256)
   GEMM_ADD_D2 = 1u << 8,      // D = A*B^T (+bias) + D2 (bf16, D's layout, read only): a residual connection; not with GEMM_GELU
+  GEMM_ROW_STORES = 1u << 9,  // epilogue stores straight from the accumulator layout (a row per lane) instead of through the
+                              // coalescing patch: for comparison runs
 };
 
 // D[M,N] (ldd) = A * B^T.  K-major operands: A is [M,K] with row stride lda, B is [N,K] with row

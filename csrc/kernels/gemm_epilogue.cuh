@@ -43,6 +43,50 @@ __device__ __forceinline__ void warp_transpose_sum32(float* v, int lane) {
   }
 }
 
+// ---- coalescing patch ------------------------------------------------------------------------------------------------
+// After tcgen05.ld a lane holds 32 consecutive columns of ONE row, so a 16-byte store per lane touches 32 different rows:
+// 32 half-filled 32-byte sectors per instruction.  Through a small per-warp patch of shared memory (32 rows x 64 bytes,
+// rows 80 bytes apart so that neither side has bank conflicts worth the name) the strip is turned around: four lanes cover
+// one row's 64 bytes, an instruction writes eight rows in full sectors.  Half the sector operations at the L2 for the same
+// bytes; an epilogue with two outputs (pre-activation and GELU) or a side input is bound by exactly that.
+constexpr int kPatchRowBytes = 80;
+constexpr int kPatchBytes = 32 * kPatchRowBytes;          // per epilogue warp
+constexpr int kPatchBytesPerCta = 4 * kPatchBytes;
+
+// the lane's 32 values -> bf16 -> rows [0, rows_valid) of the 32 x 32 strip at g0 (row stride ldd elements)
+__device__ __forceinline__ void patch_store_bf16(uint8_t* P, int lane, __nv_bfloat16* g0, long long ldd, const float* v, int rows_valid) {
+  uint8_t* mine = P + lane * kPatchRowBytes;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) *reinterpret_cast<dev::Vec16*>(mine + i * 16) = dev::pack<DT_BF16>(v + 8 * i);
+  __syncwarp();
+  const int chunk = lane & 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int rr = (lane >> 2) + 8 * j;
+    const dev::Vec16 x = *reinterpret_cast<const dev::Vec16*>(P + rr * kPatchRowBytes + chunk * 16);
+    if (rr < rows_valid) dev::st16(g0 + rr * ldd + chunk * 8, x);
+  }
+  __syncwarp();
+}
+
+// rows [0, rows_valid) of the 32 x 32 bf16 strip at g0 -> the lane's own row as 32 floats (rows past rows_valid: zeros)
+__device__ __forceinline__ void patch_load_bf16(uint8_t* P, int lane, const __nv_bfloat16* g0, long long ldd, float* out, int rows_valid) {
+  const int chunk = lane & 3;
+  dev::Vec16 x[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int rr = (lane >> 2) + 8 * j;
+    x[j] = rr < rows_valid ? dev::ld16(g0 + rr * ldd + chunk * 8) : dev::Vec16{{0u, 0u, 0u, 0u}};
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) *reinterpret_cast<dev::Vec16*>(P + ((lane >> 2) + 8 * j) * kPatchRowBytes + chunk * 16) = x[j];
+  __syncwarp();
+  const uint8_t* mine = P + lane * kPatchRowBytes;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) dev::unpack<DT_BF16>(*reinterpret_cast<const dev::Vec16*>(mine + i * 16), out + 8 * i);
+  __syncwarp();
+}
+
 // Backward of a GELU that sits between two linear layers, fused into the GEMM that produces the gradient of the
 // activation: D = (A * B^T) .* gelu'(pre), and the column sums of D (the bias gradient of the first layer) are added
 // to `colsum` (fp32, zeroed by the caller).  Full tiles only (M % 128 == 0, N % 256 == 0); `pre` has D's layout.
@@ -53,26 +97,58 @@ struct DgeluEpi {
   float* colsum;
   long long ldd;
   int M, N;
+  uint8_t* patch = nullptr;      // kPatchBytesPerCta of shared memory when the pipeline provides it (see above)
 
   __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.m * BM; }
   __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * BN; }
   __device__ __forceinline__ void attach_smem(uint8_t*) {}
-  __device__ __forceinline__ void tile_begin(const TileCoord&) {}
+  __device__ __forceinline__ void attach_patch(uint8_t* p) {
+    if ((ldd & 7) == 0 && ((reinterpret_cast<uintptr_t>(D) | reinterpret_cast<uintptr_t>(pre)) & 15) == 0) patch = p;
+  }
+  // The pre-activations of a strip are fetched one strip ahead (four 16-byte loads per lane, eight rows per instruction)
+  // and parked in registers: their latency passes behind the previous strip's arithmetic instead of in front of this one's.
+  dev::Vec16 ahead[4];
+  __device__ __forceinline__ void fetch_ahead(const TileCoord& t, int quarter, int lane, int col_in_tile) {
+    const __nv_bfloat16* g0 = pre + static_cast<long long>(t.m * BM + quarter * 32) * ldd + t.n * BN + col_in_tile + (lane & 3) * 8;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ahead[j] = dev::ld16(g0 + ((lane >> 2) + 8 * j) * ldd);
+  }
+  __device__ __forceinline__ void tile_begin(const TileCoord& t) {
+    if (patch) fetch_ahead(t, (threadIdx.x >> 5) & 3, threadIdx.x & 31, 0);
+  }
   __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
 
   __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
     const int row = t.m * BM + row_in_tile, col = t.n * BN + col_in_tile;
     const long long at = static_cast<long long>(row) * ldd + col;
     float v[32];
+    if (patch) {
+      const int lane = row_in_tile & 31, quarter = (row_in_tile >> 5) & 3;
+      uint8_t* P = patch + quarter * kPatchBytes;
+      const long long at0 = static_cast<long long>(row - lane) * ldd + col;
+      float x[32];
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
-      float x[8];
-      dev::unpack<DT_BF16>(dev::ld16(pre + at + i), x);
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<dev::Vec16*>(P + ((lane >> 2) + 8 * j) * kPatchRowBytes + (lane & 3) * 16) = ahead[j];
+      __syncwarp();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i + j] = __uint_as_float(r[i + j]) * dgelu_tanh(x[j]);
+      for (int i = 0; i < 4; ++i) dev::unpack<DT_BF16>(*reinterpret_cast<const dev::Vec16*>(P + lane * kPatchRowBytes + i * 16), x + 8 * i);
+      __syncwarp();
+      if (col_in_tile + 32 < BN) fetch_ahead(t, quarter, lane, col_in_tile + 32);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * dgelu_tanh(x[i]);
+      patch_store_bf16(P, lane, D + at0, ldd, v, 32);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        float x[8];
+        dev::unpack<DT_BF16>(dev::ld16(pre + at + i), x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i + j] = __uint_as_float(r[i + j]) * dgelu_tanh(x[j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) dev::st16(D + at + i, dev::pack<DT_BF16>(v + i));
     }
-#pragma unroll
-    for (int i = 0; i < 32; i += 8) dev::st16(D + at + i, dev::pack<DT_BF16>(v + i));
     if (colsum) {
       const int lane = threadIdx.x & 31;       // an epilogue warp holds 32 consecutive rows, one per lane
       warp_transpose_sum32(v, lane);
@@ -89,20 +165,72 @@ struct StoreEpi {
   long long ldd;
   int M, N;
   uint32_t flags;
+  uint8_t* patch = nullptr;      // kPatchBytesPerCta of shared memory when the pipeline provides it (see above)
 
   __device__ __forceinline__ int a_row0(const TileCoord& t) const { return t.m * BM; }
   __device__ __forceinline__ int b_row0(const TileCoord& t) const { return t.n * BN; }
   __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void attach_patch(uint8_t* p) { patch = p; }
   __device__ __forceinline__ void tile_begin(const TileCoord&) {}
   __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
 
+  // bf16 output, whole 32-column strip, through the coalescing patch: every lane of the warp takes part (rows past M are
+  // computed and dropped at the store)
+  __device__ __forceinline__ void strip_patched(int row, int col, int row_in_tile, float* v) {
+    const int lane = row_in_tile & 31;
+    uint8_t* P = patch + ((row_in_tile >> 5) & 3) * kPatchBytes;
+    const int row0 = row - lane, rows_valid = M - row0;
+    const long long at0 = static_cast<long long>(row0) * ldd + col;
+    if (flags & GEMM_BIAS) {
+      if ((reinterpret_cast<uintptr_t>(bias) & 15) == 0) {
+        float b[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) dev::unpack<DT_BF16>(dev::ld16(bias + col + i), b + i);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += b[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += __bfloat162float(bias[col + i]);
+      }
+    }
+    if (flags & GEMM_ADD_D2) {
+      float res[32];
+      patch_load_bf16(P, lane, static_cast<const __nv_bfloat16*>(D2) + at0, ldd, res, rows_valid);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] += res[i];
+    }
+    if (flags & GEMM_GELU_INPLACE) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+    }
+    if (flags & GEMM_ACCUMULATE) {
+      float old[32];
+      patch_load_bf16(P, lane, static_cast<const __nv_bfloat16*>(D) + at0, ldd, old, rows_valid);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] += old[i];
+    }
+    patch_store_bf16(P, lane, static_cast<__nv_bfloat16*>(D) + at0, ldd, v, rows_valid);
+    if (flags & GEMM_GELU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+      patch_store_bf16(P, lane, static_cast<__nv_bfloat16*>(D2) + at0, ldd, v, rows_valid);
+    }
+  }
+
   __device__ __forceinline__ void strip(const TileCoord& t, int row_in_tile, int col_in_tile, uint32_t* r) {
     const int row = t.m * BM + row_in_tile, col = t.n * BN + col_in_tile;
-    if (row >= M || col >= N) return;
+    if (col >= N) return;
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
     const bool full = col + 32 <= N;
+    // uniform over the warp: the patch needs all 32 lanes; 16-byte alignment of every row's strip comes with ldd % 8 == 0
+    if (patch && full && !(flags & (GEMM_OUT_F32 | GEMM_ROW_STORES)) && (col & 7) == 0 && row - (row_in_tile & 31) < M && (ldd & 7) == 0 &&
+        ((reinterpret_cast<uintptr_t>(D) | ((flags & (GEMM_GELU | GEMM_ADD_D2)) ? reinterpret_cast<uintptr_t>(D2) : 0)) & 15) == 0) {
+      strip_patched(row, col, row_in_tile, v);
+      return;
+    }
+    if (row >= M) return;
     if (flags & GEMM_BIAS) {
 #pragma unroll
       for (int i = 0; i < 32; ++i)

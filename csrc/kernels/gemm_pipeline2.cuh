@@ -27,7 +27,8 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 192;
 constexpr int BAR_BYTES = 512;     // barriers and the tile-index ring, between the operand ring and an epilogue's staging area
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+constexpr int PATCH_BYTES = 4 * 32 * 80;   // the epilogue warps' coalescing patches (gemm_epilogue.cuh), behind the barriers
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES + PATCH_BYTES;
 constexpr int EPI_SMEM_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;
 
 constexpr int SCHED_SLOTS = 4;     // tile indices in flight between the roles (dynamic scheduling)
@@ -52,6 +53,10 @@ static_assert(sizeof(Barriers) <= BAR_BYTES, "barriers overrun their area");
 // first tile_n / 2 rows of its B box -- and the epilogue is handed only the strips below it, so a ragged last tile costs
 // tensor time in proportion to its width.  `int b_box(const TileCoord&)` then picks one of several B descriptors (`tmB` is an
 // array) whose boxes hold 128 >> b_box rows, so a narrow tile does not fetch rows it will not multiply.
+// An epilogue with `attach_patch(uint8_t*)` is handed PATCH_BYTES of shared memory behind the barrier area (only where the
+// kernel was launched with SMEM_BYTES of this header and the epilogue's own staging, if any, does not live there).
+template <class E, class = void> struct HasPatch : std::false_type {};
+template <class E> struct HasPatch<E, std::void_t<decltype(std::declval<E&>().attach_patch(nullptr))>> : std::true_type {};
 template <class E, class = void> struct HasVarN : std::false_type {};
 template <class E> struct HasVarN<E, std::void_t<decltype(E::kVarN)>> : std::true_type {};
 
@@ -114,6 +119,7 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
   tc::tc_fence_after();
   const uint32_t tmem = bar->tmem_base;
   epi.attach_smem(smem + NSTAGES * STAGE_BYTES + BAR_BYTES);
+  if constexpr (HasPatch<Epi>::value && NSTAGES == STAGES) epi.attach_patch(smem + NSTAGES * STAGE_BYTES + BAR_BYTES);
 
   // Tile of iteration `it` for a role that READS the ring (every role but the leader's producer).  `warp_wide`: all lanes
   // of a warp call this together and lane 0 releases the slot.  Returns 1 (tile), 0 (end of the list) or -1 (gave up).
@@ -312,6 +318,9 @@ struct PairEpi {
   __device__ __forceinline__ int a_row0(const TileCoord& t) const { return e.a_row0(half_tile(t, cta)); }
   __device__ __forceinline__ int b_row0(const TileCoord& t) const { return e.b_row0(half_tile(t, cta)) + cta * HALF_N; }
   __device__ __forceinline__ void attach_smem(uint8_t* p) { e.attach_smem(p); }
+  __device__ __forceinline__ void attach_patch(uint8_t* p) {
+    if constexpr (HasPatch<Epi>::value) e.attach_patch(p);
+  }
   __device__ __forceinline__ void tile_begin(const TileCoord& t) { e.tile_begin(half_tile(t, cta)); }
   __device__ __forceinline__ void tile_done(const TileCoord& t, const volatile uint32_t* abort) { e.tile_done(half_tile(t, cta), abort); }
   __device__ __forceinline__ void strip(const TileCoord& t, int row, int col, uint32_t* r) { e.strip(half_tile(t, cta), row, col, r); }

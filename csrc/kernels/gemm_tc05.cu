@@ -96,6 +96,7 @@ struct DualEpi {
   __device__ __forceinline__ int a_row0(const TileCoord& t) const { return e[t.extra].a_row0(t); }
   __device__ __forceinline__ int b_row0(const TileCoord& t) const { return e[t.extra].b_row0(t); }
   __device__ __forceinline__ void attach_smem(uint8_t*) {}
+  __device__ __forceinline__ void attach_patch(uint8_t* p) { e[0].attach_patch(p); e[1].attach_patch(p); }
   __device__ __forceinline__ void tile_begin(const TileCoord&) {}
   __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
   __device__ __forceinline__ void strip(const TileCoord& t, int row, int col, uint32_t* r) { e[t.extra].strip(t, row, col, r); }

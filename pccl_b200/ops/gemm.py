@@ -57,12 +57,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          bias: Optional[torch.Tensor] = None, gelu_out: Optional[torch.Tensor] = None,
          accumulate: bool = False, sms: int = 0, pair: Optional[bool] = None,
-         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+         residual: Optional[torch.Tensor] = None, row_stores: bool = False) -> torch.Tensor:
     """``out = op(a) @ op(b)`` with ``op(a) = a.T if a_t else a`` (a: [M,K] or [K,M]) and
     ``op(b) = b if b_t else b.T`` (b: [N,K], or [K,N] when ``b_t``).  So the default is the linear
     layer form ``a @ b.T``.  ``bias`` (bf16 [N]) is added; ``gelu_out`` receives gelu_tanh(out).
     ``pair`` selects the CTA-pair kernel (cta_group::2, 256 x 256 tiles); default from PCCL_GEMM_PAIR.
-    ``residual`` (bf16, out's shape and strides) is added in the epilogue: ``out = a @ b.T + bias + residual``."""
+    ``residual`` (bf16, out's shape and strides) is added in the epilogue: ``out = a @ b.T + bias + residual``.
+    ``row_stores`` turns the epilogue's coalescing patch off (comparison runs)."""
     _check(a, "a")
     _check(b, "b")
     M, K = (a.shape[1], a.shape[0]) if a_t else (a.shape[0], a.shape[1])
@@ -86,6 +87,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         flags |= C.GEMM_ACCUMULATE
     if (_PAIR_DEFAULT and M > 128) if pair is None else pair:
         flags |= C.GEMM_PAIR
+    if row_stores:
+        flags |= C.GEMM_ROW_STORES
     bias_ptr = 0
     if bias is not None:
         if bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous():
