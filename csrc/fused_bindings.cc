@@ -49,7 +49,8 @@ void bindFused(py::module_& m) {
                            int hidden, int topk, int epr, uint64_t recv_q_off, uint64_t recv_s_off, uint64_t y_off, uint64_t epoch,
                            int flag_lane, const std::vector<uint64_t>& x, const std::vector<uint64_t>& ids,
                            const std::vector<uint64_t>& rows, const std::vector<uint64_t>& probs, const std::vector<uint64_t>& out,
-                           const std::vector<uint64_t>& status, int blocks, uint64_t spin_ns, uint64_t stream) {
+                           const std::vector<uint64_t>& status, int blocks, uint64_t spin_ns, uint64_t stream, uint64_t alias_off,
+                           uint64_t group_off, uint64_t z_off, const std::vector<uint64_t>& gate, bool dedupe) {
     MoeArgs a;
     if (e) {
       // barrier values come from the engine's per-lane counter, shared with every other user of the lane
@@ -59,8 +60,13 @@ void bindFused(py::module_& m) {
       a = moeArgs(emuWorld2(heaps, flag_off), static_cast<int>(heaps.size()), 0, tokens, hidden, topk, epr, recv_q_off, recv_s_off,
                   y_off, epoch, flag_lane, spin_ns);
     }
+    a.dedupe = dedupe && alias_off != 0 ? 1 : 0;
+    a.alias_off = alias_off;
+    a.group_off = group_off;
+    a.z_off = z_off;
     size_t n = e ? 1 : heaps.size();
     for (size_t r = 0; r < n; ++r) {
+      a.gate[r] = gate.empty() ? nullptr : reinterpret_cast<const float*>(gate.at(r));
       a.x[r] = x.empty() ? nullptr : reinterpret_cast<const void*>(x.at(r));
       a.expert_ids[r] = reinterpret_cast<const int*>(ids.at(r));
       a.dst_rows[r] = reinterpret_cast<const int*>(rows.at(r));
@@ -75,7 +81,8 @@ void bindFused(py::module_& m) {
   }, py::arg("kind"), py::arg("engine").none(true), py::arg("heaps"), py::arg("flag_off"), py::arg("tokens"), py::arg("hidden"),
      py::arg("topk"), py::arg("experts_per_rank"), py::arg("recv_q_off"), py::arg("recv_s_off"), py::arg("y_off"), py::arg("epoch"),
      py::arg("flag_lane"), py::arg("x"), py::arg("ids"), py::arg("rows"), py::arg("probs"), py::arg("out"), py::arg("status"),
-     py::arg("blocks"), py::arg("spin_ns"), py::arg("stream"));
+     py::arg("blocks"), py::arg("spin_ns"), py::arg("stream"), py::arg("alias_off") = 0, py::arg("group_off") = 0, py::arg("z_off") = 0,
+     py::arg("gate") = std::vector<uint64_t>{}, py::arg("dedupe") = false);
   m.def("moe_route", [](uint64_t logits, uint64_t ids, uint64_t probs, uint64_t pos, uint64_t counts, int tokens, int experts, int topk,
                         uint64_t stream) {
     check(launchMoeRoute(reinterpret_cast<const float*>(logits), reinterpret_cast<int*>(ids), reinterpret_cast<float*>(probs),
@@ -88,9 +95,17 @@ void bindFused(py::module_& m) {
                         reinterpret_cast<int*>(rows), reinterpret_cast<int*>(row_off), world, rank, experts, tokens, topk, cap,
                         reinterpret_cast<cudaStream_t>(stream)), "moe_plan");
   });
-  m.def("moe_dequant", [](uint64_t q, uint64_t s, uint64_t out, uint64_t n_rows, int max_rows, int hidden, uint64_t stream) {
+  m.def("moe_dequant", [](uint64_t q, uint64_t s, uint64_t out, uint64_t n_rows, int max_rows, int hidden, uint64_t stream, uint64_t alias) {
     check(launchMoeDequant(reinterpret_cast<const void*>(q), reinterpret_cast<const float*>(s), reinterpret_cast<void*>(out),
-                           reinterpret_cast<const int*>(n_rows), max_rows, hidden, reinterpret_cast<cudaStream_t>(stream)), "moe_dequant");
+                           reinterpret_cast<const int*>(n_rows), max_rows, hidden, reinterpret_cast<const int*>(alias),
+                           reinterpret_cast<cudaStream_t>(stream)), "moe_dequant");
+  }, py::arg("q"), py::arg("scales"), py::arg("out"), py::arg("n_rows"), py::arg("max_rows"), py::arg("hidden"), py::arg("stream"),
+     py::arg("alias") = 0);
+  m.def("moe_reduce_groups", [](uint64_t y, uint64_t z, uint64_t alias, uint64_t groups, uint64_t n_rows, int max_rows, int hidden,
+                                uint64_t stream) {
+    check(launchMoeReduceGroups(reinterpret_cast<const void*>(y), reinterpret_cast<void*>(z), reinterpret_cast<const int*>(alias),
+                                reinterpret_cast<const void*>(groups), reinterpret_cast<const int*>(n_rows), max_rows, hidden,
+                                reinterpret_cast<cudaStream_t>(stream)), "moe_reduce_groups");
   });
   m.def("quant_fp8_rows", [](uint64_t x, uint64_t q, uint64_t s, long long rows, int hidden, uint64_t stream) {
     check(launchQuantFp8Rows(reinterpret_cast<const void*>(x), reinterpret_cast<void*>(q), reinterpret_cast<float*>(s), rows, hidden,

@@ -60,9 +60,10 @@ __device__ __forceinline__ uint2 quant8(const float* f, float inv) {
 
 // Quantise one row held in global memory into shared memory (q: hidden bytes, s: hidden/128 floats).
 // 16 consecutive lanes own one 128-value block, so the block amax is a half-warp shuffle reduction.
-__device__ __forceinline__ void quant_row_to_smem(const __nv_bfloat16* x, int hidden, uint8_t* q, float* s) {
+__device__ __forceinline__ void quant_row_to_smem(const __nv_bfloat16* x, int hidden, uint8_t* q, float* s, int tid = threadIdx.x,
+                                                  int nthreads = blockDim.x) {
   const int nvec = hidden >> 3;
-  for (int v = threadIdx.x; v < ((nvec + 31) & ~31); v += blockDim.x) {     // warp-uniform trip count for the shuffles
+  for (int v = tid; v < ((nvec + 31) & ~31); v += nthreads) {     // warp-uniform trip count for the shuffles
     float f[8];
     float amax = 0.f;
     if (v < nvec) {
@@ -80,68 +81,135 @@ __device__ __forceinline__ void quant_row_to_smem(const __nv_bfloat16* x, int hi
   }
 }
 
-__global__ void __launch_bounds__(256) moe_dispatch_kernel(const __grid_constant__ MoeArgs A) {
+// A token is a chain of dependent steps (load the row, block maxima, quantise, store), a few microseconds long whatever the
+// bandwidth; one token at a time per SM leaves both HBM and NVLink idle most of the time.  So a CTA is kDispatchSubs groups
+// of 256 threads, each with its own staging row and its own named barrier, working on different tokens.
+constexpr int kDispatchSubs = 3, kCombineSubs = 2;
+__device__ __forceinline__ void sub_sync(int sub) { asm volatile("bar.sync %0, 256;" ::"r"(sub + 1) : "memory"); }
+__host__ __device__ inline size_t dispatch_stage_bytes(int hidden) { return (static_cast<size_t>(hidden) + (hidden >> 7) * 4 + 15) / 16 * 16; }
+
+__global__ void __launch_bounds__(256 * kDispatchSubs) moe_dispatch_kernel(const __grid_constant__ MoeArgs A) {
   extern __shared__ __align__(16) uint8_t dsm[];
   __shared__ uint32_t s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   const int me = A.nvirt > 1 ? static_cast<int>(blockIdx.y) : A.rank;
   const int slot = A.nvirt > 1 ? me : 0;
   const int H = A.hidden, G = H >> 7;
-  uint8_t* q = dsm;
-  float* s = reinterpret_cast<float*>(dsm + H);
+  const int sub = threadIdx.x >> 8, tid = threadIdx.x & 255;
+  uint8_t* q = dsm + sub * dispatch_stage_bytes(H);
+  float* s = reinterpret_cast<float*>(q + H);
   if (!moe_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(A.x[slot]);
   const int qvec = H >> 4, svec = (G + 3) >> 2;       // 16-byte vectors of payload / of scales
-  for (int t = blockIdx.x; t < A.tokens; t += gridDim.x) {
-    __syncthreads();                                    // the previous token's stores have read the staging row
-    quant_row_to_smem(x + static_cast<long long>(t) * H, H, q, s);
-    __syncthreads();
-    for (int k = 0; k < A.topk; ++k) {
-      const int e = A.expert_ids[slot][t * A.topk + k];
-      const long long row = A.dst_rows[slot][t * A.topk + k];
-      if (e < 0 || row < 0) continue;                   // dropped assignment (receive buffer full)
-      char* base = A.w.heap[e / A.experts_per_rank];
+  for (int t = blockIdx.x * kDispatchSubs + sub; t < A.tokens; t += gridDim.x * kDispatchSubs) {
+    sub_sync(sub);                                      // the previous token's stores have read the staging row
+    quant_row_to_smem(x + static_cast<long long>(t) * H, H, q, s, tid, 256);
+    sub_sync(sub);
+    // destination rank and row of every assignment; with de-duplication, the primary of each (first k to that rank)
+    int dest[8], prim[8];
+    long long rowk[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      dest[k] = -1; prim[k] = k; rowk[k] = -1;
+      if (k < A.topk) {
+        const int e = A.expert_ids[slot][t * A.topk + k];
+        rowk[k] = A.dst_rows[slot][t * A.topk + k];
+        if (e >= 0 && rowk[k] >= 0) dest[k] = e / A.experts_per_rank;
+      }
+    }
+    const bool dedupe = A.dedupe && A.alias_off && !A.probs[slot];      // scaled payloads differ per destination
+    if (dedupe) {
+#pragma unroll
+      for (int k = 1; k < 8; ++k)
+#pragma unroll
+        for (int j = k - 1; j >= 0; --j)
+          if (dest[k] >= 0 && dest[j] == dest[k]) prim[k] = prim[j];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (dest[k] < 0) continue;                        // dropped assignment (receive buffer full), or k >= topk
+      const long long row = rowk[k];
+      char* base = A.w.heap[dest[k]];
+      if (A.alias_off && tid == 0) reinterpret_cast<int*>(base + A.alias_off)[row] = static_cast<int>(rowk[prim[k]]);
+      if (prim[k] != k) continue;                       // the payload is already on its way to that rank
+      if (dedupe && A.group_off && tid < 16) {
+        // group record of this primary: the token's rows on that rank and their gate weights
+        const int j = tid & 7;
+        const bool member = dest[j] == dest[k] && prim[j] == k;
+        uint32_t word;
+        if (tid < 8) word = member ? static_cast<uint32_t>(rowk[j]) : 0xffffffffu;
+        else word = __float_as_uint(member && A.gate[slot] ? A.gate[slot][t * A.topk + j] : 0.f);
+        reinterpret_cast<uint32_t*>(base + A.group_off + row * 64)[tid] = word;
+      }
       char* dq = base + A.recv_q_off + row * H;
       char* ds = base + A.recv_s_off + row * G * 4;
-      for (int v = threadIdx.x; v < qvec; v += blockDim.x) st16(dq + v * 16, *reinterpret_cast<const Vec16*>(q + v * 16));
+      for (int v = tid; v < qvec; v += 256) st16(dq + v * 16, *reinterpret_cast<const Vec16*>(q + v * 16));
       // With gate weights attached, destination k receives p[t,k] * x[t] (the gradient of an expert's output row in
       // the backward pass): the e4m3 payload is the same for every destination, only the block scales are multiplied.
       const float pk = A.probs[slot] ? A.probs[slot][t * A.topk + k] : 1.0f;
-      if (threadIdx.x < svec) {
-        if ((G & 3) == 0 && !A.probs[slot]) st16(ds + threadIdx.x * 16, *reinterpret_cast<const Vec16*>(reinterpret_cast<uint8_t*>(s) + threadIdx.x * 16));
-        else for (int i = threadIdx.x * 4; i < min(G, threadIdx.x * 4 + 4); ++i) reinterpret_cast<float*>(ds)[i] = s[i] * pk;
+      if (tid < svec) {
+        if ((G & 3) == 0 && !A.probs[slot]) st16(ds + tid * 16, *reinterpret_cast<const Vec16*>(reinterpret_cast<uint8_t*>(s) + tid * 16));
+        else for (int i = tid * 4; i < min(G, tid * 4 + 4); ++i) reinterpret_cast<float*>(ds)[i] = s[i] * pk;
       }
     }
   }
   moe_barrier(A, me, 4 * A.epoch + 2, &s_fail);
 }
 
-__global__ void __launch_bounds__(256) moe_combine_kernel(const __grid_constant__ MoeArgs A) {
+// Two groups of 256 threads per CTA, each pulling a different token's rows: twice the loads in flight per SM (the register
+// budget of 16 vectors in flight per thread allows no more).
+__global__ void __launch_bounds__(256 * kCombineSubs) moe_combine_kernel(const __grid_constant__ MoeArgs A) {
   __shared__ uint32_t s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   const int me = A.nvirt > 1 ? static_cast<int>(blockIdx.y) : A.rank;
   const int slot = A.nvirt > 1 ? me : 0;
   const int H = A.hidden, nvec = H >> 3;
+  const int sub = threadIdx.x >> 8, tid = threadIdx.x & 255;
   if (!moe_barrier(A, me, 4 * A.epoch + 1, &s_fail)) return;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(A.out[slot]);
-  for (int t = blockIdx.x; t < A.tokens; t += gridDim.x) {
+  for (int t = blockIdx.x * kCombineSubs + sub; t < A.tokens; t += gridDim.x * kCombineSubs) {
     const char* src[8];
     float p[8];
+    int dest[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       src[k] = nullptr;
       p[k] = 0.f;
+      dest[k] = -1;
       if (k < A.topk) {
         const int e = A.expert_ids[slot][t * A.topk + k];
         const long long row = A.dst_rows[slot][t * A.topk + k];
         if (e >= 0 && row >= 0) {
-          src[k] = A.w.heap[e / A.experts_per_rank] + A.y_off + row * H * 2;
+          dest[k] = e / A.experts_per_rank;
+          src[k] = A.w.heap[dest[k]] + A.y_off + row * H * 2;
           p[k] = A.probs[slot][t * A.topk + k];
         }
       }
     }
-    for (int v0 = threadIdx.x; v0 < nvec; v0 += 2 * blockDim.x) {
-      const int v1 = v0 + blockDim.x;
+    if (A.dedupe && A.z_off) {
+      // one row per (token, rank): the first assignment to a rank stands for the token's whole group there; a group of two
+      // or more has been summed (with its weights) into z on that rank, a group of one is still the plain expert output
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (dest[k] < 0) continue;
+        bool first = true;
+        int size = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (dest[j] == dest[k]) {
+            ++size;
+            if (j < k) first = false;
+          }
+        }
+        if (!first) src[k] = nullptr;
+        else if (size > 1) {
+          src[k] = src[k] - A.y_off + A.z_off;
+          p[k] = 1.0f;
+        }
+      }
+    }
+    for (int v0 = tid; v0 < nvec; v0 += 2 * 256) {
+      const int v1 = v0 + 256;
       Vec16 a[8], b[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) {        // all loads first: up to 16 NVLink loads in flight per thread
@@ -235,12 +303,17 @@ __global__ void __launch_bounds__(256) moe_combine_dot_kernel(const __grid_const
 
 __global__ void __launch_bounds__(256) moe_dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scales,
                                                           __nv_bfloat16* __restrict__ out, const int* __restrict__ n_rows,
-                                                          int max_rows, int hidden) {
+                                                          int max_rows, int hidden, const int* __restrict__ alias) {
   const int rows = min(*n_rows, max_rows);
   const int nvec = hidden >> 4, G = hidden >> 7;      // 16 fp8 values per 16-byte vector
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
-    const uint8_t* qr = q + r * hidden;
-    const float* sr = scales + r * G;
+    long long from = r;
+    if (alias) {                                        // a de-duplicated row: its payload sits in the token's primary row
+      const int a = alias[r];
+      if (a >= 0 && a < max_rows) from = a;
+    }
+    const uint8_t* qr = q + from * hidden;
+    const float* sr = scales + from * G;
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
       float f[16];
       unpack<DT_FP8_E4M3>(ld16(qr + v * 16), f);
@@ -249,6 +322,47 @@ __global__ void __launch_bounds__(256) moe_dequant_kernel(const uint8_t* __restr
       for (int k = 0; k < 16; ++k) f[k] *= sc;
       st16(out + r * hidden + v * 16, pack<DT_BF16>(f));
       st16(out + r * hidden + v * 16 + 8, pack<DT_BF16>(f + 8));
+    }
+  }
+}
+
+// z[r] = sum_j weight_j * y[row_j] over the group record of primary row r, for groups of two or more (a group of one stays in y
+// and gets its weight in the combine).  Element-wise over the row, accumulated in fp32.
+__global__ void __launch_bounds__(256) moe_reduce_groups_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ z,
+                                                                const int* __restrict__ alias, const uint32_t* __restrict__ groups,
+                                                                const int* __restrict__ n_rows, int max_rows, int hidden) {
+  const int rows = min(*n_rows, max_rows);
+  const int nvec = hidden >> 3;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (alias[r] != static_cast<int>(r)) continue;
+    const uint32_t* g = groups + r * 16;
+    int member[8];
+    float w[8];
+    int size = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int m = static_cast<int>(g[j]);
+      member[j] = (m >= 0 && m < max_rows) ? m : -1;
+      w[j] = __uint_as_float(g[8 + j]);
+      size += member[j] >= 0;
+    }
+    if (size < 2) continue;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      Vec16 a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (member[j] >= 0) a[j] = ld16(y + static_cast<long long>(member[j]) * hidden + v * 8);
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (member[j] >= 0) {
+          float f[8];
+          unpack<DT_BF16>(a[j], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += w[j] * f[i];
+        }
+      }
+      st16(z + r * hidden + v * 8, pack<DT_BF16>(acc));
     }
   }
 }
@@ -567,11 +681,11 @@ __global__ void __launch_bounds__(256) moe_plan_kernel(const int* __restrict__ c
 }
 
 template <typename K>
-int coop(K kernel, const MoeArgs& a, int blocks, size_t smem, cudaStream_t stream) {
+int coop(K kernel, const MoeArgs& a, int blocks, size_t smem, cudaStream_t stream, int threads = 256) {
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocksPerColl) blocks = kMaxBlocksPerColl;
   if (a.topk > 8 || a.hidden % 128 || a.flag_lane < 0 || a.flag_lane >= 8) return static_cast<int>(cudaErrorInvalidValue);
-  dim3 grid(blocks, a.nvirt > 1 ? a.nvirt : 1), block(256);
+  dim3 grid(blocks, a.nvirt > 1 ? a.nvirt : 1), block(threads);
   void* args[] = {const_cast<MoeArgs*>(&a)};
   return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), grid, block, args, smem, stream));
 }
@@ -579,15 +693,34 @@ int coop(K kernel, const MoeArgs& a, int blocks, size_t smem, cudaStream_t strea
 }  // namespace
 
 int launchMoeDispatch(const MoeArgs& a, int blocks, cudaStream_t stream) {
-  return coop(moe_dispatch_kernel, a, blocks, static_cast<size_t>(a.hidden) + (a.hidden >> 7) * 4 + 16, stream);
+  const size_t smem = kDispatchSubs * dispatch_stage_bytes(a.hidden);
+  static size_t smem_set = 0;
+  if (smem > 48 * 1024 && smem > smem_set) {
+    cudaError_t e = cudaFuncSetAttribute(moe_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    smem_set = smem;
+  }
+  return coop(moe_dispatch_kernel, a, blocks, smem, stream, 256 * kDispatchSubs);
 }
 
-int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream) { return coop(moe_combine_kernel, a, blocks, 0, stream); }
+int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream) {
+  return coop(moe_combine_kernel, a, blocks, 0, stream, 256 * kCombineSubs);
+}
 int launchMoeCombineDot(const MoeArgs& a, int blocks, cudaStream_t stream) { return coop(moe_combine_dot_kernel, a, blocks, 0, stream); }
 
-int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, cudaStream_t stream) {
+int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, const int* alias,
+                     cudaStream_t stream) {
   if (hidden % 128) return static_cast<int>(cudaErrorInvalidValue);
-  moe_dequant_kernel<<<148 * 8, 256, 0, stream>>>(static_cast<const uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(out), n_rows, max_rows, hidden);
+  moe_dequant_kernel<<<148 * 8, 256, 0, stream>>>(static_cast<const uint8_t*>(q), scales, static_cast<__nv_bfloat16*>(out), n_rows, max_rows, hidden,
+                                                  alias);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launchMoeReduceGroups(const void* y, void* z, const int* alias, const void* groups, const int* n_rows, int max_rows, int hidden,
+                          cudaStream_t stream) {
+  if (hidden % 8 || !alias || !groups) return static_cast<int>(cudaErrorInvalidValue);
+  moe_reduce_groups_kernel<<<148 * 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(z), alias,
+                                                        static_cast<const uint32_t*>(groups), n_rows, max_rows, hidden);
   return static_cast<int>(cudaGetLastError());
 }
 

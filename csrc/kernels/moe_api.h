@@ -21,13 +21,20 @@ struct MoeArgs {
   uint64_t y_off;         // heap offset: expert outputs [cap, hidden] bf16 (read by the combine of every rank)
   uint64_t epoch;
   int flag_lane;
-  int pad;
+  int dedupe;             // 1: an assignment whose rank already receives this token through an earlier k is not sent again
   uint64_t spin_ns;
+  // De-duplicated exchange (dedupe = 1; needs the three areas below in the symmetric heap, 0 = feature off).  The FIRST of a
+  // token's assignments that goes to a rank is its primary on that rank; the others are told where the payload is.
+  uint64_t alias_off;     // int32 [cap]: row that holds the fp8 payload of row r (r itself for a primary)
+  uint64_t group_off;     // [cap] x {int32 rows[8], float weight[8]}: for a primary row, the rows of the same token on this
+                          // rank (-1 padded) with their gate weights; written by the dispatch, read by the group reduction
+  uint64_t z_off;         // bf16 [cap, hidden]: sum over a group of weight x expert output, for groups of two or more
   // per (virtual) rank local tensors
   const void* x[kMaxRanks];          // [tokens, hidden] bf16
   const int* expert_ids[kMaxRanks];  // [tokens, topk] global expert ids
   const int* dst_rows[kMaxRanks];    // [tokens, topk] row inside the destination rank's receive buffer
-  const float* probs[kMaxRanks];     // [tokens, topk] gate probabilities (combine)
+  const float* probs[kMaxRanks];     // [tokens, topk] gate probabilities (combine); dispatch: scale per destination
+  const float* gate[kMaxRanks];      // [tokens, topk] gate probabilities for the group records of a de-duplicating dispatch
   void* out[kMaxRanks];              // [tokens, hidden] bf16 (combine)
   uint32_t* status[kMaxRanks];
 };
@@ -39,8 +46,12 @@ int launchMoeDispatch(const MoeArgs& a, int blocks, cudaStream_t stream);
 int launchMoeCombineDot(const MoeArgs& a, int blocks, cudaStream_t stream);
 // out[t] = sum_k probs[t,k] * y[rank of expert (t,k)][dst_rows[t,k]]: pulls the rows over NVLink.
 int launchMoeCombine(const MoeArgs& a, int blocks, cudaStream_t stream);
-// bf16 rows from fp8 rows + scales, for rows [0, *n_rows) (device count).
-int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, cudaStream_t stream);
+// bf16 rows from fp8 rows + scales, for rows [0, *n_rows) (device count).  `alias` (or null): row r is read from alias[r].
+int launchMoeDequant(const void* q, const float* scales, void* out, const int* n_rows, int max_rows, int hidden, const int* alias,
+                     cudaStream_t stream);
+// z[r] = sum over the group of primary row r of weight x y[row], for groups of two or more rows (local; after the experts).
+int launchMoeReduceGroups(const void* y, void* z, const int* alias, const void* groups, const int* n_rows, int max_rows, int hidden,
+                          cudaStream_t stream);
 // Stand-alone block quantiser (1 x 128 blocks, e4m3 + fp32 scales).
 int launchQuantFp8Rows(const void* x, void* q, float* scales, long long rows, int hidden, cudaStream_t stream);
 // 128 x 128 block quantiser for weights [rows, cols] (both multiples of 128): e4m3 + fp32 scale per block.

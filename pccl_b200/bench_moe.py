@@ -57,9 +57,17 @@ def run(eng: Engine, tokens: int, hidden: int, d_ff: int, n_experts: int, topk: 
     out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
     t_route = _time(lambda: moe.route_and_plan(logits), iters, warmup, flush)
     t_route_torch = _time(lambda: moe.plan(MoEExchange.route(logits, topk)[0]), iters, warmup, flush)
-    t_disp = _time(lambda: moe.dispatch(x, ids, plan), iters, warmup, flush)
+    t_disp_all = _time(lambda: moe.dispatch(x, ids, plan), iters, warmup, flush)                   # one row per (token, expert)
+    t_disp = _time(lambda: moe.dispatch(x, ids, plan, gate=probs), iters, warmup, flush)          # one row per (token, rank)
     t_ffn = _time(lambda: moe.experts(w1, w2, plan), iters, warmup, flush)
-    t_comb = _time(lambda: moe.combine(ids, probs, plan, out), iters, warmup, flush)
+    t_comb_all = _time(lambda: moe.combine(ids, probs, plan, out), iters, warmup, flush)
+    t_comb = _time(lambda: moe.combine(ids, probs, plan, out, grouped=True), iters, warmup, flush) # local group sums + one pull per rank
+    # fraction of (token, expert) assignments that are the first of their token on their rank
+    dest = (ids // epr)
+    first = torch.ones_like(dest, dtype=torch.bool)
+    for k in range(1, topk):
+        first[:, k] = (dest[:, :k] != dest[:, k:k + 1]).all(dim=1)
+    unique_fraction = float(first.float().mean())
     t_total = _time(lambda: moe.forward(x, logits, w1, w2), iters, warmup, flush)
     check_status("moe")
 
@@ -125,10 +133,14 @@ def run(eng: Engine, tokens: int, hidden: int, d_ff: int, n_experts: int, topk: 
     disp_bytes = tokens * topk * (hidden + hidden // 128 * 4) * remote
     comb_bytes = tokens * topk * hidden * 2 * remote
     ffn_flops = 2.0 * n_rows * hidden * d_ff * 2
+    # the de-duplicated exchange moves one row per (token, destination rank)
+    disp_bytes *= unique_fraction
+    comb_bytes *= unique_fraction
     roof = {"dispatch_us": disp_bytes / (link_gbs * 1e9) * 1e6, "combine_us": comb_bytes / (link_gbs * 1e9) * 1e6,
             "ffn_us": ffn_flops / (peak_tflops * 1e12) * 1e6}
     return {"n_gpus": world, "tokens_per_rank": tokens, "hidden": hidden, "d_ff": d_ff, "experts": n_experts, "topk": topk,
-            "rows_received": n_rows, "ours_us": {"route_plan": t_route, "route_plan_torch_ops": t_route_torch, "dispatch_fp8": t_disp, "expert_ffn": t_ffn, "combine": t_comb,
+            "rows_received": n_rows, "ours_us": {"route_plan": t_route, "route_plan_torch_ops": t_route_torch, "dispatch_fp8": t_disp, "dispatch_fp8_every_assignment": t_disp_all, "expert_ffn": t_ffn, "combine": t_comb,
+                                                 "combine_every_assignment": t_comb_all, "rows_sent_fraction": unique_fraction,
                                                  "layer_total": t_total},
             "baseline_us": {"nccl_all_to_all_bf16": b_disp, "matmul_loop_ffn": b_ffn, "grouped_mm_ffn": b_ffn_grouped,
                             "nccl_all_to_all_back": b_comb, "sum": b_disp + b_ffn + b_comb,
@@ -155,7 +167,7 @@ def main():
     os.environ.setdefault("PCCL_WORKSPACE_MB", "64")
     eng = Engine(rank, world)
     cap_rows = 2 * args.tokens * args.topk + 256
-    eng.initEngine("cuda", heap_bytes=cap_rows * args.hidden * 3 + cap_rows * args.hidden // 32 + (1 << 30))
+    eng.initEngine("cuda", heap_bytes=cap_rows * args.hidden * 5 + cap_rows * (args.hidden // 32 + 68) + (1 << 30))   # fp8 rows, bf16 outputs, group sums
     if world > 1:
         eng.connect()
     peaks = {}

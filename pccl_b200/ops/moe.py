@@ -63,6 +63,12 @@ class MoEExchange:
         self.y = eng.symmetric_tensor((self.cap, hidden), torch.bfloat16)
         self.counts_all = eng.symmetric_tensor((eng.world, n_experts), torch.int32)
         self.x_bf16 = torch.empty((self.cap, hidden), dtype=torch.bfloat16, device="cuda")
+        # de-duplicated exchange: where a row's payload is (alias), the rows and gate weights of a token's group on this
+        # rank (64 bytes per row), and the groups' weighted sums of expert outputs
+        self.alias = eng.symmetric_tensor((self.cap,), torch.int32)
+        self.groups = eng.symmetric_tensor((self.cap, 16), torch.int32)
+        self.z = eng.symmetric_tensor((self.cap, hidden), torch.bfloat16)
+        self.alias.copy_(torch.arange(self.cap, dtype=torch.int32, device="cuda"))
         self.epoch = 0
         self.blocks = blocks or min(C.sm_count(), C.MAX_BLOCKS_PER_COLL)
         self.flag_lane = flag_lane
@@ -127,20 +133,33 @@ class MoEExchange:
         return ids, probs, {"rows": rows, "row_off": row_off, "n_rows": row_off[-1:]}
 
     # ---- kernels ----------------------------------------------------------------------------
-    def _exchange(self, kind: str, x, ids, rows, probs, out) -> None:
+    def _exchange(self, kind: str, x, ids, rows, probs, out, gate=None, dedupe: bool = False) -> None:
         self.epoch += 1
         st = status_words()
-        C.moe_exchange(kind, self.eng.raw, [], 0, self.T, self.H, self.K, self.epr, self.eng.heap_offset(self.recv_q),
-                       self.eng.heap_offset(self.recv_s), self.eng.heap_offset(self.y), self.epoch, self.flag_lane,
+        off = self.eng.heap_offset
+        C.moe_exchange(kind, self.eng.raw, [], 0, self.T, self.H, self.K, self.epr, off(self.recv_q),
+                       off(self.recv_s), off(self.y), self.epoch, self.flag_lane,
                        [x.data_ptr()] if x is not None else [], [ids.data_ptr()], [rows.data_ptr()],
                        [probs.data_ptr()] if probs is not None else [], [out.data_ptr()] if out is not None else [],
-                       [st.data_ptr()], self.blocks, 0, torch.cuda.current_stream().cuda_stream)
+                       [st.data_ptr()], self.blocks, 0, torch.cuda.current_stream().cuda_stream,
+                       alias_off=off(self.alias), group_off=off(self.groups), z_off=off(self.z),
+                       gate=[gate.data_ptr()] if gate is not None else [], dedupe=dedupe)
         count_launch()
 
-    def dispatch(self, x: torch.Tensor, ids: torch.Tensor, plan: Dict[str, torch.Tensor], probs: Optional[torch.Tensor] = None) -> None:
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor, plan: Dict[str, torch.Tensor], probs: Optional[torch.Tensor] = None,
+                 gate: Optional[torch.Tensor] = None) -> None:
         """Rows of ``x`` go to the ranks of their experts (e4m3 + block scales).  With ``probs`` destination k of token t
-        receives ``probs[t, k] * x[t]`` (how the backward pass sends gate-weighted output gradients)."""
-        self._exchange("dispatch", x, ids, plan["rows"], probs, None)
+        receives ``probs[t, k] * x[t]`` (how the backward pass sends gate-weighted output gradients).
+
+        With ``gate`` (the routing probabilities; not together with ``probs``) a token crosses NVLink once per destination
+        RANK instead of once per expert: the first of its assignments to a rank carries the row, the others are told
+        where it is (``received`` / ``experts`` copy it locally while they convert to bf16), and the rank gets the list of
+        the token's rows with their gate weights, which ``combine(..., grouped=True)`` needs."""
+        if gate is not None and probs is not None:
+            raise ValueError("MoEExchange.dispatch: gate (de-duplicated rows) and probs (scaled rows) exclude one another")
+        if gate is not None and (gate.dtype != torch.float32 or gate.shape != ids.shape or not gate.is_contiguous()):
+            raise ValueError("MoEExchange.dispatch: gate must be a contiguous fp32 [tokens, topk] tensor")
+        self._exchange("dispatch", x, ids, plan["rows"], probs, None, gate=gate, dedupe=gate is not None)
 
     def received(self, plan: Dict[str, torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The rows that the last dispatch delivered to this rank, as bf16 [cap, hidden] (rows past the plan's count are
@@ -148,7 +167,7 @@ class MoEExchange:
         if out is None:
             out = torch.empty((self.cap, self.H), dtype=torch.bfloat16, device="cuda")
         C.moe_dequant(self.recv_q.data_ptr(), self.recv_s.data_ptr(), out.data_ptr(), plan["n_rows"].data_ptr(), self.cap,
-                      self.H, torch.cuda.current_stream().cuda_stream)
+                      self.H, torch.cuda.current_stream().cuda_stream, alias=self.alias.data_ptr())
         count_launch()
         return out
 
@@ -162,20 +181,29 @@ class MoEExchange:
     def experts(self, w1: torch.Tensor, w2: torch.Tensor, plan: Dict[str, torch.Tensor]) -> None:
         """w1: [experts_per_rank * d_ff, hidden], w2: [experts_per_rank * hidden, d_ff]; result in self.y."""
         C.moe_dequant(self.recv_q.data_ptr(), self.recv_s.data_ptr(), self.x_bf16.data_ptr(), plan["n_rows"].data_ptr(), self.cap,
-                      self.H, torch.cuda.current_stream().cuda_stream)
+                      self.H, torch.cuda.current_stream().cuda_stream, alias=self.alias.data_ptr())
         count_launch()
         d_ff = w1.shape[0] // self.epr
         h = grouped_gemm(self.x_bf16, w1, plan["row_off"], d_ff, gelu=True)
         grouped_gemm(h, w2, plan["row_off"], self.H, out=self.y)
 
-    def combine(self, ids: torch.Tensor, probs: torch.Tensor, plan: Dict[str, torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def combine(self, ids: torch.Tensor, probs: torch.Tensor, plan: Dict[str, torch.Tensor], out: Optional[torch.Tensor] = None,
+                grouped: bool = False) -> torch.Tensor:
+        """``out[t] = sum_k probs[t, k] * (expert output of assignment (t, k))``, the rows pulled over NVLink.
+
+        ``grouped`` (after a dispatch with ``gate=probs``): every rank first adds up, locally, the weighted outputs of
+        the assignments that one token has on it, and the token then pulls one row per rank instead of one per expert."""
         if out is None:
             out = torch.empty((self.T, self.H), dtype=torch.bfloat16, device="cuda")
-        self._exchange("combine", None, ids, plan["rows"], probs, out)
+        if grouped:
+            C.moe_reduce_groups(self.y.data_ptr(), self.z.data_ptr(), self.alias.data_ptr(), self.groups.data_ptr(),
+                                plan["n_rows"].data_ptr(), self.cap, self.H, torch.cuda.current_stream().cuda_stream)
+            count_launch()
+        self._exchange("combine", None, ids, plan["rows"], probs, out, dedupe=grouped)
         return out
 
     def forward(self, x: torch.Tensor, gate_logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
         ids, probs, plan = self.route_and_plan(gate_logits)
-        self.dispatch(x, ids, plan)
+        self.dispatch(x, ids, plan, gate=probs)
         self.experts(w1, w2, plan)
-        return self.combine(ids, probs, plan)
+        return self.combine(ids, probs, plan, grouped=True)

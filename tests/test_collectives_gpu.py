@@ -558,6 +558,89 @@ def test_moe_dispatch_combine_emulated(native):
         assert (outs[r].float() - ref).abs().max().item() < 0.05
 
 
+def test_moe_deduplicated_exchange_emulated(native):
+    """Two emulated ranks, four assignments per token over four experts: most tokens have several assignments on one
+    rank.  The dispatch sends the row once per rank and tells the others where it is; the conversion to bf16 fills every
+    row; the ranks add up each token's weighted expert outputs locally and the combine pulls one row per rank."""
+    world, T, H, Kt, epr = 2, 64, 256, 4, 2
+    cap = 1024
+    G = H // 128
+    q_off = DATA_OFF
+    s_off = q_off + cap * H
+    y_off = s_off + cap * G * 4
+    alias_off = y_off + cap * H * 2
+    group_off = alias_off + cap * 4
+    z_off = group_off + cap * 64
+    heaps = [torch.zeros(z_off + cap * H * 2, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    st = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    g = torch.Generator(device="cuda").manual_seed(15)
+    xs = [(torch.randn(T, H, generator=g, device="cuda") * 2).bfloat16() for _ in range(world)]
+    ids = [torch.randint(0, world * epr, (T, Kt), generator=g, device="cuda", dtype=torch.int32) for _ in range(world)]
+    ids[0][3, 1] = -1                                   # a dropped assignment takes no part in any group
+    rows = [(torch.arange(T * Kt, device="cuda", dtype=torch.int32) + r * T * Kt).view(T, Kt).contiguous() for r in range(world)]
+    probs = [torch.rand(T, Kt, generator=g, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(T, H, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    hp = [h.data_ptr() for h in heaps]
+    native.moe_exchange("dispatch", None, hp, FLAG_OFF, T, H, Kt, epr, q_off, s_off, y_off, 1, 0,
+                        [x.data_ptr() for x in xs], [i.data_ptr() for i in ids], [r.data_ptr() for r in rows], [], [],
+                        [s.data_ptr() for s in st], 8, 0, stream, alias_off=alias_off, group_off=group_off, z_off=z_off,
+                        gate=[p.data_ptr() for p in probs], dedupe=True)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st)
+    from pccl_b200.ops.moe import quant_fp8_rows
+    n_rows = torch.tensor([world * T * Kt], dtype=torch.int32, device="cuda")
+    sent = skipped = 0
+    xb = []
+    for d in range(world):
+        out = torch.zeros(cap, H, dtype=torch.bfloat16, device="cuda")
+        native.moe_dequant(heaps[d].data_ptr() + q_off, heaps[d].data_ptr() + s_off, out.data_ptr(), n_rows.data_ptr(), cap, H, stream,
+                           alias=heaps[d].data_ptr() + alias_off)
+        xb.append(out)
+    torch.cuda.synchronize()
+    for r in range(world):
+        q_ref, s_ref = quant_fp8_rows(xs[r])
+        deq = (q_ref.view(torch.float8_e4m3fn).float().view(T, G, 128) * s_ref.view(T, G, 1)).view(T, H).bfloat16()
+        for t in range(T):
+            seen = set()
+            for k in range(Kt):
+                e = int(ids[r][t, k])
+                if e < 0:
+                    continue
+                d, row = e // epr, int(rows[r][t, k])
+                payload = heaps[d][q_off + row * H: q_off + (row + 1) * H]
+                if d in seen:
+                    skipped += 1
+                    assert not payload.any()                      # never sent
+                else:
+                    sent += 1
+                    assert torch.equal(payload, q_ref[t])
+                seen.add(d)
+                assert torch.equal(xb[d][row], deq[t]), (r, t, k)   # every row is there after the conversion
+    assert skipped > T and sent > T
+    ys = []
+    for d in range(world):
+        y = heaps[d][y_off:y_off + cap * H * 2].view(torch.bfloat16).view(cap, H)
+        y.copy_((torch.randn(cap, H, generator=g, device="cuda")).bfloat16())
+        ys.append(y)
+        native.moe_reduce_groups(heaps[d].data_ptr() + y_off, heaps[d].data_ptr() + z_off, heaps[d].data_ptr() + alias_off,
+                                 heaps[d].data_ptr() + group_off, n_rows.data_ptr(), cap, H, stream)
+    native.moe_exchange("combine", None, hp, FLAG_OFF, T, H, Kt, epr, q_off, s_off, y_off, 2, 0,
+                        [], [i.data_ptr() for i in ids], [r.data_ptr() for r in rows], [p.data_ptr() for p in probs],
+                        [o.data_ptr() for o in outs], [s.data_ptr() for s in st], 8, 0, stream, alias_off=alias_off,
+                        group_off=group_off, z_off=z_off, dedupe=True)
+    torch.cuda.synchronize()
+    assert all(s[0].item() == 0 for s in st)
+    for r in range(world):
+        ref = torch.zeros(T, H, device="cuda")
+        for t in range(T):
+            for k in range(Kt):
+                e = int(ids[r][t, k])
+                if e >= 0:
+                    ref[t] += probs[r][t, k] * ys[e // epr][int(rows[r][t, k])].float()
+        assert (outs[r].float() - ref).abs().max().item() < 0.06, r
+
+
 def test_moe_layer_world_of_one_matches_dense_reference(native):
     from pccl_b200.engine import Engine
     from pccl_b200.ops import check_status
