@@ -72,6 +72,22 @@ def test_every_algorithm_verifies_and_lowers(name, n):
     assert verify(again).ok and lower(again) == low
 
 
+@pytest.mark.parametrize("name", ["direct_allreduce", "direct_reduce_scatter", "direct_allgather"])
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+def test_pull_forms_use_no_scratch_and_stand_between_two_barriers(name, n):
+    """``direct=True``: peers' inputs are read and peers' outputs written in place.  No scratch at all, every stream begins
+    and ends with a barrier (inputs complete / every remote access over), the program verifies and lowers deadlock-free."""
+    ir = build(name, n, channels=2, direct=True)
+    assert ir.buffers["scratch"] == 0 and ir.name.endswith(("_pull", "_sym"))
+    assert verify(ir).ok
+    low = lower(ir)
+    assert check_lowered_deadlock_free(low)
+    ops = list(ir.ops.values())
+    barriers = [op for op in ops if op.op_type == PrimitiveOpType.BARRIER]
+    assert len(barriers) == 2 * 2 * n                  # entry and exit, per channel, per rank
+    assert not any(getattr(c, "buffer", "") == "scratch" for op in ops for c in (op.src_chunk, op.tgt_chunk) if c is not None)
+
+
 def test_verifier_catches_double_count_missing_data_and_races():
     ir = build("direct_reduce_scatter", 2)
     # reduce the same contribution twice
