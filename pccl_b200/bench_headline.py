@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, List
+from typing import Optional, Dict, List
 
 import torch
 import torch.distributed as dist
@@ -74,7 +74,7 @@ def _peaks() -> Dict:
 
 
 def fused_tp_block(eng: Engine, tokens: int = 8192, d_model: int = 8192, d_ff: int = 28672, iters: int = 8, warmup: int = 3,
-                   n_copy: int = 16, pieces: int = 4, link_gbs: float = 770.0) -> List[Dict]:
+                   n_copy: Optional[int] = None, pieces: int = 4, link_gbs: float = 770.0) -> List[Dict]:
     world, rank = eng.world, eng.rank
     pk = _peaks()
     peak_tflops = float(pk.get("bf16_tflops", 1590.0))

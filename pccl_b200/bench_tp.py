@@ -12,13 +12,14 @@ from __future__ import annotations
 import argparse
 import json
 import os
+from typing import Optional
 
 import torch
 import torch.distributed as dist
 
 from .engine import Engine
 from .ops import check_status
-from .ops.fused_tp import AllGatherGemm, AllGatherGemmFp8, GemmReduceScatter, GemmReduceScatterFp8
+from .ops.fused_tp import AllGatherGemm, AllGatherGemmFp8, GemmReduceScatter, GemmReduceScatterFp8, default_copy_ctas
 from .ops.gemm import gemm, gemm_fp8, quant_blocks, quant_rows
 from .utils import L2Flusher
 
@@ -42,7 +43,7 @@ def _time(fn, iters, warmup, flush):
     return float(t.item()) * 1e3      # microseconds
 
 
-def run(eng: Engine, tokens: int, d_model: int, d_ff: int, iters: int = 20, warmup: int = 5, n_copy: int = 16,
+def run(eng: Engine, tokens: int, d_model: int, d_ff: int, iters: int = 20, warmup: int = 5, n_copy: Optional[int] = None,
         peak_tflops: float = 1701.7, link_gbs: float = 770.0, fp8: bool = True):
     world, rank = eng.world, eng.rank
     n1 = d_ff // world
@@ -126,6 +127,7 @@ def _scaled_mm_us(a_q, b_q, iters, warmup, flush):
 
 def run_fp8(eng, tokens, d_model, d_ff, x_local, w1, w2, h, iters, warmup, n_copy, link_gbs, flush):
     """Block-scaled fp8 (1x128 activations, 128x128 weights) forms of the two fused paths."""
+    n_copy = n_copy or default_copy_ctas(eng.world)
     world = eng.world
     n1 = d_ff // world
     m_local = tokens // world
@@ -275,7 +277,7 @@ def main():
     ap.add_argument("--d-model", type=int, default=8192)
     ap.add_argument("--d-ff", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--n-copy", type=int, default=16)
+    ap.add_argument("--n-copy", type=int, default=0, help="copy CTAs of the fused all-gather (0 = the default for this world size)")
     ap.add_argument("--no-fp8", action="store_true")
     ap.add_argument("--probe", action="store_true", help="after the timed runs, one launch of each bf16 fused kernel with the "
                     "in-kernel wait-time probes on; prints where the CTAs waited")
@@ -295,10 +297,10 @@ def main():
             peaks = json.load(f)
     except OSError:
         pass
-    rows = run(eng, args.tokens, args.d_model, args.d_ff, iters=args.iters, n_copy=args.n_copy,
+    rows = run(eng, args.tokens, args.d_model, args.d_ff, iters=args.iters, n_copy=args.n_copy or None,
                peak_tflops=float(peaks.get("bf16_tflops", 1590.0)), fp8=not args.no_fp8)
     if args.probe:
-        rows += probe_fused(eng, args.tokens, args.d_model, args.d_ff, args.n_copy)
+        rows += probe_fused(eng, args.tokens, args.d_model, args.d_ff, args.n_copy or None)
     if rank == 0:
         for r in rows:
             print(json.dumps(r), flush=True)
