@@ -295,6 +295,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("LL_LANE_BYTES") = kLlLaneBytes;
   m.attr("LL_MAX_BYTES") = kLlMaxBytes;
   m.def("emu_program", &emuProgram);
+  m.def("interp_set_fusion", [](int mask) { throwIfCuda(setInterpreterFusion(mask), "interp_set_fusion"); });
   m.def("wait_timeout_probe", [](uint64_t flag, uint64_t spin_limit, uint64_t status, uint64_t stream) {
     throwIfCuda(launchWaitTimeoutProbe(reinterpret_cast<uint64_t*>(flag), spin_limit, reinterpret_cast<uint32_t*>(status),
                                        reinterpret_cast<cudaStream_t>(stream)), "wait_timeout_probe");

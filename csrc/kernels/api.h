@@ -80,6 +80,8 @@ struct InterpLaunch {
 
 // grid = (max n_streams, nvirt); cooperative launch.  Returns a cudaError_t as int.
 int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream);
+// Foldings of COPY instructions in the interpreter kernel (bit 0: copy + reduces, bit 1: one source, many destinations); default 3.
+int setInterpreterFusion(int mask);
 // ---- resident interpreter: launches queued by the host, taken by a kernel that stays on the GPU ----------------------
 struct alignas(16) ResidentDesc { // what InterpLaunch carries, for this rank only; copied with 16-byte vector loads
   World w;

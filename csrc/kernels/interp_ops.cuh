@@ -82,6 +82,72 @@ __device__ __forceinline__ void reduce_n_range_f(char* dst, char* const* src, in
   }
 }
 
+// dst = src[0] (op) src[1] ... (op) src[k-1] without reading dst: "COPY a -> d; REDUCE b -> d; REDUCE c -> d" as one pass.
+// 16-byte aligned ranges, 2 <= k <= kMaxFused.
+template <uint32_t DT, uint32_t OP>
+__device__ __forceinline__ void reduce_n_from_f(char* dst, char* const* src, int k, uint64_t bytes) {
+  constexpr int N = Lanes<DT>::n;
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  const uint64_t nvec = bytes >> 4;
+  for (uint64_t i = tid; i < nvec; i += nt) {
+    Vec16 v[kMaxFused];
+#pragma unroll
+    for (int s = 0; s < kMaxFused; ++s)
+      if (s < k) v[s] = ld16(src[s] + (i << 4));
+    float acc[N];
+    unpack<DT>(v[0], acc);
+#pragma unroll
+    for (int s = 1; s < kMaxFused; ++s) {
+      if (s < k) {
+        float f[N];
+        unpack<DT>(v[s], f);
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] = red1<OP>(acc[e], f[e]);
+      }
+    }
+    st16(dst + (i << 4), pack<DT>(acc));
+  }
+}
+
+template <uint32_t OP>
+__device__ __forceinline__ bool reduce_n_from_dispatch(uint32_t dt, char* dst, char* const* src, int k, uint64_t bytes) {
+  switch (dt) {
+    case DT_F32: reduce_n_from_f<DT_F32, OP>(dst, src, k, bytes); return true;
+    case DT_BF16: reduce_n_from_f<DT_BF16, OP>(dst, src, k, bytes); return true;
+    case DT_F16: reduce_n_from_f<DT_F16, OP>(dst, src, k, bytes); return true;
+    default: return false;
+  }
+}
+
+// One source, n destinations ("COPY a -> d0; COPY a -> d1; ..."): the source is read once, four vectors in flight.
+// 16-byte aligned ranges.
+__device__ __forceinline__ void copy_fan_range(char* const* dst, int n, const char* src, uint64_t bytes) {
+  const uint32_t tid = threadIdx.x, nt = blockDim.x;
+  const uint64_t nvec = bytes >> 4;
+  uint64_t i = tid;
+  for (; i + 3ull * nt < nvec; i += 4ull * nt) {
+    const Vec16 a = ld16(src + (i << 4)), b = ld16(src + ((i + nt) << 4));
+    const Vec16 c = ld16(src + ((i + 2ull * nt) << 4)), d = ld16(src + ((i + 3ull * nt) << 4));
+#pragma unroll
+    for (int q = 0; q < kMaxFused; ++q) {
+      if (q < n) {
+        st16(dst[q] + (i << 4), a);
+        st16(dst[q] + ((i + nt) << 4), b);
+        st16(dst[q] + ((i + 2ull * nt) << 4), c);
+        st16(dst[q] + ((i + 3ull * nt) << 4), d);
+      }
+    }
+  }
+  for (; i < nvec; i += nt) {
+    const Vec16 a = ld16(src + (i << 4));
+#pragma unroll
+    for (int q = 0; q < kMaxFused; ++q)
+      if (q < n) st16(dst[q] + (i << 4), a);
+  }
+  for (uint64_t b = (nvec << 4) + tid; b < bytes; b += nt)
+    for (int q = 0; q < n; ++q) dst[q][b] = src[b];
+}
+
 template <uint32_t OP>
 __device__ __forceinline__ bool reduce_n_dispatch(uint32_t dt, char* dst, char* const* src, int k, uint64_t bytes) {
   switch (dt) {

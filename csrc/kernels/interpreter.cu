@@ -25,6 +25,10 @@ using namespace iops;
 
 namespace {
 
+// Which of the COPY foldings are on: bit 0 "copy + reduces as one pass", bit 1 "one source to several destinations"
+// (setInterpreterFusion; the tests switch them off to compare).
+__device__ int g_copy_fusion = 3;
+
 // One CTA runs stream `stream` of rank R.  LaunchT is InterpLaunch (a kernel argument) or ResidentDesc (a queued launch
 // read from memory): both carry the world table and the per-launch scalars under the same names.
 template <class LaunchT>
@@ -114,36 +118,72 @@ __device__ __forceinline__ void interp_body(const LaunchT& L, const InterpRank& 
           char* s = resolve(in.src_rank, in.src_buf, in.src_off);
           char* d = resolve(in.dst_rank, in.dst_buf, in.dst_off);
           if (!s || !d) { fail = ST_UNSUPPORTED; break; }
-          if (in.op == OP_COPY) {
-            if (s != d) copy_range(d, s, in.bytes);
-          } else {
-            // Fold the reduces that follow into this one when they have the same destination ("WAIT; REDUCE" pairs: the
-            // waits are taken first, which only delays this stream): one pass over the destination instead of one per source.
-            char* srcs[kMaxFused];
-            srcs[0] = s;
-            int k = 1;
-            uint32_t j = pc + 1;
-            const bool fusable = !trace && (L.dtype == DT_F32 || L.dtype == DT_BF16 || L.dtype == DT_F16) &&
-                                 ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | in.bytes) & 15) == 0;
-            while (fusable && k < kMaxFused && !fail) {
-              const uint32_t idx = j - chunk_base;
-              if (idx + 1 >= kChunk) break;                      // look only inside the chunk that is in shared memory
-              const Instr& a = s_prog[idx];
-              const bool waits = a.op == OP_WAIT && s_prog[idx + 1].op == OP_REDUCE;
-              if (!waits && a.op != OP_REDUCE) break;
-              const Instr& r = waits ? s_prog[idx + 1] : a;
-              if (r.dst_rank != in.dst_rank || r.dst_buf != in.dst_buf || r.dst_off != in.dst_off || r.bytes != in.bytes) break;
-              if (L.bounds_check && r.src_off + r.bytes > R.buf_bytes[r.src_buf]) break;      // left to the plain path, which reports it
-              char* sp = resolve(r.src_rank, r.src_buf, r.src_off);
-              if (!sp || (reinterpret_cast<uintptr_t>(sp) & 15)) break;
-              if (waits) {
-                if (threadIdx.x == 0 && !wait_ge(my_sig + a.slot, L.epoch * a.count + a.value, L.spin_limit, R.status)) s_fail = ST_TIMEOUT;
-                __syncthreads();
-                if (s_fail) { fail = s_fail; pc = j; break; }
-              }
-              srcs[k++] = sp;
-              j += waits ? 2 : 1;
+          // Folding of what follows into this instruction (all inside the chunk that is in shared memory; "WAIT; REDUCE"
+          // pairs count, their waits are taken first, which only delays this stream):
+          //   REDUCE ... -> d, REDUCE ... -> d            one pass over d instead of one per source
+          //   COPY a -> d, REDUCE ... -> d, ...           the same without reading d at all (the pull forms)
+          //   COPY a -> d0, COPY a -> d1, ...             a is read once (a rank's slice going out to every peer)
+          const bool fusable = !trace && (L.dtype == DT_F32 || L.dtype == DT_BF16 || L.dtype == DT_F16) &&
+                               ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | in.bytes) & 15) == 0;
+          char* srcs[kMaxFused];
+          srcs[0] = s;
+          int k = 1;
+          uint32_t j = pc + 1;
+          while (fusable && k < kMaxFused && !fail && (in.op == OP_REDUCE || (s != d && (g_copy_fusion & 1)))) {
+            const uint32_t idx = j - chunk_base;
+            if (idx + 1 >= kChunk) break;
+            const Instr& a = s_prog[idx];
+            const bool waits = a.op == OP_WAIT && s_prog[idx + 1].op == OP_REDUCE;
+            if (!waits && a.op != OP_REDUCE) break;
+            const Instr& r = waits ? s_prog[idx + 1] : a;
+            if (r.dst_rank != in.dst_rank || r.dst_buf != in.dst_buf || r.dst_off != in.dst_off || r.bytes != in.bytes) break;
+            if (L.bounds_check && r.src_off + r.bytes > R.buf_bytes[r.src_buf]) break;      // left to the plain path, which reports it
+            char* sp = resolve(r.src_rank, r.src_buf, r.src_off);
+            if (!sp || (reinterpret_cast<uintptr_t>(sp) & 15)) break;
+            if (waits) {
+              if (threadIdx.x == 0 && !wait_ge(my_sig + a.slot, L.epoch * a.count + a.value, L.spin_limit, R.status)) s_fail = ST_TIMEOUT;
+              __syncthreads();
+              if (s_fail) { fail = s_fail; pc = j; break; }
             }
+            srcs[k++] = sp;
+            j += waits ? 2 : 1;
+          }
+          if (fail) break;
+          if (in.op == OP_COPY) {
+            if (k > 1) {                                          // copy + reduces: d = srcs[0] (op) srcs[1] ...
+              bool ok = false;
+              switch (L.redop) {
+                case RED_SUM: ok = reduce_n_from_dispatch<RED_SUM>(L.dtype, d, srcs, k, in.bytes); break;
+                case RED_MAX: ok = reduce_n_from_dispatch<RED_MAX>(L.dtype, d, srcs, k, in.bytes); break;
+                case RED_MIN: ok = reduce_n_from_dispatch<RED_MIN>(L.dtype, d, srcs, k, in.bytes); break;
+                case RED_PROD: ok = reduce_n_from_dispatch<RED_PROD>(L.dtype, d, srcs, k, in.bytes); break;
+              }
+              if (!ok) fail = ST_UNSUPPORTED;
+              pc = j - 1;
+              break;
+            }
+            // the same source to several destinations
+            char* dsts[kMaxFused];
+            dsts[0] = d;
+            int n = 1;
+            while (fusable && s != d && n < kMaxFused && (g_copy_fusion & 2)) {
+              const uint32_t idx = j - chunk_base;
+              if (idx >= kChunk) break;
+              const Instr& c = s_prog[idx];
+              if (c.op != OP_COPY || c.src_rank != in.src_rank || c.src_buf != in.src_buf || c.src_off != in.src_off || c.bytes != in.bytes) break;
+              if (L.bounds_check && c.dst_off + c.bytes > R.buf_bytes[c.dst_buf]) break;
+              char* dp = resolve(c.dst_rank, c.dst_buf, c.dst_off);
+              if (!dp || dp == s || (reinterpret_cast<uintptr_t>(dp) & 15)) break;
+              dsts[n++] = dp;
+              ++j;
+            }
+            if (n > 1) {
+              copy_fan_range(dsts, n, s, in.bytes);
+              pc = j - 1;
+            } else if (s != d) {
+              copy_range(d, s, in.bytes);
+            }
+          } else {
             if (fail) break;
             bool ok = false;
             if (k > 1) {
@@ -337,6 +377,10 @@ __global__ void wait_timeout_probe_kernel(uint64_t* flag, uint64_t spin_limit, u
 }
 
 }  // namespace
+
+int setInterpreterFusion(int mask) {
+  return static_cast<int>(cudaMemcpyToSymbol(g_copy_fusion, &mask, sizeof(int)));
+}
 
 int launchInterpreter(const InterpLaunch& L, int threads, cudaStream_t stream) {
   int max_streams = 0;

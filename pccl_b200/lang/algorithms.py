@@ -196,8 +196,9 @@ def direct_reduce_scatter(n: int, channels: int = 1, device_type=DeviceType.CUDA
                  for r in range(n)] if direct else [])
         last = []
         for d in range(n):
+            # (pull form: behind the barrier, so that the executor can take "copy, reduce, reduce, ..." as one pass)
             acc = ir.copy(Chunk({d}, d, 1, d * sh + ch, "input"),
-                          Chunk({d}, d, 1, ch, "output", origin=d * sh + ch), step=0, channel=ch)
+                          Chunk({d}, d, 1, ch, "output", origin=d * sh + ch), deps=bars, step=0, channel=ch)
             have = {d}
             for k in range(1, n):
                 r = (d + k) % n     # rotate so that the n ranks never all target one peer
@@ -273,7 +274,7 @@ def direct_allreduce(n: int, channels: int = 1, device_type=DeviceType.CUDA, red
         stores = []
         for d in range(n):
             u = d * sh + ch
-            acc = ir.copy(Chunk({d}, d, 1, u, "input"), Chunk({d}, d, 1, u, "output"), step=0, channel=ch)
+            acc = ir.copy(Chunk({d}, d, 1, u, "input"), Chunk({d}, d, 1, u, "output"), deps=bars, step=0, channel=ch)
             have = {d}
             for k in range(1, n):
                 r = (d + k) % n
