@@ -89,7 +89,39 @@ __device__ __forceinline__ void reduce_n_from_f(char* dst, char* const* src, int
   constexpr int N = Lanes<DT>::n;
   const uint32_t tid = threadIdx.x, nt = blockDim.x;
   const uint64_t nvec = bytes >> 4;
-  for (uint64_t i = tid; i < nvec; i += nt) {
+  uint64_t i = tid;
+  if (k <= 4) {
+    // few sources (a small world): two vectors per source in flight, or the peers' links are not kept busy
+    for (; i + nt < nvec; i += 2ull * nt) {
+      Vec16 v[4], w[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        if (s < k) {
+          v[s] = ld16(src[s] + (i << 4));
+          w[s] = ld16(src[s] + ((i + nt) << 4));
+        }
+      }
+      float acc[N], bcc[N];
+      unpack<DT>(v[0], acc);
+      unpack<DT>(w[0], bcc);
+#pragma unroll
+      for (int s = 1; s < 4; ++s) {
+        if (s < k) {
+          float f[N], g[N];
+          unpack<DT>(v[s], f);
+          unpack<DT>(w[s], g);
+#pragma unroll
+          for (int e = 0; e < N; ++e) {
+            acc[e] = red1<OP>(acc[e], f[e]);
+            bcc[e] = red1<OP>(bcc[e], g[e]);
+          }
+        }
+      }
+      st16(dst + (i << 4), pack<DT>(acc));
+      st16(dst + ((i + nt) << 4), pack<DT>(bcc));
+    }
+  }
+  for (; i < nvec; i += nt) {
     Vec16 v[kMaxFused];
 #pragma unroll
     for (int s = 0; s < kMaxFused; ++s)

@@ -159,6 +159,14 @@ __device__ __forceinline__ void interp_body(const LaunchT& L, const InterpRank& 
                 case RED_PROD: ok = reduce_n_from_dispatch<RED_PROD>(L.dtype, d, srcs, k, in.bytes); break;
               }
               if (!ok) fail = ST_UNSUPPORTED;
+              // The destination was written without having been read first, and the next instruction usually reads it (the
+              // reduced slice going out to the peers).  Measured on B200: without a fence between the two, that read now and
+              // then returned what the destination held BEFORE the stores, 64 bytes at a time, on the first launch of a
+              // process (found by the emulated-rank test of the staged all-reduce; a __threadfence() alone, or a
+              // __syncthreads() alone, removed it in every run).  The n-ary REDUCE and the plain REDUCE load the destination
+              // before they store to it and have never shown this.  One fence and one barrier per folded instruction.
+              __threadfence();
+              __syncthreads();
               pc = j - 1;
               break;
             }
@@ -179,9 +187,12 @@ __device__ __forceinline__ void interp_body(const LaunchT& L, const InterpRank& 
             }
             if (n > 1) {
               copy_fan_range(dsts, n, s, in.bytes);
+              __threadfence();                                    // see the note at the copy + reduce folding above
+              __syncthreads();
               pc = j - 1;
             } else if (s != d) {
               copy_range(d, s, in.bytes);
+              __threadfence_block();                              // a later instruction of this stream may read d (same note)
             }
           } else {
             if (fail) break;
