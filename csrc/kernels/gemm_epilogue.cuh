@@ -53,7 +53,9 @@ __device__ __forceinline__ void warp_transpose_sum32(float* v, int lane) {
 // bytes; an epilogue with two outputs (pre-activation and GELU) or a side input is bound by exactly that.
 constexpr int kPatchRowBytes = 80;
 constexpr int kPatchBytes = 32 * kPatchRowBytes;          // per epilogue warp
-constexpr int kPatchBytesPerCta = 4 * kPatchBytes;
+constexpr int kPatchBytesPerCta = 8 * kPatchBytes;       // up to eight epilogue warps
+// the calling epilogue warp's patch: warps 2, 3, ... of the CTA are the epilogue warps
+__device__ __forceinline__ uint8_t* my_patch(uint8_t* base) { return base + (((threadIdx.x >> 5) - 2) & 7) * kPatchBytes; }
 
 // the lane's 32 values -> bf16 -> rows [0, rows_valid) of the 32 x 32 strip at g0 (row stride ldd elements)
 __device__ __forceinline__ void patch_store_bf16(uint8_t* P, int lane, __nv_bfloat16* g0, long long ldd, const float* v, int rows_valid) {
@@ -115,8 +117,10 @@ struct DgeluEpi {
 #pragma unroll
     for (int j = 0; j < 4; ++j) ahead[j] = dev::ld16(g0 + ((lane >> 2) + 8 * j) * ldd);
   }
+  // columns that one epilogue warp walks through: the whole tile, or half of it where two warps share a lane quarter
+  __device__ __forceinline__ int span() const { return blockDim.x > 192 ? BN / 2 : BN; }
   __device__ __forceinline__ void tile_begin(const TileCoord& t) {
-    if (patch) fetch_ahead(t, (threadIdx.x >> 5) & 3, threadIdx.x & 31, 0);
+    if (patch) fetch_ahead(t, (threadIdx.x >> 5) & 3, threadIdx.x & 31, (((threadIdx.x >> 5) - 2) >> 2) * span());
   }
   __device__ __forceinline__ void tile_done(const TileCoord&, const volatile uint32_t*) {}
 
@@ -126,7 +130,7 @@ struct DgeluEpi {
     float v[32];
     if (patch) {
       const int lane = row_in_tile & 31, quarter = (row_in_tile >> 5) & 3;
-      uint8_t* P = patch + quarter * kPatchBytes;
+      uint8_t* P = my_patch(patch);
       const long long at0 = static_cast<long long>(row - lane) * ldd + col;
       float x[32];
 #pragma unroll
@@ -136,7 +140,7 @@ struct DgeluEpi {
 #pragma unroll
       for (int i = 0; i < 4; ++i) dev::unpack<DT_BF16>(*reinterpret_cast<const dev::Vec16*>(P + lane * kPatchRowBytes + i * 16), x + 8 * i);
       __syncwarp();
-      if (col_in_tile + 32 < BN) fetch_ahead(t, quarter, lane, col_in_tile + 32);
+      if (((col_in_tile + 32) & (span() - 1)) != 0) fetch_ahead(t, quarter, lane, col_in_tile + 32);
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * dgelu_tanh(x[i]);
       patch_store_bf16(P, lane, D + at0, ldd, v, 32);
@@ -180,7 +184,7 @@ struct StoreEpi {
   // computed and dropped at the store)
   __device__ __forceinline__ void strip_patched(int row, int col, int row_in_tile, float* v) {
     const int lane = row_in_tile & 31;
-    uint8_t* P = patch + ((row_in_tile >> 5) & 3) * kPatchBytes;
+    uint8_t* P = my_patch(patch);
     const int row0 = row - lane, rows_valid = M - row0;
     const long long at0 = static_cast<long long>(row0) * ldd + col;
     if (flags & GEMM_BIAS) {

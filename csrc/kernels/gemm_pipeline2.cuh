@@ -25,9 +25,11 @@ constexpr int PAIR_M = 256, BN = 256, HALF_N = 128, BK = 64, UMMA_K = 16;
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KiB
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 192;            // producer warp, MMA warp, four epilogue warps
+constexpr int NUM_THREADS_WIDE = 320;       // ... or eight epilogue warps (run<..., EPI_WARPS = 8>): two per TMEM lane quarter, each
+                                            // taking half of a tile's strips, for epilogues that are bound by their own latency
 constexpr int BAR_BYTES = 512;     // barriers and the tile-index ring, between the operand ring and an epilogue's staging area
-constexpr int PATCH_BYTES = 4 * 32 * 80;   // the epilogue warps' coalescing patches (gemm_epilogue.cuh), behind the barriers
+constexpr int PATCH_BYTES = 8 * 32 * 80;   // the (up to eight) epilogue warps' coalescing patches (gemm_epilogue.cuh), behind the barriers
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES + PATCH_BYTES;
 constexpr int EPI_SMEM_OFFSET = STAGES * STAGE_BYTES + BAR_BYTES;
 
@@ -73,10 +75,11 @@ template <class E> struct HasVarN<E, std::void_t<decltype(E::kVarN)>> : std::tru
 // peer's producer, the MMA thread, the eight epilogue warps) read it from there, so all of them walk the same tile list in
 // the same order.  A CTA pair that starts late -- its SMs were still held by another kernel, a collective on a second
 // stream for instance -- then simply takes fewer tiles, where the round-robin list would make the whole GEMM wait for it.
-template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES, int NPROB = 1, bool DYN = false>
+template <bool A_MN, bool B_MN, class Sched, class Gate, class Epi, int NSTAGES = STAGES, int NPROB = 1, bool DYN = false, int EPI_WARPS = 4>
 __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* tmB, int K, const Sched& sched,
                                     const Gate& gate, Epi& epi, uint32_t* status) {
   static_assert(NSTAGES >= 2 && NSTAGES <= STAGES, "ring length");
+  static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "epilogue warps per CTA");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   Barriers* bar = reinterpret_cast<Barriers*>(smem + NSTAGES * STAGE_BYTES);
@@ -93,12 +96,12 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(&bar->tmem_full[a], 1);
-      tc::mbar_init(&bar->tmem_empty[a], 8);      // four epilogue warps in each CTA of the pair
+      tc::mbar_init(&bar->tmem_empty[a], 2 * EPI_WARPS);      // the epilogue warps of both CTAs of the pair
     }
     tc::mbar_init(&bar->drain, 1);
     for (int q = 0; q < SCHED_SLOTS; ++q) {
       tc::mbar_init(&bar->sched_full[q], 1);
-      tc::mbar_init(&bar->sched_empty[q], 10);    // MMA thread + peer's producer + four epilogue warps in each CTA
+      tc::mbar_init(&bar->sched_empty[q], 2 + 2 * EPI_WARPS);    // MMA thread + peer's producer + the epilogue warps of both CTAs
       tc::mbar_init(&bar->inbox_full[q], 1);
     }
     bar->abort = 0;
@@ -281,8 +284,12 @@ __device__ __forceinline__ void run(const CUtensorMap* tmA, const CUtensorMap* t
       epi.tile_begin(t);
       int n_strips = BN / 32;
       if constexpr (HasVarN<Epi>::value) n_strips = (epi.tile_n(t) + 31) / 32;
+      // with eight epilogue warps the two warps of a lane quarter take the lower and the upper half of the strips
+      constexpr int kSplit = EPI_WARPS / 4;
+      const int per = (n_strips + kSplit - 1) / kSplit;
+      const int c_begin = ((warp - 2) >> 2) * per, c_end = c_begin + per < n_strips ? c_begin + per : n_strips;
 #pragma unroll 1
-      for (int c = 0; c < n_strips; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         tc::tmem_ld_32x32(taddr + c * 32, r);
         tc::tmem_ld_wait();

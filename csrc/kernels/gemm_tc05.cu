@@ -50,7 +50,7 @@ struct DynGroupedSched {
 };
 
 template <bool A_MN, bool B_MN, class Epi = StoreEpi, bool DYN = false>
-__global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
+__global__ void __launch_bounds__(gemm2::NUM_THREADS_WIDE, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi epi, int K,
                       uint32_t* status, uint32_t* counter) {
   const int tiles_m = (epi.M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, tiles_n = (epi.N + gemm2::BN - 1) / gemm2::BN;
@@ -60,10 +60,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   gemm2::PairGate<NoGate> pg{gate, cta};
   if constexpr (DYN) {
     DynGroupedSched sched{tiles_m, tiles_n, counter, static_cast<uint32_t>(tiles_m * tiles_n)};
-    gemm2::run<A_MN, B_MN, DynGroupedSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<Epi>, gemm2::STAGES, 1, true>(&tmA, &tmB, K, sched, pg, pe, status);
+    gemm2::run<A_MN, B_MN, DynGroupedSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<Epi>, gemm2::STAGES, 1, true, 8>(&tmA, &tmB, K, sched, pg, pe, status);
   } else {
     GroupedSched sched{tiles_m, tiles_n, static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1)};
-    gemm2::run<A_MN, B_MN>(&tmA, &tmB, K, sched, pg, pe, status);
+    gemm2::run<A_MN, B_MN, GroupedSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<Epi>, gemm2::STAGES, 1, false, 8>(&tmA, &tmB, K, sched, pg, pe, status);
   }
 }
 
@@ -103,7 +103,7 @@ struct DualEpi {
 };
 
 template <bool A_MN, bool B_MN, bool DYN>
-__global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
+__global__ void __launch_bounds__(gemm2::NUM_THREADS_WIDE, 1)
 gemm_bf16_pair_dual_kernel(const __grid_constant__ DualMaps maps, DualEpi epi, int K, uint32_t* status, uint32_t* counter) {
   DualSched sched{{(epi.e[0].M + gemm2::PAIR_M - 1) / gemm2::PAIR_M, (epi.e[1].M + gemm2::PAIR_M - 1) / gemm2::PAIR_M},
                   {(epi.e[0].N + gemm2::BN - 1) / gemm2::BN, (epi.e[1].N + gemm2::BN - 1) / gemm2::BN},
@@ -113,7 +113,7 @@ gemm_bf16_pair_dual_kernel(const __grid_constant__ DualMaps maps, DualEpi epi, i
   const int cta = static_cast<int>(tc::cluster_ctarank());
   gemm2::PairEpi<DualEpi> pe{epi, cta};
   gemm2::PairGate<NoGate> pg{gate, cta};
-  gemm2::run<A_MN, B_MN, DualSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<DualEpi>, gemm2::STAGES, 2, DYN>(maps.a, maps.b, K, sched, pg, pe, status);
+  gemm2::run<A_MN, B_MN, DualSched, gemm2::PairGate<NoGate>, gemm2::PairEpi<DualEpi>, gemm2::STAGES, 2, DYN, 8>(maps.a, maps.b, K, sched, pg, pe, status);
 }
 
 thread_local std::string g_err;
@@ -168,7 +168,7 @@ int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, int
     if (int e = setPairSmem(kern, &attr_set_dyn)) return e;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(gemm2::NUM_THREADS);
+    cfg.blockDim = dim3(gemm2::NUM_THREADS_WIDE);
     cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
@@ -189,7 +189,7 @@ int launchPair(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, int
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(gemm2::NUM_THREADS);
+  cfg.blockDim = dim3(gemm2::NUM_THREADS_WIDE);
   cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute at[1];
@@ -323,7 +323,7 @@ int gemmBf16Dual(const GemmProblem& p0, const GemmProblem& p1, int K, uint32_t f
     if (int e = setPairSmem(kern, &attr)) return e;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(gemm2::NUM_THREADS);
+    cfg.blockDim = dim3(gemm2::NUM_THREADS_WIDE);
     cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
