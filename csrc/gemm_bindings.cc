@@ -33,6 +33,7 @@ void bindGemm(py::module_& m) {
           if (err != 0) throw std::runtime_error(std::string("gemm_bf16_dgelu: ") + cudaErrorName(err) + " " + gemmLastError());
         });
   m.def("gemm_set_dynamic", &gemmSetDynamic);
+  m.def("gemm_reset_tile_counters", &gemmResetTileCounters);
   m.def("gemm_bf16_dual",
         [](uint64_t a0, int64_t lda0, uint64_t b0, int64_t ldb0, uint64_t d0, int64_t ldd0, int M0, int N0, bool acc0, uint64_t a1, int64_t lda1,
            uint64_t b1, int64_t ldb1, uint64_t d1, int64_t ldd1, int M1, int N1, bool acc1, int K, uint32_t flags, int sms, uint64_t status,

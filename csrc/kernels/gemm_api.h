@@ -80,5 +80,9 @@ const char* gemmLastError();
 // Tile scheduling of the CTA-pair kernels: 1 = tiles are handed out at run time (an atomic counter per stream), 0 = fixed
 // round-robin lists, -1 = what the environment says (PCCL_GEMM_DYNAMIC, default 1).
 void gemmSetDynamic(int mode);
+// Zeroes this device's tile counters (after a device synchronisation).  A launch leaves its counter at zero by itself; one
+// that gave up on a bounded wait does not, and every later launch on that stream would skip tiles.  The Python status check
+// calls this whenever it finds a failure recorded.
+int gemmResetTileCounters();
 
 }  // namespace pccl

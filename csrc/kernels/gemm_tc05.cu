@@ -122,17 +122,19 @@ thread_local std::string g_err;
 // the other, and each leaves the word zeroed).  One 128-byte line per stream out of a pool made on first use; a null
 // pointer (pool used up, or PCCL_GEMM_DYNAMIC=0) selects the round-robin kernels.
 int g_dynamic = -1;      // -1: PCCL_GEMM_DYNAMIC decides (default on); 0 / 1: set by gemmSetDynamic
+std::mutex g_counter_mu;
+std::map<int, std::pair<uint32_t*, int>> g_counter_pools;      // device -> (base, lines handed out)
+constexpr int kCounterPool = 64, kCounterStride = 32;          // lines per device, words per line
 
 uint32_t* tileCounterFor(cudaStream_t stream) {
   static const bool env_off = std::getenv("PCCL_GEMM_DYNAMIC") && std::getenv("PCCL_GEMM_DYNAMIC")[0] == '0';
   if (g_dynamic == 0 || (g_dynamic < 0 && env_off)) return nullptr;
-  constexpr int kPool = 64, kStride = 32;          // words
-  static std::mutex mu;
+  constexpr int kPool = kCounterPool, kStride = kCounterStride;
   static std::map<std::pair<int, cudaStream_t>, uint32_t*> by_stream;
-  static std::map<int, std::pair<uint32_t*, int>> pools;      // device -> (base, used)
+  auto& pools = g_counter_pools;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  std::lock_guard<std::mutex> g(mu);
+  std::lock_guard<std::mutex> g(g_counter_mu);
   auto it = by_stream.find({dev, stream});
   if (it != by_stream.end()) return it->second;
   auto& pool = pools[dev];
@@ -221,6 +223,16 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreEpi& epi, in
 const char* gemmLastError() { return g_err.c_str(); }
 
 void gemmSetDynamic(int mode) { g_dynamic = mode < 0 ? -1 : (mode ? 1 : 0); }
+
+int gemmResetTileCounters() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  std::lock_guard<std::mutex> g(g_counter_mu);
+  auto it = g_counter_pools.find(dev);
+  if (it == g_counter_pools.end() || !it->second.first) return 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(cudaMemset(it->second.first, 0, kCounterPool * kCounterStride * sizeof(uint32_t)));
+}
 
 int gemmBf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldd, int M, int N, int K,
              uint32_t flags, const void* bias, void* D2, int sms, uint32_t* status, cudaStream_t stream) {

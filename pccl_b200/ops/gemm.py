@@ -33,6 +33,7 @@ def check_status(what: str = "kernel") -> None:
     vals = st[:4].tolist()
     if vals[0] != 0:
         st.zero_()
+        C.gemm_reset_tile_counters()      # a GEMM that gave up leaves its run-time tile counter where it was
         raise RuntimeError(f"{what}: device status {vals} (1 = bounded wait timed out)")
 
 
