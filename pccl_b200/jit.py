@@ -119,7 +119,10 @@ def generate(streams: List[List[Tuple]], rank: int, world: int, dtype: str, redo
             if op == OP["COPY"]:
                 body.append(f"{{ char* d = {_addr(dst_rank, rank, dst_buf, dst_off)}; const char* sp = {_addr(src_rank, rank, src_buf, src_off)};")
                 body.append(f"  if (!d || !sp) {{ if (threadIdx.x == 0) report(a.status, ST_UNSUPPORTED, {s}u, {pc}u, OP_COPY); return; }}")
-                body.append(f"  if (d != sp) copy_range(d, sp, {nbytes}ull); }}")
+                # fence + barrier: a later instruction of this stream may read d, which was stored to without having been
+                # loaded first (the interpreter kernel's note on folded copies says what was seen without them)
+                body.append(f"  if (d != sp) {{ copy_range(d, sp, {nbytes}ull); __threadfence(); }} }}")
+                body.append("__syncthreads();")
                 pc += 1
             elif op == OP["REDUCE"]:
                 # fold the "WAIT; REDUCE" pairs and plain REDUCEs that follow with the same destination
