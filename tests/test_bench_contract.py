@@ -76,3 +76,10 @@ def test_clock_sampler_reads_a_stand_in_for_nvidia_smi(tmp_path, monkeypatch):
     # without the tool the sampler stays silent instead of failing the benchmark
     monkeypatch.setenv("PATH", str(tmp_path / "nowhere"))
     assert ClockSampler(0).start().stop()["sm_mhz"] is None
+
+
+def test_copy_cta_default_of_the_fused_all_gather_follows_the_world_size():
+    """Measured choice: 8 copy CTAs on up to four GPUs, 16 on eight (an even number either way: CTA pairs copy as a cluster)."""
+    from pccl_b200.ops.fused_tp import default_copy_ctas
+    assert [default_copy_ctas(w) for w in (2, 4, 8)] == [8, 8, 16]
+    assert all(default_copy_ctas(w) % 2 == 0 for w in range(2, 17))
